@@ -1,0 +1,331 @@
+// Memory-bound elementwise kernels for sm_100a: SwiGLU, GELU, RoPE, masked softmax,
+// residual add, 2-D transpose.  All use 16-byte vector accesses where the shape allows
+// and fp32 math with bf16/fp16/fp32 storage.
+//
+// Behaviour covered (reference files): silu(a) * g (src/scaling/core/nn/mlp.py:249),
+// exact-erf GELU (src/scaling/core/nn/mlp.py:139), rotary embeddings in rotate-half and
+// interleaved-pair ("complex") form with position ids and partial rotary dimensions
+// (src/scaling/core/nn/rotary.py:117-139, 68-90), softmax(masked_fill(x*scale, mask, -10000))
+// (src/scaling/core/nn/masked_softmax/masked_softmax.py:14-34).
+#include "common.cuh"
+
+namespace {
+
+__device__ __forceinline__ float silu_f(float x) { return x / (1.f + __expf(-x)); }
+__device__ __forceinline__ float sigmoid_f(float x) { return 1.f / (1.f + __expf(-x)); }
+__device__ __forceinline__ float gelu_f(float x) { return 0.5f * x * (1.f + erff(x * 0.70710678118654752f)); }
+__device__ __forceinline__ float gelu_grad_f(float x) {
+  const float kInvSqrt2Pi = 0.3989422804014327f;
+  float cdf = 0.5f * (1.f + erff(x * 0.70710678118654752f));
+  return cdf + x * kInvSqrt2Pi * __expf(-0.5f * x * x);
+}
+
+// ------------------------------------------------------------------- SwiGLU
+// out[m, f] = silu(a[m, f]) * g[m, f]; a, g, out may be column blocks of wider rows.
+template <typename T>
+__global__ void swiglu_fwd_kernel(const T* __restrict__ a, const T* __restrict__ g, T* __restrict__ out, long M, int F,
+                                  long lda, long ldg, long ldo, float act_scale) {
+  constexpr int V = sb::Vec16<T>::N;
+  const int fv = F / V;
+  long total = M * fv;
+  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
+    long m = i / fv;
+    int c = (int)(i - m * fv) * V;
+    auto av = sb::ld16(a + m * lda + c);
+    auto gv = sb::ld16(g + m * ldg + c);
+    sb::Vec16<T> o;
+#pragma unroll
+    for (int k = 0; k < V; ++k) o.e[k] = sb::from_f<T>(silu_f(sb::to_f(av.e[k])) * sb::to_f(gv.e[k]) * act_scale);
+    sb::st16(out + m * ldo + c, o);
+  }
+}
+template <typename T>
+__global__ void swiglu_bwd_kernel(const T* __restrict__ dout, const T* __restrict__ a, const T* __restrict__ g,
+                                  T* __restrict__ da, T* __restrict__ dg, long M, int F, long lddo, long lda, long ldg,
+                                  long ldda, long lddg, float act_scale) {
+  constexpr int V = sb::Vec16<T>::N;
+  const int fv = F / V;
+  long total = M * fv;
+  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
+    long m = i / fv;
+    int c = (int)(i - m * fv) * V;
+    auto dv = sb::ld16(dout + m * lddo + c);
+    auto av = sb::ld16(a + m * lda + c);
+    auto gv = sb::ld16(g + m * ldg + c);
+    sb::Vec16<T> oa, og;
+#pragma unroll
+    for (int k = 0; k < V; ++k) {
+      float x = sb::to_f(av.e[k]), gg = sb::to_f(gv.e[k]), d = sb::to_f(dv.e[k]) * act_scale;
+      float s = sigmoid_f(x);
+      float sl = x * s;
+      oa.e[k] = sb::from_f<T>(d * gg * (s + sl * (1.f - s)));
+      og.e[k] = sb::from_f<T>(d * sl);
+    }
+    sb::st16(da + m * ldda + c, oa);
+    sb::st16(dg + m * lddg + c, og);
+  }
+}
+
+// --------------------------------------------------------------------- GELU
+template <typename T>
+__global__ void gelu_fwd_kernel(const T* __restrict__ x, T* __restrict__ y, long n) {
+  constexpr int V = sb::Vec16<T>::N;
+  long nv = n / V;
+  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < nv; i += (long)gridDim.x * blockDim.x) {
+    auto v = sb::ld16(x + i * V);
+    sb::Vec16<T> o;
+#pragma unroll
+    for (int k = 0; k < V; ++k) o.e[k] = sb::from_f<T>(gelu_f(sb::to_f(v.e[k])));
+    sb::st16(y + i * V, o);
+  }
+  // tail
+  for (long i = nv * V + blockIdx.x * (long)blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x)
+    y[i] = sb::from_f<T>(gelu_f(sb::to_f(x[i])));
+}
+template <typename T>
+__global__ void gelu_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, T* __restrict__ dx, long n) {
+  constexpr int V = sb::Vec16<T>::N;
+  long nv = n / V;
+  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < nv; i += (long)gridDim.x * blockDim.x) {
+    auto v = sb::ld16(x + i * V);
+    auto d = sb::ld16(dy + i * V);
+    sb::Vec16<T> o;
+#pragma unroll
+    for (int k = 0; k < V; ++k) o.e[k] = sb::from_f<T>(sb::to_f(d.e[k]) * gelu_grad_f(sb::to_f(v.e[k])));
+    sb::st16(dx + i * V, o);
+  }
+  for (long i = nv * V + blockIdx.x * (long)blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x)
+    dx[i] = sb::from_f<T>(sb::to_f(dy[i]) * gelu_grad_f(sb::to_f(x[i])));
+}
+
+// --------------------------------------------------------------- residual add
+template <typename T>
+__global__ void add_kernel(const T* __restrict__ a, const T* __restrict__ b, T* __restrict__ y, long n) {
+  constexpr int V = sb::Vec16<T>::N;
+  long nv = n / V;
+  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < nv; i += (long)gridDim.x * blockDim.x) {
+    auto av = sb::ld16(a + i * V);
+    auto bv = sb::ld16(b + i * V);
+    sb::Vec16<T> o;
+#pragma unroll
+    for (int k = 0; k < V; ++k) o.e[k] = sb::from_f<T>(sb::to_f(av.e[k]) + sb::to_f(bv.e[k]));
+    sb::st16(y + i * V, o);
+  }
+  for (long i = nv * V + blockIdx.x * (long)blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x)
+    y[i] = sb::from_f<T>(sb::to_f(a[i]) + sb::to_f(b[i]));
+}
+
+// --------------------------------------------------------------------- RoPE
+// In place on x[t, h, d] (token stride ld_tok, head stride ld_head).  One CTA per token;
+// each thread owns one rotary pair index i and walks the heads, so sin/cos are computed
+// once per (token, i).  mode 0: pairs (i, i + rot/2) ("rotate half"); mode 1: pairs (2i, 2i+1).
+// sign = +1 forward, -1 backward (the transpose of a rotation is the rotation by -theta).
+template <typename T>
+__global__ void rope_kernel(T* __restrict__ x, const int* __restrict__ pos, int T_tokens, int n_heads, int rot_dim,
+                            long ld_tok, long ld_head, float log2_base, int mode, float sign) {
+  int t = blockIdx.x;
+  if (t >= T_tokens) return;
+  int half = rot_dim >> 1;
+  float p = (float)pos[t];
+  for (int i = threadIdx.x; i < half; i += blockDim.x) {
+    float inv_freq = exp2f(-log2_base * (2.f * i) / (float)rot_dim);
+    float sn, cs;
+    sincosf(p * inv_freq, &sn, &cs);
+    sn *= sign;
+    int i0 = mode == 0 ? i : 2 * i;
+    int i1 = mode == 0 ? i + half : 2 * i + 1;
+    T* base = x + (long)t * ld_tok;
+    for (int h = threadIdx.y; h < n_heads; h += blockDim.y) {
+      T* xh = base + h * ld_head;
+      float a = sb::to_f(xh[i0]), b = sb::to_f(xh[i1]);
+      xh[i0] = sb::from_f<T>(a * cs - b * sn);
+      xh[i1] = sb::from_f<T>(b * cs + a * sn);
+    }
+  }
+}
+
+// ----------------------------------------------------------- masked softmax
+// x: [rows, cols]; mask (uint8, 1 = masked) addressed as mask[(row / rows_per_mask_div) ...]:
+// row r of x uses mask row  (r / (heads * sq)) * sq + (r % sq)  when the mask is [b, 1, sq, sk].
+template <typename T>
+__global__ void masked_softmax_fwd_kernel(const T* __restrict__ x, const uint8_t* __restrict__ mask, T* __restrict__ y,
+                                          long rows, int cols, int heads, int sq, float scale) {
+  __shared__ float red[33];
+  long r = blockIdx.x;
+  if (r >= rows) return;
+  const T* xr = x + r * cols;
+  T* yr = y + r * cols;
+  const uint8_t* mr = nullptr;
+  if (mask) {
+    long b = r / ((long)heads * sq);
+    long q = r % sq;
+    mr = mask + (b * sq + q) * cols;
+  }
+  float mx = -INFINITY;
+  for (int c = threadIdx.x; c < cols; c += blockDim.x) {
+    float v = sb::to_f(xr[c]) * scale;
+    if (mr && mr[c]) v = -10000.f;
+    mx = fmaxf(mx, v);
+  }
+  mx = sb::block_max(mx, red);
+  float s = 0.f;
+  for (int c = threadIdx.x; c < cols; c += blockDim.x) {
+    float v = sb::to_f(xr[c]) * scale;
+    if (mr && mr[c]) v = -10000.f;
+    s += __expf(v - mx);
+  }
+  s = sb::block_sum(s, red);
+  float inv = 1.f / s;
+  for (int c = threadIdx.x; c < cols; c += blockDim.x) {
+    float v = sb::to_f(xr[c]) * scale;
+    if (mr && mr[c]) v = -10000.f;
+    yr[c] = sb::from_f<T>(__expf(v - mx) * inv);
+  }
+}
+// dx = scale * y * (dy - sum(dy * y)); masked positions receive zero gradient.
+template <typename T>
+__global__ void masked_softmax_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ y,
+                                          const uint8_t* __restrict__ mask, T* __restrict__ dx, long rows, int cols,
+                                          int heads, int sq, float scale) {
+  __shared__ float red[33];
+  long r = blockIdx.x;
+  if (r >= rows) return;
+  const T* yr = y + r * cols;
+  const T* dyr = dy + r * cols;
+  T* dxr = dx + r * cols;
+  const uint8_t* mr = nullptr;
+  if (mask) {
+    long b = r / ((long)heads * sq);
+    long q = r % sq;
+    mr = mask + (b * sq + q) * cols;
+  }
+  float s = 0.f;
+  for (int c = threadIdx.x; c < cols; c += blockDim.x) s += sb::to_f(dyr[c]) * sb::to_f(yr[c]);
+  s = sb::block_sum(s, red);
+  for (int c = threadIdx.x; c < cols; c += blockDim.x) {
+    float g = scale * sb::to_f(yr[c]) * (sb::to_f(dyr[c]) - s);
+    if (mr && mr[c]) g = 0.f;
+    dxr[c] = sb::from_f<T>(g);
+  }
+}
+
+// ------------------------------------------------------------------ transpose
+// out[c, r] = in[r, c] for a row-major [R, C] matrix (32x32 tiles through shared memory).
+template <typename T>
+__global__ void transpose_kernel(const T* __restrict__ in, T* __restrict__ out, int R, int C) {
+  __shared__ T tile[32][33];
+  int c0 = blockIdx.x * 32, r0 = blockIdx.y * 32;
+  for (int j = threadIdx.y; j < 32; j += blockDim.y) {
+    int r = r0 + j, c = c0 + threadIdx.x;
+    if (r < R && c < C) tile[j][threadIdx.x] = in[(size_t)r * C + c];
+  }
+  __syncthreads();
+  for (int j = threadIdx.y; j < 32; j += blockDim.y) {
+    int c = c0 + j, r = r0 + threadIdx.x;
+    if (r < R && c < C) out[(size_t)c * R + r] = tile[threadIdx.x][j];
+  }
+}
+
+inline int grid_for(long work, int threads, int max_blocks = 148 * 16) {
+  long b = (work + threads - 1) / threads;
+  if (b > max_blocks) b = max_blocks;
+  if (b < 1) b = 1;
+  return (int)b;
+}
+
+}  // namespace
+
+SB_API int sb200_swiglu_fwd(const void* a, const void* g, void* out, long M, int F, long lda, long ldg, long ldo,
+                            float act_scale, int dtype, cudaStream_t stream) {
+  if (M <= 0 || F <= 0) return SB_OK;
+  SB_DISPATCH_DTYPE(dtype, T, {
+    constexpr int V = sb::Vec16<T>::N;
+    if (F % V || lda % V || ldg % V || ldo % V) return SB_ERR_BAD_ARG;
+    swiglu_fwd_kernel<T><<<grid_for(M * (F / V), 256), 256, 0, stream>>>((const T*)a, (const T*)g, (T*)out, M, F, lda,
+                                                                           ldg, ldo, act_scale);
+  });
+  SB_CHECK_LAUNCH();
+  return SB_OK;
+}
+SB_API int sb200_swiglu_bwd(const void* dout, const void* a, const void* g, void* da, void* dg, long M, int F, long lddo,
+                            long lda, long ldg, long ldda, long lddg, float act_scale, int dtype, cudaStream_t stream) {
+  if (M <= 0 || F <= 0) return SB_OK;
+  SB_DISPATCH_DTYPE(dtype, T, {
+    constexpr int V = sb::Vec16<T>::N;
+    if (F % V || lda % V || ldg % V || lddo % V || ldda % V || lddg % V) return SB_ERR_BAD_ARG;
+    swiglu_bwd_kernel<T><<<grid_for(M * (F / V), 256), 256, 0, stream>>>(
+        (const T*)dout, (const T*)a, (const T*)g, (T*)da, (T*)dg, M, F, lddo, lda, ldg, ldda, lddg, act_scale);
+  });
+  SB_CHECK_LAUNCH();
+  return SB_OK;
+}
+SB_API int sb200_gelu_fwd(const void* x, void* y, long n, int dtype, cudaStream_t stream) {
+  if (n <= 0) return SB_OK;
+  SB_DISPATCH_DTYPE(dtype, T, {
+    gelu_fwd_kernel<T><<<grid_for(n / sb::Vec16<T>::N + 1, 256), 256, 0, stream>>>((const T*)x, (T*)y, n);
+  });
+  SB_CHECK_LAUNCH();
+  return SB_OK;
+}
+SB_API int sb200_gelu_bwd(const void* dy, const void* x, void* dx, long n, int dtype, cudaStream_t stream) {
+  if (n <= 0) return SB_OK;
+  SB_DISPATCH_DTYPE(dtype, T, {
+    gelu_bwd_kernel<T><<<grid_for(n / sb::Vec16<T>::N + 1, 256), 256, 0, stream>>>((const T*)dy, (const T*)x, (T*)dx,
+                                                                                     n);
+  });
+  SB_CHECK_LAUNCH();
+  return SB_OK;
+}
+SB_API int sb200_add(const void* a, const void* b, void* y, long n, int dtype, cudaStream_t stream) {
+  if (n <= 0) return SB_OK;
+  SB_DISPATCH_DTYPE(dtype, T, {
+    add_kernel<T><<<grid_for(n / sb::Vec16<T>::N + 1, 256), 256, 0, stream>>>((const T*)a, (const T*)b, (T*)y, n);
+  });
+  SB_CHECK_LAUNCH();
+  return SB_OK;
+}
+SB_API int sb200_rope(void* x, const int* pos, int tokens, int n_heads, int rot_dim, long ld_tok, long ld_head,
+                      float base, int mode, int backward, int dtype, cudaStream_t stream) {
+  if (tokens <= 0 || n_heads <= 0 || rot_dim <= 0) return SB_OK;
+  if (rot_dim & 1) return SB_ERR_BAD_ARG;
+  int half = rot_dim / 2;
+  int tx = half >= 64 ? 64 : (half >= 32 ? 32 : 16);
+  int ty = 256 / tx;
+  if (ty > n_heads) ty = n_heads;
+  dim3 block(tx, ty);
+  SB_DISPATCH_DTYPE(dtype, T, {
+    rope_kernel<T><<<tokens, block, 0, stream>>>((T*)x, pos, tokens, n_heads, rot_dim, ld_tok, ld_head, log2f(base),
+                                                  mode, backward ? -1.f : 1.f);
+  });
+  SB_CHECK_LAUNCH();
+  return SB_OK;
+}
+SB_API int sb200_masked_softmax_fwd(const void* x, const uint8_t* mask, void* y, long rows, int cols, int heads, int sq,
+                                    float scale, int dtype, cudaStream_t stream) {
+  if (rows <= 0 || cols <= 0) return SB_OK;
+  int threads = cols >= 1024 ? 256 : (cols >= 256 ? 128 : 64);
+  SB_DISPATCH_DTYPE(dtype, T, {
+    masked_softmax_fwd_kernel<T><<<(unsigned)rows, threads, 0, stream>>>((const T*)x, mask, (T*)y, rows, cols, heads,
+                                                                          sq, scale);
+  });
+  SB_CHECK_LAUNCH();
+  return SB_OK;
+}
+SB_API int sb200_masked_softmax_bwd(const void* dy, const void* y, const uint8_t* mask, void* dx, long rows, int cols,
+                                    int heads, int sq, float scale, int dtype, cudaStream_t stream) {
+  if (rows <= 0 || cols <= 0) return SB_OK;
+  int threads = cols >= 1024 ? 256 : (cols >= 256 ? 128 : 64);
+  SB_DISPATCH_DTYPE(dtype, T, {
+    masked_softmax_bwd_kernel<T><<<(unsigned)rows, threads, 0, stream>>>((const T*)dy, (const T*)y, mask, (T*)dx, rows,
+                                                                          cols, heads, sq, scale);
+  });
+  SB_CHECK_LAUNCH();
+  return SB_OK;
+}
+SB_API int sb200_transpose(const void* in, void* out, int R, int C, int dtype, cudaStream_t stream) {
+  if (R <= 0 || C <= 0) return SB_OK;
+  dim3 grid((C + 31) / 32, (R + 31) / 32), block(32, 8);
+  SB_DISPATCH_DTYPE(dtype, T, { transpose_kernel<T><<<grid, block, 0, stream>>>((const T*)in, (T*)out, R, C); });
+  SB_CHECK_LAUNCH();
+  return SB_OK;
+}

@@ -1,0 +1,243 @@
+// RMSNorm / LayerNorm forward and backward for sm_100a.
+//
+// One CTA per row in the forward pass (16-byte vector loads, fp32 statistics);
+// the backward pass is persistent over rows so that each CTA keeps its share of
+// the weight/bias gradient in registers and writes one partial row, which a
+// second kernel reduces in a fixed order (deterministic, no atomics).
+//
+// Behaviour covered: LayerNorm = F.layer_norm with weight (+ optional bias),
+// RMSNorm = x * rsqrt(mean(x^2) + eps) * weight (reference:
+// src/scaling/core/nn/norm/layernorm.py:84, src/scaling/core/nn/norm/rms_norm.py:47-50).
+// Statistics are always accumulated in fp32 (the reference RMSNorm computes in
+// the input dtype; fp32 is a strict accuracy improvement).
+#include "common.cuh"
+
+namespace {
+
+constexpr int NORM_THREADS = 256;
+constexpr int NORM_MAX_ITERS = 8;  // H <= 256 * 8 * 8 = 16384 for 2-byte types
+
+template <typename T, bool RMS>
+__global__ void __launch_bounds__(NORM_THREADS) norm_fwd_kernel(const T* __restrict__ x, const T* __restrict__ w,
+                                                                const T* __restrict__ b, T* __restrict__ y,
+                                                                float* __restrict__ mean_out,
+                                                                float* __restrict__ rstd_out, int M, int H, float eps) {
+  __shared__ float red[33];
+  constexpr int V = sb::Vec16<T>::N;
+  const int row = blockIdx.x;
+  if (row >= M) return;
+  const T* xr = x + (size_t)row * H;
+  T* yr = y + (size_t)row * H;
+  const bool vec = (H % V) == 0;
+  float s = 0.f, ss = 0.f;
+  if (vec) {
+    for (int c = threadIdx.x * V; c < H; c += NORM_THREADS * V) {
+      auto v = sb::ld16(xr + c);
+#pragma unroll
+      for (int i = 0; i < V; ++i) {
+        float f = sb::to_f(v.e[i]);
+        s += f;
+        ss += f * f;
+      }
+    }
+  } else {
+    for (int c = threadIdx.x; c < H; c += NORM_THREADS) {
+      float f = sb::to_f(xr[c]);
+      s += f;
+      ss += f * f;
+    }
+  }
+  float mean = 0.f, rstd;
+  if (RMS) {
+    ss = sb::block_sum(ss, red);
+    rstd = rsqrtf(ss / H + eps);
+  } else {
+    s = sb::block_sum(s, red);
+    mean = s / H;
+    // second pass for the variance (numerically safer than E[x^2]-E[x]^2)
+    float var = 0.f;
+    if (vec) {
+      for (int c = threadIdx.x * V; c < H; c += NORM_THREADS * V) {
+        auto v = sb::ld16(xr + c);
+#pragma unroll
+        for (int i = 0; i < V; ++i) {
+          float d = sb::to_f(v.e[i]) - mean;
+          var += d * d;
+        }
+      }
+    } else {
+      for (int c = threadIdx.x; c < H; c += NORM_THREADS) {
+        float d = sb::to_f(xr[c]) - mean;
+        var += d * d;
+      }
+    }
+    var = sb::block_sum(var, red);
+    rstd = rsqrtf(var / H + eps);
+  }
+  if (threadIdx.x == 0) {
+    if (mean_out) mean_out[row] = mean;
+    rstd_out[row] = rstd;
+  }
+  if (vec) {
+    for (int c = threadIdx.x * V; c < H; c += NORM_THREADS * V) {
+      auto v = sb::ld16(xr + c);
+      auto wv = sb::ld16(w + c);
+      sb::Vec16<T> o;
+      if (b) {
+        auto bv = sb::ld16(b + c);
+#pragma unroll
+        for (int i = 0; i < V; ++i)
+          o.e[i] = sb::from_f<T>((sb::to_f(v.e[i]) - mean) * rstd * sb::to_f(wv.e[i]) + sb::to_f(bv.e[i]));
+      } else {
+#pragma unroll
+        for (int i = 0; i < V; ++i) o.e[i] = sb::from_f<T>((sb::to_f(v.e[i]) - mean) * rstd * sb::to_f(wv.e[i]));
+      }
+      sb::st16(yr + c, o);
+    }
+  } else {
+    for (int c = threadIdx.x; c < H; c += NORM_THREADS) {
+      float o = (sb::to_f(xr[c]) - mean) * rstd * sb::to_f(w[c]);
+      if (b) o += sb::to_f(b[c]);
+      yr[c] = sb::from_f<T>(o);
+    }
+  }
+}
+
+// Backward.  Requires H % V == 0 and H <= NORM_THREADS * V * NORM_MAX_ITERS.
+template <typename T, bool RMS>
+__global__ void __launch_bounds__(NORM_THREADS)
+    norm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __restrict__ w,
+                    const float* __restrict__ mean_in, const float* __restrict__ rstd_in, T* __restrict__ dx,
+                    float* __restrict__ dw_partial, float* __restrict__ db_partial, int M, int H) {
+  __shared__ float red[33];
+  constexpr int V = sb::Vec16<T>::N;
+  float dw_acc[NORM_MAX_ITERS][V];
+  float db_acc[NORM_MAX_ITERS][V];
+#pragma unroll
+  for (int it = 0; it < NORM_MAX_ITERS; ++it)
+#pragma unroll
+    for (int i = 0; i < V; ++i) {
+      dw_acc[it][i] = 0.f;
+      db_acc[it][i] = 0.f;
+    }
+  for (int row = blockIdx.x; row < M; row += gridDim.x) {
+    const T* xr = x + (size_t)row * H;
+    const T* dyr = dy + (size_t)row * H;
+    T* dxr = dx + (size_t)row * H;
+    const float mean = RMS ? 0.f : mean_in[row];
+    const float rstd = rstd_in[row];
+    float sum_g = 0.f, sum_gx = 0.f;
+#pragma unroll
+    for (int it = 0; it < NORM_MAX_ITERS; ++it) {
+      int c = (it * NORM_THREADS + threadIdx.x) * V;
+      if (c < H) {
+        auto xv = sb::ld16(xr + c);
+        auto dv = sb::ld16(dyr + c);
+        auto wv = sb::ld16(w + c);
+#pragma unroll
+        for (int i = 0; i < V; ++i) {
+          float xh = (sb::to_f(xv.e[i]) - mean) * rstd;
+          float d = sb::to_f(dv.e[i]);
+          float g = d * sb::to_f(wv.e[i]);
+          sum_g += g;
+          sum_gx += g * xh;
+          dw_acc[it][i] += d * xh;
+          if (!RMS) db_acc[it][i] += d;
+        }
+      }
+    }
+    sum_gx = sb::block_sum(sum_gx, red) / H;
+    if (!RMS) sum_g = sb::block_sum(sum_g, red) / H; else sum_g = 0.f;
+#pragma unroll
+    for (int it = 0; it < NORM_MAX_ITERS; ++it) {
+      int c = (it * NORM_THREADS + threadIdx.x) * V;
+      if (c < H) {
+        auto xv = sb::ld16(xr + c);
+        auto dv = sb::ld16(dyr + c);
+        auto wv = sb::ld16(w + c);
+        sb::Vec16<T> o;
+#pragma unroll
+        for (int i = 0; i < V; ++i) {
+          float xh = (sb::to_f(xv.e[i]) - mean) * rstd;
+          float g = sb::to_f(dv.e[i]) * sb::to_f(wv.e[i]);
+          o.e[i] = sb::from_f<T>(rstd * (g - sum_g - xh * sum_gx));
+        }
+        sb::st16(dxr + c, o);
+      }
+    }
+  }
+  float* dwp = dw_partial + (size_t)blockIdx.x * H;
+  float* dbp = db_partial ? db_partial + (size_t)blockIdx.x * H : nullptr;
+#pragma unroll
+  for (int it = 0; it < NORM_MAX_ITERS; ++it) {
+    int c = (it * NORM_THREADS + threadIdx.x) * V;
+    if (c < H) {
+#pragma unroll
+      for (int i = 0; i < V; ++i) {
+        dwp[c + i] = dw_acc[it][i];
+        if (!RMS && dbp) dbp[c + i] = db_acc[it][i];
+      }
+    }
+  }
+}
+
+// out[c] (+)= sum_p partial[p][c], fixed order over p.
+template <typename T>
+__global__ void reduce_partials_kernel(const float* __restrict__ partial, T* __restrict__ out, int P, int H,
+                                       int accumulate) {
+  int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= H) return;
+  float s = 0.f;
+  for (int p = 0; p < P; ++p) s += partial[(size_t)p * H + c];
+  if (accumulate) s += sb::to_f(out[c]);
+  out[c] = sb::from_f<T>(s);
+}
+
+}  // namespace
+
+SB_API int sb200_norm_fwd(const void* x, const void* w, const void* b, void* y, float* mean, float* rstd, int M, int H,
+                          float eps, int rms, int dtype, cudaStream_t stream) {
+  if (M <= 0 || H <= 0) return SB_OK;
+  SB_DISPATCH_DTYPE(dtype, T, {
+    if (rms)
+      norm_fwd_kernel<T, true><<<M, NORM_THREADS, 0, stream>>>((const T*)x, (const T*)w, nullptr, (T*)y, nullptr, rstd,
+                                                                M, H, eps);
+    else
+      norm_fwd_kernel<T, false><<<M, NORM_THREADS, 0, stream>>>((const T*)x, (const T*)w, (const T*)b, (T*)y, mean,
+                                                                 rstd, M, H, eps);
+  });
+  SB_CHECK_LAUNCH();
+  return SB_OK;
+}
+
+// Number of partial rows the backward pass writes for a problem of M rows; the caller
+// provides dw_partial (and db_partial for LayerNorm with bias) of [rows, H] floats.
+SB_API int sb200_norm_bwd_partial_rows(int M, int sm_count) {
+  int p = sm_count * 2;
+  if (p > M) p = M;
+  if (p < 1) p = 1;
+  return p;
+}
+
+SB_API int sb200_norm_bwd(const void* dy, const void* x, const void* w, const float* mean, const float* rstd, void* dx,
+                          float* dw_partial, float* db_partial, void* dw, void* db, int M, int H, int rms,
+                          int accumulate, int partial_rows, int dtype, cudaStream_t stream) {
+  if (M <= 0 || H <= 0) return SB_OK;
+  SB_DISPATCH_DTYPE(dtype, T, {
+    constexpr int V = sb::Vec16<T>::N;
+    if (H % V != 0 || H > NORM_THREADS * V * NORM_MAX_ITERS) return SB_ERR_BAD_ARG;
+    if (rms)
+      norm_bwd_kernel<T, true><<<partial_rows, NORM_THREADS, 0, stream>>>(
+          (const T*)dy, (const T*)x, (const T*)w, nullptr, rstd, (T*)dx, dw_partial, nullptr, M, H);
+    else
+      norm_bwd_kernel<T, false><<<partial_rows, NORM_THREADS, 0, stream>>>(
+          (const T*)dy, (const T*)x, (const T*)w, mean, rstd, (T*)dx, dw_partial, db_partial, M, H);
+    SB_CHECK_LAUNCH();
+    int blocks = (H + 255) / 256;
+    reduce_partials_kernel<T><<<blocks, 256, 0, stream>>>(dw_partial, (T*)dw, partial_rows, H, accumulate);
+    if (!rms && db && db_partial)
+      reduce_partials_kernel<T><<<blocks, 256, 0, stream>>>(db_partial, (T*)db, partial_rows, H, accumulate);
+  });
+  SB_CHECK_LAUNCH();
+  return SB_OK;
+}

@@ -1,0 +1,165 @@
+// Optimizer-side kernels for sm_100a: fused AdamW on a flat fp32 master shard with the
+// low-precision write-out, gradient sum-of-squares with a sticky inf/nan flag, and the
+// vocab-parallel embedding gather / deterministic scatter.
+//
+// Behaviour covered (reference files): torch.optim.AdamW over fp32 masters
+// (src/scaling/core/optimizer/optimizer.py:62-66,186), per-parameter unscale + norm^2 +
+// overflow test (src/scaling/core/optimizer/parameter_group.py:497-511,
+// src/scaling/core/optimizer/loss_scaler.py:23-41), fp32 -> bf16 copy back
+// (parameter_group.py:428-486), masked embedding lookup
+// (src/scaling/core/nn/linear/vocab_parallel_embedding.py:166-189).
+#include "common.cuh"
+
+namespace {
+
+// ------------------------------------------------------------------- AdamW
+// control[0] = gradient multiplier (1/loss_scale * clip coefficient), control[1] != 0 -> skip step.
+template <typename G, typename P>
+__global__ void adamw_kernel(float* __restrict__ p, float* __restrict__ m, float* __restrict__ v,
+                             const G* __restrict__ g, P* __restrict__ p_lp, long n, float lr, float beta1, float beta2,
+                             float eps, float wd, float bc1, float bc2, const float* __restrict__ control) {
+  float gmul = 1.f;
+  if (control) {
+    if (control[1] != 0.f) return;
+    gmul = control[0];
+  }
+  const float inv_bc1 = 1.f / bc1;
+  const float inv_sqrt_bc2 = rsqrtf(bc2);
+  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x) {
+    float gr = sb::to_f(g[i]) * gmul;
+    float pi = p[i];
+    float mi = m[i] * beta1 + (1.f - beta1) * gr;
+    float vi = v[i] * beta2 + (1.f - beta2) * gr * gr;
+    pi *= (1.f - lr * wd);
+    float denom = sqrtf(vi) * inv_sqrt_bc2 + eps;
+    pi -= lr * inv_bc1 * mi / denom;
+    p[i] = pi;
+    m[i] = mi;
+    v[i] = vi;
+    if (p_lp) p_lp[i] = sb::from_f<P>(pi);
+  }
+}
+
+// ------------------------------------------- sum of squares + inf/nan flag
+template <typename G>
+__global__ void sumsq_partial_kernel(const G* __restrict__ g, long n, float* __restrict__ partial,
+                                     int* __restrict__ flag) {
+  __shared__ float red[33];
+  float s = 0.f;
+  bool bad = false;
+  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x) {
+    float f = sb::to_f(g[i]);
+    if (!isfinite(f)) bad = true;
+    s += f * f;
+  }
+  s = sb::block_sum(s, red);
+  if (threadIdx.x == 0) partial[blockIdx.x] = s;
+  if (bad && flag) *flag = 1;  // benign race: every writer stores the same value
+}
+// out[0] = (accumulate ? out[0] : 0) + scale * sum_p partial[p]   (single warp, fixed order)
+__global__ void sumsq_final_kernel(const float* __restrict__ partial, int P, float* __restrict__ out, float scale,
+                                   int accumulate) {
+  float s = 0.f;
+  for (int p = threadIdx.x; p < P; p += 32) s += partial[p];
+  s = sb::warp_sum(s);
+  if (threadIdx.x == 0) out[0] = (accumulate ? out[0] : 0.f) + s * scale;
+}
+
+// --------------------------------------------------------------- embedding
+// out[t, :] = W[id - vocab_start, :] when id is inside this rank's shard, else 0.
+template <typename T>
+__global__ void embedding_fwd_kernel(const long* __restrict__ ids, const T* __restrict__ W, T* __restrict__ out,
+                                     long tokens, int H, long vocab_start, long vocab_rows) {
+  long t = blockIdx.x;
+  if (t >= tokens) return;
+  long id = ids[t] - vocab_start;
+  bool in = id >= 0 && id < vocab_rows;
+  constexpr int V = sb::Vec16<T>::N;
+  T* o = out + t * H;
+  if (H % V == 0) {
+    sb::Vec16<T> z;
+    z.u = make_uint4(0, 0, 0, 0);
+    for (int c = threadIdx.x * V; c < H; c += blockDim.x * V) sb::st16(o + c, in ? sb::ld16(W + id * H + c) : z);
+  } else {
+    for (int c = threadIdx.x; c < H; c += blockDim.x) o[c] = in ? W[id * H + c] : sb::from_f<T>(0.f);
+  }
+}
+// Deterministic backward: ids are sorted (with the permutation `order`); the CTA at the head of
+// every run of equal ids sums the rows of that run in order and adds them to dW[id].
+template <typename T, typename GW>
+__global__ void embedding_bwd_kernel(const long* __restrict__ sorted_ids, const long* __restrict__ order,
+                                     const T* __restrict__ dout, GW* __restrict__ dW, long tokens, int H,
+                                     long vocab_start, long vocab_rows) {
+  long i = blockIdx.x;
+  if (i >= tokens) return;
+  long id = sorted_ids[i];
+  if (i > 0 && sorted_ids[i - 1] == id) return;
+  long row = id - vocab_start;
+  if (row < 0 || row >= vocab_rows) return;
+  long end = i + 1;
+  while (end < tokens && sorted_ids[end] == id) ++end;
+  for (int c = threadIdx.x; c < H; c += blockDim.x) {
+    float s = 0.f;
+    for (long j = i; j < end; ++j) s += sb::to_f(dout[order[j] * H + c]);
+    dW[row * H + c] = sb::from_f<GW>(sb::to_f(dW[row * H + c]) + s);
+  }
+}
+
+}  // namespace
+
+// g_dtype: dtype of the gradient; lp_dtype: dtype of the low-precision copy (ignored if p_lp is null)
+SB_API int sb200_adamw(float* p, float* m, float* v, const void* g, void* p_lp, long n, float lr, float beta1,
+                       float beta2, float eps, float wd, float bc1, float bc2, const float* control, int g_dtype,
+                       int lp_dtype, cudaStream_t stream) {
+  if (n <= 0) return SB_OK;
+  long b = (n + 255) / 256;
+  if (b > 148 * 8) b = 148 * 8;
+  SB_DISPATCH_DTYPE(g_dtype, G, {
+    SB_DISPATCH_DTYPE(lp_dtype, P, {
+      adamw_kernel<G, P><<<(int)b, 256, 0, stream>>>(p, m, v, (const G*)g, (P*)p_lp, n, lr, beta1, beta2, eps, wd, bc1,
+                                                     bc2, control);
+    });
+  });
+  SB_CHECK_LAUNCH();
+  return SB_OK;
+}
+
+SB_API int sb200_sumsq_max_partials() { return 1024; }
+
+// partial: scratch of >= sb200_sumsq_max_partials() floats
+SB_API int sb200_sumsq(const void* g, long n, float* partial, float* out, int* flag, float scale, int accumulate,
+                       int dtype, cudaStream_t stream) {
+  long b = (n + 1023) / 1024;
+  if (b > 1024) b = 1024;
+  if (b < 1) b = 1;
+  SB_DISPATCH_DTYPE(dtype, G, {
+    sumsq_partial_kernel<G><<<(int)b, 256, 0, stream>>>((const G*)g, n, partial, flag);
+  });
+  SB_CHECK_LAUNCH();
+  sumsq_final_kernel<<<1, 32, 0, stream>>>(partial, (int)b, out, scale, accumulate);
+  SB_CHECK_LAUNCH();
+  return SB_OK;
+}
+
+SB_API int sb200_embedding_fwd(const long* ids, const void* W, void* out, long tokens, int H, long vocab_start,
+                               long vocab_rows, int dtype, cudaStream_t stream) {
+  if (tokens <= 0) return SB_OK;
+  SB_DISPATCH_DTYPE(dtype, T, {
+    embedding_fwd_kernel<T><<<(unsigned)tokens, 128, 0, stream>>>(ids, (const T*)W, (T*)out, tokens, H, vocab_start,
+                                                                  vocab_rows);
+  });
+  SB_CHECK_LAUNCH();
+  return SB_OK;
+}
+SB_API int sb200_embedding_bwd(const long* sorted_ids, const long* order, const void* dout, void* dW, long tokens,
+                               int H, long vocab_start, long vocab_rows, int dtype, int gw_dtype, cudaStream_t stream) {
+  if (tokens <= 0) return SB_OK;
+  SB_DISPATCH_DTYPE(dtype, T, {
+    SB_DISPATCH_DTYPE(gw_dtype, GW, {
+      embedding_bwd_kernel<T, GW><<<(unsigned)tokens, 256, 0, stream>>>(sorted_ids, order, (const T*)dout, (GW*)dW,
+                                                                        tokens, H, vocab_start, vocab_rows);
+    });
+  });
+  SB_CHECK_LAUNCH();
+  return SB_OK;
+}

@@ -1,0 +1,257 @@
+"""Numerics of the sm_100a kernels against plain PyTorch fp32 references of the same op."""
+import math
+
+import pytest
+import torch
+import torch.nn.functional as F
+
+from scaling_b200.ops import functional as K
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _rel(a, b):
+    a, b = a.float(), b.float()
+    return ((a - b).norm() / (b.norm() + 1e-12)).item()
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32, torch.float16])
+@pytest.mark.parametrize("shape", [(64, 768), (37, 4096), (5, 8192), (300, 64)])
+@pytest.mark.parametrize("rms", [True, False])
+def test_norm(dtype, shape, rms):
+    torch.manual_seed(0)
+    x = torch.randn(*shape, device=DEV, dtype=dtype, requires_grad=True)
+    w = (torch.rand(shape[1], device=DEV) + 0.5).to(dtype).requires_grad_()
+    b = None if rms else (torch.randn(shape[1], device=DEV) * 0.1).to(dtype).requires_grad_()
+    y = K.rms_norm(x, w, 1e-5) if rms else K.layer_norm(x, w, b, 1e-5)
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    xr = x.detach().float().requires_grad_()
+    wr = w.detach().float().requires_grad_()
+    br = None if rms else b.detach().float().requires_grad_()
+    if rms:
+        yr = xr * torch.rsqrt(xr.pow(2).mean(-1, keepdim=True) + 1e-5) * wr
+    else:
+        yr = F.layer_norm(xr, (shape[1],), wr, br, 1e-5)
+    yr.backward(dy.float())
+    tol = 2e-2 if dtype != torch.float32 else 1e-5
+    assert _rel(y, yr) < tol
+    assert _rel(x.grad, xr.grad) < tol
+    assert _rel(w.grad, wr.grad) < tol
+    if not rms:
+        assert _rel(b.grad, br.grad) < tol
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_swiglu_gelu(dtype):
+    torch.manual_seed(1)
+    M, Fd = 333, 1024
+    ag = torch.randn(M, 2 * Fd, device=DEV, dtype=dtype, requires_grad=True)
+    a, g = ag[:, :Fd], ag[:, Fd:]
+    y = K.swiglu(a, g)
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    agr = ag.detach().float().requires_grad_()
+    yr = F.silu(agr[:, :Fd]) * agr[:, Fd:]
+    yr.backward(dy.float())
+    tol = 2e-2 if dtype != torch.float32 else 1e-5
+    assert _rel(y, yr) < tol and _rel(ag.grad, agr.grad) < tol
+    x = torch.randn(1000, 77, device=DEV, dtype=dtype, requires_grad=True)
+    y = K.gelu(x)
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    xr = x.detach().float().requires_grad_()
+    yr = F.gelu(xr)
+    yr.backward(dy.float())
+    assert _rel(y, yr) < tol and _rel(x.grad, xr.grad) < tol
+
+
+@pytest.mark.parametrize("interleaved", [False, True])
+@pytest.mark.parametrize("rot", [64, 32])
+def test_rope(interleaved, rot):
+    torch.manual_seed(2)
+    T, H, D = 257, 12, 64
+    x = torch.randn(T, H, D, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    pos = torch.randint(0, 4096, (T,), device=DEV)
+    y = K.rope(x, pos, rot, 10000.0, interleaved)
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    xr = x.detach().float().cpu().requires_grad_()
+    yr = K.rope_reference(xr, pos.cpu(), rot, 10000.0, interleaved)
+    yr.backward(dy.float().cpu())
+    assert _rel(y.cpu(), yr) < 1e-2
+    assert _rel(x.grad.cpu(), xr.grad) < 1e-2
+    # strided view (q slice of a fused qkv buffer)
+    qkv = torch.randn(T, H, 3 * D, device=DEV, dtype=torch.bfloat16)
+    q = qkv[:, :, :D]
+    yq = K.rope(q, pos, rot, 10000.0, interleaved)
+    yq_ref = K.rope_reference(q.float().cpu(), pos.cpu(), rot, 10000.0, interleaved)
+    assert _rel(yq.cpu(), yq_ref) < 1e-2
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_masked_softmax(dtype):
+    torch.manual_seed(3)
+    b, h, sq, sk = 2, 3, 65, 130
+    x = torch.randn(b, h, sq, sk, device=DEV, dtype=dtype, requires_grad=True)
+    mask = torch.rand(b, 1, sq, sk, device=DEV) > 0.7
+    y = K.masked_softmax(x, mask, 0.37)
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    xr = x.detach().float().requires_grad_()
+    yr = torch.softmax((xr * 0.37).masked_fill(mask, -10000.0), -1)
+    yr.backward(dy.float())
+    tol = 2e-2 if dtype != torch.float32 else 1e-5
+    assert _rel(y, yr) < tol and _rel(x.grad, xr.grad) < tol
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("V", [32768, 1000])
+def test_cross_entropy(dtype, V):
+    torch.manual_seed(4)
+    N = 129
+    logits = (torch.randn(N, V, device=DEV) * 3).to(dtype)
+    tg = torch.randint(0, V, (N,), device=DEV)
+    w = torch.rand(N, device=DEV)
+    ref_l = logits.float().requires_grad_()
+    per = F.cross_entropy(ref_l, tg, reduction="none")
+    (per * w).sum().backward()
+    # two "ranks": split vocab in halves and combine statistics by hand
+    half = V // 2
+    parts = [logits[:, :half], logits[:, half:]]
+    stats = [K.ce_stats(p, tg, vocab_start=i * half) for i, p in enumerate(parts)]
+    gmax = torch.maximum(stats[0][0], stats[1][0])
+    gsum = sum(s[1] * torch.exp(s[0] - gmax) for s in stats)
+    gtgt = stats[0][2] + stats[1][2]
+    losses = []
+    grads = []
+    for i, p in enumerate(parts):
+        loss, dl = K.ce_finalize(p.clone(), tg, gmax, gsum, gtgt, w, vocab_start=i * half)
+        losses.append(loss)
+        grads.append(dl)
+    tol = 2e-2 if dtype != torch.float32 else 1e-5
+    assert _rel(losses[0], per) < 1e-3 if dtype != torch.float32 else 1e-5
+    assert torch.equal(losses[0], losses[1])
+    assert _rel(torch.cat(grads, 1), ref_l.grad) < tol
+    am = torch.where(stats[0][3] >= stats[1][3], stats[0][4], stats[1][4])
+    assert (am == logits.float().argmax(-1)).float().mean() > 0.99
+
+
+def test_embedding():
+    torch.manual_seed(5)
+    V, H = 1000, 256
+    W = torch.randn(V, H, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    ids = torch.randint(0, 2 * V, (4, 300), device=DEV)
+    out = K.embedding(ids, W, vocab_start=500)
+    dy = torch.randn_like(out)
+    out.backward(dy)
+    Wr = W.detach().float().requires_grad_()
+    loc = ids - 500
+    oob = (loc < 0) | (loc >= V)
+    ref = F.embedding(loc.masked_fill(oob, 0), Wr).masked_fill(oob[..., None], 0)
+    ref.backward(dy.float())
+    assert torch.equal(out.float(), ref.detach().to(torch.bfloat16).float())
+    assert _rel(W.grad, Wr.grad) < 1e-2
+    # deterministic
+    W2 = W.detach().clone().requires_grad_()
+    K.embedding(ids, W2, vocab_start=500).backward(dy)
+    assert torch.equal(W.grad, W2.grad)
+
+
+@pytest.mark.parametrize("gdtype", [torch.bfloat16, torch.float32])
+def test_adamw_and_sumsq(gdtype):
+    torch.manual_seed(6)
+    n = 1_000_003
+    p = torch.randn(n, device=DEV)
+    pr = p.clone().requires_grad_()
+    m = torch.zeros_like(p)
+    v = torch.zeros_like(p)
+    lp = torch.empty(n, device=DEV, dtype=torch.bfloat16)
+    opt = torch.optim.AdamW([pr], lr=1e-2, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
+    ctrl = torch.tensor([0.5, 0.0], device=DEV)
+    for step in range(1, 4):
+        g = torch.randn(n, device=DEV).to(gdtype)
+        pr.grad = g.float() * 0.5
+        opt.step()
+        K.adamw_step(p, m, v, g, lp, 1e-2, 0.9, 0.95, 1e-8, 0.1, step, ctrl)
+    assert _rel(p, pr.detach()) < 1e-5
+    assert torch.equal(lp, p.to(torch.bfloat16))
+    # skip flag leaves state untouched
+    before = p.clone()
+    K.adamw_step(p, m, v, g, lp, 1e-2, 0.9, 0.95, 1e-8, 0.1, 4, torch.tensor([1.0, 1.0], device=DEV))
+    assert torch.equal(before, p)
+    out = torch.zeros(1, device=DEV)
+    flag = torch.zeros(1, device=DEV, dtype=torch.int32)
+    K.sumsq_(g, out, flag, 1.0, True)
+    assert abs(out.item() - (g.float() ** 2).sum().item()) / out.item() < 1e-4
+    assert flag.item() == 0
+    g[12345] = float("inf")
+    K.sumsq_(g, out, flag, 1.0, False)
+    assert flag.item() == 1
+
+
+GEMM_SHAPES = [(128, 256, 64), (256, 512, 128), (300, 264, 200), (2048, 2304, 768), (1000, 768, 3072), (64, 32, 1024),
+               (4096, 136, 72)]
+
+
+@pytest.mark.parametrize("M,N,K_", GEMM_SHAPES)
+@pytest.mark.parametrize("mode", ["nt", "nn", "tn"])
+@pytest.mark.parametrize("bn", [0, 128, 256])
+def test_gemm(M, N, K_, mode, bn):
+    torch.manual_seed(7)
+    dt = torch.bfloat16
+    if mode == "nt":  # forward: a [M,K], b [N,K]
+        a = torch.randn(M, K_, device=DEV, dtype=dt)
+        b = torch.randn(N, K_, device=DEV, dtype=dt)
+        ref = a.float() @ b.float().t()
+        c = K.gemm(a, b, bn=bn)
+    elif mode == "nn":  # dgrad: a [M,K], b [K,N]
+        a = torch.randn(M, K_, device=DEV, dtype=dt)
+        b = torch.randn(K_, N, device=DEV, dtype=dt)
+        ref = a.float() @ b.float()
+        c = K.gemm(a, b, b_mn=True, bn=bn)
+    else:  # wgrad: a [K,M], b [K,N]
+        a = torch.randn(K_, M, device=DEV, dtype=dt)
+        b = torch.randn(K_, N, device=DEV, dtype=dt)
+        ref = a.float().t() @ b.float()
+        c = K.gemm(a, b, a_mn=True, b_mn=True, bn=bn)
+    K.check_status()
+    assert c.shape == (M, N)
+    assert _rel(c, ref) < 1e-2, f"rel err {_rel(c, ref)}"
+
+
+def test_gemm_epilogues():
+    torch.manual_seed(8)
+    M, N, K_ = 512, 1024, 256
+    a = torch.randn(M, K_, device=DEV, dtype=torch.bfloat16)
+    b = torch.randn(N, K_, device=DEV, dtype=torch.bfloat16) * 0.1
+    bias = torch.randn(N, device=DEV, dtype=torch.bfloat16)
+    pre = torch.empty(M, N, device=DEV, dtype=torch.bfloat16)
+    c = K.gemm(a, b, bias=bias, act="gelu", pre_act_out=pre)
+    ref_pre = a.float() @ b.float().t() + bias.float()
+    assert _rel(pre, ref_pre) < 1e-2
+    assert _rel(c, F.gelu(ref_pre)) < 1e-2
+    acc = torch.randn(M, N, device=DEV, dtype=torch.float32)
+    acc0 = acc.clone()
+    K.gemm(a, b, out=acc, accumulate=True)
+    assert _rel(acc, acc0 + a.float() @ b.float().t()) < 1e-2
+    K.check_status()
+
+
+def test_linear_autograd():
+    torch.manual_seed(9)
+    x = torch.randn(4, 100, 768, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    w = (torch.randn(2304, 768, device=DEV) * 0.02).to(torch.bfloat16).requires_grad_()
+    b = torch.randn(2304, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    y = K.linear(x, w, b, act="gelu")
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    xr, wr, br = (t.detach().float().requires_grad_() for t in (x, w, b))
+    yr = F.gelu(F.linear(xr, wr, br))
+    yr.backward(dy.float())
+    K.check_status()
+    assert _rel(y, yr) < 1e-2
+    assert _rel(x.grad, xr.grad) < 2e-2
+    assert _rel(w.grad, wr.grad) < 2e-2
+    assert _rel(b.grad, br.grad) < 2e-2
