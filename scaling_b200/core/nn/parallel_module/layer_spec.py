@@ -1,0 +1,36 @@
+"""Deferred layer constructors.
+
+A model is described as a list of ``LayerSpec(module_class, *args, **kwargs)``; each pipeline stage
+instantiates only the layers it owns, directly on its device.  ``TiedLayerSpec`` marks layers that
+share parameters (``tied_weight_attributes``) with every other spec of the same ``key``
+(reference: src/scaling/core/nn/parallel_module/layer_spec.py:8-32).
+"""
+
+from __future__ import annotations
+
+from typing import Any, Optional
+
+import torch
+
+
+class LayerSpec:
+    def __init__(self, module_class: type, *args: Any, **kwargs: Any) -> None:
+        if not isinstance(module_class, type) or not issubclass(module_class, torch.nn.Module):
+            raise TypeError(f"LayerSpec needs a torch.nn.Module subclass, got {module_class!r}")
+        self.module_class = module_class
+        self.args = args
+        self.kwargs = kwargs
+
+    def initialize(self, device: Optional[torch.device] = None) -> torch.nn.Module:
+        module = self.module_class(*self.args, **self.kwargs)
+        return module if device is None else module.to(device)
+
+    def __repr__(self) -> str:
+        return f"{type(self).__name__}({self.module_class.__name__})"
+
+
+class TiedLayerSpec(LayerSpec):
+    def __init__(self, module_class: type, key: str, tied_weight_attributes: list[str], *args: Any, **kwargs: Any):
+        super().__init__(module_class, *args, **kwargs)
+        self.key = key
+        self.tied_weight_attributes = list(tied_weight_attributes)

@@ -1,0 +1,407 @@
+"""The training engine of one rank: owns the local layers and executes pipeline instructions.
+
+``train_step`` walks the precomputed 1F1B instruction list of this stage (load, receive, forward,
+loss, backward, send, tied-gradient reduction, optimizer step) through a dispatch table;
+``evaluation_step`` does the same for the fill-drain schedule without gradients;
+``run_instructions`` executes ad-hoc lists for inference.  Return records, buffer semantics, loss
+averaging (over micro batches and data-parallel ranks) and the shipping of (loss, metrics) from the
+last to the first stage follow src/scaling/core/nn/parallel_module/parallel_module.py:92-767.
+Unlike the reference, the step has a single host synchronisation (reading the loss), the step time
+is measured with CUDA events on the compute stream, and the batch is copied to the device with
+non-blocking copies from pinned memory.
+"""
+
+from __future__ import annotations
+
+import json
+from dataclasses import asdict
+from pathlib import Path
+from typing import Any, Callable, Generic, NamedTuple, Optional, Union
+
+import torch
+import torch.distributed as dist
+
+from ....parallel.topology import Topology
+from ....parallel.topology_config import ActivationCheckpointingType
+from ...profiler import Profiler, ProfilerConfig
+from ...profiler.timer import CudaEventTimer
+from ..parameter_meta import CoreParameterMeta
+from ..pipeline_schedule import InstructionBase, PipelineScheduleInference, PipelineScheduleTrain
+from .activation_checkpointing import checkpoint
+from .base_layer import BaseDatasetBatchGeneric, BaseLossInputGeneric
+from .buffers import Buffers, BufferType
+from .communicator import PipeCommunicator
+from .layer_spec import LayerSpec
+from .partitioned_module import PipePartitionedModule
+
+
+class TrainStepOutput(NamedTuple):
+    loss: Optional[float]
+    metrics: Optional[dict[str, Union[int, float]]]
+    global_grad_norm: Optional[float]
+    global_grad_norm_clipped: Optional[float]
+    learning_rates: Optional[dict[str, float]]
+    overflow: Optional[bool]
+    no_overflow_steps: Optional[int]
+    current_loss_scale: Optional[float]
+    step_duration: float
+    debug_dict: Optional[dict[str, float]]
+
+
+class EvaluationStepOutput(NamedTuple):
+    loss: Optional[float]
+    metrics: Optional[dict[str, Union[int, float]]]
+    step_duration: float
+
+
+class PipeGrad(NamedTuple):
+    tensors: list[torch.Tensor]
+    grad_tensors: list[torch.Tensor]
+
+
+def _to_python(x: Any) -> Any:
+    if isinstance(x, dict):
+        return {k: _to_python(v) for k, v in x.items()}
+    if isinstance(x, (list, tuple)):
+        return type(x)(_to_python(v) for v in x)
+    return x.tolist() if torch.is_tensor(x) else x
+
+
+def allreduce_tensor_in_float32(tensor: torch.Tensor, process_group: Any) -> None:
+    if tensor.dtype == torch.float32:
+        dist.all_reduce(tensor, group=process_group)
+        return
+    f = tensor.float()
+    dist.all_reduce(f, group=process_group)
+    tensor.copy_(f)
+
+
+def _broadcast_from_first(tensor: torch.Tensor, process_group: Any) -> None:
+    src = dist.get_global_rank(process_group, 0)
+    dist.broadcast(tensor.data, src, group=process_group)
+
+
+class ParallelModule(PipePartitionedModule, Generic[BaseLossInputGeneric, BaseDatasetBatchGeneric]):
+    def __init__(self, layer_specs: list[LayerSpec], topology: Topology,
+                 profiler_config: ProfilerConfig = ProfilerConfig(), use_continuous_recommunication: bool = False):
+        super().__init__(layer_specs=layer_specs, topology=topology)
+        self.topology: Topology
+        t = self.topology
+        self.train_schedule = PipelineScheduleTrain(topology=t)
+        self.train_instructions: list[InstructionBase] = self.train_schedule.instructions()
+        self.train_required_buffer_count = self.train_schedule.required_buffer_count()
+        self.evaluation_schedule = PipelineScheduleInference(topology=t)
+        self.evaluation_instructions: list[InstructionBase] = self.evaluation_schedule.instructions()
+        self.evaluation_required_buffer_count = self.evaluation_schedule.required_buffer_count()
+        self.pipe_buffer = Buffers()
+
+        pp = t.config.pipe_parallel_size
+        nxt = (t.pipe_parallel_rank + 1) % pp   # wraps around for inference, where the last stage
+        prv = (t.pipe_parallel_rank - 1) % pp   # hands its output back to the first
+        self.communicator_in = PipeCommunicator(
+            local_device=t.device, recv_grads=False, recv_data=True,
+            use_continuous_recommunication=use_continuous_recommunication,
+            peer_recv=t.get_global_rank(pipe_parallel_rank=prv) if pp > 1 else None,
+        )
+        self.communicator_out = PipeCommunicator(
+            local_device=t.device, recv_grads=True, recv_data=False,
+            use_continuous_recommunication=use_continuous_recommunication,
+            peer_send=t.get_global_rank(pipe_parallel_rank=nxt) if pp > 1 else None,
+        )
+        self.communicator_loss_in: Optional[PipeCommunicator] = None
+        self.communicator_loss_out: Optional[PipeCommunicator] = None
+        if pp > 1:
+            if t.is_first_pipe_parallel_rank:
+                self.communicator_loss_in = PipeCommunicator(
+                    local_device=t.device, recv_grads=False, recv_data=True, use_continuous_recommunication=True,
+                    peer_recv=t.get_global_rank(pipe_parallel_rank=pp - 1),
+                )
+            if t.is_last_pipe_parallel_rank:
+                self.communicator_loss_out = PipeCommunicator(
+                    local_device=t.device, recv_grads=False, recv_data=False, use_continuous_recommunication=True,
+                    peer_send=t.get_global_rank(pipe_parallel_rank=0),
+                )
+        self.profiler = Profiler(config=profiler_config, topology=t)
+        self.step_timer = CudaEventTimer()
+        self._handlers: dict[str, Callable[..., None]] = {
+            "LoadMicroBatch": self._do_load, "ForwardPass": self._do_forward, "Loss": self._do_loss,
+            "BackwardPass": self._do_backward, "SendActivation": self._do_send_activation,
+            "RecvActivation": self._do_recv_activation, "SendGrad": self._do_send_grad,
+            "RecvGrad": self._do_recv_grad, "ReduceTiedGrads": self._do_reduce_tied, "StoreMicroBatch": self._do_store,
+        }
+        self.broadcast_model()
+
+    # ------------------------------------------------------------------ parameters
+    def named_parameters_with_meta(self) -> list[tuple[str, torch.Tensor, CoreParameterMeta]]:
+        out = []
+        for local_index, layer in enumerate(self._layers):
+            dup = self.tied_layer_index.layer_index_to_tied_local_duplicate_parameter_names(  # type: ignore[union-attr]
+                self.first_layer_index + local_index)
+            for name, p in layer.named_parameters():
+                if name not in dup:
+                    out.append((name, p, p.core_parameter_meta))  # type: ignore[attr-defined]
+        return out
+
+    def save_checkpoint(self, dir_: Union[Path, str], separate_file_for_parameters: Optional[list[str]] = None) -> None:
+        super().save_checkpoint(dir_=dir_, separate_file_for_parameters=separate_file_for_parameters)
+        if self.topology.data_parallel_rank == 0 and self.topology.model_parallel_rank == 0:
+            self.save_parameter_meta(Path(dir_))
+
+    def save_parameter_meta(self, dir_: Path) -> None:
+        c = self._pipe_partition_coordinates[0]
+        out = {}
+        for name, _, meta in self.named_parameters_with_meta():
+            sd = meta.state_dict()
+            sd["local_shape"] = list(sd["local_shape"])
+            sd["tied_layer_indices"] = sorted(sd["tied_layer_indices"])
+            sd["umup_meta"] = asdict(sd["umup_meta"]) if sd["umup_meta"] else None
+            out[f"layer_{meta.layer_index}_{name}"] = sd
+        with open(Path(dir_) / f"parameter_meta_{c.start}_{c.end}.json", "w") as f:
+            json.dump(out, f, indent=4, default=str)
+
+    def broadcast_model(self) -> None:
+        """Make replicas identical: TP-replicated parameters from model rank 0, everything from data rank 0,
+        tied copies from the first stage that holds them."""
+        t = self.topology
+        if not t.is_distributed_initialized:
+            return
+        for p in self._layers.parameters():
+            if p.core_parameter_meta.is_model_parallel_duplicate and t.model_parallel_size > 1:  # type: ignore[attr-defined]
+                _broadcast_from_first(p, t.model_parallel_group)
+            if t.data_parallel_size > 1:
+                _broadcast_from_first(p, t.data_parallel_group)
+        for p, group, stages in self.tied_layer_index.local_parameters_and_process_groups():  # type: ignore[union-attr]
+            if len(stages) > 1:
+                _broadcast_from_first(p, group)
+
+    def umup_setup(self, effective_batch_size: int, depth: int, avg_sequence_length: int,
+                   allow_non_umup_params: bool = False) -> None:
+        super().umup_setup(effective_batch_size, depth, avg_sequence_length, allow_non_umup_params)
+        self.broadcast_model()  # weights were re-drawn
+
+    def get_params_count(self) -> tuple[int, int]:
+        """(all parameters over all ranks of one replica, parameters counted once)."""
+        t = self.topology
+        total = unique = 0
+        if t.data_parallel_rank == 0:
+            for local_index, layer in enumerate(self._layers):
+                tied_dup = self.tied_layer_index.layer_index_is_tied_global_duplicate(  # type: ignore[union-attr]
+                    self.first_layer_index + local_index)
+                for p in layer.parameters():
+                    n = p.nelement()
+                    total += n
+                    mp_dup = t.model_parallel_rank != 0 and p.core_parameter_meta.is_model_parallel_duplicate  # type: ignore[attr-defined]
+                    if not (tied_dup or mp_dup):
+                        unique += n
+        if t.is_distributed_initialized:
+            counts = torch.tensor([total, unique], dtype=torch.int64, device=t.device)
+            dist.all_reduce(counts)
+            total, unique = (int(v) for v in counts.tolist())
+        return total, unique
+
+    # ------------------------------------------------------------------ forward over local layers
+    def _forward_tuple_input(self, *args: Any) -> Any:
+        x = self._layers[0].tuple_to_input(tuple(args))
+        for layer in self._layers:
+            x = layer(x)
+        return self._layers[-1].output_to_tuple(x)
+
+    def forward(self, x: Any) -> Any:
+        mode = self.topology.config.activation_checkpointing_type
+        if self.training and torch.is_grad_enabled() and mode == ActivationCheckpointingType.EVERY_PIPE_STAGE:
+            out = checkpoint(self._forward_tuple_input, self.topology, *self._layers[0].input_to_tuple(x))
+            return self._tuple_to_stage_output(out)
+        if self.training and torch.is_grad_enabled() and mode == ActivationCheckpointingType.EVERY_LAYER:
+            for i, layer in enumerate(self._layers):
+                def run(*args: Any, _layer: Any = layer) -> Any:
+                    return _layer.output_to_tuple(_layer(_layer.tuple_to_input(tuple(args))))
+
+                out = checkpoint(run, self.topology, *layer.input_to_tuple(x))
+                if i + 1 < len(self._layers):
+                    x = self._layers[i + 1].tuple_to_input(out)
+                else:
+                    x = self._tuple_to_stage_output(out)
+            return x
+        for layer in self._layers:
+            x = layer(x)
+        return x
+
+    def _tuple_to_stage_output(self, out: tuple) -> Any:
+        last = self._layers[-1]
+        if self.topology.is_last_pipe_parallel_rank:
+            return last.tuple_to_last_stage_activation(out)
+        # an intermediate stage's output is what the first layer of the next stage takes as input
+        next_cls = self._layer_specs[self._pipe_partition_coordinates[0].end].module_class
+        return next_cls.tuple_to_input(out)
+
+    # ------------------------------------------------------------------ steps
+    def _run(self, instructions: list[InstructionBase], **ctx: Any) -> Any:
+        optimizer_out = None
+        for ins in instructions:
+            name = ins.name
+            with self.profiler.time(name, ins.micro_batch_id, ins.buffer_id):
+                if name == "OptimizerStep":
+                    optimizer_out = ctx["optimizer"].step()
+                else:
+                    self._handlers[name](ins, **ctx)
+        return optimizer_out
+
+    def train_step(self, dataloader: Any, optimizer: Any, sync_batch_to_model_parallel: Callable,
+                   loss_function: Callable, metrics_aggregation_fn: Optional[Callable] = None) -> TrainStepOutput:
+        if not torch.is_grad_enabled():
+            raise RuntimeError("train_step() requires gradients enabled. Use evaluation_step() instead.")
+        self.step_timer.start()
+        self._layers.train()
+        self.pipe_buffer.reset()
+        self.profiler.step()
+        opt_out = self._run(self.train_instructions, dataloader=dataloader, optimizer=optimizer,
+                            sync=sync_batch_to_model_parallel, loss_function=loss_function, grad=True)
+        loss, metrics = self.get_loss(metrics_aggregation_fn)
+        self.step_timer.stop()
+        self.profiler.flush()
+        return TrainStepOutput(loss=loss, metrics=metrics, step_duration=self.step_timer.duration(), **opt_out._asdict())
+
+    def evaluation_step(self, dataloader: Any, sync_batch_to_model_parallel: Callable, loss_function: Callable,
+                        metrics_aggregation_fn: Optional[Callable] = None) -> EvaluationStepOutput:
+        self.step_timer.start()
+        self._layers.eval()
+        self.pipe_buffer.reset()
+        self.profiler.step()
+        with torch.no_grad():
+            self._run(self.evaluation_instructions, dataloader=dataloader, optimizer=None,
+                      sync=sync_batch_to_model_parallel, loss_function=loss_function, grad=False)
+        loss, metrics = self.get_loss(metrics_aggregation_fn)
+        self.step_timer.stop()
+        self.profiler.flush()
+        return EvaluationStepOutput(loss=loss, metrics=metrics, step_duration=self.step_timer.duration())
+
+    def run_instructions(self, instructions: list[InstructionBase], sync_batch_to_model_parallel: Callable,
+                         collect_outputs_from_model_parallel: Callable, batch: Any = None) -> Any:
+        for ins in instructions:
+            if ins.name not in ("StoreMicroBatch", "ForwardPass", "SendActivation", "RecvActivation"):
+                raise NotImplementedError(f"Instruction '{ins.name}' not implemented for run_instructions.")
+            self._handlers[ins.name](ins, sync=sync_batch_to_model_parallel, batch=batch, take_input=True)
+        t = self.topology
+        if not instructions:
+            return None
+        last = instructions[-1]
+        if batch is not None and t.config.pipe_parallel_size == 1:
+            out = self.pipe_buffer.take(BufferType.PIPELINE_STAGE_OUTPUT, last.buffer_id)
+            return collect_outputs_from_model_parallel(t, out)
+        if t.config.pipe_parallel_size > 1 and t.pipe_parallel_rank == 0 and last.name == "RecvActivation":
+            out = self.pipe_buffer.take(BufferType.PIPELINE_STAGE_INPUT, last.buffer_id)
+            return collect_outputs_from_model_parallel(t, out)
+        return None
+
+    def get_loss(self, metrics_aggregation_fn: Optional[Callable]) -> tuple[Optional[float], Optional[dict]]:
+        t = self.topology
+        data = None
+        if t.is_last_pipe_parallel_rank:
+            losses = self.pipe_buffer.losses
+            assert losses, "no loss was recorded in this step"
+            loss = torch.stack([x.float() for x in losses]).sum() / t.config.gradient_accumulation_steps
+            metrics = None
+            if self.pipe_buffer.metrics:
+                assert metrics_aggregation_fn is not None
+                metrics = metrics_aggregation_fn(t, self.pipe_buffer.metrics)
+            if t.config.data_parallel_size > 1:
+                dist.all_reduce(loss, group=t.data_parallel_group)
+                loss = loss / t.config.data_parallel_size
+            data = (loss, metrics)
+        if t.config.pipe_parallel_size > 1:
+            if t.is_last_pipe_parallel_rank:
+                assert self.communicator_loss_out is not None
+                self.communicator_loss_out.send_data(data)
+                return None, None
+            if t.is_first_pipe_parallel_rank:
+                assert self.communicator_loss_in is not None
+                loss, metrics = self.communicator_loss_in.recv_data()
+                return float(loss.item()), _to_python(metrics)
+            return None, None
+        loss, metrics = data  # type: ignore[misc]
+        return float(loss.item()), _to_python(metrics)
+
+    # ------------------------------------------------------------------ instruction handlers
+    def _do_store(self, ins: InstructionBase, sync: Callable, batch: Any = None, **_: Any) -> None:
+        self.pipe_buffer.write(BufferType.PIPELINE_STAGE_INPUT, ins.buffer_id, sync(self.topology, batch))
+
+    def _do_load(self, ins: InstructionBase, dataloader: Any, sync: Callable, **_: Any) -> None:
+        t = self.topology
+        batch = None
+        if t.is_io_rank:
+            assert dataloader is not None
+            batch = next(dataloader)
+        batch = sync(t, batch)
+        if t.is_first_pipe_parallel_rank:
+            self.pipe_buffer.write(BufferType.PIPELINE_STAGE_INPUT, ins.buffer_id, batch.only_inputs())
+        if t.is_last_pipe_parallel_rank:
+            self.pipe_buffer.write(BufferType.TARGET, ins.buffer_id, batch.only_targets())
+
+    def _do_forward(self, ins: InstructionBase, take_input: bool = False, **_: Any) -> None:
+        op = self.pipe_buffer.take if take_input else self.pipe_buffer.get
+        x = op(BufferType.PIPELINE_STAGE_INPUT, ins.buffer_id)
+        self.pipe_buffer.write(BufferType.PIPELINE_STAGE_OUTPUT, ins.buffer_id, self(x))
+
+    def _do_loss(self, ins: InstructionBase, loss_function: Callable, **_: Any) -> None:
+        out = self.pipe_buffer.get(BufferType.PIPELINE_STAGE_OUTPUT, ins.buffer_id)
+        first_pass = True if ins.is_first_pass is None else ins.is_first_pass
+        target = (self.pipe_buffer.get if first_pass else self.pipe_buffer.take)(BufferType.TARGET, ins.buffer_id)
+        result = loss_function(out, target)
+        loss, metrics = result if isinstance(result, tuple) else (result, None)
+        assert torch.is_tensor(loss) and loss.dim() == 0, (
+            f"The loss needs to be a scalar. The loss currently has the shape: {getattr(loss, 'shape', None)}"
+        )
+        self.pipe_buffer.add_loss(loss, metrics)
+        self.pipe_buffer.write(BufferType.LOSS, ins.buffer_id, loss)
+
+    def _do_backward(self, ins: InstructionBase, optimizer: Any, **_: Any) -> None:
+        if self.topology.is_last_pipe_parallel_rank:
+            optimizer.backward(self.pipe_buffer.take(BufferType.LOSS, ins.buffer_id))
+            self.pipe_buffer.dump(BufferType.PIPELINE_STAGE_OUTPUT, ins.buffer_id)
+            self.pipe_buffer.dump(BufferType.TARGET, ins.buffer_id)
+        else:
+            g: PipeGrad = self.pipe_buffer.take(BufferType.GRAD, ins.buffer_id)
+            torch.autograd.backward(tensors=g.tensors, grad_tensors=g.grad_tensors)
+        if self.topology.is_first_pipe_parallel_rank:
+            self.pipe_buffer.dump(BufferType.PIPELINE_STAGE_INPUT, ins.buffer_id)
+
+    def _do_send_activation(self, ins: InstructionBase, **_: Any) -> None:
+        out = self.pipe_buffer.get(BufferType.PIPELINE_STAGE_OUTPUT, ins.buffer_id)
+        self.communicator_out.send_data(self._prepare_for_send(self._layers[-1].output_to_tuple(out)))
+
+    def _do_recv_activation(self, ins: InstructionBase, **_: Any) -> None:
+        tup = self._after_recv(self.communicator_in.recv_data())
+        first = self._layers[0]
+        x = first.tuple_to_last_stage_activation(tup) if self.topology.is_first_pipe_parallel_rank else first.tuple_to_input(tup)
+        self.pipe_buffer.write(BufferType.PIPELINE_STAGE_INPUT, ins.buffer_id, x)
+
+    def _do_send_grad(self, ins: InstructionBase, **_: Any) -> None:
+        x = self.pipe_buffer.take(BufferType.PIPELINE_STAGE_INPUT, ins.buffer_id)
+        self.communicator_in.send_grad(self._layers[0].input_to_tuple(x))
+
+    def _do_recv_grad(self, ins: InstructionBase, **_: Any) -> None:
+        out = self.pipe_buffer.take(BufferType.PIPELINE_STAGE_OUTPUT, ins.buffer_id)
+        tensors, grads = self.communicator_out.recv_grad(self._prepare_for_send(self._layers[-1].output_to_tuple(out)))
+        self.pipe_buffer.write(BufferType.GRAD, ins.buffer_id, PipeGrad(tensors, grads))
+
+    def _do_reduce_tied(self, ins: InstructionBase, **_: Any) -> None:
+        for p, group, stages in self.tied_layer_index.local_parameters_and_process_groups():  # type: ignore[union-attr]
+            if len(stages) > 1 and p.grad is not None:
+                allreduce_tensor_in_float32(p.grad, group)
+        if self.topology.config.model_parallel_size > 1:
+            for p in self._layers.parameters():
+                if p.core_parameter_meta.tied_grad_on_model_parallel and p.grad is not None:  # type: ignore[attr-defined]
+                    allreduce_tensor_in_float32(p.grad, self.topology.model_parallel_group)
+
+    # hooks for subclasses that strip / rebuild variable-shape fields around the pipe transfer
+    def _prepare_for_send(self, tup: tuple) -> tuple:
+        return tup
+
+    def _after_recv(self, tup: tuple) -> tuple:
+        return tup
+
+    def reset_activation_shape(self) -> None:
+        """Forget negotiated shapes; must be called on all ranks together."""
+        for c in (self.communicator_in, self.communicator_out, self.communicator_loss_in, self.communicator_loss_out):
+            if c is not None:
+                c.reset_communication_meta()

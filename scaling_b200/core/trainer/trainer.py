@@ -1,0 +1,218 @@
+"""Training loop around a ParallelModule and an Optimizer.
+
+Responsibilities (reference: src/scaling/core/trainer/trainer.py:33-330): count parameters, load a
+checkpoint (``load_dir/latest`` names the ``global_step{N}`` directory; a flat directory of ``.pt``
+files also works), optionally merge LoRA weights, create data loaders on IO ranks resuming from the
+consumed-sample counter, then loop: train step -> checkpoint every ``save_interval`` -> evaluation
+every ``eval_interval`` -> metrics on rank 0.  Checkpoints are written to
+``save_dir/global_step{N}`` and ``save_dir/latest`` is updated by rank 0.
+"""
+
+from __future__ import annotations
+
+from contextlib import nullcontext
+from pathlib import Path
+from typing import Any, Callable, Dict, Generic, List, Optional, TypeVar, Union
+
+import torch
+import torch.distributed as dist
+
+from ..context import BaseContextGeneric
+from ..data import BaseDataset, DataLoader
+from ..logging import logger
+from ..nn.parallel_module import EvaluationStepOutput, ParallelModule, TrainStepOutput
+from ..optimizer import BaseOptimizer
+from .trainer_config import TrainerConfig
+
+ParallelModuleGeneric = TypeVar("ParallelModuleGeneric", bound=ParallelModule)
+
+
+class BaseTrainer(Generic[BaseContextGeneric, ParallelModuleGeneric]):
+    def __init__(self, config: TrainerConfig, context: BaseContextGeneric, parallel_module: ParallelModuleGeneric,
+                 optimizer: BaseOptimizer, dataset: Optional[BaseDataset], sync_batch_to_model_parallel: Callable,
+                 loss_function: Callable, metrics_aggregation_fn: Optional[Callable] = None,
+                 dataset_evaluation: Optional[BaseDataset] = None):
+        self.config = config
+        self.context = context
+        self.parallel_module = parallel_module
+        self.optimizer = optimizer
+        self.dataset = dataset
+        self.dataset_evaluation = dataset_evaluation
+        self.sync_batch_to_model_parallel = sync_batch_to_model_parallel
+        self.loss_function = loss_function
+        self.metrics_aggregation_fn = metrics_aggregation_fn
+        self.parameters_total, self.parameters_unique = parallel_module.get_params_count()
+        logger.log_config_dict({"parameters_total": self.parameters_total, "parameters_unique": self.parameters_unique})
+
+        loaded = self.load_checkpoint(
+            load_dir=config.load_dir, load_optimizer_states=config.load_optimizer_states,
+            load_context=config.load_context,
+            allowed_missing_keys_in_checkpoint=config.allowed_missing_keys_in_checkpoint,
+            allowed_unexpected_keys_in_checkpoint=config.allowed_unexpected_keys_in_checkpoint,
+            ignore_keys_in_checkpoint=config.ignore_keys_in_checkpoint,
+        )
+        if config.assert_checkpoint_loaded and config.load_dir is not None:
+            assert loaded, (
+                "checkpoint could not be loaded. if this is intended you may change the parameter "
+                "'assert_checkpoint_loaded' in the TrainerConfig to False."
+            )
+        if config.merge_lora_after_loading_checkpoint:
+            for module in parallel_module.modules():
+                if hasattr(module, "merge_lora_weights") and getattr(module, "lora_config", None):
+                    module.merge_lora_weights()
+            optimizer.refresh_optimizer_after_model_change()
+            logger.info("Merged LoRa weights")
+
+        # data loaders are created after the checkpoint load so that they resume at the right sample
+        self.dataloader: Optional[DataLoader] = None
+        self.dataloader_evaluation: Optional[DataLoader] = None
+        if context.topology.is_io_rank:
+            assert dataset is not None, "io ranks need a dataset"
+            self.dataloader = self._make_loader(dataset, context.consumed_samples)
+            if dataset_evaluation is not None:
+                self.dataloader_evaluation = self._make_loader(dataset_evaluation, context.consumed_samples_evaluation)
+
+        if config.delete_past_optimizer_states and config.save_dir is not None:
+            logger.warning(
+                "delete_past_optimizer_states is set: optimizer states of all checkpoints but the latest are deleted "
+                "every time a checkpoint is saved; set the flag to false to keep them"
+            )
+        self.tensor_statistics_recorder = None
+        if config.tensor_statistics_recorder_config is not None:
+            from ..logging.tensor_statistics_recorder import TensorStatisticsRecorder, TensorStatisticsRecorderConfig
+
+            rc = config.tensor_statistics_recorder_config
+            if isinstance(rc, dict):
+                rc = TensorStatisticsRecorderConfig.from_dict(rc)
+            self.tensor_statistics_recorder = TensorStatisticsRecorder(config=rc, context=context, model=parallel_module)
+
+    def _make_loader(self, dataset: BaseDataset, consumed: int) -> DataLoader:
+        c = self.config
+        return DataLoader(seed=c.seed, consumed_samples=consumed, dataset=dataset, topology=self.context.topology,
+                          num_workers=c.dataloader_num_workers, pin_memory=c.dataloader_pin_memory,
+                          prefetch_factor=c.dataloader_prefetch_factor)
+
+    # ------------------------------------------------------------------ checkpoints
+    def save_checkpoint(self, save_dir: Optional[Path] = None) -> Path:
+        save_dir = Path(save_dir or self.config.save_dir)  # type: ignore[arg-type]
+        iteration_dir = save_dir / f"global_step{self.context.iterations}"
+        iteration_dir.mkdir(exist_ok=True, parents=True)
+        self.parallel_module.save_checkpoint(iteration_dir,
+                                             separate_file_for_parameters=self.config.separate_file_for_parameters)
+        self.optimizer.save_checkpoint(iteration_dir)
+        self.context.save_checkpoint(iteration_dir)
+        topo = self.context.topology
+        if topo.is_distributed_initialized and topo.world_size > 1:
+            dist.barrier()
+        if topo.config.global_rank == 0:
+            (save_dir / "latest").write_text(f"global_step{self.context.iterations}", encoding="UTF-8")
+            if self.config.delete_past_optimizer_states:
+                self._delete_past_optimizer_states(save_dir, keep=iteration_dir)
+        logger.info(f"saved checkpoint: {iteration_dir}")
+        return save_dir
+
+    @staticmethod
+    def _delete_past_optimizer_states(save_dir: Path, keep: Path) -> None:
+        for d in save_dir.glob("global_step*"):
+            if d.is_dir() and d != keep:
+                for f in d.glob("optimizer_state_*.pt"):
+                    f.unlink(missing_ok=True)
+
+    def load_checkpoint(self, load_dir: Optional[Path] = None, load_optimizer_states: bool = True,
+                        load_context: bool = True, allowed_missing_keys_in_checkpoint: Optional[List[str]] = None,
+                        allowed_unexpected_keys_in_checkpoint: Optional[List[str]] = None,
+                        ignore_keys_in_checkpoint: Optional[List[str]] = None) -> bool:
+        if load_dir is None:
+            return False
+        load_dir = Path(load_dir)
+        if (load_dir / "latest").is_file():
+            iteration_dir = load_dir / (load_dir / "latest").read_text(encoding="UTF-8").strip()
+        elif any(load_dir.glob("*.pt")):
+            logger.info(f"no latest file found, using load dir directly instead: {load_dir}")
+            iteration_dir = load_dir
+        else:
+            logger.error(f"no files found in load dir: {load_dir}")
+            return False
+        if not iteration_dir.is_dir():
+            logger.error(f"iteration_dir does not exist: {iteration_dir}")
+            return False
+        self.parallel_module.load_checkpoint(
+            iteration_dir, allowed_missing_keys_in_checkpoint=allowed_missing_keys_in_checkpoint,
+            allowed_unexpected_keys_in_checkpoint=allowed_unexpected_keys_in_checkpoint,
+            ignore_keys_in_checkpoint=ignore_keys_in_checkpoint,
+        )
+        if load_optimizer_states:
+            self.optimizer.load_checkpoint(iteration_dir)
+        else:
+            self.optimizer.refresh_optimizer_after_model_change()
+        if load_context:
+            self.context.load_checkpoint(iteration_dir)
+        logger.info(f"loaded checkpoint: {iteration_dir}")
+        return True
+
+    # ------------------------------------------------------------------ steps
+    def train_step(self) -> TrainStepOutput:
+        out = self.parallel_module.train_step(
+            dataloader=self.dataloader, optimizer=self.optimizer,
+            sync_batch_to_model_parallel=self.sync_batch_to_model_parallel, loss_function=self.loss_function,
+            metrics_aggregation_fn=self.metrics_aggregation_fn,
+        )
+        self.context.step()
+        return out
+
+    def eval_step(self) -> EvaluationStepOutput:
+        if self.context.topology.is_io_rank:
+            assert self.dataloader_evaluation is not None, (
+                "needs an evaluation dataloader on io ranks if evaluation is to be performed. "
+                "Remember to give the trainer a dataset_evaluation"
+            )
+        return self.parallel_module.evaluation_step(
+            dataloader=self.dataloader_evaluation, sync_batch_to_model_parallel=self.sync_batch_to_model_parallel,
+            loss_function=self.loss_function, metrics_aggregation_fn=self.metrics_aggregation_fn,
+        )
+
+    def log_metrics(self, train_step_output: TrainStepOutput,
+                    eval_step_output: Optional[EvaluationStepOutput]) -> Dict[str, Any]:
+        t = train_step_output
+        metrics: Dict[str, Any] = {f"training/{k}": v for k, v in (t.metrics or {}).items()}
+        assert "training/loss" not in metrics
+        metrics["training/loss"] = t.loss
+        metrics["training/step_duration"] = t.step_duration
+        optional = {
+            "training/global_grad_norm": t.global_grad_norm,
+            "training/global_grad_norm_clipped": t.global_grad_norm_clipped,
+            "training/overflow": None if t.overflow is None else int(t.overflow),
+            "training/no_overflow_steps": t.no_overflow_steps,
+            "training/current_loss_scale": t.current_loss_scale,
+        }
+        metrics.update({k: v for k, v in optional.items() if v is not None})
+        for name, lr in (t.learning_rates or {}).items():
+            metrics[f"training/learning_rate_{name}"] = lr
+        if eval_step_output is not None:
+            for k, v in (eval_step_output.metrics or {}).items():
+                metrics[f"evaluation/{k}"] = v
+            metrics["evaluation/loss"] = eval_step_output.loss
+            metrics["evaluation/step_duration"] = eval_step_output.step_duration
+        logger.log_metrics(metrics, step=self.context.iterations)
+        return metrics
+
+    def run_training(self, return_metrics: bool = False) -> Optional[List[Dict[str, Union[float, int]]]]:
+        collected: List[Dict[str, Any]] = []
+        c = self.config
+        while self.context.iterations < (c.train_iterations or 0):
+            recorder = nullcontext()
+            rec = self.tensor_statistics_recorder
+            if rec is not None and self.context.iterations % rec.config.interval == 0:
+                recorder = rec.trace()
+            with recorder:
+                train_out = self.train_step()
+            if c.save_interval is not None and c.save_dir is not None and self.context.iterations % c.save_interval == 0:
+                self.save_checkpoint()
+            eval_out = None
+            if c.eval_interval is not None and self.context.iterations % c.eval_interval == 0:
+                eval_out = self.eval_step()
+            if self.context.topology.config.global_rank == 0:
+                metrics = self.log_metrics(train_out, eval_out)
+                if return_metrics:
+                    collected.append(metrics)
+        return collected if return_metrics else None

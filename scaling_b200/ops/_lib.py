@@ -108,6 +108,11 @@ def lib() -> ctypes.CDLL:
         return _LIB
 
 
+def lib_has(name: str) -> bool:
+    """True when a GPU is present and the loaded library exports ``name``."""
+    return available() and hasattr(lib(), name)
+
+
 def declare(name: str, argtypes: list, restype=c_int):
     """Declare the signature of an exported symbol that is not in the static table."""
     fn = getattr(lib(), name)

@@ -1,0 +1,183 @@
+"""Autograd-aware collectives of the tensor-parallel / sequence-parallel region.
+
+forward / backward pairs (reference: src/scaling/core/nn/linear/utils.py:195-361):
+    copy_to_tensor_model_parallel_region     identity     / all-reduce
+    all_reduce                               all-reduce   / identity
+    all_concat                               all-gather of the last dim / local shard
+    all_shard                                local shard of the last dim / all-gather
+    all_reduce_scatter_to_sequence_parallel  reduce-scatter over tokens / all-gather
+    gather_from_sequence_parallel_region     all-gather over tokens / reduce-scatter
+Every function is the identity for a group of one.  The sequence-parallel shard is a contiguous
+chunk of the flattened ``batch * sequence`` tokens (dimension 1 of ``[b, s, h]`` is divided by the
+group size, memory is split rank-major), exactly like the reference.  With the gloo backend, which
+has no reduce-scatter, an all-reduce followed by a local slice stands in.
+"""
+
+from __future__ import annotations
+
+from typing import Any, Optional
+
+import torch
+import torch.distributed as dist
+
+from .topology import Topology
+
+
+def _size(topology: Optional[Topology]) -> int:
+    return 1 if topology is None else topology.model_parallel_size
+
+
+def _backend_is_gloo(group: Any) -> bool:
+    return dist.get_backend(group) == "gloo"
+
+
+# ------------------------------------------------------------------ raw (non-autograd) helpers
+def all_reduce_raw(x: torch.Tensor, group: Any, op: Any = None) -> torch.Tensor:
+    x = x.contiguous()
+    dist.all_reduce(x, op=op or dist.ReduceOp.SUM, group=group)
+    return x
+
+
+def all_gather_last_dim_raw(x: torch.Tensor, topology: Topology) -> torch.Tensor:
+    n = topology.model_parallel_size
+    x = x.contiguous()
+    parts = [torch.empty_like(x) for _ in range(n)]
+    dist.all_gather(parts, x, group=topology.model_parallel_group)
+    return torch.cat(parts, dim=-1)
+
+
+def shard_last_dim_raw(x: torch.Tensor, topology: Topology) -> torch.Tensor:
+    n, r = topology.model_parallel_size, topology.model_parallel_rank
+    assert x.shape[-1] % n == 0, f"last dim {x.shape[-1]} not divisible by model parallel size {n}"
+    w = x.shape[-1] // n
+    return x[..., r * w:(r + 1) * w].contiguous()
+
+
+def _sp_out_shape(shape: torch.Size, n: int, gather: bool) -> list[int]:
+    out = list(shape)
+    if gather:
+        out[1] = out[1] * n
+    else:
+        assert out[1] % n == 0, f"sequence dim {out[1]} not divisible by model parallel size {n}"
+        out[1] = out[1] // n
+    return out
+
+
+def reduce_scatter_tokens_raw(x: torch.Tensor, topology: Topology) -> torch.Tensor:
+    n, r = topology.model_parallel_size, topology.model_parallel_rank
+    group = topology.model_parallel_group
+    x = x.contiguous()
+    out_shape = _sp_out_shape(x.shape, n, gather=False)
+    if _backend_is_gloo(group):
+        dist.all_reduce(x, group=group)
+        flat = x.view(-1)
+        chunk = flat.numel() // n
+        return flat[r * chunk:(r + 1) * chunk].clone().view(out_shape)
+    out = torch.empty(out_shape, dtype=x.dtype, device=x.device)
+    dist.reduce_scatter_tensor(out, x, group=group)
+    return out
+
+
+def all_gather_tokens_raw(x: torch.Tensor, topology: Topology) -> torch.Tensor:
+    n = topology.model_parallel_size
+    group = topology.model_parallel_group
+    x = x.contiguous()
+    out = torch.empty(_sp_out_shape(x.shape, n, gather=True), dtype=x.dtype, device=x.device)
+    if _backend_is_gloo(group):
+        parts = [torch.empty_like(x) for _ in range(n)]
+        dist.all_gather(parts, x, group=group)
+        out.view(-1).copy_(torch.cat([p.view(-1) for p in parts]))
+        return out
+    dist.all_gather_into_tensor(out, x, group=group)
+    return out
+
+
+# ------------------------------------------------------------------ autograd functions
+class _CopyToRegion(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, topology):  # type: ignore[override]
+        ctx.topology = topology
+        return x
+
+    @staticmethod
+    def backward(ctx, g):  # type: ignore[override]
+        return all_reduce_raw(g, ctx.topology.model_parallel_group), None
+
+
+class _AllReduce(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, topology):  # type: ignore[override]
+        return all_reduce_raw(x, topology.model_parallel_group)
+
+    @staticmethod
+    def backward(ctx, g):  # type: ignore[override]
+        return g, None
+
+
+class _AllConcat(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, topology):  # type: ignore[override]
+        ctx.topology = topology
+        return all_gather_last_dim_raw(x, topology)
+
+    @staticmethod
+    def backward(ctx, g):  # type: ignore[override]
+        return shard_last_dim_raw(g, ctx.topology), None
+
+
+class _AllShard(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, topology):  # type: ignore[override]
+        ctx.topology = topology
+        return shard_last_dim_raw(x, topology)
+
+    @staticmethod
+    def backward(ctx, g):  # type: ignore[override]
+        return all_gather_last_dim_raw(g, ctx.topology), None
+
+
+class _ReduceScatterTokens(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, topology):  # type: ignore[override]
+        ctx.topology = topology
+        return reduce_scatter_tokens_raw(x, topology)
+
+    @staticmethod
+    def backward(ctx, g):  # type: ignore[override]
+        return all_gather_tokens_raw(g, ctx.topology), None
+
+
+class _GatherTokens(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, topology):  # type: ignore[override]
+        ctx.topology = topology
+        return all_gather_tokens_raw(x, topology)
+
+    @staticmethod
+    def backward(ctx, g):  # type: ignore[override]
+        return reduce_scatter_tokens_raw(g, ctx.topology), None
+
+
+# ------------------------------------------------------------------ public API
+def copy_to_tensor_model_parallel_region(x: torch.Tensor, topology: Optional[Topology]) -> torch.Tensor:
+    return x if _size(topology) == 1 else _CopyToRegion.apply(x, topology)
+
+
+def all_reduce(x: torch.Tensor, topology: Optional[Topology]) -> torch.Tensor:
+    return x if _size(topology) == 1 else _AllReduce.apply(x, topology)
+
+
+def all_concat(x: torch.Tensor, topology: Optional[Topology]) -> torch.Tensor:
+    return x if _size(topology) == 1 else _AllConcat.apply(x, topology)
+
+
+def all_shard(x: torch.Tensor, topology: Optional[Topology]) -> torch.Tensor:
+    return x if _size(topology) == 1 else _AllShard.apply(x, topology)
+
+
+def all_reduce_scatter_to_sequence_parallel(x: torch.Tensor, topology: Optional[Topology]) -> torch.Tensor:
+    return x if _size(topology) == 1 else _ReduceScatterTokens.apply(x, topology)
+
+
+def gather_from_sequence_parallel_region(x: torch.Tensor, topology: Optional[Topology]) -> torch.Tensor:
+    return x if _size(topology) == 1 else _GatherTokens.apply(x, topology)

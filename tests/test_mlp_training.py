@@ -1,0 +1,94 @@
+"""End-to-end training of the MLP application on CPU ranks (gloo): parallel layouts agree with a
+single process, and a resumed run reproduces the loss curve exactly."""
+
+import copy
+from pathlib import Path
+
+import pytest
+import torch
+
+from tests.utils import dist_launcher
+
+
+def _config(world_size, mp=1, pp=1, zero=False, ga=1, micro=16, iters=10, save_dir=None, load_dir=None,
+            save_interval=None, ckpt="disabled", precision="float32"):
+    dp = world_size // (mp * pp)
+    return {
+        "topology": {"world_size": world_size, "model_parallel_size": mp, "pipe_parallel_size": pp,
+                     "data_parallel_size": dp, "micro_batch_size": micro // dp if dp > 1 else micro,
+                     "gradient_accumulation_steps": ga, "device": "cpu", "backend": "gloo",
+                     "activation_checkpointing_type": ckpt},
+        "optimizer": {"zero": zero, "gradient_clipping": 1.0},
+        "learning_rate_scheduler": {"learning_rate": 1e-3, "learning_rate_decay_style": "constant"},
+        "trainer": {"train_iterations": iters, "seed": 7, "save_dir": save_dir, "load_dir": load_dir,
+                    "save_interval": save_interval, "assert_checkpoint_loaded": load_dir is not None,
+                    "delete_past_optimizer_states": False},
+        "architecture": {"n_hidden_layers": 1, "hidden_dim": 64, "precision": precision},
+        "data": {"n_samples": 512},
+    }
+
+
+def _run(rank, world_size, port, device, config, save_initial=None):
+    from scaling_b200.core.runner import LaunchConfig
+    from scaling_b200.core.trainer import BaseTrainer
+    from scaling_b200.models.mlp import (MLPConfig, MLPContext, SyntheticClassificationDataset, init_model,
+                                         init_optimizer, loss_function, metrics_aggregation_fn)
+    from scaling_b200.parallel import Topology
+
+    lc = LaunchConfig(master_port=port, master_addr="127.0.0.1", world_size=world_size, global_rank=rank,
+                      local_slot=rank, payload=copy.deepcopy(config))
+    cfg = MLPConfig.from_dict(lc.overwrite_config_dict_with_launcher_args(dict(lc.payload)))
+    topology = Topology(cfg.topology)
+    context = MLPContext(config=cfg, topology=topology)
+    context.initialize(master_addr="127.0.0.1", master_port=str(port), seed=cfg.trainer.seed)
+    model = init_model(context)
+    optimizer = init_optimizer(context, model)
+    dataset = SyntheticClassificationDataset(n_samples=cfg.data.n_samples, seed=cfg.trainer.seed) if topology.is_io_rank else None
+    trainer = BaseTrainer(config=cfg.trainer, context=context, parallel_module=model, optimizer=optimizer,
+                          dataset=dataset, sync_batch_to_model_parallel=SyntheticClassificationDataset.sync_batch_to_model_parallel,
+                          loss_function=loss_function, metrics_aggregation_fn=metrics_aggregation_fn)
+    if save_initial is not None:
+        trainer.save_checkpoint(Path(save_initial))
+    metrics = trainer.run_training(return_metrics=True)
+    return [m["training/loss"] for m in metrics] if metrics else None
+
+
+def _losses(world_size, save_initial=None, **kw):
+    res = dist_launcher(_run, world_size, config=_config(world_size, **kw), save_initial=save_initial)
+    return res[0]
+
+
+@pytest.mark.dist
+def test_layouts_agree_with_single_process(tmp_path: Path):
+    init = str(tmp_path / "init")
+    base = _losses(1, save_initial=init)
+    assert base[-1] < base[0]
+    for kw in (dict(world_size=2, mp=2), dict(world_size=2, pp=2, ga=2, micro=8), dict(world_size=2, zero=True),
+               dict(world_size=2), dict(world_size=1, ga=4, micro=4), dict(world_size=1, ckpt="every_layer")):
+        ws = kw.pop("world_size")
+        got = _losses(ws, load_dir=init, **kw)
+        assert len(got) == len(base)
+        for a, b in zip(got, base):
+            assert abs(a - b) < 2e-3, (kw, got, base)
+
+
+@pytest.mark.dist
+@pytest.mark.parametrize("layout", [dict(world_size=1), dict(world_size=2, mp=2), dict(world_size=2, pp=2, ga=2, micro=8),
+                                    dict(world_size=2, zero=True)])
+def test_resume_is_bit_identical(tmp_path: Path, layout):
+    layout = dict(layout)
+    ws = layout.pop("world_size")
+    full = _losses(ws, iters=10, save_dir=str(tmp_path), save_interval=6, **layout)
+    resumed = _losses(ws, iters=10, load_dir=str(tmp_path), **layout)
+    assert len(resumed) == 4
+    assert resumed == full[6:], (resumed, full[6:])
+
+
+@pytest.mark.dist
+def test_resume_into_other_layout(tmp_path: Path):
+    full = _losses(2, mp=2, iters=10, save_dir=str(tmp_path), save_interval=6)
+    for kw in (dict(world_size=1), dict(world_size=2, pp=2, ga=2, micro=8), dict(world_size=2, zero=True)):
+        ws = kw.pop("world_size")
+        resumed = _losses(ws, iters=10, load_dir=str(tmp_path), **kw)
+        for a, b in zip(resumed, full[6:]):
+            assert abs(a - b) < 2e-3, (kw, resumed, full[6:])
