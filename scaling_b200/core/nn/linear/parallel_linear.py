@@ -211,6 +211,12 @@ class RowParallelLinear(_ParallelLinear):
         self.parallel_input = parallel_input
         self.parallel_output = parallel_output
         self.input_features_per_partition = self.in_features // self.model_parallel_size
+        # partial (unreduced) output: the caller reduces it, so the bias may enter only once - it is added on
+        # tensor-parallel rank 0, whose bias gradient is then the complete one and is summed over the group
+        self._bias_on_first_rank_only = bool(parallel_output and self.model_parallel_size > 1)
+        b = self._bias()
+        if b is not None and self._bias_on_first_rank_only:
+            b.reduce_grad_over_model_parallel = True  # type: ignore[attr-defined]
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         if self.model_parallel_size > 1 and not self.parallel_input:
@@ -221,6 +227,6 @@ class RowParallelLinear(_ParallelLinear):
             y, bias = self._matmul(x, self.weight, None), self._bias()
         if not (self.parallel_output or self.topology is None):
             y = all_reduce(y, self.topology)
-        if bias is not None:
-            y = y + bias  # after the reduction, so that it is added once
+        if bias is not None and not (self._bias_on_first_rank_only and self.topology.model_parallel_rank != 0):  # type: ignore[union-attr]
+            y = y + bias  # after the reduction (or on one rank only), so that it is added once
         return y

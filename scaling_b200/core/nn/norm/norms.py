@@ -74,6 +74,14 @@ class _Norm(torch.nn.Module):
             ub = self._setup_param(getattr(self, self.bias_name), UMUP_WEIGHT_TYPE.BIAS, effective_batch_size, depth)
             self.bias_grad_multiplier = ub.grad_multiplier
 
+    def _mark_sequence_parallel(self) -> None:
+        """Under sequence parallelism a norm sees only this rank's tokens: its parameter gradients are
+        partial and are summed over the tensor-parallel group before the optimizer step."""
+        t = self.topology
+        if t is not None and t.config.sequence_parallel and t.config.model_parallel_size > 1:
+            for p in self.parameters(recurse=False):
+                p.reduce_grad_over_model_parallel = True  # type: ignore[attr-defined]
+
     def _finish(self, y: torch.Tensor) -> torch.Tensor:
         if self._use_umup:
             y = scale_fwd(y, self.forward_multiplier)
@@ -94,6 +102,7 @@ class LayerNorm(_Norm):
         CoreParameterMeta.register_on_parameter(self.weight, is_model_parallel=False)
         setattr(self, self.bias_name, torch.nn.Parameter(torch.zeros(normalized_shape, device=device, dtype=dtype)))
         CoreParameterMeta.register_on_parameter(getattr(self, self.bias_name), is_model_parallel=False)
+        self._mark_sequence_parallel()
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         w, b = self.weight, getattr(self, self.bias_name)
@@ -113,6 +122,7 @@ class RMSNorm(_Norm):
         self.eps = config.layernorm_epsilon
         self.weight = torch.nn.Parameter(torch.ones(dimensions, dtype=dtype, device=device))
         CoreParameterMeta.register_on_parameter(self.weight, is_model_parallel=False)
+        self._mark_sequence_parallel()
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         w = self.weight

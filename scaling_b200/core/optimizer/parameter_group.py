@@ -37,11 +37,9 @@ def _align(n: int, a: int) -> int:
 def needs_model_parallel_grad_reduce(name: str, p: torch.Tensor, topology: Topology) -> bool:
     if topology.config.model_parallel_size == 1:
         return False
-    if getattr(p, "reduce_grad_over_model_parallel", False):
-        return True
-    meta: CoreParameterMeta = p.core_parameter_meta  # type: ignore[attr-defined]
-    # sequence parallel: norm parameters see only this rank's tokens
-    return bool(topology.config.sequence_parallel and not meta.is_model_parallel and "norm" in name)
+    # set by the modules whose replicated parameters receive partial gradients per rank: norms under
+    # sequence parallelism, biases added on one rank only, KV projections replicated for MQA
+    return bool(getattr(p, "reduce_grad_over_model_parallel", False))
 
 
 class OptimizerParamGroup:

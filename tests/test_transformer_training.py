@@ -1,0 +1,92 @@
+"""Transformer application on CPU ranks (gloo): layouts agree and resume is exact."""
+
+import copy
+from pathlib import Path
+
+import pytest
+
+from tests.utils import dist_launcher
+
+
+def tiny_config(world_size, mp=1, pp=1, zero=False, ga=1, micro=4, iters=6, save_dir=None, load_dir=None,
+                save_interval=None, ckpt="disabled", arch=None, sp=False, kernel="flash_attention", groups=None,
+                training=None):
+    dp = world_size // (mp * pp)
+    architecture = {
+        "vocab_size": 128, "hidden_size": 64, "num_layers": 2, "num_attention_heads": 4, "sequence_length": 32,
+        "precision": "float32", "masked_softmax": {"kernel": kernel}, "weight_tying": False,
+        "dropout_embedding": 0.0,
+    }
+    architecture.update(arch or {})
+    return {
+        "topology": {"world_size": world_size, "model_parallel_size": mp, "pipe_parallel_size": pp,
+                     "data_parallel_size": dp, "micro_batch_size": micro // dp, "gradient_accumulation_steps": ga,
+                     "device": "cpu", "backend": "gloo", "activation_checkpointing_type": ckpt,
+                     "sequence_parallel": sp},
+        "optimizer": {"zero": zero, "gradient_clipping": 1.0},
+        "training_groups": groups or [{"group_name": "all", "weight_decay": 0.01,
+                                       "learning_rate_scheduler": {"learning_rate": 1e-3,
+                                                                   "learning_rate_decay_style": "constant"}}],
+        "training": training or {},
+        "trainer": {"train_iterations": iters, "seed": 11, "save_dir": save_dir, "load_dir": load_dir,
+                    "save_interval": save_interval, "assert_checkpoint_loaded": load_dir is not None,
+                    "delete_past_optimizer_states": False},
+        "transformer_architecture": architecture,
+        "data": {"synthetic_samples": 256},
+    }
+
+
+def run_training(rank, world_size, port, device, config, save_initial=None):
+    from scaling_b200.core.runner import LaunchConfig
+    from scaling_b200.parallel import Topology
+    from scaling_b200.transformer import TransformerConfig, TransformerContext, init_model, init_optimizer
+    from scaling_b200.transformer.model import metrics_aggregation_fn
+    from scaling_b200.transformer.model.losses import create_loss_function
+    from scaling_b200.transformer.train import TransformerTrainer, _get_sync_batch, _read_datasets
+
+    lc = LaunchConfig(master_port=port, master_addr="127.0.0.1", world_size=world_size, global_rank=rank,
+                      local_slot=rank, payload=copy.deepcopy(config))
+    cfg = TransformerConfig.from_dict(lc.overwrite_config_dict_with_launcher_args(dict(lc.payload)))
+    topology = Topology(cfg.topology)
+    context = TransformerContext(config=cfg, topology=topology)
+    context.initialize(master_addr="127.0.0.1", master_port=str(port), seed=cfg.trainer.seed)
+    model = init_model(context)
+    optimizer = init_optimizer(context, model)
+    dataset = _read_datasets(cfg)[0] if topology.is_io_rank else None
+    trainer = TransformerTrainer(config=cfg.trainer, context=context, parallel_module=model, optimizer=optimizer,
+                                 dataset=dataset, sync_batch_to_model_parallel=_get_sync_batch(cfg.data),
+                                 loss_function=create_loss_function(context, cfg.training.loss_function_config),
+                                 metrics_aggregation_fn=metrics_aggregation_fn)
+    if save_initial is not None:
+        trainer.save_checkpoint(Path(save_initial))
+    metrics = trainer.run_training(return_metrics=True)
+    return [m["training/loss"] for m in metrics] if metrics else None
+
+
+def losses(world_size, save_initial=None, **kw):
+    return dist_launcher(run_training, world_size, config=tiny_config(world_size, **kw), save_initial=save_initial)[0]
+
+
+@pytest.mark.dist
+def test_transformer_layouts_agree(tmp_path: Path):
+    init = str(tmp_path / "init")
+    base = losses(1, save_initial=init)
+    assert base[-1] < base[0]
+    for kw in (dict(world_size=2, mp=2), dict(world_size=2, pp=2, ga=2, micro=2), dict(world_size=2, zero=True),
+               dict(world_size=2, mp=2, sp=True), dict(world_size=1, ckpt="every_layer"),
+               dict(world_size=1, kernel="torch")):
+        ws = kw.pop("world_size")
+        got = losses(ws, load_dir=init, **kw)
+        for a, b in zip(got, base):
+            assert abs(a - b) < 2e-3, (kw, got, base)
+
+
+@pytest.mark.dist
+@pytest.mark.parametrize("layout", [dict(world_size=1), dict(world_size=2, mp=2),
+                                    dict(world_size=2, pp=2, ga=2, micro=2, arch={"weight_tying": True})])
+def test_transformer_resume_is_bit_identical(tmp_path: Path, layout):
+    layout = dict(layout)
+    ws = layout.pop("world_size")
+    full = losses(ws, iters=6, save_dir=str(tmp_path), save_interval=4, **layout)
+    resumed = losses(ws, iters=6, load_dir=str(tmp_path), **layout)
+    assert resumed == full[4:], (resumed, full[4:])
