@@ -103,7 +103,7 @@ class PipeCommunicator:
         return tensors, meta, spec
 
     def _send_meta(self, meta: list[LeafMeta], spec: Any) -> None:
-        blob = _encode_object((meta, spec), 0, self.local_device)
+        blob = _encode_object((meta, pytree.treespec_dumps(spec)), 0, self.local_device)
         n = torch.tensor([blob.numel()], dtype=torch.int64, device=self.local_device)
         dist.send(n, self.peer_send, group=self.group)
         dist.send(blob, self.peer_send, group=self.group)
@@ -133,7 +133,8 @@ class PipeCommunicator:
         dist.recv(n, self.peer_recv, group=self.group)
         blob = torch.zeros(int(n.item()), dtype=torch.uint8, device=self.local_device)
         dist.recv(blob, self.peer_recv, group=self.group)
-        self._recv_meta, self._recv_spec = _decode_object(blob)
+        self._recv_meta, spec = _decode_object(blob)
+        self._recv_spec = pytree.treespec_loads(spec)
 
     def _negotiate_recv(self) -> None:
         if self._recv_meta is None:

@@ -17,7 +17,7 @@ import torch
 
 from . import _build
 
-_LIB: Optional[ctypes.CDLL] = None
+_LIB: Optional["_Counting"] = None
 _LOCK = threading.Lock()
 
 SB_OK = 0
@@ -83,7 +83,40 @@ def available() -> bool:
     return torch.cuda.is_available()
 
 
-def lib() -> ctypes.CDLL:
+class _Counting:
+    """Proxy over the loaded library that counts calls into kernel-launching entry points."""
+
+    def __init__(self, handle: ctypes.CDLL):
+        self._handle = handle
+        self.calls = 0
+        self._cache: dict[str, object] = {}
+
+    def __getattr__(self, name: str):
+        fn = self._cache.get(name)
+        if fn is None:
+            raw = getattr(self._handle, name)
+            if name in _NO_LAUNCH:
+                fn = raw
+            else:
+                def fn(*args, _raw=raw, _self=self):
+                    _self.calls += 1
+                    return _raw(*args)
+            self._cache[name] = fn
+        return fn
+
+    def has(self, name: str) -> bool:
+        return hasattr(self._handle, name)
+
+
+_NO_LAUNCH = {"sb200_norm_bwd_partial_rows", "sb200_sumsq_max_partials"}
+
+
+def kernel_calls() -> int:
+    """Number of calls made so far into kernel-launching entry points of the native library."""
+    return 0 if _LIB is None else _LIB.calls
+
+
+def lib() -> "_Counting":
     global _LIB
     if _LIB is not None:
         return _LIB
@@ -104,18 +137,18 @@ def lib() -> ctypes.CDLL:
                 fn = getattr(handle, name)
                 fn.argtypes = argtypes
                 fn.restype = c_int
-        _LIB = handle
+        _LIB = _Counting(handle)
         return _LIB
 
 
 def lib_has(name: str) -> bool:
     """True when a GPU is present and the loaded library exports ``name``."""
-    return available() and hasattr(lib(), name)
+    return available() and lib().has(name)
 
 
 def declare(name: str, argtypes: list, restype=c_int):
     """Declare the signature of an exported symbol that is not in the static table."""
-    fn = getattr(lib(), name)
+    fn = getattr(lib()._handle, name)
     fn.argtypes = argtypes
     fn.restype = restype
     return fn
