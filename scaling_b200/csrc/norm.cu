@@ -241,3 +241,79 @@ SB_API int sb200_norm_bwd(const void* dy, const void* x, const void* w, const fl
   SB_CHECK_LAUNCH();
   return SB_OK;
 }
+
+// ---------------------------------------------------------------------------------------------------
+// Allocation-free variant of the backward pass (declared in sb200_noalloc.h): the partial-sum workspace
+// is a static device array instead of caller memory.
+#include <mutex>
+
+#include "sb200_noalloc.h"
+
+namespace {
+
+constexpr int NOALLOC_MAX_DEVICES = 64;
+
+// Workspace for the per-CTA partial sums of dW and dB.  In host code these names are only handles for
+// cudaGetSymbolAddress; the kernels receive the looked-up device pointers.
+static __device__ __align__(256) float g_noalloc_dw_partial[SB200_NOALLOC_MAX_PARTIAL_ROWS * SB200_NOALLOC_MAX_H];
+static __device__ __align__(256) float g_noalloc_db_partial[SB200_NOALLOC_MAX_PARTIAL_ROWS * SB200_NOALLOC_MAX_H];
+
+struct NoallocWorkspace {
+  float* dw = nullptr;
+  float* db = nullptr;
+  bool ready = false;
+};
+NoallocWorkspace g_noalloc_ws[NOALLOC_MAX_DEVICES];
+std::mutex g_noalloc_mutex;
+
+// Device addresses of the workspace on the current device, resolved once per device.
+int noalloc_workspace(float** dw, float** db) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= NOALLOC_MAX_DEVICES) return SB_ERR_BAD_ARG;
+  std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+  NoallocWorkspace& ws = g_noalloc_ws[dev];
+  if (!ws.ready) {
+    e = cudaGetSymbolAddress((void**)&ws.dw, g_noalloc_dw_partial);
+    if (e != cudaSuccess) return (int)e;
+    e = cudaGetSymbolAddress((void**)&ws.db, g_noalloc_db_partial);
+    if (e != cudaSuccess) return (int)e;
+    ws.ready = true;
+  }
+  *dw = ws.dw;
+  *db = ws.db;
+  return SB_OK;
+}
+
+}  // namespace
+
+SB_API int sb200_norm_bwd_noalloc(const void* dy, const void* x, const void* w, const float* mean, const float* rstd,
+                                  void* dx, void* dw, void* db, int M, int H, int rms, int accumulate, int dtype,
+                                  cudaStream_t stream) {
+  if (M <= 0 || H <= 0) return SB_OK;
+  if (H > SB200_NOALLOC_MAX_H) return SB_ERR_TOO_LARGE;
+  float* dw_partial = nullptr;
+  float* db_partial = nullptr;
+  int rc = noalloc_workspace(&dw_partial, &db_partial);
+  if (rc != SB_OK) return rc;
+  int rows = M < SB200_NOALLOC_MAX_PARTIAL_ROWS ? M : SB200_NOALLOC_MAX_PARTIAL_ROWS;
+  const bool want_db = !rms && db != nullptr;
+  SB_DISPATCH_DTYPE(dtype, T, {
+    constexpr int V = sb::Vec16<T>::N;
+    if (H % V != 0 || H > NORM_THREADS * V * NORM_MAX_ITERS) return SB_ERR_BAD_ARG;
+    if (rms)
+      norm_bwd_kernel<T, true><<<rows, NORM_THREADS, 0, stream>>>(
+          (const T*)dy, (const T*)x, (const T*)w, nullptr, rstd, (T*)dx, dw_partial, nullptr, M, H);
+    else
+      norm_bwd_kernel<T, false><<<rows, NORM_THREADS, 0, stream>>>(
+          (const T*)dy, (const T*)x, (const T*)w, mean, rstd, (T*)dx, dw_partial, want_db ? db_partial : nullptr, M,
+          H);
+    SB_CHECK_LAUNCH();
+    int blocks = (H + 255) / 256;
+    reduce_partials_kernel<T><<<blocks, 256, 0, stream>>>(dw_partial, (T*)dw, rows, H, accumulate);
+    if (want_db) reduce_partials_kernel<T><<<blocks, 256, 0, stream>>>(db_partial, (T*)db, rows, H, accumulate);
+  });
+  SB_CHECK_LAUNCH();
+  return SB_OK;
+}
