@@ -1,0 +1,926 @@
+// Packed-sequence (varlen) flash attention for sm_100a on tcgen05 tensor cores - forward and a
+// deterministic backward - with MQA/GQA, causal masking, document boundaries and sliding windows.
+//
+// It replaces the call the reference makes into the flash-attn package
+// (src/scaling/core/nn/attention/attention.py:216-271).  Tokens are packed: q[T, Hq, D], k/v[T, Hkv, D];
+// doc_start[t] / doc_end[t] give the token range of the document that token t belongs to, so a query
+// at t may attend keys in [max(doc_start[t], t - window), causal ? t : min(doc_end[t] - 1, t + window)].
+//
+// Forward, one CTA per (128-query tile, head):
+//   warp 0      TMA: Q once, then K / V tiles (128 keys) through 2-stage rings
+//   warp 1      tcgen05.mma issuer: S = Q K^T (accumulator double-buffered in TMEM) and O_j = P V_j
+//   warps 2-5   softmax: thread = query row = TMEM lane; online max / sum in the exp2 domain, P written
+//               as bf16 into shared memory in the 128-byte-swizzled K-major layout the next MMA reads,
+//               running output kept in registers and rescaled when the row maximum moves
+// Backward = three launches, no atomics (bitwise reproducible):
+//   fa_bwd_delta   delta[h, t] = sum_d dO * O
+//   fa_bwd_dkdv    one CTA per (128-key tile, KV head): loops over the query heads of the group and the
+//                  query tiles that see these keys; S^T = K Q^T, dP^T = V dO^T, then dV += P^T dO and
+//                  dK += dS^T Q accumulate in TMEM over the whole loop
+//   fa_bwd_dq      one CTA per (128-query tile, head): S = Q K^T, dP = dO V^T, dQ += dS K in TMEM
+// All waits are bounded; on expiry the CTA raises *status and leaves through the common exit (TMEM freed).
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace {
+
+constexpr int FA_THREADS = 192;
+constexpr int TILE = 128;          // queries per CTA and keys per step
+constexpr int PANEL_BYTES = 16384; // 128 rows x 64 bf16
+
+struct FaParams {
+  int T, Hq, Hkv;
+  int causal;
+  int window;        // < 0: unlimited
+  float scale_log2;  // softmax scale * log2(e)
+  float scale;       // softmax scale
+  const int* doc_start;
+  const int* doc_end;
+  int ldq_head, ldk_head, ldv_head;  // column offset between heads inside a token row (elements)
+  int ldo_head;                      // for dO / O tensor maps in the backward
+  void* O;           // [T, Hq, D]
+  float* lse2;       // [Hq, T]  log2-domain log-sum-exp of the scaled scores
+  const float* delta;  // [Hq, T]
+  void* dQ;          // [T, Hq, D]
+  void* dK;          // [T, Hkv, D]
+  void* dV;          // [T, Hkv, D]
+  int* status;
+};
+
+// byte offset of element (row r, column c) inside a K-major operand made of 64-column panels of
+// 128 rows x 128 bytes with the 128-byte swizzle (16-byte chunk index xor (row % 8))
+__device__ __forceinline__ uint32_t swz_offset(int r, int c) {
+  int panel = c >> 6, cc = c & 63;
+  int chunk = (cc >> 3) ^ (r & 7);
+  return panel * PANEL_BYTES + r * 128 + chunk * 16 + (cc & 7) * 2;
+}
+
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+__device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
+  __nv_bfloat162 t = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&t);
+}
+
+// K-major operand descriptor for k-step kk (16 elements per step) of a [128 x (64*panels)] tile
+__device__ __forceinline__ uint64_t desc_kmajor(uint32_t base, int kk) {
+  return sb::umma_smem_desc(base + (kk >> 2) * PANEL_BYTES + (kk & 3) * 32, 16, 1024);
+}
+// MN-major operand descriptor for k-step kk (16 rows per step) of a tile stored as [K rows x MN cols],
+// MN split in 64-column panels of 16 KiB
+__device__ __forceinline__ uint64_t desc_mnmajor(uint32_t base, int kk) {
+  return sb::umma_smem_desc(base + kk * 2048, PANEL_BYTES, 1024);
+}
+
+// allowed key range for query row t
+__device__ __forceinline__ void row_range(const FaParams& p, int t, int& lo, int& hi) {
+  if (t >= p.T) { lo = 1; hi = 0; return; }
+  lo = p.doc_start[t];
+  hi = p.causal ? t : p.doc_end[t] - 1;
+  if (p.window >= 0) {
+    lo = max(lo, t - p.window);
+    if (!p.causal) hi = min(hi, t + p.window);
+  }
+}
+
+// ============================================================================ forward
+template <int D>
+__global__ void __launch_bounds__(FA_THREADS, 1)
+    fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                  const __grid_constant__ CUtensorMap tmV, const FaParams p) {
+  constexpr int PANELS = D / 64;
+  constexpr int TILE_BYTES = PANELS * PANEL_BYTES;
+  constexpr int TMEM_COLS = 512;
+  constexpr uint32_t S_COL = 0;        // two S buffers of 128 columns
+  constexpr uint32_t O_COL = 256;      // two O buffers of D columns
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = smem;
+  uint8_t* sK = sQ + TILE_BYTES;           // 2 stages
+  uint8_t* sV = sK + 2 * TILE_BYTES;       // 2 stages
+  uint8_t* sP = sV + 2 * TILE_BYTES;       // 2 panels
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + 2 * PANEL_BYTES);
+  uint64_t* q_full = bars;          // 1
+  uint64_t* k_full = bars + 1;      // 2
+  uint64_t* k_empty = bars + 3;     // 2
+  uint64_t* v_full = bars + 5;      // 2
+  uint64_t* v_empty = bars + 7;     // 2
+  uint64_t* s_full = bars + 9;      // 2
+  uint64_t* p_full = bars + 11;     // 1
+  uint64_t* o_full = bars + 12;     // 2
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int q0 = blockIdx.x * TILE;
+  const int h = blockIdx.y;
+  const int hk = h / (p.Hq / p.Hkv);
+
+  // key tiles this query tile can see
+  int lo_first, hi_first, lo_last, hi_last;
+  row_range(p, q0, lo_first, hi_first);
+  row_range(p, min(q0 + TILE - 1, p.T - 1), lo_last, hi_last);
+  const int kv_begin = (lo_first / TILE);
+  const int kv_end = (hi_last / TILE) + 1;  // exclusive
+  const int n_tiles = kv_end - kv_begin;
+
+  if (threadIdx.x == 0) {
+    sb::mbar_init(q_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      sb::mbar_init(&k_full[i], 1);
+      sb::mbar_init(&k_empty[i], 1);
+      sb::mbar_init(&v_full[i], 1);
+      sb::mbar_init(&v_empty[i], 1);
+      sb::mbar_init(&s_full[i], 1);
+      sb::mbar_init(&o_full[i], 1);
+    }
+    sb::mbar_init(p_full, 4);
+    *abort_flag = 0;
+    sb::mbar_fence_init();
+  }
+  if (warp == 1) {
+    sb::tmem_alloc(tmem_slot, TMEM_COLS);
+    sb::tmem_relinquish();
+  }
+  sb::tc_fence_before();
+  __syncthreads();
+  sb::tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      sb::tma_prefetch_desc(&tmQ);
+      sb::tma_prefetch_desc(&tmK);
+      sb::tma_prefetch_desc(&tmV);
+      sb::mbar_expect_tx(q_full, TILE_BYTES);
+#pragma unroll
+      for (int pn = 0; pn < PANELS; ++pn) sb::tma_load_2d(sQ + pn * PANEL_BYTES, &tmQ, q_full, h * p.ldq_head + pn * 64, q0);
+      for (int j = 0; j < n_tiles; ++j) {
+        const int st = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        const int kv0 = (kv_begin + j) * TILE;
+        if (!sb::mbar_wait(&k_empty[st], ph ^ 1, abort_flag)) break;
+        sb::mbar_expect_tx(&k_full[st], TILE_BYTES);
+#pragma unroll
+        for (int pn = 0; pn < PANELS; ++pn)
+          sb::tma_load_2d(sK + st * TILE_BYTES + pn * PANEL_BYTES, &tmK, &k_full[st], hk * p.ldk_head + pn * 64, kv0);
+        if (!sb::mbar_wait(&v_empty[st], ph ^ 1, abort_flag)) break;
+        sb::mbar_expect_tx(&v_full[st], TILE_BYTES);
+#pragma unroll
+        for (int pn = 0; pn < PANELS; ++pn)
+          sb::tma_load_2d(sV + st * TILE_BYTES + pn * PANEL_BYTES, &tmV, &v_full[st], hk * p.ldv_head + pn * 64, kv0);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc_s = sb::umma_idesc_f16(TILE, TILE, 1, 0, 0);  // S = Q K^T: both K-major
+      const uint32_t idesc_o = sb::umma_idesc_f16(TILE, D, 1, 0, 1);     // O = P V: V is MN-major
+      const uint32_t q_addr = sb::smem_u32(sQ), p_addr = sb::smem_u32(sP);
+      bool ok = sb::mbar_wait(q_full, 0, abort_flag);
+      auto issue_s = [&](int j) -> bool {
+        const int st = j & 1;
+        if (!sb::mbar_wait(&k_full[st], (j >> 1) & 1, abort_flag)) return false;
+        sb::tc_fence_after();
+        const uint32_t k_addr = sb::smem_u32(sK + st * TILE_BYTES);
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk)
+          sb::umma_f16_ss(tmem_base + S_COL + st * TILE, desc_kmajor(q_addr, kk), desc_kmajor(k_addr, kk), idesc_s, kk != 0);
+        sb::umma_commit(&s_full[st]);
+        sb::umma_commit(&k_empty[st]);
+        return true;
+      };
+      if (ok) ok = issue_s(0);
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        const int st = j & 1;
+        if (j + 1 < n_tiles) { if (!issue_s(j + 1)) break; }
+        if (!sb::mbar_wait(p_full, j & 1, abort_flag)) break;
+        if (!sb::mbar_wait(&v_full[st], (j >> 1) & 1, abort_flag)) break;
+        sb::tc_fence_after();
+        const uint32_t v_addr = sb::smem_u32(sV + st * TILE_BYTES);
+#pragma unroll
+        for (int kk = 0; kk < TILE / 16; ++kk)
+          sb::umma_f16_ss(tmem_base + O_COL + st * D, desc_kmajor(p_addr, kk), desc_mnmajor(v_addr, kk), idesc_o, kk != 0);
+        sb::umma_commit(&o_full[st]);
+        sb::umma_commit(&v_empty[st]);
+      }
+    }
+  } else {
+    const int quad = warp & 3;
+    const int r = quad * 32 + lane;   // row inside the tile = TMEM lane
+    const int t = q0 + r;
+    int lo, hi;
+    row_range(p, t, lo, hi);
+    const uint32_t t_lane = tmem_base + ((uint32_t)(quad * 32) << 16);
+    float m = -1e30f, l = 0.f, alpha_prev = 1.f;
+    float o_acc[D];
+#pragma unroll
+    for (int i = 0; i < D; ++i) o_acc[i] = 0.f;
+    bool ok = true;
+    for (int j = 0; j < n_tiles && ok; ++j) {
+      const int st = j & 1;
+      const int kv0 = (kv_begin + j) * TILE;
+      if (!sb::mbar_wait(&s_full[st], (j >> 1) & 1, abort_flag)) { ok = false; break; }
+      sb::tc_fence_after();
+      // pass 1: row maximum
+      float mx = m;
+#pragma unroll 1
+      for (int ch = 0; ch < 4; ++ch) {
+        uint32_t v[32];
+        sb::tmem_ld32(t_lane + S_COL + st * TILE + ch * 32, v);
+        sb::tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const int kidx = kv0 + ch * 32 + i;
+          float x = __uint_as_float(v[i]) * p.scale_log2;
+          if (kidx >= lo && kidx <= hi) mx = fmaxf(mx, x);
+        }
+      }
+      const float alpha = fast_exp2(m - mx);
+      // the previous P V must be done before P is overwritten
+      if (j > 0) {
+        if (!sb::mbar_wait(&o_full[(j - 1) & 1], ((j - 1) >> 1) & 1, abort_flag)) { ok = false; break; }
+        sb::tc_fence_after();
+      }
+      // pass 2: probabilities -> shared memory (bf16, swizzled K-major), row sum
+      float rs = 0.f;
+#pragma unroll 1
+      for (int ch = 0; ch < 4; ++ch) {
+        uint32_t v[32];
+        sb::tmem_ld32(t_lane + S_COL + st * TILE + ch * 32, v);
+        sb::tmem_ld_wait();
+        float pr[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const int kidx = kv0 + ch * 32 + i;
+          float x = __uint_as_float(v[i]) * p.scale_log2;
+          float e = (kidx >= lo && kidx <= hi) ? fast_exp2(x - mx) : 0.f;
+          pr[i] = e;
+          rs += e;
+        }
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          uint4 u;
+          u.x = pack_bf16(pr[g * 8 + 0], pr[g * 8 + 1]);
+          u.y = pack_bf16(pr[g * 8 + 2], pr[g * 8 + 3]);
+          u.z = pack_bf16(pr[g * 8 + 4], pr[g * 8 + 5]);
+          u.w = pack_bf16(pr[g * 8 + 6], pr[g * 8 + 7]);
+          *reinterpret_cast<uint4*>(sP + swz_offset(r, ch * 32 + g * 8)) = u;
+        }
+      }
+      sb::fence_proxy_async_smem();
+      sb::tc_fence_before();
+      __syncwarp();
+      if (lane == 0) sb::mbar_arrive(p_full);
+      l = l * alpha + rs;
+      // fold the previous tile's partial output into the running output
+      if (j > 0) {
+        const int pst = (j - 1) & 1;
+#pragma unroll
+        for (int ch = 0; ch < D / 32; ++ch) {
+          uint32_t v[32];
+          sb::tmem_ld32(t_lane + O_COL + pst * D + ch * 32, v);
+          sb::tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o_acc[ch * 32 + i] = o_acc[ch * 32 + i] * alpha_prev + __uint_as_float(v[i]);
+        }
+      }
+      alpha_prev = alpha;
+      m = mx;
+    }
+    if (ok && n_tiles > 0) {
+      const int pst = (n_tiles - 1) & 1;
+      if (sb::mbar_wait(&o_full[pst], ((n_tiles - 1) >> 1) & 1, abort_flag)) {
+        sb::tc_fence_after();
+#pragma unroll
+        for (int ch = 0; ch < D / 32; ++ch) {
+          uint32_t v[32];
+          sb::tmem_ld32(t_lane + O_COL + pst * D + ch * 32, v);
+          sb::tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o_acc[ch * 32 + i] = o_acc[ch * 32 + i] * alpha_prev + __uint_as_float(v[i]);
+        }
+        if (t < p.T) {
+          const float inv = l > 0.f ? 1.f / l : 0.f;
+          __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(p.O) + ((long)t * p.Hq + h) * D;
+#pragma unroll
+          for (int g = 0; g < D / 8; ++g) {
+            uint4 u;
+            u.x = pack_bf16(o_acc[g * 8 + 0] * inv, o_acc[g * 8 + 1] * inv);
+            u.y = pack_bf16(o_acc[g * 8 + 2] * inv, o_acc[g * 8 + 3] * inv);
+            u.z = pack_bf16(o_acc[g * 8 + 4] * inv, o_acc[g * 8 + 5] * inv);
+            u.w = pack_bf16(o_acc[g * 8 + 6] * inv, o_acc[g * 8 + 7] * inv);
+            *reinterpret_cast<uint4*>(orow + g * 8) = u;
+          }
+          if (p.lse2) p.lse2[(long)h * p.T + t] = l > 0.f ? m + log2f(l) : -1e30f;
+        }
+      }
+    }
+  }
+
+  if (*abort_flag) {
+    for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+  }
+  sb::tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    sb::tc_fence_after();
+    sb::tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+  if (threadIdx.x == 0 && *abort_flag && p.status) *p.status = SB_ERR_WAIT_TIMEOUT;
+}
+
+// ============================================================================ backward: delta
+template <int D>
+__global__ void fa_bwd_delta_kernel(const __nv_bfloat16* __restrict__ O, const __nv_bfloat16* __restrict__ dO,
+                                    float* __restrict__ delta, int T, int Hq) {
+  // one warp per (t, h)
+  int w = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  int lane = threadIdx.x & 31;
+  if (w >= T * Hq) return;
+  int t = w / Hq, h = w % Hq;
+  const __nv_bfloat16* o = O + ((long)t * Hq + h) * D;
+  const __nv_bfloat16* d = dO + ((long)t * Hq + h) * D;
+  float s = 0.f;
+  for (int i = lane * 2; i < D; i += 64) {
+    float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(o + i));
+    float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(d + i));
+    s += a.x * b.x + a.y * b.y;
+  }
+  s = sb::warp_sum(s);
+  if (lane == 0) delta[(long)h * T + t] = s;
+}
+
+// ============================================================================ backward: dK, dV
+// CTA = (key tile, KV head).  Per (query head of the group, query tile):
+//   S^T = K Q^T, dP^T = V dO^T  ->  threads: P^T, dS^T (bf16, shared)  ->  dV += P^T dO, dK += dS^T Q
+template <int D>
+__global__ void __launch_bounds__(FA_THREADS, 1)
+    fa_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                       const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
+                       const FaParams p, const int q_tile_end_hint) {
+  constexpr int PANELS = D / 64;
+  constexpr int TILE_BYTES = PANELS * PANEL_BYTES;
+  constexpr int TMEM_COLS = 512;
+  constexpr uint32_t ST_COL = 0, DPT_COL = 128, DV_COL = 256, DK_COL = 256 + D;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sK = smem;
+  uint8_t* sV = sK + TILE_BYTES;
+  uint8_t* sQ = sV + TILE_BYTES;               // 1 stage (D = 128) - reloaded per iteration
+  uint8_t* sdO = sQ + TILE_BYTES;
+  uint8_t* sPT = sdO + TILE_BYTES;             // P^T  [keys x queries] 2 panels
+  uint8_t* sdST = sPT + 2 * PANEL_BYTES;       // dS^T [keys x queries] 2 panels
+  // per-query vectors, double buffered by iteration parity
+  float* s_lse = reinterpret_cast<float*>(sdST + 2 * PANEL_BYTES);  // 2 x 128
+  float* s_delta = s_lse + 2 * TILE;                                  // 2 x 128
+  int* s_lo = reinterpret_cast<int*>(s_delta + 2 * TILE);             // 2 x 128
+  int* s_hi = s_lo + 2 * TILE;                                        // 2 x 128
+  uint64_t* bars = reinterpret_cast<uint64_t*>(s_hi + 2 * TILE);
+  uint64_t* kv_full = bars;        // 1
+  uint64_t* qdo_full = bars + 1;   // 1
+  uint64_t* qdo_empty = bars + 2;  // 1
+  uint64_t* sdp_full = bars + 3;   // 1: S^T and dP^T ready
+  uint64_t* pds_full = bars + 4;   // 1 (count 4): P^T and dS^T written
+  uint64_t* acc_done = bars + 5;   // 1: dV / dK MMAs of the iteration retired (smem P^T/dS^T, TMEM S^T/dP^T free)
+  uint64_t* vec_ready = bars + 6;  // 1 (count 4): per-query vectors staged in shared memory
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int kv0 = blockIdx.x * TILE;
+  const int hk = blockIdx.y;
+  const int group = p.Hq / p.Hkv;
+
+  // query tiles that can see this key tile: from the tile holding the first key's earliest query to the
+  // tile holding the last key's latest query
+  const int k_last = min(kv0 + TILE - 1, p.T - 1);
+  int q_lo = kv0;                                  // causal: queries at or after the key
+  int q_hi = p.doc_end[k_last] - 1;                // queries of the last key's document
+  if (!p.causal) {
+    q_lo = p.doc_start[kv0 < p.T ? kv0 : p.T - 1];
+    if (p.window >= 0) q_lo = max(q_lo, kv0 - p.window);
+  }
+  if (p.window >= 0) q_hi = min(q_hi, k_last + p.window);
+  const int qt_begin = q_lo / TILE;
+  const int qt_end = min(q_hi / TILE + 1, q_tile_end_hint);
+  const int n_qt = max(qt_end - qt_begin, 0);
+  const int n_iter = n_qt * group;
+
+  if (threadIdx.x == 0) {
+    sb::mbar_init(kv_full, 1);
+    sb::mbar_init(qdo_full, 1);
+    sb::mbar_init(qdo_empty, 1);
+    sb::mbar_init(sdp_full, 1);
+    sb::mbar_init(pds_full, 4);
+    sb::mbar_init(acc_done, 1);
+    sb::mbar_init(vec_ready, 4);
+    *abort_flag = 0;
+    sb::mbar_fence_init();
+  }
+  if (warp == 1) {
+    sb::tmem_alloc(tmem_slot, TMEM_COLS);
+    sb::tmem_relinquish();
+  }
+  sb::tc_fence_before();
+  __syncthreads();
+  sb::tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      sb::mbar_expect_tx(kv_full, 2 * TILE_BYTES);
+#pragma unroll
+      for (int pn = 0; pn < PANELS; ++pn) {
+        sb::tma_load_2d(sK + pn * PANEL_BYTES, &tmK, kv_full, hk * p.ldk_head + pn * 64, kv0);
+        sb::tma_load_2d(sV + pn * PANEL_BYTES, &tmV, kv_full, hk * p.ldv_head + pn * 64, kv0);
+      }
+      for (int it = 0; it < n_iter; ++it) {
+        const int h = hk * group + it / n_qt;
+        const int q0 = (qt_begin + it % n_qt) * TILE;
+        if (!sb::mbar_wait(qdo_empty, (it & 1) ^ 1, abort_flag)) break;
+        sb::mbar_expect_tx(qdo_full, 2 * TILE_BYTES);
+#pragma unroll
+        for (int pn = 0; pn < PANELS; ++pn) {
+          sb::tma_load_2d(sQ + pn * PANEL_BYTES, &tmQ, qdo_full, h * p.ldq_head + pn * 64, q0);
+          sb::tma_load_2d(sdO + pn * PANEL_BYTES, &tmdO, qdo_full, h * p.ldo_head + pn * 64, q0);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc_nt = sb::umma_idesc_f16(TILE, TILE, 1, 0, 0);  // [keys x D] x [queries x D]^T
+      const uint32_t idesc_acc = sb::umma_idesc_f16(TILE, D, 1, 0, 1);    // [keys x q] x [q x D] (B MN-major)
+      const uint32_t k_addr = sb::smem_u32(sK), v_addr = sb::smem_u32(sV), q_addr = sb::smem_u32(sQ),
+                     do_addr = sb::smem_u32(sdO), pt_addr = sb::smem_u32(sPT), dst_addr = sb::smem_u32(sdST);
+      bool ok = sb::mbar_wait(kv_full, 0, abort_flag);
+      for (int it = 0; it < n_iter && ok; ++it) {
+        if (!sb::mbar_wait(qdo_full, it & 1, abort_flag)) break;
+        // S^T / dP^T buffers and P^T / dS^T tiles are free once the previous accumulation MMAs retired
+        if (it > 0 && !sb::mbar_wait(acc_done, (it - 1) & 1, abort_flag)) break;
+        sb::tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk)
+          sb::umma_f16_ss(tmem_base + ST_COL, desc_kmajor(k_addr, kk), desc_kmajor(q_addr, kk), idesc_nt, kk != 0);
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk)
+          sb::umma_f16_ss(tmem_base + DPT_COL, desc_kmajor(v_addr, kk), desc_kmajor(do_addr, kk), idesc_nt, kk != 0);
+        sb::umma_commit(sdp_full);
+        if (!sb::mbar_wait(pds_full, it & 1, abort_flag)) break;
+        sb::tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < TILE / 16; ++kk)
+          sb::umma_f16_ss(tmem_base + DV_COL, desc_kmajor(pt_addr, kk), desc_mnmajor(do_addr, kk), idesc_acc, (it | kk) != 0);
+#pragma unroll
+        for (int kk = 0; kk < TILE / 16; ++kk)
+          sb::umma_f16_ss(tmem_base + DK_COL, desc_kmajor(dst_addr, kk), desc_mnmajor(q_addr, kk), idesc_acc, (it | kk) != 0);
+        sb::umma_commit(acc_done);
+        sb::umma_commit(qdo_empty);
+      }
+    }
+  } else {
+    const int quad = warp & 3;
+    const int r = quad * 32 + lane;  // key row inside the tile
+    const int kidx = kv0 + r;
+    const uint32_t t_lane = tmem_base + ((uint32_t)(quad * 32) << 16);
+    bool ok = true;
+    for (int it = 0; it < n_iter && ok; ++it) {
+      const int h = hk * group + it / n_qt;
+      const int q0 = (qt_begin + it % n_qt) * TILE;
+      // stage the per-query vectors of this iteration into the buffer of its parity; the buffer was last read
+      // two iterations ago, and every warp has passed the vec_ready wait of the iteration in between
+      const int vb = (it & 1) * TILE;
+      const float* v_lse = s_lse + vb;
+      const float* v_delta = s_delta + vb;
+      const int* v_lo = s_lo + vb;
+      const int* v_hi = s_hi + vb;
+      {
+        const int t = q0 + r;
+        int lo, hi;
+        row_range(p, t, lo, hi);
+        s_lo[vb + r] = lo;
+        s_hi[vb + r] = hi;
+        s_lse[vb + r] = t < p.T ? p.lse2[(long)h * p.T + t] : 0.f;
+        s_delta[vb + r] = t < p.T ? p.delta[(long)h * p.T + t] : 0.f;
+      }
+      // all four warps must have staged before anyone reads
+      __syncwarp();
+      if (lane == 0) sb::mbar_arrive(vec_ready);
+      if (!sb::mbar_wait(vec_ready, it & 1, abort_flag)) { ok = false; break; }
+      if (!sb::mbar_wait(sdp_full, it & 1, abort_flag)) { ok = false; break; }
+      sb::tc_fence_after();
+#pragma unroll 1
+      for (int ch = 0; ch < 4; ++ch) {
+        uint32_t s[32], dp[32];
+        sb::tmem_ld32(t_lane + ST_COL + ch * 32, s);
+        sb::tmem_ld32(t_lane + DPT_COL + ch * 32, dp);
+        sb::tmem_ld_wait();
+        float pv[32], dsv[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const int c = ch * 32 + i;  // query column
+          const bool ok_el = kidx >= v_lo[c] && kidx <= v_hi[c];
+          const float pr = ok_el ? fast_exp2(__uint_as_float(s[i]) * p.scale_log2 - v_lse[c]) : 0.f;
+          pv[i] = pr;
+          dsv[i] = pr * (__uint_as_float(dp[i]) - v_delta[c]) * p.scale;
+        }
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          uint4 u, w;
+          u.x = pack_bf16(pv[g * 8 + 0], pv[g * 8 + 1]);
+          u.y = pack_bf16(pv[g * 8 + 2], pv[g * 8 + 3]);
+          u.z = pack_bf16(pv[g * 8 + 4], pv[g * 8 + 5]);
+          u.w = pack_bf16(pv[g * 8 + 6], pv[g * 8 + 7]);
+          w.x = pack_bf16(dsv[g * 8 + 0], dsv[g * 8 + 1]);
+          w.y = pack_bf16(dsv[g * 8 + 2], dsv[g * 8 + 3]);
+          w.z = pack_bf16(dsv[g * 8 + 4], dsv[g * 8 + 5]);
+          w.w = pack_bf16(dsv[g * 8 + 6], dsv[g * 8 + 7]);
+          const uint32_t off = swz_offset(r, ch * 32 + g * 8);
+          *reinterpret_cast<uint4*>(sPT + off) = u;
+          *reinterpret_cast<uint4*>(sdST + off) = w;
+        }
+      }
+      sb::fence_proxy_async_smem();
+      sb::tc_fence_before();
+      __syncwarp();
+      if (lane == 0) sb::mbar_arrive(pds_full);
+    }
+    // results
+    if (ok && n_iter > 0 && sb::mbar_wait(acc_done, (n_iter - 1) & 1, abort_flag)) {
+      sb::tc_fence_after();
+      __nv_bfloat16* dk = reinterpret_cast<__nv_bfloat16*>(p.dK) + ((long)kidx * p.Hkv + hk) * D;
+      __nv_bfloat16* dv = reinterpret_cast<__nv_bfloat16*>(p.dV) + ((long)kidx * p.Hkv + hk) * D;
+#pragma unroll 1
+      for (int ch = 0; ch < D / 32; ++ch) {
+        uint32_t a[32], b[32];
+        sb::tmem_ld32(t_lane + DV_COL + ch * 32, a);
+        sb::tmem_ld32(t_lane + DK_COL + ch * 32, b);
+        sb::tmem_ld_wait();
+        if (kidx < p.T) {
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            uint4 u, w;
+            u.x = pack_bf16(__uint_as_float(a[g * 8 + 0]), __uint_as_float(a[g * 8 + 1]));
+            u.y = pack_bf16(__uint_as_float(a[g * 8 + 2]), __uint_as_float(a[g * 8 + 3]));
+            u.z = pack_bf16(__uint_as_float(a[g * 8 + 4]), __uint_as_float(a[g * 8 + 5]));
+            u.w = pack_bf16(__uint_as_float(a[g * 8 + 6]), __uint_as_float(a[g * 8 + 7]));
+            w.x = pack_bf16(__uint_as_float(b[g * 8 + 0]), __uint_as_float(b[g * 8 + 1]));
+            w.y = pack_bf16(__uint_as_float(b[g * 8 + 2]), __uint_as_float(b[g * 8 + 3]));
+            w.z = pack_bf16(__uint_as_float(b[g * 8 + 4]), __uint_as_float(b[g * 8 + 5]));
+            w.w = pack_bf16(__uint_as_float(b[g * 8 + 6]), __uint_as_float(b[g * 8 + 7]));
+            *reinterpret_cast<uint4*>(dv + ch * 32 + g * 8) = u;
+            *reinterpret_cast<uint4*>(dk + ch * 32 + g * 8) = w;
+          }
+        }
+      }
+    } else if (ok && n_iter == 0 && kidx < p.T) {
+      __nv_bfloat16* dk = reinterpret_cast<__nv_bfloat16*>(p.dK) + ((long)kidx * p.Hkv + hk) * D;
+      __nv_bfloat16* dv = reinterpret_cast<__nv_bfloat16*>(p.dV) + ((long)kidx * p.Hkv + hk) * D;
+      for (int i = 0; i < D; i += 8) {
+        *reinterpret_cast<uint4*>(dk + i) = make_uint4(0, 0, 0, 0);
+        *reinterpret_cast<uint4*>(dv + i) = make_uint4(0, 0, 0, 0);
+      }
+    }
+  }
+
+  if (*abort_flag) {
+    for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+  }
+  sb::tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    sb::tc_fence_after();
+    sb::tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+  if (threadIdx.x == 0 && *abort_flag && p.status) *p.status = SB_ERR_WAIT_TIMEOUT;
+}
+
+// ============================================================================ backward: dQ
+// CTA = (query tile, head).  Per key tile: S = Q K^T, dP = dO V^T -> threads: dS (bf16) -> dQ += dS K
+template <int D>
+__global__ void __launch_bounds__(FA_THREADS, 1)
+    fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                     const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
+                     const FaParams p) {
+  constexpr int PANELS = D / 64;
+  constexpr int TILE_BYTES = PANELS * PANEL_BYTES;
+  constexpr int TMEM_COLS = 512;
+  constexpr uint32_t S_COL = 0, DP_COL = 128, DQ_COL = 256;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = smem;
+  uint8_t* sdO = sQ + TILE_BYTES;
+  uint8_t* sK = sdO + TILE_BYTES;
+  uint8_t* sV = sK + TILE_BYTES;
+  uint8_t* sdS = sV + TILE_BYTES;  // [queries x keys] 2 panels
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sdS + 2 * PANEL_BYTES);
+  uint64_t* qdo_full = bars;
+  uint64_t* kv_full = bars + 1;
+  uint64_t* kv_empty = bars + 2;
+  uint64_t* sdp_full = bars + 3;
+  uint64_t* ds_full = bars + 4;   // count 4
+  uint64_t* acc_done = bars + 5;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 6);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int q0 = blockIdx.x * TILE;
+  const int h = blockIdx.y;
+  const int hk = h / (p.Hq / p.Hkv);
+  int lo_first, hi_first, lo_last, hi_last;
+  row_range(p, q0, lo_first, hi_first);
+  row_range(p, min(q0 + TILE - 1, p.T - 1), lo_last, hi_last);
+  const int kv_begin = lo_first / TILE;
+  const int n_tiles = hi_last / TILE + 1 - kv_begin;
+
+  if (threadIdx.x == 0) {
+    sb::mbar_init(qdo_full, 1);
+    sb::mbar_init(kv_full, 1);
+    sb::mbar_init(kv_empty, 1);
+    sb::mbar_init(sdp_full, 1);
+    sb::mbar_init(ds_full, 4);
+    sb::mbar_init(acc_done, 1);
+    *abort_flag = 0;
+    sb::mbar_fence_init();
+  }
+  if (warp == 1) {
+    sb::tmem_alloc(tmem_slot, TMEM_COLS);
+    sb::tmem_relinquish();
+  }
+  sb::tc_fence_before();
+  __syncthreads();
+  sb::tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      sb::mbar_expect_tx(qdo_full, 2 * TILE_BYTES);
+#pragma unroll
+      for (int pn = 0; pn < PANELS; ++pn) {
+        sb::tma_load_2d(sQ + pn * PANEL_BYTES, &tmQ, qdo_full, h * p.ldq_head + pn * 64, q0);
+        sb::tma_load_2d(sdO + pn * PANEL_BYTES, &tmdO, qdo_full, h * p.ldo_head + pn * 64, q0);
+      }
+      for (int j = 0; j < n_tiles; ++j) {
+        const int kv0 = (kv_begin + j) * TILE;
+        if (!sb::mbar_wait(kv_empty, (j & 1) ^ 1, abort_flag)) break;
+        sb::mbar_expect_tx(kv_full, 2 * TILE_BYTES);
+#pragma unroll
+        for (int pn = 0; pn < PANELS; ++pn) {
+          sb::tma_load_2d(sK + pn * PANEL_BYTES, &tmK, kv_full, hk * p.ldk_head + pn * 64, kv0);
+          sb::tma_load_2d(sV + pn * PANEL_BYTES, &tmV, kv_full, hk * p.ldv_head + pn * 64, kv0);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc_nt = sb::umma_idesc_f16(TILE, TILE, 1, 0, 0);
+      const uint32_t idesc_acc = sb::umma_idesc_f16(TILE, D, 1, 0, 1);
+      const uint32_t q_addr = sb::smem_u32(sQ), do_addr = sb::smem_u32(sdO), k_addr = sb::smem_u32(sK),
+                     v_addr = sb::smem_u32(sV), ds_addr = sb::smem_u32(sdS);
+      bool ok = sb::mbar_wait(qdo_full, 0, abort_flag);
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        if (!sb::mbar_wait(kv_full, j & 1, abort_flag)) break;
+        if (j > 0 && !sb::mbar_wait(acc_done, (j - 1) & 1, abort_flag)) break;
+        sb::tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk)
+          sb::umma_f16_ss(tmem_base + S_COL, desc_kmajor(q_addr, kk), desc_kmajor(k_addr, kk), idesc_nt, kk != 0);
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk)
+          sb::umma_f16_ss(tmem_base + DP_COL, desc_kmajor(do_addr, kk), desc_kmajor(v_addr, kk), idesc_nt, kk != 0);
+        sb::umma_commit(sdp_full);
+        if (!sb::mbar_wait(ds_full, j & 1, abort_flag)) break;
+        sb::tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < TILE / 16; ++kk)
+          sb::umma_f16_ss(tmem_base + DQ_COL, desc_kmajor(ds_addr, kk), desc_mnmajor(k_addr, kk), idesc_acc, (j | kk) != 0);
+        sb::umma_commit(acc_done);
+        sb::umma_commit(kv_empty);
+      }
+    }
+  } else {
+    const int quad = warp & 3;
+    const int r = quad * 32 + lane;
+    const int t = q0 + r;
+    int lo, hi;
+    row_range(p, t, lo, hi);
+    const float lse = t < p.T ? p.lse2[(long)h * p.T + t] : 0.f;
+    const float dl = t < p.T ? p.delta[(long)h * p.T + t] : 0.f;
+    const uint32_t t_lane = tmem_base + ((uint32_t)(quad * 32) << 16);
+    bool ok = true;
+    for (int j = 0; j < n_tiles && ok; ++j) {
+      const int kv0 = (kv_begin + j) * TILE;
+      if (!sb::mbar_wait(sdp_full, j & 1, abort_flag)) { ok = false; break; }
+      sb::tc_fence_after();
+#pragma unroll 1
+      for (int ch = 0; ch < 4; ++ch) {
+        uint32_t s[32], dp[32];
+        sb::tmem_ld32(t_lane + S_COL + ch * 32, s);
+        sb::tmem_ld32(t_lane + DP_COL + ch * 32, dp);
+        sb::tmem_ld_wait();
+        float dsv[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const int kidx = kv0 + ch * 32 + i;
+          const float pr = (kidx >= lo && kidx <= hi) ? fast_exp2(__uint_as_float(s[i]) * p.scale_log2 - lse) : 0.f;
+          dsv[i] = pr * (__uint_as_float(dp[i]) - dl) * p.scale;
+        }
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          uint4 w;
+          w.x = pack_bf16(dsv[g * 8 + 0], dsv[g * 8 + 1]);
+          w.y = pack_bf16(dsv[g * 8 + 2], dsv[g * 8 + 3]);
+          w.z = pack_bf16(dsv[g * 8 + 4], dsv[g * 8 + 5]);
+          w.w = pack_bf16(dsv[g * 8 + 6], dsv[g * 8 + 7]);
+          *reinterpret_cast<uint4*>(sdS + swz_offset(r, ch * 32 + g * 8)) = w;
+        }
+      }
+      sb::fence_proxy_async_smem();
+      sb::tc_fence_before();
+      __syncwarp();
+      if (lane == 0) sb::mbar_arrive(ds_full);
+    }
+    if (ok && n_tiles > 0 && sb::mbar_wait(acc_done, (n_tiles - 1) & 1, abort_flag)) {
+      sb::tc_fence_after();
+      __nv_bfloat16* dq = reinterpret_cast<__nv_bfloat16*>(p.dQ) + ((long)t * p.Hq + h) * D;
+#pragma unroll 1
+      for (int ch = 0; ch < D / 32; ++ch) {
+        uint32_t a[32];
+        sb::tmem_ld32(t_lane + DQ_COL + ch * 32, a);
+        sb::tmem_ld_wait();
+        if (t < p.T) {
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            uint4 u;
+            u.x = pack_bf16(__uint_as_float(a[g * 8 + 0]), __uint_as_float(a[g * 8 + 1]));
+            u.y = pack_bf16(__uint_as_float(a[g * 8 + 2]), __uint_as_float(a[g * 8 + 3]));
+            u.z = pack_bf16(__uint_as_float(a[g * 8 + 4]), __uint_as_float(a[g * 8 + 5]));
+            u.w = pack_bf16(__uint_as_float(a[g * 8 + 6]), __uint_as_float(a[g * 8 + 7]));
+            *reinterpret_cast<uint4*>(dq + ch * 32 + g * 8) = u;
+          }
+        }
+      }
+    }
+  }
+
+  if (*abort_flag) {
+    for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+  }
+  sb::tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    sb::tc_fence_after();
+    sb::tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+  if (threadIdx.x == 0 && *abort_flag && p.status) *p.status = SB_ERR_WAIT_TIMEOUT;
+}
+
+// ============================================================================ host
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn fa_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn) return fn;
+  void* ptr = nullptr;
+  cudaDriverEntryPointQueryResult qres;
+  if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) != cudaSuccess ||
+      qres != cudaDriverEntryPointSuccess)
+    return nullptr;
+  fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  return fn;
+}
+int g_fa_last_driver_error = 0;
+// [T rows, cols] bf16 view with row pitch ld (elements); box = 128 rows x 64 columns, 128-byte swizzle
+int fa_tmap(CUtensorMap* tm, const void* base, long T, long cols, long ld) {
+  EncodeTiledFn fn = fa_encode_fn();
+  if (!fn) return SB_ERR_DRIVER;
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)T};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  cuuint32_t box[2] = {64, TILE};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) g_fa_last_driver_error = (int)r;
+  return r == CUDA_SUCCESS ? SB_OK : SB_ERR_DRIVER;
+}
+
+template <int D> constexpr int fa_fwd_smem() { return (D / 64) * PANEL_BYTES * 5 + 2 * PANEL_BYTES + 1024 + 256; }
+template <int D> constexpr int fa_dkdv_smem() { return (D / 64) * PANEL_BYTES * 4 + 4 * PANEL_BYTES + 8 * TILE * 4 + 1024 + 256; }
+template <int D> constexpr int fa_dq_smem() { return (D / 64) * PANEL_BYTES * 4 + 2 * PANEL_BYTES + 1024 + 256; }
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+}  // namespace
+
+// CUresult of the last failed tensor-map encode of the attention entry points (0 if none failed)
+SB_API int sb200_fa_last_driver_error() { return g_fa_last_driver_error; }
+
+// q: [T, Hq, D] view with token pitch ldq_tok and head pitch ldq_head (elements); k, v likewise; o: [T, Hq, D] contiguous.
+SB_API int sb200_fa_fwd(const void* q, const void* k, const void* v, void* o, float* lse2, const int* doc_start,
+                        const int* doc_end, int T, int Hq, int Hkv, int D, long ldq_tok, int ldq_head, long ldk_tok,
+                        int ldk_head, long ldv_tok, int ldv_head, int causal, int window, float scale, int* status,
+                        cudaStream_t stream) {
+  if (T <= 0 || Hq <= 0) return SB_OK;
+  if ((D != 64 && D != 128) || Hkv <= 0 || Hq % Hkv) return SB_ERR_BAD_ARG;
+  if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o)) return SB_ERR_BAD_ARG;
+  if ((ldq_tok % 8) || (ldk_tok % 8) || (ldv_tok % 8) || (ldq_head % 8) || (ldk_head % 8) || (ldv_head % 8))
+    return SB_ERR_BAD_ARG;
+  CUtensorMap tmQ, tmK, tmV;
+  int rc;
+  if ((rc = fa_tmap(&tmQ, q, T, (long)(Hq - 1) * ldq_head + D, ldq_tok))) return rc;
+  if ((rc = fa_tmap(&tmK, k, T, (long)(Hkv - 1) * ldk_head + D, ldk_tok))) return rc;
+  if ((rc = fa_tmap(&tmV, v, T, (long)(Hkv - 1) * ldv_head + D, ldv_tok))) return rc;
+  FaParams p = {};
+  p.T = T; p.Hq = Hq; p.Hkv = Hkv; p.causal = causal; p.window = window;
+  p.scale = scale; p.scale_log2 = scale * 1.4426950408889634f;
+  p.doc_start = doc_start; p.doc_end = doc_end;
+  p.ldq_head = ldq_head; p.ldk_head = ldk_head; p.ldv_head = ldv_head;
+  p.O = o; p.lse2 = lse2; p.status = status;
+  dim3 grid((T + TILE - 1) / TILE, Hq);
+  if (D == 64) {
+    static bool set = false;
+    if (!set) {
+      cudaError_t e = cudaFuncSetAttribute(fa_fwd_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, fa_fwd_smem<64>());
+      if (e != cudaSuccess) return (int)e;
+      set = true;
+    }
+    fa_fwd_kernel<64><<<grid, FA_THREADS, fa_fwd_smem<64>(), stream>>>(tmQ, tmK, tmV, p);
+  } else {
+    static bool set = false;
+    if (!set) {
+      cudaError_t e = cudaFuncSetAttribute(fa_fwd_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, fa_fwd_smem<128>());
+      if (e != cudaSuccess) return (int)e;
+      set = true;
+    }
+    fa_fwd_kernel<128><<<grid, FA_THREADS, fa_fwd_smem<128>(), stream>>>(tmQ, tmK, tmV, p);
+  }
+  SB_CHECK_LAUNCH();
+  return SB_OK;
+}
+
+// Backward.  o, d_o, dq: [T, Hq, D] contiguous; dk, dv: [T, Hkv, D] contiguous; delta: scratch [Hq, T] floats.
+SB_API int sb200_fa_bwd(const void* q, const void* k, const void* v, const void* o, const void* d_o, const float* lse2,
+                        float* delta, void* dq, void* dk, void* dv, const int* doc_start, const int* doc_end, int T,
+                        int Hq, int Hkv, int D, long ldq_tok, int ldq_head, long ldk_tok, int ldk_head, long ldv_tok,
+                        int ldv_head, int causal, int window, float scale, int* status, cudaStream_t stream) {
+  if (T <= 0 || Hq <= 0) return SB_OK;
+  if ((D != 64 && D != 128) || Hkv <= 0 || Hq % Hkv) return SB_ERR_BAD_ARG;
+  if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o) || !aligned16(d_o) || !aligned16(dq) ||
+      !aligned16(dk) || !aligned16(dv))
+    return SB_ERR_BAD_ARG;
+  CUtensorMap tmQ, tmK, tmV, tmdO;
+  int rc;
+  if ((rc = fa_tmap(&tmQ, q, T, (long)(Hq - 1) * ldq_head + D, ldq_tok))) return rc;
+  if ((rc = fa_tmap(&tmK, k, T, (long)(Hkv - 1) * ldk_head + D, ldk_tok))) return rc;
+  if ((rc = fa_tmap(&tmV, v, T, (long)(Hkv - 1) * ldv_head + D, ldv_tok))) return rc;
+  if ((rc = fa_tmap(&tmdO, d_o, T, (long)Hq * D, (long)Hq * D))) return rc;
+  FaParams p = {};
+  p.T = T; p.Hq = Hq; p.Hkv = Hkv; p.causal = causal; p.window = window;
+  p.scale = scale; p.scale_log2 = scale * 1.4426950408889634f;
+  p.doc_start = doc_start; p.doc_end = doc_end;
+  p.ldq_head = ldq_head; p.ldk_head = ldk_head; p.ldv_head = ldv_head; p.ldo_head = D;
+  p.lse2 = const_cast<float*>(lse2); p.delta = delta; p.dQ = dq; p.dK = dk; p.dV = dv; p.status = status;
+  const int tiles = (T + TILE - 1) / TILE;
+  {
+    long warps = (long)T * Hq;
+    int blocks = (int)((warps * 32 + 255) / 256);
+    if (D == 64)
+      fa_bwd_delta_kernel<64><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)o, (const __nv_bfloat16*)d_o, delta, T, Hq);
+    else
+      fa_bwd_delta_kernel<128><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)o, (const __nv_bfloat16*)d_o, delta, T, Hq);
+    SB_CHECK_LAUNCH();
+  }
+  if (D == 64) {
+    static bool set = false;
+    if (!set) {
+      cudaError_t e = cudaFuncSetAttribute(fa_bwd_dkdv_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, fa_dkdv_smem<64>());
+      if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(fa_bwd_dq_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, fa_dq_smem<64>());
+      if (e != cudaSuccess) return (int)e;
+      set = true;
+    }
+    fa_bwd_dkdv_kernel<64><<<dim3(tiles, Hkv), FA_THREADS, fa_dkdv_smem<64>(), stream>>>(tmQ, tmK, tmV, tmdO, p, tiles);
+    SB_CHECK_LAUNCH();
+    fa_bwd_dq_kernel<64><<<dim3(tiles, Hq), FA_THREADS, fa_dq_smem<64>(), stream>>>(tmQ, tmK, tmV, tmdO, p);
+  } else {
+    static bool set = false;
+    if (!set) {
+      cudaError_t e = cudaFuncSetAttribute(fa_bwd_dkdv_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, fa_dkdv_smem<128>());
+      if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(fa_bwd_dq_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, fa_dq_smem<128>());
+      if (e != cudaSuccess) return (int)e;
+      set = true;
+    }
+    fa_bwd_dkdv_kernel<128><<<dim3(tiles, Hkv), FA_THREADS, fa_dkdv_smem<128>(), stream>>>(tmQ, tmK, tmV, tmdO, p, tiles);
+    SB_CHECK_LAUNCH();
+    fa_bwd_dq_kernel<128><<<dim3(tiles, Hq), FA_THREADS, fa_dq_smem<128>(), stream>>>(tmQ, tmK, tmV, tmdO, p);
+  }
+  SB_CHECK_LAUNCH();
+  return SB_OK;
+}

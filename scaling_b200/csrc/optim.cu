@@ -163,3 +163,13 @@ SB_API int sb200_embedding_bwd(const long* sorted_ids, const long* order, const 
   SB_CHECK_LAUNCH();
   return SB_OK;
 }
+
+// Make `device` current on the calling host thread.  The library carries its own copy of the CUDA runtime, whose
+// per-thread device selection is independent of the one in the host framework; worker threads that the framework
+// creates (e.g. for backward passes) call this once before their first launch or tensor-map encode.
+SB_API int sb200_bind_device(int device) {
+  cudaError_t e = cudaSetDevice(device);
+  if (e != cudaSuccess) return (int)e;
+  e = cudaFree(nullptr);  // forces the primary context to be current on this thread
+  return (int)e;
+}

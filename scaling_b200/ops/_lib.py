@@ -90,6 +90,16 @@ class _Counting:
         self._handle = handle
         self.calls = 0
         self._cache: dict[str, object] = {}
+        self._tls = threading.local()
+
+    def _bind_thread(self) -> None:
+        """First call from a host thread: select torch's current device in the library's own CUDA runtime."""
+        dev = torch.cuda.current_device()
+        if getattr(self._tls, "device", None) != dev:
+            rc = self._handle.sb200_bind_device(int(dev))
+            if rc != 0:
+                raise KernelError(f"sb200_bind_device({dev}) failed with CUDA error {rc}")
+            self._tls.device = dev
 
     def __getattr__(self, name: str):
         fn = self._cache.get(name)
@@ -99,6 +109,7 @@ class _Counting:
                 fn = raw
             else:
                 def fn(*args, _raw=raw, _self=self):
+                    _self._bind_thread()
                     _self.calls += 1
                     return _raw(*args)
             self._cache[name] = fn

@@ -1,0 +1,104 @@
+"""Autograd wrapper of the tcgen05 flash-attention kernels (``sb200_fa_fwd`` / ``sb200_fa_bwd``)."""
+
+from __future__ import annotations
+
+from ctypes import c_float, c_int, c_long, c_void_p
+from typing import Optional
+
+import torch
+
+from . import _lib
+from ._lib import check, lib, stream
+from .functional import status_word
+
+_DECLARED = False
+
+
+def _declare() -> None:
+    global _DECLARED
+    if _DECLARED:
+        return
+    _lib.declare("sb200_fa_fwd", [c_void_p] * 7 + [c_int] * 4 + [c_long, c_int, c_long, c_int, c_long, c_int, c_int,
+                                                                 c_int, c_float, c_void_p, c_void_p])
+    _lib.declare("sb200_fa_bwd", [c_void_p] * 12 + [c_int] * 4 + [c_long, c_int, c_long, c_int, c_long, c_int, c_int,
+                                                                  c_int, c_float, c_void_p, c_void_p])
+    _DECLARED = True
+
+
+_DOC_CACHE: dict[str, tuple] = {}
+
+
+def doc_ranges(cu_seqlens: torch.Tensor, total: int) -> tuple[torch.Tensor, torch.Tensor]:
+    """Per token: first token index of its document and one past its last (int32, cached per cu_seqlens tensor)."""
+    key = (cu_seqlens.data_ptr(), cu_seqlens._version, total, cu_seqlens.numel())
+    hit = _DOC_CACHE.get("last")
+    if hit is not None and hit[0] == key:
+        return hit[1], hit[2]
+    cu = cu_seqlens.to(torch.int64)
+    idx = torch.arange(total, device=cu.device)
+    doc = (torch.searchsorted(cu, idx, right=True) - 1).clamp_(0, cu.numel() - 2)
+    start = cu[doc].to(torch.int32).contiguous()
+    end = cu[doc + 1].to(torch.int32).contiguous()
+    _DOC_CACHE["last"] = (key, start, end, cu_seqlens)  # keep cu_seqlens alive so the pointer stays unique
+    return start, end
+
+
+def _strides_ok(t: torch.Tensor) -> bool:
+    return t.stride(2) == 1 and t.stride(0) % 8 == 0 and t.stride(1) % 8 == 0 and t.data_ptr() % 16 == 0
+
+
+def _prep(t: torch.Tensor) -> torch.Tensor:
+    return t if _strides_ok(t) else t.contiguous()
+
+
+class _FlashAttention(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, doc_start, doc_end, causal, scale, window):  # type: ignore[override]
+        _declare()
+        q, k, v = _prep(q), _prep(k), _prep(v)
+        T, Hq, D = q.shape
+        Hkv = k.shape[1]
+        o = torch.empty((T, Hq, D), dtype=q.dtype, device=q.device)
+        lse2 = torch.empty((Hq, T), dtype=torch.float32, device=q.device)
+        check(
+            lib().sb200_fa_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse2.data_ptr(),
+                               doc_start.data_ptr(), doc_end.data_ptr(), T, Hq, Hkv, D, q.stride(0), q.stride(1),
+                               k.stride(0), k.stride(1), v.stride(0), v.stride(1), int(causal),
+                               -1 if window is None else int(window), float(scale), status_word().data_ptr(), stream()),
+            "sb200_fa_fwd",
+        )
+        ctx.save_for_backward(q, k, v, o, lse2, doc_start, doc_end)
+        ctx.cfg = (causal, scale, window)
+        return o
+
+    @staticmethod
+    def backward(ctx, do):  # type: ignore[override]
+        q, k, v, o, lse2, doc_start, doc_end = ctx.saved_tensors
+        causal, scale, window = ctx.cfg
+        T, Hq, D = q.shape
+        Hkv = k.shape[1]
+        do = do.contiguous()
+        dq = torch.empty((T, Hq, D), dtype=q.dtype, device=q.device)
+        dk = torch.empty((T, Hkv, D), dtype=q.dtype, device=q.device)
+        dv = torch.empty((T, Hkv, D), dtype=q.dtype, device=q.device)
+        delta = torch.empty((Hq, T), dtype=torch.float32, device=q.device)
+        check(
+            lib().sb200_fa_bwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), do.data_ptr(), lse2.data_ptr(),
+                               delta.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), doc_start.data_ptr(),
+                               doc_end.data_ptr(), T, Hq, Hkv, D, q.stride(0), q.stride(1), k.stride(0), k.stride(1),
+                               v.stride(0), v.stride(1), int(causal), -1 if window is None else int(window),
+                               float(scale), status_word().data_ptr(), stream()),
+            "sb200_fa_bwd",
+        )
+        return dq, dk, dv, None, None, None, None, None
+
+
+def flash_attention_kernel(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seqlens: torch.Tensor, causal: bool,
+                           scale: float, window: Optional[int]) -> torch.Tensor:
+    if q.dtype != torch.bfloat16:
+        # the kernels are bf16; fp16 inputs are converted (same exponent-safe range for attention inputs)
+        out = flash_attention_kernel(q.to(torch.bfloat16), k.to(torch.bfloat16), v.to(torch.bfloat16), cu_seqlens,
+                                     causal, scale, window)
+        return out.to(q.dtype)
+    start, end = doc_ranges(cu_seqlens, q.shape[0])
+    return _FlashAttention.apply(q, k, v, start, end, causal, scale, window)
