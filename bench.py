@@ -125,7 +125,7 @@ def run_ours(args: argparse.Namespace) -> None:
     from scaling_b200.ops import functional as K
     from scaling_b200.parallel import Topology
     from scaling_b200.transformer import SyntheticTextDataset, TransformerConfig, TransformerContext, init_model, init_optimizer
-    from scaling_b200.transformer.data import TextDatasetBatch
+    from scaling_b200.transformer.data import TextDatasetBatchBeforeSync
     from scaling_b200.transformer.model import metrics_aggregation_fn
     from scaling_b200.transformer.model.losses import create_loss_function
     from scaling_b200.core.data import DataLoader
@@ -171,10 +171,9 @@ def run_ours(args: argparse.Namespace) -> None:
         def __next__(self):
             ids = staged[self.i % len(staged)]
             self.i += 1
-            return ids
+            return TextDatasetBatchBeforeSync(token_ids=ids)
 
-    def sync_staged(topology, ids):
-        return TextDatasetBatch(input_token_ids=ids[:, :-1], target_token_ids=ids[:, 1:].contiguous())
+    sync_staged = sync
 
     def barrier():
         if world > 1:

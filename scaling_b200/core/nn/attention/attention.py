@@ -150,16 +150,17 @@ class FlashAttention(_AttentionCore):
         self.local_attention_window_size = local_attention_window_size
 
     def forward(self, query: torch.Tensor, key: torch.Tensor, value: torch.Tensor,
-                cumulative_seq_lengths_query: torch.Tensor,
+                cumulative_seq_lengths_query: Optional[torch.Tensor],
                 cumulative_seq_lengths_key: Optional[torch.Tensor] = None,
-                local: Optional[bool] = None) -> torch.Tensor:
+                local: Optional[bool] = None,
+                doc_ranges: Optional[tuple[torch.Tensor, torch.Tensor]] = None) -> torch.Tensor:
         """query ``[Tq, h, d]``, key/value ``[Tk, hkv, d]`` (token-major, packed) -> ``[Tq, h, d]``."""
         query, key, value = self._pre(query, key, value)
         use_window = self.local_attention_window_size if (local is None or local) else None
         out = flash_attention(
             query, key, value, cumulative_seq_lengths_query, cumulative_seq_lengths_key, causal=self.causal,
             scale=self.query_key_scaling_factor, window=use_window,
-            dropout_p=self.dropout_p if self.training else 0.0,
+            dropout_p=self.dropout_p if self.training else 0.0, doc_ranges=doc_ranges,
         )
         return self._post(out)
 
@@ -361,11 +362,15 @@ class ParallelSelfAttention(torch.nn.Module):
         return norm(t)
 
     # ------------------------------------------------------------------ forward
-    def forward(self, x: torch.Tensor, cumulative_seq_lengths: torch.Tensor, position_ids: Optional[torch.Tensor],
+    def forward(self, x: torch.Tensor, cumulative_seq_lengths: Optional[torch.Tensor],
+                position_ids: Optional[torch.Tensor],
                 cumulative_seq_lengths_key: Optional[torch.Tensor] = None, use_cache: bool = False,
                 reset_cache: bool = False, cache_index: int = 0,
                 attention_scores_manipulation: Optional[torch.Tensor] = None,
-                attentions_score_manipulation_log_additive: Union[bool, List[bool]] = True) -> torch.Tensor:
+                attentions_score_manipulation_log_additive: Union[bool, List[bool]] = True,
+                doc_ranges: Optional[tuple[torch.Tensor, torch.Tensor]] = None) -> torch.Tensor:
+        """``doc_ranges`` (per-token document start / end, int32) may stand in for ``cumulative_seq_lengths`` on
+        the fused attention path; it is what a captured CUDA graph passes, since it has a fixed shape."""
         b, s, _ = x.shape
         T = b * s
         d = self.hidden_size_per_attention_head
@@ -408,7 +413,8 @@ class ParallelSelfAttention(torch.nn.Module):
             nl = self.num_local_attention_heads
             if nl <= 0 or nl == self.num_attention_heads:
                 ctx = core(q, k.contiguous() if use_cache else k, v.contiguous() if use_cache else v,
-                           cumulative_seq_lengths, cumulative_seq_lengths_key, local=nl > 0)
+                           cumulative_seq_lengths, cumulative_seq_lengths_key, local=nl > 0,
+                           doc_ranges=None if use_cache else doc_ranges)
             else:  # first `nl` heads attend locally, the rest globally (tensor parallel size 1 only)
                 rep = self.num_repeat_kv
                 k_full = k.repeat_interleave(rep, dim=1) if rep > 1 else k

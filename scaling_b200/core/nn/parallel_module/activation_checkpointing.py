@@ -19,7 +19,13 @@ import torch
 from ....parallel.topology import Topology
 
 
+def _capturing() -> bool:
+    return torch.cuda.is_available() and torch.cuda.is_initialized() and torch.cuda.is_current_stream_capturing()
+
+
 def _capture_rng(topology: Optional[Topology]) -> dict[str, Any]:
+    if _capturing():
+        return {}  # a captured step contains no random ops (the engine only captures dropout-free models)
     state: dict[str, Any] = {"cpu": torch.get_rng_state()}
     if torch.cuda.is_available() and torch.cuda.is_initialized():
         state["cuda"] = torch.cuda.get_rng_state()
@@ -29,6 +35,8 @@ def _capture_rng(topology: Optional[Topology]) -> dict[str, Any]:
 
 
 def _restore_rng(state: dict[str, Any], topology: Optional[Topology]) -> None:
+    if not state:
+        return
     torch.set_rng_state(state["cpu"])
     if "cuda" in state:
         torch.cuda.set_rng_state(state["cuda"])

@@ -14,6 +14,7 @@ non-blocking copies from pinned memory.
 from __future__ import annotations
 
 import json
+import os
 from dataclasses import asdict
 from pathlib import Path
 from typing import Any, Callable, Generic, NamedTuple, Optional, Union
@@ -123,6 +124,18 @@ class ParallelModule(PipePartitionedModule, Generic[BaseLossInputGeneric, BaseDa
                 )
         self.profiler = Profiler(config=profiler_config, topology=t)
         self.step_timer = CudaEventTimer()
+        # whole-step CUDA graph (see _graph_eligible); SB200_CUDA_GRAPH=0 disables it
+        self.enable_cuda_graph = os.environ.get("SB200_CUDA_GRAPH", "1") != "0"
+        self._graph: Any = None
+        self._graph_failed = False
+        self._graph_warmup_left = 2
+        self._graph_inputs: list[Any] = []
+        self._graph_loss: Any = None
+        self._graph_metrics: Optional[dict[str, torch.Tensor]] = None
+        self._graph_signature: Any = None
+        self._graph_captures = 0
+        self._graph_kernel_calls = 0
+        self._graph_pending: list[Any] = []
         self._handlers: dict[str, Callable[..., None]] = {
             "LoadMicroBatch": self._do_load, "ForwardPass": self._do_forward, "Loss": self._do_loss,
             "BackwardPass": self._do_backward, "SendActivation": self._do_send_activation,
@@ -246,11 +259,155 @@ class ParallelModule(PipePartitionedModule, Generic[BaseLossInputGeneric, BaseDa
                     self._handlers[name](ins, **ctx)
         return optimizer_out
 
+    # ------------------------------------------------------------------ CUDA-graph training step
+    def _graph_eligible(self, optimizer: Any) -> bool:
+        """A whole optimizer step (all micro batches, backward, gradient reduction, AdamW, parameter all-gather)
+        can be captured once and replayed when nothing in it depends on the host: one pipeline stage, batches
+        that reach the device without a tensor-parallel broadcast, no dropout, no loss scaling, profiler idle."""
+        if not self.enable_cuda_graph or self._graph_failed:
+            return False
+        t = self.topology
+        if t.device.type != "cuda" or t.config.pipe_parallel_size != 1 or t.config.model_parallel_size != 1:
+            return False
+        if not all(hasattr(optimizer, a) for a in ("begin_step", "step_device", "finish_step")):
+            return False
+        if optimizer.config.loss_scaler.enable or optimizer.config.debug_log:
+            return False
+        if self.profiler.config.profile_steps > 0:
+            return False
+        if torch._C._get_tracing_state() is not None:
+            return False
+        for m in self._layers.modules():
+            if isinstance(m, torch.nn.Dropout) and m.p > 0.0:
+                return False
+            if getattr(m, "dropout_p", 0.0) and m.training:
+                return False
+        return True
+
+    @staticmethod
+    def _batch_tensors(batch: Any) -> list[tuple[str, torch.Tensor]]:
+        if isinstance(batch, torch.Tensor):
+            return [("", batch)]
+        return [(k, v) for k, v in sorted(vars(batch).items()) if isinstance(v, torch.Tensor)]
+
+    def _static_copy(self, batch: Any) -> Any:
+        """Device-resident copy of a batch whose tensors keep their addresses for the life of the graph."""
+        device = self.topology.device
+        if isinstance(batch, torch.Tensor):
+            return batch.to(device).clone()
+        clone = type(batch).__new__(type(batch))
+        clone.__dict__.update(vars(batch))
+        for k, v in self._batch_tensors(batch):
+            setattr(clone, k, v.to(device).clone())
+        return clone
+
+    def _graph_device_step(self, optimizer: Any, sync: Callable, loss_function: Callable,
+                           metrics_aggregation_fn: Optional[Callable]) -> None:
+        """Device work of one step on the static input batches; runs eagerly for warm-up and under capture."""
+        t = self.topology
+        self.pipe_buffer.reset()
+        for batch in self._graph_inputs:
+            b = sync(t, batch)
+            out = self(b.only_inputs())
+            result = loss_function(out, b.only_targets())
+            loss, metrics = result if isinstance(result, tuple) else (result, None)
+            self.pipe_buffer.add_loss(loss, metrics)
+            optimizer.backward(loss)
+        optimizer.step_device()
+        total = torch.stack([x.float() for x in self.pipe_buffer.losses]).sum() / t.config.gradient_accumulation_steps
+        if t.config.data_parallel_size > 1:
+            dist.all_reduce(total, group=t.data_parallel_group)
+            total = total / t.config.data_parallel_size
+        self._graph_loss.copy_(total)
+        if self.pipe_buffer.metrics and metrics_aggregation_fn is not None:
+            agg = metrics_aggregation_fn(t, self.pipe_buffer.metrics)
+            if self._graph_metrics is None:
+                self._graph_metrics = {k: torch.zeros((), dtype=torch.float32, device=t.device) for k in agg}
+            for k, v in agg.items():
+                self._graph_metrics[k].copy_(torch.as_tensor(v, dtype=torch.float32, device=t.device))
+
+    def _graphed_train_step(self, dataloader: Any, optimizer: Any, sync: Callable, loss_function: Callable,
+                            metrics_aggregation_fn: Optional[Callable]) -> Optional[TrainStepOutput]:
+        """One training step through the captured graph.  Returns None (with the batches it already drew kept in
+        ``_graph_pending``) when the step has to run through the instruction list instead."""
+        from ....ops import _lib
+
+        t = self.topology
+        ga = t.config.gradient_accumulation_steps
+        raw = [next(dataloader) for _ in range(ga)]
+        key = (sync, loss_function, metrics_aggregation_fn,
+               tuple(tuple((type(b).__name__, k, tuple(v.shape), v.dtype) for k, v in self._batch_tensors(b)) for b in raw))
+        if key != self._graph_signature:
+            # new input signature: drop the old graph and start over (a bounded number of times)
+            self._graph = None
+            self._graph_captures += 1
+            if self._graph_captures > 4:
+                self._graph_failed = True
+                self._graph_pending = raw
+                return None
+            self._graph_signature = key
+            self._graph_warmup_left = 2 if self._graph_captures == 1 else 1
+            self._graph_inputs = [self._static_copy(b) for b in raw]
+            self._graph_loss = torch.zeros((), dtype=torch.float32, device=t.device)
+            self._graph_metrics = None
+        else:
+            for static, b in zip(self._graph_inputs, raw):
+                if isinstance(static, torch.Tensor):
+                    static.copy_(b, non_blocking=True)
+                    continue
+                for k, v in self._batch_tensors(b):
+                    getattr(static, k).copy_(v, non_blocking=True)
+        optimizer.begin_step()
+        if self._graph is None:
+            self._graph_warmup_left -= 1
+            if self._graph_warmup_left >= 0:
+                # the first steps run eagerly: lazy initialisation (kernel attributes, NCCL, allocator) must not
+                # happen under capture
+                self._graph_device_step(optimizer, sync, loss_function, metrics_aggregation_fn)
+            else:
+                try:
+                    torch.cuda.synchronize()
+                    graph = torch.cuda.CUDAGraph()
+                    calls0 = _lib.kernel_calls()
+                    with torch.cuda.graph(graph, capture_error_mode="thread_local"):
+                        self._graph_device_step(optimizer, sync, loss_function, metrics_aggregation_fn)
+                    self._graph_kernel_calls = _lib.kernel_calls() - calls0
+                    self._graph = graph
+                    graph.replay()
+                except Exception as e:  # noqa: BLE001 - any capture problem means: stay eager
+                    from ...logging import logger
+
+                    logger.warning(f"CUDA-graph capture of the training step failed ({type(e).__name__}: {e}); "
+                                   "continuing without graphs")
+                    self._graph = None
+                    self._graph_failed = True
+                    torch.cuda.synchronize()
+                    optimizer.zero_grad()
+                    self._graph_device_step(optimizer, sync, loss_function, metrics_aggregation_fn)
+        else:
+            self._graph.replay()
+            _lib.note_replayed_calls(self._graph_kernel_calls)
+        opt_out = optimizer.finish_step()
+        loss = float(self._graph_loss.item())
+        metrics = None if self._graph_metrics is None else {k: v.item() for k, v in self._graph_metrics.items()}
+        self.step_timer.stop()
+        return TrainStepOutput(loss=loss, metrics=metrics, step_duration=self.step_timer.duration(), **opt_out._asdict())
+
     def train_step(self, dataloader: Any, optimizer: Any, sync_batch_to_model_parallel: Callable,
                    loss_function: Callable, metrics_aggregation_fn: Optional[Callable] = None) -> TrainStepOutput:
         if not torch.is_grad_enabled():
             raise RuntimeError("train_step() requires gradients enabled. Use evaluation_step() instead.")
         self.step_timer.start()
+        if self._graph_eligible(optimizer):
+            self._layers.train()
+            out = self._graphed_train_step(dataloader, optimizer, sync_batch_to_model_parallel, loss_function,
+                                           metrics_aggregation_fn)
+            if out is not None:
+                return out
+            if self._graph_pending:
+                import itertools
+
+                dataloader, self._graph_pending = itertools.chain(self._graph_pending, dataloader), []
         self._layers.train()
         self.pipe_buffer.reset()
         self.profiler.step()

@@ -102,6 +102,11 @@ class Optimizer(BaseOptimizer):
         self._stats = torch.zeros(2, dtype=torch.float32, device=dev)     # [sum of squares, overflow count]
         self._flag = torch.zeros(1, dtype=torch.int32, device=dev)
         self._control = torch.zeros(2, dtype=torch.float32, device=dev)   # [gradient multiplier, skip]
+        self._result = torch.zeros(2, dtype=torch.float32, device=dev)    # [global norm, overflow] read by the host
+        self._hyper_host: Optional[torch.Tensor] = None                    # [lr, 1-b1^t, 1-b2^t] per group (pinned)
+        self._hyper: Optional[torch.Tensor] = None
+        self._learning_rates: dict[str, float] = {}
+        self._debug = None
         self._slot_variable_names = ["exp_avg", "exp_avg_sq"]
         self._fused = None
         if config.fused_collectives and config.zero and topology.config.data_parallel_size > 1 and dev.type == "cuda":
@@ -156,14 +161,37 @@ class Optimizer(BaseOptimizer):
         return g.reduced_grad
 
     def step(self) -> OptimizerStepOutput:
+        self.begin_step()
+        self.step_device()
+        return self.finish_step()
+
+    # The step is split in three so that the device part can live inside a captured CUDA graph:
+    # begin_step (host: counters, learning rates -> device), step_device (kernels and collectives only),
+    # finish_step (host: the step's single device -> host read, loss-scaler state machine).
+    def begin_step(self) -> None:
         self.step_index += 1
+        cfg = self.config
+        t = self.adam_steps + 1
+        values = []
+        self._learning_rates = {}
+        for i, g in enumerate(self.parameter_groups):
+            lr = g.set_learning_rate(self.step_index)
+            self._learning_rates[g.config.name or f"parameter_group_{i}"] = lr
+            values += [lr, 1.0 - cfg.beta1 ** t, 1.0 - cfg.beta2 ** t]
+        if self._hyper_host is None:
+            self._hyper_host = torch.empty(len(values), dtype=torch.float32,
+                                           pin_memory=self.topology.device.type == "cuda")
+            self._hyper = torch.empty(len(values), dtype=torch.float32, device=self.topology.device)
+        self._hyper_host.copy_(torch.tensor(values, dtype=torch.float32))
+        self._hyper.copy_(self._hyper_host, non_blocking=True)
+        self._debug = self._debug_norms() if cfg.debug_log else None
+
+    def step_device(self) -> None:
         t = self.topology
         dp = t.config.data_parallel_size
         cfg = self.config
         self._stats.zero_()
         self._flag.zero_()
-        debug = self._debug_norms() if cfg.debug_log else None
-
         if self._fused is not None:
             reduced = self._fused.reduce_scatter(self)
         else:
@@ -184,15 +212,14 @@ class Optimizer(BaseOptimizer):
             coef = torch.where(norm >= cfg.gradient_clipping, cfg.gradient_clipping / norm, coef)
         self._control[0] = torch.where(bad, torch.zeros_like(coef), coef * inv)
         self._control[1] = bad.to(torch.float32)
-
-        learning_rates = {}
+        self._result[0] = norm
+        self._result[1] = bad.to(torch.float32)
         for i, (g, r) in enumerate(zip(self.parameter_groups, reduced)):
-            lr = g.set_learning_rate(self.step_index)
-            learning_rates[g.config.name or f"parameter_group_{i}"] = lr
             lo, hi = g.owned_range
             p_lp = None if g.dtype == torch.float32 else g.flat_param[lo:hi]
             K.adamw_step(g.master, g.exp_avg, g.exp_avg_sq, r if r.numel() == g.master.numel() else r[lo:hi], p_lp,
-                         lr, cfg.beta1, cfg.beta2, cfg.eps, g.weight_decay, self.adam_steps + 1, self._control)
+                         g.current_lr, cfg.beta1, cfg.beta2, cfg.eps, g.weight_decay, self.adam_steps + 1,
+                         self._control, self._hyper[3 * i:3 * i + 3])
         if self._fused is not None:
             self._fused.all_gather(self)
         elif cfg.zero and dp > 1:
@@ -207,8 +234,9 @@ class Optimizer(BaseOptimizer):
                     dist.all_gather_into_tensor(g.flat_param, g.flat_param[lo:hi], group=grp)
         self.zero_grad()
 
-        # the only device -> host transfer of the step
-        norm_host, bad_host = torch.stack((norm, bad.to(norm.dtype))).tolist()
+    def finish_step(self) -> OptimizerStepOutput:
+        cfg = self.config
+        norm_host, bad_host = self._result.tolist()  # the only device -> host transfer of the step
         overflow = bool(bad_host)
         scaler_out = self.loss_scaler.step(overflow)
         if overflow:
@@ -222,9 +250,9 @@ class Optimizer(BaseOptimizer):
                                        scaler_out.current_loss_scale, None)
         self.adam_steps += 1
         return OptimizerStepOutput(
-            global_grad_norm=norm_host, global_grad_norm_clipped=None, learning_rates=learning_rates,
+            global_grad_norm=norm_host, global_grad_norm_clipped=None, learning_rates=dict(self._learning_rates),
             overflow=scaler_out.overflow, no_overflow_steps=scaler_out.no_overflow_steps,
-            current_loss_scale=scaler_out.current_loss_scale, debug_dict=debug,
+            current_loss_scale=scaler_out.current_loss_scale, debug_dict=self._debug,
         )
 
     def _debug_norms(self) -> dict[str, float]:

@@ -356,51 +356,52 @@ __global__ void fa_bwd_delta_kernel(const __nv_bfloat16* __restrict__ O, const _
 }
 
 // ============================================================================ backward: dK, dV
-// CTA = (key tile, KV head).  Per (query head of the group, query tile):
-//   S^T = K Q^T, dP^T = V dO^T  ->  threads: P^T, dS^T (bf16, shared)  ->  dV += P^T dO, dK += dS^T Q
+// CTA = (key tile, KV head, split of the query-head group).  Per (query head, query tile) that sees the keys:
+//   S = Q K^T, dP = dO V^T (TMEM lanes = queries)  ->  threads: P, dS as bf16 [queries x keys] in shared memory
+//   ->  dV += P^T dO, dK += dS^T Q, reading the same tiles as MN-major A operands; both accumulate in TMEM
+//   (lanes = keys) over the whole loop.  With more than one split the results are written as fp32 partials
+//   and summed in a fixed order by fa_bwd_reduce_kernel.
 template <int D>
 __global__ void __launch_bounds__(FA_THREADS, 1)
     fa_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                        const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
-                       const FaParams p, const int q_tile_end_hint) {
+                       const FaParams p, const int q_tile_end_hint, const int heads_per_split,
+                       float* __restrict__ dk_partial, float* __restrict__ dv_partial) {
   constexpr int PANELS = D / 64;
   constexpr int TILE_BYTES = PANELS * PANEL_BYTES;
+  constexpr int NS = D == 64 ? 2 : 1;  // stages of the Q / dO ring
   constexpr int TMEM_COLS = 512;
-  constexpr uint32_t ST_COL = 0, DPT_COL = 128, DV_COL = 256, DK_COL = 256 + D;
+  constexpr uint32_t S_COL = 0, DP_COL = 128, DV_COL = 256, DK_COL = 256 + D;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sK = smem;
   uint8_t* sV = sK + TILE_BYTES;
-  uint8_t* sQ = sV + TILE_BYTES;               // 1 stage (D = 128) - reloaded per iteration
-  uint8_t* sdO = sQ + TILE_BYTES;
-  uint8_t* sPT = sdO + TILE_BYTES;             // P^T  [keys x queries] 2 panels
-  uint8_t* sdST = sPT + 2 * PANEL_BYTES;       // dS^T [keys x queries] 2 panels
-  // per-query vectors, double buffered by iteration parity
-  float* s_lse = reinterpret_cast<float*>(sdST + 2 * PANEL_BYTES);  // 2 x 128
-  float* s_delta = s_lse + 2 * TILE;                                  // 2 x 128
-  int* s_lo = reinterpret_cast<int*>(s_delta + 2 * TILE);             // 2 x 128
-  int* s_hi = s_lo + 2 * TILE;                                        // 2 x 128
-  uint64_t* bars = reinterpret_cast<uint64_t*>(s_hi + 2 * TILE);
-  uint64_t* kv_full = bars;        // 1
-  uint64_t* qdo_full = bars + 1;   // 1
-  uint64_t* qdo_empty = bars + 2;  // 1
-  uint64_t* sdp_full = bars + 3;   // 1: S^T and dP^T ready
-  uint64_t* pds_full = bars + 4;   // 1 (count 4): P^T and dS^T written
-  uint64_t* acc_done = bars + 5;   // 1: dV / dK MMAs of the iteration retired (smem P^T/dS^T, TMEM S^T/dP^T free)
-  uint64_t* vec_ready = bars + 6;  // 1 (count 4): per-query vectors staged in shared memory
+  uint8_t* sQ = sV + TILE_BYTES;               // NS stages
+  uint8_t* sdO = sQ + NS * TILE_BYTES;         // NS stages
+  uint8_t* sP = sdO + NS * TILE_BYTES;         // P  [queries x keys] 2 panels
+  uint8_t* sdS = sP + 2 * PANEL_BYTES;         // dS [queries x keys] 2 panels
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sdS + 2 * PANEL_BYTES);
+  uint64_t* kv_full = bars;          // 1
+  uint64_t* qdo_full = bars + 1;     // NS
+  uint64_t* qdo_empty = bars + 3;    // NS
+  uint64_t* sdp_full = bars + 5;     // S and dP ready
+  uint64_t* pds_full = bars + 6;     // (count 4) P and dS written
+  uint64_t* acc_done = bars + 7;     // dV / dK MMAs of the iteration retired
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int kv0 = blockIdx.x * TILE;
   const int hk = blockIdx.y;
+  const int split = blockIdx.z;
   const int group = p.Hq / p.Hkv;
+  const int h_begin = split * heads_per_split;
+  const int n_heads = max(min(group - h_begin, heads_per_split), 0);
 
-  // query tiles that can see this key tile: from the tile holding the first key's earliest query to the
-  // tile holding the last key's latest query
+  // query tiles that can see this key tile (a superset; the element mask decides)
   const int k_last = min(kv0 + TILE - 1, p.T - 1);
-  int q_lo = kv0;                                  // causal: queries at or after the key
-  int q_hi = p.doc_end[k_last] - 1;                // queries of the last key's document
+  int q_lo = kv0;
+  int q_hi = p.doc_end[k_last] - 1;
   if (!p.causal) {
     q_lo = p.doc_start[kv0 < p.T ? kv0 : p.T - 1];
     if (p.window >= 0) q_lo = max(q_lo, kv0 - p.window);
@@ -409,16 +410,17 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
   const int qt_begin = q_lo / TILE;
   const int qt_end = min(q_hi / TILE + 1, q_tile_end_hint);
   const int n_qt = max(qt_end - qt_begin, 0);
-  const int n_iter = n_qt * group;
+  const int n_iter = n_qt * n_heads;
 
   if (threadIdx.x == 0) {
     sb::mbar_init(kv_full, 1);
-    sb::mbar_init(qdo_full, 1);
-    sb::mbar_init(qdo_empty, 1);
+    for (int i = 0; i < NS; ++i) {
+      sb::mbar_init(&qdo_full[i], 1);
+      sb::mbar_init(&qdo_empty[i], 1);
+    }
     sb::mbar_init(sdp_full, 1);
     sb::mbar_init(pds_full, 4);
     sb::mbar_init(acc_done, 1);
-    sb::mbar_init(vec_ready, 4);
     *abort_flag = 0;
     sb::mbar_fence_init();
   }
@@ -440,93 +442,78 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
         sb::tma_load_2d(sV + pn * PANEL_BYTES, &tmV, kv_full, hk * p.ldv_head + pn * 64, kv0);
       }
       for (int it = 0; it < n_iter; ++it) {
-        const int h = hk * group + it / n_qt;
+        const int st = it % NS;
+        const uint32_t ph = (it / NS) & 1;
+        const int h = hk * group + h_begin + it / n_qt;
         const int q0 = (qt_begin + it % n_qt) * TILE;
-        if (!sb::mbar_wait(qdo_empty, (it & 1) ^ 1, abort_flag)) break;
-        sb::mbar_expect_tx(qdo_full, 2 * TILE_BYTES);
+        if (!sb::mbar_wait(&qdo_empty[st], ph ^ 1, abort_flag)) break;
+        sb::mbar_expect_tx(&qdo_full[st], 2 * TILE_BYTES);
 #pragma unroll
         for (int pn = 0; pn < PANELS; ++pn) {
-          sb::tma_load_2d(sQ + pn * PANEL_BYTES, &tmQ, qdo_full, h * p.ldq_head + pn * 64, q0);
-          sb::tma_load_2d(sdO + pn * PANEL_BYTES, &tmdO, qdo_full, h * p.ldo_head + pn * 64, q0);
+          sb::tma_load_2d(sQ + st * TILE_BYTES + pn * PANEL_BYTES, &tmQ, &qdo_full[st], h * p.ldq_head + pn * 64, q0);
+          sb::tma_load_2d(sdO + st * TILE_BYTES + pn * PANEL_BYTES, &tmdO, &qdo_full[st], h * p.ldo_head + pn * 64, q0);
         }
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      const uint32_t idesc_nt = sb::umma_idesc_f16(TILE, TILE, 1, 0, 0);  // [keys x D] x [queries x D]^T
-      const uint32_t idesc_acc = sb::umma_idesc_f16(TILE, D, 1, 0, 1);    // [keys x q] x [q x D] (B MN-major)
-      const uint32_t k_addr = sb::smem_u32(sK), v_addr = sb::smem_u32(sV), q_addr = sb::smem_u32(sQ),
-                     do_addr = sb::smem_u32(sdO), pt_addr = sb::smem_u32(sPT), dst_addr = sb::smem_u32(sdST);
+      const uint32_t idesc_nt = sb::umma_idesc_f16(TILE, TILE, 1, 0, 0);  // [q x D] x [keys x D]^T
+      const uint32_t idesc_acc = sb::umma_idesc_f16(TILE, D, 1, 1, 1);    // [q x keys]^T x [q x D]: both MN-major
+      const uint32_t k_addr = sb::smem_u32(sK), v_addr = sb::smem_u32(sV), p_addr = sb::smem_u32(sP),
+                     ds_addr = sb::smem_u32(sdS);
       bool ok = sb::mbar_wait(kv_full, 0, abort_flag);
       for (int it = 0; it < n_iter && ok; ++it) {
-        if (!sb::mbar_wait(qdo_full, it & 1, abort_flag)) break;
-        // S^T / dP^T buffers and P^T / dS^T tiles are free once the previous accumulation MMAs retired
-        if (it > 0 && !sb::mbar_wait(acc_done, (it - 1) & 1, abort_flag)) break;
+        const int st = it % NS;
+        if (!sb::mbar_wait(&qdo_full[st], (it / NS) & 1, abort_flag)) break;
         sb::tc_fence_after();
+        const uint32_t q_addr = sb::smem_u32(sQ + st * TILE_BYTES), do_addr = sb::smem_u32(sdO + st * TILE_BYTES);
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk)
-          sb::umma_f16_ss(tmem_base + ST_COL, desc_kmajor(k_addr, kk), desc_kmajor(q_addr, kk), idesc_nt, kk != 0);
+          sb::umma_f16_ss(tmem_base + S_COL, desc_kmajor(q_addr, kk), desc_kmajor(k_addr, kk), idesc_nt, kk != 0);
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk)
-          sb::umma_f16_ss(tmem_base + DPT_COL, desc_kmajor(v_addr, kk), desc_kmajor(do_addr, kk), idesc_nt, kk != 0);
-        sb::umma_commit(sdp_full);
+          sb::umma_f16_ss(tmem_base + DP_COL, desc_kmajor(do_addr, kk), desc_kmajor(v_addr, kk), idesc_nt, kk != 0);
+        sb::umma_commit(sdp_full);  // also covers the accumulation MMAs of the previous iteration
         if (!sb::mbar_wait(pds_full, it & 1, abort_flag)) break;
         sb::tc_fence_after();
 #pragma unroll
         for (int kk = 0; kk < TILE / 16; ++kk)
-          sb::umma_f16_ss(tmem_base + DV_COL, desc_kmajor(pt_addr, kk), desc_mnmajor(do_addr, kk), idesc_acc, (it | kk) != 0);
+          sb::umma_f16_ss(tmem_base + DV_COL, desc_mnmajor(p_addr, kk), desc_mnmajor(do_addr, kk), idesc_acc, (it | kk) != 0);
 #pragma unroll
         for (int kk = 0; kk < TILE / 16; ++kk)
-          sb::umma_f16_ss(tmem_base + DK_COL, desc_kmajor(dst_addr, kk), desc_mnmajor(q_addr, kk), idesc_acc, (it | kk) != 0);
+          sb::umma_f16_ss(tmem_base + DK_COL, desc_mnmajor(ds_addr, kk), desc_mnmajor(q_addr, kk), idesc_acc, (it | kk) != 0);
         sb::umma_commit(acc_done);
-        sb::umma_commit(qdo_empty);
+        sb::umma_commit(&qdo_empty[st]);
       }
     }
   } else {
     const int quad = warp & 3;
-    const int r = quad * 32 + lane;  // key row inside the tile
-    const int kidx = kv0 + r;
+    const int r = quad * 32 + lane;  // query row inside the tile while computing P / dS, key row in the epilogue
     const uint32_t t_lane = tmem_base + ((uint32_t)(quad * 32) << 16);
     bool ok = true;
     for (int it = 0; it < n_iter && ok; ++it) {
-      const int h = hk * group + it / n_qt;
+      const int h = hk * group + h_begin + it / n_qt;
       const int q0 = (qt_begin + it % n_qt) * TILE;
-      // stage the per-query vectors of this iteration into the buffer of its parity; the buffer was last read
-      // two iterations ago, and every warp has passed the vec_ready wait of the iteration in between
-      const int vb = (it & 1) * TILE;
-      const float* v_lse = s_lse + vb;
-      const float* v_delta = s_delta + vb;
-      const int* v_lo = s_lo + vb;
-      const int* v_hi = s_hi + vb;
-      {
-        const int t = q0 + r;
-        int lo, hi;
-        row_range(p, t, lo, hi);
-        s_lo[vb + r] = lo;
-        s_hi[vb + r] = hi;
-        s_lse[vb + r] = t < p.T ? p.lse2[(long)h * p.T + t] : 0.f;
-        s_delta[vb + r] = t < p.T ? p.delta[(long)h * p.T + t] : 0.f;
-      }
-      // all four warps must have staged before anyone reads
-      __syncwarp();
-      if (lane == 0) sb::mbar_arrive(vec_ready);
-      if (!sb::mbar_wait(vec_ready, it & 1, abort_flag)) { ok = false; break; }
+      const int t = q0 + r;
+      int lo, hi;
+      row_range(p, t, lo, hi);
+      const float lse = t < p.T ? p.lse2[(long)h * p.T + t] : 0.f;
+      const float dl = t < p.T ? p.delta[(long)h * p.T + t] : 0.f;
       if (!sb::mbar_wait(sdp_full, it & 1, abort_flag)) { ok = false; break; }
       sb::tc_fence_after();
 #pragma unroll 1
       for (int ch = 0; ch < 4; ++ch) {
         uint32_t s[32], dp[32];
-        sb::tmem_ld32(t_lane + ST_COL + ch * 32, s);
-        sb::tmem_ld32(t_lane + DPT_COL + ch * 32, dp);
+        sb::tmem_ld32(t_lane + S_COL + ch * 32, s);
+        sb::tmem_ld32(t_lane + DP_COL + ch * 32, dp);
         sb::tmem_ld_wait();
         float pv[32], dsv[32];
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
-          const int c = ch * 32 + i;  // query column
-          const bool ok_el = kidx >= v_lo[c] && kidx <= v_hi[c];
-          const float pr = ok_el ? fast_exp2(__uint_as_float(s[i]) * p.scale_log2 - v_lse[c]) : 0.f;
+          const int kidx = kv0 + ch * 32 + i;
+          const float pr = (kidx >= lo && kidx <= hi) ? fast_exp2(__uint_as_float(s[i]) * p.scale_log2 - lse) : 0.f;
           pv[i] = pr;
-          dsv[i] = pr * (__uint_as_float(dp[i]) - v_delta[c]) * p.scale;
+          dsv[i] = pr * (__uint_as_float(dp[i]) - dl) * p.scale;
         }
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
@@ -540,8 +527,8 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
           w.z = pack_bf16(dsv[g * 8 + 4], dsv[g * 8 + 5]);
           w.w = pack_bf16(dsv[g * 8 + 6], dsv[g * 8 + 7]);
           const uint32_t off = swz_offset(r, ch * 32 + g * 8);
-          *reinterpret_cast<uint4*>(sPT + off) = u;
-          *reinterpret_cast<uint4*>(sdST + off) = w;
+          *reinterpret_cast<uint4*>(sP + off) = u;
+          *reinterpret_cast<uint4*>(sdS + off) = w;
         }
       }
       sb::fence_proxy_async_smem();
@@ -549,40 +536,51 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
       __syncwarp();
       if (lane == 0) sb::mbar_arrive(pds_full);
     }
-    // results
-    if (ok && n_iter > 0 && sb::mbar_wait(acc_done, (n_iter - 1) & 1, abort_flag)) {
-      sb::tc_fence_after();
-      __nv_bfloat16* dk = reinterpret_cast<__nv_bfloat16*>(p.dK) + ((long)kidx * p.Hkv + hk) * D;
-      __nv_bfloat16* dv = reinterpret_cast<__nv_bfloat16*>(p.dV) + ((long)kidx * p.Hkv + hk) * D;
+    // results: TMEM lane = key row
+    const int kidx = kv0 + r;
+    const bool have = ok && n_iter > 0 && sb::mbar_wait(acc_done, (n_iter - 1) & 1, abort_flag);
+    if (have) sb::tc_fence_after();
+    if (ok && (have || n_iter == 0)) {
+      const long row = (long)kidx * p.Hkv + hk;
 #pragma unroll 1
       for (int ch = 0; ch < D / 32; ++ch) {
         uint32_t a[32], b[32];
-        sb::tmem_ld32(t_lane + DV_COL + ch * 32, a);
-        sb::tmem_ld32(t_lane + DK_COL + ch * 32, b);
-        sb::tmem_ld_wait();
-        if (kidx < p.T) {
+        if (have) {
+          sb::tmem_ld32(t_lane + DV_COL + ch * 32, a);
+          sb::tmem_ld32(t_lane + DK_COL + ch * 32, b);
+          sb::tmem_ld_wait();
+        } else {
 #pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            uint4 u, w;
-            u.x = pack_bf16(__uint_as_float(a[g * 8 + 0]), __uint_as_float(a[g * 8 + 1]));
-            u.y = pack_bf16(__uint_as_float(a[g * 8 + 2]), __uint_as_float(a[g * 8 + 3]));
-            u.z = pack_bf16(__uint_as_float(a[g * 8 + 4]), __uint_as_float(a[g * 8 + 5]));
-            u.w = pack_bf16(__uint_as_float(a[g * 8 + 6]), __uint_as_float(a[g * 8 + 7]));
-            w.x = pack_bf16(__uint_as_float(b[g * 8 + 0]), __uint_as_float(b[g * 8 + 1]));
-            w.y = pack_bf16(__uint_as_float(b[g * 8 + 2]), __uint_as_float(b[g * 8 + 3]));
-            w.z = pack_bf16(__uint_as_float(b[g * 8 + 4]), __uint_as_float(b[g * 8 + 5]));
-            w.w = pack_bf16(__uint_as_float(b[g * 8 + 6]), __uint_as_float(b[g * 8 + 7]));
-            *reinterpret_cast<uint4*>(dv + ch * 32 + g * 8) = u;
-            *reinterpret_cast<uint4*>(dk + ch * 32 + g * 8) = w;
+          for (int i = 0; i < 32; ++i) { a[i] = 0u; b[i] = 0u; }
+        }
+        if (kidx < p.T) {
+          if (dk_partial) {
+            float* pk = dk_partial + ((long)split * p.T * p.Hkv + row) * D + ch * 32;
+            float* pv2 = dv_partial + ((long)split * p.T * p.Hkv + row) * D + ch * 32;
+#pragma unroll
+            for (int g = 0; g < 8; ++g) {
+              *reinterpret_cast<uint4*>(pv2 + g * 4) = make_uint4(a[g * 4], a[g * 4 + 1], a[g * 4 + 2], a[g * 4 + 3]);
+              *reinterpret_cast<uint4*>(pk + g * 4) = make_uint4(b[g * 4], b[g * 4 + 1], b[g * 4 + 2], b[g * 4 + 3]);
+            }
+          } else {
+            __nv_bfloat16* dk = reinterpret_cast<__nv_bfloat16*>(p.dK) + row * D + ch * 32;
+            __nv_bfloat16* dv = reinterpret_cast<__nv_bfloat16*>(p.dV) + row * D + ch * 32;
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              uint4 u, w;
+              u.x = pack_bf16(__uint_as_float(a[g * 8 + 0]), __uint_as_float(a[g * 8 + 1]));
+              u.y = pack_bf16(__uint_as_float(a[g * 8 + 2]), __uint_as_float(a[g * 8 + 3]));
+              u.z = pack_bf16(__uint_as_float(a[g * 8 + 4]), __uint_as_float(a[g * 8 + 5]));
+              u.w = pack_bf16(__uint_as_float(a[g * 8 + 6]), __uint_as_float(a[g * 8 + 7]));
+              w.x = pack_bf16(__uint_as_float(b[g * 8 + 0]), __uint_as_float(b[g * 8 + 1]));
+              w.y = pack_bf16(__uint_as_float(b[g * 8 + 2]), __uint_as_float(b[g * 8 + 3]));
+              w.z = pack_bf16(__uint_as_float(b[g * 8 + 4]), __uint_as_float(b[g * 8 + 5]));
+              w.w = pack_bf16(__uint_as_float(b[g * 8 + 6]), __uint_as_float(b[g * 8 + 7]));
+              *reinterpret_cast<uint4*>(dv + g * 8) = u;
+              *reinterpret_cast<uint4*>(dk + g * 8) = w;
+            }
           }
         }
-      }
-    } else if (ok && n_iter == 0 && kidx < p.T) {
-      __nv_bfloat16* dk = reinterpret_cast<__nv_bfloat16*>(p.dK) + ((long)kidx * p.Hkv + hk) * D;
-      __nv_bfloat16* dv = reinterpret_cast<__nv_bfloat16*>(p.dV) + ((long)kidx * p.Hkv + hk) * D;
-      for (int i = 0; i < D; i += 8) {
-        *reinterpret_cast<uint4*>(dk + i) = make_uint4(0, 0, 0, 0);
-        *reinterpret_cast<uint4*>(dv + i) = make_uint4(0, 0, 0, 0);
       }
     }
   }
@@ -597,6 +595,22 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
     sb::tmem_dealloc(tmem_base, TMEM_COLS);
   }
   if (threadIdx.x == 0 && *abort_flag && p.status) *p.status = SB_ERR_WAIT_TIMEOUT;
+}
+
+// out[i] = bf16(sum_s partial[s][i]) in fixed order
+__global__ void fa_bwd_reduce_kernel(const float* __restrict__ partial, __nv_bfloat16* __restrict__ out, long n,
+                                     int splits) {
+  long i = (blockIdx.x * (long)blockDim.x + threadIdx.x) * 4;
+  if (i >= n) return;
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int s = 0; s < splits; ++s) {
+    float4 v = *reinterpret_cast<const float4*>(partial + (long)s * n + i);
+    acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+  }
+  uint2 u;
+  u.x = pack_bf16(acc.x, acc.y);
+  u.y = pack_bf16(acc.z, acc.w);
+  *reinterpret_cast<uint2*>(out + i) = u;
 }
 
 // ============================================================================ backward: dQ
@@ -811,7 +825,7 @@ int fa_tmap(CUtensorMap* tm, const void* base, long T, long cols, long ld) {
 }
 
 template <int D> constexpr int fa_fwd_smem() { return (D / 64) * PANEL_BYTES * 5 + 2 * PANEL_BYTES + 1024 + 256; }
-template <int D> constexpr int fa_dkdv_smem() { return (D / 64) * PANEL_BYTES * 4 + 4 * PANEL_BYTES + 8 * TILE * 4 + 1024 + 256; }
+template <int D> constexpr int fa_dkdv_smem() { return (D / 64) * PANEL_BYTES * (2 + 2 * (D == 64 ? 2 : 1)) + 4 * PANEL_BYTES + 1024 + 256; }
 template <int D> constexpr int fa_dq_smem() { return (D / 64) * PANEL_BYTES * 4 + 2 * PANEL_BYTES + 1024 + 256; }
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
@@ -864,9 +878,25 @@ SB_API int sb200_fa_fwd(const void* q, const void* k, const void* v, void* o, fl
   return SB_OK;
 }
 
-// Backward.  o, d_o, dq: [T, Hq, D] contiguous; dk, dv: [T, Hkv, D] contiguous; delta: scratch [Hq, T] floats.
+// Number of splits of the query-head group the dK/dV kernel uses for this problem (1 = results written directly).
+// With more than one split the caller passes a scratch of 2 * splits * T * Hkv * D floats.
+SB_API int sb200_fa_bwd_splits(int T, int Hq, int Hkv, int sm_count) {
+  if (Hkv <= 0 || Hq % Hkv) return 1;
+  const int group = Hq / Hkv;
+  const int tiles = (T + TILE - 1) / TILE;
+  const long ctas = (long)tiles * Hkv;
+  if (group == 1 || ctas >= 2L * sm_count) return 1;
+  int want = (int)((2L * sm_count + ctas - 1) / ctas);
+  if (want > group) want = group;
+  const int hps = (group + want - 1) / want;
+  return (group + hps - 1) / hps;
+}
+
+// Backward.  o, d_o, dq: [T, Hq, D] contiguous; dk, dv: [T, Hkv, D] contiguous; delta: scratch [Hq, T] floats;
+// dkv_partial: scratch for split accumulation (see sb200_fa_bwd_splits), may be null when splits == 1.
 SB_API int sb200_fa_bwd(const void* q, const void* k, const void* v, const void* o, const void* d_o, const float* lse2,
-                        float* delta, void* dq, void* dk, void* dv, const int* doc_start, const int* doc_end, int T,
+                        float* delta, float* dkv_partial, int splits, void* dq, void* dk, void* dv,
+                        const int* doc_start, const int* doc_end, int T,
                         int Hq, int Hkv, int D, long ldq_tok, int ldq_head, long ldk_tok, int ldk_head, long ldv_tok,
                         int ldv_head, int causal, int window, float scale, int* status, cudaStream_t stream) {
   if (T <= 0 || Hq <= 0) return SB_OK;
@@ -887,6 +917,12 @@ SB_API int sb200_fa_bwd(const void* q, const void* k, const void* v, const void*
   p.ldq_head = ldq_head; p.ldk_head = ldk_head; p.ldv_head = ldv_head; p.ldo_head = D;
   p.lse2 = const_cast<float*>(lse2); p.delta = delta; p.dQ = dq; p.dK = dk; p.dV = dv; p.status = status;
   const int tiles = (T + TILE - 1) / TILE;
+  const int group = Hq / Hkv;
+  if (splits < 1) splits = 1;
+  if (splits > 1 && !dkv_partial) return SB_ERR_BAD_ARG;
+  const int hps = (group + splits - 1) / splits;
+  float* dk_part = splits > 1 ? dkv_partial : nullptr;
+  float* dv_part = splits > 1 ? dkv_partial + (long)splits * T * Hkv * D : nullptr;
   {
     long warps = (long)T * Hq;
     int blocks = (int)((warps * 32 + 255) / 256);
@@ -905,7 +941,8 @@ SB_API int sb200_fa_bwd(const void* q, const void* k, const void* v, const void*
       if (e != cudaSuccess) return (int)e;
       set = true;
     }
-    fa_bwd_dkdv_kernel<64><<<dim3(tiles, Hkv), FA_THREADS, fa_dkdv_smem<64>(), stream>>>(tmQ, tmK, tmV, tmdO, p, tiles);
+    fa_bwd_dkdv_kernel<64><<<dim3(tiles, Hkv, splits), FA_THREADS, fa_dkdv_smem<64>(), stream>>>(
+        tmQ, tmK, tmV, tmdO, p, tiles, hps, dk_part, dv_part);
     SB_CHECK_LAUNCH();
     fa_bwd_dq_kernel<64><<<dim3(tiles, Hq), FA_THREADS, fa_dq_smem<64>(), stream>>>(tmQ, tmK, tmV, tmdO, p);
   } else {
@@ -917,10 +954,18 @@ SB_API int sb200_fa_bwd(const void* q, const void* k, const void* v, const void*
       if (e != cudaSuccess) return (int)e;
       set = true;
     }
-    fa_bwd_dkdv_kernel<128><<<dim3(tiles, Hkv), FA_THREADS, fa_dkdv_smem<128>(), stream>>>(tmQ, tmK, tmV, tmdO, p, tiles);
+    fa_bwd_dkdv_kernel<128><<<dim3(tiles, Hkv, splits), FA_THREADS, fa_dkdv_smem<128>(), stream>>>(
+        tmQ, tmK, tmV, tmdO, p, tiles, hps, dk_part, dv_part);
     SB_CHECK_LAUNCH();
     fa_bwd_dq_kernel<128><<<dim3(tiles, Hq), FA_THREADS, fa_dq_smem<128>(), stream>>>(tmQ, tmK, tmV, tmdO, p);
   }
   SB_CHECK_LAUNCH();
+  if (splits > 1) {
+    const long n = (long)T * Hkv * D;
+    const int blocks = (int)((n / 4 + 255) / 256);
+    fa_bwd_reduce_kernel<<<blocks, 256, 0, stream>>>(dk_part, (__nv_bfloat16*)dk, n, splits);
+    fa_bwd_reduce_kernel<<<blocks, 256, 0, stream>>>(dv_part, (__nv_bfloat16*)dv, n, splits);
+    SB_CHECK_LAUNCH();
+  }
   return SB_OK;
 }

@@ -181,6 +181,93 @@ __global__ void __launch_bounds__(NORM_THREADS)
   }
 }
 
+// Backward with one warp per row (H <= 32 * V * NV): no block-wide synchronisation, row statistics by
+// warp shuffles, every warp keeps its share of dW / dB in registers and writes one partial row.
+template <typename T, bool RMS, int NV>
+__global__ void __launch_bounds__(NORM_THREADS)
+    norm_bwd_warp_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __restrict__ w,
+                         const float* __restrict__ mean_in, const float* __restrict__ rstd_in, T* __restrict__ dx,
+                         float* __restrict__ dw_partial, float* __restrict__ db_partial, int M, int H) {
+  constexpr int V = sb::Vec16<T>::N;
+  constexpr int WARPS = NORM_THREADS / 32;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int gw = blockIdx.x * WARPS + warp;
+  const int total_warps = gridDim.x * WARPS;
+  float dw_acc[NV][V], db_acc[NV][V];
+  float wreg[NV][V];
+#pragma unroll
+  for (int it = 0; it < NV; ++it) {
+    const int c = (it * 32 + lane) * V;
+#pragma unroll
+    for (int i = 0; i < V; ++i) {
+      dw_acc[it][i] = 0.f;
+      db_acc[it][i] = 0.f;
+      wreg[it][i] = 0.f;
+    }
+    if (c < H) {
+      auto wv = sb::ld16(w + c);
+#pragma unroll
+      for (int i = 0; i < V; ++i) wreg[it][i] = sb::to_f(wv.e[i]);
+    }
+  }
+  const float inv_h = 1.f / H;
+  for (int row = gw; row < M; row += total_warps) {
+    const T* xr = x + (size_t)row * H;
+    const T* dyr = dy + (size_t)row * H;
+    T* dxr = dx + (size_t)row * H;
+    const float mean = RMS ? 0.f : mean_in[row];
+    const float rstd = rstd_in[row];
+    float xh[NV][V], g[NV][V];
+    float sum_g = 0.f, sum_gx = 0.f;
+#pragma unroll
+    for (int it = 0; it < NV; ++it) {
+      const int c = (it * 32 + lane) * V;
+      if (c < H) {
+        auto xv = sb::ld16(xr + c);
+        auto dv = sb::ld16(dyr + c);
+#pragma unroll
+        for (int i = 0; i < V; ++i) {
+          const float d = sb::to_f(dv.e[i]);
+          xh[it][i] = (sb::to_f(xv.e[i]) - mean) * rstd;
+          g[it][i] = d * wreg[it][i];
+          sum_g += g[it][i];
+          sum_gx += g[it][i] * xh[it][i];
+          dw_acc[it][i] += d * xh[it][i];
+          if (!RMS) db_acc[it][i] += d;
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < V; ++i) { xh[it][i] = 0.f; g[it][i] = 0.f; }
+      }
+    }
+    sum_gx = sb::warp_sum(sum_gx) * inv_h;
+    sum_g = RMS ? 0.f : sb::warp_sum(sum_g) * inv_h;
+#pragma unroll
+    for (int it = 0; it < NV; ++it) {
+      const int c = (it * 32 + lane) * V;
+      if (c < H) {
+        sb::Vec16<T> o;
+#pragma unroll
+        for (int i = 0; i < V; ++i) o.e[i] = sb::from_f<T>(rstd * (g[it][i] - sum_g - xh[it][i] * sum_gx));
+        sb::st16(dxr + c, o);
+      }
+    }
+  }
+  float* dwp = dw_partial + (size_t)gw * H;
+  float* dbp = db_partial ? db_partial + (size_t)gw * H : nullptr;
+#pragma unroll
+  for (int it = 0; it < NV; ++it) {
+    const int c = (it * 32 + lane) * V;
+    if (c < H) {
+#pragma unroll
+      for (int i = 0; i < V; ++i) {
+        dwp[c + i] = dw_acc[it][i];
+        if (!RMS && dbp) dbp[c + i] = db_acc[it][i];
+      }
+    }
+  }
+}
+
 // out[c] (+)= sum_p partial[p][c], fixed order over p.
 template <typename T>
 __global__ void reduce_partials_kernel(const float* __restrict__ partial, T* __restrict__ out, int P, int H,
@@ -219,26 +306,73 @@ SB_API int sb200_norm_bwd_partial_rows(int M, int sm_count) {
   return p;
 }
 
+// Partial rows for a problem of M rows of width H: rows narrow enough for the warp-per-row kernel get one
+// partial row per warp (a multiple of 8), wider rows one per CTA.
+SB_API int sb200_norm_bwd_partial_rows_h(int M, int H, int elem_size, int sm_count) {
+  const int V = 16 / (elem_size > 0 ? elem_size : 2);
+  if (H % V == 0 && H <= 32 * V * 8) {
+    int ctas = (M + 7) / 8;
+    if (ctas > sm_count * 4) ctas = sm_count * 4;
+    if (ctas < 1) ctas = 1;
+    return ctas * 8;
+  }
+  return sb200_norm_bwd_partial_rows(M, sm_count);
+}
+
+namespace {
+
+template <typename T, bool RMS, int NV>
+void launch_norm_bwd_warp(const void* dy, const void* x, const void* w, const float* mean, const float* rstd, void* dx,
+                          float* dw_partial, float* db_partial, int M, int H, int partial_rows, cudaStream_t stream) {
+  norm_bwd_warp_kernel<T, RMS, NV><<<partial_rows / 8, NORM_THREADS, 0, stream>>>(
+      (const T*)dy, (const T*)x, (const T*)w, RMS ? nullptr : mean, rstd, (T*)dx, dw_partial,
+      RMS ? nullptr : db_partial, M, H);
+}
+
+template <typename T, bool RMS>
+int norm_bwd_dispatch(const void* dy, const void* x, const void* w, const float* mean, const float* rstd, void* dx,
+                      float* dw_partial, float* db_partial, void* dw, void* db, int M, int H, int accumulate,
+                      int partial_rows, cudaStream_t stream) {
+  constexpr int V = sb::Vec16<T>::N;
+  if (H % V != 0 || H > NORM_THREADS * V * NORM_MAX_ITERS) return SB_ERR_BAD_ARG;
+  const bool warp_rows = H <= 32 * V * 8 && partial_rows >= 8 && partial_rows % 8 == 0;
+  const int nv = (H + 32 * V - 1) / (32 * V);
+  if (warp_rows && nv <= 1)
+    launch_norm_bwd_warp<T, RMS, 1>(dy, x, w, mean, rstd, dx, dw_partial, db_partial, M, H, partial_rows, stream);
+  else if (warp_rows && nv <= 2)
+    launch_norm_bwd_warp<T, RMS, 2>(dy, x, w, mean, rstd, dx, dw_partial, db_partial, M, H, partial_rows, stream);
+  else if (warp_rows && nv <= 3)
+    launch_norm_bwd_warp<T, RMS, 3>(dy, x, w, mean, rstd, dx, dw_partial, db_partial, M, H, partial_rows, stream);
+  else if (warp_rows && nv <= 4)
+    launch_norm_bwd_warp<T, RMS, 4>(dy, x, w, mean, rstd, dx, dw_partial, db_partial, M, H, partial_rows, stream);
+  else if (warp_rows && nv <= 8)
+    launch_norm_bwd_warp<T, RMS, 8>(dy, x, w, mean, rstd, dx, dw_partial, db_partial, M, H, partial_rows, stream);
+  else
+    norm_bwd_kernel<T, RMS><<<partial_rows, NORM_THREADS, 0, stream>>>(
+        (const T*)dy, (const T*)x, (const T*)w, RMS ? nullptr : mean, rstd, (T*)dx, dw_partial,
+        RMS ? nullptr : db_partial, M, H);
+  SB_CHECK_LAUNCH();
+  int blocks = (H + 255) / 256;
+  reduce_partials_kernel<T><<<blocks, 256, 0, stream>>>(dw_partial, (T*)dw, partial_rows, H, accumulate);
+  if (!RMS && db && db_partial)
+    reduce_partials_kernel<T><<<blocks, 256, 0, stream>>>(db_partial, (T*)db, partial_rows, H, accumulate);
+  SB_CHECK_LAUNCH();
+  return SB_OK;
+}
+
+}  // namespace
+
 SB_API int sb200_norm_bwd(const void* dy, const void* x, const void* w, const float* mean, const float* rstd, void* dx,
                           float* dw_partial, float* db_partial, void* dw, void* db, int M, int H, int rms,
                           int accumulate, int partial_rows, int dtype, cudaStream_t stream) {
   if (M <= 0 || H <= 0) return SB_OK;
   SB_DISPATCH_DTYPE(dtype, T, {
-    constexpr int V = sb::Vec16<T>::N;
-    if (H % V != 0 || H > NORM_THREADS * V * NORM_MAX_ITERS) return SB_ERR_BAD_ARG;
     if (rms)
-      norm_bwd_kernel<T, true><<<partial_rows, NORM_THREADS, 0, stream>>>(
-          (const T*)dy, (const T*)x, (const T*)w, nullptr, rstd, (T*)dx, dw_partial, nullptr, M, H);
-    else
-      norm_bwd_kernel<T, false><<<partial_rows, NORM_THREADS, 0, stream>>>(
-          (const T*)dy, (const T*)x, (const T*)w, mean, rstd, (T*)dx, dw_partial, db_partial, M, H);
-    SB_CHECK_LAUNCH();
-    int blocks = (H + 255) / 256;
-    reduce_partials_kernel<T><<<blocks, 256, 0, stream>>>(dw_partial, (T*)dw, partial_rows, H, accumulate);
-    if (!rms && db && db_partial)
-      reduce_partials_kernel<T><<<blocks, 256, 0, stream>>>(db_partial, (T*)db, partial_rows, H, accumulate);
+      return norm_bwd_dispatch<T, true>(dy, x, w, mean, rstd, dx, dw_partial, db_partial, dw, db, M, H, accumulate,
+                                        partial_rows, stream);
+    return norm_bwd_dispatch<T, false>(dy, x, w, mean, rstd, dx, dw_partial, db_partial, dw, db, M, H, accumulate,
+                                       partial_rows, stream);
   });
-  SB_CHECK_LAUNCH();
   return SB_OK;
 }
 

@@ -17,7 +17,15 @@ namespace {
 template <typename G, typename P>
 __global__ void adamw_kernel(float* __restrict__ p, float* __restrict__ m, float* __restrict__ v,
                              const G* __restrict__ g, P* __restrict__ p_lp, long n, float lr, float beta1, float beta2,
-                             float eps, float wd, float bc1, float bc2, const float* __restrict__ control) {
+                             float eps, float wd, float bc1, float bc2, const float* __restrict__ control,
+                             const float* __restrict__ hyper) {
+  // hyper (optional, device memory): [learning rate, 1 - beta1^t, 1 - beta2^t] - lets a captured CUDA graph
+  // be replayed with new values
+  if (hyper) {
+    lr = hyper[0];
+    bc1 = hyper[1];
+    bc2 = hyper[2];
+  }
   float gmul = 1.f;
   if (control) {
     if (control[1] != 0.f) return;
@@ -109,15 +117,15 @@ __global__ void embedding_bwd_kernel(const long* __restrict__ sorted_ids, const 
 
 // g_dtype: dtype of the gradient; lp_dtype: dtype of the low-precision copy (ignored if p_lp is null)
 SB_API int sb200_adamw(float* p, float* m, float* v, const void* g, void* p_lp, long n, float lr, float beta1,
-                       float beta2, float eps, float wd, float bc1, float bc2, const float* control, int g_dtype,
-                       int lp_dtype, cudaStream_t stream) {
+                       float beta2, float eps, float wd, float bc1, float bc2, const float* control,
+                       const float* hyper, int g_dtype, int lp_dtype, cudaStream_t stream) {
   if (n <= 0) return SB_OK;
   long b = (n + 255) / 256;
   if (b > 148 * 8) b = 148 * 8;
   SB_DISPATCH_DTYPE(g_dtype, G, {
     SB_DISPATCH_DTYPE(lp_dtype, P, {
       adamw_kernel<G, P><<<(int)b, 256, 0, stream>>>(p, m, v, (const G*)g, (P*)p_lp, n, lr, beta1, beta2, eps, wd, bc1,
-                                                     bc2, control);
+                                                     bc2, control, hyper);
     });
   });
   SB_CHECK_LAUNCH();

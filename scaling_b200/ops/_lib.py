@@ -56,6 +56,7 @@ _SIGS = {
     # name: argtypes (restype is always int unless listed in _RESTYPES)
     "sb200_norm_fwd": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_int, c_void_p],
     "sb200_norm_bwd_partial_rows": [c_int, c_int],
+    "sb200_norm_bwd_partial_rows_h": [c_int, c_int, c_int, c_int],
     "sb200_norm_bwd": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "sb200_swiglu_fwd": [c_void_p, c_void_p, c_void_p, c_long, c_int, c_long, c_long, c_long, c_float, c_int, c_void_p],
     "sb200_swiglu_bwd": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_long, c_int, c_long, c_long, c_long, c_long, c_long, c_float, c_int, c_void_p],
@@ -69,7 +70,7 @@ _SIGS = {
     "sb200_ce_stats": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_long, c_int, c_long, c_long, c_int, c_void_p],
     "sb200_ce_finalize": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_long, c_int, c_long, c_long, c_long, c_int, c_void_p],
     "sb200_scale_by_dev": [c_void_p, c_void_p, c_float, c_long, c_int, c_void_p],
-    "sb200_adamw": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_long, c_float, c_float, c_float, c_float, c_float, c_float, c_float, c_void_p, c_int, c_int, c_void_p],
+    "sb200_adamw": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_long, c_float, c_float, c_float, c_float, c_float, c_float, c_float, c_void_p, c_void_p, c_int, c_int, c_void_p],
     "sb200_sumsq_max_partials": [],
     "sb200_sumsq": [c_void_p, c_long, c_void_p, c_void_p, c_void_p, c_float, c_int, c_int, c_void_p],
     "sb200_embedding_fwd": [c_void_p, c_void_p, c_void_p, c_long, c_int, c_long, c_long, c_int, c_void_p],
@@ -119,12 +120,19 @@ class _Counting:
         return hasattr(self._handle, name)
 
 
-_NO_LAUNCH = {"sb200_norm_bwd_partial_rows", "sb200_sumsq_max_partials"}
+_NO_LAUNCH = {"sb200_norm_bwd_partial_rows", "sb200_norm_bwd_partial_rows_h", "sb200_sumsq_max_partials",
+              "sb200_bind_device", "sb200_fa_last_driver_error"}
 
 
 def kernel_calls() -> int:
     """Number of calls made so far into kernel-launching entry points of the native library."""
     return 0 if _LIB is None else _LIB.calls
+
+
+def note_replayed_calls(n: int) -> None:
+    """Account for ``n`` kernel-launching calls that a CUDA-graph replay repeated on the device."""
+    if _LIB is not None:
+        _LIB.calls += int(n)
 
 
 def lib() -> "_Counting":

@@ -90,15 +90,18 @@ def kernel_supported(q: torch.Tensor, k: torch.Tensor, cu_k: Optional[torch.Tens
     )
 
 
-def flash_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seqlens_q: torch.Tensor,
+def flash_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seqlens_q: Optional[torch.Tensor],
                     cu_seqlens_k: Optional[torch.Tensor] = None, causal: bool = True,
                     scale: Optional[float] = None, window: Optional[int] = None,
-                    dropout_p: float = 0.0) -> torch.Tensor:
+                    dropout_p: float = 0.0,
+                    doc_ranges: Optional[tuple[torch.Tensor, torch.Tensor]] = None) -> torch.Tensor:
+    """``doc_ranges = (doc_start[T], doc_end[T])`` (int32) may replace ``cu_seqlens_q`` for self-attention."""
     scale = 1.0 / math.sqrt(q.shape[-1]) if scale is None else scale
     if dropout_p == 0.0 and kernel_supported(q, k, cu_seqlens_k):
         from .attention_kernel import flash_attention_kernel
 
-        return flash_attention_kernel(q, k, v, cu_seqlens_q, causal, scale, window)
+        return flash_attention_kernel(q, k, v, cu_seqlens_q, causal, scale, window, doc_ranges)
+    assert cu_seqlens_q is not None, "the dense attention path needs cumulative sequence lengths"
     if q.is_cuda and cu_seqlens_k is None and window is None:
         # head sizes the tcgen05 kernel does not cover: batched library attention over equal-length documents
         L = _uniform_docs(cu_seqlens_q, q.shape[0])

@@ -20,7 +20,8 @@ def _declare() -> None:
         return
     _lib.declare("sb200_fa_fwd", [c_void_p] * 7 + [c_int] * 4 + [c_long, c_int, c_long, c_int, c_long, c_int, c_int,
                                                                  c_int, c_float, c_void_p, c_void_p])
-    _lib.declare("sb200_fa_bwd", [c_void_p] * 12 + [c_int] * 4 + [c_long, c_int, c_long, c_int, c_long, c_int, c_int,
+    _lib.declare("sb200_fa_bwd_splits", [c_int] * 4)
+    _lib.declare("sb200_fa_bwd", [c_void_p] * 8 + [c_int] + [c_void_p] * 5 + [c_int] * 4 + [c_long, c_int, c_long, c_int, c_long, c_int, c_int,
                                                                   c_int, c_float, c_void_p, c_void_p])
     _DECLARED = True
 
@@ -82,9 +83,14 @@ class _FlashAttention(torch.autograd.Function):
         dk = torch.empty((T, Hkv, D), dtype=q.dtype, device=q.device)
         dv = torch.empty((T, Hkv, D), dtype=q.dtype, device=q.device)
         delta = torch.empty((Hq, T), dtype=torch.float32, device=q.device)
+        splits = lib()._handle.sb200_fa_bwd_splits(T, Hq, Hkv, _lib.sm_count())
+        partial = None
+        if splits > 1:
+            partial = torch.empty((2, splits, T, Hkv, D), dtype=torch.float32, device=q.device)
         check(
             lib().sb200_fa_bwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), do.data_ptr(), lse2.data_ptr(),
-                               delta.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), doc_start.data_ptr(),
+                               delta.data_ptr(), _lib.ptr(partial), splits, dq.data_ptr(), dk.data_ptr(),
+                               dv.data_ptr(), doc_start.data_ptr(),
                                doc_end.data_ptr(), T, Hq, Hkv, D, q.stride(0), q.stride(1), k.stride(0), k.stride(1),
                                v.stride(0), v.stride(1), int(causal), -1 if window is None else int(window),
                                float(scale), status_word().data_ptr(), stream()),
@@ -93,12 +99,13 @@ class _FlashAttention(torch.autograd.Function):
         return dq, dk, dv, None, None, None, None, None
 
 
-def flash_attention_kernel(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seqlens: torch.Tensor, causal: bool,
-                           scale: float, window: Optional[int]) -> torch.Tensor:
+def flash_attention_kernel(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seqlens: Optional[torch.Tensor],
+                           causal: bool, scale: float, window: Optional[int],
+                           ranges: Optional[tuple[torch.Tensor, torch.Tensor]] = None) -> torch.Tensor:
     if q.dtype != torch.bfloat16:
         # the kernels are bf16; fp16 inputs are converted (same exponent-safe range for attention inputs)
         out = flash_attention_kernel(q.to(torch.bfloat16), k.to(torch.bfloat16), v.to(torch.bfloat16), cu_seqlens,
-                                     causal, scale, window)
+                                     causal, scale, window, ranges)
         return out.to(q.dtype)
-    start, end = doc_ranges(cu_seqlens, q.shape[0])
+    start, end = ranges if ranges is not None else doc_ranges(cu_seqlens, q.shape[0])
     return _FlashAttention.apply(q, k, v, start, end, causal, scale, window)

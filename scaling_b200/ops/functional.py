@@ -229,7 +229,7 @@ class _NormFn(torch.autograd.Function):
         if not dy2.is_contiguous():
             dy2 = dy2.contiguous()
         dx = torch.empty_like(x2)
-        rows = lib().sb200_norm_bwd_partial_rows(M, sm_count())
+        rows = lib().sb200_norm_bwd_partial_rows_h(M, H, x2.element_size(), sm_count())
         dwp = torch.empty((rows, H), dtype=torch.float32, device=x2.device)
         dbp = torch.empty((rows, H), dtype=torch.float32, device=x2.device) if ctx.has_bias else None
         dw = torch.empty(H, dtype=x2.dtype, device=x2.device)
@@ -585,10 +585,12 @@ def scale_by_device_scalar(x: torch.Tensor, scale_dev: Optional[torch.Tensor], s
 # --------------------------------------------------------------------------- optimizer kernels
 def adamw_step(p: torch.Tensor, m: torch.Tensor, v: torch.Tensor, g: torch.Tensor, p_lp: Optional[torch.Tensor],
                lr: float, beta1: float, beta2: float, eps: float, weight_decay: float, step: int,
-               control: Optional[torch.Tensor] = None) -> None:
+               control: Optional[torch.Tensor] = None, hyper: Optional[torch.Tensor] = None) -> None:
     """Fused AdamW on flat fp32 ``p, m, v`` with gradient ``g`` (any float dtype) and optional low-precision copy.
 
     ``control`` is a device float[2]: gradient multiplier and a skip flag (non-zero = leave everything untouched).
+    ``hyper`` is an optional device float[3] ``[lr, 1 - beta1^t, 1 - beta2^t]`` that overrides ``lr`` and ``step``
+    (so that a captured CUDA graph can be replayed with new values).
     """
     bc1 = 1.0 - beta1 ** step
     bc2 = 1.0 - beta2 ** step
@@ -596,11 +598,13 @@ def adamw_step(p: torch.Tensor, m: torch.Tensor, v: torch.Tensor, g: torch.Tenso
         assert p.dtype == torch.float32 and p.is_contiguous() and g.is_contiguous()
         check(
             lib().sb200_adamw(p.data_ptr(), m.data_ptr(), v.data_ptr(), g.data_ptr(), ptr(p_lp), p.numel(), lr, beta1,
-                              beta2, eps, weight_decay, bc1, bc2, ptr(control), dt(g.dtype),
+                              beta2, eps, weight_decay, bc1, bc2, ptr(control), ptr(hyper), dt(g.dtype),
                               dt(p_lp.dtype) if p_lp is not None else 0, stream()),
             "sb200_adamw",
         )
         return
+    if hyper is not None:
+        lr, bc1, bc2 = (float(v) for v in hyper.tolist())
     gmul = 1.0
     if control is not None:
         if float(control[1]) != 0.0:

@@ -11,9 +11,14 @@ from .inference_settings import InferenceSettings
 from .utils import (
     add_cumulative_seq_lengths_padding,
     get_cumulative_seq_lengths,
+    get_cumulative_seq_lengths_padded,
     get_position_ids,
     remove_cumulative_seq_lengths_padding,
 )
+
+
+def _capturing() -> bool:
+    return torch.cuda.is_available() and torch.cuda.is_current_stream_capturing()
 
 
 class _FieldRecord:
@@ -67,14 +72,16 @@ class TextDatasetBatch(_FieldRecord, BaseDatasetBatch):
         self.embeddings = embeddings
         if input_token_ids is None:
             return
-        if self.cumulative_seq_lengths is None:
-            if self.cumulative_seq_lengths_padded is not None:  # after a pipe transfer only the padded form exists
-                self.cumulative_seq_lengths = remove_cumulative_seq_lengths_padding(self.cumulative_seq_lengths_padded)
-            else:
-                self.cumulative_seq_lengths = get_cumulative_seq_lengths(input_token_ids, reset_attention_mask)
         if self.cumulative_seq_lengths_padded is None:
-            b, s = input_token_ids.shape
-            self.cumulative_seq_lengths_padded = add_cumulative_seq_lengths_padding(self.cumulative_seq_lengths, b * (s + 1))
+            if self.cumulative_seq_lengths is not None:
+                b, s = input_token_ids.shape
+                self.cumulative_seq_lengths_padded = add_cumulative_seq_lengths_padding(self.cumulative_seq_lengths, b * (s + 1))
+            else:
+                self.cumulative_seq_lengths_padded = get_cumulative_seq_lengths_padded(input_token_ids, reset_attention_mask)
+        # the un-padded form has a data-dependent length; while a CUDA graph is being captured only the padded
+        # form exists and consumers derive what they need from it
+        if self.cumulative_seq_lengths is None and not _capturing():
+            self.cumulative_seq_lengths = remove_cumulative_seq_lengths_padding(self.cumulative_seq_lengths_padded)
         if self.position_ids is None:
             self.position_ids = get_position_ids(input_token_ids, reset_position_ids)
         if self.loss_weights is None:

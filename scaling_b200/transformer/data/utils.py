@@ -44,6 +44,41 @@ def get_cumulative_seq_lengths(input_token_ids: torch.Tensor, reset_attention_ma
     return torch.cat((torch.zeros(1, dtype=torch.int32, device=dev), flat_ends.to(torch.int32)))
 
 
+def get_cumulative_seq_lengths_padded(input_token_ids: torch.Tensor, reset_attention_mask: bool = True,
+                                      eod_token: int = EOD_TOKEN) -> torch.Tensor:
+    """Cumulative document lengths padded with -1 to the fixed length ``b * (s + 1)``.
+
+    Computed with fixed-shape operations only (a sort instead of ``nonzero``), so it neither synchronises the
+    host nor breaks CUDA-graph capture; equals ``add_cumulative_seq_lengths_padding(get_cumulative_seq_lengths(..))``.
+    """
+    b, s = input_token_ids.shape
+    dev = input_token_ids.device
+    total = b * s
+    if reset_attention_mask:
+        ends = _document_ends(input_token_ids, eod_token).reshape(-1)
+    else:
+        ends = torch.zeros(b, s, dtype=torch.bool, device=dev)
+        ends[:, -1] = True
+        ends = ends.reshape(-1)
+    big = total + 1
+    marks = torch.where(ends, torch.arange(1, total + 1, dtype=torch.int32, device=dev),
+                        torch.full((total,), big, dtype=torch.int32, device=dev))
+    ordered = torch.sort(marks).values
+    ordered = torch.where(ordered == big, torch.full_like(ordered, -1), ordered)
+    head = torch.zeros(1, dtype=torch.int32, device=dev)
+    tail = torch.full((b - 1,), -1, dtype=torch.int32, device=dev)
+    return torch.cat((head, ordered, tail))
+
+
+def document_ranges_from_padded(cumulative_seq_lengths_padded: torch.Tensor, total: int) -> tuple[torch.Tensor, torch.Tensor]:
+    """Per token ``(first token of its document, one past its last token)`` as int32, fixed-shape operations only."""
+    cu = cumulative_seq_lengths_padded.to(torch.int64)
+    cu = torch.where(cu < 0, torch.full_like(cu, total + 1), cu)
+    idx = torch.arange(total, device=cu.device)
+    doc = (torch.searchsorted(cu, idx, right=True) - 1).clamp_(0, cu.numel() - 2)
+    return cu[doc].to(torch.int32).contiguous(), cu[doc + 1].clamp(max=total).to(torch.int32).contiguous()
+
+
 def get_position_ids(input_token_ids: torch.Tensor, reset_position_ids: bool = True,
                      eod_token: int = EOD_TOKEN) -> torch.Tensor:
     b, s = input_token_ids.shape

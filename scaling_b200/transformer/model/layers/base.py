@@ -43,7 +43,24 @@ class TransformerLayerIO(_FieldRecord, BaseLayerIO):
         """Copy with some fields replaced."""
         fields = {n: getattr(self, n) for n in self.field_names()}
         fields.update(changes)
-        return TransformerLayerIO(**fields)
+        out = TransformerLayerIO(**fields)
+        out._doc_ranges = getattr(self, "_doc_ranges", None)
+        return out
+
+    def document_ranges(self) -> Optional[tuple[torch.Tensor, torch.Tensor]]:
+        """Per-token ``(document start, document end)`` for the fused attention kernel, derived once per micro
+        batch from the fixed-length padded cumulative lengths (fixed shapes, no host synchronisation)."""
+        cached = getattr(self, "_doc_ranges", None)
+        if cached is not None:
+            return cached
+        padded = self.cumulative_seq_lengths_padded
+        if padded is None or not padded.is_cuda or self.inference_settings is not None:
+            return None
+        from ...data.utils import document_ranges_from_padded
+
+        total = self.activations.shape[0] * self.activations.shape[1]
+        self._doc_ranges = document_ranges_from_padded(padded, total)
+        return self._doc_ranges
 
 
 class TransformerLayerBaseIO(BaseLayer[TransformerLayerIO, TransformerLayerIO, TransformerLayerIO]):

@@ -108,13 +108,15 @@ class TransformerLayer(TransformerLayerBaseIO):
     def attention_block(self, hidden_state: torch.Tensor, cumulative_seq_lengths: torch.Tensor,
                         position_ids: torch.Tensor, use_cache: bool = False, reset_cache: bool = False,
                         cache_index: int = 0, attention_scores_manipulation: Optional[torch.Tensor] = None,
-                        attentions_score_manipulation_log_additive: Union[bool, list[bool]] = True) -> torch.Tensor:
+                        attentions_score_manipulation_log_additive: Union[bool, list[bool]] = True,
+                        doc_ranges: Optional[tuple[torch.Tensor, torch.Tensor]] = None) -> torch.Tensor:
         branch, skip = self.attn_residual_split(hidden_state)
         branch = self.self_attention(
             self.input_layernorm(branch), cumulative_seq_lengths=cumulative_seq_lengths, position_ids=position_ids,
             use_cache=use_cache, reset_cache=reset_cache, cache_index=cache_index,
             attention_scores_manipulation=attention_scores_manipulation,
             attentions_score_manipulation_log_additive=attentions_score_manipulation_log_additive,
+            doc_ranges=doc_ranges,
         )
         h = self.attn_residual_add(self._dropout(self.dropout_attention, branch), skip)
         if hasattr(self, "attn_adapter_name"):
@@ -131,12 +133,13 @@ class TransformerLayer(TransformerLayerBaseIO):
 
     def forward(self, x: TransformerLayerIO) -> TransformerLayerIO:
         s = x.inference_settings
-        assert x.cumulative_seq_lengths is not None
+        assert x.cumulative_seq_lengths is not None or x.cumulative_seq_lengths_padded is not None
         h = self.attention_block(
             x.activations, cumulative_seq_lengths=x.cumulative_seq_lengths, position_ids=x.position_ids,
             use_cache=s.use_cache if s else False, reset_cache=s.reset_cache if s else False,
             cache_index=s.cache_index if s else 0, attention_scores_manipulation=x.attention_scores_manipulation,
             attentions_score_manipulation_log_additive=s.control_log_additive_batch if s else True,
+            doc_ranges=x.document_ranges(),
         )
         h = self.mlp_block(h)
         record_embedding(x, self.layer_index + 1, h)

@@ -77,7 +77,9 @@ def test_noalloc_matches_regular_entry_point_twice(rms, dtype, code):
                 continue
             rel = ((a.float() - b.float()).norm() / (b.float().norm() + 1e-12)).item()
             assert rel < tol, rel
-        assert torch.equal(out["noalloc"][0], out["regular"][0])  # dx does not depend on the partial-row count
+        # dx does not depend on the partial-row count, only on the order of the per-row sums, which may differ
+        # between the block-per-row kernel of this entry point and the kernel the regular entry point picks
+        assert torch.allclose(out["noalloc"][0].float(), out["regular"][0].float(), rtol=tol, atol=tol)
 
 
 def test_noalloc_rejects_oversized_rows():
