@@ -374,6 +374,9 @@ class ParallelSelfAttention(torch.nn.Module):
         b, s, _ = x.shape
         T = b * s
         d = self.hidden_size_per_attention_head
+        if self._packed_path_ok(x, use_cache, reset_cache):
+            hidden = self._packed_attention(x, cumulative_seq_lengths, position_ids, doc_ranges)
+            return self._output_projection(hidden)
         q, k, v = self._project_qkv(x)
 
         if self.key_query_norm:
@@ -437,8 +440,49 @@ class ParallelSelfAttention(torch.nn.Module):
             ctx = core2(q.view(b, s, -1, d), kb, vb, cumulative_seq_lengths,
                         attention_scores_manipulation=attention_scores_manipulation,
                         attentions_score_manipulation_log_additive=attentions_score_manipulation_log_additive)
-        hidden = ctx.reshape(b, s, -1)
+        return self._output_projection(ctx.reshape(b, s, -1))
 
+    def _packed_path_ok(self, x: torch.Tensor, use_cache: bool, reset_cache: bool) -> bool:
+        """The fused projection -> rotary -> attention path covers training-style self-attention on CUDA with a
+        packed qkv weight, all heads global or all local, no adapters, no q/k norm, no attention dropout."""
+        if not (self.use_flash_attention and self.qkv_in_one and x.is_cuda and x.dtype == torch.bfloat16):
+            return False
+        if use_cache or reset_cache or self.key_query_norm:
+            return False
+        if self.lora_config is not None and not self.lora_merged_state:
+            return False
+        if self.hidden_size_per_attention_head not in (64, 128):
+            return False
+        if 0 < self.num_local_attention_heads < self.num_attention_heads:
+            return False
+        core = self.scaled_dot_product_attention
+        if core._use_umup or (core.dropout_p > 0.0 and self.training):
+            return False
+        from ....ops import _lib
+
+        return _lib.lib_has("sb200_fa_bwd_strided")
+
+    def _packed_attention(self, x: torch.Tensor, cumulative_seq_lengths: Optional[torch.Tensor],
+                          position_ids: Optional[torch.Tensor],
+                          doc_ranges: Optional[tuple[torch.Tensor, torch.Tensor]]) -> torch.Tensor:
+        from ....ops.attention_kernel import packed_qkv_attention
+
+        b, s, _ = x.shape
+        d = self.hidden_size_per_attention_head
+        qkv = self.query_key_value(x).view(b * s, self.num_attention_heads_per_partition, 3 * d)
+        rotary = pos = None
+        if self.rotary_embedding is not None:
+            rot = self.rotary_embedding
+            rotary = (rot.dimensions, rot.base, rot.interleaved)
+            pos = (position_ids.reshape(-1) if position_ids is not None
+                   else torch.arange(s, device=x.device, dtype=torch.int32).repeat(b))
+        core = self.scaled_dot_product_attention
+        window = core.local_attention_window_size if self.num_local_attention_heads > 0 else None
+        ctx = packed_qkv_attention(qkv, pos, rotary, cumulative_seq_lengths, self.causal,
+                                   core.query_key_scaling_factor, window, doc_ranges)
+        return ctx.reshape(b, s, -1)
+
+    def _output_projection(self, hidden: torch.Tensor) -> torch.Tensor:
         lora_dense = None
         if self.lora_config and not self.lora_merged_state and LoRAModuleType.DENSE in self.lora_config.parallel_modules:
             full = all_concat(hidden, self.topology) if self.model_parallel_size > 1 else hidden

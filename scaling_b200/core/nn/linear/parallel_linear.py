@@ -223,6 +223,9 @@ class RowParallelLinear(_ParallelLinear):
             x = all_shard(x, self.topology)
         if self._use_umup:
             y, bias = self._umup_matmul(x)
+        elif self.model_parallel_size == 1:
+            # nothing is reduced afterwards: the bias goes into the GEMM epilogue
+            return self._matmul(x, self.weight, self._bias())
         else:
             y, bias = self._matmul(x, self.weight, None), self._bias()
         if not (self.parallel_output or self.topology is None):

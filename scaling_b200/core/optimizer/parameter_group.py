@@ -106,6 +106,8 @@ class OptimizerParamGroup:
                 view.copy_(p.data)
                 p.data = view
                 p.grad = self.flat_grad[off:off + p.numel()].view(p.shape)
+                # backward kernels may add into this persistent buffer from their epilogue
+                p.fused_grad_accumulation = True  # type: ignore[attr-defined]
 
         lo, hi = self.owned_range
         if self.dtype == torch.float32:

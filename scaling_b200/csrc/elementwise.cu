@@ -144,6 +144,109 @@ __global__ void rope_kernel(T* __restrict__ x, const int* __restrict__ pos, int 
   }
 }
 
+// Vectorised form: one thread rotates 16 bytes of the first operand of the pairs and their partners.  Work items
+// are ordered (token, head, sub-tensor, chunk), so that a packed [q | k | v] head layout (n_sub = 2, ld_sub = d) is
+// swept with contiguous accesses.  mode 0: chunk c pairs elements [c*V, c*V + V) with the same range + rot/2;
+// mode 1: chunk c holds V/2 pairs (2i, 2i + 1).
+template <typename T>
+__global__ void rope_vec_kernel(T* __restrict__ x, const int* __restrict__ pos, long total, int n_heads, int n_sub,
+                                int n_chunk, int rot_dim, long ld_tok, long ld_head, long ld_sub, float log2_base,
+                                int mode, float sign) {
+  constexpr int V = sb::Vec16<T>::N;
+  const int half = rot_dim >> 1;
+  for (long idx = blockIdx.x * (long)blockDim.x + threadIdx.x; idx < total; idx += (long)gridDim.x * blockDim.x) {
+    const int c = (int)(idx % n_chunk);
+    long r = idx / n_chunk;
+    const int sub = (int)(r % n_sub);
+    r /= n_sub;
+    const int h = (int)(r % n_heads);
+    const long t = r / n_heads;
+    const float p = (float)pos[t];
+    T* base = x + t * ld_tok + h * ld_head + sub * ld_sub;
+    if (mode == 0) {
+      sb::Vec16<T> a = sb::ld16(base + c * V), b = sb::ld16(base + half + c * V);
+#pragma unroll
+      for (int i = 0; i < V; ++i) {
+        float sn, cs;
+        sincosf(p * exp2f(-log2_base * (2.f * (float)(c * V + i)) / (float)rot_dim), &sn, &cs);
+        sn *= sign;
+        const float fa = sb::to_f(a.e[i]), fb = sb::to_f(b.e[i]);
+        a.e[i] = sb::from_f<T>(fa * cs - fb * sn);
+        b.e[i] = sb::from_f<T>(fb * cs + fa * sn);
+      }
+      sb::st16(base + c * V, a);
+      sb::st16(base + half + c * V, b);
+    } else {
+      sb::Vec16<T> a = sb::ld16(base + c * V);
+#pragma unroll
+      for (int i = 0; i < V / 2; ++i) {
+        float sn, cs;
+        sincosf(p * exp2f(-log2_base * (2.f * (float)(c * (V / 2) + i)) / (float)rot_dim), &sn, &cs);
+        sn *= sign;
+        const float fa = sb::to_f(a.e[2 * i]), fb = sb::to_f(a.e[2 * i + 1]);
+        a.e[2 * i] = sb::from_f<T>(fa * cs - fb * sn);
+        a.e[2 * i + 1] = sb::from_f<T>(fb * cs + fa * sn);
+      }
+      sb::st16(base + c * V, a);
+    }
+  }
+}
+
+// ------------------------------------------------------------- column sums
+// partial[r][c] = sum over the rows of split r of x[row][c].  A CTA owns a strip of 32 * V columns and one row
+// split; warp w takes rows w, w + 8, ... of the split, and the eight warp sums are added in a fixed order.
+template <typename T>
+__global__ void __launch_bounds__(256)
+    colsum_partial_kernel(const T* __restrict__ x, float* __restrict__ partial, long M, int N, long ld,
+                          long rows_per_split) {
+  constexpr int V = sb::Vec16<T>::N;
+  __shared__ float red[8][32 * V];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int c = (blockIdx.x * 32 + lane) * V;
+  const long r0 = blockIdx.y * rows_per_split;
+  long r1 = r0 + rows_per_split;
+  if (r1 > M) r1 = M;
+  float acc[V];
+#pragma unroll
+  for (int i = 0; i < V; ++i) acc[i] = 0.f;
+  if (c < N) {
+    long r = r0 + warp;
+    for (; r + 8 < r1; r += 16) {
+      sb::Vec16<T> a = sb::ld16(x + r * ld + c), b = sb::ld16(x + (r + 8) * ld + c);
+#pragma unroll
+      for (int i = 0; i < V; ++i) acc[i] += sb::to_f(a.e[i]) + sb::to_f(b.e[i]);
+    }
+    for (; r < r1; r += 8) {
+      sb::Vec16<T> a = sb::ld16(x + r * ld + c);
+#pragma unroll
+      for (int i = 0; i < V; ++i) acc[i] += sb::to_f(a.e[i]);
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < V; ++i) red[warp][lane * V + i] = acc[i];
+  __syncthreads();
+  for (int t = threadIdx.x; t < 32 * V; t += 256) {
+    const int col = blockIdx.x * 32 * V + t;
+    if (col < N) {
+      float s = 0.f;
+#pragma unroll
+      for (int w = 0; w < 8; ++w) s += red[w][t];
+      partial[(long)blockIdx.y * N + col] = s;
+    }
+  }
+}
+// out[c] = (accumulate ? out[c] : 0) + sum_r partial[r][c], fixed order
+template <typename T>
+__global__ void colsum_final_kernel(const float* __restrict__ partial, T* __restrict__ out, int R, int N,
+                                    int accumulate) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= N) return;
+  float s = 0.f;
+  for (int r = 0; r < R; ++r) s += partial[(long)r * N + c];
+  if (accumulate) s += sb::to_f(out[c]);
+  out[c] = sb::from_f<T>(s);
+}
+
 // ----------------------------------------------------------- masked softmax
 // x: [rows, cols]; mask (uint8, 1 = masked) addressed as mask[(row / rows_per_mask_div) ...]:
 // row r of x uses mask row  (r / (heads * sq)) * sq + (r % sq)  when the mask is [b, 1, sq, sk].
@@ -284,18 +387,66 @@ SB_API int sb200_add(const void* a, const void* b, void* y, long n, int dtype, c
   SB_CHECK_LAUNCH();
   return SB_OK;
 }
-SB_API int sb200_rope(void* x, const int* pos, int tokens, int n_heads, int rot_dim, long ld_tok, long ld_head,
-                      float base, int mode, int backward, int dtype, cudaStream_t stream) {
-  if (tokens <= 0 || n_heads <= 0 || rot_dim <= 0) return SB_OK;
+// In-place rotary embedding of n_sub tensors that share token and head strides and start ld_sub elements apart
+// (e.g. the q and k parts of a packed [tokens, heads, 3 * d] projection: n_sub = 2, ld_sub = d).
+SB_API int sb200_rope_multi(void* x, const int* pos, int tokens, int n_heads, int rot_dim, long ld_tok, long ld_head,
+                            int n_sub, long ld_sub, float base, int mode, int backward, int dtype,
+                            cudaStream_t stream) {
+  if (tokens <= 0 || n_heads <= 0 || rot_dim <= 0 || n_sub <= 0) return SB_OK;
   if (rot_dim & 1) return SB_ERR_BAD_ARG;
   int half = rot_dim / 2;
-  int tx = half >= 64 ? 64 : (half >= 32 ? 32 : 16);
-  int ty = 256 / tx;
-  if (ty > n_heads) ty = n_heads;
-  dim3 block(tx, ty);
   SB_DISPATCH_DTYPE(dtype, T, {
-    rope_kernel<T><<<tokens, block, 0, stream>>>((T*)x, pos, tokens, n_heads, rot_dim, ld_tok, ld_head, log2f(base),
-                                                  mode, backward ? -1.f : 1.f);
+    constexpr int V = sb::Vec16<T>::N;
+    const int span = mode == 0 ? half : rot_dim;
+    const bool vec = span % V == 0 && ld_tok % V == 0 && ld_head % V == 0 && ld_sub % V == 0 &&
+                     (reinterpret_cast<uintptr_t>(x) & 15) == 0;
+    if (vec) {
+      const int n_chunk = span / V;
+      const long total = (long)tokens * n_heads * n_sub * n_chunk;
+      rope_vec_kernel<T><<<grid_for(total, 256), 256, 0, stream>>>((T*)x, pos, total, n_heads, n_sub, n_chunk, rot_dim,
+                                                                   ld_tok, ld_head, ld_sub, log2f(base), mode,
+                                                                   backward ? -1.f : 1.f);
+    } else {
+      int tx = half >= 64 ? 64 : (half >= 32 ? 32 : 16);
+      int ty = 256 / tx;
+      if (ty > n_heads) ty = n_heads;
+      dim3 block(tx, ty);
+      for (int sub = 0; sub < n_sub; ++sub)
+        rope_kernel<T><<<tokens, block, 0, stream>>>((T*)x + sub * ld_sub, pos, tokens, n_heads, rot_dim, ld_tok,
+                                                      ld_head, log2f(base), mode, backward ? -1.f : 1.f);
+    }
+  });
+  SB_CHECK_LAUNCH();
+  return SB_OK;
+}
+SB_API int sb200_rope(void* x, const int* pos, int tokens, int n_heads, int rot_dim, long ld_tok, long ld_head,
+                      float base, int mode, int backward, int dtype, cudaStream_t stream) {
+  return sb200_rope_multi(x, pos, tokens, n_heads, rot_dim, ld_tok, ld_head, 1, 0, base, mode, backward, dtype, stream);
+}
+// Row splits used by sb200_colsum for an [M, N] input; the caller provides `partial` of [splits, N] floats.
+SB_API int sb200_colsum_splits(long M, int N, int elem_size, int sm_count) {
+  const int V = 16 / (elem_size > 0 ? elem_size : 2);
+  const int strips = (N + 32 * V - 1) / (32 * V);
+  long r = (2L * sm_count + strips - 1) / strips;
+  const long max_r = (M + 63) / 64;
+  if (r > max_r) r = max_r;
+  if (r > 128) r = 128;
+  if (r < 1) r = 1;
+  return (int)r;
+}
+// out[N] (+)= column sums of x[M, N] (row stride ld elements, N and ld multiples of 16 bytes); deterministic.
+SB_API int sb200_colsum(const void* x, void* out, float* partial, long M, int N, long ld, int splits, int accumulate,
+                        int dtype, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return SB_OK;
+  if (splits < 1) return SB_ERR_BAD_ARG;
+  SB_DISPATCH_DTYPE(dtype, T, {
+    constexpr int V = sb::Vec16<T>::N;
+    if (N % V || ld % V || (reinterpret_cast<uintptr_t>(x) & 15)) return SB_ERR_BAD_ARG;
+    const int strips = (N + 32 * V - 1) / (32 * V);
+    const long rows_per = (M + splits - 1) / splits;
+    colsum_partial_kernel<T><<<dim3(strips, splits), 256, 0, stream>>>((const T*)x, partial, M, N, ld, rows_per);
+    SB_CHECK_LAUNCH();
+    colsum_final_kernel<T><<<(N + 127) / 128, 128, 0, stream>>>(partial, (T*)out, splits, N, accumulate);
   });
   SB_CHECK_LAUNCH();
   return SB_OK;

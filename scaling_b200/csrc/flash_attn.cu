@@ -45,6 +45,8 @@ struct FaParams {
   void* dQ;          // [T, Hq, D]
   void* dK;          // [T, Hkv, D]
   void* dV;          // [T, Hkv, D]
+  long lddq_tok, lddk_tok, lddv_tok;     // element strides of the gradient outputs: token rows ...
+  int lddq_head, lddk_head, lddv_head;   // ... and heads inside a row
   int* status;
 };
 
@@ -563,8 +565,10 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
               *reinterpret_cast<uint4*>(pk + g * 4) = make_uint4(b[g * 4], b[g * 4 + 1], b[g * 4 + 2], b[g * 4 + 3]);
             }
           } else {
-            __nv_bfloat16* dk = reinterpret_cast<__nv_bfloat16*>(p.dK) + row * D + ch * 32;
-            __nv_bfloat16* dv = reinterpret_cast<__nv_bfloat16*>(p.dV) + row * D + ch * 32;
+            __nv_bfloat16* dk = reinterpret_cast<__nv_bfloat16*>(p.dK) + (long)kidx * p.lddk_tok +
+                                (long)hk * p.lddk_head + ch * 32;
+            __nv_bfloat16* dv = reinterpret_cast<__nv_bfloat16*>(p.dV) + (long)kidx * p.lddv_tok +
+                                (long)hk * p.lddv_head + ch * 32;
 #pragma unroll
             for (int g = 0; g < 4; ++g) {
               uint4 u, w;
@@ -597,9 +601,10 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
   if (threadIdx.x == 0 && *abort_flag && p.status) *p.status = SB_ERR_WAIT_TIMEOUT;
 }
 
-// out[i] = bf16(sum_s partial[s][i]) in fixed order
+// out[t, h, c] = bf16(sum_s partial[s][t, h, c]) in fixed order; partial rows are dense [T, H, D], the output has
+// element strides (ld_tok, ld_head)
 __global__ void fa_bwd_reduce_kernel(const float* __restrict__ partial, __nv_bfloat16* __restrict__ out, long n,
-                                     int splits) {
+                                     int splits, int H, int D, long ld_tok, int ld_head) {
   long i = (blockIdx.x * (long)blockDim.x + threadIdx.x) * 4;
   if (i >= n) return;
   float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -610,7 +615,11 @@ __global__ void fa_bwd_reduce_kernel(const float* __restrict__ partial, __nv_bfl
   uint2 u;
   u.x = pack_bf16(acc.x, acc.y);
   u.y = pack_bf16(acc.z, acc.w);
-  *reinterpret_cast<uint2*>(out + i) = u;
+  const long th = i / D;
+  const int c = (int)(i - th * D);
+  const long t = th / H;
+  const int h = (int)(th - t * H);
+  *reinterpret_cast<uint2*>(out + t * ld_tok + (long)h * ld_head + c) = u;
 }
 
 // ============================================================================ backward: dQ
@@ -760,7 +769,7 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
     }
     if (ok && n_tiles > 0 && sb::mbar_wait(acc_done, (n_tiles - 1) & 1, abort_flag)) {
       sb::tc_fence_after();
-      __nv_bfloat16* dq = reinterpret_cast<__nv_bfloat16*>(p.dQ) + ((long)t * p.Hq + h) * D;
+      __nv_bfloat16* dq = reinterpret_cast<__nv_bfloat16*>(p.dQ) + (long)t * p.lddq_tok + (long)h * p.lddq_head;
 #pragma unroll 1
       for (int ch = 0; ch < D / 32; ++ch) {
         uint32_t a[32];
@@ -892,13 +901,18 @@ SB_API int sb200_fa_bwd_splits(int T, int Hq, int Hkv, int sm_count) {
   return (group + hps - 1) / hps;
 }
 
-// Backward.  o, d_o, dq: [T, Hq, D] contiguous; dk, dv: [T, Hkv, D] contiguous; delta: scratch [Hq, T] floats;
-// dkv_partial: scratch for split accumulation (see sb200_fa_bwd_splits), may be null when splits == 1.
-SB_API int sb200_fa_bwd(const void* q, const void* k, const void* v, const void* o, const void* d_o, const float* lse2,
-                        float* delta, float* dkv_partial, int splits, void* dq, void* dk, void* dv,
-                        const int* doc_start, const int* doc_end, int T,
-                        int Hq, int Hkv, int D, long ldq_tok, int ldq_head, long ldk_tok, int ldk_head, long ldv_tok,
-                        int ldv_head, int causal, int window, float scale, int* status, cudaStream_t stream) {
+// Backward.  o, d_o: [T, Hq, D] contiguous; delta: scratch [Hq, T] floats; dkv_partial: scratch for split
+// accumulation (see sb200_fa_bwd_splits), may be null when splits == 1.  The gradients dq [T, Hq, D] and
+// dk, dv [T, Hkv, D] have unit stride in D and the given element strides between token rows and heads (multiples
+// of 8), so that they can be views into one packed buffer.
+SB_API int sb200_fa_bwd_strided(const void* q, const void* k, const void* v, const void* o, const void* d_o,
+                                const float* lse2, float* delta, float* dkv_partial, int splits, void* dq, void* dk,
+                                void* dv, const int* doc_start, const int* doc_end, int T, int Hq, int Hkv, int D,
+                                long ldq_tok, int ldq_head, long ldk_tok, int ldk_head, long ldv_tok, int ldv_head,
+                                long lddq_tok, int lddq_head, long lddk_tok, int lddk_head, long lddv_tok,
+                                int lddv_head, int causal, int window, float scale, int* status,
+                                cudaStream_t stream) {
+  if ((lddq_tok | lddq_head | lddk_tok | lddk_head | lddv_tok | lddv_head) & 7) return SB_ERR_BAD_ARG;
   if (T <= 0 || Hq <= 0) return SB_OK;
   if ((D != 64 && D != 128) || Hkv <= 0 || Hq % Hkv) return SB_ERR_BAD_ARG;
   if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o) || !aligned16(d_o) || !aligned16(dq) ||
@@ -916,6 +930,8 @@ SB_API int sb200_fa_bwd(const void* q, const void* k, const void* v, const void*
   p.doc_start = doc_start; p.doc_end = doc_end;
   p.ldq_head = ldq_head; p.ldk_head = ldk_head; p.ldv_head = ldv_head; p.ldo_head = D;
   p.lse2 = const_cast<float*>(lse2); p.delta = delta; p.dQ = dq; p.dK = dk; p.dV = dv; p.status = status;
+  p.lddq_tok = lddq_tok; p.lddk_tok = lddk_tok; p.lddv_tok = lddv_tok;
+  p.lddq_head = lddq_head; p.lddk_head = lddk_head; p.lddv_head = lddv_head;
   const int tiles = (T + TILE - 1) / TILE;
   const int group = Hq / Hkv;
   if (splits < 1) splits = 1;
@@ -963,9 +979,22 @@ SB_API int sb200_fa_bwd(const void* q, const void* k, const void* v, const void*
   if (splits > 1) {
     const long n = (long)T * Hkv * D;
     const int blocks = (int)((n / 4 + 255) / 256);
-    fa_bwd_reduce_kernel<<<blocks, 256, 0, stream>>>(dk_part, (__nv_bfloat16*)dk, n, splits);
-    fa_bwd_reduce_kernel<<<blocks, 256, 0, stream>>>(dv_part, (__nv_bfloat16*)dv, n, splits);
+    fa_bwd_reduce_kernel<<<blocks, 256, 0, stream>>>(dk_part, (__nv_bfloat16*)dk, n, splits, Hkv, D, lddk_tok,
+                                                     lddk_head);
+    fa_bwd_reduce_kernel<<<blocks, 256, 0, stream>>>(dv_part, (__nv_bfloat16*)dv, n, splits, Hkv, D, lddv_tok,
+                                                     lddv_head);
     SB_CHECK_LAUNCH();
   }
   return SB_OK;
+}
+
+// Same with contiguous gradient outputs.
+SB_API int sb200_fa_bwd(const void* q, const void* k, const void* v, const void* o, const void* d_o, const float* lse2,
+                        float* delta, float* dkv_partial, int splits, void* dq, void* dk, void* dv,
+                        const int* doc_start, const int* doc_end, int T,
+                        int Hq, int Hkv, int D, long ldq_tok, int ldq_head, long ldk_tok, int ldk_head, long ldv_tok,
+                        int ldv_head, int causal, int window, float scale, int* status, cudaStream_t stream) {
+  return sb200_fa_bwd_strided(q, k, v, o, d_o, lse2, delta, dkv_partial, splits, dq, dk, dv, doc_start, doc_end, T, Hq,
+                              Hkv, D, ldq_tok, ldq_head, ldk_tok, ldk_head, ldv_tok, ldv_head, (long)Hq * D, D,
+                              (long)Hkv * D, D, (long)Hkv * D, D, causal, window, scale, status, stream);
 }

@@ -14,8 +14,15 @@
 // Structure: persistent CTAs (one per SM), 128 x BN output tiles, BK = 64.
 //   warp 0    TMA producer: cp.async.bulk.tensor tiles (128-byte swizzle) into a ring of stages
 //   warp 1    allocates TMEM, issues tcgen05.mma (one elected thread), commits to mbarriers
-//   warps 2-5 epilogue: tcgen05.ld the accumulator (TMEM is double buffered, so the epilogue of
-//             tile i overlaps the MMAs of tile i+1), bias / GELU / accumulate, 16-byte stores
+//   warps 2-9 epilogue: tcgen05.ld the accumulator (TMEM is double buffered, so the epilogue of
+//             tile i overlaps the MMAs of tile i+1); two warps share a TMEM lane quadrant and take half of
+//             the columns each.  bias (staged in shared memory) / GELU / optional pre-activation output;
+//             16-bit results are packed into a swizzled staging box and leave through TMA stores, which
+//             also clip partial tiles.  fp32 output, accumulation into C and unaligned C use 16-byte
+//             stores from registers instead.
+// Split-K: a work unit is (tile, k-split).  Every split writes its fp32 partial tile to a workspace and
+//   bumps a per-tile counter; the CTA that arrives last adds the partials in split order (a fixed
+//   order, so results do not depend on timing) and runs the epilogue.  Nothing waits on another CTA.
 // All mbarrier waits are bounded; on expiry the CTA sets *status and unwinds (TMEM is freed).
 #include <cuda.h>
 
@@ -25,7 +32,9 @@ namespace {
 
 constexpr int BM = 128;
 constexpr int BK = 64;
-constexpr int GEMM_THREADS = 192;
+constexpr int EPI_WARPS = 8;
+constexpr int GEMM_THREADS = 64 + EPI_WARPS * 32;
+constexpr int STAGE_BOX_BYTES = 32 * 128;  // one epilogue staging box: 32 rows x 64 16-bit columns
 
 struct GemmParams {
   void* C;
@@ -36,6 +45,10 @@ struct GemmParams {
   int act;         // 0 none, 1 gelu
   int accumulate;  // C += result
   int ab_fmt;      // 0 fp16, 1 bf16
+  int splits;      // k-splits per tile (1: none)
+  int tma_store;   // 1: 16-bit C (and C_pre) leave through the tensor maps tmC / tmP
+  float* ws_partial;  // split-K: [tiles * splits][BN / 32][128][32] floats
+  int* ws_counter;    // split-K: one arrival counter per tile, zero between launches
   int* status;
 };
 
@@ -45,10 +58,48 @@ template <int BN> struct GemmCfg {
   static constexpr int B_BYTES = BN * BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int TMEM_COLS = 2 * BN;
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+  static constexpr int EPI_BYTES = EPI_WARPS * STAGE_BOX_BYTES;
+  static constexpr int BIAS_BYTES = 2 * BN * 2;  // two tiles' worth of 16-bit bias values
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_BYTES + BIAS_BYTES + 1024 /*align*/ + (BN == 256 ? 128 : 256) /*barriers*/;
 };
 
-__device__ __forceinline__ float gelu_erf(float x) { return 0.5f * x * (1.f + erff(x * 0.70710678118654752f)); }
+// Exact-form GELU 0.5 x (1 + erf(x / sqrt 2)) with erf from the rational approximation 7.1.26 of Abramowitz and
+// Stegun (absolute error below 1.5e-7, far under the rounding of 16-bit outputs); about a third of the
+// instructions of erff, which matters because the epilogue shares the SM with the MMA issue.
+__device__ __forceinline__ float gelu_erf(float x) {
+  const float z = fabsf(x) * 0.70710678118654752f;
+  const float t = __frcp_rn(fmaf(0.3275911f, z, 1.f));
+  float poly = fmaf(1.061405429f, t, -1.453152027f);
+  poly = fmaf(poly, t, 1.421413741f);
+  poly = fmaf(poly, t, -0.284496736f);
+  poly = fmaf(poly, t, 0.254829592f);
+  float e;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(-z * z * 1.4426950408889634f));
+  const float erfc_abs = poly * t * e;            // 1 - erf(|x| / sqrt 2)
+  const float cdf_neg = 0.5f * erfc_abs;          // Phi(-|x|)
+  return x * (x >= 0.f ? 1.f - cdf_neg : cdf_neg);
+}
+__device__ __forceinline__ uint32_t pack2(float a, float b, __nv_bfloat16) {
+  __nv_bfloat162 t = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&t);
+}
+__device__ __forceinline__ uint32_t pack2(float a, float b, __half) {
+  __half2 t = __floats2half2_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&t);
+}
+__device__ __forceinline__ uint32_t pack2(float a, float, float) { return __float_as_uint(a); }  // unused for fp32
+// the two 16-bit bias values packed in w, as floats
+__device__ __forceinline__ void bias_pair(uint32_t w, int is_bf16, float& lo, float& hi) {
+  if (is_bf16) {
+    lo = __uint_as_float(w << 16);
+    hi = __uint_as_float(w & 0xffff0000u);
+  } else {
+    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w));
+    lo = f.x;
+    hi = f.y;
+  }
+}
+__device__ __forceinline__ void epi_bar_sync() { asm volatile("bar.sync 1, %0;" ::"n"(EPI_WARPS * 32) : "memory"); }
 
 template <typename OutT> __device__ __forceinline__ void store8(OutT* dst, const float* v);
 template <> __device__ __forceinline__ void store8<float>(float* dst, const float* v) {
@@ -83,26 +134,31 @@ template <typename OutT> __device__ __forceinline__ void load8(const OutT* src, 
 template <int BN, bool A_MN, bool B_MN, typename OutT>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
     gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                        const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmP,
                         const GemmParams p) {
   using Cfg = GemmCfg<BN>;
   constexpr int STAGES = Cfg::STAGES;
   extern __shared__ uint8_t smem_raw[];
   // 1024-byte alignment for the 128-byte swizzle atoms
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * Cfg::STAGE_BYTES);
+  uint8_t* epi_stage = smem + STAGES * Cfg::STAGE_BYTES;                       // [EPI_WARPS][4 KB]
+  uint16_t* sbias = reinterpret_cast<uint16_t*>(epi_stage + Cfg::EPI_BYTES);   // [2][BN] raw 16-bit values
+  uint64_t* bars = reinterpret_cast<uint64_t*>(epi_stage + Cfg::EPI_BYTES + Cfg::BIAS_BYTES);
   uint64_t* full_bar = bars;                  // [STAGES]
   uint64_t* empty_bar = bars + STAGES;        // [STAGES]
   uint64_t* tfull_bar = bars + 2 * STAGES;    // [2]
   uint64_t* tempty_bar = bars + 2 * STAGES + 2;  // [2]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  volatile int* last_flag = reinterpret_cast<volatile int*>(tmem_slot + 2);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int m_tiles = (p.M + BM - 1) / BM;
   const int n_tiles = (p.N + BN - 1) / BN;
-  const int num_tiles = m_tiles * n_tiles;
   const int num_kb = (p.K + BK - 1) / BK;
+  const int S = p.splits;
+  const int num_units = m_tiles * n_tiles * S;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -111,9 +167,10 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
     }
     for (int a = 0; a < 2; ++a) {
       sb::mbar_init(&tfull_bar[a], 1);
-      sb::mbar_init(&tempty_bar[a], 4);  // one arrive per epilogue warp
+      sb::mbar_init(&tempty_bar[a], EPI_WARPS);  // one arrive per epilogue warp
     }
     *abort_flag = 0;
+    *last_flag = 0;
     sb::mbar_fence_init();
   }
   if (warp == 1) {
@@ -133,9 +190,11 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      for (int unit = blockIdx.x; unit < num_units && ok; unit += gridDim.x) {
+        const int tile = unit / S, split = unit - tile * S;
         const int m_blk = tile / n_tiles, n_blk = tile % n_tiles;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        const int kb0 = (int)((long)split * num_kb / S), kb1 = (int)((long)(split + 1) * num_kb / S);
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!sb::mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag)) { ok = false; break; }
           uint8_t* a_s = smem + stage * Cfg::STAGE_BYTES;
           uint8_t* b_s = a_s + Cfg::A_BYTES;
@@ -167,11 +226,13 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      for (int unit = blockIdx.x; unit < num_units && ok; unit += gridDim.x) {
+        const int tile = unit / S, split = unit - tile * S;
+        const int kb0 = (int)((long)split * num_kb / S), kb1 = (int)((long)(split + 1) * num_kb / S);
         if (!sb::mbar_wait(&tempty_bar[acc], acc_phase ^ 1, abort_flag)) { ok = false; break; }
         sb::tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!sb::mbar_wait(&full_bar[stage], phase, abort_flag)) { ok = false; break; }
           sb::tc_fence_after();
           const uint32_t a_addr = sb::smem_u32(smem + stage * Cfg::STAGE_BYTES);
@@ -182,7 +243,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
                                         : sb::umma_smem_desc(a_addr + k * 32, 16, 1024);
             const uint64_t bdesc = B_MN ? sb::umma_smem_desc(b_addr + k * 2048, 8192, 1024)
                                         : sb::umma_smem_desc(b_addr + k * 32, 16, 1024);
-            sb::umma_f16_ss(d_tmem, adesc, bdesc, idesc, (kb | k) != 0);
+            sb::umma_f16_ss(d_tmem, adesc, bdesc, idesc, (kb > kb0) || (k != 0));
           }
           sb::umma_commit(&empty_bar[stage]);  // frees the smem stage once these MMAs retire
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
@@ -194,75 +255,214 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
     }
   } else {
     // ------------------------------------------------------------ epilogue
-    const int quad = warp & 3;  // TMEM lane quadrant this warp may access
+    const int ew = warp - 2;            // 0 .. EPI_WARPS-1
+    const int quad = warp & 3;          // TMEM lane quadrant this warp may access
+    const int chalf = ew >> 2;          // which half of the tile's columns this warp owns
+    const int et = threadIdx.x - 64;    // epilogue thread index
+    constexpr int HALF = BN / 2;
+    constexpr int CHUNKS = HALF / 32;   // 32-column chunks per warp
+    constexpr bool OUT16 = sizeof(OutT) == 2;
+    uint8_t* stage_buf = epi_stage + ew * STAGE_BOX_BYTES;
     int acc = 0;
     uint32_t acc_phase = 0;
+    int bias_buf = 0;
     OutT* C = reinterpret_cast<OutT*>(p.C);
     OutT* Cpre = reinterpret_cast<OutT*>(p.C_pre);
-    const __nv_bfloat16* bias_bf = reinterpret_cast<const __nv_bfloat16*>(p.bias);
-    const __half* bias_h = reinterpret_cast<const __half*>(p.bias);
+    const uint16_t* bias_raw = reinterpret_cast<const uint16_t*>(p.bias);
     const bool vec_ok = (p.ldc % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0) &&
                         (!p.C_pre || (reinterpret_cast<uintptr_t>(p.C_pre) & 15) == 0);
+    const bool use_tma = OUT16 && p.tma_store;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+    // A warp whose wait expired keeps walking the units without touching data, so that the named barriers
+    // below still see all their participants and nobody is left waiting.
+    for (int unit = blockIdx.x; unit < num_units; unit += gridDim.x) {
+      const int tile = unit / S;
       const int m_blk = tile / n_tiles, n_blk = tile % n_tiles;
-      if (!sb::mbar_wait(&tfull_bar[acc], acc_phase, abort_flag)) { ok = false; break; }
+      if (ok && !sb::mbar_wait(&tfull_bar[acc], acc_phase, abort_flag)) ok = false;
       sb::tc_fence_after();
       const int row = m_blk * BM + quad * 32 + lane;
-      const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + acc * BN;
+      const uint32_t t_acc = tmem_base + ((uint32_t)(quad * 32) << 16) + acc * BN;
+      const int acc_used = acc;
+      if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+
+      if (S > 1) {
+        // park this split's partial tile, then find out whether every other split has arrived already
+        float* part = p.ws_partial + ((long)unit * (BN / 32) * 128 + quad * 32 + lane) * 32;
 #pragma unroll 1
-      for (int ch = 0; ch < BN / 32; ++ch) {
-        uint32_t r[32];
-        sb::tmem_ld32(t_row + ch * 32, r);
-        sb::tmem_ld_wait();
-        const int n0 = n_blk * BN + ch * 32;
-        if (row < p.M && n0 < p.N) {
-          OutT* crow = C + (long)row * p.ldc + n0;
-          OutT* prow = Cpre ? Cpre + (long)row * p.ldc + n0 : nullptr;
+        for (int c = 0; c < CHUNKS && ok; ++c) {
+          const int ch = chalf * CHUNKS + c;
+          uint32_t r[32];
+          sb::tmem_ld32(t_acc + ch * 32, r);
+          sb::tmem_ld_wait();
+          float4* dst = reinterpret_cast<float4*>(part + (long)ch * 128 * 32);
 #pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            const int n = n0 + g * 8;
-            if (n >= p.N) break;
-            float v[8];
+          for (int g = 0; g < 8; ++g)
+            dst[g] = make_float4(__uint_as_float(r[g * 4]), __uint_as_float(r[g * 4 + 1]), __uint_as_float(r[g * 4 + 2]),
+                                 __uint_as_float(r[g * 4 + 3]));
+        }
+        sb::tc_fence_before();
+        __syncwarp();
+        if (lane == 0 && ok) sb::mbar_arrive(&tempty_bar[acc_used]);
+        __threadfence();
+        epi_bar_sync();
+        if (et == 0) {
+          const int old = atomicAdd(&p.ws_counter[tile], 1);
+          const int last = old == S - 1;
+          if (last) p.ws_counter[tile] = 0;  // every split has arrived: leave the counter clean for the next launch
+          *last_flag = last;
+        }
+        epi_bar_sync();
+        if (!*last_flag) continue;
+        __threadfence();
+      }
+
+      // v[0..32) = accumulator values of 32-column chunk `ch` of this thread's row
+      auto load_chunk = [&](int ch, float* v) {
+        if (S == 1) {
+          uint32_t r[32];
+          sb::tmem_ld32(t_acc + ch * 32, r);
+          sb::tmem_ld_wait();
 #pragma unroll
-            for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[g * 8 + i]);
-            const bool full8 = (n + 8 <= p.N);
-            if (p.bias) {
+          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+        } else {
 #pragma unroll
-              for (int i = 0; i < 8; ++i)
-                if (full8 || n + i < p.N)
-                  v[i] += p.ab_fmt ? __bfloat162float(bias_bf[n + i]) : __half2float(bias_h[n + i]);
+          for (int i = 0; i < 32; ++i) v[i] = 0.f;
+          for (int s2 = 0; s2 < S; ++s2) {  // split order: the sum does not depend on which CTA came last
+            const float4* src = reinterpret_cast<const float4*>(
+                p.ws_partial + (((long)(tile * S + s2) * (BN / 32) + ch) * 128 + quad * 32 + lane) * 32);
+#pragma unroll
+            for (int g = 0; g < 8; ++g) {
+              const float4 f = __ldcg(src + g);
+              v[g * 4] += f.x; v[g * 4 + 1] += f.y; v[g * 4 + 2] += f.z; v[g * 4 + 3] += f.w;
             }
-            if (p.accumulate) {
-              if (full8 && vec_ok) {
-                float o[8];
-                load8<OutT>(crow + g * 8, o);
+          }
+        }
+      };
+
+      const uint32_t* sb_tile = reinterpret_cast<const uint32_t*>(sbias + bias_buf * BN);  // pairs of columns
+      if (p.bias) {
+        if (et < BN) {
+          const int n = n_blk * BN + et;
+          sbias[bias_buf * BN + et] = n < p.N ? bias_raw[n] : (uint16_t)0;
+        }
+        epi_bar_sync();
+        bias_buf ^= 1;
+      }
+
+      if (!ok) continue;
+      if (use_tma) {
+        const int row0 = m_blk * BM + quad * 32;
+        // swizzled position of 16-byte chunk j of this lane's row inside the 32 x 128-byte staging box
+        uint8_t* my_row = stage_buf + lane * 128;
+        const int sw = lane & 7;
+#pragma unroll 1
+        for (int bx = 0; bx < CHUNKS / 2; ++bx) {
+          const int col0 = chalf * HALF + bx * 64;  // first column of this box inside the tile
+          const int n0 = n_blk * BN + col0;
+          if (n0 >= p.N || row0 >= p.M) break;
+          const int passes = Cpre ? 2 : 1;
+          for (int pass = 0; pass < passes; ++pass) {
+            const bool pre_pass = Cpre && pass == 0;
+            if (lane == 0) sb::tma_store_wait_read0();  // the previous store has finished reading the staging box
+            __syncwarp();
 #pragma unroll
-                for (int i = 0; i < 8; ++i) v[i] += o[i];
-              } else {
-                for (int i = 0; i < 8 && n + i < p.N; ++i) v[i] += sb::to_f(crow[g * 8 + i]);
+            for (int h = 0; h < 2; ++h) {
+              float v[32];
+              load_chunk(col0 / 32 + h, v);
+              if (p.bias) {
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                  float lo, hi;
+                  bias_pair(sb_tile[(col0 + h * 32) / 2 + i], p.ab_fmt, lo, hi);
+                  v[2 * i] += lo;
+                  v[2 * i + 1] += hi;
+                }
+              }
+              if (p.act == 1 && !pre_pass) {
+#pragma unroll
+                for (int i = 0; i < 32; ++i) v[i] = gelu_erf(v[i]);
+              }
+#pragma unroll
+              for (int g = 0; g < 4; ++g) {
+                uint4 u;
+                u.x = pack2(v[g * 8 + 0], v[g * 8 + 1], OutT());
+                u.y = pack2(v[g * 8 + 2], v[g * 8 + 3], OutT());
+                u.z = pack2(v[g * 8 + 4], v[g * 8 + 5], OutT());
+                u.w = pack2(v[g * 8 + 6], v[g * 8 + 7], OutT());
+                *reinterpret_cast<uint4*>(my_row + (((h * 4 + g) ^ sw) << 4)) = u;
               }
             }
-            if (prow) {
-              if (full8 && vec_ok) store8<OutT>(prow + g * 8, v);
-              else
-                for (int i = 0; i < 8 && n + i < p.N; ++i) prow[g * 8 + i] = sb::from_f<OutT>(v[i]);
+            sb::fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              sb::tma_store_2d(pre_pass ? &tmP : &tmC, stage_buf, n0, row0);
+              sb::tma_store_commit();
             }
-            if (p.act == 1) {
+          }
+        }
+      } else {
+#pragma unroll 1
+        for (int c = 0; c < CHUNKS; ++c) {
+          const int ch = chalf * CHUNKS + c;
+          const int n0 = n_blk * BN + ch * 32;
+          if (n0 >= p.N) break;  // warp-uniform
+          float r[32];
+          load_chunk(ch, r);
+          if (row < p.M) {
+            OutT* crow = C + (long)row * p.ldc + n0;
+            OutT* prow = Cpre ? Cpre + (long)row * p.ldc + n0 : nullptr;
 #pragma unroll
-              for (int i = 0; i < 8; ++i) v[i] = gelu_erf(v[i]);
+            for (int g = 0; g < 4; ++g) {
+              const int n = n0 + g * 8;
+              if (n >= p.N) break;
+              float v[8];
+#pragma unroll
+              for (int i = 0; i < 8; ++i) v[i] = r[g * 8 + i];
+              const bool full8 = (n + 8 <= p.N);
+              if (p.bias) {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                  float lo, hi;
+                  bias_pair(sb_tile[(ch * 32 + g * 8) / 2 + i], p.ab_fmt, lo, hi);
+                  v[2 * i] += lo;
+                  v[2 * i + 1] += hi;
+                }
+              }
+              if (p.accumulate) {
+                if (full8 && vec_ok) {
+                  float o[8];
+                  load8<OutT>(crow + g * 8, o);
+#pragma unroll
+                  for (int i = 0; i < 8; ++i) v[i] += o[i];
+                } else {
+                  for (int i = 0; i < 8 && n + i < p.N; ++i) v[i] += sb::to_f(crow[g * 8 + i]);
+                }
+              }
+              if (prow) {
+                if (full8 && vec_ok) store8<OutT>(prow + g * 8, v);
+                else
+                  for (int i = 0; i < 8 && n + i < p.N; ++i) prow[g * 8 + i] = sb::from_f<OutT>(v[i]);
+              }
+              if (p.act == 1) {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) v[i] = gelu_erf(v[i]);
+              }
+              if (full8 && vec_ok) store8<OutT>(crow + g * 8, v);
+              else
+                for (int i = 0; i < 8 && n + i < p.N; ++i) crow[g * 8 + i] = sb::from_f<OutT>(v[i]);
             }
-            if (full8 && vec_ok) store8<OutT>(crow + g * 8, v);
-            else
-              for (int i = 0; i < 8 && n + i < p.N; ++i) crow[g * 8 + i] = sb::from_f<OutT>(v[i]);
           }
         }
       }
-      sb::tc_fence_before();
-      __syncwarp();
-      if (lane == 0) sb::mbar_arrive(&tempty_bar[acc]);
-      if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+      if (S == 1) {
+        sb::tc_fence_before();
+        __syncwarp();
+        if (lane == 0) sb::mbar_arrive(&tempty_bar[acc_used]);
+      }
     }
+    // stores in flight read the staging boxes: drain them before shared memory goes away
+    if (lane == 0) sb::tma_store_wait_all0();
+    __syncwarp();
   }
 
   // ---------------------------------------------------------------- teardown
@@ -312,8 +512,8 @@ int make_tmap_2d(CUtensorMap* tm, const void* base, long rows, long cols, long l
 }
 
 template <int BN, bool A_MN, bool B_MN, typename OutT>
-int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, int sm_count,
-                cudaStream_t stream) {
+int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmC, const CUtensorMap& tmP,
+                const GemmParams& p, int sm_count, cudaStream_t stream) {
   using Cfg = GemmCfg<BN>;
   auto kern = gemm_tcgen05_kernel<BN, A_MN, B_MN, OutT>;
   static bool attr_set = false;
@@ -322,27 +522,67 @@ int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams
     if (e != cudaSuccess) return (int)e;
     attr_set = true;
   }
-  int tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
-  int grid = tiles < sm_count ? tiles : sm_count;
-  kern<<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, stream>>>(tmA, tmB, p);
+  int units = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN) * p.splits;
+  int grid = units < sm_count ? units : sm_count;
+  kern<<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, stream>>>(tmA, tmB, tmC, tmP, p);
   SB_CHECK_LAUNCH();
   return SB_OK;
 }
 
 template <bool A_MN, bool B_MN, typename OutT>
-int dispatch_bn(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, int bn, int sm_count,
-                cudaStream_t stream) {
-  if (bn == 256) return launch_gemm<256, A_MN, B_MN, OutT>(tmA, tmB, p, sm_count, stream);
-  return launch_gemm<128, A_MN, B_MN, OutT>(tmA, tmB, p, sm_count, stream);
+int dispatch_bn(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmC, const CUtensorMap& tmP,
+                const GemmParams& p, int bn, int sm_count, cudaStream_t stream) {
+  if (bn == 256) return launch_gemm<256, A_MN, B_MN, OutT>(tmA, tmB, tmC, tmP, p, sm_count, stream);
+  return launch_gemm<128, A_MN, B_MN, OutT>(tmA, tmB, tmC, tmP, p, sm_count, stream);
 }
 
 template <typename OutT>
-int dispatch_major(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, int a_mn, int b_mn, int bn,
-                   int sm_count, cudaStream_t stream) {
-  if (!a_mn && !b_mn) return dispatch_bn<false, false, OutT>(tmA, tmB, p, bn, sm_count, stream);
-  if (!a_mn && b_mn) return dispatch_bn<false, true, OutT>(tmA, tmB, p, bn, sm_count, stream);
-  if (a_mn && b_mn) return dispatch_bn<true, true, OutT>(tmA, tmB, p, bn, sm_count, stream);
+int dispatch_major(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmC, const CUtensorMap& tmP,
+                   const GemmParams& p, int a_mn, int b_mn, int bn, int sm_count, cudaStream_t stream) {
+  if (!a_mn && !b_mn) return dispatch_bn<false, false, OutT>(tmA, tmB, tmC, tmP, p, bn, sm_count, stream);
+  if (!a_mn && b_mn) return dispatch_bn<false, true, OutT>(tmA, tmB, tmC, tmP, p, bn, sm_count, stream);
+  if (a_mn && b_mn) return dispatch_bn<true, true, OutT>(tmA, tmB, tmC, tmP, p, bn, sm_count, stream);
   return SB_ERR_BAD_ARG;
+}
+
+constexpr long WS_COUNTER_BYTES = 4096;  // 1024 tile counters at the head of the workspace
+
+// Tile width and k-splits for an [M, N, K] problem: the estimated time is (waves of work units) x (time of one
+// unit); a 128-wide tile moves 1.25x the operand bytes per flop of a 256-wide one, and each split adds the
+// traffic of its fp32 partial tile.
+void choose_shape(int M, int N, int K, int bn_hint, int split_hint, int sm_count, long ws_bytes, int* bn_out,
+                  int* splits_out) {
+  const int m_tiles = (M + BM - 1) / BM;
+  const int num_kb = (K + BK - 1) / BK;
+  double best = 1e30;
+  int best_bn = 128, best_s = 1;
+  for (int bn = 128; bn <= 256; bn += 128) {
+    if (bn_hint && bn != bn_hint) continue;
+    if (bn == 256 && N <= 128 && !bn_hint) continue;
+    const long tiles = (long)m_tiles * ((N + bn - 1) / bn);
+    for (int s = 1; s <= 16; ++s) {
+      if (split_hint > 0 && s != split_hint && !(s == 1 && split_hint > 1)) continue;
+      if (s > 1) {
+        if (tiles > 1024 || num_kb / s < (split_hint > 0 ? 1 : 8)) break;
+        const long need = WS_COUNTER_BYTES + tiles * s * (long)BM * bn * 4;
+        if (need > ws_bytes) break;
+      }
+      const long units = tiles * s;
+      const long waves = (units + sm_count - 1) / sm_count;
+      const double unit_time = (bn == 256 ? 2.0 : 1.25) * ((double)num_kb / s + (s > 1 ? 6.0 : 3.0));
+      const double t = waves * unit_time;
+      if (t < best * 0.97 || (split_hint > 1 && s == split_hint && best_s != split_hint)) {
+        best = t; best_bn = bn; best_s = s;
+      }
+    }
+  }
+  *bn_out = best_bn;
+  *splits_out = best_s;
+}
+
+// box = [32 rows, 64 columns] of a 16-bit row-major [rows, cols] matrix, 128-byte swizzle (epilogue stores)
+int make_tmap_out(CUtensorMap* tm, const void* base, long rows, long cols, long ld, int fp16) {
+  return make_tmap_2d(tm, base, rows, cols, ld, 32, fp16);
 }
 
 }  // namespace
@@ -351,26 +591,26 @@ int dispatch_major(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmPar
 //   a_mn = 0: A is [M, K] (lda >= K);  a_mn = 1: A is [K, M] (lda >= M)
 //   b_mn = 0: B is [N, K] (ldb >= K);  b_mn = 1: B is [K, N] (ldb >= N)
 //   in_dtype / out_dtype: SB_DT_* (inputs bf16 or fp16; output bf16, fp16 (fp16 in only) or fp32)
+//   bn_hint / split_hint: 0 = choose; otherwise the tile width (128 / 256) and the number of k-splits to use
+//   workspace: optional device scratch for split-K (first 4 KB: tile counters, zero before the first use and
+//              left zero by every launch; then fp32 partial tiles); without it no problem is split.  One
+//              workspace serves one stream at a time.
 //   status: device int, set to SB_ERR_WAIT_TIMEOUT if a bounded wait expired (may be null)
-SB_API int sb200_gemm(const void* A, const void* B, void* C, void* C_pre, const void* bias, int M, int N, int K,
-                      long lda, long ldb, long ldc, int a_mn, int b_mn, int act, int accumulate, int in_dtype,
-                      int out_dtype, int bn_hint, int sm_count, int* status, cudaStream_t stream) {
+SB_API int sb200_gemm_ws(const void* A, const void* B, void* C, void* C_pre, const void* bias, int M, int N, int K,
+                         long lda, long ldb, long ldc, int a_mn, int b_mn, int act, int accumulate, int in_dtype,
+                         int out_dtype, int bn_hint, int split_hint, int sm_count, void* workspace, long workspace_bytes,
+                         int* status, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return SB_OK;
   if (K <= 0) return SB_ERR_BAD_ARG;
   if (in_dtype != SB_DT_BF16 && in_dtype != SB_DT_F16) return SB_ERR_BAD_ARG;
   if ((lda % 8) || (ldb % 8)) return SB_ERR_BAD_ARG;  // TMA: strides are multiples of 16 bytes
   if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15)) return SB_ERR_BAD_ARG;
   const int fp16 = in_dtype == SB_DT_F16;
-  int bn = bn_hint == 128 || bn_hint == 256 ? bn_hint : (N > 128 ? 256 : 128);
-  // prefer the tile width that leaves fewer idle SMs in the last wave
-  if (bn_hint == 0 && N > 128) {
-    long t256 = (long)((M + BM - 1) / BM) * ((N + 255) / 256);
-    long t128 = (long)((M + BM - 1) / BM) * ((N + 127) / 128);
-    double w256 = (double)((t256 + sm_count - 1) / sm_count) * 2.0;  // relative time units
-    double w128 = (double)((t128 + sm_count - 1) / sm_count) * 1.08;
-    bn = w128 < w256 ? 128 : 256;
-  }
-  CUtensorMap tmA, tmB;
+  if (bn_hint != 128 && bn_hint != 256) bn_hint = 0;
+  int bn = 128, splits = 1;
+  const bool ws_ok = workspace && (reinterpret_cast<uintptr_t>(workspace) & 15) == 0;
+  choose_shape(M, N, K, bn_hint, split_hint, sm_count, ws_ok ? workspace_bytes : 0, &bn, &splits);
+  CUtensorMap tmA, tmB, tmC, tmP;
   int rc;
   if (a_mn) rc = make_tmap_2d(&tmA, A, K, M, lda, 64, fp16);
   else rc = make_tmap_2d(&tmA, A, M, K, lda, BM, fp16);
@@ -381,9 +621,30 @@ SB_API int sb200_gemm(const void* A, const void* B, void* C, void* C_pre, const 
   GemmParams p;
   p.C = C; p.C_pre = C_pre; p.bias = bias; p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.act = act;
   p.accumulate = accumulate; p.ab_fmt = fp16 ? 0 : 1; p.status = status;
-  if (out_dtype == SB_DT_F32) return dispatch_major<float>(tmA, tmB, p, a_mn, b_mn, bn, sm_count, stream);
+  p.splits = splits;
+  p.ws_counter = reinterpret_cast<int*>(workspace);
+  p.ws_partial = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(workspace) + WS_COUNTER_BYTES);
+  const bool out16 = out_dtype != SB_DT_F32;
+  p.tma_store = out16 && !accumulate && (ldc % 8 == 0) && (reinterpret_cast<uintptr_t>(C) & 15) == 0 &&
+                (!C_pre || (reinterpret_cast<uintptr_t>(C_pre) & 15) == 0);
+  tmC = tmA;
+  tmP = tmA;  // placeholders when the epilogue stores from registers
+  if (p.tma_store) {
+    if ((rc = make_tmap_out(&tmC, C, M, N, ldc, fp16))) return rc;
+    if (C_pre && (rc = make_tmap_out(&tmP, C_pre, M, N, ldc, fp16))) return rc;
+  }
+  if (out_dtype == SB_DT_F32) return dispatch_major<float>(tmA, tmB, tmC, tmP, p, a_mn, b_mn, bn, sm_count, stream);
   if (out_dtype == SB_DT_BF16 && !fp16)
-    return dispatch_major<__nv_bfloat16>(tmA, tmB, p, a_mn, b_mn, bn, sm_count, stream);
-  if (out_dtype == SB_DT_F16 && fp16) return dispatch_major<__half>(tmA, tmB, p, a_mn, b_mn, bn, sm_count, stream);
+    return dispatch_major<__nv_bfloat16>(tmA, tmB, tmC, tmP, p, a_mn, b_mn, bn, sm_count, stream);
+  if (out_dtype == SB_DT_F16 && fp16)
+    return dispatch_major<__half>(tmA, tmB, tmC, tmP, p, a_mn, b_mn, bn, sm_count, stream);
   return SB_ERR_BAD_ARG;
+}
+
+// Same without a split-K workspace.
+SB_API int sb200_gemm(const void* A, const void* B, void* C, void* C_pre, const void* bias, int M, int N, int K,
+                      long lda, long ldb, long ldc, int a_mn, int b_mn, int act, int accumulate, int in_dtype,
+                      int out_dtype, int bn_hint, int sm_count, int* status, cudaStream_t stream) {
+  return sb200_gemm_ws(A, B, C, C_pre, bias, M, N, K, lda, ldb, ldc, a_mn, b_mn, act, accumulate, in_dtype, out_dtype,
+                       bn_hint, 0, sm_count, nullptr, 0, status, stream);
 }

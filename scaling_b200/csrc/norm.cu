@@ -184,7 +184,7 @@ __global__ void __launch_bounds__(NORM_THREADS)
 // Backward with one warp per row (H <= 32 * V * NV): no block-wide synchronisation, row statistics by
 // warp shuffles, every warp keeps its share of dW / dB in registers and writes one partial row.
 template <typename T, bool RMS, int NV>
-__global__ void __launch_bounds__(NORM_THREADS)
+__global__ void __launch_bounds__(NORM_THREADS, 2)
     norm_bwd_warp_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __restrict__ w,
                          const float* __restrict__ mean_in, const float* __restrict__ rstd_in, T* __restrict__ dx,
                          float* __restrict__ dw_partial, float* __restrict__ db_partial, int M, int H) {
@@ -194,7 +194,7 @@ __global__ void __launch_bounds__(NORM_THREADS)
   const int gw = blockIdx.x * WARPS + warp;
   const int total_warps = gridDim.x * WARPS;
   float dw_acc[NV][V], db_acc[NV][V];
-  float wreg[NV][V];
+  sb::Vec16<T> wv[NV];  // packed: the row data of an iteration stays in its load format to save registers
 #pragma unroll
   for (int it = 0; it < NV; ++it) {
     const int c = (it * 32 + lane) * V;
@@ -202,13 +202,9 @@ __global__ void __launch_bounds__(NORM_THREADS)
     for (int i = 0; i < V; ++i) {
       dw_acc[it][i] = 0.f;
       db_acc[it][i] = 0.f;
-      wreg[it][i] = 0.f;
     }
-    if (c < H) {
-      auto wv = sb::ld16(w + c);
-#pragma unroll
-      for (int i = 0; i < V; ++i) wreg[it][i] = sb::to_f(wv.e[i]);
-    }
+    wv[it].u = make_uint4(0, 0, 0, 0);
+    if (c < H) wv[it] = sb::ld16(w + c);
   }
   const float inv_h = 1.f / H;
   for (int row = gw; row < M; row += total_warps) {
@@ -217,27 +213,32 @@ __global__ void __launch_bounds__(NORM_THREADS)
     T* dxr = dx + (size_t)row * H;
     const float mean = RMS ? 0.f : mean_in[row];
     const float rstd = rstd_in[row];
-    float xh[NV][V], g[NV][V];
+    sb::Vec16<T> xv[NV], dv[NV];
+#pragma unroll
+    for (int it = 0; it < NV; ++it) {
+      const int c = (it * 32 + lane) * V;
+      xv[it].u = make_uint4(0, 0, 0, 0);
+      dv[it].u = make_uint4(0, 0, 0, 0);
+      if (c < H) {
+        xv[it] = sb::ld16(xr + c);
+        dv[it] = sb::ld16(dyr + c);
+      }
+    }
     float sum_g = 0.f, sum_gx = 0.f;
 #pragma unroll
     for (int it = 0; it < NV; ++it) {
       const int c = (it * 32 + lane) * V;
       if (c < H) {
-        auto xv = sb::ld16(xr + c);
-        auto dv = sb::ld16(dyr + c);
 #pragma unroll
         for (int i = 0; i < V; ++i) {
-          const float d = sb::to_f(dv.e[i]);
-          xh[it][i] = (sb::to_f(xv.e[i]) - mean) * rstd;
-          g[it][i] = d * wreg[it][i];
-          sum_g += g[it][i];
-          sum_gx += g[it][i] * xh[it][i];
-          dw_acc[it][i] += d * xh[it][i];
+          const float d = sb::to_f(dv[it].e[i]);
+          const float xh = (sb::to_f(xv[it].e[i]) - mean) * rstd;
+          const float g = d * sb::to_f(wv[it].e[i]);
+          sum_g += g;
+          sum_gx += g * xh;
+          dw_acc[it][i] += d * xh;
           if (!RMS) db_acc[it][i] += d;
         }
-      } else {
-#pragma unroll
-        for (int i = 0; i < V; ++i) { xh[it][i] = 0.f; g[it][i] = 0.f; }
       }
     }
     sum_gx = sb::warp_sum(sum_gx) * inv_h;
@@ -248,21 +249,37 @@ __global__ void __launch_bounds__(NORM_THREADS)
       if (c < H) {
         sb::Vec16<T> o;
 #pragma unroll
-        for (int i = 0; i < V; ++i) o.e[i] = sb::from_f<T>(rstd * (g[it][i] - sum_g - xh[it][i] * sum_gx));
+        for (int i = 0; i < V; ++i) {
+          const float xh = (sb::to_f(xv[it].e[i]) - mean) * rstd;
+          const float g = sb::to_f(dv[it].e[i]) * sb::to_f(wv[it].e[i]);
+          o.e[i] = sb::from_f<T>(rstd * (g - sum_g - xh * sum_gx));
+        }
         sb::st16(dxr + c, o);
       }
     }
   }
-  float* dwp = dw_partial + (size_t)gw * H;
-  float* dbp = db_partial ? db_partial + (size_t)gw * H : nullptr;
+  // one partial row per CTA: the 8 warps' accumulators are summed in a fixed order through shared memory,
+  // one chunk of 32*V columns at a time
+  __shared__ float red[WARPS][32 * V];
+  float* dwp = dw_partial + (size_t)blockIdx.x * H;
+  float* dbp = db_partial ? db_partial + (size_t)blockIdx.x * H : nullptr;
 #pragma unroll
   for (int it = 0; it < NV; ++it) {
-    const int c = (it * 32 + lane) * V;
-    if (c < H) {
+    const int c0 = it * 32 * V;
 #pragma unroll
-      for (int i = 0; i < V; ++i) {
-        dwp[c + i] = dw_acc[it][i];
-        if (!RMS && dbp) dbp[c + i] = db_acc[it][i];
+    for (int pass = 0; pass < (RMS ? 1 : 2); ++pass) {
+      if (pass == 1 && !dbp) break;
+      __syncthreads();
+#pragma unroll
+      for (int i = 0; i < V; ++i) red[warp][lane * V + i] = pass == 0 ? dw_acc[it][i] : db_acc[it][i];
+      __syncthreads();
+      for (int t = threadIdx.x; t < 32 * V; t += NORM_THREADS) {
+        if (c0 + t < H) {
+          float s = 0.f;
+#pragma unroll
+          for (int wi = 0; wi < WARPS; ++wi) s += red[wi][t];
+          (pass == 0 ? dwp : dbp)[c0 + t] = s;
+        }
       }
     }
   }
@@ -278,6 +295,40 @@ __global__ void reduce_partials_kernel(const float* __restrict__ partial, T* __r
   for (int p = 0; p < P; ++p) s += partial[(size_t)p * H + c];
   if (accumulate) s += sb::to_f(out[c]);
   out[c] = sb::from_f<T>(s);
+}
+
+// Same result layout, parallel over the partial rows: a CTA owns 32 columns, warp w sums rows w, w+32, ...
+// and the 32 warp sums are added in a fixed order.  blockIdx.y selects (partial0, out0) or (partial1, out1).
+template <typename T>
+__global__ void __launch_bounds__(1024)
+    reduce_partials_wide_kernel(const float* __restrict__ partial0, T* __restrict__ out0,
+                                const float* __restrict__ partial1, T* __restrict__ out1, int P, int H,
+                                int accumulate) {
+  __shared__ float red[32][33];
+  const float* partial = blockIdx.y == 0 ? partial0 : partial1;
+  T* out = blockIdx.y == 0 ? out0 : out1;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int c = blockIdx.x * 32 + lane;
+  float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+  if (c < H) {
+    int p = warp;
+    for (; p + 96 < P; p += 128) {
+      s0 += partial[(size_t)p * H + c];
+      s1 += partial[(size_t)(p + 32) * H + c];
+      s2 += partial[(size_t)(p + 64) * H + c];
+      s3 += partial[(size_t)(p + 96) * H + c];
+    }
+    for (; p < P; p += 32) s0 += partial[(size_t)p * H + c];
+  }
+  red[warp][lane] = (s0 + s1) + (s2 + s3);
+  __syncthreads();
+  if (warp == 0 && c < H) {
+    float s = 0.f;
+#pragma unroll
+    for (int w = 0; w < 32; ++w) s += red[w][lane];
+    if (accumulate) s += sb::to_f(out[c]);
+    out[c] = sb::from_f<T>(s);
+  }
 }
 
 }  // namespace
@@ -306,15 +357,15 @@ SB_API int sb200_norm_bwd_partial_rows(int M, int sm_count) {
   return p;
 }
 
-// Partial rows for a problem of M rows of width H: rows narrow enough for the warp-per-row kernel get one
-// partial row per warp (a multiple of 8), wider rows one per CTA.
+// Partial rows (one per CTA) for a problem of M rows of width H: the warp-per-row kernel used for narrow rows
+// keeps 8 rows in flight per CTA and is launched with more CTAs than the block-per-row kernel.
 SB_API int sb200_norm_bwd_partial_rows_h(int M, int H, int elem_size, int sm_count) {
   const int V = 16 / (elem_size > 0 ? elem_size : 2);
-  if (H % V == 0 && H <= 32 * V * 8) {
-    int ctas = (M + 7) / 8;
-    if (ctas > sm_count * 4) ctas = sm_count * 4;
+  if (H % V == 0 && H <= 32 * V * 4) {
+    int ctas = (M + 15) / 16;
+    if (ctas > sm_count * 2) ctas = sm_count * 2;
     if (ctas < 1) ctas = 1;
-    return ctas * 8;
+    return ctas;
   }
   return sb200_norm_bwd_partial_rows(M, sm_count);
 }
@@ -324,7 +375,7 @@ namespace {
 template <typename T, bool RMS, int NV>
 void launch_norm_bwd_warp(const void* dy, const void* x, const void* w, const float* mean, const float* rstd, void* dx,
                           float* dw_partial, float* db_partial, int M, int H, int partial_rows, cudaStream_t stream) {
-  norm_bwd_warp_kernel<T, RMS, NV><<<partial_rows / 8, NORM_THREADS, 0, stream>>>(
+  norm_bwd_warp_kernel<T, RMS, NV><<<partial_rows, NORM_THREADS, 0, stream>>>(
       (const T*)dy, (const T*)x, (const T*)w, RMS ? nullptr : mean, rstd, (T*)dx, dw_partial,
       RMS ? nullptr : db_partial, M, H);
 }
@@ -335,7 +386,7 @@ int norm_bwd_dispatch(const void* dy, const void* x, const void* w, const float*
                       int partial_rows, cudaStream_t stream) {
   constexpr int V = sb::Vec16<T>::N;
   if (H % V != 0 || H > NORM_THREADS * V * NORM_MAX_ITERS) return SB_ERR_BAD_ARG;
-  const bool warp_rows = H <= 32 * V * 8 && partial_rows >= 8 && partial_rows % 8 == 0;
+  const bool warp_rows = H <= 32 * V * 4;
   const int nv = (H + 32 * V - 1) / (32 * V);
   if (warp_rows && nv <= 1)
     launch_norm_bwd_warp<T, RMS, 1>(dy, x, w, mean, rstd, dx, dw_partial, db_partial, M, H, partial_rows, stream);
@@ -345,17 +396,14 @@ int norm_bwd_dispatch(const void* dy, const void* x, const void* w, const float*
     launch_norm_bwd_warp<T, RMS, 3>(dy, x, w, mean, rstd, dx, dw_partial, db_partial, M, H, partial_rows, stream);
   else if (warp_rows && nv <= 4)
     launch_norm_bwd_warp<T, RMS, 4>(dy, x, w, mean, rstd, dx, dw_partial, db_partial, M, H, partial_rows, stream);
-  else if (warp_rows && nv <= 8)
-    launch_norm_bwd_warp<T, RMS, 8>(dy, x, w, mean, rstd, dx, dw_partial, db_partial, M, H, partial_rows, stream);
   else
     norm_bwd_kernel<T, RMS><<<partial_rows, NORM_THREADS, 0, stream>>>(
         (const T*)dy, (const T*)x, (const T*)w, RMS ? nullptr : mean, rstd, (T*)dx, dw_partial,
         RMS ? nullptr : db_partial, M, H);
   SB_CHECK_LAUNCH();
-  int blocks = (H + 255) / 256;
-  reduce_partials_kernel<T><<<blocks, 256, 0, stream>>>(dw_partial, (T*)dw, partial_rows, H, accumulate);
-  if (!RMS && db && db_partial)
-    reduce_partials_kernel<T><<<blocks, 256, 0, stream>>>(db_partial, (T*)db, partial_rows, H, accumulate);
+  const bool want_db = !RMS && db && db_partial;
+  reduce_partials_wide_kernel<T><<<dim3((H + 31) / 32, want_db ? 2 : 1), 1024, 0, stream>>>(
+      dw_partial, (T*)dw, db_partial, (T*)db, partial_rows, H, accumulate);
   SB_CHECK_LAUNCH();
   return SB_OK;
 }

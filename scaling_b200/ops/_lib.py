@@ -66,6 +66,8 @@ _SIGS = {
     "sb200_rope": [c_void_p, c_void_p, c_int, c_int, c_int, c_long, c_long, c_float, c_int, c_int, c_int, c_void_p],
     "sb200_masked_softmax_fwd": [c_void_p, c_void_p, c_void_p, c_long, c_int, c_int, c_int, c_float, c_int, c_void_p],
     "sb200_masked_softmax_bwd": [c_void_p, c_void_p, c_void_p, c_void_p, c_long, c_int, c_int, c_int, c_float, c_int, c_void_p],
+    "sb200_colsum_splits": [c_long, c_int, c_int, c_int],
+    "sb200_colsum": [c_void_p, c_void_p, c_void_p, c_long, c_int, c_long, c_int, c_int, c_int, c_void_p],
     "sb200_transpose": [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     "sb200_ce_stats": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_long, c_int, c_long, c_long, c_int, c_void_p],
     "sb200_ce_finalize": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_long, c_int, c_long, c_long, c_long, c_int, c_void_p],
@@ -75,6 +77,7 @@ _SIGS = {
     "sb200_sumsq": [c_void_p, c_long, c_void_p, c_void_p, c_void_p, c_float, c_int, c_int, c_void_p],
     "sb200_embedding_fwd": [c_void_p, c_void_p, c_void_p, c_long, c_int, c_long, c_long, c_int, c_void_p],
     "sb200_embedding_bwd": [c_void_p, c_void_p, c_void_p, c_void_p, c_long, c_int, c_long, c_long, c_int, c_int, c_void_p],
+    "sb200_gemm_ws": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_long, c_long, c_long, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_long, c_void_p, c_void_p],
     "sb200_gemm": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_long, c_long, c_long, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
 }
 
@@ -120,7 +123,7 @@ class _Counting:
         return hasattr(self._handle, name)
 
 
-_NO_LAUNCH = {"sb200_norm_bwd_partial_rows", "sb200_norm_bwd_partial_rows_h", "sb200_sumsq_max_partials",
+_NO_LAUNCH = {"sb200_colsum_splits", "sb200_norm_bwd_partial_rows", "sb200_norm_bwd_partial_rows_h", "sb200_sumsq_max_partials",
               "sb200_bind_device", "sb200_fa_last_driver_error"}
 
 

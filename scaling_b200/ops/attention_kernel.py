@@ -23,6 +23,10 @@ def _declare() -> None:
     _lib.declare("sb200_fa_bwd_splits", [c_int] * 4)
     _lib.declare("sb200_fa_bwd", [c_void_p] * 8 + [c_int] + [c_void_p] * 5 + [c_int] * 4 + [c_long, c_int, c_long, c_int, c_long, c_int, c_int,
                                                                   c_int, c_float, c_void_p, c_void_p])
+    _lib.declare("sb200_fa_bwd_strided", [c_void_p] * 8 + [c_int] + [c_void_p] * 5 + [c_int] * 4
+                 + [c_long, c_int] * 6 + [c_int, c_int, c_float, c_void_p, c_void_p])
+    _lib.declare("sb200_rope_multi", [c_void_p, c_void_p, c_int, c_int, c_int, c_long, c_long, c_int, c_long, c_float,
+                                      c_int, c_int, c_int, c_void_p])
     _DECLARED = True
 
 
@@ -109,3 +113,92 @@ def flash_attention_kernel(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu
         return out.to(q.dtype)
     start, end = ranges if ranges is not None else doc_ranges(cu_seqlens, q.shape[0])
     return _FlashAttention.apply(q, k, v, start, end, causal, scale, window)
+
+
+class _PackedQKVAttention(torch.autograd.Function):
+    """Self-attention on a packed projection ``qkv[T, heads, 3 * d]`` (per head ``[q | k | v]``).
+
+    The rotary embedding is applied in place on the q and k parts, the attention kernels read q, k and v as strided
+    views, and the backward pass writes dq, dk and dv straight into one ``[T, heads, 3 * d]`` gradient (followed by
+    the inverse rotation in place) - no slicing, concatenation or copies on either pass.  ``qkv`` is consumed: its
+    contents are the rotated projection afterwards.
+    """
+
+    @staticmethod
+    def forward(ctx, qkv, pos, rot, doc_start, doc_end, causal, scale, window):  # type: ignore[override]
+        _declare()
+        T, H, D3 = qkv.shape
+        D = D3 // 3
+        assert qkv.is_contiguous() and qkv.dtype == torch.bfloat16
+        if rot is not None:
+            rot_dim, base, interleaved = rot
+            check(lib().sb200_rope_multi(qkv.data_ptr(), pos.data_ptr(), T, H, rot_dim, H * D3, D3, 2, D, float(base),
+                                         int(interleaved), 0, _lib.dt(qkv.dtype), stream()), "sb200_rope_multi")
+        q, k, v = qkv[..., :D], qkv[..., D:2 * D], qkv[..., 2 * D:]
+        o = torch.empty((T, H, D), dtype=qkv.dtype, device=qkv.device)
+        lse2 = torch.empty((H, T), dtype=torch.float32, device=qkv.device)
+        check(
+            lib().sb200_fa_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse2.data_ptr(),
+                               doc_start.data_ptr(), doc_end.data_ptr(), T, H, H, D, H * D3, D3, H * D3, D3, H * D3, D3,
+                               int(causal), -1 if window is None else int(window), float(scale),
+                               status_word().data_ptr(), stream()),
+            "sb200_fa_fwd",
+        )
+        ctx.save_for_backward(qkv, o, lse2, doc_start, doc_end, pos if rot is not None else None)
+        ctx.cfg = (causal, scale, window, rot)
+        return o
+
+    @staticmethod
+    def backward(ctx, do):  # type: ignore[override]
+        qkv, o, lse2, doc_start, doc_end, pos = ctx.saved_tensors
+        causal, scale, window, rot = ctx.cfg
+        T, H, D3 = qkv.shape
+        D = D3 // 3
+        do = do.contiguous()
+        q, k, v = qkv[..., :D], qkv[..., D:2 * D], qkv[..., 2 * D:]
+        dqkv = torch.empty_like(qkv)
+        dq, dk, dv = dqkv[..., :D], dqkv[..., D:2 * D], dqkv[..., 2 * D:]
+        delta = torch.empty((H, T), dtype=torch.float32, device=qkv.device)
+        splits = lib()._handle.sb200_fa_bwd_splits(T, H, H, _lib.sm_count())
+        partial = None
+        if splits > 1:
+            partial = torch.empty((2, splits, T, H, D), dtype=torch.float32, device=qkv.device)
+        ld = (H * D3, D3)
+        check(
+            lib().sb200_fa_bwd_strided(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), do.data_ptr(),
+                                       lse2.data_ptr(), delta.data_ptr(), _lib.ptr(partial), splits, dq.data_ptr(),
+                                       dk.data_ptr(), dv.data_ptr(), doc_start.data_ptr(), doc_end.data_ptr(), T, H, H,
+                                       D, *ld, *ld, *ld, *ld, *ld, *ld, int(causal),
+                                       -1 if window is None else int(window), float(scale),
+                                       status_word().data_ptr(), stream()),
+            "sb200_fa_bwd_strided",
+        )
+        if rot is not None:
+            rot_dim, base, interleaved = rot
+            check(lib().sb200_rope_multi(dqkv.data_ptr(), pos.data_ptr(), T, H, rot_dim, H * D3, D3, 2, D, float(base),
+                                         int(interleaved), 1, _lib.dt(dqkv.dtype), stream()), "sb200_rope_multi")
+        return dqkv, None, None, None, None, None, None, None
+
+
+def packed_qkv_supported(qkv: torch.Tensor) -> bool:
+    """True when ``packed_qkv_attention`` can run on ``qkv[T, heads, 3 * d]``."""
+    return (qkv.is_cuda and qkv.dtype == torch.bfloat16 and qkv.dim() == 3 and qkv.shape[-1] % 3 == 0
+            and qkv.shape[-1] // 3 in (64, 128) and qkv.is_contiguous() and _lib.lib_has("sb200_fa_bwd_strided"))
+
+
+def packed_qkv_attention(qkv: torch.Tensor, positions: Optional[torch.Tensor],
+                         rotary: Optional[tuple[int, float, bool]], cu_seqlens: Optional[torch.Tensor], causal: bool,
+                         scale: float, window: Optional[int],
+                         ranges: Optional[tuple[torch.Tensor, torch.Tensor]] = None) -> torch.Tensor:
+    """Rotary embedding + self-attention on a packed projection; returns ``[T, heads, d]``.
+
+    ``rotary = (rotary dimensions, base, interleaved)`` or None; ``positions`` is ``[T]``.  ``qkv`` is overwritten
+    with the rotated projection.
+    """
+    start, end = ranges if ranges is not None else doc_ranges(cu_seqlens, qkv.shape[0])
+    pos = None
+    if rotary is not None:
+        assert positions is not None
+        pos = positions if positions.dtype == torch.int32 else positions.to(torch.int32)
+        pos = pos.contiguous()
+    return _PackedQKVAttention.apply(qkv, pos, rotary, start, end, causal, scale, window)

@@ -45,6 +45,8 @@ def check_status() -> None:
         v = int(_STATUS[d].item())
         if v != 0:
             _STATUS[d].zero_()
+            if d in _GEMM_WS:
+                _GEMM_WS[d][:4096].zero_()  # an aborted split-K launch may have left tile counters behind
             check(v, "device status word")
 
 
@@ -77,6 +79,7 @@ def gemm(
     out_dtype: Optional[torch.dtype] = None,
     pre_act_out: Optional[torch.Tensor] = None,
     bn: int = 0,
+    split: int = 0,
 ) -> torch.Tensor:
     """``C = op(a) @ op(b)^T``-style GEMM on tcgen05.
 
@@ -119,13 +122,31 @@ def gemm(
     if out is None:
         out = torch.empty((M, N), dtype=odt, device=a.device)
         assert not accumulate
-    rc = lib().sb200_gemm(
+    ws = _gemm_workspace(a.device)
+    rc = lib().sb200_gemm_ws(
         a.data_ptr(), b.data_ptr(), out.data_ptr(), ptr(pre_act_out), ptr(bias), M, N, K,
         a.stride(0), b.stride(0), out.stride(0), int(a_mn), int(b_mn), 1 if act == "gelu" else 0,
-        int(accumulate), dt(a.dtype), dt(out.dtype), bn, sm_count(), status_word().data_ptr(), stream(),
+        int(accumulate), dt(a.dtype), dt(out.dtype), bn, split, sm_count(), ws.data_ptr(), ws.numel(),
+        status_word().data_ptr(), stream(),
     )
-    check(rc, "sb200_gemm")
+    check(rc, "sb200_gemm_ws")
     return out
+
+
+_GEMM_WS: dict[int, torch.Tensor] = {}
+_GEMM_WS_BYTES = 64 * 1024 * 1024
+
+
+def _gemm_workspace(device: torch.device) -> torch.Tensor:
+    """Split-K scratch of the GEMM (tile counters + fp32 partial tiles), one per device.  GEMMs that may run
+    concurrently (issued on different streams without ordering between them) must not share it; the framework
+    issues all its GEMMs on the current compute stream.  The kernel leaves the counters zero."""
+    key = device.index if device.index is not None else torch.cuda.current_device()
+    ws = _GEMM_WS.get(key)
+    if ws is None:
+        ws = torch.zeros(_GEMM_WS_BYTES, dtype=torch.uint8, device=device)
+        _GEMM_WS[key] = ws
+    return ws
 
 
 def _gemm_shape_exempt(a: torch.Tensor, b: torch.Tensor) -> bool:
@@ -156,6 +177,7 @@ class _LinearFn(torch.autograd.Function):
             pre = torch.empty((x2.shape[0], w.shape[0]), dtype=x.dtype, device=x.device)
         y = gemm(x2, w, bias=bias, act=act, pre_act_out=pre)
         ctx.save_for_backward(x2, w, pre)
+        ctx.weight, ctx.bias = w, bias  # the parameter objects themselves (for their persistent .grad buffers)
         ctx.has_bias = bias is not None
         ctx.act = act
         ctx.wgrad = wgrad
@@ -174,10 +196,53 @@ class _LinearFn(torch.autograd.Function):
         if ctx.needs_input_grad[0]:
             dx = gemm(dy2, w, b_mn=True).view(ctx.x_shape)
         if ctx.needs_input_grad[1] and ctx.wgrad:
-            dw = gemm(dy2, x2, a_mn=True, b_mn=True)
+            main = fused_grad_target(ctx.weight)
+            if main is not None and main.dtype in (torch.float32, dy2.dtype):
+                gemm(dy2, x2, a_mn=True, b_mn=True, out=main, accumulate=True)
+            else:
+                dw = gemm(dy2, x2, a_mn=True, b_mn=True)
         if ctx.has_bias and ctx.needs_input_grad[2]:
-            db = dy2.sum(0)
+            main = fused_grad_target(ctx.bias)
+            if main is not None and main.dtype == dy2.dtype:
+                column_sum(dy2, out=main, accumulate=True)
+            else:
+                db = column_sum(dy2)
         return dx, dw, db, None, None
+
+
+def fused_grad_target(p: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
+    """The persistent gradient buffer of a parameter that opted into in-kernel gradient accumulation.
+
+    An optimizer that keeps ``param.grad`` as a permanent, zero-initialised view of a flat buffer sets
+    ``param.fused_grad_accumulation = True``; backward kernels then add into ``param.grad`` from their epilogue and
+    return no gradient for the parameter, which saves the separate accumulation pass per parameter.
+    """
+    if p is None or not getattr(p, "fused_grad_accumulation", False):
+        return None
+    g = p.grad
+    if g is None or not g.is_contiguous() or g.shape != p.shape or not g.is_cuda:
+        return None
+    return g
+
+
+def column_sum(x: torch.Tensor, out: Optional[torch.Tensor] = None, accumulate: bool = False) -> torch.Tensor:
+    """Deterministic ``x[M, N].sum(0)`` (bias gradients); optionally added into ``out``."""
+    M, N = x.shape
+    if not (x.is_cuda and x.dtype in _KERNEL_DTYPES and x.stride(1) == 1 and N % (16 // x.element_size()) == 0
+            and x.stride(0) % (16 // x.element_size()) == 0 and M > 0):
+        r = x.sum(0)
+        if out is None:
+            return r
+        return out.add_(r.to(out.dtype)) if accumulate else out.copy_(r)
+    if out is None:
+        out = torch.empty(N, dtype=x.dtype, device=x.device)
+        accumulate = False
+    assert out.dtype == x.dtype and out.is_contiguous()
+    splits = lib().sb200_colsum_splits(M, N, x.element_size(), sm_count())
+    partial = torch.empty((splits, N), dtype=torch.float32, device=x.device)
+    check(lib().sb200_colsum(x.data_ptr(), out.data_ptr(), partial.data_ptr(), M, N, x.stride(0), splits,
+                             int(accumulate), dt(x.dtype), stream()), "sb200_colsum")
+    return out
 
 
 def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None, act: str = "none") -> torch.Tensor:
@@ -216,6 +281,7 @@ class _NormFn(torch.autograd.Function):
             "sb200_norm_fwd",
         )
         ctx.save_for_backward(x2, wc, mean, rstd)
+        ctx.weight, ctx.bias = w, b
         ctx.rms = rms
         ctx.has_bias = b is not None
         ctx.w_dtype = w.dtype
@@ -232,14 +298,24 @@ class _NormFn(torch.autograd.Function):
         rows = lib().sb200_norm_bwd_partial_rows_h(M, H, x2.element_size(), sm_count())
         dwp = torch.empty((rows, H), dtype=torch.float32, device=x2.device)
         dbp = torch.empty((rows, H), dtype=torch.float32, device=x2.device) if ctx.has_bias else None
-        dw = torch.empty(H, dtype=x2.dtype, device=x2.device)
-        db = torch.empty(H, dtype=x2.dtype, device=x2.device) if ctx.has_bias else None
+        # parameters with a persistent gradient buffer of the compute dtype get their gradients added in place
+        main_w = fused_grad_target(ctx.weight)
+        main_b = fused_grad_target(ctx.bias) if ctx.has_bias else None
+        fused = (main_w is not None and main_w.dtype == x2.dtype
+                 and (not ctx.has_bias or (main_b is not None and main_b.dtype == x2.dtype)))
+        if fused:
+            dw, db = main_w, main_b
+        else:
+            dw = torch.empty(H, dtype=x2.dtype, device=x2.device)
+            db = torch.empty(H, dtype=x2.dtype, device=x2.device) if ctx.has_bias else None
         check(
             lib().sb200_norm_bwd(dy2.data_ptr(), x2.data_ptr(), w.data_ptr(), ptr(mean), rstd.data_ptr(),
                                  dx.data_ptr(), dwp.data_ptr(), ptr(dbp), dw.data_ptr(), ptr(db), M, H,
-                                 int(ctx.rms), 0, rows, dt(x2.dtype), stream()),
+                                 int(ctx.rms), int(fused), rows, dt(x2.dtype), stream()),
             "sb200_norm_bwd",
         )
+        if fused:
+            return dx.view(dy.shape), None, None, None, None
         return dx.view(dy.shape), dw.to(ctx.w_dtype), (db.to(ctx.w_dtype) if db is not None else None), None, None
 
 

@@ -192,7 +192,9 @@ def test_adamw_and_sumsq(gdtype):
 
 
 GEMM_SHAPES = [(128, 256, 64), (256, 512, 128), (300, 264, 200), (2048, 2304, 768), (1000, 768, 3072), (64, 32, 1024),
-               (4096, 136, 72)]
+               (4096, 136, 72),
+               # few output tiles with a long reduction: these take the split-K path
+               (256, 384, 8192), (640, 768, 4096), (136, 200, 2048)]
 
 
 @pytest.mark.parametrize("M,N,K_", GEMM_SHAPES)
@@ -239,6 +241,34 @@ def test_gemm_epilogues():
     K.check_status()
 
 
+def test_gemm_split_k_epilogues_and_determinism():
+    """Long-K problems with few tiles are split; bias, accumulation and fp32 / fp16 outputs go through the same
+    finishing code, and the result is bitwise reproducible."""
+    torch.manual_seed(18)
+    M, N, K_ = 384, 768, 8192
+    a = torch.randn(K_, M, device=DEV, dtype=torch.bfloat16)
+    b = torch.randn(K_, N, device=DEV, dtype=torch.bfloat16)
+    ref = a.float().t() @ b.float()
+    base = torch.randn(M, N, device=DEV, dtype=torch.bfloat16)
+    out = base.clone()
+    K.gemm(a, b, a_mn=True, b_mn=True, out=out, accumulate=True)
+    assert _rel(out, ref + base.float()) < 1e-2
+    out2 = base.clone()
+    K.gemm(a, b, a_mn=True, b_mn=True, out=out2, accumulate=True)
+    assert torch.equal(out, out2)
+    c32 = K.gemm(a, b, a_mn=True, b_mn=True, out_dtype=torch.float32)
+    assert _rel(c32, ref) < 1e-2
+    x = torch.randn(M, K_, device=DEV, dtype=torch.float16) * 0.1
+    w = torch.randn(N, K_, device=DEV, dtype=torch.float16) * 0.1
+    bias = torch.randn(N, device=DEV, dtype=torch.float16)
+    pre = torch.empty(M, N, device=DEV, dtype=torch.float16)
+    y = K.gemm(x, w, bias=bias, act="gelu", pre_act_out=pre)
+    ref_pre = x.float() @ w.float().t() + bias.float()
+    assert _rel(pre, ref_pre) < 1e-2
+    assert _rel(y, F.gelu(ref_pre)) < 1e-2
+    K.check_status()
+
+
 def test_linear_autograd():
     torch.manual_seed(9)
     x = torch.randn(4, 100, 768, device=DEV, dtype=torch.bfloat16, requires_grad=True)
@@ -255,6 +285,50 @@ def test_linear_autograd():
     assert _rel(x.grad, xr.grad) < 2e-2
     assert _rel(w.grad, wr.grad) < 2e-2
     assert _rel(b.grad, br.grad) < 2e-2
+
+
+@pytest.mark.parametrize("M,N", [(16384, 768), (1000, 3072), (77, 40), (5, 8)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_column_sum(M, N, dtype):
+    torch.manual_seed(5)
+    x = torch.randn(M, N, device=DEV, dtype=dtype)
+    ref = x.double().sum(0)
+    out = K.column_sum(x)
+    assert _rel(out, ref) < (1e-2 if dtype == torch.bfloat16 else 1e-5)
+    base = torch.randn(N, device=DEV, dtype=dtype)
+    acc = base.clone()
+    K.column_sum(x, out=acc, accumulate=True)
+    assert _rel(acc, ref + base.double()) < (1e-2 if dtype == torch.bfloat16 else 1e-5)
+    assert torch.equal(K.column_sum(x), out)  # deterministic
+
+
+def test_fused_gradient_accumulation_matches_autograd():
+    """Parameters flagged for in-kernel accumulation receive the same gradients as through autograd."""
+    torch.manual_seed(6)
+    M, Kd, N = 512, 256, 384
+    x = torch.randn(M, Kd, device=DEV, dtype=torch.bfloat16)
+    dy = torch.randn(M, N, device=DEV, dtype=torch.bfloat16)
+    w0 = torch.randn(N, Kd, device=DEV, dtype=torch.bfloat16) * 0.05
+    b0 = torch.randn(N, device=DEV, dtype=torch.bfloat16)
+    results = []
+    for fused in (False, True):
+        w = torch.nn.Parameter(w0.clone())
+        b = torch.nn.Parameter(b0.clone())
+        g = torch.nn.Parameter(torch.ones(N, device=DEV, dtype=torch.bfloat16))
+        gb = torch.nn.Parameter(torch.zeros(N, device=DEV, dtype=torch.bfloat16))
+        params = (w, b, g, gb)
+        for p in params:
+            p.grad = torch.zeros_like(p)
+            if fused:
+                p.fused_grad_accumulation = True
+        for _ in range(2):  # two micro batches accumulate
+            xin = x.clone().requires_grad_()
+            y = K.layer_norm(K.linear(xin, w, b, act="gelu"), g, gb, 1e-5)
+            y.backward(dy)
+        K.check_status()
+        results.append([p.grad.clone() for p in params] + [xin.grad.clone()])
+    for a, b_ in zip(*results):
+        assert _rel(a, b_) < 1e-2, _rel(a, b_)
 
 
 FA_CASES = [
@@ -294,6 +368,47 @@ def test_flash_attention(T, Hq, Hkv, D, cu, causal, window):
     q2, k2, v2 = (t.detach().clone().requires_grad_() for t in (q, k, v))
     flash_attention(q2, k2, v2, cu_t, None, causal=causal, scale=scale, window=window).backward(do)
     assert torch.equal(q.grad, q2.grad) and torch.equal(k.grad, k2.grad) and torch.equal(v.grad, v2.grad)
+
+
+@pytest.mark.parametrize("T,H,D,cu,window,rot,interleaved", [
+    (384, 4, 64, [0, 100, 384], None, 64, False),
+    (300, 2, 128, [0, 300], None, 64, True),
+    (4352, 12, 64, [0, 2048, 4352], None, 64, False),   # enough heads x tiles to take the split dK/dV path
+    (512, 3, 64, [0, 512], 100, None, False),
+])
+def test_packed_qkv_attention(T, H, D, cu, window, rot, interleaved):
+    """Fused rotary + attention on a packed [T, H, 3D] projection against rope + attention on separate tensors."""
+    from scaling_b200.ops.attention import attention_reference
+    from scaling_b200.ops.attention_kernel import packed_qkv_attention, packed_qkv_supported
+
+    torch.manual_seed(12)
+    src = torch.randn(T, H, 3 * D, device=DEV, dtype=torch.bfloat16)
+    cu_t = torch.tensor(cu, device=DEV, dtype=torch.int32)
+    pos = torch.cat([torch.arange(b - a, device=DEV, dtype=torch.int32) for a, b in zip(cu[:-1], cu[1:])])
+    scale = D ** -0.5
+    rotary = None if rot is None else (rot, 10000.0, interleaved)
+
+    x = src.clone().requires_grad_()
+    qkv = x * 1.0  # the fused op consumes its input, as it does the projection's output inside the model
+    assert packed_qkv_supported(qkv)
+    out = packed_qkv_attention(qkv, pos, rotary, cu_t, True, scale, window)
+    do = torch.randn_like(out)
+    out.backward(do)
+    K.check_status()
+
+    xr = src.detach().float().requires_grad_()
+    q, k, v = xr[..., :D], xr[..., D:2 * D], xr[..., 2 * D:]
+    if rotary is not None:
+        q = K.rope_reference(q, pos, rot, 10000.0, interleaved)
+        k = K.rope_reference(k, pos, rot, 10000.0, interleaved)
+    ref = attention_reference(q, k, v, cu_t, None, True, scale, window)
+    ref.backward(do.float())
+    assert _rel(out, ref) < 2e-2, _rel(out, ref)
+    for sl in (slice(0, D), slice(D, 2 * D), slice(2 * D, 3 * D)):
+        assert _rel(x.grad[..., sl], xr.grad[..., sl]) < 3e-2, _rel(x.grad[..., sl], xr.grad[..., sl])
+    x2 = src.clone().requires_grad_()
+    packed_qkv_attention(x2 * 1.0, pos, rotary, cu_t, True, scale, window).backward(do)
+    assert torch.equal(x.grad, x2.grad)
 
 
 def test_flash_attention_strided_qkv():
