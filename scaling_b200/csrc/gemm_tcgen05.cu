@@ -52,16 +52,21 @@ struct GemmParams {
   int* status;
 };
 
-template <int BN> struct GemmCfg {
-  static constexpr int STAGES = BN == 256 ? 4 : 6;
+// PAIR: two CTAs of a cluster compute one 256 x BN tile with cta_group::2 MMAs; each CTA loads its own 128 rows of A
+// and half of the B rows, which halves the operand bytes every SM pulls from L2 per flop.
+template <int BN, bool PAIR> struct GemmCfg {
+  static constexpr int CTAS = PAIR ? 2 : 1;
+  static constexpr int LOAD_BN = BN / CTAS;  // B rows (output columns) this CTA loads per stage
   static constexpr int A_BYTES = BM * BK * 2;
-  static constexpr int B_BYTES = BN * BK * 2;
+  static constexpr int B_BYTES = LOAD_BN * BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int STAGES = STAGE_BYTES == 49152 ? 4 : 6;
   static constexpr int TMEM_COLS = 2 * BN;
   static constexpr int EPI_BYTES = EPI_WARPS * STAGE_BOX_BYTES;
   static constexpr int BIAS_BYTES = 2 * BN * 2;  // two tiles' worth of 16-bit bias values
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_BYTES + BIAS_BYTES + 1024 /*align*/ + (BN == 256 ? 128 : 256) /*barriers*/;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_BYTES + BIAS_BYTES + 1024 /*align*/ + 256 /*barriers*/;
 };
+static_assert(GemmCfg<256, false>::SMEM_BYTES <= 232448 && GemmCfg<256, true>::SMEM_BYTES <= 232448, "shared memory");
 
 // Exact-form GELU 0.5 x (1 + erf(x / sqrt 2)) with erf from the rational approximation 7.1.26 of Abramowitz and
 // Stegun (absolute error below 1.5e-7, far under the rounding of 16-bit outputs); about a third of the
@@ -126,18 +131,40 @@ template <> __device__ __forceinline__ void store8<__half>(__half* dst, const fl
   u.w = *reinterpret_cast<uint32_t*>(&t3);
   *reinterpret_cast<uint4*>(dst) = u;
 }
-template <typename OutT> __device__ __forceinline__ void load8(const OutT* src, float* v) {
+template <typename OutT> __device__ __forceinline__ void load8(const OutT* src, float* v);
+template <> __device__ __forceinline__ void load8<float>(const float* src, float* v) {
+  const float4 a = *reinterpret_cast<const float4*>(src), b = *reinterpret_cast<const float4*>(src + 4);
+  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+template <> __device__ __forceinline__ void load8<__nv_bfloat16>(const __nv_bfloat16* src, float* v) {
+  const uint4 u = *reinterpret_cast<const uint4*>(src);
+  const uint32_t w[4] = {u.x, u.y, u.z, u.w};
 #pragma unroll
-  for (int i = 0; i < 8; ++i) v[i] = sb::to_f(src[i]);
+  for (int i = 0; i < 4; ++i) {
+    v[2 * i] = __uint_as_float(w[i] << 16);
+    v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+  }
+}
+template <> __device__ __forceinline__ void load8<__half>(const __half* src, float* v) {
+  const uint4 u = *reinterpret_cast<const uint4*>(src);
+  const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+    v[2 * i] = f.x;
+    v[2 * i + 1] = f.y;
+  }
 }
 
-template <int BN, bool A_MN, bool B_MN, typename OutT>
+template <int BN, bool A_MN, bool B_MN, typename OutT, bool PAIR>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
     gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                         const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmP,
                         const GemmParams p) {
-  using Cfg = GemmCfg<BN>;
+  using Cfg = GemmCfg<BN, PAIR>;
   constexpr int STAGES = Cfg::STAGES;
+  constexpr int CTAS = Cfg::CTAS;
+  constexpr int LOAD_BN = Cfg::LOAD_BN;
   extern __shared__ uint8_t smem_raw[];
   // 1024-byte alignment for the 128-byte swizzle atoms
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -154,7 +181,11 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int m_tiles = (p.M + BM - 1) / BM;
+  // a tile is BM * CTAS rows: with PAIR, CTA `rank` of the cluster owns rows [rank * BM, rank * BM + BM) of it
+  const int rank = PAIR ? (int)sb::cluster_ctarank() : 0;
+  const int worker = PAIR ? blockIdx.x >> 1 : blockIdx.x;        // index of this CTA (pair) among the workers
+  const int num_workers = PAIR ? gridDim.x >> 1 : gridDim.x;
+  const int m_tiles = (p.M + BM * CTAS - 1) / (BM * CTAS);
   const int n_tiles = (p.N + BN - 1) / BN;
   const int num_kb = (p.K + BK - 1) / BK;
   const int S = p.splits;
@@ -167,18 +198,24 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
     }
     for (int a = 0; a < 2; ++a) {
       sb::mbar_init(&tfull_bar[a], 1);
-      sb::mbar_init(&tempty_bar[a], EPI_WARPS);  // one arrive per epilogue warp
+      sb::mbar_init(&tempty_bar[a], EPI_WARPS * CTAS);  // one arrive per epilogue warp (of both CTAs of a pair)
     }
     *abort_flag = 0;
     *last_flag = 0;
     sb::mbar_fence_init();
   }
   if (warp == 1) {
-    sb::tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
-    sb::tmem_relinquish();
+    if (PAIR) {
+      sb::tmem_alloc_pair(tmem_slot, Cfg::TMEM_COLS);
+      sb::tmem_relinquish_pair();
+    } else {
+      sb::tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
+      sb::tmem_relinquish();
+    }
   }
   sb::tc_fence_before();
-  __syncthreads();
+  if (PAIR) sb::cluster_sync_all();  // the peer's barriers are initialised before anything signals them
+  else __syncthreads();
   sb::tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
@@ -190,28 +227,49 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int unit = blockIdx.x; unit < num_units && ok; unit += gridDim.x) {
+      for (int unit = worker; unit < num_units && ok; unit += num_workers) {
         const int tile = unit / S, split = unit - tile * S;
-        const int m_blk = tile / n_tiles, n_blk = tile % n_tiles;
+        const int m_blk = (tile / n_tiles) * CTAS + rank, n_blk = tile % n_tiles;
         const int kb0 = (int)((long)split * num_kb / S), kb1 = (int)((long)(split + 1) * num_kb / S);
+        const int b_col0 = n_blk * BN + rank * LOAD_BN;  // first output column whose B rows this CTA loads
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!sb::mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag)) { ok = false; break; }
           uint8_t* a_s = smem + stage * Cfg::STAGE_BYTES;
           uint8_t* b_s = a_s + Cfg::A_BYTES;
-          sb::mbar_expect_tx(&full_bar[stage], Cfg::STAGE_BYTES);
-          if (A_MN) {
+          if (PAIR) {
+            // the leader's barrier counts the bytes of both CTAs; the MMAs it guards read both shared memories
+            const uint32_t bar = sb::mapa_u32(&full_bar[stage], 0);
+            if (rank == 0) sb::mbar_expect_tx(&full_bar[stage], CTAS * Cfg::STAGE_BYTES);
+            if (A_MN) {
 #pragma unroll
-            for (int j = 0; j < BM / 64; ++j)
-              sb::tma_load_2d(a_s + j * 8192, &tmA, &full_bar[stage], m_blk * BM + j * 64, kb * BK);
-          } else {
-            sb::tma_load_2d(a_s, &tmA, &full_bar[stage], kb * BK, m_blk * BM);
-          }
-          if (B_MN) {
+              for (int j = 0; j < BM / 64; ++j)
+                sb::tma_load_2d_pair(a_s + j * 8192, &tmA, bar, m_blk * BM + j * 64, kb * BK);
+            } else {
+              sb::tma_load_2d_pair(a_s, &tmA, bar, kb * BK, m_blk * BM);
+            }
+            if (B_MN) {
 #pragma unroll
-            for (int j = 0; j < BN / 64; ++j)
-              sb::tma_load_2d(b_s + j * 8192, &tmB, &full_bar[stage], n_blk * BN + j * 64, kb * BK);
+              for (int j = 0; j < LOAD_BN / 64; ++j)
+                sb::tma_load_2d_pair(b_s + j * 8192, &tmB, bar, b_col0 + j * 64, kb * BK);
+            } else {
+              sb::tma_load_2d_pair(b_s, &tmB, bar, kb * BK, b_col0);
+            }
           } else {
-            sb::tma_load_2d(b_s, &tmB, &full_bar[stage], kb * BK, n_blk * BN);
+            sb::mbar_expect_tx(&full_bar[stage], Cfg::STAGE_BYTES);
+            if (A_MN) {
+#pragma unroll
+              for (int j = 0; j < BM / 64; ++j)
+                sb::tma_load_2d(a_s + j * 8192, &tmA, &full_bar[stage], m_blk * BM + j * 64, kb * BK);
+            } else {
+              sb::tma_load_2d(a_s, &tmA, &full_bar[stage], kb * BK, m_blk * BM);
+            }
+            if (B_MN) {
+#pragma unroll
+              for (int j = 0; j < BN / 64; ++j)
+                sb::tma_load_2d(b_s + j * 8192, &tmB, &full_bar[stage], n_blk * BN + j * 64, kb * BK);
+            } else {
+              sb::tma_load_2d(b_s, &tmB, &full_bar[stage], kb * BK, n_blk * BN);
+            }
           }
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
@@ -219,14 +277,14 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
     }
   } else if (warp == 1) {
     // ---------------------------------------------------------- MMA issuer
-    if (lane == 0) {
-      const uint32_t idesc = sb::umma_idesc_f16(BM, BN, p.ab_fmt, A_MN ? 1u : 0u, B_MN ? 1u : 0u);
+    if (lane == 0 && rank == 0) {  // of a pair, the leader issues the MMAs for both CTAs
+      const uint32_t idesc = sb::umma_idesc_f16(BM * CTAS, BN, p.ab_fmt, A_MN ? 1u : 0u, B_MN ? 1u : 0u);
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
-      for (int unit = blockIdx.x; unit < num_units && ok; unit += gridDim.x) {
+      for (int unit = worker; unit < num_units && ok; unit += num_workers) {
         const int tile = unit / S, split = unit - tile * S;
         const int kb0 = (int)((long)split * num_kb / S), kb1 = (int)((long)(split + 1) * num_kb / S);
         if (!sb::mbar_wait(&tempty_bar[acc], acc_phase ^ 1, abort_flag)) { ok = false; break; }
@@ -243,13 +301,18 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
                                         : sb::umma_smem_desc(a_addr + k * 32, 16, 1024);
             const uint64_t bdesc = B_MN ? sb::umma_smem_desc(b_addr + k * 2048, 8192, 1024)
                                         : sb::umma_smem_desc(b_addr + k * 32, 16, 1024);
-            sb::umma_f16_ss(d_tmem, adesc, bdesc, idesc, (kb > kb0) || (k != 0));
+            if (PAIR) sb::umma_f16_ss_pair(d_tmem, adesc, bdesc, idesc, (kb > kb0) || (k != 0));
+            else sb::umma_f16_ss(d_tmem, adesc, bdesc, idesc, (kb > kb0) || (k != 0));
           }
-          sb::umma_commit(&empty_bar[stage]);  // frees the smem stage once these MMAs retire
+          // frees the smem stage (in both CTAs of a pair) once these MMAs retire
+          if (PAIR) sb::umma_commit_pair(&empty_bar[stage], 3);
+          else sb::umma_commit(&empty_bar[stage]);
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
         if (!ok) break;
-        sb::umma_commit(&tfull_bar[acc]);  // accumulator ready for the epilogue
+        // accumulator ready for the epilogue (of both CTAs of a pair: each reads its own TMEM)
+        if (PAIR) sb::umma_commit_pair(&tfull_bar[acc], 3);
+        else sb::umma_commit(&tfull_bar[acc]);
         if (++acc == 2) { acc = 0; acc_phase ^= 1; }
       }
     }
@@ -275,9 +338,16 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
     bool ok = true;
     // A warp whose wait expired keeps walking the units without touching data, so that the named barriers
     // below still see all their participants and nobody is left waiting.
-    for (int unit = blockIdx.x; unit < num_units; unit += gridDim.x) {
+    const uint32_t tempty_leader[2] = {PAIR ? sb::mapa_u32(&tempty_bar[0], 0) : 0u,
+                                       PAIR ? sb::mapa_u32(&tempty_bar[1], 0) : 0u};
+    auto release_acc = [&](int a) {  // this warp has read its part of accumulator `a`
+      if (PAIR) sb::mbar_arrive_cluster(tempty_leader[a]);
+      else sb::mbar_arrive(&tempty_bar[a]);
+    };
+    for (int unit = worker; unit < num_units; unit += num_workers) {
       const int tile = unit / S;
-      const int m_blk = tile / n_tiles, n_blk = tile % n_tiles;
+      const int m_blk = (tile / n_tiles) * CTAS + rank, n_blk = tile % n_tiles;
+      const int ctile = tile * CTAS + rank;  // this CTA's part of the tile: index of its counter and partial slots
       if (ok && !sb::mbar_wait(&tfull_bar[acc], acc_phase, abort_flag)) ok = false;
       sb::tc_fence_after();
       const int row = m_blk * BM + quad * 32 + lane;
@@ -287,7 +357,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
 
       if (S > 1) {
         // park this split's partial tile, then find out whether every other split has arrived already
-        float* part = p.ws_partial + ((long)unit * (BN / 32) * 128 + quad * 32 + lane) * 32;
+        float* part = p.ws_partial + (((long)ctile * S + (unit - tile * S)) * (BN / 32) * 128 + quad * 32 + lane) * 32;
 #pragma unroll 1
         for (int c = 0; c < CHUNKS && ok; ++c) {
           const int ch = chalf * CHUNKS + c;
@@ -302,18 +372,42 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
         }
         sb::tc_fence_before();
         __syncwarp();
-        if (lane == 0 && ok) sb::mbar_arrive(&tempty_bar[acc_used]);
+        if (lane == 0 && ok) release_acc(acc_used);
         __threadfence();
         epi_bar_sync();
         if (et == 0) {
-          const int old = atomicAdd(&p.ws_counter[tile], 1);
+          const int old = atomicAdd(&p.ws_counter[ctile], 1);
           const int last = old == S - 1;
-          if (last) p.ws_counter[tile] = 0;  // every split has arrived: leave the counter clean for the next launch
+          if (last) p.ws_counter[ctile] = 0;  // every split has arrived: leave the counter clean for the next launch
           *last_flag = last;
         }
         epi_bar_sync();
         if (!*last_flag) continue;
         __threadfence();
+        // last arrival: fold the partial tiles of splits 1 .. S-1 into the slot of split 0, in split order, with all
+        // epilogue threads striding over the tile (many independent loads in flight); the finishing code below
+        // then reads one reduced tile
+        {
+          float4* slot0 = reinterpret_cast<float4*>(p.ws_partial + (long)ctile * S * (BN / 32) * 128 * 32);
+          constexpr int TILE_F4 = (BN / 32) * 128 * 32 / 4;
+          for (int i = et; i < TILE_F4; i += EPI_WARPS * 32 * 2) {
+            const int j = i + EPI_WARPS * 32;
+            float4 a0 = __ldcg(slot0 + i);
+            float4 a1 = j < TILE_F4 ? __ldcg(slot0 + j) : make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int s2 = 1; s2 < S; ++s2) {
+              const float4 b0 = __ldcg(slot0 + (long)s2 * TILE_F4 + i);
+              a0.x += b0.x; a0.y += b0.y; a0.z += b0.z; a0.w += b0.w;
+              if (j < TILE_F4) {
+                const float4 b1 = __ldcg(slot0 + (long)s2 * TILE_F4 + j);
+                a1.x += b1.x; a1.y += b1.y; a1.z += b1.z; a1.w += b1.w;
+              }
+            }
+            slot0[i] = a0;
+            if (j < TILE_F4) slot0[j] = a1;
+          }
+          __threadfence_block();
+          epi_bar_sync();
+        }
       }
 
       // v[0..32) = accumulator values of 32-column chunk `ch` of this thread's row
@@ -325,16 +419,12 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
 #pragma unroll
           for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
         } else {
+          const float4* src = reinterpret_cast<const float4*>(
+              p.ws_partial + (((long)ctile * S * (BN / 32) + ch) * 128 + quad * 32 + lane) * 32);
 #pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = 0.f;
-          for (int s2 = 0; s2 < S; ++s2) {  // split order: the sum does not depend on which CTA came last
-            const float4* src = reinterpret_cast<const float4*>(
-                p.ws_partial + (((long)(tile * S + s2) * (BN / 32) + ch) * 128 + quad * 32 + lane) * 32);
-#pragma unroll
-            for (int g = 0; g < 8; ++g) {
-              const float4 f = __ldcg(src + g);
-              v[g * 4] += f.x; v[g * 4 + 1] += f.y; v[g * 4 + 2] += f.z; v[g * 4 + 3] += f.w;
-            }
+          for (int g = 0; g < 8; ++g) {
+            const float4 f = __ldcg(src + g);
+            v[g * 4] = f.x; v[g * 4 + 1] = f.y; v[g * 4 + 2] = f.z; v[g * 4 + 3] = f.w;
           }
         }
       };
@@ -457,7 +547,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
       if (S == 1) {
         sb::tc_fence_before();
         __syncwarp();
-        if (lane == 0) sb::mbar_arrive(&tempty_bar[acc_used]);
+        if (lane == 0) release_acc(acc_used);
       }
     }
     // stores in flight read the staging boxes: drain them before shared memory goes away
@@ -471,10 +561,13 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
     for (int i = 0; i < 2000; ++i) __nanosleep(1000);
   }
   sb::tc_fence_before();
-  __syncthreads();
+  // a pair leaves together: the leader's MMAs read the peer's shared memory, and both signal each other's barriers
+  if (PAIR) sb::cluster_sync_all();
+  else __syncthreads();
   if (warp == 1) {
     sb::tc_fence_after();
-    sb::tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+    if (PAIR) sb::tmem_dealloc_pair(tmem_base, Cfg::TMEM_COLS);
+    else sb::tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
   }
   if (threadIdx.x == 0 && *abort_flag && p.status) *p.status = SB_ERR_WAIT_TIMEOUT;
 }
@@ -511,72 +604,96 @@ int make_tmap_2d(CUtensorMap* tm, const void* base, long rows, long cols, long l
   return r == CUDA_SUCCESS ? SB_OK : SB_ERR_DRIVER;
 }
 
-template <int BN, bool A_MN, bool B_MN, typename OutT>
+template <int BN, bool A_MN, bool B_MN, typename OutT, bool PAIR>
 int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmC, const CUtensorMap& tmP,
                 const GemmParams& p, int sm_count, cudaStream_t stream) {
-  using Cfg = GemmCfg<BN>;
-  auto kern = gemm_tcgen05_kernel<BN, A_MN, B_MN, OutT>;
+  using Cfg = GemmCfg<BN, PAIR>;
+  auto kern = gemm_tcgen05_kernel<BN, A_MN, B_MN, OutT, PAIR>;
   static bool attr_set = false;
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
     if (e != cudaSuccess) return (int)e;
     attr_set = true;
   }
-  int units = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN) * p.splits;
-  int grid = units < sm_count ? units : sm_count;
-  kern<<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, stream>>>(tmA, tmB, tmC, tmP, p);
-  SB_CHECK_LAUNCH();
+  const int rows = BM * Cfg::CTAS;
+  const int units = ((p.M + rows - 1) / rows) * ((p.N + BN - 1) / BN) * p.splits;
+  const int max_workers = sm_count / Cfg::CTAS;
+  const int workers = units < max_workers ? units : max_workers;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(workers * Cfg::CTAS);
+  cfg.blockDim = dim3(GEMM_THREADS);
+  cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = Cfg::CTAS;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = PAIR ? 1 : 0;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, tmA, tmB, tmC, tmP, p);
+  if (e != cudaSuccess) return (int)e;
   return SB_OK;
 }
 
+// shape: 128 / 256 = tile width of a single CTA; 512 = CTA pair on a 256 x 256 tile
 template <bool A_MN, bool B_MN, typename OutT>
 int dispatch_bn(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmC, const CUtensorMap& tmP,
-                const GemmParams& p, int bn, int sm_count, cudaStream_t stream) {
-  if (bn == 256) return launch_gemm<256, A_MN, B_MN, OutT>(tmA, tmB, tmC, tmP, p, sm_count, stream);
-  return launch_gemm<128, A_MN, B_MN, OutT>(tmA, tmB, tmC, tmP, p, sm_count, stream);
+                const GemmParams& p, int shape, int sm_count, cudaStream_t stream) {
+  if (shape == 512) return launch_gemm<256, A_MN, B_MN, OutT, true>(tmA, tmB, tmC, tmP, p, sm_count, stream);
+  if (shape == 256) return launch_gemm<256, A_MN, B_MN, OutT, false>(tmA, tmB, tmC, tmP, p, sm_count, stream);
+  return launch_gemm<128, A_MN, B_MN, OutT, false>(tmA, tmB, tmC, tmP, p, sm_count, stream);
 }
 
 template <typename OutT>
 int dispatch_major(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmC, const CUtensorMap& tmP,
-                   const GemmParams& p, int a_mn, int b_mn, int bn, int sm_count, cudaStream_t stream) {
-  if (!a_mn && !b_mn) return dispatch_bn<false, false, OutT>(tmA, tmB, tmC, tmP, p, bn, sm_count, stream);
-  if (!a_mn && b_mn) return dispatch_bn<false, true, OutT>(tmA, tmB, tmC, tmP, p, bn, sm_count, stream);
-  if (a_mn && b_mn) return dispatch_bn<true, true, OutT>(tmA, tmB, tmC, tmP, p, bn, sm_count, stream);
+                   const GemmParams& p, int a_mn, int b_mn, int shape, int sm_count, cudaStream_t stream) {
+  if (!a_mn && !b_mn) return dispatch_bn<false, false, OutT>(tmA, tmB, tmC, tmP, p, shape, sm_count, stream);
+  if (!a_mn && b_mn) return dispatch_bn<false, true, OutT>(tmA, tmB, tmC, tmP, p, shape, sm_count, stream);
+  if (a_mn && b_mn) return dispatch_bn<true, true, OutT>(tmA, tmB, tmC, tmP, p, shape, sm_count, stream);
   return SB_ERR_BAD_ARG;
 }
 
 constexpr long WS_COUNTER_BYTES = 4096;  // 1024 tile counters at the head of the workspace
 
-// Tile width and k-splits for an [M, N, K] problem: the estimated time is (waves of work units) x (time of one
-// unit); a 128-wide tile moves 1.25x the operand bytes per flop of a 256-wide one, and each split adds the
-// traffic of its fp32 partial tile.
-void choose_shape(int M, int N, int K, int bn_hint, int split_hint, int sm_count, long ws_bytes, int* bn_out,
+// Tile shape (128, 256, or 512 = CTA pair) and k-splits for an [M, N, K] problem.  The estimate is
+// (waves of work units) x (time of one unit); a unit's time is its k-blocks times a per-block cost that reflects
+// the operand bytes an SM pulls from L2 per flop (the bound of these kernels), plus a fixed cost per unit and per
+// split.  The constants are fitted to measurements of the transformer shapes on a B200.
+void choose_shape(int M, int N, int K, int shape_hint, int split_hint, int sm_count, long ws_bytes, int* shape_out,
                   int* splits_out) {
-  const int m_tiles = (M + BM - 1) / BM;
   const int num_kb = (K + BK - 1) / BK;
   double best = 1e30;
-  int best_bn = 128, best_s = 1;
-  for (int bn = 128; bn <= 256; bn += 128) {
-    if (bn_hint && bn != bn_hint) continue;
-    if (bn == 256 && N <= 128 && !bn_hint) continue;
-    const long tiles = (long)m_tiles * ((N + bn - 1) / bn);
+  int best_shape = 128, best_s = 1;
+  const int shapes[3] = {128, 256, 512};
+  for (int si = 0; si < 3; ++si) {
+    const int shape = shapes[si];
+    if (shape_hint && shape != shape_hint) continue;
+    const int bn = shape == 128 ? 128 : 256;
+    const int ctas = shape == 512 ? 2 : 1;
+    if (!shape_hint && ((bn == 256 && N <= 128) || (ctas == 2 && M <= 128))) continue;
+    const long tiles = (long)((M + BM * ctas - 1) / (BM * ctas)) * ((N + bn - 1) / bn);
+    const double kb_cost = shape == 128 ? 0.37 : (shape == 256 ? 0.45 : 0.42);  // microseconds per k-block
+    const double split_cost = bn == 128 ? 3.5 : 7.0;  // per split: writing and folding one fp32 partial tile
+    const int workers = sm_count / ctas;
     for (int s = 1; s <= 16; ++s) {
-      if (split_hint > 0 && s != split_hint && !(s == 1 && split_hint > 1)) continue;
+      if (split_hint > 0 && s != split_hint) continue;
       if (s > 1) {
-        if (tiles > 1024 || num_kb / s < (split_hint > 0 ? 1 : 8)) break;
-        const long need = WS_COUNTER_BYTES + tiles * s * (long)BM * bn * 4;
+        if (tiles * ctas > 1024 || num_kb / s < (split_hint > 0 ? 1 : 8)) break;
+        const long need = WS_COUNTER_BYTES + tiles * ctas * s * (long)BM * bn * 4;
         if (need > ws_bytes) break;
       }
       const long units = tiles * s;
-      const long waves = (units + sm_count - 1) / sm_count;
-      const double unit_time = (bn == 256 ? 2.0 : 1.25) * ((double)num_kb / s + (s > 1 ? 6.0 : 3.0));
-      const double t = waves * unit_time;
-      if (t < best * 0.97 || (split_hint > 1 && s == split_hint && best_s != split_hint)) {
-        best = t; best_bn = bn; best_s = s;
-      }
+      const long waves = (units + workers - 1) / workers;
+      // fewer busy SMs run at higher clocks and see less contention in L2
+      const double busy = (double)(units < workers ? units : workers) * ctas / sm_count;
+      const double load = 0.75 + 0.25 * (busy < 1.0 ? busy : 1.0);
+      const double unit_time = (double)num_kb / s * kb_cost * load + 1.0 + (s > 1 ? s * split_cost : 0.0);
+      const double t = waves * unit_time + 7.0;
+      if (t < best * 0.97) { best = t; best_shape = shape; best_s = s; }
     }
   }
-  *bn_out = best_bn;
+  *shape_out = best_shape;
   *splits_out = best_s;
 }
 
@@ -591,7 +708,8 @@ int make_tmap_out(CUtensorMap* tm, const void* base, long rows, long cols, long 
 //   a_mn = 0: A is [M, K] (lda >= K);  a_mn = 1: A is [K, M] (lda >= M)
 //   b_mn = 0: B is [N, K] (ldb >= K);  b_mn = 1: B is [K, N] (ldb >= N)
 //   in_dtype / out_dtype: SB_DT_* (inputs bf16 or fp16; output bf16, fp16 (fp16 in only) or fp32)
-//   bn_hint / split_hint: 0 = choose; otherwise the tile width (128 / 256) and the number of k-splits to use
+//   bn_hint / split_hint: 0 = choose; otherwise the tile shape (128 / 256 wide single-CTA tiles, 512 = a CTA pair
+//              on a 256 x 256 tile) and the number of k-splits to use
 //   workspace: optional device scratch for split-K (first 4 KB: tile counters, zero before the first use and
 //              left zero by every launch; then fp32 partial tiles); without it no problem is split.  One
 //              workspace serves one stream at a time.
@@ -606,17 +724,19 @@ SB_API int sb200_gemm_ws(const void* A, const void* B, void* C, void* C_pre, con
   if ((lda % 8) || (ldb % 8)) return SB_ERR_BAD_ARG;  // TMA: strides are multiples of 16 bytes
   if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15)) return SB_ERR_BAD_ARG;
   const int fp16 = in_dtype == SB_DT_F16;
-  if (bn_hint != 128 && bn_hint != 256) bn_hint = 0;
-  int bn = 128, splits = 1;
+  if (bn_hint != 128 && bn_hint != 256 && bn_hint != 512) bn_hint = 0;
+  int shape = 128, splits = 1;
   const bool ws_ok = workspace && (reinterpret_cast<uintptr_t>(workspace) & 15) == 0;
-  choose_shape(M, N, K, bn_hint, split_hint, sm_count, ws_ok ? workspace_bytes : 0, &bn, &splits);
+  choose_shape(M, N, K, bn_hint, split_hint, sm_count, ws_ok ? workspace_bytes : 0, &shape, &splits);
+  const int bn = shape == 128 ? 128 : 256;
+  const int b_rows = shape == 512 ? 128 : bn;  // B rows one CTA loads per stage
   CUtensorMap tmA, tmB, tmC, tmP;
   int rc;
   if (a_mn) rc = make_tmap_2d(&tmA, A, K, M, lda, 64, fp16);
   else rc = make_tmap_2d(&tmA, A, M, K, lda, BM, fp16);
   if (rc) return rc;
   if (b_mn) rc = make_tmap_2d(&tmB, B, K, N, ldb, 64, fp16);
-  else rc = make_tmap_2d(&tmB, B, N, K, ldb, bn, fp16);
+  else rc = make_tmap_2d(&tmB, B, N, K, ldb, b_rows, fp16);
   if (rc) return rc;
   GemmParams p;
   p.C = C; p.C_pre = C_pre; p.bias = bias; p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.act = act;
@@ -633,11 +753,11 @@ SB_API int sb200_gemm_ws(const void* A, const void* B, void* C, void* C_pre, con
     if ((rc = make_tmap_out(&tmC, C, M, N, ldc, fp16))) return rc;
     if (C_pre && (rc = make_tmap_out(&tmP, C_pre, M, N, ldc, fp16))) return rc;
   }
-  if (out_dtype == SB_DT_F32) return dispatch_major<float>(tmA, tmB, tmC, tmP, p, a_mn, b_mn, bn, sm_count, stream);
+  if (out_dtype == SB_DT_F32) return dispatch_major<float>(tmA, tmB, tmC, tmP, p, a_mn, b_mn, shape, sm_count, stream);
   if (out_dtype == SB_DT_BF16 && !fp16)
-    return dispatch_major<__nv_bfloat16>(tmA, tmB, tmC, tmP, p, a_mn, b_mn, bn, sm_count, stream);
+    return dispatch_major<__nv_bfloat16>(tmA, tmB, tmC, tmP, p, a_mn, b_mn, shape, sm_count, stream);
   if (out_dtype == SB_DT_F16 && fp16)
-    return dispatch_major<__half>(tmA, tmB, tmC, tmP, p, a_mn, b_mn, bn, sm_count, stream);
+    return dispatch_major<__half>(tmA, tmB, tmC, tmP, p, a_mn, b_mn, shape, sm_count, stream);
   return SB_ERR_BAD_ARG;
 }
 

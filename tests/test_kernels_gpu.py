@@ -199,7 +199,7 @@ GEMM_SHAPES = [(128, 256, 64), (256, 512, 128), (300, 264, 200), (2048, 2304, 76
 
 @pytest.mark.parametrize("M,N,K_", GEMM_SHAPES)
 @pytest.mark.parametrize("mode", ["nt", "nn", "tn"])
-@pytest.mark.parametrize("bn", [0, 128, 256])
+@pytest.mark.parametrize("bn", [0, 128, 256, 512])
 def test_gemm(M, N, K_, mode, bn):
     torch.manual_seed(7)
     dt = torch.bfloat16
@@ -258,6 +258,9 @@ def test_gemm_split_k_epilogues_and_determinism():
     assert torch.equal(out, out2)
     c32 = K.gemm(a, b, a_mn=True, b_mn=True, out_dtype=torch.float32)
     assert _rel(c32, ref) < 1e-2
+    for shape, split in ((512, 1), (512, 2), (512, 5), (256, 3), (128, 4)):  # CTA pairs and single CTAs, split or not
+        c = K.gemm(a, b, a_mn=True, b_mn=True, bn=shape, split=split)
+        assert _rel(c, ref) < 1e-2, (shape, split, _rel(c, ref))
     x = torch.randn(M, K_, device=DEV, dtype=torch.float16) * 0.1
     w = torch.randn(N, K_, device=DEV, dtype=torch.float16) * 0.1
     bias = torch.randn(N, device=DEV, dtype=torch.float16)
