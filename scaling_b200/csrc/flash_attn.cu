@@ -25,7 +25,8 @@
 
 namespace {
 
-constexpr int FA_THREADS = 192;
+constexpr int FA_THREADS = 192;      // forward: TMA warp, MMA warp, 4 softmax warps (thread = query row)
+constexpr int FA_BWD_THREADS = 320;  // backward: TMA warp, MMA warp, 8 warps (two threads share a row, 64 columns each)
 constexpr int TILE = 128;          // queries per CTA and keys per step
 constexpr int PANEL_BYTES = 16384; // 128 rows x 64 bf16
 
@@ -91,21 +92,37 @@ __device__ __forceinline__ void row_range(const FaParams& p, int t, int& lo, int
 }
 
 // ============================================================================ forward
+// D = 64 runs two CTAs per SM (256 TMEM columns and under 113 KB of shared memory each: one S buffer, one V stage),
+// so that the softmax of one CTA overlaps the MMAs of the other; D = 128 runs one CTA per SM with S and V double
+// buffered.  Softmax per tile: pass 1 takes the row maximum of the raw scores, pass 2 computes
+// exp2(score * scale_log2 - max) with one FMA + ex2 per element; tiles that lie fully inside a row's allowed key range
+// skip the per-element mask tests.
+template <int D> struct FaFwdCfg {
+  static constexpr bool TWO = D == 64;             // two CTAs per SM
+  static constexpr int SBUF = TWO ? 1 : 2;         // S accumulators in TMEM
+  static constexpr int VST = TWO ? 1 : 2;          // V stages (K always has two)
+  static constexpr int TMEM_COLS = TWO ? 256 : 512;
+  static constexpr int PANELS = D / 64;
+  static constexpr int TILE_BYTES = PANELS * PANEL_BYTES;
+  static constexpr int SMEM = TILE_BYTES * (1 + 2 + VST) + 2 * PANEL_BYTES + 1024 + 256;
+};
+
 template <int D>
-__global__ void __launch_bounds__(FA_THREADS, 1)
+__global__ void __launch_bounds__(FA_THREADS, FaFwdCfg<D>::TWO ? 2 : 1)
     fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                   const __grid_constant__ CUtensorMap tmV, const FaParams p) {
-  constexpr int PANELS = D / 64;
-  constexpr int TILE_BYTES = PANELS * PANEL_BYTES;
-  constexpr int TMEM_COLS = 512;
-  constexpr uint32_t S_COL = 0;        // two S buffers of 128 columns
-  constexpr uint32_t O_COL = 256;      // two O buffers of D columns
+  using Cfg = FaFwdCfg<D>;
+  constexpr int PANELS = Cfg::PANELS;
+  constexpr int TILE_BYTES = Cfg::TILE_BYTES;
+  constexpr int SBUF = Cfg::SBUF, VST = Cfg::VST;
+  constexpr uint32_t S_COL = 0;               // SBUF buffers of 128 columns
+  constexpr uint32_t O_COL = SBUF * TILE;     // two O buffers of D columns
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sQ = smem;
   uint8_t* sK = sQ + TILE_BYTES;           // 2 stages
-  uint8_t* sV = sK + 2 * TILE_BYTES;       // 2 stages
-  uint8_t* sP = sV + 2 * TILE_BYTES;       // 2 panels
+  uint8_t* sV = sK + 2 * TILE_BYTES;       // VST stages
+  uint8_t* sP = sV + VST * TILE_BYTES;     // 2 panels
   uint64_t* bars = reinterpret_cast<uint64_t*>(sP + 2 * PANEL_BYTES);
   uint64_t* q_full = bars;          // 1
   uint64_t* k_full = bars + 1;      // 2
@@ -115,7 +132,8 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
   uint64_t* s_full = bars + 9;      // 2
   uint64_t* p_full = bars + 11;     // 1
   uint64_t* o_full = bars + 12;     // 2
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
+  uint64_t* s_empty = bars + 14;    // 1 (single S buffer only)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -142,11 +160,12 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
       sb::mbar_init(&o_full[i], 1);
     }
     sb::mbar_init(p_full, 4);
+    sb::mbar_init(s_empty, 4);
     *abort_flag = 0;
     sb::mbar_fence_init();
   }
   if (warp == 1) {
-    sb::tmem_alloc(tmem_slot, TMEM_COLS);
+    sb::tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
     sb::tmem_relinquish();
   }
   sb::tc_fence_before();
@@ -163,19 +182,19 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
 #pragma unroll
       for (int pn = 0; pn < PANELS; ++pn) sb::tma_load_2d(sQ + pn * PANEL_BYTES, &tmQ, q_full, h * p.ldq_head + pn * 64, q0);
       for (int j = 0; j < n_tiles; ++j) {
-        const int st = j & 1;
-        const uint32_t ph = (j >> 1) & 1;
+        const int kst = j & 1, vst = j % VST;
+        const uint32_t kph = (j >> 1) & 1, vph = (j / VST) & 1;
         const int kv0 = (kv_begin + j) * TILE;
-        if (!sb::mbar_wait(&k_empty[st], ph ^ 1, abort_flag)) break;
-        sb::mbar_expect_tx(&k_full[st], TILE_BYTES);
+        if (!sb::mbar_wait(&k_empty[kst], kph ^ 1, abort_flag)) break;
+        sb::mbar_expect_tx(&k_full[kst], TILE_BYTES);
 #pragma unroll
         for (int pn = 0; pn < PANELS; ++pn)
-          sb::tma_load_2d(sK + st * TILE_BYTES + pn * PANEL_BYTES, &tmK, &k_full[st], hk * p.ldk_head + pn * 64, kv0);
-        if (!sb::mbar_wait(&v_empty[st], ph ^ 1, abort_flag)) break;
-        sb::mbar_expect_tx(&v_full[st], TILE_BYTES);
+          sb::tma_load_2d(sK + kst * TILE_BYTES + pn * PANEL_BYTES, &tmK, &k_full[kst], hk * p.ldk_head + pn * 64, kv0);
+        if (!sb::mbar_wait(&v_empty[vst], vph ^ 1, abort_flag)) break;
+        sb::mbar_expect_tx(&v_full[vst], TILE_BYTES);
 #pragma unroll
         for (int pn = 0; pn < PANELS; ++pn)
-          sb::tma_load_2d(sV + st * TILE_BYTES + pn * PANEL_BYTES, &tmV, &v_full[st], hk * p.ldv_head + pn * 64, kv0);
+          sb::tma_load_2d(sV + vst * TILE_BYTES + pn * PANEL_BYTES, &tmV, &v_full[vst], hk * p.ldv_head + pn * 64, kv0);
       }
     }
   } else if (warp == 1) {
@@ -185,30 +204,33 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
       const uint32_t q_addr = sb::smem_u32(sQ), p_addr = sb::smem_u32(sP);
       bool ok = sb::mbar_wait(q_full, 0, abort_flag);
       auto issue_s = [&](int j) -> bool {
-        const int st = j & 1;
-        if (!sb::mbar_wait(&k_full[st], (j >> 1) & 1, abort_flag)) return false;
+        const int kst = j & 1, sbuf = j % SBUF;
+        if (!sb::mbar_wait(&k_full[kst], (j >> 1) & 1, abort_flag)) return false;
+        if (SBUF == 1 && j > 0) {  // the softmax threads have read S(j - 1) out of the only buffer
+          if (!sb::mbar_wait(s_empty, (j - 1) & 1, abort_flag)) return false;
+        }
         sb::tc_fence_after();
-        const uint32_t k_addr = sb::smem_u32(sK + st * TILE_BYTES);
+        const uint32_t k_addr = sb::smem_u32(sK + kst * TILE_BYTES);
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk)
-          sb::umma_f16_ss(tmem_base + S_COL + st * TILE, desc_kmajor(q_addr, kk), desc_kmajor(k_addr, kk), idesc_s, kk != 0);
-        sb::umma_commit(&s_full[st]);
-        sb::umma_commit(&k_empty[st]);
+          sb::umma_f16_ss(tmem_base + S_COL + sbuf * TILE, desc_kmajor(q_addr, kk), desc_kmajor(k_addr, kk), idesc_s, kk != 0);
+        sb::umma_commit(&s_full[sbuf]);
+        sb::umma_commit(&k_empty[kst]);
         return true;
       };
       if (ok) ok = issue_s(0);
       for (int j = 0; j < n_tiles && ok; ++j) {
-        const int st = j & 1;
+        const int vst = j % VST, obuf = j & 1;
         if (j + 1 < n_tiles) { if (!issue_s(j + 1)) break; }
         if (!sb::mbar_wait(p_full, j & 1, abort_flag)) break;
-        if (!sb::mbar_wait(&v_full[st], (j >> 1) & 1, abort_flag)) break;
+        if (!sb::mbar_wait(&v_full[vst], (j / VST) & 1, abort_flag)) break;
         sb::tc_fence_after();
-        const uint32_t v_addr = sb::smem_u32(sV + st * TILE_BYTES);
+        const uint32_t v_addr = sb::smem_u32(sV + vst * TILE_BYTES);
 #pragma unroll
         for (int kk = 0; kk < TILE / 16; ++kk)
-          sb::umma_f16_ss(tmem_base + O_COL + st * D, desc_kmajor(p_addr, kk), desc_mnmajor(v_addr, kk), idesc_o, kk != 0);
-        sb::umma_commit(&o_full[st]);
-        sb::umma_commit(&v_empty[st]);
+          sb::umma_f16_ss(tmem_base + O_COL + obuf * D, desc_kmajor(p_addr, kk), desc_mnmajor(v_addr, kk), idesc_o, kk != 0);
+        sb::umma_commit(&o_full[obuf]);
+        sb::umma_commit(&v_empty[vst]);
       }
     }
   } else {
@@ -218,30 +240,41 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
     int lo, hi;
     row_range(p, t, lo, hi);
     const uint32_t t_lane = tmem_base + ((uint32_t)(quad * 32) << 16);
-    float m = -1e30f, l = 0.f, alpha_prev = 1.f;
+    const float sl2 = p.scale_log2;
+    float m_raw = -1e30f;   // running maximum of the raw scores (the softmax scale is positive)
+    float m = __fmul_rn(m_raw, sl2);  // the same in the exp2 domain; kept as a value of its own so that m - mx is exactly 0
+                            // while the maximum does not move (recomputing the product could be fused differently)
+    float l = 0.f, alpha_prev = 1.f;
     float o_acc[D];
 #pragma unroll
     for (int i = 0; i < D; ++i) o_acc[i] = 0.f;
     bool ok = true;
     for (int j = 0; j < n_tiles && ok; ++j) {
-      const int st = j & 1;
+      const int sbuf = j % SBUF;
       const int kv0 = (kv_begin + j) * TILE;
-      if (!sb::mbar_wait(&s_full[st], (j >> 1) & 1, abort_flag)) { ok = false; break; }
+      const uint32_t s_addr = t_lane + S_COL + sbuf * TILE;
+      if (!sb::mbar_wait(&s_full[sbuf], (j / SBUF) & 1, abort_flag)) { ok = false; break; }
       sb::tc_fence_after();
+      const bool interior = kv0 >= lo && kv0 + TILE - 1 <= hi;  // every key of the tile is allowed for this row
       // pass 1: row maximum
-      float mx = m;
+      float mx_raw = m_raw;
 #pragma unroll 1
       for (int ch = 0; ch < 4; ++ch) {
         uint32_t v[32];
-        sb::tmem_ld32(t_lane + S_COL + st * TILE + ch * 32, v);
+        sb::tmem_ld32(s_addr + ch * 32, v);
         sb::tmem_ld_wait();
+        if (interior) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const int kidx = kv0 + ch * 32 + i;
-          float x = __uint_as_float(v[i]) * p.scale_log2;
-          if (kidx >= lo && kidx <= hi) mx = fmaxf(mx, x);
+          for (int i = 0; i < 32; ++i) mx_raw = fmaxf(mx_raw, __uint_as_float(v[i]));
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const int kidx = kv0 + ch * 32 + i;
+            if (kidx >= lo && kidx <= hi) mx_raw = fmaxf(mx_raw, __uint_as_float(v[i]));
+          }
         }
       }
+      const float mx = __fmul_rn(mx_raw, sl2);  // never contracted into an FMA with its consumers
       const float alpha = fast_exp2(m - mx);
       // the previous P V must be done before P is overwritten
       if (j > 0) {
@@ -253,17 +286,26 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
 #pragma unroll 1
       for (int ch = 0; ch < 4; ++ch) {
         uint32_t v[32];
-        sb::tmem_ld32(t_lane + S_COL + st * TILE + ch * 32, v);
+        sb::tmem_ld32(s_addr + ch * 32, v);
         sb::tmem_ld_wait();
-        float pr[32];
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const int kidx = kv0 + ch * 32 + i;
-          float x = __uint_as_float(v[i]) * p.scale_log2;
-          float e = (kidx >= lo && kidx <= hi) ? fast_exp2(x - mx) : 0.f;
-          pr[i] = e;
-          rs += e;
+        if (SBUF == 1 && ch == 3) {  // S is in registers: the next Q K^T may overwrite the buffer
+          sb::tc_fence_before();
+          __syncwarp();
+          if (lane == 0) sb::mbar_arrive(s_empty);
         }
+        float pr[32];
+        if (interior) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) pr[i] = fast_exp2(fmaf(__uint_as_float(v[i]), sl2, -mx));
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const int kidx = kv0 + ch * 32 + i;
+            pr[i] = (kidx >= lo && kidx <= hi) ? fast_exp2(fmaf(__uint_as_float(v[i]), sl2, -mx)) : 0.f;
+          }
+        }
+#pragma unroll
+        for (int i = 0; i < 32; ++i) rs += pr[i];
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
           uint4 u;
@@ -288,10 +330,11 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
           sb::tmem_ld32(t_lane + O_COL + pst * D + ch * 32, v);
           sb::tmem_ld_wait();
 #pragma unroll
-          for (int i = 0; i < 32; ++i) o_acc[ch * 32 + i] = o_acc[ch * 32 + i] * alpha_prev + __uint_as_float(v[i]);
+          for (int i = 0; i < 32; ++i) o_acc[ch * 32 + i] = fmaf(o_acc[ch * 32 + i], alpha_prev, __uint_as_float(v[i]));
         }
       }
       alpha_prev = alpha;
+      m_raw = mx_raw;
       m = mx;
     }
     if (ok && n_tiles > 0) {
@@ -304,7 +347,7 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
           sb::tmem_ld32(t_lane + O_COL + pst * D + ch * 32, v);
           sb::tmem_ld_wait();
 #pragma unroll
-          for (int i = 0; i < 32; ++i) o_acc[ch * 32 + i] = o_acc[ch * 32 + i] * alpha_prev + __uint_as_float(v[i]);
+          for (int i = 0; i < 32; ++i) o_acc[ch * 32 + i] = fmaf(o_acc[ch * 32 + i], alpha_prev, __uint_as_float(v[i]));
         }
         if (t < p.T) {
           const float inv = l > 0.f ? 1.f / l : 0.f;
@@ -331,7 +374,7 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
   __syncthreads();
   if (warp == 1) {
     sb::tc_fence_after();
-    sb::tmem_dealloc(tmem_base, TMEM_COLS);
+    sb::tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
   }
   if (threadIdx.x == 0 && *abort_flag && p.status) *p.status = SB_ERR_WAIT_TIMEOUT;
 }
@@ -364,7 +407,7 @@ __global__ void fa_bwd_delta_kernel(const __nv_bfloat16* __restrict__ O, const _
 //   (lanes = keys) over the whole loop.  With more than one split the results are written as fp32 partials
 //   and summed in a fixed order by fa_bwd_reduce_kernel.
 template <int D>
-__global__ void __launch_bounds__(FA_THREADS, 1)
+__global__ void __launch_bounds__(FA_BWD_THREADS, 1)
     fa_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                        const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
                        const FaParams p, const int q_tile_end_hint, const int heads_per_split,
@@ -421,7 +464,7 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
       sb::mbar_init(&qdo_empty[i], 1);
     }
     sb::mbar_init(sdp_full, 1);
-    sb::mbar_init(pds_full, 4);
+    sb::mbar_init(pds_full, 8);
     sb::mbar_init(acc_done, 1);
     *abort_flag = 0;
     sb::mbar_fence_init();
@@ -490,8 +533,10 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
     }
   } else {
     const int quad = warp & 3;
+    const int half = (warp - 2) >> 2;  // which 64 columns of the row this thread handles
     const int r = quad * 32 + lane;  // query row inside the tile while computing P / dS, key row in the epilogue
     const uint32_t t_lane = tmem_base + ((uint32_t)(quad * 32) << 16);
+    const float sl2 = p.scale_log2, sc = p.scale;
     bool ok = true;
     for (int it = 0; it < n_iter && ok; ++it) {
       const int h = hk * group + h_begin + it / n_qt;
@@ -500,22 +545,32 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
       int lo, hi;
       row_range(p, t, lo, hi);
       const float lse = t < p.T ? p.lse2[(long)h * p.T + t] : 0.f;
-      const float dl = t < p.T ? p.delta[(long)h * p.T + t] : 0.f;
+      const float dls = (t < p.T ? p.delta[(long)h * p.T + t] : 0.f) * sc;
+      const bool interior = kv0 >= lo && kv0 + TILE - 1 <= hi;  // every key of the tile is allowed for this row
       if (!sb::mbar_wait(sdp_full, it & 1, abort_flag)) { ok = false; break; }
       sb::tc_fence_after();
 #pragma unroll 1
-      for (int ch = 0; ch < 4; ++ch) {
+      for (int ch = half * 2; ch < half * 2 + 2; ++ch) {
         uint32_t s[32], dp[32];
         sb::tmem_ld32(t_lane + S_COL + ch * 32, s);
         sb::tmem_ld32(t_lane + DP_COL + ch * 32, dp);
         sb::tmem_ld_wait();
         float pv[32], dsv[32];
+        if (interior) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const int kidx = kv0 + ch * 32 + i;
-          const float pr = (kidx >= lo && kidx <= hi) ? fast_exp2(__uint_as_float(s[i]) * p.scale_log2 - lse) : 0.f;
-          pv[i] = pr;
-          dsv[i] = pr * (__uint_as_float(dp[i]) - dl) * p.scale;
+          for (int i = 0; i < 32; ++i) {
+            const float pr = fast_exp2(fmaf(__uint_as_float(s[i]), sl2, -lse));
+            pv[i] = pr;
+            dsv[i] = pr * fmaf(__uint_as_float(dp[i]), sc, -dls);
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const int kidx = kv0 + ch * 32 + i;
+            const float pr = (kidx >= lo && kidx <= hi) ? fast_exp2(fmaf(__uint_as_float(s[i]), sl2, -lse)) : 0.f;
+            pv[i] = pr;
+            dsv[i] = pr * fmaf(__uint_as_float(dp[i]), sc, -dls);
+          }
         }
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
@@ -545,7 +600,7 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
     if (ok && (have || n_iter == 0)) {
       const long row = (long)kidx * p.Hkv + hk;
 #pragma unroll 1
-      for (int ch = 0; ch < D / 32; ++ch) {
+      for (int ch = half; ch < D / 32; ch += 2) {
         uint32_t a[32], b[32];
         if (have) {
           sb::tmem_ld32(t_lane + DV_COL + ch * 32, a);
@@ -625,7 +680,7 @@ __global__ void fa_bwd_reduce_kernel(const float* __restrict__ partial, __nv_bfl
 // ============================================================================ backward: dQ
 // CTA = (query tile, head).  Per key tile: S = Q K^T, dP = dO V^T -> threads: dS (bf16) -> dQ += dS K
 template <int D>
-__global__ void __launch_bounds__(FA_THREADS, 1)
+__global__ void __launch_bounds__(FA_BWD_THREADS, 1)
     fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                      const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
                      const FaParams p) {
@@ -665,7 +720,7 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
     sb::mbar_init(kv_full, 1);
     sb::mbar_init(kv_empty, 1);
     sb::mbar_init(sdp_full, 1);
-    sb::mbar_init(ds_full, 4);
+    sb::mbar_init(ds_full, 8);
     sb::mbar_init(acc_done, 1);
     *abort_flag = 0;
     sb::mbar_fence_init();
@@ -727,30 +782,39 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
     }
   } else {
     const int quad = warp & 3;
+    const int half = (warp - 2) >> 2;  // which 64 columns of the row this thread handles
     const int r = quad * 32 + lane;
     const int t = q0 + r;
     int lo, hi;
     row_range(p, t, lo, hi);
+    const float sl2 = p.scale_log2, sc = p.scale;
     const float lse = t < p.T ? p.lse2[(long)h * p.T + t] : 0.f;
-    const float dl = t < p.T ? p.delta[(long)h * p.T + t] : 0.f;
+    const float dls = (t < p.T ? p.delta[(long)h * p.T + t] : 0.f) * sc;
     const uint32_t t_lane = tmem_base + ((uint32_t)(quad * 32) << 16);
     bool ok = true;
     for (int j = 0; j < n_tiles && ok; ++j) {
       const int kv0 = (kv_begin + j) * TILE;
+      const bool interior = kv0 >= lo && kv0 + TILE - 1 <= hi;  // every key of the tile is allowed for this row
       if (!sb::mbar_wait(sdp_full, j & 1, abort_flag)) { ok = false; break; }
       sb::tc_fence_after();
 #pragma unroll 1
-      for (int ch = 0; ch < 4; ++ch) {
+      for (int ch = half * 2; ch < half * 2 + 2; ++ch) {
         uint32_t s[32], dp[32];
         sb::tmem_ld32(t_lane + S_COL + ch * 32, s);
         sb::tmem_ld32(t_lane + DP_COL + ch * 32, dp);
         sb::tmem_ld_wait();
         float dsv[32];
+        if (interior) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const int kidx = kv0 + ch * 32 + i;
-          const float pr = (kidx >= lo && kidx <= hi) ? fast_exp2(__uint_as_float(s[i]) * p.scale_log2 - lse) : 0.f;
-          dsv[i] = pr * (__uint_as_float(dp[i]) - dl) * p.scale;
+          for (int i = 0; i < 32; ++i)
+            dsv[i] = fast_exp2(fmaf(__uint_as_float(s[i]), sl2, -lse)) * fmaf(__uint_as_float(dp[i]), sc, -dls);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const int kidx = kv0 + ch * 32 + i;
+            const float pr = (kidx >= lo && kidx <= hi) ? fast_exp2(fmaf(__uint_as_float(s[i]), sl2, -lse)) : 0.f;
+            dsv[i] = pr * fmaf(__uint_as_float(dp[i]), sc, -dls);
+          }
         }
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
@@ -771,7 +835,7 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
       sb::tc_fence_after();
       __nv_bfloat16* dq = reinterpret_cast<__nv_bfloat16*>(p.dQ) + (long)t * p.lddq_tok + (long)h * p.lddq_head;
 #pragma unroll 1
-      for (int ch = 0; ch < D / 32; ++ch) {
+      for (int ch = half; ch < D / 32; ch += 2) {
         uint32_t a[32];
         sb::tmem_ld32(t_lane + DQ_COL + ch * 32, a);
         sb::tmem_ld_wait();
@@ -833,7 +897,7 @@ int fa_tmap(CUtensorMap* tm, const void* base, long T, long cols, long ld) {
   return r == CUDA_SUCCESS ? SB_OK : SB_ERR_DRIVER;
 }
 
-template <int D> constexpr int fa_fwd_smem() { return (D / 64) * PANEL_BYTES * 5 + 2 * PANEL_BYTES + 1024 + 256; }
+template <int D> constexpr int fa_fwd_smem() { return FaFwdCfg<D>::SMEM; }
 template <int D> constexpr int fa_dkdv_smem() { return (D / 64) * PANEL_BYTES * (2 + 2 * (D == 64 ? 2 : 1)) + 4 * PANEL_BYTES + 1024 + 256; }
 template <int D> constexpr int fa_dq_smem() { return (D / 64) * PANEL_BYTES * 4 + 2 * PANEL_BYTES + 1024 + 256; }
 
@@ -957,10 +1021,10 @@ SB_API int sb200_fa_bwd_strided(const void* q, const void* k, const void* v, con
       if (e != cudaSuccess) return (int)e;
       set = true;
     }
-    fa_bwd_dkdv_kernel<64><<<dim3(tiles, Hkv, splits), FA_THREADS, fa_dkdv_smem<64>(), stream>>>(
+    fa_bwd_dkdv_kernel<64><<<dim3(tiles, Hkv, splits), FA_BWD_THREADS, fa_dkdv_smem<64>(), stream>>>(
         tmQ, tmK, tmV, tmdO, p, tiles, hps, dk_part, dv_part);
     SB_CHECK_LAUNCH();
-    fa_bwd_dq_kernel<64><<<dim3(tiles, Hq), FA_THREADS, fa_dq_smem<64>(), stream>>>(tmQ, tmK, tmV, tmdO, p);
+    fa_bwd_dq_kernel<64><<<dim3(tiles, Hq), FA_BWD_THREADS, fa_dq_smem<64>(), stream>>>(tmQ, tmK, tmV, tmdO, p);
   } else {
     static bool set = false;
     if (!set) {
@@ -970,10 +1034,10 @@ SB_API int sb200_fa_bwd_strided(const void* q, const void* k, const void* v, con
       if (e != cudaSuccess) return (int)e;
       set = true;
     }
-    fa_bwd_dkdv_kernel<128><<<dim3(tiles, Hkv, splits), FA_THREADS, fa_dkdv_smem<128>(), stream>>>(
+    fa_bwd_dkdv_kernel<128><<<dim3(tiles, Hkv, splits), FA_BWD_THREADS, fa_dkdv_smem<128>(), stream>>>(
         tmQ, tmK, tmV, tmdO, p, tiles, hps, dk_part, dv_part);
     SB_CHECK_LAUNCH();
-    fa_bwd_dq_kernel<128><<<dim3(tiles, Hq), FA_THREADS, fa_dq_smem<128>(), stream>>>(tmQ, tmK, tmV, tmdO, p);
+    fa_bwd_dq_kernel<128><<<dim3(tiles, Hq), FA_BWD_THREADS, fa_dq_smem<128>(), stream>>>(tmQ, tmK, tmV, tmdO, p);
   }
   SB_CHECK_LAUNCH();
   if (splits > 1) {
