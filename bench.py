@@ -216,13 +216,43 @@ def run_ours(args: argparse.Namespace) -> None:
         tokens = MICRO_BATCH * seq * world
         h2d = MICRO_BATCH * (seq + 1) * 8
         print(json.dumps(result_line(args, world, tokens, dev_ms, e2e_ms, clocks, launches, h2d, 4, "ours")), flush=True)
-    if world > 1:
-        dist.barrier()
-        dist.destroy_process_group()
+    shutdown(model, world)
+
+
+def shutdown(model, world: int) -> None:
+    """Release captured graphs (they pin NCCL resources) and tear the process group down.  The result line is out
+    already; should the teardown block on a communicator that a graph still references, leave after a grace period
+    instead of holding the launcher until the process-group timeout."""
+    import gc
+    import threading
+
+    import torch
+    import torch.distributed as dist
+
+    sys.stdout.flush()
+    if world <= 1 or not dist.is_initialized():
+        return
+    dist.barrier()
+    torch.cuda.synchronize()
+    if model is not None and hasattr(model, "release_cuda_graph"):
+        model.release_cuda_graph()
+    gc.collect()
+    torch.cuda.synchronize()
+    timer = threading.Timer(20.0, lambda: os._exit(0))
+    timer.daemon = True
+    timer.start()
+    dist.destroy_process_group()
+    timer.cancel()
 
 
 def main() -> None:
     args = parse_args()
+    # a stuck collective would otherwise block until the process-group timeout: dump every thread's stack and exit
+    watchdog = int(os.environ.get("SB200_BENCH_WATCHDOG_S", "900"))
+    if watchdog > 0:
+        import faulthandler
+
+        faulthandler.dump_traceback_later(watchdog, exit=True)
     if args.impl == "reference":
         sys.path.insert(0, str(ROOT))
         from baseline.reference_arm import run_reference

@@ -326,6 +326,15 @@ class ParallelModule(PipePartitionedModule, Generic[BaseLossInputGeneric, BaseDa
             for k, v in agg.items():
                 self._graph_metrics[k].copy_(torch.as_tensor(v, dtype=torch.float32, device=t.device))
 
+    def release_cuda_graph(self) -> None:
+        """Drop the captured training step and its static buffers (call before destroying process groups: a graph
+        that holds collectives keeps their communicators busy)."""
+        self._graph = None
+        self._graph_inputs = []
+        self._graph_loss = None
+        self._graph_metrics = None
+        self._graph_signature = None
+
     def _graphed_train_step(self, dataloader: Any, optimizer: Any, sync: Callable, loss_function: Callable,
                             metrics_aggregation_fn: Optional[Callable]) -> Optional[TrainStepOutput]:
         """One training step through the captured graph.  Returns None (with the batches it already drew kept in
