@@ -215,7 +215,10 @@ def run_ours(args: argparse.Namespace) -> None:
     if rank == 0:
         tokens = MICRO_BATCH * seq * world
         h2d = MICRO_BATCH * (seq + 1) * 8
-        print(json.dumps(result_line(args, world, tokens, dev_ms, e2e_ms, clocks, launches, h2d, 4, "ours")), flush=True)
+        line = result_line(args, world, tokens, dev_ms, e2e_ms, clocks, launches, h2d, 4, "ours")
+        line["config"]["data_parallel_exchange"] = optimizer.data_parallel_exchange
+        line["config"]["cuda_graph"] = bool(getattr(model, "_graph", None) is not None)
+        print(json.dumps(line), flush=True)
     shutdown(model, world)
 
 

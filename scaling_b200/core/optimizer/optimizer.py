@@ -126,6 +126,15 @@ class Optimizer(BaseOptimizer):
         )
 
     # ------------------------------------------------------------------ backward / step
+    @property
+    def data_parallel_exchange(self) -> str:
+        """How gradients and parameters cross the data-parallel group: "none", "nccl", "p2p" or "p2p+multicast"."""
+        if self.topology.config.data_parallel_size <= 1:
+            return "none"
+        if self._fused is None:
+            return "nccl"
+        return "p2p+multicast" if self._fused.use_multicast else "p2p"
+
     def zero_grad(self, set_to_none: bool = True) -> None:
         for g in self.parameter_groups:
             g.zero_grad(set_to_none)
@@ -417,7 +426,11 @@ def _try_fused_zero(optimizer: "Optimizer") -> Any:
     try:
         from ...parallel.fused_zero import FusedZero
 
-        return FusedZero.create(optimizer)
+        fused = FusedZero.create(optimizer)
+        if fused is not None:
+            logger.info("ZeRO data-parallel exchange: peer-memory kernels over NVLink "
+                        f"(multicast stores: {'yes' if fused.use_multicast else 'no'})")
+        return fused
     except Exception as e:  # pragma: no cover - depends on the machine
         logger.warning(f"fused NVLink ZeRO path unavailable ({type(e).__name__}: {e}); using NCCL collectives")
         return None

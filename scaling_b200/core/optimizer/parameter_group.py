@@ -126,6 +126,23 @@ class OptimizerParamGroup:
         self.weight_decay = wd
         self.initialized = True
 
+    def rehome(self, flat_param: torch.Tensor, flat_grad: torch.Tensor) -> None:
+        """Move the flat parameter and gradient buffers into caller-provided storage of the same size and dtype
+        (e.g. symmetric memory that peers can address); parameters and their ``.grad`` become views of it."""
+        assert self.initialized
+        assert flat_param.shape == self.flat_param.shape and flat_param.dtype == self.flat_param.dtype
+        assert flat_grad.shape == self.flat_grad.shape and flat_grad.dtype == self.flat_grad.dtype
+        with torch.no_grad():
+            flat_param.copy_(self.flat_param)
+            flat_grad.copy_(self.flat_grad)
+            for p, off in zip(self.parameters_original, self.offsets):
+                p.data = flat_param[off:off + p.numel()].view(p.shape)
+                p.grad = flat_grad[off:off + p.numel()].view(p.shape)
+        self.flat_param, self.flat_grad = flat_param, flat_grad
+        if self.dtype == torch.float32:
+            lo, hi = self.owned_range
+            self.master = self.flat_param[lo:hi]
+
     @property
     def owned_range(self) -> tuple[int, int]:
         """Element range of the flat buffer whose optimizer state lives on this rank."""

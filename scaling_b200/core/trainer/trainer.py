@@ -215,4 +215,9 @@ class BaseTrainer(Generic[BaseContextGeneric, ParallelModuleGeneric]):
                 metrics = self.log_metrics(train_out, eval_out)
                 if return_metrics:
                     collected.append(metrics)
+        # a captured training step holds communicators and static buffers; training is over, let them go so that
+        # process groups can be destroyed
+        release = getattr(self.parallel_module, "release_cuda_graph", None)
+        if release is not None:
+            release()
         return collected if return_metrics else None

@@ -77,6 +77,10 @@ _SIGS = {
     "sb200_sumsq": [c_void_p, c_long, c_void_p, c_void_p, c_void_p, c_float, c_int, c_int, c_void_p],
     "sb200_embedding_fwd": [c_void_p, c_void_p, c_void_p, c_long, c_int, c_long, c_long, c_int, c_void_p],
     "sb200_embedding_bwd": [c_void_p, c_void_p, c_void_p, c_void_p, c_long, c_int, c_long, c_long, c_int, c_int, c_void_p],
+    "sb200_p2p_max_ranks": [],
+    "sb200_p2p_barrier": [c_void_p, c_void_p, c_int, c_int, c_void_p, ctypes.c_double, c_void_p],
+    "sb200_p2p_reduce_scatter": [c_void_p, c_void_p, c_long, c_long, c_int, c_int, c_int, c_void_p],
+    "sb200_p2p_all_gather": [c_void_p, c_void_p, c_void_p, c_long, c_long, c_int, c_int, c_int, c_void_p],
     "sb200_gemm_ws": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_long, c_long, c_long, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_long, c_void_p, c_void_p],
     "sb200_gemm": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_long, c_long, c_long, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
 }
@@ -123,7 +127,7 @@ class _Counting:
         return hasattr(self._handle, name)
 
 
-_NO_LAUNCH = {"sb200_colsum_splits", "sb200_norm_bwd_partial_rows", "sb200_norm_bwd_partial_rows_h", "sb200_sumsq_max_partials",
+_NO_LAUNCH = {"sb200_p2p_max_ranks", "sb200_colsum_splits", "sb200_norm_bwd_partial_rows", "sb200_norm_bwd_partial_rows_h", "sb200_sumsq_max_partials",
               "sb200_bind_device", "sb200_fa_last_driver_error"}
 
 

@@ -11,7 +11,7 @@ from typing import Any, Callable
 import torch
 import torch.multiprocessing as mp
 
-PROCESS_TIMEOUT = 180
+PROCESS_TIMEOUT = 120
 
 
 def find_free_port() -> int:
@@ -29,8 +29,14 @@ def _worker(rank: int, world_size: int, port: int, fn: Callable, kwargs: dict, r
     except BaseException:  # noqa: BLE001 - report everything to the parent
         results[rank] = ("error", traceback.format_exc())
     finally:
+        import gc
+
         import torch.distributed as dist
 
+        # captured CUDA graphs pin communicators: collect the finished run's objects before the teardown
+        gc.collect()
+        if torch.cuda.is_available() and device == "cuda":
+            torch.cuda.synchronize()
         if dist.is_initialized():
             try:
                 dist.destroy_process_group()
