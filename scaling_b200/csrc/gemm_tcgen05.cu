@@ -73,7 +73,8 @@ static_assert(GemmCfg<256, false>::SMEM_BYTES <= 232448 && GemmCfg<256, true>::S
 // instructions of erff, which matters because the epilogue shares the SM with the MMA issue.
 __device__ __forceinline__ float gelu_erf(float x) {
   const float z = fabsf(x) * 0.70710678118654752f;
-  const float t = __frcp_rn(fmaf(0.3275911f, z, 1.f));
+  float t;  // 1 / (1 + p z): the approximate reciprocal is one MUFU instruction, its error (1 ulp) is irrelevant here
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(t) : "f"(fmaf(0.3275911f, z, 1.f)));
   float poly = fmaf(1.061405429f, t, -1.453152027f);
   poly = fmaf(poly, t, 1.421413741f);
   poly = fmaf(poly, t, -0.284496736f);

@@ -14,11 +14,30 @@ namespace {
 
 // ------------------------------------------------------------------- AdamW
 // control[0] = gradient multiplier (1/loss_scale * clip coefficient), control[1] != 0 -> skip step.
+template <typename T> struct Vec4 {};  // four consecutive elements as one load / store
+template <> struct Vec4<float> { using type = float4; };
+template <> struct Vec4<__nv_bfloat16> { using type = uint2; };
+template <> struct Vec4<__half> { using type = uint2; };
+
+template <typename T> __device__ __forceinline__ void load4(const T* p, float* v) {
+  typename Vec4<T>::type raw = *reinterpret_cast<const typename Vec4<T>::type*>(p);
+  const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+  for (int k = 0; k < 4; ++k) v[k] = sb::to_f(e[k]);
+}
+template <typename T> __device__ __forceinline__ void store4(T* p, const float* v) {
+  typename Vec4<T>::type raw;
+  T* e = reinterpret_cast<T*>(&raw);
+#pragma unroll
+  for (int k = 0; k < 4; ++k) e[k] = sb::from_f<T>(v[k]);
+  *reinterpret_cast<typename Vec4<T>::type*>(p) = raw;
+}
+
 template <typename G, typename P>
 __global__ void adamw_kernel(float* __restrict__ p, float* __restrict__ m, float* __restrict__ v,
                              const G* __restrict__ g, P* __restrict__ p_lp, long n, float lr, float beta1, float beta2,
                              float eps, float wd, float bc1, float bc2, const float* __restrict__ control,
-                             const float* __restrict__ hyper) {
+                             const float* __restrict__ hyper, int vec_ok) {
   // hyper (optional, device memory): [learning rate, 1 - beta1^t, 1 - beta2^t] - lets a captured CUDA graph
   // be replayed with new values
   if (hyper) {
@@ -33,14 +52,37 @@ __global__ void adamw_kernel(float* __restrict__ p, float* __restrict__ m, float
   }
   const float inv_bc1 = 1.f / bc1;
   const float inv_sqrt_bc2 = rsqrtf(bc2);
-  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x) {
-    float gr = sb::to_f(g[i]) * gmul;
-    float pi = p[i];
-    float mi = m[i] * beta1 + (1.f - beta1) * gr;
-    float vi = v[i] * beta2 + (1.f - beta2) * gr * gr;
-    pi *= (1.f - lr * wd);
-    float denom = sqrtf(vi) * inv_sqrt_bc2 + eps;
-    pi -= lr * inv_bc1 * mi / denom;
+  const float decay = 1.f - lr * wd;
+  const float step = lr * inv_bc1;
+  auto update = [&](float& pi, float& mi, float& vi, float gr) {
+    gr *= gmul;
+    mi = mi * beta1 + (1.f - beta1) * gr;
+    vi = vi * beta2 + (1.f - beta2) * gr * gr;
+    pi *= decay;
+    pi -= step * mi / (sqrtf(vi) * inv_sqrt_bc2 + eps);
+  };
+  const long tid = blockIdx.x * (long)blockDim.x + threadIdx.x, stride = (long)gridDim.x * blockDim.x;
+  long done = 0;
+  if (vec_ok) {  // all pointers 16-byte aligned: four elements per thread and step
+    const long n4 = n / 4;
+    for (long i = tid; i < n4; i += stride) {
+      float pv[4], mv[4], vv[4], gv[4];
+      load4(p + i * 4, pv);
+      load4(m + i * 4, mv);
+      load4(v + i * 4, vv);
+      load4(g + i * 4, gv);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) update(pv[k], mv[k], vv[k], gv[k]);
+      store4(p + i * 4, pv);
+      store4(m + i * 4, mv);
+      store4(v + i * 4, vv);
+      if (p_lp) store4(p_lp + i * 4, pv);
+    }
+    done = n4 * 4;
+  }
+  for (long i = done + tid; i < n; i += stride) {
+    float pi = p[i], mi = m[i], vi = v[i];
+    update(pi, mi, vi, sb::to_f(g[i]));
     p[i] = pi;
     m[i] = mi;
     v[i] = vi;
@@ -120,12 +162,16 @@ SB_API int sb200_adamw(float* p, float* m, float* v, const void* g, void* p_lp, 
                        float beta2, float eps, float wd, float bc1, float bc2, const float* control,
                        const float* hyper, int g_dtype, int lp_dtype, cudaStream_t stream) {
   if (n <= 0) return SB_OK;
-  long b = (n + 255) / 256;
+  long b = (n / 4 + 255) / 256;
   if (b > 148 * 8) b = 148 * 8;
+  if (b < 1) b = 1;
+  const uintptr_t all = reinterpret_cast<uintptr_t>(p) | reinterpret_cast<uintptr_t>(m) | reinterpret_cast<uintptr_t>(v) |
+                        reinterpret_cast<uintptr_t>(g) | reinterpret_cast<uintptr_t>(p_lp);
+  const int vec_ok = (all & 15) == 0;
   SB_DISPATCH_DTYPE(g_dtype, G, {
     SB_DISPATCH_DTYPE(lp_dtype, P, {
       adamw_kernel<G, P><<<(int)b, 256, 0, stream>>>(p, m, v, (const G*)g, (P*)p_lp, n, lr, beta1, beta2, eps, wd, bc1,
-                                                     bc2, control, hyper);
+                                                     bc2, control, hyper, vec_ok);
     });
   });
   SB_CHECK_LAUNCH();
