@@ -22,6 +22,7 @@ import numpy as np
 import torch
 import torch.distributed as dist
 
+from ...core.data.blended_dataset import BaseBlendedDataset
 from ...core.data import BaseDataset, BaseDatasetItem, FileDataset, MemoryMapDataset, MemoryMapDatasetBuilder, broadcast_data
 from ...parallel.topology import Topology
 from .text_dataset_batch import TextDatasetBatch, TextDatasetBatchBeforeSync
@@ -240,3 +241,7 @@ class SyntheticTextDataset(BaseDataset[TextDatasetItem, TextDatasetBatchBeforeSy
         )
 
     sync_batch_to_model_parallel = staticmethod(TextDataset.sync_batch_to_model_parallel)
+
+
+class TextBlendedDataset(BaseBlendedDataset[TextDataset]):
+    """Several ``TextDataset``s blended by weight (src/scaling/transformer/data/text_dataset.py:455-469)."""

@@ -1,0 +1,172 @@
+"""Datasets, blending, tokenizer and sampling helpers (CPU)."""
+
+import json
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+from scaling_b200.core.data import BlendedDatasetConfig, MemoryMapDatasetBuilder
+from scaling_b200.core.data.blended_dataset import (build_blend_index, weights_by_num_docs,
+                                                    weights_examples_proportional)
+from scaling_b200.transformer.data import (EmbeddingDataset, FinetuningChatDataset, FinetuningTextBlendedDataset,
+                                           FinetuningTextDataset, TextBlendedDataset, TextDataset)
+from scaling_b200.transformer.inference import sample_argmax, sample_temperature, top_k_transform, top_p_transform
+from scaling_b200.transformer.tokenizer import Tokenizer, load_tokenizers
+
+WORDS = ["the", "cat", "sat", "on", "mat", "a", "dog", "ran", "far", "query", "doc", "good", "bad", "find", ":"]
+
+
+@pytest.fixture()
+def tok() -> Tokenizer:
+    return Tokenizer.from_words(WORDS)
+
+
+def _oracle(targets):
+    t = np.array(targets)
+    s = np.zeros(len(t), dtype=np.int64)
+    out = []
+    while (s < t).all():
+        i = int((s / t).argmin())
+        out.append((i, int(s[i])))
+        s[i] += 1
+    return out
+
+
+@pytest.mark.parametrize("targets", [[5, 3, 9], [1, 1], [7], [100, 1, 33, 33], [2, 4, 8, 16, 32]])
+def test_blend_index_matches_greedy_oracle(tmp_path: Path, targets):
+    n = build_blend_index(targets, str(tmp_path / "idx"))
+    pairs = np.fromfile(tmp_path / "idx.bin", dtype=np.int64).reshape(-1, 2)
+    assert n == len(pairs)
+    assert [tuple(p) for p in pairs.tolist()] == _oracle(targets)
+    meta = json.loads((tmp_path / "idx.meta.json").read_text())
+    assert meta == {"dtype": "int64", "shape": [n, 2]}
+
+
+def test_blend_weights():
+    w = weights_by_num_docs([100, 10], alpha=1.0)
+    assert np.allclose(w, [0.5, 0.5])  # alpha 1 keeps the natural proportions: equal multipliers
+    w0 = weights_by_num_docs([100, 10], alpha=0.0)
+    assert w0[1] / w0[0] == pytest.approx(10.0)  # alpha 0: equal sampling -> the small set is boosted 10x
+    e = weights_examples_proportional([100, 10], temperature=1.0, maximum=None)
+    assert np.allclose(e, [0.5, 0.5])
+    capped = weights_examples_proportional([100, 10], temperature=1.0, maximum=10)
+    assert capped[1] / capped[0] == pytest.approx(10.0)
+    with pytest.raises(AssertionError):
+        weights_examples_proportional([1, 2], temperature=0)
+
+
+def _text_map(prefix: Path, n_docs: int, seed: int) -> None:
+    rng = np.random.default_rng(seed)
+    with MemoryMapDatasetBuilder(prefix_path=prefix) as b:
+        for _ in range(n_docs):
+            b.add(np_array=np.concatenate([rng.integers(1, 50, size=rng.integers(3, 20)), [0]]).astype(np.int32))
+
+
+def test_text_blended_dataset(tmp_path: Path):
+    _text_map(tmp_path / "a", 60, 1)
+    _text_map(tmp_path / "b", 15, 2)
+    sets = [TextDataset(data_prefix=tmp_path / n, sequence_length=16, seed=3) for n in ("a", "b")]
+    cfg = BlendedDatasetConfig(weight_by_num_documents=True, weighted_sampler_alpha=0.5, cache_directory=tmp_path / "cache")
+    blend = TextBlendedDataset(seed=3, config=cfg, datasets=sets)
+    assert len(blend) > 0
+    counts = np.bincount(np.asarray(blend.dataset_indices)[:, 0], minlength=2)
+    assert counts[0] > 0 and counts[1] > 0
+    item = blend[0]
+    batch = blend.collate([blend[i] for i in range(4)])
+    assert batch.token_ids.shape == (4, 17)
+    assert torch.equal(item.token_ids, sets[int(blend.dataset_indices[0][0])][int(blend.dataset_indices[0][1])].token_ids)
+    # a second instance finds the cached index
+    again = TextBlendedDataset(seed=3, config=cfg, datasets=sets)
+    assert np.array_equal(np.asarray(again.dataset_indices), np.asarray(blend.dataset_indices))
+    single = TextBlendedDataset(seed=3, config=cfg, datasets=sets[:1])
+    assert len(single) == len(sets[0])
+
+
+def test_finetuning_text_dataset_json_and_memory_map(tmp_path: Path, tok: Tokenizer):
+    records = [{"prompt": "the cat sat", "completion": "on the mat"}, {"prompt": "a dog", "completion": "ran far"}]
+    (tmp_path / "ft.json").write_text(json.dumps(records))
+    ds = FinetuningTextDataset(tmp_path / "ft.json", sequence_length=12, seed=1, softprompt_n_tokens=2, tokenizer=tok,
+                               tokenizer_no_prefix_space=tok, shuffle=False)
+    item = ds[0]
+    p, c = tok.encode("the cat sat"), tok.encode("on the mat")
+    assert item.input_token_ids.tolist()[:2 + len(p) + len(c)] == [0, 0] + p + c
+    # loss on the completion and on exactly one end-of-text token
+    n_prompt = 2 + len(p)
+    assert item.loss_weights.tolist() == [0.0] * (n_prompt - 1) + [1.0] * (len(c) + 1) + [0.0] * (12 - n_prompt - len(c))
+    assert item.target_token_ids[n_prompt + len(c) - 1].item() == tok.eos_token_id
+    batch = ds.collate([ds[0], ds[1]])
+    assert batch.input_token_ids.shape == (2, 12) and batch.input_images is None
+    assert FinetuningTextDataset.sync_batch_to_model_parallel(None, batch) is batch
+
+    (tmp_path / "ft.jsonl").write_text("\n".join(json.dumps(r) for r in records) + "\n")
+    FinetuningTextDataset.convert_jsonl(tmp_path / "ft.jsonl", tok, tok, tmp_path / "ftmap")
+    mm = FinetuningTextDataset(tmp_path / "ftmap", sequence_length=12, seed=1, softprompt_n_tokens=2, tokenizer=tok,
+                               tokenizer_no_prefix_space=tok, memory_map_dataset=True, shuffle=False)
+    assert torch.equal(mm[0].input_token_ids, item.input_token_ids)
+    assert torch.equal(mm[0].loss_weights, item.loss_weights)
+    cfg = BlendedDatasetConfig(cache_directory=tmp_path / "c")
+    assert len(FinetuningTextBlendedDataset(seed=1, config=cfg, datasets=[ds])) == 2
+
+
+def test_finetuning_chat_dataset(tmp_path: Path, tok: Tokenizer):
+    conv = [{"type": "text", "content": "the cat", "has_loss": False}, {"type": "text", "content": "sat on", "has_loss": True},
+            {"type": "text", "content": "a mat", "has_loss": False}]
+    (tmp_path / "chat.jsonl").write_text(json.dumps(conv) + "\n")
+    ds = FinetuningChatDataset(tmp_path / "chat.jsonl", sequence_length=8, seed=1, softprompt_n_tokens=0, tokenizer=tok,
+                               tokenizer_no_prefix_space=tok)
+    item = ds[0]
+    ids = tok.encode("the cat") + tok.encode("sat on") + tok.encode("a mat")
+    assert item.input_token_ids.tolist() == ids[:-1] + [tok.padding_token_id] * (8 - len(ids) + 1)
+    assert item.target_token_ids.tolist()[:len(ids) - 1] == ids[1:]
+    assert item.loss_weights.tolist() == [0, 1, 1, 0, 0, 0, 0, 0]  # targets "sat", "on" carry the loss
+    with pytest.raises(NotImplementedError):
+        (tmp_path / "bad.jsonl").write_text(json.dumps([{"type": "audio", "content": "x"}]) + "\n")
+        FinetuningChatDataset(tmp_path / "bad.jsonl", 8, 1, 0, tok, tok)
+
+
+def test_embedding_dataset(tmp_path: Path, tok: Tokenizer):
+    rec = {"query": ["find :", "cat"], "positives": [["doc :", "the cat sat"]], "negatives": [["doc :", "a dog ran"]]}
+    (tmp_path / "emb.jsonl").write_text(json.dumps(rec) + "\n")
+    ds = EmbeddingDataset(tmp_path / "emb.jsonl", sequence_length=8, seed=1, tokenizer=tok, number_of_hard_negatives=1)
+    item = ds[0]
+    assert item.input_token_ids.shape == (3, 8)
+    q = tok.encode("find : cat")
+    assert item.input_token_ids[0].tolist()[:len(q)] == q
+    assert item.loss_weights[0].tolist() == [0, 0, 1] + [0] * 5  # instruction and padding are not pooled
+    batch = ds.collate([item, item])
+    assert batch.input_token_ids.shape == (6, 8)
+    no_instr = EmbeddingDataset(tmp_path / "emb.jsonl", 8, 1, tok, 1, use_instruction=False)
+    assert no_instr[0].input_token_ids[0].tolist()[:1] == tok.encode("cat")
+    EmbeddingDataset.jsonl_to_embedding_mmap(tmp_path / "emb.jsonl", tok, tmp_path / "embmap")
+    mm = EmbeddingDataset(tmp_path / "embmap", 8, 1, tok, 1, memory_map_dataset=True)
+    assert torch.equal(mm[0].input_token_ids, item.input_token_ids)
+    assert torch.equal(mm[0].loss_weights, item.loss_weights)
+    with pytest.raises(NotImplementedError):
+        EmbeddingDataset(tmp_path / "emb.jsonl", 8, 1, tok, 2)
+
+
+def test_tokenizer_variants(tmp_path: Path, tok: Tokenizer):
+    assert tok.decode(tok.encode("the cat")) == "the cat"
+    assert tok.eos_token_id == tok.padding_token_id == 0
+    definition = json.loads(tok.tokenizer.to_str())
+    definition["pre_tokenizer"] = {"type": "ByteLevel", "add_prefix_space": True, "trim_offsets": True, "use_regex": True}
+    (tmp_path / "vocab.json").write_text(json.dumps(definition))
+    plain, no_space = load_tokenizers(tmp_path / "vocab.json")
+    assert plain is not no_space
+    (tmp_path / "plain.json").write_text(tok.tokenizer.to_str())
+    a, b = load_tokenizers(tmp_path / "plain.json")
+    assert a is b  # nothing to switch off
+
+
+def test_samplers():
+    torch.manual_seed(0)
+    logits = torch.tensor([[[0.0, 1.0, 5.0, 2.0], [3.0, 0.5, 0.1, 0.2]]])
+    assert sample_argmax(logits).tolist() == [0]
+    k = top_k_transform(logits, k=2)
+    assert torch.isinf(k[0, 0, 0]) and torch.isinf(k[0, 0, 1]) and not torch.isinf(k[0, 0, 2])
+    p = top_p_transform(logits, threshold=0.5)
+    assert not torch.isinf(p[0, 0, 2]) and torch.isinf(p[0, 0, 0])  # the top token alone carries > 50 %
+    draws = torch.stack([sample_temperature(logits, 0.01) for _ in range(20)])
+    assert (draws == 0).all()  # near-zero temperature = argmax
