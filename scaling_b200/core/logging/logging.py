@@ -102,12 +102,13 @@ class Logger:
         self._console.setFormatter(ColorFormatter(name, use_color=sys.stdout.isatty()))
 
     # ---- metrics / config
-    def log_metrics(self, metrics: dict[str, Any], step: int) -> None:
+    def log_metrics(self, metrics: dict[str, Any], step: int, to_info: bool = True, to_wandb: bool = True) -> None:
         if not self.config.is_rank_in_metrics_ranks(self.global_rank) and self.global_rank is not None:
             return
         plain = {k: (v.item() if hasattr(v, "item") else v) for k, v in metrics.items()}
-        self.info(json.dumps({"step": step, **plain}, default=str))
-        if self._wandb is not None:
+        if to_info:
+            self.info(json.dumps({"step": step, **plain}, default=str))
+        if self._wandb is not None and to_wandb:
             self._wandb.log(plain, step=step)
         if self._tb is not None:
             for k, v in plain.items():
@@ -151,8 +152,8 @@ class DeterminedLogger(Logger):
         self.determined_profiler = determined_profiler
         super().__init__(config, name=name, global_rank=global_rank, tensorboard_ranks=tensorboard_ranks)
 
-    def log_metrics(self, metrics: dict[str, Any], step: int) -> None:
-        super().log_metrics(metrics, step)
+    def log_metrics(self, metrics: dict[str, Any], step: int, to_info: bool = True, to_wandb: bool = True) -> None:
+        super().log_metrics(metrics, step, to_info=to_info, to_wandb=to_wandb)
         if self.config.is_rank_in_determined_metrics_ranks(self.global_rank):
             train = {k: v for k, v in metrics.items() if not k.startswith("evaluation")}
             evaluation = {k: v for k, v in metrics.items() if k.startswith("evaluation")}

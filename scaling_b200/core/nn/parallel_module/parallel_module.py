@@ -266,6 +266,8 @@ class ParallelModule(PipePartitionedModule, Generic[BaseLossInputGeneric, BaseDa
         that reach the device without a tensor-parallel broadcast, no dropout, no loss scaling, profiler idle."""
         if not self.enable_cuda_graph or self._graph_failed:
             return False
+        if getattr(self, "_tensor_statistics_active", False):  # hooks of a statistics trace need the eager step
+            return False
         t = self.topology
         if t.device.type != "cuda" or t.config.pipe_parallel_size != 1 or t.config.model_parallel_size != 1:
             return False

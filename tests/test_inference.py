@@ -1,0 +1,72 @@
+"""TransformerInferenceModule on CPU: logits, cached vs uncached generation, checkpoint round trip, recorder."""
+
+from pathlib import Path
+
+import torch
+import yaml
+
+from scaling_b200.core.nn.parallel_module.inference_module import RecorderSetting
+from scaling_b200.transformer.context.config import TransformerArchitectureConfig
+from scaling_b200.transformer.inference import TransformerInferenceModule, sample_argmax
+from scaling_b200.transformer.model.model import get_transformer_layer_specs
+from scaling_b200.transformer.tokenizer import Tokenizer
+
+ARCH = {"vocab_size": 32, "hidden_size": 32, "num_layers": 2, "num_attention_heads": 4, "sequence_length": 64,
+        "precision": "float32", "masked_softmax": {"kernel": "torch"}, "weight_tying": False,
+        "relative_position_embedding_type": "rotary"}
+
+
+def _module(tokenizer=None) -> TransformerInferenceModule:
+    torch.manual_seed(0)
+    arch = TransformerArchitectureConfig.from_dict(dict(ARCH))
+    return TransformerInferenceModule(get_transformer_layer_specs(architecture_config=arch), devices=("cpu",),
+                                      tokenizer=tokenizer)
+
+
+def test_logits_and_generate_cache_agrees_with_recompute():
+    m = _module()
+    prompt = [3, 7, 1, 9, 4]
+    logits = m.logits(input_tokens=prompt)
+    assert logits.shape == (5, 32) and torch.isfinite(logits).all()
+    cached = m.generate(max_tokens=6, input_tokens=prompt, stop_tokens=[31], use_cache=True)
+    plain = m.generate(max_tokens=6, input_tokens=prompt, stop_tokens=[31], use_cache=False)
+    assert cached.completion_tokens == plain.completion_tokens
+    assert len(cached.completion_tokens) <= 6
+    assert cached.completion_logits.shape == (len(cached.completion_tokens), 32)
+    assert torch.allclose(cached.completion_logits, plain.completion_logits, atol=1e-4)
+    # greedy decoding follows the argmax of the returned logits
+    assert cached.completion_tokens == cached.completion_logits.argmax(-1).tolist()
+
+
+def test_generate_stops_at_stop_token_and_decodes_text():
+    tok = Tokenizer.from_words([f"w{i}" for i in range(30)])
+    m = _module(tok)
+    first = m.generate(max_tokens=1, input_text="w1 w2 w3").completion_tokens[0]
+    out = m.generate(max_tokens=8, input_text="w1 w2 w3", stop_tokens=[first])
+    assert out.completion_tokens == [first]
+    assert isinstance(out.completion_text, str)
+    assert sample_argmax(torch.zeros(1, 2, 4)).shape == (1,)
+
+
+def test_hidden_state_recorder():
+    m = _module()
+    logits, record = m.logits_with_hidden_state_recorder(input_tokens=[1, 2, 3],
+                                                         recorder_settings_per_layer={1: RecorderSetting()})
+    assert logits.shape == (3, 32)
+    assert list(record.keys()) == [1] and len(record[1]) > 0
+
+
+def test_from_checkpoint_round_trip(tmp_path: Path):
+    m = _module()
+    m.save_checkpoint(tmp_path) if hasattr(m, "save_checkpoint") else None
+    tok = Tokenizer.from_words([f"w{i}" for i in range(30)])
+    (tmp_path / "vocab.json").write_text(tok.tokenizer.to_str())
+    (tmp_path / "config.yml").write_text(yaml.safe_dump({"transformer_architecture": dict(ARCH)}))
+    if not any(tmp_path.glob("model_state_layer_*")):
+        import pytest
+
+        pytest.skip("inference modules cannot write checkpoints")
+    loaded = TransformerInferenceModule.from_checkpoint(tmp_path, devices=("cpu",))
+    a, b = m.logits(input_tokens=[5, 6, 7]), loaded.logits(input_tokens=[5, 6, 7])
+    assert torch.allclose(a, b, atol=1e-6)
+    assert loaded.tokenizer is not None
