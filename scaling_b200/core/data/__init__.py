@@ -7,8 +7,10 @@ from .dataloader import DataLoader, RandomSampler
 from .file_dataset import FileDataset
 from .file_handles import FileHandle, RetryableException
 from .memory_map import MemoryMapDataset, MemoryMapDatasetBuilder
+from .pb_memory_map import PbMemoryMap, PbMemoryMapBuilder, PromptImageLocation, TextImageExample
 
 __all__ = ["BaseBlendedDataset", "BlendedDatasetConfig", "weights_by_num_docs", "weights_examples_proportional",
            "BaseDataset", "BaseDatasetBatch", "BaseDatasetItem", "BaseLayerIO", "DataLoader", "FileDataset",
-           "FileHandle", "MemoryMapDataset", "MemoryMapDatasetBuilder", "RandomSampler", "RetryableException",
+           "FileHandle", "MemoryMapDataset", "MemoryMapDatasetBuilder", "PbMemoryMap", "PbMemoryMapBuilder", "PromptImageLocation",
+           "TextImageExample", "RandomSampler", "RetryableException",
            "broadcast_data"]

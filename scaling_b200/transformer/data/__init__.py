@@ -3,7 +3,8 @@ from .embedding_dataset import EmbeddingBlendedDataset, EmbeddingDataset, Embedd
 from .finetuning_chat_dataset import FinetuningChatBlendedDataset, FinetuningChatDataset
 from .finetuning_text_dataset import FinetuningTextBlendedDataset, FinetuningTextDataset
 from .inference_settings import Control, InferenceSettings, InferenceSuppressionParameters
-from .text_dataset import SyntheticTextDataset, TextBlendedDataset, TextDataset, TextDatasetItem, pack_windows
+from .text_dataset import LegacyBlendedDataset, SyntheticTextDataset, TextBlendedDataset, TextDataset, TextDatasetItem, pack_windows
+from .text_image_dataset import TextImageBlendedDataset, TextImageDataset
 from .text_dataset_batch import TextDatasetBatch, TextDatasetBatchBeforeSync
 from .utils import (
     add_cumulative_seq_lengths_padding,
@@ -16,6 +17,6 @@ from .utils import (
 
 __all__ = ["EmbeddingBlendedDataset", "EmbeddingDataset", "EmbeddingDatasetItem", "FinetuningChatBlendedDataset",
            "FinetuningChatDataset", "FinetuningTextBlendedDataset", "FinetuningTextDataset", "TextBlendedDataset",
-           "TextImageDatasetItem", "Control", "InferenceSettings", "InferenceSuppressionParameters", "SyntheticTextDataset", "TextDataset",
+           "TextImageDatasetItem", "TextImageBlendedDataset", "TextImageDataset", "LegacyBlendedDataset", "Control", "InferenceSettings", "InferenceSuppressionParameters", "SyntheticTextDataset", "TextDataset",
            "TextDatasetBatch", "TextDatasetBatchBeforeSync", "TextDatasetItem", "add_cumulative_seq_lengths_padding", "document_ranges_from_padded", "get_cumulative_seq_lengths_padded",
            "get_cumulative_seq_lengths", "get_position_ids", "pack_windows", "remove_cumulative_seq_lengths_padding"]

@@ -116,9 +116,9 @@ def blended_dataset_type(data_config: DataConfig) -> type[BaseBlendedDataset]:
         from .data.embedding_dataset import EmbeddingBlendedDataset
 
         return EmbeddingBlendedDataset
-    from .data.text_dataset import TextBlendedDataset
+    from .data.text_dataset import LegacyBlendedDataset, TextBlendedDataset
 
-    return TextBlendedDataset
+    return LegacyBlendedDataset if data_config.legacy_dataset else TextBlendedDataset
 
 
 def load_blended_datasets(config: TransformerConfig) -> tuple[BaseDataset, Optional[BaseDataset]]:

@@ -170,3 +170,57 @@ def test_samplers():
     assert not torch.isinf(p[0, 0, 2]) and torch.isinf(p[0, 0, 0])  # the top token alone carries > 50 %
     draws = torch.stack([sample_temperature(logits, 0.01) for _ in range(20)])
     assert (draws == 0).all()  # near-zero temperature = argmax
+
+
+def test_pb_memory_map_and_text_image_dataset(tmp_path: Path, tok: Tokenizer):
+    from io import BytesIO
+
+    from PIL import Image
+
+    from scaling_b200.core.data import PbMemoryMap, PbMemoryMapBuilder
+    from scaling_b200.transformer.data import TextImageDataset
+
+    img = tmp_path / "x.png"
+    Image.new("RGB", (40, 30), (200, 10, 10)).save(img)
+    b = PbMemoryMapBuilder(tmp_path / "ti", tokenizer=tok, tokenizer_no_prefix_space=tok, image_encoder_token_counts=4)
+    b.add([{"type": "image", "content": str(img)}, {"type": "text", "content": "the cat", "has_loss": False},
+           {"type": "text", "content": "sat on", "has_loss": True}])
+    b.add([{"type": "text", "content": "a dog ran far", "has_loss": True}])
+    b.finalize()
+    mm = PbMemoryMap(tmp_path / "ti")
+    assert len(mm) == 2
+    assert mm[0]["prompt_image_locations"] == [{"start_index": 0, "end_index": 4}]
+    assert mm[0]["input_token_list"] == [0, 0, 0, 0] + tok.encode("the cat") + tok.encode("sat")
+    assert Image.open(BytesIO(mm[0]["prompt_image_data"][0])).size == (40, 30)
+    with pytest.raises(ValueError):
+        PbMemoryMapBuilder(tmp_path / "ti")  # refuses to overwrite
+
+    ds = TextImageDataset(tmp_path / "ti", sequence_length=10, softprompt_n_tokens=1, shuffle=False, seed=5)
+    item = ds[0]
+    assert item.input_image_locations == [(1, 5)]  # shifted by the soft prompt
+    assert item.input_images[0].shape == (3, 384, 384)
+    assert item.loss_weights.tolist() == [0, 0, 0, 0, 0, 0, 1, 1, 0, 0]
+    batch = ds.collate([ds[0], ds[1]])
+    assert batch.input_images.shape == (1, 3, 384, 384) and batch.input_image_locations.tolist() == [[0, 1, 5]]
+
+
+def test_legacy_indexed_datasets(tmp_path: Path):
+    from scaling_b200.transformer.data.legacy_dataset.indexed_dataset import (infer_dataset_impl, make_builder,
+                                                                              make_dataset)
+
+    docs = [np.arange(5), np.arange(3) + 10, np.array([7])]
+    for impl in ("mmap", "cached"):
+        prefix = str(tmp_path / impl)
+        b = make_builder(prefix + ".bin", impl, vocab_size=1000)
+        for d in docs:
+            b.add_item(torch.tensor(d))
+            if impl == "mmap":
+                b.end_document()
+        b.finalize(prefix + ".idx")
+        assert infer_dataset_impl(prefix) == impl
+        ds = make_dataset(prefix)
+        assert [ds[i].tolist() for i in range(len(ds))] == [d.tolist() for d in docs]
+    ds = make_dataset(str(tmp_path / "mmap"))
+    assert ds.sizes.tolist() == [5, 3, 1] and ds.get(0, offset=1, length=2).tolist() == [1, 2]
+    text = TextDataset(data_prefix=tmp_path / "mmap", sequence_length=4, seed=1, legacy_dataset=True)
+    assert len(text) >= 1 and text[0].token_ids.numel() == 5
