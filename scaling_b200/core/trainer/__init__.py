@@ -1,4 +1,4 @@
-from .trainer import BaseTrainer
+from .trainer import BaseTrainer, DeterminedBaseTrainer
 from .trainer_config import TrainerConfig
 
-__all__ = ["BaseTrainer", "TrainerConfig"]
+__all__ = ["BaseTrainer", "DeterminedBaseTrainer", "TrainerConfig"]

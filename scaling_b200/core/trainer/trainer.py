@@ -150,6 +150,17 @@ class BaseTrainer(Generic[BaseContextGeneric, ParallelModuleGeneric]):
         logger.info(f"loaded checkpoint: {iteration_dir}")
         return True
 
+    # ------------------------------------------------------------------ extension points of the loop
+    def _before_train_step(self) -> None:
+        """Called at the top of every iteration of ``run_training``."""
+
+    def _after_train_step(self) -> None:
+        """Called right after the training step, before checkpointing and evaluation."""
+
+    def _saves_without_save_dir(self) -> bool:
+        """True when checkpoints have a destination other than ``config.save_dir``."""
+        return False
+
     # ------------------------------------------------------------------ steps
     def train_step(self) -> TrainStepOutput:
         out = self.parallel_module.train_step(
@@ -204,9 +215,12 @@ class BaseTrainer(Generic[BaseContextGeneric, ParallelModuleGeneric]):
             rec = self.tensor_statistics_recorder
             if rec is not None and self.context.iterations % rec.config.interval == 0:
                 recorder = rec.trace()
+            self._before_train_step()
             with recorder:
                 train_out = self.train_step()
-            if c.save_interval is not None and c.save_dir is not None and self.context.iterations % c.save_interval == 0:
+            self._after_train_step()
+            if (c.save_interval is not None and (c.save_dir is not None or self._saves_without_save_dir())
+                    and self.context.iterations % c.save_interval == 0):
                 self.save_checkpoint()
             eval_out = None
             if c.eval_interval is not None and self.context.iterations % c.eval_interval == 0:
@@ -221,3 +235,128 @@ class BaseTrainer(Generic[BaseContextGeneric, ParallelModuleGeneric]):
         if release is not None:
             release()
         return collected if return_metrics else None
+
+
+class DeterminedBaseTrainer(BaseTrainer[BaseContextGeneric, ParallelModuleGeneric]):
+    """Trainer for runs managed by Determined (src/scaling/core/trainer/trainer.py:336-560): checkpoints go through the
+    experiment's storage manager and are reported to the master, a paused / restarted trial resumes from the
+    master's latest checkpoint, and a preemption request is answered with a checkpoint and a clean exit.  Without a
+    Determined context on ``self.context`` it behaves exactly like ``BaseTrainer``."""
+
+    def __init__(self, *args: Any, **kwargs: Any) -> None:
+        super().__init__(*args, **kwargs)
+        if self._determined() and self.context.topology.config.global_rank == 0:
+            self.delete_preempted_checkpoints_determined()
+
+    def _determined(self) -> bool:
+        return bool(getattr(self.context, "_use_determined", False))
+
+    def _saves_without_save_dir(self) -> bool:
+        return self._determined()
+
+    def _before_train_step(self) -> None:
+        profiler = getattr(self.context, "determined_profiler", None)
+        if self._determined() and profiler is not None:
+            profiler.update_batch_idx(self.context.iterations)
+
+    def _after_train_step(self) -> None:
+        if not self._determined():
+            return
+        ctx = self.context.determined_context
+        assert ctx is not None
+        if ctx.preempt.should_preempt():
+            self.determined_save_checkpoint()
+            logger.info("exiting program after preemption.")
+            raise SystemExit(0)
+
+    def save_checkpoint(self, save_dir: Optional[Path] = None) -> Path:
+        if self._determined():
+            return self.determined_save_checkpoint()
+        return super().save_checkpoint(save_dir=save_dir)
+
+    def determined_save_checkpoint(self) -> Path:
+        """Rank 0 opens a storage path and broadcasts it; every rank writes its files there; files of nodes without
+        a shared file system are gathered before the checkpoint is reported."""
+        import uuid
+
+        from determined.common import storage
+
+        ctx = self.context.determined_context
+        assert ctx is not None, "tried to save Determined checkpoint but no determined context is given"
+        manager = ctx.checkpoint._storage_manager
+        shared = isinstance(manager, storage.SharedFSStorageManager)
+        if self.context.topology.config.global_rank == 0:
+            storage_id = str(uuid.uuid4())
+            with manager.store_path(storage_id) as path:
+                ctx.distributed.broadcast((storage_id, path))
+                BaseTrainer.save_checkpoint(self, save_dir=path)
+                resources = storage.StorageManager._list_directory(path)
+                gathered = [resources] if shared else ctx.distributed.gather(resources)
+            merged = {k: v for d in gathered for k, v in d.items()}
+            ctx.checkpoint._report_checkpoint(storage_id, merged, {"steps_completed": self.context.iterations})
+            if self.config.delete_past_optimizer_states:
+                self.delete_previous_optimizer_states_determined(storage_id)
+        else:
+            storage_id, path = ctx.distributed.broadcast(None)
+            BaseTrainer.save_checkpoint(self, save_dir=path)
+            if not shared:
+                local = storage.StorageManager._list_directory(path) if ctx.distributed.local_rank == 0 else {}
+                ctx.distributed.gather(local)
+            if ctx.distributed.local_rank == 0:
+                manager.post_store_path(str(path), storage_id)
+        return Path(path)
+
+    def load_checkpoint(self, load_dir: Optional[Path] = None, load_optimizer_states: bool = True,  # type: ignore[override]
+                        load_context: bool = True, **kwargs: Any) -> bool:
+        resumed = False
+        if self._determined():
+            import determined as det
+
+            info = det.get_cluster_info()
+            if info is not None and info.latest_checkpoint is not None:
+                resumed = True
+                with self.context.determined_context.checkpoint.restore_path(info.latest_checkpoint) as path:
+                    logger.info(f"Updating load checkpoint directory from {self.config.load_dir} to {path} "
+                                "according to determined setting")
+                    return super().load_checkpoint(load_dir=Path(path), load_optimizer_states=True, load_context=True,
+                                                   **kwargs)
+        return super().load_checkpoint(load_dir=load_dir, load_optimizer_states=load_optimizer_states or resumed,
+                                       load_context=load_context or resumed, **kwargs)
+
+    def delete_preempted_checkpoints_determined(self) -> None:
+        """Remove checkpoints that earlier preemptions of this trial left behind (all but the latest)."""
+        import os
+
+        if os.environ.get("DETERMINED_TEST", None) == "True":
+            return
+        try:
+            import determined as det
+            from determined.experimental import client
+
+            info = det.get_cluster_info()
+            if info is None:
+                return
+            trial = client.get_trial(info.trial.trial_id)
+            checkpoints = trial.list_checkpoints() if hasattr(trial, "list_checkpoints") else trial.get_checkpoints()
+            for ckpt in checkpoints:
+                if ckpt.uuid != info.latest_checkpoint:
+                    ckpt.delete()
+        except Exception as e:  # noqa: BLE001 - clean-up must never stop a run
+            logger.warning(f"could not delete preempted checkpoints: {e}")
+
+    def delete_previous_optimizer_states_determined(self, keep_storage_id: str) -> None:
+        """Drop optimizer-state files from this trial's older checkpoints (keeps the model weights)."""
+        try:
+            import determined as det
+            from determined.experimental import client
+
+            info = det.get_cluster_info()
+            if info is None:
+                return
+            trial = client.get_trial(info.trial.trial_id)
+            checkpoints = trial.list_checkpoints() if hasattr(trial, "list_checkpoints") else trial.get_checkpoints()
+            for ckpt in checkpoints:
+                if ckpt.uuid != keep_storage_id:
+                    ckpt.remove_files(["**/optimizer_state_*.pt"])
+        except Exception as e:  # noqa: BLE001
+            logger.warning(f"could not delete previous optimizer states: {e}")

@@ -1,7 +1,12 @@
 from .context import TransformerArchitectureConfig, TransformerConfig, TransformerContext
-from .data import SyntheticTextDataset, TextDataset, TextDatasetBatch, TextDatasetItem
+from .data import (EmbeddingBlendedDataset, EmbeddingDataset, FinetuningChatBlendedDataset, FinetuningChatDataset,
+                   FinetuningTextBlendedDataset, FinetuningTextDataset, LegacyBlendedDataset, SyntheticTextDataset,
+                   TextBlendedDataset, TextDataset, TextDatasetBatch, TextDatasetItem, TextImageBlendedDataset,
+                   TextImageDataset)
 from .model import TransformerLayerIO, TransformerParallelModule, init_model, init_optimizer
 
-__all__ = ["SyntheticTextDataset", "TextDataset", "TextDatasetBatch", "TextDatasetItem", "TransformerArchitectureConfig",
-           "TransformerConfig", "TransformerContext", "TransformerLayerIO", "TransformerParallelModule", "init_model",
-           "init_optimizer"]
+__all__ = ["EmbeddingBlendedDataset", "EmbeddingDataset", "FinetuningChatBlendedDataset", "FinetuningChatDataset",
+           "FinetuningTextBlendedDataset", "FinetuningTextDataset", "LegacyBlendedDataset", "SyntheticTextDataset",
+           "TextBlendedDataset", "TextDataset", "TextDatasetBatch", "TextDatasetItem", "TextImageBlendedDataset",
+           "TextImageDataset", "TransformerArchitectureConfig", "TransformerConfig", "TransformerContext",
+           "TransformerLayerIO", "TransformerParallelModule", "init_model", "init_optimizer"]
