@@ -227,6 +227,13 @@ class RowParallelLinear(_ParallelLinear):
             # nothing is reduced afterwards: the bias goes into the GEMM epilogue
             return self._matmul(x, self.weight, self._bias())
         else:
+            if not self.parallel_output and self.fp8_config is None and self._distributed():
+                # the all-reduce runs inside the GEMM kernel (peer memory / NVSwitch) where the group supports it
+                from ....parallel.fused_tp import row_parallel_linear
+
+                fused = row_parallel_linear(x, self.weight, self._bias(), self.topology)
+                if fused is not None:
+                    return fused
             y, bias = self._matmul(x, self.weight, None), self._bias()
         if not (self.parallel_output or self.topology is None):
             y = all_reduce(y, self.topology)

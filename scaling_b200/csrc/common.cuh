@@ -288,6 +288,31 @@ __device__ __forceinline__ bool wait_flag_ge(const uint32_t* flag, uint32_t valu
   }
 }
 
+// ------------------------------------------------------ NVSwitch multicast (multimem)
+// Addresses come from a multicast mapping of a symmetric allocation: a load-reduce returns the sum over all
+// GPUs' replicas (added inside the switch, fp32 accumulation), a store writes every replica.
+__device__ __forceinline__ uint4 multimem_ld_reduce_add_bf16x2(const void* mc_addr) {
+  uint4 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(mc_addr)
+               : "memory");
+  return v;
+}
+__device__ __forceinline__ uint4 multimem_ld_reduce_add_f16x2(const void* mc_addr) {
+  uint4 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.f16x2 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(mc_addr)
+               : "memory");
+  return v;
+}
+__device__ __forceinline__ void multimem_st_b128(void* mc_addr, uint4 v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.bf16x2 [%0], {%1, %2, %3, %4};" ::"l"(mc_addr), "r"(v.x), "r"(v.y),
+               "r"(v.z), "r"(v.w)
+               : "memory");
+}
+
 // ------------------------------------------------------------- small helpers
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll

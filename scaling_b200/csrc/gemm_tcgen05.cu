@@ -36,6 +36,24 @@ constexpr int EPI_WARPS = 8;
 constexpr int GEMM_THREADS = 64 + EPI_WARPS * 32;
 constexpr int STAGE_BOX_BYTES = 32 * 128;  // one epilogue staging box: 32 rows x 64 16-bit columns
 
+// Fused all-reduce of the output over the tensor-parallel group (see the reducer role in the kernel).  All pointer
+// tables are indexed by rank; entry r is rank r's buffer as mapped into this process.
+constexpr int AR_MAX_RANKS = 8;
+constexpr int REDUCER_THREADS = 128;
+struct ArParams {
+  void* partial[AR_MAX_RANKS];   // [M, ldc] partial products (this rank writes partial[rank])
+  void* out[AR_MAX_RANKS];       // [M, ldc] reduced result, every rank receives all of it
+  uint32_t* flags[AR_MAX_RANKS]; // [(W + 1) * flag_stride]: flags[r][q * stride + t] = rank q finished tile t (t owned by
+                                 // r); flags[r][W * stride + q] = rank q has finished all its reductions
+  void* partial_mc;              // multicast addresses of the two buffers, or null (plain peer loads / stores)
+  void* out_mc;
+  uint32_t* epoch;               // local: number of completed fused launches on this workspace
+  unsigned int* done_ctas;       // local: CTAs of this launch that have finished
+  int flag_stride;
+  int rank, W;
+  unsigned long long timeout_ns;
+};
+
 struct GemmParams {
   void* C;
   void* C_pre;  // optional: pre-activation output (same dtype / ld as C)
@@ -50,6 +68,7 @@ struct GemmParams {
   float* ws_partial;  // split-K: [tiles * splits][BN / 32][128][32] floats
   int* ws_counter;    // split-K: one arrival counter per tile, zero between launches
   int* status;
+  ArParams ar;        // used by the FUSE instantiations only
 };
 
 // PAIR: two CTAs of a cluster compute one 256 x BN tile with cta_group::2 MMAs; each CTA loads its own 128 rows of A
@@ -106,6 +125,15 @@ __device__ __forceinline__ void bias_pair(uint32_t w, int is_bf16, float& lo, fl
   }
 }
 __device__ __forceinline__ void epi_bar_sync() { asm volatile("bar.sync 1, %0;" ::"n"(EPI_WARPS * 32) : "memory"); }
+__device__ __forceinline__ void red_bar_sync() { asm volatile("bar.sync 2, %0;" ::"n"(REDUCER_THREADS) : "memory"); }
+template <typename OutT> __device__ __forceinline__ uint4 multimem_sum16(const void* mc);
+template <> __device__ __forceinline__ uint4 multimem_sum16<__nv_bfloat16>(const void* mc) {
+  return sb::multimem_ld_reduce_add_bf16x2(mc);
+}
+template <> __device__ __forceinline__ uint4 multimem_sum16<__half>(const void* mc) {
+  return sb::multimem_ld_reduce_add_f16x2(mc);
+}
+template <> __device__ __forceinline__ uint4 multimem_sum16<float>(const void*) { return make_uint4(0, 0, 0, 0); }
 
 template <typename OutT> __device__ __forceinline__ void store8(OutT* dst, const float* v);
 template <> __device__ __forceinline__ void store8<float>(float* dst, const float* v) {
@@ -157,8 +185,15 @@ template <> __device__ __forceinline__ void load8<__half>(const __half* src, flo
   }
 }
 
-template <int BN, bool A_MN, bool B_MN, typename OutT, bool PAIR>
-__global__ void __launch_bounds__(GEMM_THREADS, 1)
+// FUSE: the output is summed over the ranks of a tensor-parallel group inside the kernel.  Every rank runs the same
+// launch on its own operands.  The epilogue writes the partial tile to this rank's buffer and flags it at the
+// tile's owner (tile number modulo group size); four extra warps per CTA ("reducers") wait until all ranks have
+// flagged a tile they own, sum the partial tiles (one multimem.ld_reduce per 16 bytes: the switch adds the
+// replicas; or peer loads added in rank order) and store the result to every rank's output (multimem.st or peer
+// stores).  Tiles are reduced while later tiles are still being multiplied.  The last CTA of a launch exchanges
+// completion flags with the peers, so the kernel ends only when this rank's output is complete.
+template <int BN, bool A_MN, bool B_MN, typename OutT, bool PAIR, bool FUSE>
+__global__ void __launch_bounds__(FUSE ? GEMM_THREADS + REDUCER_THREADS : GEMM_THREADS, 1)
     gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                         const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmP,
                         const GemmParams p) {
@@ -191,6 +226,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
   const int num_kb = (p.K + BK - 1) / BK;
   const int S = p.splits;
   const int num_units = m_tiles * n_tiles * S;
+  const uint32_t epoch = FUSE ? *p.ar.epoch + 1 : 0;  // identifies this launch in the peers' flag words
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -317,7 +353,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
         if (++acc == 2) { acc = 0; acc_phase ^= 1; }
       }
     }
-  } else {
+  } else if (warp < 2 + EPI_WARPS) {
     // ------------------------------------------------------------ epilogue
     const int ew = warp - 2;            // 0 .. EPI_WARPS-1
     const int quad = warp & 3;          // TMEM lane quadrant this warp may access
@@ -440,7 +476,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
         bias_buf ^= 1;
       }
 
-      if (!ok) continue;
+      if (ok) {
       if (use_tma) {
         const int row0 = m_blk * BM + quad * 32;
         // swizzled position of 16-byte chunk j of this lane's row inside the 32 x 128-byte staging box
@@ -545,15 +581,103 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
           }
         }
       }
-      if (S == 1) {
+      }  // ok
+      if (S == 1 && ok) {
         sb::tc_fence_before();
         __syncwarp();
         if (lane == 0) release_acc(acc_used);
+      }
+      if (FUSE) {
+        // the partial tile is complete in memory before its owner is told so
+        if (lane == 0) sb::tma_store_wait_all0();
+        __syncwarp();
+        __threadfence_system();
+        epi_bar_sync();
+        if (et == 0) {
+          const int owner = (tile + rank) % p.ar.W;  // rotated per CTA of a pair: every CTA owns 1 / W of its tiles
+          sb::st_release_sys(p.ar.flags[owner] + (long)p.ar.rank * p.ar.flag_stride + ctile, epoch);
+        }
       }
     }
     // stores in flight read the staging boxes: drain them before shared memory goes away
     if (lane == 0) sb::tma_store_wait_all0();
     __syncwarp();
+  }
+
+  else if (FUSE) {
+    // ------------------------------------------------------------ reducers
+    const int rt = threadIdx.x - (64 + EPI_WARPS * 32);
+    const ArParams& ar = p.ar;
+    constexpr int VPR = BN / 8;  // 16-byte vectors per tile row
+    bool rok = true;
+    for (int unit = worker; unit < num_units; unit += num_workers) {
+      const int ctile = unit * CTAS + rank;  // S == 1 in fused launches: unit = tile
+      if ((unit + rank) % ar.W != ar.rank) continue;  // same rule as in the epilogue (unit = tile here)
+      const int m0 = ((unit / n_tiles) * CTAS + rank) * BM, n0 = (unit % n_tiles) * BN;
+      if (rok && rt < ar.W) {
+        if (!sb::wait_flag_ge(ar.flags[ar.rank] + (long)rt * ar.flag_stride + ctile, epoch, ar.timeout_ns))
+          *abort_flag = 1;
+      }
+      red_bar_sync();
+      if (*abort_flag) rok = false;
+      if (!rok) continue;
+      // several 16-byte pieces per thread and pass: all loads are issued before the first result is needed, which
+      // keeps enough bytes in flight to cover the NVLink round trip
+      auto piece = [&](int idx, long& off) -> bool {
+        const int row = m0 + idx / VPR, col = n0 + (idx % VPR) * 8;
+        off = (long)row * p.ldc + col;
+        return idx < BM * VPR && row < p.M && col < p.N;
+      };
+      if (ar.partial_mc) {
+        constexpr int UNR = 8;
+        for (int base = rt; base < BM * VPR; base += REDUCER_THREADS * UNR) {
+          long off[UNR];
+          bool valid[UNR];
+          uint4 v[UNR];
+#pragma unroll
+          for (int j = 0; j < UNR; ++j) {
+            valid[j] = piece(base + j * REDUCER_THREADS, off[j]);
+            if (valid[j]) v[j] = multimem_sum16<OutT>(reinterpret_cast<const OutT*>(ar.partial_mc) + off[j]);
+          }
+#pragma unroll
+          for (int j = 0; j < UNR; ++j)
+            if (valid[j]) sb::multimem_st_b128(reinterpret_cast<OutT*>(ar.out_mc) + off[j], v[j]);
+        }
+      } else {
+        constexpr int UNR = 4;
+        for (int base = rt; base < BM * VPR; base += REDUCER_THREADS * UNR) {
+          long off[UNR];
+          bool valid[UNR];
+          float acc[UNR][8];
+#pragma unroll
+          for (int j = 0; j < UNR; ++j) {
+            valid[j] = piece(base + j * REDUCER_THREADS, off[j]);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc[j][i] = 0.f;
+          }
+          for (int q = 0; q < ar.W; ++q) {  // rank order: the sum is the same on every launch
+            uint4 raw[UNR];
+#pragma unroll
+            for (int j = 0; j < UNR; ++j)
+              if (valid[j]) raw[j] = *reinterpret_cast<const uint4*>(reinterpret_cast<const OutT*>(ar.partial[q]) + off[j]);
+#pragma unroll
+            for (int j = 0; j < UNR; ++j)
+              if (valid[j]) {
+                float v[8];
+                load8<OutT>(reinterpret_cast<const OutT*>(&raw[j]), v);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) acc[j][i] += v[i];
+              }
+          }
+          for (int q = 0; q < ar.W; ++q) {
+#pragma unroll
+            for (int j = 0; j < UNR; ++j)
+              if (valid[j]) store8<OutT>(reinterpret_cast<OutT*>(ar.out[q]) + off[j], acc[j]);
+          }
+        }
+      }
+    }
+    __threadfence_system();  // this CTA's share of the result is visible to the peers before it reports completion
   }
 
   // ---------------------------------------------------------------- teardown
@@ -571,6 +695,23 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
     else sb::tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
   }
   if (threadIdx.x == 0 && *abort_flag && p.status) *p.status = SB_ERR_WAIT_TIMEOUT;
+  if (FUSE && threadIdx.x == 0) {
+    // The last CTA of this launch tells every peer that this rank has finished reducing, then waits for the same
+    // message from all of them: when the launch ends, every tile of this rank's output has been written, and no
+    // peer reads this rank's partial buffer any more.
+    const ArParams& ar = p.ar;
+    __threadfence_system();
+    if (atomicAdd(ar.done_ctas, 1u) == gridDim.x - 1) {
+      *ar.done_ctas = 0;
+      for (int q = 0; q < ar.W; ++q)
+        sb::st_release_sys(ar.flags[q] + (long)ar.W * ar.flag_stride + ar.rank, epoch);
+      for (int q = 0; q < ar.W; ++q)
+        if (!sb::wait_flag_ge(ar.flags[ar.rank] + (long)ar.W * ar.flag_stride + q, epoch, ar.timeout_ns) && p.status)
+          *p.status = SB_ERR_WAIT_TIMEOUT;
+      *ar.epoch = epoch;
+      __threadfence();
+    }
+  }
 }
 
 // ------------------------------------------------------------------ host side
@@ -605,11 +746,11 @@ int make_tmap_2d(CUtensorMap* tm, const void* base, long rows, long cols, long l
   return r == CUDA_SUCCESS ? SB_OK : SB_ERR_DRIVER;
 }
 
-template <int BN, bool A_MN, bool B_MN, typename OutT, bool PAIR>
+template <int BN, bool A_MN, bool B_MN, typename OutT, bool PAIR, bool FUSE = false>
 int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmC, const CUtensorMap& tmP,
                 const GemmParams& p, int sm_count, cudaStream_t stream) {
   using Cfg = GemmCfg<BN, PAIR>;
-  auto kern = gemm_tcgen05_kernel<BN, A_MN, B_MN, OutT, PAIR>;
+  auto kern = gemm_tcgen05_kernel<BN, A_MN, B_MN, OutT, PAIR, FUSE>;
   static bool attr_set = false;
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
@@ -622,7 +763,7 @@ int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMa
   const int workers = units < max_workers ? units : max_workers;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(workers * Cfg::CTAS);
-  cfg.blockDim = dim3(GEMM_THREADS);
+  cfg.blockDim = dim3(FUSE ? GEMM_THREADS + REDUCER_THREADS : GEMM_THREADS);
   cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
@@ -768,4 +909,59 @@ SB_API int sb200_gemm(const void* A, const void* B, void* C, void* C_pre, const 
                       int out_dtype, int bn_hint, int sm_count, int* status, cudaStream_t stream) {
   return sb200_gemm_ws(A, B, C, C_pre, bias, M, N, K, lda, ldb, ldc, a_mn, b_mn, act, accumulate, in_dtype, out_dtype,
                        bn_hint, 0, sm_count, nullptr, 0, status, stream);
+}
+
+// C = sum over the W ranks of a tensor-parallel group of op(A_r) op(B_r) (+ bias, given on one rank only), every rank
+// receiving the full [M, N] result: the row-parallel linear (A = activations [M, K_local], B = weight shard
+// [N, K_local], b_mn = 0) and the input gradient of a column-parallel linear (b_mn = 1).  All ranks call this with
+// the same M, N and their own operands; the buffers behind partial_ptrs / out_ptrs / flag_ptrs are symmetric
+// allocations mapped into every process (tables of W device pointers in host memory, entry r = rank r's buffer).
+//   partial, out: [M, ldc] elements of the input dtype each;  flags: (W + 1) * flag_stride uint32, zero before the
+//   first use, flag_stride >= number of 128-row output tiles;  partial_mc / out_mc: multicast addresses or null;
+//   epoch, done_ctas: one uint32 each in local device memory, zero before the first use.
+// The result is in out_ptrs[rank] when the launch completes.
+SB_API int sb200_gemm_allreduce(const void* A, const void* B, const void* bias, int M, int N, int K, long lda, long ldb,
+                                long ldc, int b_mn, int in_dtype, void* const* partial_ptrs, void* const* out_ptrs,
+                                void* const* flag_ptrs, void* partial_mc, void* out_mc, int flag_stride,
+                                uint32_t* epoch, unsigned int* done_ctas, int rank, int W, double timeout_seconds,
+                                int sm_count, int* status, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return SB_OK;
+  if (K <= 0 || W < 1 || W > AR_MAX_RANKS || rank < 0 || rank >= W) return SB_ERR_BAD_ARG;
+  if (in_dtype != SB_DT_BF16) return SB_ERR_BAD_ARG;
+  if ((lda % 8) || (ldb % 8) || (ldc % 8) || (N % 8)) return SB_ERR_BAD_ARG;
+  if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15)) return SB_ERR_BAD_ARG;
+  const bool pair = M > BM && N > 128;
+  const int bn = pair ? 256 : 128;
+  const int rows = pair ? 2 * BM : BM;
+  const long ctiles = (long)((M + rows - 1) / rows) * ((N + bn - 1) / bn) * (pair ? 2 : 1);
+  if (ctiles > flag_stride) return SB_ERR_TOO_LARGE;
+  GemmParams p = {};
+  p.C = partial_ptrs[rank]; p.C_pre = nullptr; p.bias = bias; p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.act = 0;
+  p.accumulate = 0; p.ab_fmt = 1; p.status = status; p.splits = 1; p.ws_counter = nullptr; p.ws_partial = nullptr;
+  if (reinterpret_cast<uintptr_t>(p.C) & 15) return SB_ERR_BAD_ARG;
+  p.tma_store = 1;
+  for (int q = 0; q < AR_MAX_RANKS; ++q) {
+    p.ar.partial[q] = q < W ? partial_ptrs[q] : nullptr;
+    p.ar.out[q] = q < W ? out_ptrs[q] : nullptr;
+    p.ar.flags[q] = q < W ? reinterpret_cast<uint32_t*>(flag_ptrs[q]) : nullptr;
+  }
+  p.ar.partial_mc = partial_mc; p.ar.out_mc = out_mc; p.ar.epoch = epoch; p.ar.done_ctas = done_ctas;
+  p.ar.flag_stride = flag_stride; p.ar.rank = rank; p.ar.W = W;
+  if (timeout_seconds <= 0.0 || timeout_seconds > 60.0) timeout_seconds = 10.0;
+  p.ar.timeout_ns = (unsigned long long)(timeout_seconds * 1e9);
+  CUtensorMap tmA, tmB, tmC, tmP;
+  int rc;
+  if ((rc = make_tmap_2d(&tmA, A, M, K, lda, BM, 0))) return rc;
+  if (b_mn) rc = make_tmap_2d(&tmB, B, K, N, ldb, 64, 0);
+  else rc = make_tmap_2d(&tmB, B, N, K, ldb, pair ? 128 : bn, 0);
+  if (rc) return rc;
+  if ((rc = make_tmap_out(&tmC, p.C, M, N, ldc, 0))) return rc;
+  tmP = tmC;
+  using T = __nv_bfloat16;
+  if (pair) {
+    if (b_mn) return launch_gemm<256, false, true, T, true, true>(tmA, tmB, tmC, tmP, p, sm_count, stream);
+    return launch_gemm<256, false, false, T, true, true>(tmA, tmB, tmC, tmP, p, sm_count, stream);
+  }
+  if (b_mn) return launch_gemm<128, false, true, T, false, true>(tmA, tmB, tmC, tmP, p, sm_count, stream);
+  return launch_gemm<128, false, false, T, false, true>(tmA, tmB, tmC, tmP, p, sm_count, stream);
 }
