@@ -144,10 +144,11 @@ __global__ void rope_kernel(T* __restrict__ x, const int* __restrict__ pos, int 
   }
 }
 
-// Vectorised form: one thread rotates 16 bytes of the first operand of the pairs and their partners.  Work items
-// are ordered (token, head, sub-tensor, chunk), so that a packed [q | k | v] head layout (n_sub = 2, ld_sub = d) is
-// swept with contiguous accesses.  mode 0: chunk c pairs elements [c*V, c*V + V) with the same range + rot/2;
-// mode 1: chunk c holds V/2 pairs (2i, 2i + 1).
+// Vectorised form: a thread owns one 16-byte chunk position of one token, computes the sines and cosines of that
+// chunk's frequencies once, and applies them to every head and sub-tensor of the token (the angles depend on the
+// position and the frequency only).  A packed [q | k | v] head layout is covered with n_sub = 2, ld_sub = d.
+// mode 0: chunk c pairs elements [c*V, c*V + V) with the same range + rot/2; mode 1: chunk c holds V/2 pairs
+// (2i, 2i + 1).
 template <typename T>
 __global__ void rope_vec_kernel(T* __restrict__ x, const int* __restrict__ pos, long total, int n_heads, int n_sub,
                                 int n_chunk, int rot_dim, long ld_tok, long ld_head, long ld_sub, float log2_base,
@@ -156,38 +157,44 @@ __global__ void rope_vec_kernel(T* __restrict__ x, const int* __restrict__ pos, 
   const int half = rot_dim >> 1;
   for (long idx = blockIdx.x * (long)blockDim.x + threadIdx.x; idx < total; idx += (long)gridDim.x * blockDim.x) {
     const int c = (int)(idx % n_chunk);
-    long r = idx / n_chunk;
-    const int sub = (int)(r % n_sub);
-    r /= n_sub;
-    const int h = (int)(r % n_heads);
-    const long t = r / n_heads;
+    const long t = idx / n_chunk;
     const float p = (float)pos[t];
-    T* base = x + t * ld_tok + h * ld_head + sub * ld_sub;
-    if (mode == 0) {
-      sb::Vec16<T> a = sb::ld16(base + c * V), b = sb::ld16(base + half + c * V);
+    constexpr int NF = V;  // frequencies per chunk: V in mode 0, V / 2 in mode 1
+    float sn[NF], cs[NF];
+    const int nf = mode == 0 ? V : V / 2;
 #pragma unroll
-      for (int i = 0; i < V; ++i) {
-        float sn, cs;
-        sincosf(p * exp2f(-log2_base * (2.f * (float)(c * V + i)) / (float)rot_dim), &sn, &cs);
-        sn *= sign;
-        const float fa = sb::to_f(a.e[i]), fb = sb::to_f(b.e[i]);
-        a.e[i] = sb::from_f<T>(fa * cs - fb * sn);
-        b.e[i] = sb::from_f<T>(fb * cs + fa * sn);
+    for (int i = 0; i < NF; ++i) {
+      if (i < nf) {
+        const int f = mode == 0 ? c * V + i : c * (V / 2) + i;
+        sincosf(p * exp2f(-log2_base * (2.f * (float)f) / (float)rot_dim), &sn[i], &cs[i]);
+        sn[i] *= sign;
       }
-      sb::st16(base + c * V, a);
-      sb::st16(base + half + c * V, b);
-    } else {
-      sb::Vec16<T> a = sb::ld16(base + c * V);
+    }
+    T* tok = x + t * ld_tok;
+    for (int h = 0; h < n_heads; ++h) {
+      for (int sub = 0; sub < n_sub; ++sub) {
+        T* base = tok + h * ld_head + sub * ld_sub;
+        if (mode == 0) {
+          sb::Vec16<T> a = sb::ld16(base + c * V), b = sb::ld16(base + half + c * V);
 #pragma unroll
-      for (int i = 0; i < V / 2; ++i) {
-        float sn, cs;
-        sincosf(p * exp2f(-log2_base * (2.f * (float)(c * (V / 2) + i)) / (float)rot_dim), &sn, &cs);
-        sn *= sign;
-        const float fa = sb::to_f(a.e[2 * i]), fb = sb::to_f(a.e[2 * i + 1]);
-        a.e[2 * i] = sb::from_f<T>(fa * cs - fb * sn);
-        a.e[2 * i + 1] = sb::from_f<T>(fb * cs + fa * sn);
+          for (int i = 0; i < V; ++i) {
+            const float fa = sb::to_f(a.e[i]), fb = sb::to_f(b.e[i]);
+            a.e[i] = sb::from_f<T>(fa * cs[i] - fb * sn[i]);
+            b.e[i] = sb::from_f<T>(fb * cs[i] + fa * sn[i]);
+          }
+          sb::st16(base + c * V, a);
+          sb::st16(base + half + c * V, b);
+        } else {
+          sb::Vec16<T> a = sb::ld16(base + c * V);
+#pragma unroll
+          for (int i = 0; i < V / 2; ++i) {
+            const float fa = sb::to_f(a.e[2 * i]), fb = sb::to_f(a.e[2 * i + 1]);
+            a.e[2 * i] = sb::from_f<T>(fa * cs[i] - fb * sn[i]);
+            a.e[2 * i + 1] = sb::from_f<T>(fb * cs[i] + fa * sn[i]);
+          }
+          sb::st16(base + c * V, a);
+        }
       }
-      sb::st16(base + c * V, a);
     }
   }
 }
@@ -402,8 +409,8 @@ SB_API int sb200_rope_multi(void* x, const int* pos, int tokens, int n_heads, in
                      (reinterpret_cast<uintptr_t>(x) & 15) == 0;
     if (vec) {
       const int n_chunk = span / V;
-      const long total = (long)tokens * n_heads * n_sub * n_chunk;
-      rope_vec_kernel<T><<<grid_for(total, 256), 256, 0, stream>>>((T*)x, pos, total, n_heads, n_sub, n_chunk, rot_dim,
+      const long total = (long)tokens * n_chunk;
+      rope_vec_kernel<T><<<grid_for(total, 128), 128, 0, stream>>>((T*)x, pos, total, n_heads, n_sub, n_chunk, rot_dim,
                                                                    ld_tok, ld_head, ld_sub, log2f(base), mode,
                                                                    backward ? -1.f : 1.f);
     } else {

@@ -17,6 +17,84 @@ namespace {
 constexpr int NORM_THREADS = 256;
 constexpr int NORM_MAX_ITERS = 8;  // H <= 256 * 8 * 8 = 16384 for 2-byte types
 
+// Forward for rows of at most 32 * V * NV elements: one warp per row, the row stays in registers between the
+// statistics and the normalisation (one read of x, one write of y), eight rows in flight per CTA.
+template <typename T, bool RMS, int NV>
+__global__ void __launch_bounds__(NORM_THREADS)
+    norm_fwd_warp_kernel(const T* __restrict__ x, const T* __restrict__ w, const T* __restrict__ b, T* __restrict__ y,
+                         float* __restrict__ mean_out, float* __restrict__ rstd_out, int M, int H, float eps) {
+  constexpr int V = sb::Vec16<T>::N;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int total_warps = gridDim.x * (NORM_THREADS / 32);
+  sb::Vec16<T> wv[NV], bv[NV];
+#pragma unroll
+  for (int it = 0; it < NV; ++it) {
+    const int c = (it * 32 + lane) * V;
+    wv[it].u = make_uint4(0, 0, 0, 0);
+    bv[it].u = make_uint4(0, 0, 0, 0);
+    if (c < H) {
+      wv[it] = sb::ld16(w + c);
+      if (!RMS && b) bv[it] = sb::ld16(b + c);
+    }
+  }
+  const float inv_h = 1.f / H;
+  for (int row = blockIdx.x * (NORM_THREADS / 32) + warp; row < M; row += total_warps) {
+    const T* xr = x + (size_t)row * H;
+    sb::Vec16<T> xv[NV];
+    float s = 0.f, ss = 0.f;
+#pragma unroll
+    for (int it = 0; it < NV; ++it) {
+      const int c = (it * 32 + lane) * V;
+      xv[it].u = make_uint4(0, 0, 0, 0);
+      if (c < H) xv[it] = sb::ld16(xr + c);
+#pragma unroll
+      for (int i = 0; i < V; ++i) {
+        const float f = sb::to_f(xv[it].e[i]);
+        s += f;
+        ss += f * f;
+      }
+    }
+    float mean = 0.f, rstd;
+    if (RMS) {
+      rstd = rsqrtf(sb::warp_sum(ss) * inv_h + eps);
+    } else {
+      mean = sb::warp_sum(s) * inv_h;
+      float var = 0.f;  // second pass over the registers: numerically safer than E[x^2] - E[x]^2
+#pragma unroll
+      for (int it = 0; it < NV; ++it) {
+        const int c = (it * 32 + lane) * V;
+        if (c < H) {
+#pragma unroll
+          for (int i = 0; i < V; ++i) {
+            const float d = sb::to_f(xv[it].e[i]) - mean;
+            var += d * d;
+          }
+        }
+      }
+      rstd = rsqrtf(sb::warp_sum(var) * inv_h + eps);
+    }
+    if (lane == 0) {
+      if (!RMS && mean_out) mean_out[row] = mean;
+      rstd_out[row] = rstd;
+    }
+    T* yr = y + (size_t)row * H;
+#pragma unroll
+    for (int it = 0; it < NV; ++it) {
+      const int c = (it * 32 + lane) * V;
+      if (c < H) {
+        sb::Vec16<T> o;
+#pragma unroll
+        for (int i = 0; i < V; ++i) {
+          float v = (sb::to_f(xv[it].e[i]) - mean) * rstd * sb::to_f(wv[it].e[i]);
+          if (!RMS && b) v += sb::to_f(bv[it].e[i]);
+          o.e[i] = sb::from_f<T>(v);
+        }
+        sb::st16(yr + c, o);
+      }
+    }
+  }
+}
+
 template <typename T, bool RMS>
 __global__ void __launch_bounds__(NORM_THREADS) norm_fwd_kernel(const T* __restrict__ x, const T* __restrict__ w,
                                                                 const T* __restrict__ b, T* __restrict__ y,
@@ -333,17 +411,48 @@ __global__ void __launch_bounds__(1024)
 
 }  // namespace
 
+namespace {
+
+template <typename T, int NV>
+void launch_norm_fwd_warp(const void* x, const void* w, const void* b, void* y, float* mean, float* rstd, int M, int H,
+                          float eps, int rms, cudaStream_t stream) {
+  int ctas = (M + 7) / 8;
+  if (ctas > 148 * 8) ctas = 148 * 8;
+  if (rms)
+    norm_fwd_warp_kernel<T, true, NV><<<ctas, NORM_THREADS, 0, stream>>>((const T*)x, (const T*)w, nullptr, (T*)y, nullptr,
+                                                                         rstd, M, H, eps);
+  else
+    norm_fwd_warp_kernel<T, false, NV><<<ctas, NORM_THREADS, 0, stream>>>((const T*)x, (const T*)w, (const T*)b, (T*)y,
+                                                                          mean, rstd, M, H, eps);
+}
+
+template <typename T>
+void norm_fwd_dispatch(const void* x, const void* w, const void* b, void* y, float* mean, float* rstd, int M, int H,
+                       float eps, int rms, cudaStream_t stream) {
+  constexpr int V = sb::Vec16<T>::N;
+  const bool aligned = ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y) |
+                         reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(b)) & 15) == 0;
+  if (H % V == 0 && H <= 32 * V * 4 && aligned) {
+    const int nv = (H + 32 * V - 1) / (32 * V);
+    if (nv <= 1) launch_norm_fwd_warp<T, 1>(x, w, b, y, mean, rstd, M, H, eps, rms, stream);
+    else if (nv == 2) launch_norm_fwd_warp<T, 2>(x, w, b, y, mean, rstd, M, H, eps, rms, stream);
+    else if (nv == 3) launch_norm_fwd_warp<T, 3>(x, w, b, y, mean, rstd, M, H, eps, rms, stream);
+    else launch_norm_fwd_warp<T, 4>(x, w, b, y, mean, rstd, M, H, eps, rms, stream);
+  } else if (rms) {
+    norm_fwd_kernel<T, true><<<M, NORM_THREADS, 0, stream>>>((const T*)x, (const T*)w, nullptr, (T*)y, nullptr, rstd, M,
+                                                              H, eps);
+  } else {
+    norm_fwd_kernel<T, false><<<M, NORM_THREADS, 0, stream>>>((const T*)x, (const T*)w, (const T*)b, (T*)y, mean, rstd,
+                                                               M, H, eps);
+  }
+}
+
+}  // namespace
+
 SB_API int sb200_norm_fwd(const void* x, const void* w, const void* b, void* y, float* mean, float* rstd, int M, int H,
                           float eps, int rms, int dtype, cudaStream_t stream) {
   if (M <= 0 || H <= 0) return SB_OK;
-  SB_DISPATCH_DTYPE(dtype, T, {
-    if (rms)
-      norm_fwd_kernel<T, true><<<M, NORM_THREADS, 0, stream>>>((const T*)x, (const T*)w, nullptr, (T*)y, nullptr, rstd,
-                                                                M, H, eps);
-    else
-      norm_fwd_kernel<T, false><<<M, NORM_THREADS, 0, stream>>>((const T*)x, (const T*)w, (const T*)b, (T*)y, mean,
-                                                                 rstd, M, H, eps);
-  });
+  SB_DISPATCH_DTYPE(dtype, T, { norm_fwd_dispatch<T>(x, w, b, y, mean, rstd, M, H, eps, rms, stream); });
   SB_CHECK_LAUNCH();
   return SB_OK;
 }

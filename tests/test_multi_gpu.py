@@ -54,3 +54,44 @@ def test_tensor_parallel_matches_single_gpu(tmp_path: Path):
         got = _losses(2, load_dir=init, **kw)
         for a, b in zip(got, base):
             assert abs(a - b) < 5e-2 * max(1.0, abs(b)), (kw, got, base)
+
+
+def _fused_gemm_allreduce_worker(rank, world_size, port, device):
+    import torch.distributed as dist
+
+    from scaling_b200.ops import functional as K
+    from scaling_b200.parallel.fused_tp import FusedTPWorkspace
+
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world_size,
+                            device_id=torch.device("cuda", rank))
+    dev = torch.device("cuda", rank)
+    errors = []
+    for multicast in (False, True):
+        ws = FusedTPWorkspace(dist.group.WORLD, dev, 4096 * 1024, use_multicast=multicast)
+        for M, N, Kd, b_mn in [(256, 256, 128, False), (4096, 768, 384, False), (1000, 264, 200, False),
+                               (2048, 768, 1152, True), (128, 64, 64, False)]:
+            torch.manual_seed(1 + rank)
+            x = torch.randn(M, Kd, device=dev, dtype=torch.bfloat16)
+            shape = (Kd, N) if b_mn else (N, Kd)
+            w = torch.randn(*shape, device=dev, dtype=torch.bfloat16) * 0.05
+            bias = None if b_mn else torch.randn(N, device=dev, dtype=torch.bfloat16)
+            ref = K.gemm(x, w, b_mn=b_mn, bias=bias if rank == 0 else None)
+            dist.all_reduce(ref)
+            got = ws.gemm_allreduce(x, w, bias if rank == 0 else None, b_mn=b_mn)
+            again = ws.gemm_allreduce(x, w, bias if rank == 0 else None, b_mn=b_mn)
+            torch.cuda.synchronize()
+            K.check_status()
+            rel = ((got.float() - ref.float()).norm() / ref.float().norm()).item()
+            # peer loads add in rank order like the library; the switch's adder rounds once from fp32
+            errors.append((multicast and ws.use_multicast, (M, N, Kd, b_mn), rel, torch.equal(got, again)))
+        del ws
+    return errors
+
+
+def test_gemm_with_in_kernel_allreduce():
+    results = dist_launcher(_fused_gemm_allreduce_worker, 2, device="cuda")
+    for per_rank in results:
+        for multicast, shape, rel, repeatable in per_rank:
+            assert repeatable, shape
+            assert rel < (6e-3 if multicast else 1e-6), (multicast, shape, rel)
