@@ -507,9 +507,12 @@ __global__ void __launch_bounds__(FA_BWD_THREADS, 1)
       const uint32_t k_addr = sb::smem_u32(sK), v_addr = sb::smem_u32(sV), p_addr = sb::smem_u32(sP),
                      ds_addr = sb::smem_u32(sdS);
       bool ok = sb::mbar_wait(kv_full, 0, abort_flag);
-      for (int it = 0; it < n_iter && ok; ++it) {
+      // S = Q K^T and dP = dO V^T of iteration it + 1 are issued ahead of the accumulation MMAs of iteration it where
+      // the Q / dO ring has a second stage, so that the threads compute P and dS of the next tile while the tensor
+      // core accumulates dV and dK of this one
+      auto issue_sdp = [&](int it) -> bool {
         const int st = it % NS;
-        if (!sb::mbar_wait(&qdo_full[st], (it / NS) & 1, abort_flag)) break;
+        if (!sb::mbar_wait(&qdo_full[st], (it / NS) & 1, abort_flag)) return false;
         sb::tc_fence_after();
         const uint32_t q_addr = sb::smem_u32(sQ + st * TILE_BYTES), do_addr = sb::smem_u32(sdO + st * TILE_BYTES);
 #pragma unroll
@@ -518,8 +521,15 @@ __global__ void __launch_bounds__(FA_BWD_THREADS, 1)
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk)
           sb::umma_f16_ss(tmem_base + DP_COL, desc_kmajor(do_addr, kk), desc_kmajor(v_addr, kk), idesc_nt, kk != 0);
-        sb::umma_commit(sdp_full);  // also covers the accumulation MMAs of the previous iteration
+        sb::umma_commit(sdp_full);
+        return true;
+      };
+      if (ok && n_iter > 0) ok = issue_sdp(0);
+      for (int it = 0; it < n_iter && ok; ++it) {
+        const int st = it % NS;
+        const uint32_t q_addr = sb::smem_u32(sQ + st * TILE_BYTES), do_addr = sb::smem_u32(sdO + st * TILE_BYTES);
         if (!sb::mbar_wait(pds_full, it & 1, abort_flag)) break;
+        if (NS > 1 && it + 1 < n_iter && !issue_sdp(it + 1)) break;
         sb::tc_fence_after();
 #pragma unroll
         for (int kk = 0; kk < TILE / 16; ++kk)
@@ -529,6 +539,7 @@ __global__ void __launch_bounds__(FA_BWD_THREADS, 1)
           sb::umma_f16_ss(tmem_base + DK_COL, desc_mnmajor(ds_addr, kk), desc_mnmajor(q_addr, kk), idesc_acc, (it | kk) != 0);
         sb::umma_commit(acc_done);
         sb::umma_commit(&qdo_empty[st]);
+        if (NS == 1 && it + 1 < n_iter && !issue_sdp(it + 1)) break;
       }
     }
   } else {
@@ -571,6 +582,10 @@ __global__ void __launch_bounds__(FA_BWD_THREADS, 1)
             pv[i] = pr;
             dsv[i] = pr * fmaf(__uint_as_float(dp[i]), sc, -dls);
           }
+        }
+        if (it > 0 && ch == half * 2) {
+          // P and dS are single buffered: the accumulation MMAs of the previous iteration must have read them
+          if (!sb::mbar_wait(acc_done, (it - 1) & 1, abort_flag)) { ok = false; break; }
         }
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
@@ -692,17 +707,17 @@ __global__ void __launch_bounds__(FA_BWD_THREADS, 1)
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sQ = smem;
   uint8_t* sdO = sQ + TILE_BYTES;
-  uint8_t* sK = sdO + TILE_BYTES;
-  uint8_t* sV = sK + TILE_BYTES;
-  uint8_t* sdS = sV + TILE_BYTES;  // [queries x keys] 2 panels
+  uint8_t* sK = sdO + TILE_BYTES;           // 2 stages
+  uint8_t* sV = sK + 2 * TILE_BYTES;        // 2 stages
+  uint8_t* sdS = sV + 2 * TILE_BYTES;       // [queries x keys] 2 panels
   uint64_t* bars = reinterpret_cast<uint64_t*>(sdS + 2 * PANEL_BYTES);
   uint64_t* qdo_full = bars;
-  uint64_t* kv_full = bars + 1;
-  uint64_t* kv_empty = bars + 2;
-  uint64_t* sdp_full = bars + 3;
-  uint64_t* ds_full = bars + 4;   // count 4
-  uint64_t* acc_done = bars + 5;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 6);
+  uint64_t* kv_full = bars + 1;    // 2
+  uint64_t* kv_empty = bars + 3;   // 2
+  uint64_t* sdp_full = bars + 5;
+  uint64_t* ds_full = bars + 6;    // count 8
+  uint64_t* acc_done = bars + 7;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -717,8 +732,10 @@ __global__ void __launch_bounds__(FA_BWD_THREADS, 1)
 
   if (threadIdx.x == 0) {
     sb::mbar_init(qdo_full, 1);
-    sb::mbar_init(kv_full, 1);
-    sb::mbar_init(kv_empty, 1);
+    for (int i = 0; i < 2; ++i) {
+      sb::mbar_init(&kv_full[i], 1);
+      sb::mbar_init(&kv_empty[i], 1);
+    }
     sb::mbar_init(sdp_full, 1);
     sb::mbar_init(ds_full, 8);
     sb::mbar_init(acc_done, 1);
@@ -744,12 +761,13 @@ __global__ void __launch_bounds__(FA_BWD_THREADS, 1)
       }
       for (int j = 0; j < n_tiles; ++j) {
         const int kv0 = (kv_begin + j) * TILE;
-        if (!sb::mbar_wait(kv_empty, (j & 1) ^ 1, abort_flag)) break;
-        sb::mbar_expect_tx(kv_full, 2 * TILE_BYTES);
+        const int st = j & 1;
+        if (!sb::mbar_wait(&kv_empty[st], ((j >> 1) & 1) ^ 1, abort_flag)) break;
+        sb::mbar_expect_tx(&kv_full[st], 2 * TILE_BYTES);
 #pragma unroll
         for (int pn = 0; pn < PANELS; ++pn) {
-          sb::tma_load_2d(sK + pn * PANEL_BYTES, &tmK, kv_full, hk * p.ldk_head + pn * 64, kv0);
-          sb::tma_load_2d(sV + pn * PANEL_BYTES, &tmV, kv_full, hk * p.ldv_head + pn * 64, kv0);
+          sb::tma_load_2d(sK + st * TILE_BYTES + pn * PANEL_BYTES, &tmK, &kv_full[st], hk * p.ldk_head + pn * 64, kv0);
+          sb::tma_load_2d(sV + st * TILE_BYTES + pn * PANEL_BYTES, &tmV, &kv_full[st], hk * p.ldv_head + pn * 64, kv0);
         }
       }
     }
@@ -757,13 +775,17 @@ __global__ void __launch_bounds__(FA_BWD_THREADS, 1)
     if (lane == 0) {
       const uint32_t idesc_nt = sb::umma_idesc_f16(TILE, TILE, 1, 0, 0);
       const uint32_t idesc_acc = sb::umma_idesc_f16(TILE, D, 1, 0, 1);
-      const uint32_t q_addr = sb::smem_u32(sQ), do_addr = sb::smem_u32(sdO), k_addr = sb::smem_u32(sK),
-                     v_addr = sb::smem_u32(sV), ds_addr = sb::smem_u32(sdS);
+      const uint32_t q_addr = sb::smem_u32(sQ), do_addr = sb::smem_u32(sdO), k_base = sb::smem_u32(sK),
+                     v_base = sb::smem_u32(sV), ds_addr = sb::smem_u32(sdS);
       bool ok = sb::mbar_wait(qdo_full, 0, abort_flag);
-      for (int j = 0; j < n_tiles && ok; ++j) {
-        if (!sb::mbar_wait(kv_full, j & 1, abort_flag)) break;
-        if (j > 0 && !sb::mbar_wait(acc_done, (j - 1) & 1, abort_flag)) break;
+      // S(j) = Q K_j^T and dP(j) = dO V_j^T share one TMEM buffer each; they are issued for tile j + 1 as soon as
+      // the threads have read tile j, ahead of dQ += dS_j K_j, so that the threads work on tile j + 1 while the
+      // tensor core accumulates dQ of tile j
+      auto issue_sdp = [&](int j) -> bool {
+        const int st = j & 1;
+        if (!sb::mbar_wait(&kv_full[st], (j >> 1) & 1, abort_flag)) return false;
         sb::tc_fence_after();
+        const uint32_t k_addr = k_base + st * TILE_BYTES, v_addr = v_base + st * TILE_BYTES;
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk)
           sb::umma_f16_ss(tmem_base + S_COL, desc_kmajor(q_addr, kk), desc_kmajor(k_addr, kk), idesc_nt, kk != 0);
@@ -771,13 +793,20 @@ __global__ void __launch_bounds__(FA_BWD_THREADS, 1)
         for (int kk = 0; kk < D / 16; ++kk)
           sb::umma_f16_ss(tmem_base + DP_COL, desc_kmajor(do_addr, kk), desc_kmajor(v_addr, kk), idesc_nt, kk != 0);
         sb::umma_commit(sdp_full);
-        if (!sb::mbar_wait(ds_full, j & 1, abort_flag)) break;
+        return true;
+      };
+      if (ok && n_tiles > 0) ok = issue_sdp(0);
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        const int st = j & 1;
+        if (!sb::mbar_wait(ds_full, j & 1, abort_flag)) break;  // dS(j) is in shared memory, S / dP(j) have been read
+        if (j + 1 < n_tiles && !issue_sdp(j + 1)) break;
         sb::tc_fence_after();
+        const uint32_t k_addr = k_base + st * TILE_BYTES;
 #pragma unroll
         for (int kk = 0; kk < TILE / 16; ++kk)
           sb::umma_f16_ss(tmem_base + DQ_COL, desc_kmajor(ds_addr, kk), desc_mnmajor(k_addr, kk), idesc_acc, (j | kk) != 0);
         sb::umma_commit(acc_done);
-        sb::umma_commit(kv_empty);
+        sb::umma_commit(&kv_empty[st]);
       }
     }
   } else {
@@ -815,6 +844,11 @@ __global__ void __launch_bounds__(FA_BWD_THREADS, 1)
             const float pr = (kidx >= lo && kidx <= hi) ? fast_exp2(fmaf(__uint_as_float(s[i]), sl2, -lse)) : 0.f;
             dsv[i] = pr * fmaf(__uint_as_float(dp[i]), sc, -dls);
           }
+        }
+        if (j > 0 && ch == half * 2) {
+          // dS is single buffered: dQ += dS(j - 1) K must have finished reading it (it was issued right behind this
+          // tile's S / dP, so the wait is short and the first chunk's arithmetic above already overlapped it)
+          if (!sb::mbar_wait(acc_done, (j - 1) & 1, abort_flag)) { ok = false; break; }
         }
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
@@ -899,7 +933,7 @@ int fa_tmap(CUtensorMap* tm, const void* base, long T, long cols, long ld) {
 
 template <int D> constexpr int fa_fwd_smem() { return FaFwdCfg<D>::SMEM; }
 template <int D> constexpr int fa_dkdv_smem() { return (D / 64) * PANEL_BYTES * (2 + 2 * (D == 64 ? 2 : 1)) + 4 * PANEL_BYTES + 1024 + 256; }
-template <int D> constexpr int fa_dq_smem() { return (D / 64) * PANEL_BYTES * 4 + 2 * PANEL_BYTES + 1024 + 256; }
+template <int D> constexpr int fa_dq_smem() { return (D / 64) * PANEL_BYTES * 6 + 2 * PANEL_BYTES + 1024 + 256; }
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
