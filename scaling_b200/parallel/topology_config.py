@@ -44,6 +44,10 @@ def _fill_parallel_sizes(mp, pp, dp, world):
         pp = world // (mp * dp)
     if dp is None:
         dp = world // (mp * pp)
+    assert mp >= 1 and pp >= 1 and dp >= 1 and mp * pp * dp == world, (
+        f"world_size {world} does not equal the product of model_parallel_size ({mp}), pipe_parallel_size ({pp}) "
+        f"and data_parallel_size ({dp})."
+    )
     return mp, pp, dp, world
 
 

@@ -1,0 +1,157 @@
+"""Engine plumbing on CPU ranks (gloo): batch broadcast, pipeline communicator, data loader resume, schedules, and
+how failures of a rank surface (on the host, never on a device)."""
+
+import numpy as np
+import pytest
+import torch
+
+from scaling_b200.core.nn.pipeline_schedule import PipelineScheduleInference, PipelineScheduleTrain
+from scaling_b200.core.nn.pipeline_schedule.simulator import SimulationEngine, illustrate
+from tests.utils import dist_launcher
+
+pytestmark = pytest.mark.dist
+
+
+def _topology(rank, world_size, port, mp=1, pp=1, micro=2, ga=1):
+    from scaling_b200.parallel import Topology, TopologyConfig
+
+    cfg = TopologyConfig.from_dict({
+        "world_size": world_size, "model_parallel_size": mp, "pipe_parallel_size": pp, "global_rank": rank,
+        "local_slot": rank, "micro_batch_size": micro, "gradient_accumulation_steps": ga, "device": "cpu",
+        "backend": "gloo"})
+    t = Topology(cfg)
+    t.initialize_distributed(master_addr="127.0.0.1", master_port=str(port), seed=3)
+    return t
+
+
+# ---------------------------------------------------------------------------------------------- broadcast_data
+def _broadcast_worker(rank, world_size, port, device):
+    from scaling_b200.core.data import broadcast_data
+
+    t = _topology(rank, world_size, port, mp=2)
+    src = [torch.arange(24).reshape(2, 3, 4), torch.tensor([7]), torch.arange(5).reshape(1, 5)]
+    got = broadcast_data(src if t.model_parallel_rank == 0 else [None] * 3, dtype=torch.long, topology=t)
+    flags = broadcast_data([torch.tensor([True, False, True])] if t.model_parallel_rank == 0 else [None],
+                           dtype=torch.bool, topology=t)
+    return [None if g is None else (tuple(g.shape), g.flatten().tolist()) for g in got], flags[0].tolist()
+
+
+def test_broadcast_data_shapes_and_bool():
+    r0, r1 = dist_launcher(_broadcast_worker, 2)
+    assert r0 == r1
+    tensors, flags = r1
+    assert tensors[0] == ((2, 3, 4), list(range(24)))
+    assert tensors[1] == ((1,), [7]) and tensors[2] == ((1, 5), [0, 1, 2, 3, 4])
+    assert flags == [True, False, True]
+
+
+# ---------------------------------------------------------------------------------------------- pipe communicator
+def _pipe_worker(rank, world_size, port, device):
+    from scaling_b200.core.nn.parallel_module.communicator import PipeCommunicator
+
+    t = _topology(rank, world_size, port, pp=2)
+    comm = PipeCommunicator(local_device=torch.device("cpu"), recv_grads=rank == 0, recv_data=rank == 1,
+                            use_continuous_recommunication=True, group=t.pipe_parallel_group,
+                            peer_send=1 if rank == 0 else None, peer_recv=0 if rank == 1 else None)
+    log = []
+    for step, width in enumerate((4, 4, 6)):  # the third payload changes shape: shapes are renegotiated per exchange
+        payload = {"h": torch.full((2, width), float(step), requires_grad=True), "meta": ("text", 3, None),
+                   "ids": torch.arange(3), "np": np.arange(2)}
+        if rank == 0:
+            comm.send_data(payload)
+            tensors, grads = comm.recv_grad(payload)
+            log.append([g.tolist() for g in grads])
+        else:
+            got = comm.recv_data()
+            assert got["meta"] == ("text", 3, None) and got["ids"].tolist() == [0, 1, 2]
+            assert got["np"].tolist() == [0, 1] and got["h"].requires_grad
+            got["h"].grad = torch.full_like(got["h"], 10.0 + step)
+            comm.send_grad(got)
+            log.append((tuple(got["h"].shape), got["h"].detach().mean().item()))
+    return log
+
+
+def test_pipe_communicator_moves_pytrees_and_gradients():
+    sender, receiver = dist_launcher(_pipe_worker, 2)
+    assert receiver == [((2, 4), 0.0), ((2, 4), 1.0), ((2, 6), 2.0)]
+    assert [g[0][0][0] for g in sender] == [10.0, 11.0, 12.0]
+
+
+# ---------------------------------------------------------------------------------------------- data loader
+def _loader_worker(rank, world_size, port, device, consumed):
+    from scaling_b200.core.data import DataLoader
+    from scaling_b200.transformer.data import SyntheticTextDataset
+
+    t = _topology(rank, world_size, port, micro=2)
+    ds = SyntheticTextDataset(n_samples=20, sequence_length=4, vocab_size=50, seed=1, low=1)
+    loader = DataLoader(seed=1, consumed_samples=consumed, dataset=ds, topology=t, pin_memory=False)
+    return [next(loader).token_ids.tolist() for _ in range(4)]
+
+
+def test_dataloader_resumes_and_shards_by_data_parallel_rank():
+    fresh = dist_launcher(_loader_worker, 2, consumed=0)
+    resumed = dist_launcher(_loader_worker, 2, consumed=8)  # two global steps of 2 ranks x 2 samples
+    for rank in range(2):
+        assert fresh[rank][2:] == resumed[rank][:2]
+    rows0 = {tuple(r) for batch in fresh[0] for r in batch}
+    rows1 = {tuple(r) for batch in fresh[1] for r in batch}
+    assert not rows0 & rows1  # the ranks read disjoint samples
+
+
+# ---------------------------------------------------------------------------------------------- schedules (no ranks)
+@pytest.mark.parametrize("pp", [1, 2, 7])
+@pytest.mark.parametrize("ga", [1, 2, 7, 16, 32])
+def test_schedules_simulate_without_deadlock(pp, ga):
+    out = illustrate(PipelineScheduleTrain, ga, pp)
+    assert out["steps"] and 0.0 <= out["pct_idling_total"] < 1.0
+    engine = SimulationEngine(PipelineScheduleTrain, ga, pp)
+    engine.simulate()
+    summary = engine.summarize()
+    assert summary["total_time"] > 0
+    infer = illustrate(PipelineScheduleInference, ga, pp)
+    assert infer["steps"]
+
+
+def test_one_forward_one_backward_bubble():
+    out = illustrate(PipelineScheduleTrain, 4, 2)
+    assert len(out["steps"]) == 29 and out["pct_idling_total"] == pytest.approx(0.172, abs=1e-3)
+    # more micro batches amortise the bubble
+    assert illustrate(PipelineScheduleTrain, 32, 2)["pct_idling_total"] < out["pct_idling_total"]
+
+
+# ---------------------------------------------------------------------------------------------- failures on the host
+def _failing_worker(rank, world_size, port, device):
+    t = _topology(rank, world_size, port)
+    if rank == 1:
+        raise RuntimeError("injected failure on rank 1")
+    return t.data_parallel_rank
+
+
+def test_an_exception_on_one_rank_is_reported_with_its_traceback():
+    with pytest.raises(AssertionError, match="injected failure on rank 1"):
+        dist_launcher(_failing_worker, 2)
+
+
+def _overflow_worker(rank, world_size, port, device):
+    """A non-finite gradient on one rank makes every rank skip the step (fp16-style loss scaling) or raise."""
+    from scaling_b200.core.optimizer import (LearningRateSchedulerConfig, LossScalerConfig, Optimizer, OptimizerConfig,
+                                             OptimizerParamGroup, OptimizerParamGroupConfig)
+    from scaling_b200.core.nn.parameter_meta import CoreParameterMeta
+
+    t = _topology(rank, world_size, port)
+    torch.manual_seed(0)
+    p = torch.nn.Parameter(torch.ones(8))
+    CoreParameterMeta.register_on_parameter(p, is_model_parallel=False, layer_index=0, parameter_name="w")
+    group = OptimizerParamGroup([("w", p, p.core_parameter_meta)], OptimizerParamGroupConfig(
+        name="g", weight_decay=0.0, learning_rate_scheduler=LearningRateSchedulerConfig(learning_rate=0.1)))
+    opt = Optimizer(OptimizerConfig(zero=False, loss_scaler=LossScalerConfig(enable=True, initial_scale=4.0, hysteresis=1)),
+                    [group], t)
+    before = p.detach().clone()
+    p.grad.fill_(float("inf") if rank == 1 else 1.0)
+    out = opt.step()
+    return out.overflow, out.current_loss_scale, torch.equal(p.detach(), before)
+
+
+def test_overflow_on_one_rank_skips_the_step_everywhere():
+    results = dist_launcher(_overflow_worker, 2)
+    assert results[0] == results[1] == (True, 2.0, True)

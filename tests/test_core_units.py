@@ -1,0 +1,195 @@
+"""Unit tests of the engine's host-side pieces (no GPU, no process groups)."""
+
+import errno
+import json
+from pathlib import Path
+from typing import Optional
+
+import pytest
+import torch
+from pydantic import Field, ValidationError
+
+from scaling_b200.core.config import BaseConfig
+from scaling_b200.core.data.file_handles import FileHandle, RetryableException
+from scaling_b200.core.nn.parallel_module.pipeline_partitioning import (PipePartitionCoordinates, balanced_boundaries,
+                                                                        pipe_partition_from_indices,
+                                                                        pipe_partition_uniform)
+from scaling_b200.core.optimizer import (LearningRateDecayStyle, LearningRateScheduler, LearningRateSchedulerConfig,
+                                         LossScaler, LossScalerConfig)
+from scaling_b200.core.runner import RunnerConfig
+from scaling_b200.core.runner.runner import hosts_str_to_resource_pool, parse_host
+from scaling_b200.parallel import TopologyConfig
+
+
+# ---------------------------------------------------------------------------------------------- config
+class _Inner(BaseConfig):
+    width: int = Field(4, description="inner width")
+
+
+class _Outer(BaseConfig):
+    name: str = Field("x", description="a name")
+    inner: _Inner = Field(_Inner(), description="nested settings")
+    items: Optional[list[int]] = Field(None, description="numbers")
+
+
+def test_config_is_frozen_and_forbids_unknown_keys():
+    c = _Outer.from_dict({"name": "a", "inner": {"width": 8}})
+    assert c.inner.width == 8
+    with pytest.raises(ValidationError):
+        c.name = "b"
+    with pytest.raises(ValidationError):
+        _Outer.from_dict({"nam": "typo"})
+
+
+def test_config_round_trips_and_overwrites(tmp_path: Path):
+    c = _Outer.from_dict({"name": "a", "items": [1, 2]}, overwrite_values={"inner": {"width": 16}})
+    assert c.inner.width == 16 and c.items == [1, 2]
+    assert _Outer.from_str(c.as_str()) == c
+    assert json.loads(c.as_str())["inner"]["width"] == 16
+    c.save(tmp_path / "c.yml")
+    assert _Outer.from_yaml(tmp_path / "c.yml") == c
+    assert _Outer.from_yaml(tmp_path / "c.yml", overwrite_values={"name": "z"}).name == "z"
+
+
+def test_config_template_lists_every_field_with_its_description(tmp_path: Path):
+    text = _Outer.get_template_str()
+    for needle in ("name", "a name", "inner", "width", "inner width", "items"):
+        assert needle in text
+    _Outer.save_template(tmp_path / "t.yml")
+    assert (tmp_path / "t.yml").read_text()
+
+
+# ---------------------------------------------------------------------------------------------- topology
+@pytest.mark.parametrize("given,expected", [
+    (dict(world_size=8, model_parallel_size=2, pipe_parallel_size=2), dict(data_parallel_size=2)),
+    (dict(world_size=8, model_parallel_size=2, data_parallel_size=4), dict(pipe_parallel_size=1)),
+    (dict(model_parallel_size=2, pipe_parallel_size=2, data_parallel_size=3), dict(world_size=12)),
+    (dict(world_size=4, pipe_parallel_size=2, data_parallel_size=2), dict(model_parallel_size=1)),
+])
+def test_topology_infers_the_missing_parallel_size(given, expected):
+    t = TopologyConfig.from_dict(dict(given, micro_batch_size=2, gradient_accumulation_steps=1))
+    for k, v in expected.items():
+        assert getattr(t, k) == v
+    assert t.world_size == t.model_parallel_size * t.pipe_parallel_size * t.data_parallel_size
+
+
+def test_topology_batch_triple():
+    base = dict(world_size=4, model_parallel_size=1, pipe_parallel_size=1, data_parallel_size=4)
+    t = TopologyConfig.from_dict(dict(base, micro_batch_size=2, gradient_accumulation_steps=3))
+    assert t.global_batch_size == 24
+    t = TopologyConfig.from_dict(dict(base, global_batch_size=32, micro_batch_size=2))
+    assert t.gradient_accumulation_steps == 4
+    t = TopologyConfig.from_dict(dict(base, global_batch_size=32, gradient_accumulation_steps=2))
+    assert t.micro_batch_size == 4
+    with pytest.raises((ValidationError, AssertionError, ValueError)):
+        TopologyConfig.from_dict(dict(base, global_batch_size=30, micro_batch_size=2, gradient_accumulation_steps=2))
+    with pytest.raises((ValidationError, AssertionError, ValueError)):
+        TopologyConfig.from_dict(dict(world_size=8, model_parallel_size=3, pipe_parallel_size=1, micro_batch_size=1,
+                                      gradient_accumulation_steps=1))
+
+
+# ---------------------------------------------------------------------------------------------- learning rate
+def test_learning_rate_warmup_and_decay_styles():
+    def sched(style, **kw):
+        return LearningRateScheduler(LearningRateSchedulerConfig(
+            learning_rate=1.0, learning_rate_minimum=0.1, learning_rate_decay_style=style,
+            learning_rate_decay_iters=100, learning_rate_warmup_steps=10, **kw))
+
+    cos = sched(LearningRateDecayStyle.COSINE)
+    assert cos.get_lr(0) == pytest.approx(0.0)
+    assert cos.get_lr(5) == pytest.approx(0.5)
+    assert cos.get_lr(10) == pytest.approx(1.0)
+    assert cos.get_lr(55) == pytest.approx(0.55, abs=1e-6)  # halfway through the cosine
+    assert cos.get_lr(100) == pytest.approx(0.1)
+    assert cos.get_lr(10_000) == pytest.approx(0.1)
+    lin = sched(LearningRateDecayStyle.LINEAR)
+    assert lin.get_lr(55) == pytest.approx(0.55, abs=1e-6)
+    const = sched(LearningRateDecayStyle.CONSTANT)
+    assert const.get_lr(50) == pytest.approx(1.0)
+    lrs = [cos.get_lr(i) for i in range(10, 101)]
+    assert all(a >= b for a, b in zip(lrs, lrs[1:]))  # monotone after warm-up
+
+
+# ---------------------------------------------------------------------------------------------- loss scaler
+def test_loss_scaler_state_machine():
+    s = LossScaler(LossScalerConfig(enable=True, initial_scale=2.0 ** 8, window=3, hysteresis=2, factor=2.0, min_scale=1.0))
+    assert s.scale_loss(torch.tensor(1.0)).item() == 256.0
+    out = s.step(overflow=True)  # first overflow only spends hysteresis
+    assert out.overflow and out.current_loss_scale == 256.0
+    out = s.step(overflow=True)  # second one halves the scale
+    assert out.current_loss_scale == 128.0
+    for _ in range(3):
+        out = s.step(overflow=False)
+    assert out.current_loss_scale == 128.0 and out.no_overflow_steps == 3
+    out = s.step(overflow=False)  # the step after a full clean window doubles the scale
+    assert out.current_loss_scale == 256.0
+    state = s.state_dict()
+    s2 = LossScaler(LossScalerConfig(enable=True))
+    s2.load_state_dict(state)
+    assert s2.current_scale == s.current_scale
+    off = LossScaler(LossScalerConfig(enable=False))
+    assert off.scale_loss(torch.tensor(3.0)).item() == 3.0
+    assert off.step(False).current_loss_scale is None
+
+
+# ---------------------------------------------------------------------------------------------- retryable reads
+class _Flaky:
+    def __init__(self, failures: int, exc: BaseException):
+        self.failures, self.exc, self.calls = failures, exc, 0
+
+    def __call__(self, f):
+        self.calls += 1
+        if self.calls <= self.failures:
+            raise self.exc
+        return f.read()
+
+
+def test_file_handle_retries_stale_handles(tmp_path: Path, monkeypatch):
+    monkeypatch.setattr(FileHandle, "sleep", staticmethod(lambda _s: None))  # no real back-off in the test
+    path = tmp_path / "data.bin"
+    path.write_bytes(b"payload")
+    handle = FileHandle(path)
+    flaky = _Flaky(2, OSError(errno.ESTALE, "stale file handle"))
+    assert handle.retry_operation(flaky) == b"payload" and flaky.calls == 3
+    flaky = _Flaky(1, RetryableException("try again"))
+    assert handle.retry_operation(flaky) == b"payload"
+    with pytest.raises(OSError):  # other errors are not retried
+        handle.retry_operation(_Flaky(1, OSError(errno.EACCES, "denied")))
+    always = _Flaky(99, OSError(errno.ESTALE, "stale"))
+    with pytest.raises(Exception, match="even after 4 retries"):
+        handle.retry_operation(always, max_attempts=4)
+    assert always.calls == 4
+    handle.close()
+
+
+# ---------------------------------------------------------------------------------------------- partitioning
+@pytest.mark.parametrize("items,parts", [(10, 3), (4, 4), (7, 2), (16, 5), (3, 1)])
+def test_uniform_partition_covers_all_layers(items, parts):
+    coords = pipe_partition_uniform(items, parts)
+    assert len(coords) == parts and coords[0].start == 0 and coords[-1].end == items
+    assert all(a.end == b.start for a, b in zip(coords, coords[1:]))
+    lengths = [c.length for c in coords]
+    assert max(lengths) - min(lengths) <= 1 and lengths == sorted(lengths, reverse=True)  # remainder goes first
+
+
+def test_manual_and_balanced_partitions():
+    assert pipe_partition_from_indices([0, 3, 5, 9], num_layers=9) == [
+        PipePartitionCoordinates(0, 3), PipePartitionCoordinates(3, 5), PipePartitionCoordinates(5, 9)]
+    with pytest.raises(ValueError):
+        pipe_partition_from_indices([0, 3, 5], num_layers=9)  # the last boundary has to be the layer count
+    bounds = balanced_boundaries([10, 1, 1, 1, 1, 10], 3)
+    assert bounds[0] == 0 and bounds[-1] == 6 and len(bounds) == 4
+    loads = [sum([10, 1, 1, 1, 1, 10][a:b]) for a, b in zip(bounds, bounds[1:])]
+    assert max(loads) == 10  # the optimum: no stage heavier than the heaviest single layer
+
+
+# ---------------------------------------------------------------------------------------------- runner
+def test_runner_parses_hosts():
+    cfg = RunnerConfig(default_gpu_count=8)
+    assert parse_host(cfg, "node-1 slots=4") == ("node-1", [0, 1, 2, 3])
+    assert parse_host(cfg, "node-2 slots=0,2,5") == ("node-2", [0, 2, 5])
+    assert parse_host(cfg, "node-3") == ("node-3", list(range(8)))
+    pool = hosts_str_to_resource_pool(cfg, ["a slots=2", "b slots=1"])
+    assert list(pool.items()) == [("a", [0, 1]), ("b", [0])]
+    with pytest.raises((ValueError, AssertionError)):
+        hosts_str_to_resource_pool(cfg, ["a slots=2", "a slots=2"])

@@ -426,3 +426,35 @@ def test_flash_attention_strided_qkv():
     ref = attention_reference(q.float(), k.float(), v.float(), cu, None, True, D ** -0.5)
     K.check_status()
     assert _rel(out, ref) < 2e-2
+
+
+def test_peer_barrier_wait_runs_out_and_reports_timeout():
+    """A flag that nobody sets: the bounded wait gives up, the host sees CommTimeout, the context stays usable."""
+    import ctypes
+    import time
+
+    from scaling_b200.ops import _lib
+    from scaling_b200.ops._lib import CommTimeout, lib
+
+    mine = torch.zeros(16, dtype=torch.int32, device=DEV)    # this rank's flag words
+    peer = torch.zeros(16, dtype=torch.int32, device=DEV)    # stands in for a peer that never arrives
+    rounds = torch.zeros(1, dtype=torch.int32, device=DEV)
+    ptrs = (ctypes.c_void_p * 2)(mine.data_ptr(), peer.data_ptr())
+    K.check_status()
+    t0 = time.time()
+    rc = lib().sb200_p2p_barrier(ptrs, rounds.data_ptr(), 0, 2, K.status_word().data_ptr(), 0.05, _lib.stream())
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert time.time() - t0 < 5.0
+    assert peer[0].item() == 1 and mine[0].item() == 1 and mine[1].item() == 0  # signalled both, heard from itself only
+    with pytest.raises(CommTimeout):
+        K.check_status()
+    K.check_status()  # the status word was cleared
+    x = torch.randn(64, 64, device=DEV, dtype=torch.bfloat16)
+    assert torch.isfinite(K.gemm(x, x).float()).all()  # kernels still run
+    # a complete round: both "ranks" set each other's flags
+    peer.zero_(); mine.zero_(); rounds.zero_()
+    mine[1] = 1
+    rc = lib().sb200_p2p_barrier(ptrs, rounds.data_ptr(), 0, 2, K.status_word().data_ptr(), 0.05, _lib.stream())
+    torch.cuda.synchronize()
+    K.check_status()
