@@ -175,6 +175,14 @@ class ColumnParallelLinear(_ParallelLinear):
         """``activation="gelu"`` fuses the exact GELU into the GEMM epilogue (parallel output only)."""
         # the backward of the identity below is the all-reduce of dX; in sequence-parallel mode the
         # caller gathers tokens before and reduce-scatters the gradient instead
+        if (self._distributed() and not self.topology.config.sequence_parallel  # type: ignore[union-attr]
+                and not self._use_umup and self.fp8_config is None and (self.parallel_output or activation == "none")):
+            # the all-reduce of the input gradient runs inside the dgrad GEMM where the group supports it
+            from ....parallel.fused_tp import column_parallel_linear
+
+            y = column_parallel_linear(x, self.weight, self._bias(), activation, self.topology)
+            if y is not None:
+                return y if self.parallel_output else all_concat(y, self.topology)
         if self._distributed() and not self.topology.config.sequence_parallel:  # type: ignore[union-attr]
             x = copy_to_tensor_model_parallel_region(x, self.topology)
         if self._use_umup:

@@ -161,3 +161,69 @@ def row_parallel_linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.T
     if ws is None or M * N > ws.max_elements:
         return None
     return _RowParallelLinearFn.apply(x, w, bias, ws)
+
+
+class _ColumnParallelLinearFn(torch.autograd.Function):
+    """Column-parallel ``act(x @ w^T + b)``: no communication forward; the input gradient ``dy @ w`` is summed over the
+    tensor-parallel ranks inside the GEMM kernel (the backward of the identity that feeds replicated activations into
+    a column-parallel layer)."""
+
+    @staticmethod
+    def forward(ctx, x, w, bias, act: str, ws: FusedTPWorkspace):  # type: ignore[override]
+        x2 = x.reshape(-1, x.shape[-1])
+        if not x2.is_contiguous():
+            x2 = x2.contiguous()
+        pre = torch.empty((x2.shape[0], w.shape[0]), dtype=x.dtype, device=x.device) if act == "gelu" else None
+        y = K.gemm(x2, w, bias=bias, act=act, pre_act_out=pre)
+        ctx.save_for_backward(x2, w, pre)
+        ctx.weight, ctx.bias, ctx.act, ctx.ws, ctx.x_shape = w, bias, act, ws, x.shape
+        return y.view(*x.shape[:-1], w.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):  # type: ignore[override]
+        x2, w, pre = ctx.saved_tensors
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        if ctx.act == "gelu":
+            dy2 = K.gelu_backward(dy2, pre)
+        dx = dw = db = None
+        if ctx.needs_input_grad[0]:
+            dx = ctx.ws.gemm_allreduce(dy2, w, None, b_mn=True).view(ctx.x_shape)
+        if ctx.needs_input_grad[1]:
+            main = K.fused_grad_target(ctx.weight)
+            if main is not None and main.dtype in (torch.float32, dy2.dtype):
+                K.gemm(dy2, x2, a_mn=True, b_mn=True, out=main, accumulate=True)
+            else:
+                dw = K.gemm(dy2, x2, a_mn=True, b_mn=True)
+        if ctx.bias is not None and ctx.needs_input_grad[2]:
+            main = K.fused_grad_target(ctx.bias)
+            if main is not None and main.dtype == dy2.dtype:
+                K.column_sum(dy2, out=main, accumulate=True)
+            else:
+                db = K.column_sum(dy2)
+        return dx, dw, db, None, None
+
+
+def column_parallel_linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], act: str,
+                           topology: Any) -> Optional[torch.Tensor]:
+    """Column-parallel linear whose input-gradient all-reduce is fused into the dgrad GEMM, or None when the caller
+    has to take the unfused path (``x`` must be the replicated activation itself, not the output of the identity
+    whose backward reduces)."""
+    if not (x.is_cuda and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.is_contiguous()):
+        return None
+    if not x.requires_grad or act not in ("none", "gelu"):
+        return None
+    M = x.numel() // x.shape[-1]
+    N, Kd = w.shape
+    if N % 8 or Kd % 8 or (bias is not None and bias.dtype != torch.bfloat16):
+        return None
+    mode = os.environ.get("SB200_FUSED_TP", "1")
+    if mode != "always" and M * Kd > FUSED_TP_MAX_ELEMENTS:
+        return None
+    if (M + 127) // 128 * ((Kd + 127) // 128) > FLAG_STRIDE:
+        return None
+    ws = workspace_for(topology, M * Kd)
+    if ws is None or M * Kd > ws.max_elements:
+        return None
+    return _ColumnParallelLinearFn.apply(x, w, bias, act, ws)

@@ -90,3 +90,37 @@ def test_transformer_resume_is_bit_identical(tmp_path: Path, layout):
     full = losses(ws, iters=6, save_dir=str(tmp_path), save_interval=4, **layout)
     resumed = losses(ws, iters=6, load_dir=str(tmp_path), **layout)
     assert resumed == full[4:], (resumed, full[4:])
+
+
+LLAMA_ARCH = {"norm_type": "rms", "mlp_type": "swiglu", "mlp_factor": 2.5, "attention_bias": False, "mlp_bias": False,
+              "attention_qkv_in_one": False, "attention_num_kv_heads": 2, "num_attention_heads": 4,
+              "relative_position_embedding_type": "rotary_complex"}
+
+
+@pytest.mark.dist
+def test_llama_style_architecture_layouts_agree(tmp_path: Path):
+    """RMSNorm + SwiGLU + grouped-query attention + interleaved rotary, with activation checkpointing: tensor,
+    sequence and pipeline parallel layouts reproduce the single-process losses."""
+    init = str(tmp_path / "init")
+    base = losses(1, save_initial=init, arch=LLAMA_ARCH)
+    for kw in (dict(world_size=2, mp=2, ckpt="every_layer"), dict(world_size=2, mp=2, sp=True),
+               dict(world_size=2, pp=2, ga=2, micro=2, ckpt="every_layer"), dict(world_size=2, zero=True)):
+        ws = kw.pop("world_size")
+        got = losses(ws, load_dir=init, arch=LLAMA_ARCH, **kw)
+        for a, b in zip(got, base):
+            assert abs(a - b) < 2e-4 * max(1.0, abs(b)), (kw, got, base)
+
+
+@pytest.mark.dist
+def test_lora_finetuning_trains_only_the_adapters(tmp_path: Path):
+    """LoRA on q/k/v/dense with a frozen base under tensor parallelism: the losses agree with one process."""
+    arch = dict(LLAMA_ARCH, lora_config={"name": "lora", "rank": 4, "alpha": 8,
+                                         "parallel_modules": ["query", "key", "value", "dense"]})
+    groups = [{"group_name": "lora", "parameters_include": ["lora"], "weight_decay": 0.0,
+               "learning_rate_scheduler": {"learning_rate": 1e-2, "learning_rate_decay_style": "constant"}}]
+    training = {"allow_missing_params_in_optimizer": True}
+    init = str(tmp_path / "init")
+    base = losses(1, save_initial=init, arch=arch, groups=groups, training=training, iters=8)
+    got = losses(2, mp=2, load_dir=init, arch=arch, groups=groups, training=training, iters=8)
+    for a, b in zip(got, base):
+        assert abs(a - b) < 2e-4 * max(1.0, abs(b)), (got, base)
