@@ -31,6 +31,30 @@ MODEL = dict(vocab_size=32768, hidden_size=768, num_layers=12, num_attention_hea
              mlp_factor=4.0)
 MICRO_BATCH = 8
 
+LLAMA = dict(norm_type="rms", mlp_type="swiglu", attention_bias=False, mlp_bias=False, attention_qkv_in_one=False,
+             relative_position_embedding_type="rotary_complex")
+LORA = {"name": "lora", "rank": 16, "alpha": 32, "parallel_modules": ["query", "key", "value", "dense"]}
+# name -> (label, architecture, micro batch, global batch per step (None: micro x dp), tensor-parallel size,
+#          pipeline stages, activation checkpointing, trains only the LoRA weights)
+CONFIGS = {
+    "125m": dict(label="decoder-125M (12L, h768, 12 heads, vocab 32768, LayerNorm, GELU, RoPE)",
+                 arch=dict(MODEL, norm_type="layernorm", mlp_type="default", relative_position_embedding_type="rotary"),
+                 micro=MICRO_BATCH, global_batch=None, mp=1, pp=1, ckpt="disabled", lora=False),
+    "7b": dict(label="llama-7B (32L, h4096, 32q/8kv heads of 128, vocab 65536, RMSNorm, SwiGLU 11008, RoPE)",
+               arch=dict(LLAMA, vocab_size=65536, hidden_size=4096, num_layers=32, num_attention_heads=32,
+                         attention_num_kv_heads=8, sequence_length=4096, mlp_factor=11008 / 4096),
+               micro=1, global_batch=64, mp=4, pp=1, ckpt="every_layer", lora=False),
+    "7b_lora": dict(label="llama-7B frozen + LoRA r16 on q/k/v/o, seq 8192",
+                    arch=dict(LLAMA, vocab_size=65536, hidden_size=4096, num_layers=32, num_attention_heads=32,
+                              attention_num_kv_heads=8, sequence_length=8192, mlp_factor=11008 / 4096,
+                              lora_config=LORA),
+                    micro=1, global_batch=32, mp=8, pp=1, ckpt="every_layer", lora=True),
+    "13b": dict(label="13B MQA (40L, h5120, 40q/1kv heads of 128, vocab 65536, RMSNorm, SwiGLU 13824, RoPE)",
+                arch=dict(LLAMA, vocab_size=65536, hidden_size=5120, num_layers=40, num_attention_heads=40,
+                          attention_num_kv_heads=1, sequence_length=4096, mlp_factor=13824 / 5120),
+                micro=1, global_batch=32, mp=2, pp=2, ckpt="every_layer", lora=False),
+}
+
 
 def parse_args() -> argparse.Namespace:
     p = argparse.ArgumentParser()
@@ -38,7 +62,42 @@ def parse_args() -> argparse.Namespace:
     p.add_argument("--steps", type=int, default=10)
     p.add_argument("--warmup", type=int, default=3)
     p.add_argument("--impl", type=str, default="ours", choices=["ours", "reference"])
+    p.add_argument("--config", type=str, default="125m", choices=sorted(CONFIGS),
+                   help="model and layout; the tensor/pipeline sizes shrink to what --gpus allows")
+    p.add_argument("--grad-accum", type=int, default=None,
+                   help="micro batches per step and data-parallel rank (default: from the config's global batch)")
+    p.add_argument("--layers", type=int, default=None, help="override the layer count (exploration only)")
     return p.parse_args()
+
+
+def layout(args: argparse.Namespace, world: int) -> dict:
+    """Resolve the named config against the number of ranks: parallel sizes, accumulation steps, labels."""
+    c = CONFIGS[args.config]
+    pp = c["pp"] if world % c["pp"] == 0 and world >= c["pp"] * min(c["mp"], 2) else 1
+    mp = c["mp"]
+    while mp > 1 and (world // pp) % mp:
+        mp //= 2
+    dp = world // (mp * pp)
+    ga = args.grad_accum or (max(1, c["global_batch"] // (c["micro"] * dp)) if c["global_batch"] else 1)
+    arch = dict(c["arch"])
+    if args.layers:
+        arch["num_layers"] = args.layers
+    par = "+".join(f"{k}{v}" for k, v in (("tp", mp), ("pp", pp), ("dp", dp)) if v > 1 or k == "dp") + "+zero1"
+    return dict(c, arch=arch, mp=mp, pp=pp, dp=dp, ga=ga, parallelism=par)
+
+
+def model_flops_per_token(arch: dict, trains_base: bool) -> float:
+    """Forward+backward model FLOPs per token (no recomputation counted): 6 per weight of the blocks and the head
+    (4 when the base is frozen: no weight gradients), plus causal attention 6 * layers * seq * hidden."""
+    h, L, s, V = arch["hidden_size"], arch["num_layers"], arch["sequence_length"], arch["vocab_size"]
+    heads = arch["num_attention_heads"]
+    kv = arch.get("attention_num_kv_heads") or heads
+    d = h // heads
+    attn = h * heads * d + 2 * h * kv * d + heads * d * h
+    inner = int(round(arch.get("mlp_factor", 4.0) * h))
+    mlp = (3 if arch.get("mlp_type") == "swiglu" else 2) * h * inner
+    weights = L * (attn + mlp) + V * h
+    return (6.0 if trains_base else 4.0) * weights + 6.0 * L * s * h
 
 
 # ---------------------------------------------------------------------------------------------- clocks
@@ -97,16 +156,18 @@ def dist_env(args: argparse.Namespace) -> tuple[int, int, int]:
     return rank, world, local
 
 
-def result_line(args, world, tokens_per_step, dev_ms, e2e_ms, clocks, launches, h2d, d2h, impl) -> dict:
+def result_line(args, world, tokens_per_step, dev_ms, e2e_ms, clocks, launches, h2d, d2h, impl, lay=None) -> dict:
+    lay = lay or layout(args, world)
     value = tokens_per_step / (dev_ms / 1000.0)
     e2e = tokens_per_step / (e2e_ms / 1000.0)
     return {
         "metric": "train tokens/s", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": dev_ms, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": impl,
-        "config": {"model": "decoder-125M (12L, h768, 12 heads, vocab 32768, LayerNorm, GELU, RoPE)",
-                   "global_batch": MICRO_BATCH * world, "seq_len": MODEL["sequence_length"],
-                   "parallelism": f"dp{world}" + ("+zero1" if True else ""), "micro_batch": MICRO_BATCH,
+        "config": {"model": lay["label"], "global_batch": lay["micro"] * lay["dp"] * lay["ga"],
+                   "seq_len": lay["arch"]["sequence_length"], "parallelism": lay["parallelism"],
+                   "micro_batch": lay["micro"], "gradient_accumulation_steps": lay["ga"],
+                   "activation_checkpointing": lay["ckpt"],
                    "l2": "inputs and activations per step exceed L2 (>1 GB touched per step)"},
         "clocks": clocks,
         "e2e": {"value": e2e, "unit": "tokens/s", "ms_per_step": e2e_ms, "h2d_bytes_per_step": h2d,
@@ -131,15 +192,20 @@ def run_ours(args: argparse.Namespace) -> None:
     from scaling_b200.core.data import DataLoader
 
     rank, world, local = dist_env(args)
+    lay = layout(args, world)
+    arch, micro, ga, dp = lay["arch"], lay["micro"], lay["ga"], lay["dp"]
+    group = {"group_name": "all", "weight_decay": 0.1,
+             "learning_rate_scheduler": {"learning_rate": 3e-4, "learning_rate_decay_style": "constant"}}
+    if lay["lora"]:
+        group = dict(group, group_name="lora", parameters_include=["lora"], weight_decay=0.0)
     cfg = TransformerConfig.from_dict({
-        "topology": {"world_size": world, "global_rank": rank, "local_slot": local, "model_parallel_size": 1,
-                     "pipe_parallel_size": 1, "data_parallel_size": world, "micro_batch_size": MICRO_BATCH,
-                     "gradient_accumulation_steps": 1},
+        "topology": {"world_size": world, "global_rank": rank, "local_slot": local, "model_parallel_size": lay["mp"],
+                     "pipe_parallel_size": lay["pp"], "data_parallel_size": dp, "micro_batch_size": micro,
+                     "gradient_accumulation_steps": ga, "activation_checkpointing_type": lay["ckpt"]},
         "optimizer": {"zero": True, "gradient_clipping": 1.0, "beta1": 0.9, "beta2": 0.95},
-        "training_groups": [{"group_name": "all", "weight_decay": 0.1,
-                             "learning_rate_scheduler": {"learning_rate": 3e-4, "learning_rate_decay_style": "constant"}}],
-        "transformer_architecture": dict(MODEL, precision="bfloat16", norm_type="layernorm", mlp_type="default",
-                                         relative_position_embedding_type="rotary", weight_tying=False,
+        "training_groups": [group],
+        "training": {"allow_missing_params_in_optimizer": True} if lay["lora"] else {},
+        "transformer_architecture": dict(arch, precision="bfloat16", weight_tying=False,
                                          masked_softmax={"kernel": "flash_attention"}, causal=True),
         "trainer": {"seed": 42},
     })
@@ -149,19 +215,21 @@ def run_ours(args: argparse.Namespace) -> None:
     model = init_model(context)
     optimizer = init_optimizer(context, model)
     loss_fn = create_loss_function(context, cfg.training.loss_function_config)
-    seq = MODEL["sequence_length"]
+    seq = arch["sequence_length"]
     total_steps = 2 * (args.steps + args.warmup) + 2
-    dataset = SyntheticTextDataset(n_samples=MICRO_BATCH * world * total_steps, sequence_length=seq,
-                                   vocab_size=MODEL["vocab_size"], seed=42, low=1)
-    loader = DataLoader(seed=42, consumed_samples=0, dataset=dataset, topology=topology, pin_memory=True)
+    dataset = SyntheticTextDataset(n_samples=micro * dp * ga * total_steps, sequence_length=seq,
+                                   vocab_size=arch["vocab_size"], seed=42, low=1)
+    loader = DataLoader(seed=42, consumed_samples=0, dataset=dataset, topology=topology, pin_memory=True) \
+        if topology.is_io_rank else None
     sync = SyntheticTextDataset.sync_batch_to_model_parallel
     dev = topology.device
 
     # device-resident batches for the kernel-only measurement
     staged = []
-    for _ in range(args.steps + args.warmup):
-        b = next(loader)
-        staged.append(b.token_ids.to(dev))
+    if loader is not None:
+        for _ in range(min(args.steps + args.warmup, 8) * ga):
+            b = next(loader)
+            staged.append(b.token_ids.to(dev))
     torch.cuda.synchronize()
 
     class Staged:
@@ -193,7 +261,7 @@ def run_ours(args: argparse.Namespace) -> None:
         ms = torch.tensor([e0.elapsed_time(e1) / n_steps], device=dev)
         if world > 1:
             dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-        assert out.loss is not None and out.loss == out.loss, "loss is NaN"
+        assert out.loss is None or out.loss == out.loss, "loss is NaN"
         return float(ms.item())
 
     sampler = ClockSampler(local)
@@ -202,8 +270,8 @@ def run_ours(args: argparse.Namespace) -> None:
     calls0 = None
     # kernel-only: inputs resident on the device
     for _ in range(args.warmup):
-        model.train_step(Staged(), optimizer, sync_staged, loss_fn, metrics_aggregation_fn)
-    st = Staged()
+        model.train_step(Staged() if staged else None, optimizer, sync_staged, loss_fn, metrics_aggregation_fn)
+    st = Staged() if staged else None
     barrier()
     calls0 = _lib.kernel_calls()
     dev_ms = timed(0, args.steps, st, sync_staged)
@@ -213,11 +281,14 @@ def run_ours(args: argparse.Namespace) -> None:
     clocks = sampler.stop() if rank == 0 else {}
     K.check_status()
     if rank == 0:
-        tokens = MICRO_BATCH * seq * world
-        h2d = MICRO_BATCH * (seq + 1) * 8
-        line = result_line(args, world, tokens, dev_ms, e2e_ms, clocks, launches, h2d, 4, "ours")
+        tokens = micro * seq * dp * ga
+        h2d = micro * ga * (seq + 1) * 8
+        line = result_line(args, world, tokens, dev_ms, e2e_ms, clocks, launches, h2d, 4 * ga, "ours", lay)
         line["config"]["data_parallel_exchange"] = optimizer.data_parallel_exchange
         line["config"]["cuda_graph"] = bool(getattr(model, "_graph", None) is not None)
+        tflops = model_flops_per_token(arch, not lay["lora"]) * line["value"] / world / 1e12
+        line["config"]["model_tflops_per_gpu"] = round(tflops, 1)
+        line["config"]["mfu_of_nominal_2250"] = round(tflops / 2250.0, 4)
         print(json.dumps(line), flush=True)
     shutdown(model, world)
 
@@ -256,6 +327,9 @@ def main() -> None:
         import faulthandler
 
         faulthandler.dump_traceback_later(watchdog, exit=True)
+    if args.impl == "reference" and args.config != "125m":
+        print(json.dumps({"impl": "reference", "unavailable": "the reference arm runs the 125M headline config only"}))
+        return
     if args.impl == "reference":
         sys.path.insert(0, str(ROOT))
         from baseline.reference_arm import run_reference

@@ -78,6 +78,8 @@ def broadcast_data(tensors: list[Optional[torch.Tensor]], dtype: torch.dtype, to
             assert t is not None and t.dtype == dtype, (
                 f"broadcast_data requires a list of tensors of the same dtype; expected {dtype} got {getattr(t, 'dtype', None)}"
             )
+        if len({t.device for t in tensors}) > 1:  # type: ignore[union-attr]
+            tensors = [t.to(dev, non_blocking=True) for t in tensors]  # type: ignore[union-attr]
         flat = torch.cat([t.contiguous().view(-1) for t in tensors]).to(wire_dtype).to(dev, non_blocking=True)  # type: ignore[union-attr]
     else:
         flat = torch.empty(sum(numels), dtype=wire_dtype, device=dev)

@@ -20,7 +20,7 @@ import torch
 
 from ....ops import functional as K
 from ....ops.attention import attention_mask_from_cu_seqlens, flash_attention
-from ....parallel.collectives import all_concat, all_reduce_scatter_to_sequence_parallel, all_shard
+from ....parallel.collectives import SequenceShard, all_concat, all_reduce_scatter_to_sequence_parallel, all_shard
 from ....parallel.topology import Topology
 from ..linear import ColumnParallelLinear, RowParallelLinear, get_device
 from ..lora import LoRaConfig, LoRAModuleType, ParallelLoRa
@@ -371,6 +371,9 @@ class ParallelSelfAttention(torch.nn.Module):
                 doc_ranges: Optional[tuple[torch.Tensor, torch.Tensor]] = None) -> torch.Tensor:
         """``doc_ranges`` (per-token document start / end, int32) may stand in for ``cumulative_seq_lengths`` on
         the fused attention path; it is what a captured CUDA graph passes, since it has a fixed shape."""
+        if isinstance(x, SequenceShard) and (use_cache or reset_cache or
+                                             (self.lora_config is not None and not self.lora_merged_state)):
+            x = x.gathered()  # something besides the projections reads the input
         b, s, _ = x.shape
         T = b * s
         d = self.hidden_size_per_attention_head
@@ -487,10 +490,13 @@ class ParallelSelfAttention(torch.nn.Module):
         if self.lora_config and not self.lora_merged_state and LoRAModuleType.DENSE in self.lora_config.parallel_modules:
             full = all_concat(hidden, self.topology) if self.model_parallel_size > 1 else hidden
             lora_dense = self.lora_modules[f"dense_{self.lora_config.name}"](full)
+        sp = self.topology is not None and self.topology.config.sequence_parallel
+        if sp and lora_dense is None:
+            return self.dense.forward_to_sequence_parallel(hidden)
         out = self.dense(hidden)
         if lora_dense is not None:
             out = out + lora_dense
-        if self.topology is not None and self.topology.config.sequence_parallel:
+        if sp:
             out = all_reduce_scatter_to_sequence_parallel(out, self.topology)
         return out
 

@@ -17,6 +17,7 @@ import torch
 
 from ....ops import functional as K
 from ....parallel.collectives import (
+    SequenceShard,
     all_concat,
     all_reduce,
     all_shard,
@@ -175,6 +176,17 @@ class ColumnParallelLinear(_ParallelLinear):
         """``activation="gelu"`` fuses the exact GELU into the GEMM epilogue (parallel output only)."""
         # the backward of the identity below is the all-reduce of dX; in sequence-parallel mode the
         # caller gathers tokens before and reduce-scatters the gradient instead
+        if isinstance(x, SequenceShard):
+            y = None
+            if (self._distributed() and not self._use_umup and self.fp8_config is None
+                    and (self.parallel_output or activation == "none")):
+                from ....parallel.fused_tp import column_parallel_linear_sp
+
+                y = column_parallel_linear_sp(x.shard, self.weight, self._bias(), activation, self.topology,
+                                              list(x.shape))
+            if y is not None:
+                return y if self.parallel_output else all_concat(y, self.topology)
+            x = x.gathered()
         if (self._distributed() and not self.topology.config.sequence_parallel  # type: ignore[union-attr]
                 and not self._use_umup and self.fp8_config is None and (self.parallel_output or activation == "none")):
             # the all-reduce of the input gradient runs inside the dgrad GEMM where the group supports it
@@ -225,6 +237,22 @@ class RowParallelLinear(_ParallelLinear):
         b = self._bias()
         if b is not None and self._bias_on_first_rank_only:
             b.reduce_grad_over_model_parallel = True  # type: ignore[attr-defined]
+
+    def forward_to_sequence_parallel(self, x: torch.Tensor) -> torch.Tensor:
+        """``forward`` followed by the reduce-scatter over tokens (sequence parallelism; this layer was built with
+        ``parallel_output=True``): one kernel where the group supports it."""
+        from ....parallel.collectives import _sp_out_shape, all_reduce_scatter_to_sequence_parallel
+
+        if (self.parallel_input and self.parallel_output and not self._use_umup and self.fp8_config is None
+                and self._distributed() and x.dim() == 3):
+            from ....parallel.fused_tp import row_parallel_linear_sp
+
+            out_shape = _sp_out_shape(x.shape, self.model_parallel_size, gather=False)
+            out_shape[-1] = self.out_features
+            y = row_parallel_linear_sp(x, self.weight, self._bias(), self.topology, out_shape)
+            if y is not None:
+                return y
+        return all_reduce_scatter_to_sequence_parallel(self.forward(x), self.topology)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         if self.model_parallel_size > 1 and not self.parallel_input:

@@ -50,10 +50,9 @@ class _MLPBase(torch.nn.Module):
         self.output_scale_factor = 1.0
 
     def _project_out(self, x: torch.Tensor) -> torch.Tensor:
-        x = self.dense_out(x)
         if self.topology is not None and self.topology.config.sequence_parallel:
-            x = all_reduce_scatter_to_sequence_parallel(x, self.topology)
-        return x
+            return self.dense_out.forward_to_sequence_parallel(x)
+        return self.dense_out(x)
 
 
 class ParallelMLP(_MLPBase):

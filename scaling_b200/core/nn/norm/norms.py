@@ -16,7 +16,7 @@ import torch
 from pydantic import Field
 
 from ....ops import functional as K
-from ....parallel.collectives import gather_from_sequence_parallel_region
+from ....parallel.collectives import SequenceShard, gather_from_sequence_parallel_region
 from ....parallel.topology import Topology
 from ...config import BaseConfig
 from ..parameter_meta import UMUP_WEIGHT_TYPE, CoreParameterMeta, UMuPParameterMeta
@@ -86,6 +86,9 @@ class _Norm(torch.nn.Module):
         if self._use_umup:
             y = scale_fwd(y, self.forward_multiplier)
         if self.topology is not None and self.topology.config.sequence_parallel:
+            if getattr(self, "defer_gather", False) and not self._forward_hooks:
+                # the linears behind this norm gather inside their GEMM (or once, on first need)
+                return SequenceShard(y, self.topology)  # type: ignore[return-value]
             y = gather_from_sequence_parallel_region(y, self.topology)
         return y
 

@@ -52,7 +52,18 @@ struct ArParams {
   int flag_stride;
   int rank, W;
   unsigned long long timeout_ns;
+  // mode 0: all-reduce.  mode 1: reduce-scatter along the rows, rank r keeps rows [r * shard_rows, (r + 1) *
+  // shard_rows) in out[rank] ([shard_rows, ld_out], local memory is enough).  mode 2: all-gather of the A operand:
+  // every rank pushes its [shard_rows, K] shard a_src into the rows [rank * shard_rows, ...) of partial[q] ([M, K])
+  // of every rank q, and the tile loads of a row block wait for its arrival; the output is a plain local GEMM result.
+  int mode;
+  int shard_rows;
+  int unit_shift;     // tiles are visited from this one on (modulo their number): a different start on every rank
+  long ld_out;
+  const void* a_src;
+  long lda_src;
 };
+constexpr int AR_ALLREDUCE = 0, AR_REDUCE_SCATTER = 1, AR_ALLGATHER = 2;
 
 struct GemmParams {
   void* C;
@@ -227,6 +238,9 @@ __global__ void __launch_bounds__(FUSE ? GEMM_THREADS + REDUCER_THREADS : GEMM_T
   const int S = p.splits;
   const int num_units = m_tiles * n_tiles * S;
   const uint32_t epoch = FUSE ? *p.ar.epoch + 1 : 0;  // identifies this launch in the peers' flag words
+  const int ushift = FUSE ? p.ar.unit_shift : 0;
+  // position in this worker's sequence -> unit (tile, split); fused launches start at a rank-specific tile
+  auto unit_at = [&](int i) { return FUSE ? (i + ushift) % num_units : i; };
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -264,11 +278,22 @@ __global__ void __launch_bounds__(FUSE ? GEMM_THREADS + REDUCER_THREADS : GEMM_T
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int unit = worker; unit < num_units && ok; unit += num_workers) {
+      for (int it = worker; it < num_units && ok; it += num_workers) {
+        const int unit = unit_at(it);
         const int tile = unit / S, split = unit - tile * S;
         const int m_blk = (tile / n_tiles) * CTAS + rank, n_blk = tile % n_tiles;
         const int kb0 = (int)((long)split * num_kb / S), kb1 = (int)((long)(split + 1) * num_kb / S);
         const int b_col0 = n_blk * BN + rank * LOAD_BN;  // first output column whose B rows this CTA loads
+        if (FUSE && p.ar.mode == AR_ALLGATHER) {
+          // the rows of this block come from rank `src`: wait until its gather warps have delivered them
+          const int src = (m_blk * BM) / p.ar.shard_rows, rb = (m_blk * BM - src * p.ar.shard_rows) / BM;
+          if (!sb::wait_flag_ge(p.ar.flags[p.ar.rank] + (long)src * p.ar.flag_stride + rb, epoch, p.ar.timeout_ns)) {
+            *abort_flag = 1;
+            ok = false;
+            break;
+          }
+          sb::fence_proxy_async_global();
+        }
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!sb::mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag)) { ok = false; break; }
           uint8_t* a_s = smem + stage * Cfg::STAGE_BYTES;
@@ -321,7 +346,8 @@ __global__ void __launch_bounds__(FUSE ? GEMM_THREADS + REDUCER_THREADS : GEMM_T
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
-      for (int unit = worker; unit < num_units && ok; unit += num_workers) {
+      for (int it = worker; it < num_units && ok; it += num_workers) {
+        const int unit = unit_at(it);
         const int tile = unit / S, split = unit - tile * S;
         const int kb0 = (int)((long)split * num_kb / S), kb1 = (int)((long)(split + 1) * num_kb / S);
         if (!sb::mbar_wait(&tempty_bar[acc], acc_phase ^ 1, abort_flag)) { ok = false; break; }
@@ -381,7 +407,8 @@ __global__ void __launch_bounds__(FUSE ? GEMM_THREADS + REDUCER_THREADS : GEMM_T
       if (PAIR) sb::mbar_arrive_cluster(tempty_leader[a]);
       else sb::mbar_arrive(&tempty_bar[a]);
     };
-    for (int unit = worker; unit < num_units; unit += num_workers) {
+    for (int it = worker; it < num_units; it += num_workers) {
+      const int unit = unit_at(it);
       const int tile = unit / S;
       const int m_blk = (tile / n_tiles) * CTAS + rank, n_blk = tile % n_tiles;
       const int ctile = tile * CTAS + rank;  // this CTA's part of the tile: index of its counter and partial slots
@@ -587,14 +614,15 @@ __global__ void __launch_bounds__(FUSE ? GEMM_THREADS + REDUCER_THREADS : GEMM_T
         __syncwarp();
         if (lane == 0) release_acc(acc_used);
       }
-      if (FUSE) {
+      if (FUSE && p.ar.mode != AR_ALLGATHER) {
         // the partial tile is complete in memory before its owner is told so
         if (lane == 0) sb::tma_store_wait_all0();
         __syncwarp();
         __threadfence_system();
         epi_bar_sync();
         if (et == 0) {
-          const int owner = (tile + rank) % p.ar.W;  // rotated per CTA of a pair: every CTA owns 1 / W of its tiles
+          // all-reduce: rotated per CTA of a pair, every CTA owns 1 / W of its tiles; reduce-scatter: by row range
+          const int owner = p.ar.mode == AR_REDUCE_SCATTER ? (m_blk * BM) / p.ar.shard_rows : (tile + rank) % p.ar.W;
           sb::st_release_sys(p.ar.flags[owner] + (long)p.ar.rank * p.ar.flag_stride + ctile, epoch);
         }
       }
@@ -610,10 +638,61 @@ __global__ void __launch_bounds__(FUSE ? GEMM_THREADS + REDUCER_THREADS : GEMM_T
     const ArParams& ar = p.ar;
     constexpr int VPR = BN / 8;  // 16-byte vectors per tile row
     bool rok = true;
-    for (int unit = worker; unit < num_units; unit += num_workers) {
+    if (ar.mode == AR_ALLGATHER) {
+      // ---------------------------------------------------------- gather: push this rank's rows of A to every rank
+      // A rank may be written to only once it has entered this launch: everything that read its copy of the
+      // gathered operand before (earlier kernels of its stream) has finished by then.
+      uint32_t* entered = ar.flags[ar.rank] + (long)(ar.W + 1) * ar.flag_stride;
+      if (blockIdx.x == 0 && rt < ar.W)
+        sb::st_release_sys(ar.flags[rt] + (long)(ar.W + 1) * ar.flag_stride + ar.rank, epoch);
+      if (rt < ar.W && !sb::wait_flag_ge(entered + rt, epoch, ar.timeout_ns)) *abort_flag = 1;
+      red_bar_sync();
+      if (*abort_flag) rok = false;
+      const int kvec = p.K / 8;  // 16-byte vectors per row
+      const int blocks = (ar.shard_rows + BM - 1) / BM;
+      const uint16_t* src = reinterpret_cast<const uint16_t*>(ar.a_src);
+      for (int rb = blockIdx.x; rb < blocks && rok; rb += gridDim.x) {
+        const int r0 = rb * BM;
+        const int nrows = ar.shard_rows - r0 < BM ? ar.shard_rows - r0 : BM;
+        const int total = nrows * kvec;
+        constexpr int UNR = 8;
+        for (int base = rt; base < total; base += REDUCER_THREADS * UNR) {
+          uint4 v[UNR];
+          long doff[UNR];
+          bool valid[UNR];
+#pragma unroll
+          for (int j = 0; j < UNR; ++j) {
+            const int idx = base + j * REDUCER_THREADS;
+            valid[j] = idx < total;
+            const int row = r0 + idx / kvec, col = (idx % kvec) * 8;
+            doff[j] = ((long)ar.rank * ar.shard_rows + row) * p.K + col;
+            if (valid[j]) v[j] = __ldg(reinterpret_cast<const uint4*>(src + (long)row * ar.lda_src + col));
+          }
+          if (ar.partial_mc) {
+#pragma unroll
+            for (int j = 0; j < UNR; ++j)
+              if (valid[j]) sb::multimem_st_b128(reinterpret_cast<uint16_t*>(ar.partial_mc) + doff[j], v[j]);
+          } else {
+            for (int q = 0; q < ar.W; ++q) {
+#pragma unroll
+              for (int j = 0; j < UNR; ++j)
+                if (valid[j]) *reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(ar.partial[q]) + doff[j]) = v[j];
+            }
+          }
+        }
+        __threadfence_system();  // the rows have landed everywhere before any rank is told so
+        red_bar_sync();
+        if (rt < ar.W) sb::st_release_sys(ar.flags[rt] + (long)ar.rank * ar.flag_stride + rb, epoch);
+      }
+    } else
+    for (int it = worker; it < num_units; it += num_workers) {
+      const int unit = unit_at(it);
       const int ctile = unit * CTAS + rank;  // S == 1 in fused launches: unit = tile
-      if ((unit + rank) % ar.W != ar.rank) continue;  // same rule as in the epilogue (unit = tile here)
       const int m0 = ((unit / n_tiles) * CTAS + rank) * BM, n0 = (unit % n_tiles) * BN;
+      const bool scatter = ar.mode == AR_REDUCE_SCATTER;
+      // same ownership rule as in the epilogue
+      if ((scatter ? m0 / ar.shard_rows : (unit + rank) % ar.W) != ar.rank) continue;
+      const long out_shift = scatter ? (long)ar.rank * ar.shard_rows * p.ldc : 0;  // the shard starts at row 0 of out
       if (rok && rt < ar.W) {
         if (!sb::wait_flag_ge(ar.flags[ar.rank] + (long)rt * ar.flag_stride + ctile, epoch, ar.timeout_ns))
           *abort_flag = 1;
@@ -628,6 +707,7 @@ __global__ void __launch_bounds__(FUSE ? GEMM_THREADS + REDUCER_THREADS : GEMM_T
         off = (long)row * p.ldc + col;
         return idx < BM * VPR && row < p.M && col < p.N;
       };
+      OutT* out_local = reinterpret_cast<OutT*>(ar.out[ar.rank]);
       if (ar.partial_mc) {
         constexpr int UNR = 8;
         for (int base = rt; base < BM * VPR; base += REDUCER_THREADS * UNR) {
@@ -639,9 +719,15 @@ __global__ void __launch_bounds__(FUSE ? GEMM_THREADS + REDUCER_THREADS : GEMM_T
             valid[j] = piece(base + j * REDUCER_THREADS, off[j]);
             if (valid[j]) v[j] = multimem_sum16<OutT>(reinterpret_cast<const OutT*>(ar.partial_mc) + off[j]);
           }
+          if (scatter) {
 #pragma unroll
-          for (int j = 0; j < UNR; ++j)
-            if (valid[j]) sb::multimem_st_b128(reinterpret_cast<OutT*>(ar.out_mc) + off[j], v[j]);
+            for (int j = 0; j < UNR; ++j)
+              if (valid[j]) *reinterpret_cast<uint4*>(out_local + (off[j] - out_shift)) = v[j];
+          } else {
+#pragma unroll
+            for (int j = 0; j < UNR; ++j)
+              if (valid[j]) sb::multimem_st_b128(reinterpret_cast<OutT*>(ar.out_mc) + off[j], v[j]);
+          }
         }
       } else {
         constexpr int UNR = 4;
@@ -669,10 +755,16 @@ __global__ void __launch_bounds__(FUSE ? GEMM_THREADS + REDUCER_THREADS : GEMM_T
                 for (int i = 0; i < 8; ++i) acc[j][i] += v[i];
               }
           }
-          for (int q = 0; q < ar.W; ++q) {
+          if (scatter) {
 #pragma unroll
             for (int j = 0; j < UNR; ++j)
-              if (valid[j]) store8<OutT>(reinterpret_cast<OutT*>(ar.out[q]) + off[j], acc[j]);
+              if (valid[j]) store8<OutT>(out_local + (off[j] - out_shift), acc[j]);
+          } else {
+            for (int q = 0; q < ar.W; ++q) {
+#pragma unroll
+              for (int j = 0; j < UNR; ++j)
+                if (valid[j]) store8<OutT>(reinterpret_cast<OutT*>(ar.out[q]) + off[j], acc[j]);
+            }
           }
         }
       }
@@ -911,52 +1003,75 @@ SB_API int sb200_gemm(const void* A, const void* B, void* C, void* C_pre, const 
                        bn_hint, 0, sm_count, nullptr, 0, status, stream);
 }
 
-// C = sum over the W ranks of a tensor-parallel group of op(A_r) op(B_r) (+ bias, given on one rank only), every rank
-// receiving the full [M, N] result: the row-parallel linear (A = activations [M, K_local], B = weight shard
-// [N, K_local], b_mn = 0) and the input gradient of a column-parallel linear (b_mn = 1).  All ranks call this with
-// the same M, N and their own operands; the buffers behind partial_ptrs / out_ptrs / flag_ptrs are symmetric
-// allocations mapped into every process (tables of W device pointers in host memory, entry r = rank r's buffer).
-//   partial, out: [M, ldc] elements of the input dtype each;  flags: (W + 1) * flag_stride uint32, zero before the
-//   first use, flag_stride >= number of 128-row output tiles;  partial_mc / out_mc: multicast addresses or null;
-//   epoch, done_ctas: one uint32 each in local device memory, zero before the first use.
-// The result is in out_ptrs[rank] when the launch completes.
-SB_API int sb200_gemm_allreduce(const void* A, const void* B, const void* bias, int M, int N, int K, long lda, long ldb,
-                                long ldc, int b_mn, int in_dtype, void* const* partial_ptrs, void* const* out_ptrs,
-                                void* const* flag_ptrs, void* partial_mc, void* out_mc, int flag_stride,
-                                uint32_t* epoch, unsigned int* done_ctas, int rank, int W, double timeout_seconds,
-                                int sm_count, int* status, cudaStream_t stream) {
+// Tensor-parallel GEMMs with the collective inside the kernel.  All ranks of the group call this with the same
+// shapes and mode and their own operands.  The buffers behind partial_ptrs / out_ptrs / flag_ptrs are symmetric
+// allocations mapped into every process (tables of W device pointers in host memory, entry r = rank r's buffer);
+// flags: (W + 2) * flag_stride uint32, zero before the first use, flag_stride >= number of 128-row output tiles;
+// partial_mc / out_mc: multicast addresses or null; epoch, done_ctas: one uint32 each in local device memory, zero
+// before the first use.  bias is given on one rank only in modes 0 and 1 (it is added once to the sum).
+//   mode 0 (all-reduce):     out_ptrs[rank][M, ldc] = sum_r A_r[M, K] op(B_r); partial: [M, ldc] per rank.
+//   mode 1 (reduce-scatter): C[M / W, ldc] = rows [rank * M / W, ...) of that sum (C is local memory).
+//   mode 2 (all-gather):     C[M, ldc] = act([A_0; A_1; ...; A_{W-1}] op(B) + bias) with A_r the [M / W, K] shard
+//                            given as A on rank r; the gathered operand is left in partial_ptrs[rank] ([M, K]).
+// Modes 1 and 2 need M to be a multiple of W * 128 rows.
+SB_API int sb200_gemm_tp(const void* A, const void* B, void* C, void* C_pre, const void* bias, int M, int N, int K,
+                         long lda, long ldb, long ldc, int b_mn, int act, int in_dtype, int mode,
+                         void* const* partial_ptrs, void* const* out_ptrs, void* const* flag_ptrs, void* partial_mc,
+                         void* out_mc, int flag_stride, uint32_t* epoch, unsigned int* done_ctas, int rank, int W,
+                         double timeout_seconds, int sm_count, int* status, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return SB_OK;
   if (K <= 0 || W < 1 || W > AR_MAX_RANKS || rank < 0 || rank >= W) return SB_ERR_BAD_ARG;
-  if (in_dtype != SB_DT_BF16) return SB_ERR_BAD_ARG;
-  if ((lda % 8) || (ldb % 8) || (ldc % 8) || (N % 8)) return SB_ERR_BAD_ARG;
+  if (in_dtype != SB_DT_BF16 || mode < 0 || mode > 2) return SB_ERR_BAD_ARG;
+  if ((lda % 8) || (ldb % 8) || (ldc % 8) || (N % 8) || (K % 8)) return SB_ERR_BAD_ARG;
   if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15)) return SB_ERR_BAD_ARG;
   const bool pair = M > BM && N > 128;
   const int bn = pair ? 256 : 128;
   const int rows = pair ? 2 * BM : BM;
-  const long ctiles = (long)((M + rows - 1) / rows) * ((N + bn - 1) / bn) * (pair ? 2 : 1);
+  const int m_tiles = (M + rows - 1) / rows, n_tiles = (N + bn - 1) / bn;
+  const long ctiles = (long)m_tiles * n_tiles * (pair ? 2 : 1);
   if (ctiles > flag_stride) return SB_ERR_TOO_LARGE;
+  if (mode != AR_ALLREDUCE && (M % (W * BM))) return SB_ERR_BAD_ARG;  // a 128-row block belongs to one rank
   GemmParams p = {};
-  p.C = partial_ptrs[rank]; p.C_pre = nullptr; p.bias = bias; p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.act = 0;
-  p.accumulate = 0; p.ab_fmt = 1; p.status = status; p.splits = 1; p.ws_counter = nullptr; p.ws_partial = nullptr;
-  if (reinterpret_cast<uintptr_t>(p.C) & 15) return SB_ERR_BAD_ARG;
-  p.tma_store = 1;
+  p.bias = bias; p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.accumulate = 0; p.ab_fmt = 1; p.status = status;
+  p.splits = 1; p.ws_counter = nullptr; p.ws_partial = nullptr; p.tma_store = 1;
+  const void* a_operand = A;
+  long a_ld = lda;
+  if (mode == AR_ALLGATHER) {
+    p.C = C; p.C_pre = C_pre; p.act = act;
+    a_operand = partial_ptrs[rank];  // the gathered [M, K] operand
+    a_ld = K;
+    if (C_pre && (reinterpret_cast<uintptr_t>(C_pre) & 15)) return SB_ERR_BAD_ARG;
+  } else {
+    p.C = partial_ptrs[rank]; p.C_pre = nullptr; p.act = 0;
+    if (mode == AR_REDUCE_SCATTER && (!C || (reinterpret_cast<uintptr_t>(C) & 15))) return SB_ERR_BAD_ARG;
+  }
+  if (!p.C || (reinterpret_cast<uintptr_t>(p.C) & 15)) return SB_ERR_BAD_ARG;
   for (int q = 0; q < AR_MAX_RANKS; ++q) {
     p.ar.partial[q] = q < W ? partial_ptrs[q] : nullptr;
-    p.ar.out[q] = q < W ? out_ptrs[q] : nullptr;
+    p.ar.out[q] = q < W && out_ptrs ? out_ptrs[q] : nullptr;
     p.ar.flags[q] = q < W ? reinterpret_cast<uint32_t*>(flag_ptrs[q]) : nullptr;
   }
+  if (mode == AR_REDUCE_SCATTER) p.ar.out[rank] = C;
   p.ar.partial_mc = partial_mc; p.ar.out_mc = out_mc; p.ar.epoch = epoch; p.ar.done_ctas = done_ctas;
   p.ar.flag_stride = flag_stride; p.ar.rank = rank; p.ar.W = W;
+  p.ar.mode = mode; p.ar.shard_rows = mode == AR_ALLREDUCE ? M : M / W; p.ar.ld_out = ldc;
+  p.ar.a_src = A; p.ar.lda_src = lda;
+  // reduce-scatter: a rank multiplies its own rows last, so that the tiles it has to reduce arrive from the peers
+  // while it is still busy; all-gather: it starts with its own rows, which are there first
+  const int tiles_per_rank = (m_tiles / W) * n_tiles;
+  p.ar.unit_shift = mode == AR_REDUCE_SCATTER ? ((rank + 1) % W) * tiles_per_rank
+                  : mode == AR_ALLGATHER ? rank * tiles_per_rank : 0;
   if (timeout_seconds <= 0.0 || timeout_seconds > 60.0) timeout_seconds = 10.0;
   p.ar.timeout_ns = (unsigned long long)(timeout_seconds * 1e9);
   CUtensorMap tmA, tmB, tmC, tmP;
   int rc;
-  if ((rc = make_tmap_2d(&tmA, A, M, K, lda, BM, 0))) return rc;
+  if ((rc = make_tmap_2d(&tmA, a_operand, M, K, a_ld, BM, 0))) return rc;
   if (b_mn) rc = make_tmap_2d(&tmB, B, K, N, ldb, 64, 0);
   else rc = make_tmap_2d(&tmB, B, N, K, ldb, pair ? 128 : bn, 0);
   if (rc) return rc;
   if ((rc = make_tmap_out(&tmC, p.C, M, N, ldc, 0))) return rc;
   tmP = tmC;
+  if (p.C_pre && (rc = make_tmap_out(&tmP, p.C_pre, M, N, ldc, 0))) return rc;
   using T = __nv_bfloat16;
   if (pair) {
     if (b_mn) return launch_gemm<256, false, true, T, true, true>(tmA, tmB, tmC, tmP, p, sm_count, stream);
@@ -964,4 +1079,15 @@ SB_API int sb200_gemm_allreduce(const void* A, const void* B, const void* bias, 
   }
   if (b_mn) return launch_gemm<128, false, true, T, false, true>(tmA, tmB, tmC, tmP, p, sm_count, stream);
   return launch_gemm<128, false, false, T, false, true>(tmA, tmB, tmC, tmP, p, sm_count, stream);
+}
+
+// The all-reduce form with its earlier argument list.
+SB_API int sb200_gemm_allreduce(const void* A, const void* B, const void* bias, int M, int N, int K, long lda, long ldb,
+                                long ldc, int b_mn, int in_dtype, void* const* partial_ptrs, void* const* out_ptrs,
+                                void* const* flag_ptrs, void* partial_mc, void* out_mc, int flag_stride,
+                                uint32_t* epoch, unsigned int* done_ctas, int rank, int W, double timeout_seconds,
+                                int sm_count, int* status, cudaStream_t stream) {
+  return sb200_gemm_tp(A, B, nullptr, nullptr, bias, M, N, K, lda, ldb, ldc, b_mn, 0, in_dtype, AR_ALLREDUCE, partial_ptrs,
+                       out_ptrs, flag_ptrs, partial_mc, out_mc, flag_stride, epoch, done_ctas, rank, W, timeout_seconds,
+                       sm_count, status, stream);
 }

@@ -181,3 +181,36 @@ def all_reduce_scatter_to_sequence_parallel(x: torch.Tensor, topology: Optional[
 
 def gather_from_sequence_parallel_region(x: torch.Tensor, topology: Optional[Topology]) -> torch.Tensor:
     return x if _size(topology) == 1 else _GatherTokens.apply(x, topology)
+
+
+class SequenceShard:
+    """This rank's tokens of an activation that is split over the tensor-parallel group (sequence parallelism), handed
+    from a norm to the linears behind it without gathering first.  A consumer that can gather inside its GEMM takes
+    ``shard``; every other consumer calls :meth:`gathered`, which runs the all-gather once and keeps the result for
+    the consumers that follow."""
+
+    def __init__(self, shard: torch.Tensor, topology: Topology):
+        self.shard = shard
+        self.topology = topology
+        self._full: Optional[torch.Tensor] = None
+
+    @property
+    def shape(self) -> torch.Size:
+        return torch.Size(_sp_out_shape(self.shard.shape, self.topology.model_parallel_size, gather=True))
+
+    @property
+    def device(self) -> torch.device:
+        return self.shard.device
+
+    @property
+    def dtype(self) -> torch.dtype:
+        return self.shard.dtype
+
+    @property
+    def is_cuda(self) -> bool:
+        return self.shard.is_cuda
+
+    def gathered(self) -> torch.Tensor:
+        if self._full is None:
+            self._full = gather_from_sequence_parallel_region(self.shard, self.topology)
+        return self._full

@@ -67,6 +67,10 @@ class TransformerLayer(TransformerLayerBaseIO):
         self.attn_residual_split = NormedResidualSplit(residual_mults, 2 * layer_index, True)
         self.attn_residual_add = NormedResidualAdd(residual_mults, 2 * layer_index, True)
         self.post_attention_layernorm = norm()
+        if topology is not None and topology.config.sequence_parallel and topology.config.model_parallel_size > 1:
+            # attention and MLP take this rank's tokens and gather them inside their first GEMMs
+            self.input_layernorm.defer_gather = True
+            self.post_attention_layernorm.defer_gather = True
         mlp_cls = {MLPType.DEFAULT: ParallelMLP, MLPType.SWIGLU: ParallelSwiGLUMLP}[a.mlp_type]
         self.mlp: Union[ParallelMLP, ParallelSwiGLUMLP] = mlp_cls(
             io_features=a.hidden_size, intermediate_feature_factor=a.mlp_factor, bias=a.mlp_bias, topology=topology,
