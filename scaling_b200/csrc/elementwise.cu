@@ -218,6 +218,17 @@ __global__ void __launch_bounds__(256)
   for (int i = 0; i < V; ++i) acc[i] = 0.f;
   if (c < N) {
     long r = r0 + warp;
+    // eight independent 16-byte loads per thread before the first add: enough bytes in flight to keep HBM busy
+    for (; r + 56 < r1; r += 64) {
+      sb::Vec16<T> v[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] = sb::ld16(x + (r + 8 * j) * ld + c);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+#pragma unroll
+        for (int i = 0; i < V; ++i) acc[i] += sb::to_f(v[j].e[i]);
+      }
+    }
     for (; r + 8 < r1; r += 16) {
       sb::Vec16<T> a = sb::ld16(x + r * ld + c), b = sb::ld16(x + (r + 8) * ld + c);
 #pragma unroll

@@ -284,7 +284,7 @@ __global__ void __launch_bounds__(FUSE ? GEMM_THREADS + REDUCER_THREADS : GEMM_T
         const int m_blk = (tile / n_tiles) * CTAS + rank, n_blk = tile % n_tiles;
         const int kb0 = (int)((long)split * num_kb / S), kb1 = (int)((long)(split + 1) * num_kb / S);
         const int b_col0 = n_blk * BN + rank * LOAD_BN;  // first output column whose B rows this CTA loads
-        if (FUSE && p.ar.mode == AR_ALLGATHER) {
+        if (FUSE && p.ar.mode == AR_ALLGATHER && m_blk * BM < p.M) {
           // the rows of this block come from rank `src`: wait until its gather warps have delivered them
           const int src = (m_blk * BM) / p.ar.shard_rows, rb = (m_blk * BM - src * p.ar.shard_rows) / BM;
           if (!sb::wait_flag_ge(p.ar.flags[p.ar.rank] + (long)src * p.ar.flag_stride + rb, epoch, p.ar.timeout_ns)) {
@@ -623,7 +623,8 @@ __global__ void __launch_bounds__(FUSE ? GEMM_THREADS + REDUCER_THREADS : GEMM_T
         if (et == 0) {
           // all-reduce: rotated per CTA of a pair, every CTA owns 1 / W of its tiles; reduce-scatter: by row range
           const int owner = p.ar.mode == AR_REDUCE_SCATTER ? (m_blk * BM) / p.ar.shard_rows : (tile + rank) % p.ar.W;
-          sb::st_release_sys(p.ar.flags[owner] + (long)p.ar.rank * p.ar.flag_stride + ctile, epoch);
+          if (owner < p.ar.W)  // a block below the last row (odd number of blocks under a CTA pair) has no owner
+            sb::st_release_sys(p.ar.flags[owner] + (long)p.ar.rank * p.ar.flag_stride + ctile, epoch);
         }
       }
     }

@@ -48,6 +48,13 @@ def doc_ranges(cu_seqlens: torch.Tensor, total: int) -> tuple[torch.Tensor, torc
     return start, end
 
 
+def _check_ranges(start: torch.Tensor, end: torch.Tensor, tokens: int) -> None:
+    # the kernels read one (start, end) pair per token
+    if start.numel() != tokens or end.numel() != tokens or start.dtype != torch.int32 or end.dtype != torch.int32:
+        raise ValueError(f"document ranges cover {start.numel()} / {end.numel()} tokens ({start.dtype}), "
+                         f"attention runs on {tokens}")
+
+
 def _strides_ok(t: torch.Tensor) -> bool:
     return t.stride(2) == 1 and t.stride(0) % 8 == 0 and t.stride(1) % 8 == 0 and t.data_ptr() % 16 == 0
 
@@ -112,6 +119,7 @@ def flash_attention_kernel(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu
                                      causal, scale, window, ranges)
         return out.to(q.dtype)
     start, end = ranges if ranges is not None else doc_ranges(cu_seqlens, q.shape[0])
+    _check_ranges(start, end, q.shape[0])
     return _FlashAttention.apply(q, k, v, start, end, causal, scale, window)
 
 
@@ -196,6 +204,7 @@ def packed_qkv_attention(qkv: torch.Tensor, positions: Optional[torch.Tensor],
     with the rotated projection.
     """
     start, end = ranges if ranges is not None else doc_ranges(cu_seqlens, qkv.shape[0])
+    _check_ranges(start, end, qkv.shape[0])
     pos = None
     if rotary is not None:
         assert positions is not None

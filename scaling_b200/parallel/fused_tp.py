@@ -34,6 +34,7 @@ FUSED_TP_MAX_ELEMENTS = 2 * 1024 * 1024  # largest output (elements) routed to t
 
 
 MODE_ALLREDUCE, MODE_REDUCE_SCATTER, MODE_ALLGATHER = 0, 1, 2
+_VERIFY = os.environ.get("SB200_FUSED_TP_VERIFY", "0") == "1"
 _ACT = {"none": 0, "gelu": 1}
 
 
@@ -86,13 +87,29 @@ class FusedTPWorkspace:
             FLAG_STRIDE, self.local.data_ptr(), self.local.data_ptr() + 4, self.rank, self.world, self.timeout_s,
             _lib.sm_count(), K.status_word().data_ptr(), _lib.stream()), "sb200_gemm_tp")
 
+    def _verify(self, what: str, got: torch.Tensor, ref: torch.Tensor, shape: tuple) -> None:
+        """SB200_FUSED_TP_VERIFY=1: every fused launch is compared with GEMM + NCCL (debugging aid; slow)."""
+        torch.cuda.synchronize()
+        K.check_status()
+        err = (got.float() - ref.float()).norm() / ref.float().norm().clamp_min(1e-20)
+        bad = torch.tensor([float(not torch.isfinite(err) or err > 1e-2)], device=got.device)
+        dist.all_reduce(bad, group=self.group)
+        if bad.item() > 0:
+            raise RuntimeError(f"fused tensor-parallel GEMM ({what}, M/N/K/b_mn={shape}, launch {self.launches}) "
+                               f"differs from GEMM + NCCL on rank {self.rank}: relative error {err.item():.3e}")
+
     def gemm_allreduce(self, x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None,
                        b_mn: bool = False) -> torch.Tensor:
         """``x [M, K] @ op(w)`` summed over the group; ``w`` is ``[N, K]`` (``b_mn=False``) or ``[K, N]``."""
         M, Kd = x.shape
         N = w.shape[1] if b_mn else w.shape[0]
         self._launch(MODE_ALLREDUCE, x, w, None, None, bias, M, N, Kd, b_mn, "none")
-        return self.out.tensor[:M * N].view(M, N).clone()
+        out = self.out.tensor[:M * N].view(M, N).clone()
+        if _VERIFY:
+            ref = K.gemm(x, w, b_mn=b_mn, bias=bias)
+            dist.all_reduce(ref, group=self.group)
+            self._verify("all-reduce", out, ref, (M, N, Kd, b_mn))
+        return out
 
     def gemm_reduce_scatter(self, x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None,
                             b_mn: bool = False) -> torch.Tensor:
@@ -101,6 +118,11 @@ class FusedTPWorkspace:
         N = w.shape[1] if b_mn else w.shape[0]
         out = torch.empty((M // self.world, N), dtype=x.dtype, device=x.device)
         self._launch(MODE_REDUCE_SCATTER, x, w, out, None, bias, M, N, Kd, b_mn, "none")
+        if _VERIFY:
+            ref = K.gemm(x, w, b_mn=b_mn, bias=bias)
+            dist.all_reduce(ref, group=self.group)
+            rows = M // self.world
+            self._verify("reduce-scatter", out, ref[self.rank * rows:(self.rank + 1) * rows], (M, N, Kd, b_mn))
         return out
 
     def allgather_gemm(self, shard: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None,
@@ -114,6 +136,11 @@ class FusedTPWorkspace:
         out = torch.empty((M, N), dtype=shard.dtype, device=shard.device)
         self._launch(MODE_ALLGATHER, shard, w, out, pre_act_out, bias, M, N, Kd, b_mn, act)
         self._gathered_key = (shard.data_ptr(), shard._version, Ms, Kd, self.launches)
+        if _VERIFY:
+            full = torch.empty((M, Kd), dtype=shard.dtype, device=shard.device)
+            dist.all_gather_into_tensor(full, shard.contiguous(), group=self.group)
+            self._verify("all-gather operand", self.gathered(M, Kd), full, (M, N, Kd, b_mn))
+            self._verify("all-gather", out, K.gemm(full, w, b_mn=b_mn, bias=bias, act=act), (M, N, Kd, b_mn))
         return out
 
     def gathered(self, M: int, Kd: int) -> torch.Tensor:
@@ -137,7 +164,8 @@ class FusedTPWorkspace:
             return self._regathered[1]
         full = torch.empty((shard.shape[0] * self.world, shard.shape[1]), dtype=shard.dtype, device=shard.device)
         dist.all_gather_into_tensor(full, shard, group=self.group)
-        self._regathered = (key, full)
+        # the entry holds the shard itself: its address cannot be handed to another tensor while the copy is cached
+        self._regathered = (key, full, shard)
         return full
 
     def drop_regathered(self) -> None:
@@ -363,6 +391,10 @@ class _ColumnParallelSPFn(torch.autograd.Function):
         pre = torch.empty((M, w.shape[0]), dtype=s2.dtype, device=s2.device) if act == "gelu" else None
         full = ws.cached_gather(s2)
         if full is not None:
+            if _VERIFY:
+                ref = torch.empty_like(full)
+                dist.all_gather_into_tensor(ref, s2, group=ws.group)
+                ws._verify("reused gathered operand", full, ref, (M, w.shape[0], s2.shape[1], False))
             y = K.gemm(full, w, bias=bias, act=act, pre_act_out=pre)
         else:
             y = ws.allgather_gemm(s2, w, bias, act, pre)

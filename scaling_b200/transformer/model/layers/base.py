@@ -58,7 +58,12 @@ class TransformerLayerIO(_FieldRecord, BaseLayerIO):
             return None
         from ...data.utils import document_ranges_from_padded
 
-        total = self.activations.shape[0] * self.activations.shape[1]
+        # all tokens of the micro batch: under sequence parallelism the activations hold only this rank's share,
+        # while attention runs on the gathered sequence
+        if self.position_ids is not None:
+            total = self.position_ids.numel()
+        else:
+            total = self.activations.shape[0] * self.activations.shape[1]
         self._doc_ranges = document_ranges_from_padded(padded, total)
         return self._doc_ranges
 
