@@ -67,6 +67,8 @@ def parse_args() -> argparse.Namespace:
     p.add_argument("--grad-accum", type=int, default=None,
                    help="micro batches per step and data-parallel rank (default: from the config's global batch)")
     p.add_argument("--layers", type=int, default=None, help="override the layer count (exploration only)")
+    p.add_argument("--sequence-parallel", action="store_true",
+                   help="shard the activations between the tensor-parallel linears over the tokens")
     return p.parse_args()
 
 
@@ -83,6 +85,8 @@ def layout(args: argparse.Namespace, world: int) -> dict:
     if args.layers:
         arch["num_layers"] = args.layers
     par = "+".join(f"{k}{v}" for k, v in (("tp", mp), ("pp", pp), ("dp", dp)) if v > 1 or k == "dp") + "+zero1"
+    if getattr(args, "sequence_parallel", False) and mp > 1:
+        par += "+sp"
     return dict(c, arch=arch, mp=mp, pp=pp, dp=dp, ga=ga, parallelism=par)
 
 
@@ -201,7 +205,8 @@ def run_ours(args: argparse.Namespace) -> None:
     cfg = TransformerConfig.from_dict({
         "topology": {"world_size": world, "global_rank": rank, "local_slot": local, "model_parallel_size": lay["mp"],
                      "pipe_parallel_size": lay["pp"], "data_parallel_size": dp, "micro_batch_size": micro,
-                     "gradient_accumulation_steps": ga, "activation_checkpointing_type": lay["ckpt"]},
+                     "gradient_accumulation_steps": ga, "activation_checkpointing_type": lay["ckpt"],
+                     "sequence_parallel": bool(args.sequence_parallel and lay["mp"] > 1)},
         "optimizer": {"zero": True, "gradient_clipping": 1.0, "beta1": 0.9, "beta2": 0.95},
         "training_groups": [group],
         "training": {"allow_missing_params_in_optimizer": True} if lay["lora"] else {},
