@@ -135,6 +135,15 @@ __device__ __forceinline__ void bias_pair(uint32_t w, int is_bf16, float& lo, fl
     hi = f.y;
   }
 }
+// Number of CTAs that share the push of one 128-row block in the all-gather mode (the same on every rank and in every
+// CTA of a launch: it depends on the grid and the shapes only).
+constexpr int GATHER_MAX_GROUPS = 16;
+__device__ __forceinline__ int gather_groups(int grid, int blocks, int kvec) {
+  int g = grid / (blocks > 0 ? blocks : 1);
+  if (g > GATHER_MAX_GROUPS) g = GATHER_MAX_GROUPS;
+  if (g > kvec) g = kvec;
+  return g < 1 ? 1 : g;
+}
 __device__ __forceinline__ void epi_bar_sync() { asm volatile("bar.sync 1, %0;" ::"n"(EPI_WARPS * 32) : "memory"); }
 __device__ __forceinline__ void red_bar_sync() { asm volatile("bar.sync 2, %0;" ::"n"(REDUCER_THREADS) : "memory"); }
 template <typename OutT> __device__ __forceinline__ uint4 multimem_sum16(const void* mc);
@@ -287,9 +296,12 @@ __global__ void __launch_bounds__(FUSE ? GEMM_THREADS + REDUCER_THREADS : GEMM_T
         if (FUSE && p.ar.mode == AR_ALLGATHER && m_blk * BM < p.M) {
           // the rows of this block come from rank `src`: wait until its gather warps have delivered them
           const int src = (m_blk * BM) / p.ar.shard_rows, rb = (m_blk * BM - src * p.ar.shard_rows) / BM;
-          if (!sb::wait_flag_ge(p.ar.flags[p.ar.rank] + (long)src * p.ar.flag_stride + rb, epoch, p.ar.timeout_ns)) {
+          const int groups = gather_groups(gridDim.x, (p.ar.shard_rows + BM - 1) / BM, p.K / 8);
+          const uint32_t* arrived = p.ar.flags[p.ar.rank] + (long)src * p.ar.flag_stride + rb * groups;
+          for (int g = 0; g < groups && ok; ++g)  // one flag per column range of the block
+            if (!sb::wait_flag_ge(arrived + g, epoch, p.ar.timeout_ns)) ok = false;
+          if (!ok) {
             *abort_flag = 1;
-            ok = false;
             break;
           }
           sb::fence_proxy_async_global();
@@ -651,11 +663,18 @@ __global__ void __launch_bounds__(FUSE ? GEMM_THREADS + REDUCER_THREADS : GEMM_T
       if (*abort_flag) rok = false;
       const int kvec = p.K / 8;  // 16-byte vectors per row
       const int blocks = (ar.shard_rows + BM - 1) / BM;
+      // a 128-row block is pushed by `groups` CTAs, each a range of columns, so that all CTAs of the launch share
+      // the work; neighbouring CTAs take the same block: the first blocks (multiplied first by the peers) land first
+      const int groups = gather_groups(gridDim.x, blocks, kvec);
+      const int cw = (kvec + groups - 1) / groups;  // vectors per row and group
       const uint16_t* src = reinterpret_cast<const uint16_t*>(ar.a_src);
-      for (int rb = blockIdx.x; rb < blocks && rok; rb += gridDim.x) {
+      for (int item = blockIdx.x; item < blocks * groups && rok; item += gridDim.x) {
+        const int rb = item / groups, g = item - rb * groups;
         const int r0 = rb * BM;
         const int nrows = ar.shard_rows - r0 < BM ? ar.shard_rows - r0 : BM;
-        const int total = nrows * kvec;
+        const int v0 = g * cw;
+        const int nv = kvec - v0 < cw ? (kvec - v0 > 0 ? kvec - v0 : 0) : cw;
+        const int total = nrows * nv;
         constexpr int UNR = 8;
         for (int base = rt; base < total; base += REDUCER_THREADS * UNR) {
           uint4 v[UNR];
@@ -665,7 +684,7 @@ __global__ void __launch_bounds__(FUSE ? GEMM_THREADS + REDUCER_THREADS : GEMM_T
           for (int j = 0; j < UNR; ++j) {
             const int idx = base + j * REDUCER_THREADS;
             valid[j] = idx < total;
-            const int row = r0 + idx / kvec, col = (idx % kvec) * 8;
+            const int row = r0 + idx / nv, col = (v0 + idx % nv) * 8;
             doff[j] = ((long)ar.rank * ar.shard_rows + row) * p.K + col;
             if (valid[j]) v[j] = __ldg(reinterpret_cast<const uint4*>(src + (long)row * ar.lda_src + col));
           }
@@ -681,9 +700,9 @@ __global__ void __launch_bounds__(FUSE ? GEMM_THREADS + REDUCER_THREADS : GEMM_T
             }
           }
         }
-        __threadfence_system();  // the rows have landed everywhere before any rank is told so
+        __threadfence_system();  // the piece has landed everywhere before any rank is told so
         red_bar_sync();
-        if (rt < ar.W) sb::st_release_sys(ar.flags[rt] + (long)ar.rank * ar.flag_stride + rb, epoch);
+        if (rt < ar.W) sb::st_release_sys(ar.flags[rt] + (long)ar.rank * ar.flag_stride + item, epoch);
       }
     } else
     for (int it = worker; it < num_units; it += num_workers) {
@@ -1032,6 +1051,7 @@ SB_API int sb200_gemm_tp(const void* A, const void* B, void* C, void* C_pre, con
   const long ctiles = (long)m_tiles * n_tiles * (pair ? 2 : 1);
   if (ctiles > flag_stride) return SB_ERR_TOO_LARGE;
   if (mode != AR_ALLREDUCE && (M % (W * BM))) return SB_ERR_BAD_ARG;  // a 128-row block belongs to one rank
+  if (mode == AR_ALLGATHER && (long)(M / W / BM) * GATHER_MAX_GROUPS > flag_stride) return SB_ERR_TOO_LARGE;
   GemmParams p = {};
   p.bias = bias; p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.accumulate = 0; p.ab_fmt = 1; p.status = status;
   p.splits = 1; p.ws_counter = nullptr; p.ws_partial = nullptr; p.tma_store = 1;
@@ -1054,6 +1074,10 @@ SB_API int sb200_gemm_tp(const void* A, const void* B, void* C, void* C_pre, con
   }
   if (mode == AR_REDUCE_SCATTER) p.ar.out[rank] = C;
   p.ar.partial_mc = partial_mc; p.ar.out_mc = out_mc; p.ar.epoch = epoch; p.ar.done_ctas = done_ctas;
+  // Pushing through the switch's multicast sends every byte over NVLink once, whatever the group size, this GPU's own
+  // copy included; with two ranks the plain peer store moves the same bytes and keeps the local copy off the link
+  // (measured: 207 us against 235 us for a 4096 x 4096 x 5504 problem).
+  if (mode == AR_ALLGATHER && W <= 2) p.ar.partial_mc = nullptr;
   p.ar.flag_stride = flag_stride; p.ar.rank = rank; p.ar.W = W;
   p.ar.mode = mode; p.ar.shard_rows = mode == AR_ALLREDUCE ? M : M / W; p.ar.ld_out = ldc;
   p.ar.a_src = A; p.ar.lda_src = lda;
