@@ -193,3 +193,46 @@ def test_runner_parses_hosts():
     assert list(pool.items()) == [("a", [0, 1]), ("b", [0])]
     with pytest.raises((ValueError, AssertionError)):
         hosts_str_to_resource_pool(cfg, ["a slots=2", "a slots=2"])
+
+
+# ---------------------------------------------------------------------------------------------- attention ranges
+def test_document_ranges_have_to_cover_every_token():
+    from scaling_b200.ops.attention_kernel import _check_ranges
+
+    ok = torch.zeros(8, dtype=torch.int32)
+    _check_ranges(ok, ok, 8)
+    with pytest.raises(ValueError, match="cover 4"):
+        _check_ranges(ok[:4], ok[:4], 8)  # e.g. ranges of one sequence-parallel shard handed to the gathered sequence
+    with pytest.raises(ValueError):
+        _check_ranges(ok.long(), ok.long(), 8)
+
+
+def test_document_ranges_follow_the_position_ids_not_the_local_activations():
+    from scaling_b200.transformer.data.utils import document_ranges_from_padded
+
+    padded = torch.tensor([0, 3, 8, -1, -1])
+    start, end = document_ranges_from_padded(padded, 8)
+    assert start.tolist() == [0, 0, 0, 3, 3, 3, 3, 3] and end.tolist() == [3, 3, 3, 8, 8, 8, 8, 8]
+
+
+# ---------------------------------------------------------------------------------------------- benchmark layouts
+@pytest.mark.parametrize("config,gpus,expected", [
+    ("125m", 8, dict(mp=1, pp=1, dp=8, ga=1)),
+    ("7b", 8, dict(mp=4, pp=1, dp=2, ga=32)),
+    ("7b", 2, dict(mp=2, pp=1, dp=1, ga=64)),
+    ("7b_lora", 8, dict(mp=8, pp=1, dp=1, ga=32)),
+    ("13b", 8, dict(mp=2, pp=2, dp=2, ga=16)),
+    ("13b", 2, dict(mp=2, pp=1, dp=1, ga=32)),
+])
+def test_benchmark_layouts_fit_the_gpus(config, gpus, expected):
+    import argparse
+    import importlib.util
+    from pathlib import Path as _P
+
+    spec = importlib.util.spec_from_file_location("bench_module", _P(__file__).resolve().parent.parent / "bench.py")
+    bench = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(bench)
+    lay = bench.layout(argparse.Namespace(config=config, grad_accum=None, layers=None, sequence_parallel=False), gpus)
+    assert {k: lay[k] for k in expected} == expected
+    assert lay["mp"] * lay["pp"] * lay["dp"] == gpus
+    assert bench.model_flops_per_token(lay["arch"], True) > bench.model_flops_per_token(lay["arch"], False) > 0
