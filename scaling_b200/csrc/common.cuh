@@ -81,6 +81,19 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   return false;
 }
 
+// The same over `rounds` spin limits: for roles whose progress depends on another GPU (whose own wait has a time
+// budget and raises `abort_flag` when it runs out), so that a late peer within that budget does not end them early.
+__device__ __forceinline__ bool mbar_wait_rounds(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int rounds) {
+  for (int r = 0; r < rounds; ++r) {
+    for (uint32_t i = 0; i < SB_SPIN_LIMIT; ++i) {
+      if (mbar_try_wait(bar, parity)) return true;
+      if ((i & 0xfff) == 0xfff && *abort_flag) return false;
+    }
+  }
+  *abort_flag = 1;
+  return false;
+}
+
 // ----------------------------------------------------------------------- TMA
 __device__ __forceinline__ void tma_prefetch_desc(const void* tmap) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(tmap) : "memory");

@@ -248,6 +248,9 @@ __global__ void __launch_bounds__(FUSE ? GEMM_THREADS + REDUCER_THREADS : GEMM_T
   const int num_units = m_tiles * n_tiles * S;
   const uint32_t epoch = FUSE ? *p.ar.epoch + 1 : 0;  // identifies this launch in the peers' flag words
   const int ushift = FUSE ? p.ar.unit_shift : 0;
+  // In the all-gather mode the tile loads wait for a peer (time budget ar.timeout_ns); the roles behind them keep
+  // waiting for as long: one spin limit is about three seconds.
+  const int wait_rounds = (FUSE && p.ar.mode == AR_ALLGATHER) ? (int)(p.ar.timeout_ns / 2000000000ull) + 2 : 1;
   // position in this worker's sequence -> unit (tile, split); fused launches start at a rank-specific tile
   auto unit_at = [&](int i) { return FUSE ? (i + ushift) % num_units : i; };
 
@@ -307,7 +310,7 @@ __global__ void __launch_bounds__(FUSE ? GEMM_THREADS + REDUCER_THREADS : GEMM_T
           sb::fence_proxy_async_global();
         }
         for (int kb = kb0; kb < kb1; ++kb) {
-          if (!sb::mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag)) { ok = false; break; }
+          if (!sb::mbar_wait_rounds(&empty_bar[stage], phase ^ 1, abort_flag, wait_rounds)) { ok = false; break; }
           uint8_t* a_s = smem + stage * Cfg::STAGE_BYTES;
           uint8_t* b_s = a_s + Cfg::A_BYTES;
           if (PAIR) {
@@ -362,11 +365,11 @@ __global__ void __launch_bounds__(FUSE ? GEMM_THREADS + REDUCER_THREADS : GEMM_T
         const int unit = unit_at(it);
         const int tile = unit / S, split = unit - tile * S;
         const int kb0 = (int)((long)split * num_kb / S), kb1 = (int)((long)(split + 1) * num_kb / S);
-        if (!sb::mbar_wait(&tempty_bar[acc], acc_phase ^ 1, abort_flag)) { ok = false; break; }
+        if (!sb::mbar_wait_rounds(&tempty_bar[acc], acc_phase ^ 1, abort_flag, wait_rounds)) { ok = false; break; }
         sb::tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
         for (int kb = kb0; kb < kb1; ++kb) {
-          if (!sb::mbar_wait(&full_bar[stage], phase, abort_flag)) { ok = false; break; }
+          if (!sb::mbar_wait_rounds(&full_bar[stage], phase, abort_flag, wait_rounds)) { ok = false; break; }
           sb::tc_fence_after();
           const uint32_t a_addr = sb::smem_u32(smem + stage * Cfg::STAGE_BYTES);
           const uint32_t b_addr = a_addr + Cfg::A_BYTES;
@@ -424,7 +427,7 @@ __global__ void __launch_bounds__(FUSE ? GEMM_THREADS + REDUCER_THREADS : GEMM_T
       const int tile = unit / S;
       const int m_blk = (tile / n_tiles) * CTAS + rank, n_blk = tile % n_tiles;
       const int ctile = tile * CTAS + rank;  // this CTA's part of the tile: index of its counter and partial slots
-      if (ok && !sb::mbar_wait(&tfull_bar[acc], acc_phase, abort_flag)) ok = false;
+      if (ok && !sb::mbar_wait_rounds(&tfull_bar[acc], acc_phase, abort_flag, wait_rounds)) ok = false;
       sb::tc_fence_after();
       const int row = m_blk * BM + quad * 32 + lane;
       const uint32_t t_acc = tmem_base + ((uint32_t)(quad * 32) << 16) + acc * BN;
