@@ -1,0 +1,92 @@
+"""Parameter-efficient fine-tuning through the config (BitFit biases, adapters, soft prompt, LoRA merge): only the new
+parameters train, they go to their own checkpoint files, and a base checkpoint without them loads non-strictly."""
+
+import copy
+from pathlib import Path
+
+import pytest
+import torch
+
+from tests.test_transformer_training import losses, tiny_config
+from tests.utils import dist_launcher
+
+pytestmark = pytest.mark.dist
+
+FINETUNE_ARCH = {
+    "bitfit_bias_config": {"name": "ft"},
+    "adapter_config": {"name": "ad", "attention_downsampling_factor": 0.25, "mlp_downsampling_factor": 0.25},
+    "softprompt_config": {"name": "sp", "n_tokens": 4},
+}
+GROUPS = [{"group_name": "new", "parameters_include": ["bias_ft", "adapter_ad", "softprompt_sp"], "weight_decay": 0.0,
+           "learning_rate_scheduler": {"learning_rate": 1e-2, "learning_rate_decay_style": "constant"}}]
+
+
+def _finetune(rank, world_size, port, device, config):
+    from scaling_b200.core.runner import LaunchConfig
+    from scaling_b200.parallel import Topology
+    from scaling_b200.transformer import TransformerConfig, TransformerContext, init_model, init_optimizer
+    from scaling_b200.transformer.model import metrics_aggregation_fn
+    from scaling_b200.transformer.model.losses import create_loss_function
+    from scaling_b200.transformer.train import TransformerTrainer, _get_sync_batch, _read_datasets
+
+    lc = LaunchConfig(master_port=port, master_addr="127.0.0.1", world_size=world_size, global_rank=rank,
+                      local_slot=rank, payload=copy.deepcopy(config))
+    cfg = TransformerConfig.from_dict(lc.overwrite_config_dict_with_launcher_args(dict(lc.payload)))
+    topology = Topology(cfg.topology)
+    context = TransformerContext(config=cfg, topology=topology)
+    context.initialize(master_addr="127.0.0.1", master_port=str(port), seed=cfg.trainer.seed)
+    model = init_model(context)
+    optimizer = init_optimizer(context, model)
+    dataset = _read_datasets(cfg)[0] if topology.is_io_rank else None
+    trainer = TransformerTrainer(config=cfg.trainer, context=context, parallel_module=model, optimizer=optimizer,
+                                 dataset=dataset, sync_batch_to_model_parallel=_get_sync_batch(cfg.data),
+                                 loss_function=create_loss_function(context, cfg.training.loss_function_config),
+                                 metrics_aggregation_fn=metrics_aggregation_fn)
+    before = {n: p.detach().clone() for n, p in model.named_parameters()}
+    metrics = trainer.run_training(return_metrics=True)
+    changed = sorted(n for n, p in model.named_parameters() if not torch.equal(p.detach(), before[n]))
+    frozen = sorted(n for n, p in model.named_parameters() if torch.equal(p.detach(), before[n]))
+    return ([m["training/loss"] for m in metrics] if metrics else None, changed, frozen,
+            cfg.trainer.separate_file_for_parameters)
+
+
+def _is_new(name: str) -> bool:
+    return any(tag in name for tag in ("bias_ft", "adapter_ad", "softprompt_sp"))
+
+
+@pytest.mark.parametrize("world_size,mp", [(1, 1), (2, 2)])
+def test_bitfit_adapter_softprompt_train_alone_and_get_their_own_files(tmp_path: Path, world_size, mp):
+    base_dir = str(tmp_path / "base")
+    losses(1, save_dir=base_dir, save_interval=2, iters=2)  # a plain pretrained checkpoint without the new parameters
+    cfg = tiny_config(world_size, mp=mp, arch=FINETUNE_ARCH, groups=GROUPS, iters=3, load_dir=base_dir,
+                      save_dir=str(tmp_path / "ft"), save_interval=3,
+                      training={"allow_missing_params_in_optimizer": True})
+    # with a named bias set the layers carry `bias_ft` in place of `bias`: the pretrained biases stay in the file
+    cfg["trainer"].update(allowed_missing_keys_in_checkpoint=["bias_ft", "adapter_ad", "softprompt_sp"],
+                          allowed_unexpected_keys_in_checkpoint=[r"\.bias$"],
+                          load_optimizer_states=False, load_context=False)
+    out = dist_launcher(_finetune, world_size, config=cfg)
+    loss, changed, frozen, separate = out[0]
+    assert sorted(separate) == ["adapter_ad", "bias_ft", "softprompt_sp"]
+    assert changed and all(_is_new(n) for n in changed), changed
+    assert frozen and not any(_is_new(n) for n in frozen), [n for n in frozen if _is_new(n)]
+    assert all(l == l for l in loss)
+    files = sorted(f.name for f in (tmp_path / "ft" / "global_step3").glob("model_state_layer_*.pt"))
+    for tag in ("bias_ft", "adapter_ad", "softprompt_sp"):
+        assert any(f.endswith(f"_{tag}.pt") for f in files), (tag, files)
+    # the base files hold none of the new parameters, the separate files nothing else
+    for f in (tmp_path / "ft" / "global_step3").glob("model_state_layer_*.pt"):
+        keys = list(torch.load(f, map_location="cpu", weights_only=False).keys())
+        separate_file = any(f.name.endswith(f"_{tag}.pt") for tag in ("bias_ft", "adapter_ad", "softprompt_sp"))
+        assert all(_is_new(k) == separate_file for k in keys), (f.name, keys)
+
+
+def test_base_checkpoint_without_the_new_parameters_needs_the_allowance(tmp_path: Path):
+    base_dir = str(tmp_path / "base")
+    losses(1, save_dir=base_dir, save_interval=2, iters=2)
+    cfg = tiny_config(1, arch=FINETUNE_ARCH, groups=GROUPS, iters=1, load_dir=base_dir,
+                      training={"allow_missing_params_in_optimizer": True})
+    cfg["trainer"].update(load_optimizer_states=False, load_context=False,
+                          allowed_unexpected_keys_in_checkpoint=[r"\.bias$"])
+    with pytest.raises(AssertionError, match="(?i)missing|bias_ft|adapter_ad|softprompt"):
+        dist_launcher(_finetune, 1, config=cfg)
