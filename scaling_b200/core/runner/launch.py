@@ -14,6 +14,7 @@ import signal
 import subprocess
 import sys
 import time
+from pathlib import Path
 from typing import Any, Optional
 
 from .launch_config import decode_base64
@@ -67,6 +68,21 @@ def _terminate(children: list[subprocess.Popen]) -> None:
                 pass
 
 
+def script_command(script: str) -> tuple[list[str], Optional[str]]:
+    """How to start ``script``: a file that belongs to a package (``__init__.py`` in its folder and above) runs as
+    ``python -m package.module`` with the package's parent folder on the import path, so that its relative imports
+    work; any other file runs as a plain script."""
+    path = Path(script).resolve()
+    if path.suffix != ".py" or not (path.parent / "__init__.py").is_file():
+        return [sys.executable, "-u", script], None
+    parts = [path.stem]
+    folder = path.parent
+    while (folder / "__init__.py").is_file():
+        parts.append(folder.name)
+        folder = folder.parent
+    return [sys.executable, "-u", "-m", ".".join(reversed(parts))], str(folder)
+
+
 def main(argv: Optional[list[str]] = None) -> int:
     args = parse_args(argv)
     pool = decode_base64(args.resource_pool)
@@ -74,9 +90,12 @@ def main(argv: Optional[list[str]] = None) -> int:
     env = os.environ.copy()
     env.update(MASTER_ADDR=args.master_addr, MASTER_PORT=str(args.master_port), WORLD_SIZE=str(world_size))
     children: list[subprocess.Popen] = []
+    base_cmd, import_root = script_command(args.script)
+    if import_root is not None:
+        env["PYTHONPATH"] = import_root + (os.pathsep + env["PYTHONPATH"] if env.get("PYTHONPATH") else "")
     for slot, rank in zip(slots, ranks):
         child_env = dict(env, RANK=str(rank), LOCAL_SLOT=str(slot))
-        cmd = [sys.executable, "-u", args.script]
+        cmd = list(base_cmd)
         if args.payload is not None:
             cmd += ["--payload", args.payload]
         children.append(subprocess.Popen(cmd, env=child_env))
