@@ -74,17 +74,32 @@ class PipeCommunicator:
         self.group = group
         self.peer_send = peer_send
         self.peer_recv = peer_recv
-        self._sent_meta: Optional[list[LeafMeta]] = None
-        self._sent_spec: Any = None
-        self._obj_capacity: dict[int, int] = {}
-        self._recv_meta: Optional[list[LeafMeta]] = None
-        self._recv_spec: Any = None
+        # Negotiated structure per channel: a training step and an evaluation step send differently flagged trees
+        # (gradients wanted or not) over the same link; both sides switch channel together, so nothing extra is sent.
+        self.channel = "train"
+        self._state: dict[str, dict[str, Any]] = {}
         self._posted: Optional[tuple[list[torch.Tensor], list]] = None
 
     def reset_communication_meta(self) -> None:
-        self._sent_meta = self._recv_meta = None
-        self._sent_spec = self._recv_spec = None
+        self._state = {}
         self._posted = None
+
+    def _channel_state(self) -> dict[str, Any]:
+        st = self._state.get(self.channel)
+        if st is None:
+            st = self._state[self.channel] = dict(sent_meta=None, sent_spec=None, recv_meta=None, recv_spec=None,
+                                                  obj_capacity={})
+        return st
+
+    _sent_meta = property(lambda self: self._channel_state()["sent_meta"],
+                          lambda self, v: self._channel_state().__setitem__("sent_meta", v))
+    _sent_spec = property(lambda self: self._channel_state()["sent_spec"],
+                          lambda self, v: self._channel_state().__setitem__("sent_spec", v))
+    _recv_meta = property(lambda self: self._channel_state()["recv_meta"],
+                          lambda self, v: self._channel_state().__setitem__("recv_meta", v))
+    _recv_spec = property(lambda self: self._channel_state()["recv_spec"],
+                          lambda self, v: self._channel_state().__setitem__("recv_spec", v))
+    _obj_capacity = property(lambda self: self._channel_state()["obj_capacity"])
 
     # ------------------------------------------------------------------ data: sender side
     def _to_wire(self, data: Any) -> tuple[list[torch.Tensor], list[LeafMeta], Any]:

@@ -420,6 +420,7 @@ class ParallelModule(PipePartitionedModule, Generic[BaseLossInputGeneric, BaseDa
 
                 dataloader, self._graph_pending = itertools.chain(self._graph_pending, dataloader), []
         self._layers.train()
+        self._set_channel("train")
         self.pipe_buffer.reset()
         self.profiler.step()
         opt_out = self._run(self.train_instructions, dataloader=dataloader, optimizer=optimizer,
@@ -433,6 +434,7 @@ class ParallelModule(PipePartitionedModule, Generic[BaseLossInputGeneric, BaseDa
                         metrics_aggregation_fn: Optional[Callable] = None) -> EvaluationStepOutput:
         self.step_timer.start()
         self._layers.eval()
+        self._set_channel("eval")
         self.pipe_buffer.reset()
         self.profiler.step()
         with torch.no_grad():
@@ -567,6 +569,12 @@ class ParallelModule(PipePartitionedModule, Generic[BaseLossInputGeneric, BaseDa
 
     def _after_recv(self, tup: tuple) -> tuple:
         return tup
+
+    def _set_channel(self, channel: str) -> None:
+        """Training and evaluation steps negotiate the structure of what crosses a stage boundary separately."""
+        for c in (self.communicator_in, self.communicator_out, self.communicator_loss_in, self.communicator_loss_out):
+            if c is not None:
+                c.channel = channel
 
     def reset_activation_shape(self) -> None:
         """Forget negotiated shapes; must be called on all ranks together."""

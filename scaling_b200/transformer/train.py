@@ -134,7 +134,13 @@ def _read_datasets(config: TransformerConfig):
         train = SyntheticTextDataset(n_samples=n, sequence_length=a.sequence_length, vocab_size=a.vocab_size, seed=seed,
                                      low=1, reset_attention_mask=a.reset_attention_mask,
                                      reset_position_ids=a.reset_position_ids)
-        return train, None
+        validation = None
+        if config.trainer.eval_interval is not None:  # held-out synthetic samples: evaluation works without data files
+            validation = SyntheticTextDataset(n_samples=max(64, n // 8), sequence_length=a.sequence_length,
+                                              vocab_size=a.vocab_size, seed=seed + 1, low=1,
+                                              reset_attention_mask=a.reset_attention_mask,
+                                              reset_position_ids=a.reset_position_ids)
+        return train, validation
     from .dataset_loader import load_blended_datasets
 
     return load_blended_datasets(config)

@@ -88,3 +88,31 @@ def test_mlp_example_trains_when_started_by_the_launcher(tmp_path: Path):
     assert (tmp_path / "ckpt" / "latest").read_text().strip() == "global_step3"
     assert any(step_dir.glob("model_state_layer_*.pt")) and any(step_dir.glob("optimizer_state_layer_*.pt"))
     assert (step_dir / "context_global_rank_0.pt").is_file() and (step_dir / "context_global_rank_1.pt").is_file()
+
+
+@pytest.mark.dist
+def test_transformer_training_script_under_the_launcher(tmp_path: Path):
+    """The transformer entry point as the runner starts it: pipeline of two stages, evaluation and a checkpoint."""
+    from tests.test_transformer_training import tiny_config
+
+    import numpy as np
+
+    from scaling_b200.core.data import MemoryMapDatasetBuilder
+
+    rng = np.random.default_rng(0)
+    for name, docs in (("train", 80), ("valid", 30)):  # token files as the tokeniser script leaves them (0 = end of document)
+        with MemoryMapDatasetBuilder(prefix_path=tmp_path / name) as b:
+            for _ in range(docs):
+                b.add(np_array=np.concatenate([rng.integers(1, 128, size=rng.integers(5, 60)), [0]]).astype(np.int32))
+    payload = tiny_config(2, pp=2, ga=2, micro=2, iters=2, save_dir=str(tmp_path / "ckpt"), save_interval=2)
+    payload["trainer"].update(eval_interval=2, eval_iterations=1)
+    payload["data"] = {"data_prefixes": [str(tmp_path / "train")], "validation_data_prefixes": [str(tmp_path / "valid")]}
+    payload["logger"] = {"log_dir": str(tmp_path / "logs")}
+    rc = launch_main(["--resource_pool", encode_base64(_pool(2)), "--master_port", str(find_free_port()),
+                      str(ROOT / "scaling_b200" / "transformer" / "train.py"), "--payload", encode_base64(payload)])
+    assert rc == 0
+    step_dir = tmp_path / "ckpt" / "global_step2"
+    names = sorted(f.name for f in step_dir.glob("model_state_layer_*.pt"))
+    # embedding, two blocks, final norm, head: one file per layer whatever stage holds it
+    assert [n.split("_")[3] for n in names] == ["0", "1", "2", "3", "4"], names
+    assert (step_dir / "config.yml").is_file()
