@@ -90,3 +90,66 @@ def test_base_checkpoint_without_the_new_parameters_needs_the_allowance(tmp_path
                           allowed_unexpected_keys_in_checkpoint=[r"\.bias$"])
     with pytest.raises(AssertionError, match="(?i)missing|bias_ft|adapter_ad|softprompt"):
         dist_launcher(_finetune, 1, config=cfg)
+
+
+# ---------------------------------------------------------------------------------------------- embeddings
+def _embedding_setup(tmp_path: Path) -> tuple[str, str]:
+    import json
+
+    from scaling_b200.transformer.tokenizer import Tokenizer
+
+    words = ["the", "cat", "sat", "on", "mat", "a", "dog", "ran", "far", "query", "doc", "good", "bad", "find", ":"]
+    tok = Tokenizer.from_words(words)
+    vocab = tmp_path / "vocab.json"
+    vocab.write_text(tok.tokenizer.to_str())
+    records = []
+    for i in range(32):
+        a, b, c = words[i % 9], words[(i + 3) % 9], words[(i + 5) % 9]
+        records.append({"query": ["find :", f"{a} {b}"], "positives": [["doc :", f"the {a} {b} {c}"]],
+                        "negatives": [["doc :", f"a {c} ran far"]]})
+    data = tmp_path / "emb.jsonl"
+    data.write_text("\n".join(json.dumps(r) for r in records) + "\n")
+    return str(vocab), str(data)
+
+
+@pytest.mark.parametrize("world_size", [1, 2])
+def test_embedding_head_trains_with_the_contrastive_loss(tmp_path: Path, world_size):
+    """Query / positive / hard-negative triples, pooled embedding head, in-batch negatives gathered over the
+    data-parallel ranks; the language-model head is left out."""
+    vocab, data = _embedding_setup(tmp_path)
+    arch = {"vocab_size": 32, "vocab_file": vocab, "lm_head": False, "sequence_length": 12, "causal": True,
+            "embedding_head_config": {"name": "emb", "proj_layers": [16], "pooling": "weighted_mean"}}
+    training = {"loss_function_config": {"loss_type": "contrastive_loss", "number_of_hard_negatives": 1,
+                                         "use_instructions": True}}
+    cfg = tiny_config(world_size, arch=arch, iters=4, micro=4, training=training)
+    cfg["data"] = {"embedding_dataset": True, "data_prefixes": [data]}
+    out = dist_launcher(_finetune, world_size, config=cfg)
+    loss, changed, _, _ = out[0]
+    assert len(loss) == 4 and all(l == l and l > 0 for l in loss)
+    assert any("embedding_head" in n or "emb" in n for n in changed)
+    assert not any("lm_head" in n for n in changed)
+
+
+# ---------------------------------------------------------------------------------------------- instruction / chat data
+@pytest.mark.parametrize("kind,world_size,mp", [("finetuning_dataset", 1, 1), ("finetuning_chat_dataset", 2, 2)])
+def test_prompt_completion_and_chat_data_train_with_masked_loss(tmp_path: Path, kind, world_size, mp):
+    import json
+
+    vocab, _ = _embedding_setup(tmp_path)
+    words = ["the", "cat", "sat", "on", "mat", "a", "dog", "ran", "far"]
+    if kind == "finetuning_dataset":
+        records = [{"prompt": f"the {words[i % 9]} sat", "completion": f"on a {words[(i + 2) % 9]}"} for i in range(24)]
+        data = tmp_path / "data.json"  # prompt / completion records are one json list
+        data.write_text(json.dumps(records))
+    else:
+        records = [[{"type": "text", "content": f"the {words[i % 9]}", "has_loss": False},
+                    {"type": "text", "content": f"ran {words[(i + 4) % 9]}", "has_loss": True}] for i in range(24)]
+        data = tmp_path / "data.jsonl"  # one conversation per line
+        data.write_text("\n".join(json.dumps(r) for r in records) + "\n")
+    arch = {"vocab_size": 32, "vocab_file": vocab, "sequence_length": 12,
+            "softprompt_config": {"name": "sp", "n_tokens": 2}}
+    cfg = tiny_config(world_size, mp=mp, arch=arch, iters=3, micro=4)
+    cfg["data"] = {kind: True, "data_prefixes": [str(data)]}
+    loss, changed, _, _ = dist_launcher(_finetune, world_size, config=cfg)[0]
+    assert len(loss) == 3 and all(l == l for l in loss)
+    assert any("softprompt" in n for n in changed)
