@@ -124,3 +124,39 @@ def test_lora_finetuning_trains_only_the_adapters(tmp_path: Path):
     got = losses(2, mp=2, load_dir=init, arch=arch, groups=groups, training=training, iters=8)
     for a, b in zip(got, base):
         assert abs(a - b) < 2e-4 * max(1.0, abs(b)), (got, base)
+
+
+UMUP_ARCH = {"umup": {"enable": True}, "norm_type": "rms", "mlp_bias": False, "attention_bias": False,
+             "weight_tying": False, "relative_position_embedding_type": "rotary"}
+
+
+@pytest.mark.dist
+def test_unit_scaled_parametrization_layouts_agree(tmp_path: Path):
+    """u-μP (unit-scaled weights, forward / backward multipliers, residual scaling): tensor- and pipeline-parallel
+    layouts and the torch attention path reproduce the single-process losses; the losses start near log(vocab)."""
+    import math
+
+    init = str(tmp_path / "init")
+    base = losses(1, save_initial=init, arch=UMUP_ARCH)
+    assert abs(base[0] - math.log(128)) < 1.0, base
+    for kw in (dict(world_size=2, mp=2), dict(world_size=2, pp=2, ga=2, micro=2), dict(world_size=1, kernel="torch")):
+        ws = kw.pop("world_size")
+        got = losses(ws, load_dir=init, arch=UMUP_ARCH, **kw)
+        for a, b in zip(got, base):
+            assert abs(a - b) < 5e-4 * max(1.0, abs(b)), (kw, got, base)
+
+
+@pytest.mark.dist
+def test_tied_embedding_and_head_across_pipeline_stages(tmp_path: Path):
+    """The embedding on the first stage and the head on the last share one weight: gradients of the two copies are
+    summed and the copies stay equal; layouts agree and the checkpoint holds the weight once per owner layer."""
+    arch = {"weight_tying": True}
+    init = str(tmp_path / "init")
+    base = losses(1, save_initial=init, arch=arch)
+    for kw in (dict(world_size=2, pp=2, ga=2, micro=2), dict(world_size=2, mp=2), dict(world_size=2, zero=True)):
+        ws = kw.pop("world_size")
+        got = losses(ws, load_dir=init, arch=arch, **kw)
+        for a, b in zip(got, base):
+            assert abs(a - b) < 2e-4 * max(1.0, abs(b)), (kw, got, base)
+    untied = losses(1, arch={"weight_tying": False})
+    assert untied != base
