@@ -42,3 +42,37 @@ def test_gpu_training_follows_the_fp32_reference(tmp_path: Path, name, arch, kw)
     assert len(gpu) == len(cpu) == 4
     for a, b in zip(gpu, cpu):
         assert abs(a - b) < 3e-2 * max(1.0, abs(b)), (name, gpu, cpu)
+
+
+# ---------------------------------------------------------------------------------------------- inference on the GPU
+def _inference_module(arch: dict, device: str):
+    from scaling_b200.transformer.context.config import TransformerArchitectureConfig
+    from scaling_b200.transformer.inference import TransformerInferenceModule
+    from scaling_b200.transformer.model.model import get_transformer_layer_specs
+
+    torch.manual_seed(0)
+    cfg = TransformerArchitectureConfig.from_dict(arch)
+    return TransformerInferenceModule(get_transformer_layer_specs(architecture_config=cfg), devices=(device,))
+
+
+@pytest.mark.parametrize("name,extra", [("gpt", GPT_ARCH), ("llama", LLAMA_ARCH)])
+def test_gpu_inference_matches_the_fp32_module_and_the_cache_agrees_with_recompute(name, extra):
+    base = dict(SIZE, weight_tying=False, dropout_embedding=0.0, **extra)
+    gpu = _inference_module(dict(base, precision="bfloat16", masked_softmax={"kernel": "flash_attention"}), "cuda:0")
+    cpu = _inference_module(dict(base, precision="float32", masked_softmax={"kernel": "torch"}), "cpu")
+    # same weights: the fp32 module takes the bf16 values
+    state = {k: v.detach().float().cpu() for k, v in gpu.state_dict().items()}
+    missing, unexpected = cpu.load_state_dict(state, strict=False)
+    assert not unexpected and not [m for m in missing if "inv_freq" not in m and "cache" not in m], (missing, unexpected)
+    prompt = [3, 700, 15, 9, 420, 77, 5, 1000, 31, 8]
+    lg, lc = gpu.logits(input_tokens=prompt).float().cpu(), cpu.logits(input_tokens=prompt)
+    assert lg.shape == lc.shape == (len(prompt), SIZE["vocab_size"])
+    assert (lg - lc).abs().max() < 0.15 * max(1.0, lc.abs().max().item()), (lg - lc).abs().max()
+    cached = gpu.generate(max_tokens=8, input_tokens=prompt, use_cache=True, stop_tokens=[1023])
+    plain = gpu.generate(max_tokens=8, input_tokens=prompt, use_cache=False, stop_tokens=[1023])
+    n = min(len(cached.completion_tokens), len(plain.completion_tokens))
+    assert n >= 1
+    # bf16 rounding may flip a near-tie: compare the logits of the steps up to the first differing token
+    same = next((i for i in range(n) if cached.completion_tokens[i] != plain.completion_tokens[i]), n - 1)
+    assert torch.allclose(cached.completion_logits[:same + 1].float(), plain.completion_logits[:same + 1].float(),
+                          atol=0.1, rtol=0.05)
