@@ -29,16 +29,30 @@ def _losses(device, arch, save_initial=None, **kw):
     return dist_launcher(run_training, 1, device=device, config=_config(device, arch, **kw), save_initial=save_initial)[0]
 
 
+UMUP_ARCH = {"umup": {"enable": True}, "norm_type": "rms", "mlp_bias": False, "attention_bias": False,
+             "relative_position_embedding_type": "rotary"}
+PEFT_ARCH = dict(GPT_ARCH, bitfit_bias_config={"name": "ft"}, softprompt_config={"name": "sp", "n_tokens": 4},
+                 adapter_config={"name": "ad", "attention_downsampling_factor": 0.25, "mlp_downsampling_factor": 0.25},
+                 lora_config={"name": "lora", "rank": 4, "alpha": 8, "parallel_modules": ["query", "key", "value", "dense"]})
+PEFT_KW = {"groups": [{"group_name": "new", "parameters_include": ["bias_ft", "adapter_ad", "softprompt_sp", "lora"],
+                       "weight_decay": 0.0,
+                       "learning_rate_scheduler": {"learning_rate": 1e-3, "learning_rate_decay_style": "constant"}}],
+           "training": {"allow_missing_params_in_optimizer": True}}
+
+
 @pytest.mark.parametrize("name,arch,kw", [
     ("gpt", GPT_ARCH, {}),
     ("llama", LLAMA_ARCH, {}),
     ("llama_checkpointed", LLAMA_ARCH, {"ckpt": "every_layer"}),
     ("sliding_window", WINDOW_ARCH, {}),
+    ("unit_scaled", UMUP_ARCH, {}),
+    ("tied_head", dict(GPT_ARCH, weight_tying=True), {}),
+    ("bitfit_adapter_softprompt_lora", PEFT_ARCH, PEFT_KW),
 ])
 def test_gpu_training_follows_the_fp32_reference(tmp_path: Path, name, arch, kw):
     init = str(tmp_path / "init")
     gpu = _losses("cuda", arch, save_initial=init, **kw)  # bf16 weights: exactly representable in the fp32 model
-    cpu = _losses("cpu", arch, load_dir=init)
+    cpu = _losses("cpu", arch, load_dir=init, **{k: v for k, v in kw.items() if k != "ckpt"})
     assert len(gpu) == len(cpu) == 4
     for a, b in zip(gpu, cpu):
         assert abs(a - b) < 3e-2 * max(1.0, abs(b)), (name, gpu, cpu)
