@@ -126,6 +126,7 @@ class ParallelModule(PipePartitionedModule, Generic[BaseLossInputGeneric, BaseDa
         self.step_timer = CudaEventTimer()
         # whole-step CUDA graph (see _graph_eligible); SB200_CUDA_GRAPH=0 disables it
         self.enable_cuda_graph = os.environ.get("SB200_CUDA_GRAPH", "1") != "0"
+        self._nvtx = os.environ.get("SB200_NVTX", "0") == "1" and self.topology.device.type == "cuda"
         self._graph: Any = None
         self._graph_failed = False
         self._graph_warmup_left = 2
@@ -250,13 +251,21 @@ class ParallelModule(PipePartitionedModule, Generic[BaseLossInputGeneric, BaseDa
     # ------------------------------------------------------------------ steps
     def _run(self, instructions: list[InstructionBase], **ctx: Any) -> Any:
         optimizer_out = None
+        # SB200_NVTX=1: one NVTX range per schedule instruction, for timelines of external profilers
+        nvtx = self._nvtx
         for ins in instructions:
             name = ins.name
-            with self.profiler.time(name, ins.micro_batch_id, ins.buffer_id):
-                if name == "OptimizerStep":
-                    optimizer_out = ctx["optimizer"].step()
-                else:
-                    self._handlers[name](ins, **ctx)
+            if nvtx:
+                torch.cuda.nvtx.range_push(f"{name}[mb={ins.micro_batch_id},buf={ins.buffer_id}]")
+            try:
+                with self.profiler.time(name, ins.micro_batch_id, ins.buffer_id):
+                    if name == "OptimizerStep":
+                        optimizer_out = ctx["optimizer"].step()
+                    else:
+                        self._handlers[name](ins, **ctx)
+            finally:
+                if nvtx:
+                    torch.cuda.nvtx.range_pop()
         return optimizer_out
 
     # ------------------------------------------------------------------ CUDA-graph training step
