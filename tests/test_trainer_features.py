@@ -85,3 +85,70 @@ def test_every_rank_writes_its_own_log_file(tmp_path: Path):
     dist_launcher(_main_entry, 2, config=cfg)
     files = sorted(p.name for p in (tmp_path / "logs").rglob("*") if p.is_file())
     assert len(files) >= 2, files
+
+
+def test_truncated_checkpoint_file_is_reported_not_loaded(tmp_path: Path):
+    save = tmp_path / "ckpt"
+    losses(1, save_dir=str(save), save_interval=2, iters=2)
+    victim = sorted((save / "global_step2").glob("model_state_layer_1_*.pt"))[0]
+    victim.write_bytes(victim.read_bytes()[:200])
+    with pytest.raises(AssertionError, match="(?s)rank failures.*(Error|error)"):
+        losses(1, load_dir=str(save), iters=3)
+
+
+def test_a_killed_rank_takes_the_job_down_and_the_last_checkpoint_resumes_exactly(tmp_path: Path):
+    """Failure on the host: one of two ranks is killed in the middle of training.  The launcher ends the other rank
+    and reports the failure; a new job resumes from the last checkpoint and ends with the weights of a run that was
+    never interrupted."""
+    import os
+    import signal
+    import subprocess
+    import sys
+    import time
+
+    import psutil
+    import torch
+
+    from scaling_b200.core.runner.launch_config import encode_base64
+    from tests.utils import find_free_port
+
+    root = Path(__file__).resolve().parent.parent
+    reference = tmp_path / "reference"
+    dist_launcher(run_training, 2, config=tiny_config(2, mp=2, iters=14, save_dir=str(reference), save_interval=14))
+
+    crashed = tmp_path / "crashed"
+    payload = tiny_config(2, mp=2, iters=1_000_000, save_dir=str(crashed), save_interval=10)
+    pool = {"nodes": [{"name": "localhost", "slots": [0, 1]}], "world_size": 2}
+    launcher = subprocess.Popen(
+        [sys.executable, "-m", "scaling_b200.core.runner.launch", "--resource_pool", encode_base64(pool),
+         "--master_port", str(find_free_port()), str(root / "scaling_b200" / "transformer" / "train.py"),
+         "--payload", encode_base64(payload)], cwd=str(root), stdout=subprocess.DEVNULL, stderr=subprocess.DEVNULL,
+        env=dict(os.environ, OMP_NUM_THREADS="1", MKL_NUM_THREADS="1"))  # one thread, as the in-process test ranks
+    try:
+        deadline = time.time() + 120
+        while not (crashed / "global_step10" / "context_global_rank_1.pt").is_file() or not (crashed / "latest").is_file():
+            assert launcher.poll() is None, "the job ended before its first checkpoint"
+            assert time.time() < deadline, "no checkpoint within two minutes"
+            time.sleep(0.2)
+        children = psutil.Process(launcher.pid).children(recursive=False)
+        assert len(children) == 2
+        victim = children[1]
+        victim.send_signal(signal.SIGKILL)  # this exact process: a rank that dies without a word
+        rc = launcher.wait(timeout=60)
+        assert rc != 0
+        time.sleep(0.5)
+        assert not any(c.is_running() and c.status() != psutil.STATUS_ZOMBIE for c in children)
+    finally:
+        if launcher.poll() is None:
+            launcher.kill()
+    (crashed / "latest").write_text("global_step10")  # later checkpoints may exist; resume from a known one
+    resumed = tmp_path / "resumed"
+    dist_launcher(run_training, 2, config=tiny_config(2, mp=2, iters=14, load_dir=str(crashed), save_dir=str(resumed),
+                                                      save_interval=14))
+    files = sorted(f.name for f in (reference / "global_step14").glob("model_state_layer_*.pt"))
+    assert files
+    for name in files:
+        a = torch.load(reference / "global_step14" / name, map_location="cpu", weights_only=False)
+        b = torch.load(resumed / "global_step14" / name, map_location="cpu", weights_only=False)
+        assert a.keys() == b.keys()
+        assert all(torch.equal(a[k], b[k]) for k in a), name
