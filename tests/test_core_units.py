@@ -236,3 +236,67 @@ def test_benchmark_layouts_fit_the_gpus(config, gpus, expected):
     assert {k: lay[k] for k in expected} == expected
     assert lay["mp"] * lay["pp"] * lay["dp"] == gpus
     assert bench.model_flops_per_token(lay["arch"], True) > bench.model_flops_per_token(lay["arch"], False) > 0
+
+
+# ---------------------------------------------------------------------------------------------- 1F1B order
+def test_one_forward_one_backward_instruction_order():
+    from scaling_b200.core.nn.pipeline_schedule import PipelineScheduleTrain
+    from scaling_b200.parallel import Topology
+
+    def order(stage):
+        cfg = TopologyConfig.from_dict({"world_size": 2, "model_parallel_size": 1, "pipe_parallel_size": 2,
+                                        "global_rank": stage, "micro_batch_size": 1, "gradient_accumulation_steps": 4,
+                                        "device": "cpu", "backend": "gloo"})
+        short = {"LoadMicroBatch": "Load", "ForwardPass": "F", "BackwardPass": "B", "SendActivation": "SendA",
+                 "RecvActivation": "RecvA", "SendGrad": "SendG", "RecvGrad": "RecvG", "Loss": "Loss",
+                 "ReduceTiedGrads": "ReduceTied", "OptimizerStep": "OptStep"}
+        return [(short[i.name], i.micro_batch_id, i.buffer_id) for i in PipelineScheduleTrain(Topology(cfg)).instructions()]
+
+    names0 = [f"{n}{'' if m is None else m}" for n, m, _ in order(0)]
+    assert names0 == ("Load0 F0 SendA0 Load1 F1 SendA1 RecvG0 B0 Load2 F2 SendA2 RecvG1 B1 Load3 F3 SendA3 RecvG2 B2 "
+                      "RecvG3 B3 ReduceTied OptStep").split()
+    names1 = [f"{n}{'' if m is None else m}" for n, m, _ in order(1)]
+    assert names1 == ("RecvA0 Load0 F0 Loss0 B0 RecvA1 SendG0 Load1 F1 Loss1 B1 RecvA2 SendG1 Load2 F2 Loss2 B2 "
+                      "RecvA3 SendG2 Load3 F3 Loss3 B3 SendG3 ReduceTied OptStep").split()
+    # buffers: micro batch modulo max(2, min(stages - stage + 1, micro batches))
+    assert {m: b for n, m, b in order(0) if n == "Load"} == {0: 0, 1: 1, 2: 2, 3: 0}
+    assert {m: b for n, m, b in order(1) if n == "RecvA"} == {0: 0, 1: 1, 2: 0, 3: 1}
+
+
+# ---------------------------------------------------------------------------------------------- public names
+def test_public_names_of_the_two_packages():
+    import scaling_b200.core as core
+    import scaling_b200.transformer as transformer
+
+    core_names = """BaseConfig BaseContext BaseContextGeneric DeterminedBaseContext BaseBlendedDataset BaseDataset
+        BaseDatasetBatch BaseDatasetItem BaseLayerIO BlendedDatasetConfig DataLoader FileDataset MemoryMapDataset
+        MemoryMapDatasetBuilder broadcast_data ActivationFunction BaseLayer ColumnParallelLinear CoreParameterMeta
+        LayerNorm LayerNormConfig LayerNormOptimizationType LayerSpec LoRaConfig LoRAModuleType MaskedSoftmax
+        MaskedSoftmaxConfig MaskedSoftmaxKernel NormType ParallelLoRa ParallelMLP ParallelModule ParallelSelfAttention
+        ParallelSwiGLUMLP PipelineScheduleInference PipelineScheduleTrain PipePartitionCoordinates
+        RelativePositionEmbeddingType RMSNorm RotaryConfig RotaryEmbedding RotaryEmbeddingComplex RowParallelLinear
+        TiedLayerSpec VocabParallelEmbedding get_activation_function get_norm pipe_partition_uniform BaseOptimizer
+        LearningRateDecayStyle LearningRateScheduler LearningRateSchedulerConfig LossScaler LossScalerConfig Optimizer
+        OptimizerConfig OptimizerParamGroup OptimizerParamGroupConfig Profiler ProfilerConfig SynchronizedTimer
+        RunnerConfig RunnerDockerConfig RunnerType runner_main PipePartitionMethod Topology TopologyConfig BaseTrainer
+        DeterminedBaseTrainer TrainerConfig""".split()
+    assert [n for n in core_names if not hasattr(core, n)] == []
+    transformer_names = """TransformerConfig TransformerContext EmbeddingDataset EmbeddingBlendedDataset
+        FinetuningChatDataset FinetuningChatBlendedDataset FinetuningTextDataset FinetuningTextBlendedDataset
+        LegacyBlendedDataset TextDataset TextBlendedDataset TextDatasetItem TransformerLayerIO TransformerParallelModule
+        init_model init_optimizer""".split()
+    assert [n for n in transformer_names if not hasattr(transformer, n)] == []
+    from scaling_b200.core.nn.parallel_module import EvaluationStepOutput, TrainStepOutput
+    from scaling_b200.core.nn.parallel_module.inference_module import InferenceModule, RecorderSetting  # noqa: F401
+    from scaling_b200.core.runner.launch_config import LaunchConfig  # noqa: F401
+    from scaling_b200.core.utils.port import find_free_port  # noqa: F401
+    from scaling_b200.transformer.inference import TransformerInferenceModule  # noqa: F401
+    from scaling_b200.transformer.model.losses import create_loss_function  # noqa: F401
+    from scaling_b200.transformer.model.model import get_transformer_layer_specs  # noqa: F401
+    from scaling_b200.transformer.tokenizer import Tokenizer, load_tokenizers  # noqa: F401
+    from scaling_b200.transformer.train import main  # noqa: F401
+
+    assert TrainStepOutput._fields == ("loss", "metrics", "global_grad_norm", "global_grad_norm_clipped",
+                                       "learning_rates", "overflow", "no_overflow_steps", "current_loss_scale",
+                                       "step_duration", "debug_dict")
+    assert EvaluationStepOutput._fields == ("loss", "metrics", "step_duration")
