@@ -152,3 +152,41 @@ def test_a_killed_rank_takes_the_job_down_and_the_last_checkpoint_resumes_exactl
         b = torch.load(resumed / "global_step14" / name, map_location="cpu", weights_only=False)
         assert a.keys() == b.keys()
         assert all(torch.equal(a[k], b[k]) for k in a), name
+
+
+def test_checkpoint_layout_and_key_names(tmp_path: Path):
+    """One model and one optimizer file per global layer index, module-path state keys, optimizer keys built from the
+    parameter meta, a tied weight stored under each of its layer indices."""
+    import torch
+
+    save = tmp_path / "ckpt"
+    losses(1, save_dir=str(save), save_interval=2, iters=2, arch={"weight_tying": True})
+    step = save / "global_step2"
+    names = sorted(f.name for f in step.iterdir())
+    assert names == [
+        "config.yml", "context_global_rank_0.pt",
+        "model_state_layer_0_EmbeddingInput.pt", "model_state_layer_1_TransformerLayer.pt",
+        "model_state_layer_2_TransformerLayer.pt", "model_state_layer_3_LayerNormWrapper.pt",
+        "model_state_layer_4_TransformerLMHeadTied.pt",
+        "optimizer_state_layer_0.pt", "optimizer_state_layer_1.pt", "optimizer_state_layer_2.pt",
+        "optimizer_state_layer_3.pt", "optimizer_state_layer_4.pt", "parameter_meta_0_5.json"]
+    block = torch.load(step / "model_state_layer_1_TransformerLayer.pt", weights_only=False)
+    assert list(block) == ["input_layernorm.weight", "input_layernorm.bias", "self_attention.query_key_value.weight",
+                           "self_attention.query_key_value.bias", "self_attention.dense.weight",
+                           "self_attention.dense.bias", "post_attention_layernorm.weight",
+                           "post_attention_layernorm.bias", "mlp.dense_in.weight", "mlp.dense_in.bias",
+                           "mlp.dense_out.weight", "mlp.dense_out.bias"]
+    first = torch.load(step / "optimizer_state_layer_0.pt", weights_only=False)
+    last = torch.load(step / "optimizer_state_layer_4.pt", weights_only=False)
+    assert set(first) == {"step_index", "loss_scaler", "parameters", "optimizer_param_groups"}
+    key0 = "layer_index_0_parameter_name_embedding.weight_is_model_parallel_True_model_parallel_dimension_0"
+    key4 = "layer_index_4_parameter_name_embedding.weight_is_model_parallel_True_model_parallel_dimension_0"
+    assert list(first["parameters"]) == [key0] and list(last["parameters"]) == [key4]
+    entry = first["parameters"][key0]
+    assert set(entry) == {"parameter", "meta", "optimizer_state"}
+    assert set(entry["optimizer_state"]) == {"step", "exp_avg", "exp_avg_sq"}
+    assert entry["parameter"].dtype == torch.float32
+    assert torch.equal(entry["parameter"], last["parameters"][key4]["parameter"])  # the tied copies are one weight
+    meta = json.loads((step / "parameter_meta_0_5.json").read_text())
+    assert any("embedding.weight" in str(k) or "embedding.weight" in str(v) for k, v in (meta.items() if isinstance(meta, dict) else enumerate(meta)))
+    assert (save / "latest").read_text() == "global_step2"
