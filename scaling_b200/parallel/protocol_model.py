@@ -45,13 +45,17 @@ class Workspace:
         self.epoch = [0] * W
         self.done_ctas = [0] * W
         self.lock = [threading.Lock() for _ in range(W)]  # the atomicAdd on done_ctas
+        self.failed = threading.Event()  # a rank of the model found a violation: the others stop waiting for it
 
 
-def _wait(flags: np.ndarray, index: int, value: int, timeout: float, what: str) -> None:
+def _wait(flags: np.ndarray, index: int, value: int, timeout: float, what: str,
+          failed: Optional[threading.Event] = None) -> None:
     deadline = time.monotonic() + timeout
     while flags[index] < value:
         if time.monotonic() > deadline:
             raise ProtocolError(f"wait ran out: {what}")
+        if failed is not None and failed.is_set():
+            raise ProtocolError(f"stopped while waiting ({what}): another rank reported a violation")
         time.sleep(0)
 
 
@@ -100,7 +104,7 @@ def launch(ws: Workspace, rank: int, mode: int, a: np.ndarray, b: np.ndarray, ct
                     rb = (tile * BM - src * shard_rows) // BM
                     for g in range(groups):  # tile loads wait for every column group of the row block
                         _wait(ws.flags[rank], src * stride + rb * groups + g, epoch, timeout,
-                              f"rank {rank} rows of rank {src} block {rb} group {g}")
+                              f"rank {rank} rows of rank {src} block {rb} group {g}", ws.failed)
                     gathered = ws.partial[rank][:M * K].reshape(M, K)
                     result[rows] = gathered[rows] @ b
                 else:
@@ -118,7 +122,8 @@ def launch(ws: Workspace, rank: int, mode: int, a: np.ndarray, b: np.ndarray, ct
                     for q in range(W):
                         ws.flags[q][(W + 1) * stride + rank] = epoch  # "entered": this rank may be written to
                 for q in range(W if wait_for_entry else 0):  # (switched off only to show what the rule prevents)
-                    _wait(ws.flags[rank], (W + 1) * stride + q, epoch, timeout, f"rank {rank}: entry of rank {q}")
+                    _wait(ws.flags[rank], (W + 1) * stride + q, epoch, timeout, f"rank {rank}: entry of rank {q}",
+                          ws.failed)
                 blocks = shard_rows // BM
                 cw = (K + groups - 1) // groups
                 for item in range(cta, blocks * groups, ctas):
@@ -137,7 +142,8 @@ def launch(ws: Workspace, rank: int, mode: int, a: np.ndarray, b: np.ndarray, ct
                 if owner_of(tile) != rank:
                     continue
                 for q in range(W):
-                    _wait(ws.flags[rank], q * stride + tile, epoch, timeout, f"rank {rank}: tile {tile} of rank {q}")
+                    _wait(ws.flags[rank], q * stride + tile, epoch, timeout, f"rank {rank}: tile {tile} of rank {q}",
+                          ws.failed)
                 _jitter(rng, jitter)
                 rows = slice(tile * BM, (tile + 1) * BM)
                 total = sum(ws.partial[q][:M * N].reshape(M, N)[rows] for q in range(W))  # rank order
@@ -165,7 +171,7 @@ def launch(ws: Workspace, rank: int, mode: int, a: np.ndarray, b: np.ndarray, ct
                 for q in range(W):
                     ws.flags[q][W * stride + rank] = epoch
                 for q in range(W):
-                    _wait(ws.flags[rank], W * stride + q, epoch, timeout, f"rank {rank}: end of rank {q}")
+                    _wait(ws.flags[rank], W * stride + q, epoch, timeout, f"rank {rank}: end of rank {q}", ws.failed)
                 ws.epoch[rank] = epoch
             except BaseException as e:  # noqa: BLE001
                 errors.append(e)
@@ -227,6 +233,7 @@ def run_sequence(W: int, modes: list[int], seed: int = 0, ctas: int = 3, M: int 
                     _jitter(rng, 4 * jitter)
         except BaseException as e:  # noqa: BLE001
             failures.append(e)
+            ws.failed.set()
 
     threads = [threading.Thread(target=rank_main, args=(r,)) for r in range(W)]
     for t in threads:
@@ -234,4 +241,5 @@ def run_sequence(W: int, modes: list[int], seed: int = 0, ctas: int = 3, M: int 
     for t in threads:
         t.join()
     if failures:
-        raise failures[0]
+        first = [f for f in failures if "another rank reported" not in str(f)]
+        raise (first or failures)[0]

@@ -9,7 +9,7 @@ LAYER_BACKWARD = [ALLGATHER, REDUCE_SCATTER, REDUCE_SCATTER, ALLGATHER, REDUCE_S
 
 
 @pytest.mark.parametrize("ranks", [2, 4])
-@pytest.mark.parametrize("seed", [0, 1, 2])
+@pytest.mark.parametrize("seed", [0, 1, 2, 3])
 def test_a_training_step_worth_of_launches_completes_with_the_right_sums(ranks, seed):
     run_sequence(ranks, LAYER_FORWARD * 2 + LAYER_BACKWARD * 2, seed=seed)
 
@@ -29,5 +29,5 @@ def test_pushing_before_the_peer_has_entered_is_what_the_entry_flags_prevent():
     overwritten by a peer that has already started the next all-gather launch."""
     with pytest.raises(ProtocolError, match="gathered operand changed"):
         for seed in range(5):  # the slow reader makes the overlap all but certain; a few seeds make it certain
-            run_sequence(2, [ALLGATHER, ALLGATHER, ALLGATHER], seed=seed, wait_for_entry=False, slow_reader=1)
-    run_sequence(2, [ALLGATHER, ALLGATHER, ALLGATHER], seed=0, wait_for_entry=True, slow_reader=1)
+            run_sequence(2, [ALLGATHER, ALLGATHER], seed=seed, wait_for_entry=False, slow_reader=1, M=8, ctas=2)
+    run_sequence(2, [ALLGATHER, ALLGATHER], seed=0, wait_for_entry=True, slow_reader=1, M=8, ctas=2)
