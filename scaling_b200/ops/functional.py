@@ -686,11 +686,13 @@ def adamw_step(p: torch.Tensor, m: torch.Tensor, v: torch.Tensor, g: torch.Tenso
         if float(control[1]) != 0.0:
             return
         gmul = float(control[0])
-    gf = g.float() * gmul
+    gf = g if g.dtype == torch.float32 else g.float()
+    if gmul != 1.0:
+        gf = gf * gmul
     p.mul_(1.0 - lr * weight_decay)
     m.mul_(beta1).add_(gf, alpha=1.0 - beta1)
     v.mul_(beta2).addcmul_(gf, gf, value=1.0 - beta2)
-    denom = v.sqrt() / math.sqrt(bc2) + eps
+    denom = v.sqrt().div_(math.sqrt(bc2)).add_(eps)
     p.addcdiv_(m, denom, value=-lr / bc1)
     if p_lp is not None:
         p_lp.copy_(p)
@@ -713,13 +715,14 @@ def sumsq_(g: torch.Tensor, out: torch.Tensor, flag: Optional[torch.Tensor], sca
             "sb200_sumsq",
         )
         return
-    gf = g.float()
-    s = (gf * gf).sum() * scale
+    gf = g.reshape(-1) if g.dtype == torch.float32 else g.reshape(-1).float()
+    raw = torch.dot(gf, gf)  # no squared copy; inf / nan anywhere in g makes the sum non-finite
+    s = raw * scale
     if accumulate:
         out[0] += s
     else:
         out[0] = s
-    if flag is not None and not bool(torch.isfinite(gf).all()):
+    if flag is not None and not bool(torch.isfinite(raw)):
         flag[0] = 1
 
 

@@ -153,3 +153,61 @@ def test_prompt_completion_and_chat_data_train_with_masked_loss(tmp_path: Path, 
     loss, changed, _, _ = dist_launcher(_finetune, world_size, config=cfg)[0]
     assert len(loss) == 3 and all(l == l for l in loss)
     assert any("softprompt" in n for n in changed)
+
+
+# ---------------------------------------------------------------------------------------------- images in the prompt
+def test_image_prefix_finetuning_through_the_clip_tower(tmp_path: Path):
+    """Prompt = image + text: the image is encoded by the CLIP tower into 144 positions of the input sequence and
+    the loss is finite; gradients reach the tower."""
+    import json
+
+    import numpy as np
+    from PIL import Image
+
+    vocab, _ = _embedding_setup(tmp_path)
+    rng = np.random.default_rng(0)
+    records = []
+    for i in range(2):
+        Image.fromarray(rng.integers(0, 255, size=(48, 64, 3), dtype=np.uint8)).save(tmp_path / f"img{i}.jpg")
+        records.append({"prompt": [f"img{i}.jpg", "the cat"], "completion": "sat on a mat"})
+    data = tmp_path / "data.json"
+    data.write_text(json.dumps(records))
+    arch = {"vocab_size": 32, "vocab_file": vocab, "sequence_length": 160, "image_encoder": True, "num_layers": 1}
+    cfg = tiny_config(1, arch=arch, iters=1, micro=1)  # one image, one process: the tower is slow on one CPU thread
+    cfg["data"] = {"finetuning_dataset": True, "data_prefixes": [str(data)]}
+    loss, changed, _, _ = dist_launcher(_finetune, 1, config=cfg)[0]
+    assert len(loss) == 1 and loss[0] == loss[0]
+    assert any("image_encoder" in n for n in changed)  # gradients reach the tower through the spliced positions
+
+
+def _image_batch_sync_worker(rank, world_size, port, device):
+    import torch
+
+    from scaling_b200.transformer.data._finetuning_common import sync_text_image_batch
+    from scaling_b200.transformer.data.text_dataset import TextDatasetBatch
+    from tests.test_core_distributed import _topology
+
+    t = _topology(rank, world_size, port, mp=2)
+    out = []
+    for with_images in (True, False):
+        batch = None
+        if t.model_parallel_rank == 0:
+            batch = TextDatasetBatch(
+                input_token_ids=torch.arange(12).view(2, 6), target_token_ids=torch.arange(12).view(2, 6) + 1,
+                cumulative_seq_lengths=torch.tensor([0, 6, 12], dtype=torch.int32),
+                cumulative_seq_lengths_padded=torch.tensor([0, 6, 12, -1], dtype=torch.int32),
+                position_ids=torch.arange(6).repeat(2, 1), loss_weights=torch.ones(2, 6),
+                input_images=torch.full((1, 3, 4, 4), 0.5) if with_images else None,
+                input_image_locations=torch.tensor([[1, 0, 4]]) if with_images else None)
+        got = sync_text_image_batch(t, batch)
+        out.append((got.input_token_ids.tolist(), got.loss_weights.sum().item(),
+                    None if got.input_images is None else (tuple(got.input_images.shape), got.input_images.mean().item()),
+                    None if got.input_image_locations is None else got.input_image_locations.tolist()))
+    return out
+
+
+def test_text_and_image_batches_reach_every_tensor_parallel_rank():
+    r0, r1 = dist_launcher(_image_batch_sync_worker, 2)
+    assert r0 == r1
+    assert r1[0][2] == ((1, 3, 4, 4), 0.5) and r1[0][3] == [[1, 0, 4]]
+    assert r1[1][2] is None and r1[1][3] is None  # a batch without images stays without
