@@ -15,7 +15,6 @@
 
 from __future__ import annotations
 
-import ctypes
 import os
 from ctypes import c_double, c_int, c_long, c_void_p
 from typing import Any, Optional
