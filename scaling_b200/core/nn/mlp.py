@@ -15,7 +15,6 @@ from typing import Any, Callable, Optional
 import torch
 
 from ...ops import functional as K
-from ...parallel.collectives import all_reduce_scatter_to_sequence_parallel
 from ...parallel.topology import Topology
 from .activation_function import ActivationFunction, get_activation_function
 from .linear import ColumnParallelLinear, RowParallelLinear

@@ -25,7 +25,6 @@ fp32 master weight and Adam moments (``optimizer.py:342-455``), or raw per-rank 
 from __future__ import annotations
 
 import collections
-import math
 from pathlib import Path
 from typing import Any, List, Optional, Union
 

@@ -4,7 +4,7 @@ row-parallel layers alternating, as in the reference example (examples/mlp_examp
 
 from __future__ import annotations
 
-from typing import Any, Callable, Optional
+from typing import Any, Callable
 
 import torch
 import torch.distributed as dist

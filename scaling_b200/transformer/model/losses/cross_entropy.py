@@ -10,7 +10,7 @@ matrix is neither gathered nor copied to fp32.
 
 from __future__ import annotations
 
-from typing import Any, Dict, Optional, Tuple
+from typing import Dict, Optional, Tuple
 
 import torch
 import torch.distributed as dist

@@ -1,5 +1,4 @@
 """Numerics of the sm_100a kernels against plain PyTorch fp32 references of the same op."""
-import math
 
 import pytest
 import torch

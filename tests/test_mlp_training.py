@@ -5,7 +5,6 @@ import copy
 from pathlib import Path
 
 import pytest
-import torch
 
 from tests.utils import dist_launcher
 
