@@ -70,3 +70,34 @@ def test_from_checkpoint_round_trip(tmp_path: Path):
     a, b = m.logits(input_tokens=[5, 6, 7]), loaded.logits(input_tokens=[5, 6, 7])
     assert torch.allclose(a, b, atol=1e-6)
     assert loaded.tokenizer is not None
+
+
+def test_attention_manipulation_controls():
+    """Per-token attention controls: factor 1 leaves the logits alone, factor 0 removes the token from every later
+    position's view (the positions before it are untouched under the causal mask), both in the log-additive and in
+    the multiplicative form."""
+    from scaling_b200.transformer.data.inference_settings import (Control, InferenceSettings,
+                                                                  InferenceSuppressionParameters)
+    from scaling_b200.transformer.data.text_dataset import TextDatasetBatch
+
+    m = _module()
+    prompt = [3, 7, 1, 9, 4, 11]
+
+    def run(controls, log_additive=True):
+        params = None if controls is None else [InferenceSuppressionParameters(None, log_additive, controls)]
+        settings = InferenceSettings(use_cache=False, reset_cache=True, cache_index=0, embedding_layers=[-1],
+                                     inference_control_parameters=params)
+        batch = TextDatasetBatch(input_token_ids=torch.tensor([prompt]), inference_settings=settings)
+        with torch.no_grad():
+            return m.forward(batch).activations.squeeze(0)
+
+    plain = run(None)
+    assert torch.allclose(run([Control(token_index=2, factor=1.0)]), plain, atol=1e-5)
+    assert torch.allclose(run([Control(token_index=2, factor=1.0)], log_additive=False), plain, atol=1e-5)
+    for log_additive in (True, False):
+        suppressed = run([Control(token_index=2, factor=0.0)], log_additive=log_additive)
+        assert torch.allclose(suppressed[:2], plain[:2], atol=1e-5)  # earlier positions never saw token 2
+        assert not torch.allclose(suppressed[3:], plain[3:], atol=1e-4)
+    damped = run([Control(token_index=2, factor=0.5)])
+    gap = lambda t: (t[3:] - plain[3:]).abs().max().item()  # noqa: E731
+    assert 0 < gap(damped) < gap(run([Control(token_index=2, factor=0.0)]))
