@@ -224,3 +224,58 @@ def test_legacy_indexed_datasets(tmp_path: Path):
     assert ds.sizes.tolist() == [5, 3, 1] and ds.get(0, offset=1, length=2).tolist() == [1, 2]
     text = TextDataset(data_prefix=tmp_path / "mmap", sequence_length=4, seed=1, legacy_dataset=True)
     assert len(text) >= 1 and text[0].token_ids.numel() == 5
+
+
+def test_text_windows_overlap_by_one_token_and_drop_the_tail():
+    """Documents are walked in the given order; a window holds sequence_length + 1 tokens, its last token opens the
+    next window, what cannot fill a window is dropped; `only_full_sequences` starts every window inside one document."""
+    from scaling_b200.transformer.data.text_dataset import pack_windows
+
+    sizes = [7, 3, 12]
+    windows = pack_windows(sizes, doc_order=[0, 1, 2], sequence_length=4)
+    triples = [w.reshape(-1, 3).tolist() for w in windows]
+    flat = [[(d, i) for d, s, e in t for i in range(s, e)] for t in triples]
+    assert all(len(f) == 5 for f in flat)
+    for a, b in zip(flat, flat[1:]):
+        assert a[-1] == b[0]  # the target of the last position is the input of the next window's first
+    stream = [(d, i) for d in (0, 1, 2) for i in range(sizes[d])]
+    covered = [flat[0][0]] + [p for f in flat for p in f[1:]]
+    assert covered == stream[:len(covered)] and len(stream) - len(covered) < 4  # only a tail shorter than a window is lost
+    full = pack_windows(sizes, doc_order=[0, 1, 2], sequence_length=4, only_full_sequences=True)
+    for w in full:
+        t = w.reshape(-1, 3).tolist()
+        assert len(t) == 1 and t[0][2] - t[0][1] == 5  # one document per window, never a stitched one
+    assert {w.reshape(-1, 3)[0][0] for w in full} == {0, 2}  # the 3-token document cannot fill a window
+
+
+def test_sampler_indices_follow_the_consumed_samples():
+    """epoch = consumed // usable, indices stride over the data-parallel ranks, the remainder of an epoch is cut."""
+    from scaling_b200.core.data.dataloader import RandomSampler
+
+    class _DS:
+        def __len__(self):
+            return 23
+
+        def set_seed(self, seed, shuffle=True):
+            self.seed = seed
+
+    def batches(dp_rank, consumed, n):
+        from types import SimpleNamespace
+
+        ds = _DS()
+        topology = SimpleNamespace(config=SimpleNamespace(micro_batch_size=2, data_parallel_size=2),
+                                   data_parallel_rank=dp_rank)
+        s = iter(RandomSampler(dataset=ds, seed=5, consumed_samples=consumed, topology=topology))
+        out = [b for _, b in zip(range(n), s)]
+        return out, ds.seed
+
+    r0, seed0 = batches(0, 0, 99)
+    r1, _ = batches(1, 0, 99)
+    usable = (23 // 2 // 2) * 2 * 2  # 20 samples per epoch: five micro batches of two per rank
+    assert len(r0) == len(r1) == 5 and seed0 == 5
+    assert r0[0] == [0, 2] and r1[0] == [1, 3]
+    assert sorted(i for b in r0 + r1 for i in b) == list(range(usable))
+    resumed, seed = batches(0, 8, 99)
+    assert resumed == r0[2:] and seed == 5
+    wrapped, seed = batches(0, usable + 4, 1)
+    assert wrapped == [r0[1]] and seed == 6  # the next epoch reshuffles the data with seed + epoch
