@@ -300,3 +300,36 @@ def test_public_names_of_the_two_packages():
                                        "learning_rates", "overflow", "no_overflow_steps", "current_loss_scale",
                                        "step_duration", "debug_dict")
     assert EvaluationStepOutput._fields == ("loss", "metrics", "step_duration")
+
+
+# ---------------------------------------------------------------------------------------------- u-muP multipliers
+def test_unit_scaled_multipliers_and_residual_scales():
+    from scaling_b200.core.nn.parameter_meta import UMUP_WEIGHT_TYPE, CoreParameterMeta, UMuPParameterMeta
+    from scaling_b200.core.nn.umup import UMuParametrization as U
+
+    def meta(shape, kind, parallel_dim=None, on_residual=False):
+        m = CoreParameterMeta(local_shape=shape, is_model_parallel=parallel_dim is not None,
+                              model_parallel_dimension=parallel_dim)
+        m.umup_meta = UMuPParameterMeta(weight_type=kind, on_residual=on_residual)
+        return m
+
+    B, depth = 4096, 16
+    assert U.get_parameter_multipliers(meta((64,), UMUP_WEIGHT_TYPE.NORM), 1, B, depth) == (1.0, 1.0, B ** -0.5, 1.0)
+    # column-parallel hidden weight [out / 2, in]: fan-in is the full input width
+    f, b, g, lr = U.get_parameter_multipliers(meta((32, 256), UMUP_WEIGHT_TYPE.HIDDEN_WEIGHT, 0, True), 2, B, depth)
+    assert (f, b, g) == (256 ** -0.5, 256 ** -0.5, B ** -0.5) and lr == pytest.approx(256 ** -0.5 * depth ** -0.5)
+    # row-parallel output weight [out, in / 2]: fan-in counts every rank's slice
+    f, b, g, lr = U.get_parameter_multipliers(meta((100, 128), UMUP_WEIGHT_TYPE.OUTPUT_WEIGHT, 1), 2, B, depth)
+    assert (f, b, g, lr) == (1.0 / 256, 100 ** -0.5, B ** -0.5, 1.0)
+    f, b, g, lr = U.get_parameter_multipliers(meta((500, 64), UMUP_WEIGHT_TYPE.INPUT_EMBEDDING, 0), 2, B, depth)
+    assert (f, b, lr) == (1.0, 1.0, 64 ** -0.5) and g == pytest.approx((B / 1000) ** -0.5)
+    # residual scales keep unit variance: a^2 + b^2 = 1, later branches weigh less under pre-norm
+    mults = U.get_umup_transformer_residual_mults(1.0, 1.0, num_layers=2)
+    assert mults == [1.0, 1.0, 1.0, 1.0]
+    scales = [U.get_umup_residual_scales(mults, i, pre_norm=True, depth=4) for i in range(4)]
+    assert all(a * a + b * b == pytest.approx(1.0) for a, b in scales)
+    assert [a for a, _ in scales] == sorted((a for a, _ in scales), reverse=True)
+    mult, out_scale = U.get_umup_cross_entropy_scales(1.0, 1000)
+    assert mult == 1.0 and out_scale == pytest.approx(1000 / 999 ** 0.5)
+    att, _ = U.get_umup_attention_scales(head_dim=64, sequence_length=2048, mult=1.0, dropout_p=0.0)
+    assert att == 1.0 / 64
