@@ -333,3 +333,20 @@ def test_unit_scaled_multipliers_and_residual_scales():
     assert mult == 1.0 and out_scale == pytest.approx(1000 / 999 ** 0.5)
     att, _ = U.get_umup_attention_scales(head_dim=64, sequence_length=2048, mult=1.0, dropout_p=0.0)
     assert att == 1.0 / 64
+
+
+# ---------------------------------------------------------------------------------------------- Determined glue
+def test_hyper_parameters_become_config_overrides():
+    from scaling_b200.transformer.train_determined import hparams_to_overrides
+
+    hp = {"learning_rate": 3e-4, "target_train_tokens": 2_000_000, "warmup_tokens": 200_000, "sequence_length": 1000,
+          "global_batch_size": 20, "kernel": "flash_attention", "sequence_parallel": True}
+    out = hparams_to_overrides(hp, {"trainer": {"seed": 7}})
+    assert out["trainer"] == {"seed": 7, "train_iterations": 100}
+    assert out["learning_rate_scheduler"] == {"learning_rate": 3e-4, "learning_rate_warmup_steps": 10}
+    assert out["transformer_architecture"]["masked_softmax"] == {"kernel": "flash_attention"}
+    assert out["topology"]["sequence_parallel"] is True
+    # a restarted single run carries its whole layout, which replaces the search space
+    assert hparams_to_overrides({"layout": {"learning_rate": 1.0}, "learning_rate": 2.0})["learning_rate_scheduler"] == {
+        "learning_rate": 1.0}
+    assert hparams_to_overrides(None, {"a": 1}) == {"a": 1}
