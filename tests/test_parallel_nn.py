@@ -182,3 +182,28 @@ def test_lora_merge_keeps_the_output_and_changes_the_weights(world_size, qkv_in_
     for err, scale, changed, has_lora in dist_launcher(_lora_worker, world_size, qkv_in_one=qkv_in_one, kv_heads=kv_heads):
         assert err < 1e-4 * max(1.0, scale), (err, scale)
         assert changed >= 2 and not has_lora
+
+
+# ---------------------------------------------------------------------------------------------- fp8 linear (no ranks)
+def test_fp8_linear_stays_close_to_the_full_precision_linear():
+    from scaling_b200.core.fp8.fp8_linear import fp8_linear
+
+    torch.manual_seed(0)
+    x = torch.randn(16, 64, requires_grad=True)
+    w = (torch.randn(32, 64) * 0.2).requires_grad_()
+    b = torch.randn(32, requires_grad=True)
+    e4, e5 = torch.float8_e4m3fn, torch.float8_e5m2
+    y = fp8_linear(x, w, b, dtypes_forward=(e4, e4), dtypes_grad_input=(e5, e4), dtypes_grad_weight=(e4, e5))
+    y.square().mean().backward()
+    got = (y.detach(), x.grad.clone(), w.grad.clone(), b.grad.clone())
+    x.grad = w.grad = b.grad = None
+    ref = torch.nn.functional.linear(x, w, b)
+    ref.square().mean().backward()
+    for g, r in zip(got, (ref.detach(), x.grad, w.grad, b.grad)):
+        assert (g - r).norm() / r.norm() < 0.1
+    assert not torch.equal(got[0], ref.detach())  # the operands were rounded
+    # saturation instead of inf: values beyond the format's range clamp to its maximum
+    big = fp8_linear(torch.full((1, 4), 1e6), torch.eye(4), None, dtypes_forward=(e4, e4))
+    assert torch.isfinite(big).all() and big.max() == torch.finfo(e4).max
+    # a product without a dtype pair runs unquantised
+    assert torch.allclose(fp8_linear(x, w, b), ref)
