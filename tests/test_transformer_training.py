@@ -160,3 +160,20 @@ def test_tied_embedding_and_head_across_pipeline_stages(tmp_path: Path):
             assert abs(a - b) < 2e-4 * max(1.0, abs(b)), (kw, got, base)
     untied = losses(1, arch={"weight_tying": False})
     assert untied != base
+
+
+@pytest.mark.dist
+def test_activation_checkpointing_replays_dropout_exactly(tmp_path: Path):
+    """Recomputation restores the random state of the first pass: with dropout everywhere, per-layer and per-stage
+    checkpointing give the losses of the run that keeps its activations, bit for bit, also under tensor parallelism
+    (where the dropout masks of the tensor-parallel ranks have to agree)."""
+    arch = {"dropout_embedding": 0.1, "dropout_after_attention": 0.1, "dropout_after_mlp": 0.1,
+            "dropout_attention_probs": 0.1, "masked_softmax": {"kernel": "torch"}}
+    init = str(tmp_path / "init")
+    plain = losses(1, save_initial=init, arch=arch)
+    assert plain != losses(1, load_dir=init, arch=dict(arch, dropout_after_mlp=0.0, dropout_after_attention=0.0,
+                                                       dropout_embedding=0.0, dropout_attention_probs=0.0))
+    for ckpt in ("every_layer", "every_pipe_stage"):
+        assert losses(1, load_dir=init, arch=arch, ckpt=ckpt) == plain, ckpt
+    tp_plain = losses(2, mp=2, load_dir=init, arch=arch)
+    assert losses(2, mp=2, load_dir=init, arch=arch, ckpt="every_layer") == tp_plain
