@@ -190,3 +190,35 @@ def test_checkpoint_layout_and_key_names(tmp_path: Path):
     meta = json.loads((step / "parameter_meta_0_5.json").read_text())
     assert any("embedding.weight" in str(k) or "embedding.weight" in str(v) for k, v in (meta.items() if isinstance(meta, dict) else enumerate(meta)))
     assert (save / "latest").read_text() == "global_step2"
+
+
+def _count_worker(rank, world_size, port, device, config):
+    import copy
+
+    from scaling_b200.core.runner import LaunchConfig
+    from scaling_b200.parallel import Topology
+    from scaling_b200.transformer import TransformerConfig, TransformerContext, init_model
+
+    lc = LaunchConfig(master_port=port, master_addr="127.0.0.1", world_size=world_size, global_rank=rank,
+                      local_slot=rank, payload=copy.deepcopy(config))
+    cfg = TransformerConfig.from_dict(lc.overwrite_config_dict_with_launcher_args(dict(lc.payload)))
+    context = TransformerContext(config=cfg, topology=Topology(cfg.topology))
+    context.initialize(master_addr="127.0.0.1", master_port=str(port), seed=1)
+    return init_model(context).get_params_count()
+
+
+@pytest.mark.parametrize("layout", [dict(world_size=1), dict(world_size=2, mp=2), dict(world_size=2, pp=2, ga=2, micro=2)])
+def test_parameter_counts_do_not_depend_on_the_layout(layout):
+    """Unique = every weight once (tied weights and copies replicated over the tensor-parallel ranks counted once):
+    the same in every layout and on every rank.  Total = every stored copy."""
+    h, v, layers = 64, 128, 2
+    replicated = 2 * (2 * h) + h + h  # per block: two norms (weight, bias), attention-out bias, mlp-out bias
+    block = (3 * h * h + 3 * h) + (h * h) + 2 * (4 * h * h) + 4 * h + replicated
+    unique = v * h + layers * block + 2 * h + v * h
+    kw = dict(layout)
+    ws = kw.pop("world_size")
+    mp = kw.get("mp", 1)
+    copies = (mp - 1) * (layers * replicated + 2 * h)  # replicated parameters live on every tensor-parallel rank
+    for tying, expected in ((False, (unique + copies, unique)), (True, (unique + copies, unique - v * h))):
+        counts = dist_launcher(_count_worker, ws, config=tiny_config(ws, arch={"weight_tying": tying}, **kw))
+        assert all(tuple(c) == expected for c in counts), (tying, counts, expected)
