@@ -20,7 +20,8 @@ import torch
 
 from ....ops import functional as K
 from ....ops.attention import attention_mask_from_cu_seqlens, flash_attention
-from ....parallel.collectives import SequenceShard, all_concat, all_reduce_scatter_to_sequence_parallel, all_shard
+from ....parallel.collectives import (SequenceShard, all_concat, all_reduce_scatter_to_sequence_parallel, all_shard,
+                                       copy_to_tensor_model_parallel_region)
 from ....parallel.topology import Topology
 from ..linear import ColumnParallelLinear, RowParallelLinear, get_device
 from ..lora import LoRaConfig, LoRAModuleType, ParallelLoRa
@@ -325,8 +326,14 @@ class ParallelSelfAttention(torch.nn.Module):
             q, k, v = qkv[..., :d], qkv[..., d:2 * d], qkv[..., 2 * d:]
         else:
             q = self.query(x).view(T, npp, d)
-            k = self.key(x).view(T, -1, d)
-            v = self.value(x).view(T, -1, d)
+            x_kv = x
+            if (self.kv_replicated and self.model_parallel_size > 1 and isinstance(x, torch.Tensor)
+                    and self.topology is not None and not self.topology.config.sequence_parallel):
+                # every rank back-propagates only through the KV heads its own queries read: the input gradient of
+                # the replicated projections is a partial sum and is reduced like that of a column-parallel linear
+                x_kv = copy_to_tensor_model_parallel_region(x, self.topology)
+            k = self.key(x_kv).view(T, -1, d)
+            v = self.value(x_kv).view(T, -1, d)
             if self.kv_replicated and k.shape[1] > 1:
                 # keep only the KV heads that this rank's query heads read
                 r = self.topology.model_parallel_rank if self.topology is not None else 0

@@ -78,11 +78,13 @@ class OptimizerParamGroup:
                 return 2
             return 0 if self.parameter_metas[i].is_model_parallel else 1
 
-        order = sorted(range(len(params)), key=lambda i: (rank_of(i), i))
+        # classes are taken before the lists are permuted (rank_of indexes them)
+        class_of = [rank_of(i) for i in range(len(params))]
+        order = sorted(range(len(params)), key=lambda i: (class_of[i], i))
+        classes = [class_of[i] for i in order]
         self.parameter_names = [self.parameter_names[i] for i in order]
         self.parameter_metas = [self.parameter_metas[i] for i in order]
         self.parameters_original = params = [params[i] for i in order]
-        classes = [rank_of(i) for i in order]
 
         self.offsets: list[int] = []
         cursor = 0

@@ -177,3 +177,16 @@ def test_activation_checkpointing_replays_dropout_exactly(tmp_path: Path):
         assert losses(1, load_dir=init, arch=arch, ckpt=ckpt) == plain, ckpt
     tp_plain = losses(2, mp=2, load_dir=init, arch=arch)
     assert losses(2, mp=2, load_dir=init, arch=arch, ckpt="every_layer") == tp_plain
+
+
+@pytest.mark.dist
+def test_multi_query_attention_with_fewer_kv_heads_than_tensor_parallel_ranks(tmp_path: Path):
+    """One KV head, two tensor-parallel ranks: the KV projections are replicated, each rank back-propagates only
+    through its own query heads; weight and input gradients of the replicated projections are summed over the group."""
+    arch = dict(LLAMA_ARCH, attention_num_kv_heads=1)
+    init = str(tmp_path / "init")
+    base = losses(1, save_initial=init, arch=arch)
+    for kw in (dict(mp=2), dict(mp=2, sp=True)):
+        got = losses(2, load_dir=init, arch=arch, **kw)
+        for a, b in zip(got, base):
+            assert abs(a - b) < 2e-5 * max(1.0, abs(b)), (kw, got, base)
