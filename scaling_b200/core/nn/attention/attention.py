@@ -21,7 +21,7 @@ import torch
 from ....ops import functional as K
 from ....ops.attention import attention_mask_from_cu_seqlens, flash_attention
 from ....parallel.collectives import (SequenceShard, all_concat, all_reduce_scatter_to_sequence_parallel, all_shard,
-                                       copy_to_tensor_model_parallel_region)
+                                       copy_to_tensor_model_parallel_region, shard_to_sequence_parallel_region)
 from ....parallel.topology import Topology
 from ..linear import ColumnParallelLinear, RowParallelLinear, get_device
 from ..lora import LoRaConfig, LoRAModuleType, ParallelLoRa
@@ -498,13 +498,16 @@ class ParallelSelfAttention(torch.nn.Module):
             full = all_concat(hidden, self.topology) if self.model_parallel_size > 1 else hidden
             lora_dense = self.lora_modules[f"dense_{self.lora_config.name}"](full)
         sp = self.topology is not None and self.topology.config.sequence_parallel
-        if sp and lora_dense is None:
-            return self.dense.forward_to_sequence_parallel(hidden)
+        if sp:
+            out = self.dense.forward_to_sequence_parallel(hidden)
+            if lora_dense is not None:
+                # the adapter's output is already summed over the ranks: it joins after the reduction, as this
+                # rank's tokens of it (added to the partial sums it would be counted once per rank)
+                out = out + shard_to_sequence_parallel_region(lora_dense, self.topology)
+            return out
         out = self.dense(hidden)
         if lora_dense is not None:
             out = out + lora_dense
-        if sp:
-            out = all_reduce_scatter_to_sequence_parallel(out, self.topology)
         return out
 
     # ------------------------------------------------------------------ LoRA merge

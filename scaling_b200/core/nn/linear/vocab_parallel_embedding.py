@@ -70,7 +70,9 @@ class VocabParallelEmbedding(torch.nn.Module):
         self.forward_multiplier = meta.umup_meta.forward_multiplier
         self.weight_grad_multiplier = meta.umup_meta.grad_multiplier
 
-    def forward(self, x: torch.Tensor) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, scatter_tokens: bool = True) -> torch.Tensor:
+        """``scatter_tokens=False`` keeps the full (all-reduced) output under sequence parallelism, for callers that
+        edit positions of the sequence before they shard it themselves."""
         w = scale_bwd(self.weight, self.weight_grad_multiplier) if self._use_umup else self.weight
         # ids outside [vocab_start, vocab_end) come back as zero rows
         out = K.embedding(x, w, self.vocab_start_index)
@@ -78,7 +80,7 @@ class VocabParallelEmbedding(torch.nn.Module):
             out = scale_fwd(out, self.forward_multiplier)
         if self.model_parallel_size > 1:
             assert self.topology is not None
-            if self.topology.config.sequence_parallel:
+            if self.topology.config.sequence_parallel and scatter_tokens:
                 out = all_reduce_scatter_to_sequence_parallel(out, self.topology)
             else:
                 out = all_reduce(out, self.topology)

@@ -19,6 +19,7 @@ import torch
 import torch.distributed as dist
 from pydantic import Field
 
+from ...parallel.collectives import copy_to_tensor_model_parallel_region
 from ...parallel.topology import Topology
 from ..config import BaseConfig
 from .linear import ColumnParallelLinear, RowParallelLinear
@@ -84,9 +85,19 @@ class ParallelLoRa(torch.nn.Module):
             )
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
+        # Under sequence parallelism a column-parallel linear takes its input from the token gather, whose backward
+        # pass sums the partial input gradients.  Two inputs here are replicated tensors instead (the full attention
+        # output fed to the dense adapter, and the gathered low-rank activations fed to the second linear): their
+        # gradient is summed explicitly.
+        sp = (self.topology is not None and self.model_parallel_size > 1 and self.topology.config.sequence_parallel)
+        is_dense = self.lora_module_type == LoRAModuleType.DENSE
+        if sp and is_dense:
+            x = copy_to_tensor_model_parallel_region(x, self.topology)
         x = self.dense_in(x)
         if self.dropout is not None:
             x = self.dropout(x)
+        if sp and not is_dense:
+            x = copy_to_tensor_model_parallel_region(x, self.topology)
         return self.dense_out(x) * self.scaling
 
     def get_delta_weights(self) -> torch.Tensor:

@@ -158,7 +158,28 @@ class _GatherTokens(torch.autograd.Function):
         return reduce_scatter_tokens_raw(g, ctx.topology), None
 
 
+class _ShardTokens(torch.autograd.Function):
+    """Keep this rank's contiguous chunk of the tokens of a replicated activation; backward gathers the chunks."""
+
+    @staticmethod
+    def forward(ctx, x, topology):  # type: ignore[override]
+        ctx.topology = topology
+        n, r = topology.model_parallel_size, topology.model_parallel_rank
+        flat = x.contiguous().view(-1)
+        chunk = flat.numel() // n
+        return flat[r * chunk:(r + 1) * chunk].clone().view(_sp_out_shape(x.shape, n, gather=False))
+
+    @staticmethod
+    def backward(ctx, g):  # type: ignore[override]
+        return all_gather_tokens_raw(g, ctx.topology), None
+
+
 # ------------------------------------------------------------------ public API
+def shard_to_sequence_parallel_region(x: torch.Tensor, topology: Optional[Topology]) -> torch.Tensor:
+    """Replicated activation -> this rank's tokens (the layout a reduce-scatter over tokens leaves behind)."""
+    return x if _size(topology) == 1 else _ShardTokens.apply(x, topology)
+
+
 def copy_to_tensor_model_parallel_region(x: torch.Tensor, topology: Optional[Topology]) -> torch.Tensor:
     return x if _size(topology) == 1 else _CopyToRegion.apply(x, topology)
 

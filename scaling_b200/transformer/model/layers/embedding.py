@@ -84,7 +84,12 @@ class BaseEmbeddingInput(BaseLayer[TextDatasetBatch, TransformerLayerIO, Transfo
         if reset_cache:
             self.cache[cache_index] = None
         assert x.input_token_ids is not None
-        h = self.embedding(x.input_token_ids)
+        t = self.topology
+        sequence_parallel = t is not None and t.config.sequence_parallel and t.config.model_parallel_size > 1
+        # image and soft-prompt positions are written into the whole sequence: under sequence parallelism the
+        # embedding then stays replicated until they are in, and is split over the ranks afterwards
+        splice_full = sequence_parallel and (x.input_images is not None or self.softprompt_name is not None)
+        h = self.embedding(x.input_token_ids, scatter_tokens=not splice_full)
         if self.dropout.p > 0.0:
             h = self._dropout(self.dropout, h)
 
@@ -105,6 +110,11 @@ class BaseEmbeddingInput(BaseLayer[TextDatasetBatch, TransformerLayerIO, Transfo
         if self.softprompt_name is not None:
             sp = getattr(self, f"softprompt_{self.softprompt_name}")
             h = torch.cat([sp.unsqueeze(0).expand(h.shape[0], -1, -1), h[:, sp.shape[0]:, :]], dim=1).contiguous()
+
+        if splice_full:
+            from ....parallel.collectives import shard_to_sequence_parallel_region
+
+            h = shard_to_sequence_parallel_region(h, t)
 
         out = TransformerLayerIO(
             activations=h, position_ids=x.position_ids, cumulative_seq_lengths=x.cumulative_seq_lengths,

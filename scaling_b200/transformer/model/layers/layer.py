@@ -99,6 +99,13 @@ class TransformerLayer(TransformerLayerBaseIO):
 
     def apply_adapter(self, x: torch.Tensor, adapter_name: str) -> torch.Tensor:
         assert hasattr(self, adapter_name), f"cannot use adapter '{adapter_name}' as it is not initialized"
+        t = self.topology
+        if t is not None and t.config.sequence_parallel and t.config.model_parallel_size > 1:
+            # the residual stream holds this rank's tokens: the adapter's first linear gathers them, its last one
+            # scatters the result again
+            from ....parallel.collectives import SequenceShard
+
+            x = SequenceShard(x, t)  # type: ignore[assignment]
         return getattr(self, adapter_name)(x)
 
     def _dropout(self, module: torch.nn.Dropout, x: torch.Tensor) -> torch.Tensor:

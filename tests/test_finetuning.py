@@ -216,3 +216,18 @@ def test_text_and_image_batches_reach_every_tensor_parallel_rank():
     assert r0 == r1
     assert r1[0][2] == ((1, 3, 4, 4), 0.5) and r1[0][3] == [[1, 0, 4]]
     assert r1[1][2] is None and r1[1][3] is None  # a batch without images stays without
+
+
+def test_adapters_soft_prompt_bias_set_and_lora_under_sequence_parallelism(tmp_path: Path):
+    """With the residual stream split over the tokens: adapters gather and scatter like the MLP, the soft prompt is
+    written into the whole sequence before it is split, the dense LoRA output joins after the reduction, gradients of
+    replicated LoRA inputs are summed — the losses equal those of one process."""
+    arch = dict(FINETUNE_ARCH, lora_config={"name": "lora", "rank": 4, "alpha": 8,
+                                            "parallel_modules": ["query", "key", "value", "dense"]})
+    groups = [dict(GROUPS[0], parameters_include=GROUPS[0]["parameters_include"] + ["lora"])]
+    training = {"allow_missing_params_in_optimizer": True}
+    init = str(tmp_path / "init")
+    base = losses(1, save_initial=init, arch=arch, groups=groups, training=training)
+    got = losses(2, mp=2, sp=True, load_dir=init, arch=arch, groups=groups, training=training)
+    for a, b in zip(got, base):
+        assert abs(a - b) < 2e-5 * max(1.0, abs(b)), (got, base)
