@@ -19,6 +19,7 @@ import torch
 from ....core.nn.linear import ColumnParallelLinear, VocabParallelEmbedding
 from ....core.nn.norm import get_norm
 from ....core.nn.parameter_meta import UMUP_WEIGHT_TYPE
+from ....core.nn.scale import scale_bwd
 from ....ops import functional as K
 from ....parallel.collectives import all_concat, copy_to_tensor_model_parallel_region
 from ....parallel.topology import Topology
@@ -121,6 +122,7 @@ class TransformerEmbeddingHead(TransformerLayerBaseIO):
         cfg = architecture_config.embedding_head_config
         assert cfg is not None, "Initializing EmbeddingHead without embedding_head_config is not possible"
         self.embedding_head_config = cfg
+        self.topology = topology
         dev = device if device is not None else _device(topology)
         width = architecture_config.hidden_size
         for i, out in enumerate(cfg.proj_layers or []):
@@ -167,7 +169,13 @@ class TransformerEmbeddingHead(TransformerLayerBaseIO):
 
     def forward(self, x: TransformerLayerIO) -> TransformerLayerIO:
         assert x.loss_weights is not None, "loss_weights are required for embedding pooling"
-        h = self.apply_embedding_head_proj(x.activations) if self.embedding_head_config.proj_layers else x.activations
+        acts = x.activations
+        t = self.topology
+        if t is not None and t.config.sequence_parallel and t.config.model_parallel_size > 1:
+            # This head is replicated: every tensor-parallel rank computes the same loss from the gathered sequence
+            # and sends the same, complete gradient back into the gather, whose backward pass sums over the ranks.
+            acts = scale_bwd(acts, 1.0 / t.config.model_parallel_size)
+        h = self.apply_embedding_head_proj(acts) if self.embedding_head_config.proj_layers else acts
         pooled = self.apply_pooling(h.float(), x.loss_weights, self.embedding_head_config.pooling)
         return TransformerLayerIO(
             activations=pooled, position_ids=x.position_ids, cumulative_seq_lengths=x.cumulative_seq_lengths,

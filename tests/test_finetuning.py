@@ -231,3 +231,28 @@ def test_adapters_soft_prompt_bias_set_and_lora_under_sequence_parallelism(tmp_p
     got = losses(2, mp=2, sp=True, load_dir=init, arch=arch, groups=groups, training=training)
     for a, b in zip(got, base):
         assert abs(a - b) < 2e-5 * max(1.0, abs(b)), (got, base)
+
+
+def test_embedding_head_layouts_agree(tmp_path: Path):
+    """The replicated pooling head behind tensor, sequence and pipeline parallel trunks: same losses as one process
+    (under sequence parallelism every rank sends the same complete gradient into the token gather: it is scaled so
+    that the sum over the ranks is the gradient itself)."""
+    from tests.test_transformer_training import run_training
+
+    vocab, data = _embedding_setup(tmp_path)
+    arch = {"vocab_size": 32, "vocab_file": vocab, "lm_head": False, "sequence_length": 12, "causal": True,
+            "embedding_head_config": {"name": "emb", "proj_layers": [16], "pooling": "weighted_mean"}}
+    training = {"loss_function_config": {"loss_type": "contrastive_loss", "number_of_hard_negatives": 1,
+                                         "use_instructions": True}}
+
+    def cfg(ws, **kw):
+        c = tiny_config(ws, arch=arch, iters=4, micro=4, training=training, **kw)
+        c["data"] = {"embedding_dataset": True, "data_prefixes": [data]}
+        return c
+
+    init = str(tmp_path / "init")
+    base = dist_launcher(run_training, 1, config=cfg(1), save_initial=init)[0]
+    for kw in (dict(mp=2, sp=True), dict(pp=2, ga=1)):
+        got = dist_launcher(run_training, 2, config=cfg(2, load_dir=init, **kw))[0]
+        for a, b in zip(got, base):
+            assert abs(a - b) < 2e-5 * max(1.0, abs(b)), (kw, got, base)
