@@ -43,6 +43,10 @@ class TransformerTrainer(BaseTrainer[TransformerContext, TransformerParallelModu
         vocab_file = self.context.config.transformer_architecture.vocab_file
         if vocab_file is not None and save_dir is not None and self.context.topology.config.global_rank == 0:
             shutil.copy(vocab_file, Path(save_dir) / "vocab.json")
+            # also beside the weights, where TransformerInferenceModule.from_checkpoint looks for it
+            step_dir = Path(save_dir) / f"global_step{self.context.iterations}"
+            if step_dir.is_dir():
+                shutil.copy(vocab_file, step_dir / "vocab.json")
         return save_dir
 
     def _tflops_metrics(self, iter_time_s: float) -> dict[str, float]:

@@ -101,3 +101,26 @@ def test_attention_manipulation_controls():
     damped = run([Control(token_index=2, factor=0.5)])
     gap = lambda t: (t[3:] - plain[3:]).abs().max().item()  # noqa: E731
     assert 0 < gap(damped) < gap(run([Control(token_index=2, factor=0.0)]))
+
+
+def test_checkpoint_of_a_tensor_parallel_run_loads_into_the_inference_module(tmp_path: Path):
+    """Training checkpoints are layout independent: one written by two tensor-parallel ranks (multi-query attention with
+    replicated KV projections) gives the logits of the checkpoint written by a single process."""
+    import pytest
+
+    from tests.test_finetuning import _embedding_setup
+    from tests.test_transformer_training import LLAMA_ARCH, losses
+
+    vocab, _ = _embedding_setup(tmp_path)
+    arch = dict(LLAMA_ARCH, attention_num_kv_heads=1, vocab_file=vocab)
+    init = str(tmp_path / "init")
+    losses(1, save_initial=init, arch=arch, iters=1)
+    logits = {}
+    for name, ws, kw in (("one", 1, {}), ("tp", 2, dict(mp=2, sp=True))):
+        losses(ws, load_dir=init, arch=arch, iters=3, save_dir=str(tmp_path / name), save_interval=3, **kw)
+        module = TransformerInferenceModule.from_checkpoint(tmp_path / name / "global_step3", devices=("cpu",))
+        logits[name] = module.logits(input_tokens=[3, 9, 27, 81, 5])
+    assert logits["one"].shape == (5, 128)
+    assert torch.allclose(logits["tp"], logits["one"], atol=2e-4), (logits["tp"] - logits["one"]).abs().max()
+    with pytest.raises(AssertionError, match="Config file not found"):
+        TransformerInferenceModule.from_checkpoint(tmp_path / "one", devices=("cpu",))  # the step folder is the checkpoint
