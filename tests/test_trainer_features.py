@@ -222,3 +222,33 @@ def test_parameter_counts_do_not_depend_on_the_layout(layout):
     for tying, expected in ((False, (unique + copies, unique)), (True, (unique + copies, unique - v * h))):
         counts = dist_launcher(_count_worker, ws, config=tiny_config(ws, arch={"weight_tying": tying}, **kw))
         assert all(tuple(c) == expected for c in counts), (tying, counts, expected)
+
+
+def _losses_with_evaluation(rank, world_size, port, device, config):
+    from scaling_b200.core.runner import LaunchConfig
+    from scaling_b200.transformer.train import main
+
+    lc = LaunchConfig(master_port=port, master_addr="127.0.0.1", world_size=world_size, global_rank=rank,
+                      local_slot=rank, payload=config)
+    metrics = main(lc, return_metrics=True)
+    return [{k: v for k, v in m.items() if k in ("training/loss", "evaluation/loss")} for m in metrics] if metrics else None
+
+
+def test_evaluation_between_training_steps_agrees_across_layouts(tmp_path: Path):
+    """Evaluation every second step on held-out data: the training and evaluation losses of a sequence-parallel and
+    of a two-stage pipeline run equal those of one process."""
+    init = str(tmp_path / "init")
+    dist_launcher(run_training, 1, config=tiny_config(1, iters=1), save_initial=init)
+
+    def config(ws, **kw):
+        cfg = tiny_config(ws, iters=4, load_dir=init, **kw)
+        cfg["trainer"].update(eval_interval=2, eval_iterations=2, load_optimizer_states=False, load_context=False)
+        return cfg
+
+    base = dist_launcher(_losses_with_evaluation, 1, config=config(1))[0]
+    assert [sorted(m) for m in base] == [["training/loss"], ["evaluation/loss", "training/loss"]] * 2
+    for kw in (dict(mp=2, sp=True), dict(pp=2, ga=2, micro=2)):
+        got = dist_launcher(_losses_with_evaluation, 2, config=config(2, **kw))[0]
+        for a, b in zip(got, base):
+            assert a.keys() == b.keys()
+            assert all(abs(a[k] - b[k]) < 2e-5 * max(1.0, abs(b[k])) for k in a), (kw, got, base)
