@@ -393,7 +393,14 @@ class Optimizer(BaseOptimizer):
                     data = layer_file(li)
                     if data is None:
                         continue
-                    for key in meta.possible_keys():
+                    keys = [k for k in meta.possible_keys() if k in data["parameters"]]
+                    if not keys:
+                        # The same weight can be sharded in one layout and replicated in another (KV projections of
+                        # multi-query attention are replicated once the group outgrows the KV heads): its key then
+                        # differs in the parallel flags only.  The stored tensors are always the complete weight.
+                        stem = f"layer_index_{li}_parameter_name_{meta.parameter_name}_is_model_parallel_"
+                        keys = [k for k in data["parameters"] if k.startswith(stem)]
+                    for key in keys[:1]:
                         if key in data["parameters"]:
                             entry = data["parameters"][key]
                             self.step_index = data["step_index"]

@@ -190,3 +190,10 @@ def test_multi_query_attention_with_fewer_kv_heads_than_tensor_parallel_ranks(tm
         got = losses(2, load_dir=init, arch=arch, **kw)
         for a, b in zip(got, base):
             assert abs(a - b) < 2e-5 * max(1.0, abs(b)), (kw, got, base)
+    # the KV projections are replicated with two ranks and ordinary column-parallel weights with one: a checkpoint of
+    # the former resumes into the latter with its optimizer states (the keys differ in the parallel flags only)
+    ckpt = str(tmp_path / "tp")
+    head = losses(2, mp=2, load_dir=init, arch=arch, iters=3, save_dir=ckpt, save_interval=3)
+    tail = losses(1, load_dir=ckpt, arch=arch)
+    for a, b in zip(head + tail, base):
+        assert abs(a - b) < 2e-5 * max(1.0, abs(b)), (head, tail, base)
