@@ -143,7 +143,21 @@ class ParallelModule(PipePartitionedModule, Generic[BaseLossInputGeneric, BaseDa
             "RecvActivation": self._do_recv_activation, "SendGrad": self._do_send_grad,
             "RecvGrad": self._do_recv_grad, "ReduceTiedGrads": self._do_reduce_tied, "StoreMicroBatch": self._do_store,
         }
+        self._mark_tied_copies()
         self.broadcast_model()
+
+    def _mark_tied_copies(self) -> None:
+        """A tied weight held by this stage whose first owner lives on an earlier stage is a copy: the optimizer
+        keeps it in step with the owner (summed gradients, identical update) but counts it once in the gradient norm."""
+        tli = self.tied_layer_index
+        for local_index, layer in enumerate(self._layers):
+            index = self.first_layer_index + local_index
+            if tli.layer_index_is_tied_global_duplicate(index) and not tli.layer_index_is_tied_local_duplicate(index):  # type: ignore[union-attr]
+                for attr in tli.get_tied_weight_attributes_by_layer_index(index):  # type: ignore[union-attr]
+                    target: Any = layer
+                    for part in attr.split("."):
+                        target = getattr(target, part)
+                    target.tied_copy_of_earlier_stage = True
 
     # ------------------------------------------------------------------ parameters
     def named_parameters_with_meta(self) -> list[tuple[str, torch.Tensor, CoreParameterMeta]]:

@@ -158,7 +158,25 @@ class OptimizerParamGroup:
         lo, hi = self.owned_range
         end = self.padded_numel if topology.model_parallel_rank == 0 else self.segment_ends[0]
         a, b = max(lo, 0), min(hi, end)
-        return [(a - lo, b - lo)] if b > a else []
+        if b <= a:
+            return []
+        # copies of a weight tied to an earlier pipeline stage are not counted again (the reference counts every
+        # copy, which makes gradient clipping depend on the layout)
+        ranges = [(a, b)]
+        for p, (s0, s1) in zip(self.parameters_original, self.param_slices()):
+            if not getattr(p, "tied_copy_of_earlier_stage", False):
+                continue
+            cut: list[tuple[int, int]] = []
+            for r0, r1 in ranges:
+                if s1 <= r0 or s0 >= r1:
+                    cut.append((r0, r1))
+                    continue
+                if r0 < s0:
+                    cut.append((r0, s0))
+                if s1 < r1:
+                    cut.append((s1, r1))
+            ranges = cut
+        return [(r0 - lo, r1 - lo) for r0, r1 in ranges if r1 > r0]
 
     # ------------------------------------------------------------------ step helpers
     def set_learning_rate(self, step_index: int) -> float:

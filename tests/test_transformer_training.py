@@ -157,7 +157,8 @@ def test_tied_embedding_and_head_across_pipeline_stages(tmp_path: Path):
         ws = kw.pop("world_size")
         got = losses(ws, load_dir=init, arch=arch, **kw)
         for a, b in zip(got, base):
-            assert abs(a - b) < 2e-4 * max(1.0, abs(b)), (kw, got, base)
+            # the shared weight counts once in the gradient norm, whichever stages hold copies of it
+            assert abs(a - b) < 2e-5 * max(1.0, abs(b)), (kw, got, base)
     untied = losses(1, arch={"weight_tying": False})
     assert untied != base
 
