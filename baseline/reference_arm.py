@@ -22,7 +22,21 @@ def _unavailable(reason: str) -> None:
         print(json.dumps({"impl": "reference", "unavailable": reason.replace("\n", " ")[:300]}), flush=True)
 
 
-def run_reference(args, MODEL, MICRO_BATCH, ClockSampler, dist_env, result_line) -> None:
+def reference_architecture(lay: dict) -> tuple[dict, str | None]:
+    """Architecture dict for the reference and, where the reference cannot run the named one, a note on what was
+    changed.  The reference divides the KV heads by the tensor-parallel size with integer division and then
+    divides by the result (scaling/core/nn/attention/attention.py), so fewer KV heads than tensor-parallel ranks
+    raise ZeroDivisionError: in that case its arm runs with as many KV heads as tensor-parallel ranks."""
+    arch = dict(lay["arch"])
+    note = None
+    kv = arch.get("attention_num_kv_heads")
+    if kv is not None and kv < lay["mp"]:
+        arch["attention_num_kv_heads"] = lay["mp"]
+        note = f"reference run with attention_num_kv_heads={lay['mp']} (it cannot run {kv} KV heads on TP={lay['mp']})"
+    return arch, note
+
+
+def run_reference(args, lay, ClockSampler, dist_env, result_line) -> None:
     if not (REF / "scaling").is_dir():
         _unavailable("baseline/_ref is missing (pip install --target baseline/_ref of the reference was not run)")
         return
@@ -30,6 +44,7 @@ def run_reference(args, MODEL, MICRO_BATCH, ClockSampler, dist_env, result_line)
     try:
         import torch
         import torch.distributed as dist
+        import scaling
         from scaling.core import DataLoader, Topology
         from scaling.core.data import BaseDataset
         from scaling.transformer import TransformerConfig, TransformerContext, init_model, init_optimizer
@@ -41,17 +56,22 @@ def run_reference(args, MODEL, MICRO_BATCH, ClockSampler, dist_env, result_line)
     except Exception as e:  # noqa: BLE001
         _unavailable(f"import of the reference failed: {type(e).__name__}: {e}")
         return
+    if REF.resolve() not in Path(scaling.__file__).resolve().parents:
+        _unavailable(f"`scaling` resolved to {scaling.__file__}, not to the installed reference")
+        return
     if not torch.cuda.is_available():
         _unavailable("the reference hard-codes CUDA/NCCL and no GPU is visible")
         return
 
     rank, world, local = dist_env(args)
-    seq = MODEL["sequence_length"]
+    arch, note = reference_architecture(lay)
+    seq, vocab = arch["sequence_length"], arch["vocab_size"]
+    micro, ga, dp = lay["micro"], lay["ga"], lay["dp"]
 
     class SyntheticDataset(BaseDataset):
         def __init__(self, n, seed):
             g = torch.Generator().manual_seed(1234)
-            self.table = torch.randint(1, MODEL["vocab_size"], (n, seq + 1), generator=g, dtype=torch.int64)
+            self.table = torch.randint(1, vocab, (n, seq + 1), generator=g, dtype=torch.int64)
             super().__init__(seed=seed, shuffle=True)
 
         def ident(self):
@@ -74,16 +94,20 @@ def run_reference(args, MODEL, MICRO_BATCH, ClockSampler, dist_env, result_line)
             return TextDataset.sync_batch_to_model_parallel(topology, batch)
 
     try:
+        group = {"group_name": "all", "weight_decay": 0.1,
+                 "learning_rate_scheduler": {"learning_rate": 3e-4, "learning_rate_decay_style": "constant"}}
+        if lay["lora"]:
+            group = dict(group, group_name="lora", parameters_include=["lora"], weight_decay=0.0)
         cfg = TransformerConfig.from_dict({
-            "topology": {"world_size": world, "global_rank": rank, "local_slot": local, "model_parallel_size": 1,
-                         "pipe_parallel_size": 1, "data_parallel_size": world, "micro_batch_size": MICRO_BATCH,
-                         "gradient_accumulation_steps": 1},
+            "topology": {"world_size": world, "global_rank": rank, "local_slot": local,
+                         "model_parallel_size": lay["mp"], "pipe_parallel_size": lay["pp"],
+                         "data_parallel_size": dp, "micro_batch_size": micro, "gradient_accumulation_steps": ga,
+                         "activation_checkpointing_type": lay["ckpt"],
+                         "sequence_parallel": bool(getattr(args, "sequence_parallel", False) and lay["mp"] > 1)},
             "optimizer": {"zero": True, "gradient_clipping": 1.0, "beta1": 0.9, "beta2": 0.95},
-            "training_groups": [{"group_name": "all", "weight_decay": 0.1,
-                                 "learning_rate_scheduler": {"learning_rate": 3e-4,
-                                                             "learning_rate_decay_style": "constant"}}],
-            "transformer_architecture": dict(MODEL, precision="bfloat16", norm_type="layernorm", mlp_type="default",
-                                             relative_position_embedding_type="rotary", weight_tying=False,
+            "training_groups": [group],
+            "training": {"allow_missing_params_in_optimizer": True} if lay["lora"] else {},
+            "transformer_architecture": dict(arch, precision="bfloat16", weight_tying=False,
                                              masked_softmax={"kernel": "flash_attention"}, causal=True),
             "trainer": {"seed": 42},
         })
@@ -94,8 +118,9 @@ def run_reference(args, MODEL, MICRO_BATCH, ClockSampler, dist_env, result_line)
         optimizer = init_optimizer(context, model)
         loss_fn = create_loss_function(context, cfg.training.loss_function_config)
         total = 2 * (args.steps + args.warmup) + 2
-        dataset = SyntheticDataset(MICRO_BATCH * world * total, 42)
-        loader = DataLoader(seed=42, consumed_samples=0, dataset=dataset, topology=topology, pin_memory=True)
+        dataset = SyntheticDataset(micro * dp * ga * total, 42)
+        loader = DataLoader(seed=42, consumed_samples=0, dataset=dataset, topology=topology, pin_memory=True) \
+            if topology.is_io_rank else None
         sync = SyntheticDataset.sync_batch_to_model_parallel
         dev = topology.device
 
@@ -135,9 +160,12 @@ def run_reference(args, MODEL, MICRO_BATCH, ClockSampler, dist_env, result_line)
         _unavailable(f"the reference failed to run: {type(e).__name__}: {e}")
         return
     if rank == 0:
-        tokens = MICRO_BATCH * seq * world
-        line = result_line(args, world, tokens, dev_ms, e2e_ms, clocks, 0, MICRO_BATCH * (seq + 1) * 8, 4, "reference")
+        tokens = micro * seq * dp * ga
+        line = result_line(args, world, tokens, dev_ms, e2e_ms, clocks, 0, micro * ga * (seq + 1) * 8, 4 * ga,
+                           "reference", lay)
         line["gpu_launches"] = None
+        if note:
+            line["details"] = {"reference_deviation": note}
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()

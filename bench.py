@@ -103,6 +103,16 @@ def model_flops_per_token(arch: dict, trains_base: bool) -> float:
     return (6.0 if trains_base else 4.0) * weights + 6.0 * L * s * h
 
 
+def measured_peak_tflops() -> tuple[float, str]:
+    """Denominator of the reported MFU: the sustained bf16 matmul throughput measured on this pool's GPUs (the
+    file the benchmark driver writes next to this script), else the sustained figure of an earlier measurement."""
+    try:
+        peaks = json.loads((ROOT / "MEASURED_PEAKS.json").read_text())
+        return float(peaks["bf16_tflops_sustained"]), "bf16_tflops_sustained of measured"
+    except Exception:
+        return 1400.0, "1400 TFLOP/s sustained of fallback"
+
+
 # ---------------------------------------------------------------------------------------------- clocks
 class ClockSampler:
     QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
@@ -288,11 +298,12 @@ def run_ours(args: argparse.Namespace) -> None:
         tokens = micro * seq * dp * ga
         h2d = micro * ga * (seq + 1) * 8
         line = result_line(args, world, tokens, dev_ms, e2e_ms, clocks, launches, h2d, 4 * ga, "ours", lay)
-        line["config"]["data_parallel_exchange"] = optimizer.data_parallel_exchange
-        line["config"]["cuda_graph"] = bool(getattr(model, "_graph", None) is not None)
         tflops = model_flops_per_token(arch, not lay["lora"]) * line["value"] / world / 1e12
-        line["config"]["model_tflops_per_gpu"] = round(tflops, 1)
-        line["config"]["mfu_of_nominal_2250"] = round(tflops / 2250.0, 4)
+        peak, peak_name = measured_peak_tflops()
+        line["details"] = {"data_parallel_exchange": optimizer.data_parallel_exchange,
+                           "cuda_graph": model.cuda_graph_state(),
+                           "model_tflops_per_gpu": round(tflops, 1),
+                           "mfu": round(tflops / peak, 4), "mfu_denominator": peak_name}
         print(json.dumps(line), flush=True)
     shutdown(model, world)
 
@@ -331,14 +342,12 @@ def main() -> None:
         import faulthandler
 
         faulthandler.dump_traceback_later(watchdog, exit=True)
-    if args.impl == "reference" and args.config != "125m":
-        print(json.dumps({"impl": "reference", "unavailable": "the reference arm runs the 125M headline config only"}))
-        return
     if args.impl == "reference":
         sys.path.insert(0, str(ROOT))
         from baseline.reference_arm import run_reference
 
-        run_reference(args, MODEL, MICRO_BATCH, ClockSampler, dist_env, result_line)
+        world = int(os.environ.get("WORLD_SIZE", str(args.gpus)))
+        run_reference(args, layout(args, world), ClockSampler, dist_env, result_line)
         return
     run_ours(args)
 

@@ -9,8 +9,17 @@ tree* (shape, dtype, requires_grad per leaf); afterwards the meta is assumed unc
 every exchange.  Gradients travel back for exactly the leaves that require grad, in leaf order.
 
 All leaves of one exchange are posted as a single ``batch_isend_irecv`` group (one NCCL group launch
-instead of one blocking send per leaf), and receives can be posted ahead of time with
-``post_recv`` so that the transfer overlaps the compute of the previous instruction.
+instead of one blocking send per leaf).  Transfers overlap compute in both directions:
+
+* sends are not waited for where they are issued: the handles (and the tensors they read) are kept until
+  the next send on the same link or ``drain()``, so the compute stream never stalls behind an outgoing copy;
+* receives can be posted ahead of time (``post_recv`` for activations, ``post_recv_grad`` for gradients), which
+  the schedule loop does as soon as the previous compute instruction has been enqueued; ``recv_data`` /
+  ``recv_grad`` then only wait for them.
+
+Activations and gradients of one link travel over different process groups (``group`` / ``grad_group``): each has
+its own communicator and stream, so a receive that was posted early and is still waiting for its sender cannot
+hold up a send in the other direction between the same two ranks.
 """
 
 from __future__ import annotations
@@ -59,19 +68,25 @@ def _run(ops: list) -> None:
         work.wait()
 
 
+def _start(ops: list) -> list:
+    return dist.batch_isend_irecv(ops) if ops else []
+
+
 class PipeCommunicator:
     def __init__(self, local_device: torch.device, recv_grads: bool, recv_data: bool,
                  use_continuous_recommunication: bool, group: Any = None, peer_send: Optional[int] = None,
-                 peer_recv: Optional[int] = None):
+                 peer_recv: Optional[int] = None, grad_group: Any = None):
         """
         ``peer_send``: global rank data is sent to (and gradients are received from);
-        ``peer_recv``: global rank data is received from (and gradients are sent to).
+        ``peer_recv``: global rank data is received from (and gradients are sent to);
+        ``group`` / ``grad_group``: process groups that carry the data and the gradients (default: the world group).
         """
         self.local_device = local_device
         self.can_recv_grads = recv_grads
         self.can_recv_data = recv_data
         self.use_continuous_recommunication = use_continuous_recommunication
         self.group = group
+        self.grad_group = grad_group if grad_group is not None else group
         self.peer_send = peer_send
         self.peer_recv = peer_recv
         # Negotiated structure per channel: a training step and an evaluation step send differently flagged trees
@@ -79,10 +94,30 @@ class PipeCommunicator:
         self.channel = "train"
         self._state: dict[str, dict[str, Any]] = {}
         self._posted: Optional[tuple[list[torch.Tensor], list]] = None
+        self._posted_grad: Optional[tuple[list[torch.Tensor], list[torch.Tensor], list]] = None
+        self._sends_in_flight: list[tuple[list, list[torch.Tensor]]] = []
 
     def reset_communication_meta(self) -> None:
+        self.drain()
         self._state = {}
         self._posted = None
+        self._posted_grad = None
+
+    # ------------------------------------------------------------------ sends in flight
+    def _send_async(self, tensors: list[torch.Tensor], peer: int, group: Any) -> None:
+        """Issue the sends and return at once.  The previous batch on this link is retired first (it has long
+        finished; on a GPU this only orders the stream after it), so at most one batch of handles is kept."""
+        self.drain()
+        works = _start([dist.P2POp(dist.isend, t, peer, group=group) for t in tensors])
+        if works:
+            self._sends_in_flight.append((works, tensors))
+
+    def drain(self) -> None:
+        """Wait for outgoing transfers that were issued without waiting (end of a step, before shapes change)."""
+        for works, _tensors in self._sends_in_flight:
+            for w in works:
+                w.wait()
+        self._sends_in_flight = []
 
     def _channel_state(self) -> dict[str, Any]:
         st = self._state.get(self.channel)
@@ -140,7 +175,7 @@ class PipeCommunicator:
                 "use_continuous_recommunication to renegotiate shapes on every exchange"
             )
         self._sent_meta, self._sent_spec = meta, spec
-        _run([dist.P2POp(dist.isend, t, self.peer_send, group=self.group) for t in tensors])
+        self._send_async(tensors, self.peer_send, self.group)
 
     # ------------------------------------------------------------------ data: receiver side
     def _recv_meta_blob(self) -> None:
@@ -160,14 +195,16 @@ class PipeCommunicator:
             if int(flag.item()) == 1:
                 self._recv_meta_blob()
 
-    def post_recv(self) -> None:
-        """Post the receives of the next exchange now; ``recv_data`` later only waits for them."""
+    def post_recv(self) -> bool:
+        """Post the receives of the next exchange now; ``recv_data`` later only waits for them.  Possible once the
+        structure of the data is known (after the first exchange) and fixed (no per-exchange renegotiation)."""
         assert self.peer_recv is not None
         if self._posted is not None or self._recv_meta is None or self.use_continuous_recommunication:
-            return
+            return False
         bufs = [torch.empty(m.shape, dtype=m.dtype, device=self.local_device) for m in self._recv_meta]
-        works = dist.batch_isend_irecv([dist.P2POp(dist.irecv, b, self.peer_recv, group=self.group) for b in bufs])
+        works = _start([dist.P2POp(dist.irecv, b, self.peer_recv, group=self.group) for b in bufs])
         self._posted = (bufs, works)
+        return True
 
     def recv_data(self) -> Any:
         assert self.can_recv_data and self.peer_recv is not None
@@ -200,17 +237,42 @@ class PipeCommunicator:
         for leaf in leaves:
             if isinstance(leaf, torch.Tensor) and leaf.requires_grad:
                 g = leaf.grad if leaf.grad is not None else torch.zeros_like(leaf)
-                ops.append(dist.P2POp(dist.isend, g.contiguous(), self.peer_recv, group=self.group))
-        _run(ops)
+                ops.append(g.contiguous())
+        self._send_async(ops, self.peer_recv, self.grad_group)
 
     def recv_grad(self, data: Any) -> tuple[list[torch.Tensor], list[torch.Tensor]]:
         """For the output tree that was sent, receive gradients; returns (tensors, grads) for autograd."""
         assert self.can_recv_grads and self.peer_send is not None
-        leaves, _ = pytree.tree_flatten(data)
-        tensors = [leaf for leaf in leaves if isinstance(leaf, torch.Tensor) and leaf.requires_grad]
+        tensors = self._grad_leaves(data)
+        if self._posted_grad is not None:
+            posted_for, grads, works = self._posted_grad
+            self._posted_grad = None
+            assert len(posted_for) == len(tensors) and all(a is b for a, b in zip(posted_for, tensors)), (
+                "gradient receives were posted for another micro batch than the one now asked for"
+            )
+            for w in works:
+                w.wait()
+            return tensors, grads
         grads = [torch.empty_like(t, memory_format=torch.contiguous_format) for t in tensors]
-        _run([dist.P2POp(dist.irecv, g, self.peer_send, group=self.group) for g in grads])
+        _run([dist.P2POp(dist.irecv, g, self.peer_send, group=self.grad_group) for g in grads])
         return tensors, grads
+
+    @staticmethod
+    def _grad_leaves(data: Any) -> list[torch.Tensor]:
+        leaves, _ = pytree.tree_flatten(data)
+        return [leaf for leaf in leaves if isinstance(leaf, torch.Tensor) and leaf.requires_grad]
+
+    def post_recv_grad(self, data: Any) -> bool:
+        """Post the receives for the gradients of the output tree ``data`` now; the matching ``recv_grad(data)`` only
+        waits.  Returns False (nothing posted) while an earlier posting is still outstanding."""
+        assert self.can_recv_grads and self.peer_send is not None
+        if self._posted_grad is not None:
+            return False
+        tensors = self._grad_leaves(data)
+        grads = [torch.empty_like(t, memory_format=torch.contiguous_format) for t in tensors]
+        works = _start([dist.P2POp(dist.irecv, g, self.peer_send, group=self.grad_group) for g in grads])
+        self._posted_grad = (tensors, grads, works)
+        return True
 
 
 class ModelParallelCommunicator:

@@ -99,15 +99,16 @@ class ParallelModule(PipePartitionedModule, Generic[BaseLossInputGeneric, BaseDa
         pp = t.config.pipe_parallel_size
         nxt = (t.pipe_parallel_rank + 1) % pp   # wraps around for inference, where the last stage
         prv = (t.pipe_parallel_rank - 1) % pp   # hands its output back to the first
+        down, up = t.pipe_down_group, t.pipe_up_group  # activations / gradients travel on separate groups
         self.communicator_in = PipeCommunicator(
             local_device=t.device, recv_grads=False, recv_data=True,
             use_continuous_recommunication=use_continuous_recommunication,
-            peer_recv=t.get_global_rank(pipe_parallel_rank=prv) if pp > 1 else None,
+            peer_recv=t.get_global_rank(pipe_parallel_rank=prv) if pp > 1 else None, group=down, grad_group=up,
         )
         self.communicator_out = PipeCommunicator(
             local_device=t.device, recv_grads=True, recv_data=False,
             use_continuous_recommunication=use_continuous_recommunication,
-            peer_send=t.get_global_rank(pipe_parallel_rank=nxt) if pp > 1 else None,
+            peer_send=t.get_global_rank(pipe_parallel_rank=nxt) if pp > 1 else None, group=down, grad_group=up,
         )
         self.communicator_loss_in: Optional[PipeCommunicator] = None
         self.communicator_loss_out: Optional[PipeCommunicator] = None
@@ -115,15 +116,19 @@ class ParallelModule(PipePartitionedModule, Generic[BaseLossInputGeneric, BaseDa
             if t.is_first_pipe_parallel_rank:
                 self.communicator_loss_in = PipeCommunicator(
                     local_device=t.device, recv_grads=False, recv_data=True, use_continuous_recommunication=True,
-                    peer_recv=t.get_global_rank(pipe_parallel_rank=pp - 1),
+                    peer_recv=t.get_global_rank(pipe_parallel_rank=pp - 1), group=up,
                 )
             if t.is_last_pipe_parallel_rank:
                 self.communicator_loss_out = PipeCommunicator(
                     local_device=t.device, recv_grads=False, recv_data=False, use_continuous_recommunication=True,
-                    peer_send=t.get_global_rank(pipe_parallel_rank=0),
+                    peer_send=t.get_global_rank(pipe_parallel_rank=0), group=up,
                 )
         self.profiler = Profiler(config=profiler_config, topology=t)
         self.step_timer = CudaEventTimer()
+        # receives between pipeline stages are posted ahead of the compute that precedes them (SB200_PIPE_OVERLAP=0:
+        # every receive is posted where the schedule names it); a list here records instructions and postings
+        self.overlap_pipe_communication = os.environ.get("SB200_PIPE_OVERLAP", "1") != "0"
+        self.instruction_trace: Optional[list[str]] = None
         # whole-step CUDA graph (see _graph_eligible); SB200_CUDA_GRAPH=0 disables it
         self.enable_cuda_graph = os.environ.get("SB200_CUDA_GRAPH", "1") != "0"
         self._nvtx = os.environ.get("SB200_NVTX", "0") == "1" and self.topology.device.type == "cuda"
@@ -267,11 +272,14 @@ class ParallelModule(PipePartitionedModule, Generic[BaseLossInputGeneric, BaseDa
         optimizer_out = None
         # SB200_NVTX=1: one NVTX range per schedule instruction, for timelines of external profilers
         nvtx = self._nvtx
-        for ins in instructions:
+        post_ahead = self.topology.config.pipe_parallel_size > 1 and self.overlap_pipe_communication
+        for position, ins in enumerate(instructions):
             name = ins.name
             if nvtx:
                 torch.cuda.nvtx.range_push(f"{name}[mb={ins.micro_batch_id},buf={ins.buffer_id}]")
             try:
+                if self.instruction_trace is not None:
+                    self.instruction_trace.append(f"{name} mb={ins.micro_batch_id}")
                 with self.profiler.time(name, ins.micro_batch_id, ins.buffer_id):
                     if name == "OptimizerStep":
                         optimizer_out = ctx["optimizer"].step()
@@ -280,7 +288,34 @@ class ParallelModule(PipePartitionedModule, Generic[BaseLossInputGeneric, BaseDa
             finally:
                 if nvtx:
                     torch.cuda.nvtx.range_pop()
+            if post_ahead:
+                self._post_receives_ahead(instructions, position)
+        if post_ahead:
+            self.communicator_in.drain()
+            self.communicator_out.drain()
         return optimizer_out
+
+    def _post_receives_ahead(self, instructions: list[InstructionBase], position: int) -> None:
+        """Post the receives of the next RecvActivation and the next RecvGrad of this step now, so that the
+        transfers run while the instructions in between compute (the reference blocks in every receive:
+        src/scaling/core/nn/parallel_module/communicator.py:388-482).  Only the first receive of each kind that is
+        still ahead is posted, in schedule order, which keeps every link's receives in the order of its sends; a
+        gradient receive needs the output it belongs to, so it is posted once that forward pass has run."""
+        seen_act = seen_grad = False
+        for ins in instructions[position + 1:]:
+            if ins.name == "RecvActivation" and not seen_act:
+                seen_act = True
+                if self.communicator_in.post_recv() and self.instruction_trace is not None:
+                    self.instruction_trace.append(f"post RecvActivation mb={ins.micro_batch_id}")
+            elif ins.name == "RecvGrad" and not seen_grad:
+                seen_grad = True
+                if self.pipe_buffer.has(BufferType.PIPELINE_STAGE_OUTPUT, ins.buffer_id):
+                    out = self.pipe_buffer.get(BufferType.PIPELINE_STAGE_OUTPUT, ins.buffer_id)
+                    tup = self._prepare_for_send(self._layers[-1].output_to_tuple(out))
+                    if self.communicator_out.post_recv_grad(tup) and self.instruction_trace is not None:
+                        self.instruction_trace.append(f"post RecvGrad mb={ins.micro_batch_id}")
+            if seen_act and seen_grad:
+                break
 
     # ------------------------------------------------------------------ CUDA-graph training step
     def _graph_eligible(self, optimizer: Any) -> bool:
@@ -505,6 +540,7 @@ class ParallelModule(PipePartitionedModule, Generic[BaseLossInputGeneric, BaseDa
             if t.is_last_pipe_parallel_rank:
                 assert self.communicator_loss_out is not None
                 self.communicator_loss_out.send_data(data)
+                self.communicator_loss_out.drain()
                 return None, None
             if t.is_first_pipe_parallel_rank:
                 assert self.communicator_loss_in is not None

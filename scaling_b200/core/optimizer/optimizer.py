@@ -32,6 +32,7 @@ import torch
 import torch.distributed as dist
 
 from ...ops import functional as K
+from ...ops._lib import CommTimeout
 from ...parallel.topology import Topology
 from ..logging import logger
 from ..nn.parameter_meta import CoreParameterMeta
@@ -98,10 +99,11 @@ class Optimizer(BaseOptimizer):
         self.loss_scaler = LossScaler(config=config.loss_scaler)
         self.scale_backward_by_grad_acc = scale_backward_by_grad_acc
         dev = topology.device
-        self._stats = torch.zeros(2, dtype=torch.float32, device=dev)     # [sum of squares, overflow count]
+        self._stats = torch.zeros(3, dtype=torch.float32, device=dev)     # [sum of squares, overflows, waits given up]
         self._flag = torch.zeros(1, dtype=torch.int32, device=dev)
         self._control = torch.zeros(2, dtype=torch.float32, device=dev)   # [gradient multiplier, skip]
-        self._result = torch.zeros(2, dtype=torch.float32, device=dev)    # [global norm, overflow] read by the host
+        # read by the host once per step: [global norm, skip, a device-side wait gave up, norm after clipping]
+        self._result = torch.zeros(4, dtype=torch.float32, device=dev)
         self._hyper_host: Optional[torch.Tensor] = None                    # [lr, 1-b1^t, 1-b2^t] per group (pinned)
         self._hyper: Optional[torch.Tensor] = None
         self._learning_rates: dict[str, float] = {}
@@ -207,21 +209,18 @@ class Optimizer(BaseOptimizer):
         for g, r in zip(self.parameter_groups, reduced):
             for a, b in g.norm_ranges(t):
                 K.sumsq_(r[a:b], self._stats[0:1], self._flag, 1.0, True)
-        self._stats[1] = self._flag[0].to(torch.float32)
+        # The overflow flag and the status word of the kernels with bounded waits (peer barriers, fused tensor-parallel
+        # GEMMs) travel with the sum of squares: one all-reduce makes every rank agree on norm, overflow and on
+        # whether some rank's wait gave up, in which case all of them skip the update.
+        K.step_control(0, self._stats, self._flag, self._control, self._result)
+        replicas = 1.0
         if t.is_distributed_initialized and t.world_size > 1:
             dist.all_reduce(self._stats)
             if not cfg.zero and dp > 1:
-                self._stats[0] /= dp  # replicas hold identical gradients: count them once
-        inv = 1.0 / (dp * self.loss_scaler.current_scale)
-        norm = torch.sqrt(self._stats[0]) * inv
-        bad = (self._stats[1] > 0) | ~torch.isfinite(norm)
-        coef = torch.ones_like(norm)
-        if cfg.gradient_clipping > 0.0:
-            coef = torch.where(norm >= cfg.gradient_clipping, cfg.gradient_clipping / norm, coef)
-        self._control[0] = torch.where(bad, torch.zeros_like(coef), coef * inv)
-        self._control[1] = bad.to(torch.float32)
-        self._result[0] = norm
-        self._result[1] = bad.to(torch.float32)
+                replicas = float(dp)  # replicas hold identical gradients: count them once
+        K.step_control(1, self._stats, self._flag, self._control, self._result,
+                       inv=1.0 / (dp * self.loss_scaler.current_scale), clip=float(cfg.gradient_clipping),
+                       replicas=replicas)
         for i, (g, r) in enumerate(zip(self.parameter_groups, reduced)):
             lo, hi = g.owned_range
             p_lp = None if g.dtype == torch.float32 else g.flat_param[lo:hi]
@@ -241,10 +240,22 @@ class Optimizer(BaseOptimizer):
                 else:
                     dist.all_gather_into_tensor(g.flat_param, g.flat_param[lo:hi], group=grp)
         self.zero_grad()
+        if self._result.is_cuda:  # a wait of the parameter exchange that gave up after the statistics were taken
+            K.step_control(2, self._stats, self._flag, self._control, self._result)
 
     def finish_step(self) -> OptimizerStepOutput:
         cfg = self.config
-        norm_host, bad_host = self._result.tolist()  # the only device -> host transfer of the step
+        # the only device -> host transfer of the step
+        norm_host, bad_host, timed_out, clipped_host = self._result.tolist()
+        if timed_out:
+            # Some rank's kernel stopped waiting for a peer (SB200_P2P_TIMEOUT_S): its result is incomplete.  Every
+            # rank skipped the update (the flag was summed over the ranks before AdamW ran) unless the wait that gave
+            # up was the parameter exchange after it; either way the replicas can no longer be trusted to agree.
+            K.status_word().zero_()
+            raise CommTimeout(
+                f"optimizer step {self.step_index}: a device-side wait on a peer gave up (a rank arrived more than "
+                "SB200_P2P_TIMEOUT_S late or has left); the step was skipped - resume from the last checkpoint"
+            )
         overflow = bool(bad_host)
         scaler_out = self.loss_scaler.step(overflow)
         if overflow:
@@ -258,7 +269,7 @@ class Optimizer(BaseOptimizer):
                                        scaler_out.current_loss_scale, None)
         self.adam_steps += 1
         return OptimizerStepOutput(
-            global_grad_norm=norm_host, global_grad_norm_clipped=None, learning_rates=dict(self._learning_rates),
+            global_grad_norm=norm_host, global_grad_norm_clipped=clipped_host, learning_rates=dict(self._learning_rates),
             overflow=scaler_out.overflow, no_overflow_steps=scaler_out.no_overflow_steps,
             current_loss_scale=scaler_out.current_loss_scale, debug_dict=self._debug,
         )
@@ -428,15 +439,29 @@ class Optimizer(BaseOptimizer):
 
 
 def _try_fused_zero(optimizer: "Optimizer") -> Any:
-    """The in-kernel NVLink path of the ZeRO step, if symmetric memory is available for the group."""
+    """The in-kernel NVLink path of the ZeRO step, if symmetric memory is available for the group.
+
+    The decision is taken by the data-parallel group as a whole: a rank on which the set-up failed must not fall
+    back to library collectives while its peers wait at flag barriers, so the ranks exchange a success flag and
+    use the peer-memory kernels only if every one of them has them."""
+    t = optimizer.topology
+    fused = None
+    error = ""
     try:
         from ...parallel.fused_zero import FusedZero
 
         fused = FusedZero.create(optimizer)
-        if fused is not None:
-            logger.info("ZeRO data-parallel exchange: peer-memory kernels over NVLink "
-                        f"(multicast stores: {'yes' if fused.use_multicast else 'no'})")
-        return fused
     except Exception as e:  # pragma: no cover - depends on the machine
-        logger.warning(f"fused NVLink ZeRO path unavailable ({type(e).__name__}: {e}); using NCCL collectives")
-        return None
+        error = f"{type(e).__name__}: {e}"
+    ok = torch.tensor([1.0 if fused is not None else 0.0], device=t.device)
+    if t.is_distributed_initialized:
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=t.data_parallel_group)
+    if ok.item() < 1.0:
+        if fused is not None:
+            logger.warning("fused NVLink ZeRO path available here but not on every data-parallel rank; using NCCL")
+        elif error:
+            logger.warning(f"fused NVLink ZeRO path unavailable ({error}); using NCCL collectives")
+        return None  # the buffers of groups that already moved into symmetric memory stay valid as plain tensors
+    logger.info("ZeRO data-parallel exchange: peer-memory kernels over NVLink "
+                f"(multicast stores: {'yes' if fused.use_multicast else 'no'})")
+    return fused

@@ -1089,7 +1089,8 @@ SB_API int sb200_gemm_tp(const void* A, const void* B, void* C, void* C_pre, con
   const int tiles_per_rank = (m_tiles / W) * n_tiles;
   p.ar.unit_shift = mode == AR_REDUCE_SCATTER ? ((rank + 1) % W) * tiles_per_rank
                   : mode == AR_ALLGATHER ? rank * tiles_per_rank : 0;
-  if (timeout_seconds <= 0.0 || timeout_seconds > 60.0) timeout_seconds = 10.0;
+  if (timeout_seconds <= 0.0) timeout_seconds = 10.0;
+  if (timeout_seconds > 60.0) timeout_seconds = 60.0;  // longest wait a kernel may spin
   p.ar.timeout_ns = (unsigned long long)(timeout_seconds * 1e9);
   CUtensorMap tmA, tmB, tmC, tmP;
   int rc;

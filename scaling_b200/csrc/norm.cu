@@ -584,6 +584,12 @@ SB_API int sb200_norm_bwd_noalloc(const void* dy, const void* x, const void* w, 
                                   cudaStream_t stream) {
   if (M <= 0 || H <= 0) return SB_OK;
   if (H > SB200_NOALLOC_MAX_H) return SB_ERR_TOO_LARGE;
+  // the kernels use 16-byte loads and stores on the rows and on the weight / gradient vectors: a misaligned pointer
+  // would be a device fault (the context is lost), so it is refused here, before anything is launched
+  if ((reinterpret_cast<uintptr_t>(dy) | reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w) |
+       reinterpret_cast<uintptr_t>(dx) | reinterpret_cast<uintptr_t>(dw) | reinterpret_cast<uintptr_t>(db)) & 15)
+    return SB_ERR_BAD_ARG;
+  if (!dy || !x || !w || !dx || !dw || !rstd || (!rms && !mean)) return SB_ERR_BAD_ARG;
   float* dw_partial = nullptr;
   float* db_partial = nullptr;
   int rc = noalloc_workspace(&dw_partial, &db_partial);

@@ -115,6 +115,33 @@ __global__ void sumsq_final_kernel(const float* __restrict__ partial, int P, flo
   if (threadIdx.x == 0) out[0] = (accumulate ? out[0] : 0.f) + s * scale;
 }
 
+// ------------------------------------------- step control (one thread each)
+// Before the all-reduce of the step statistics: stats = [sum of squares (already there), overflow flag, status word].
+__global__ void step_pack_kernel(float* __restrict__ stats, const int* __restrict__ flag,
+                                 const int* __restrict__ status) {
+  stats[1] = flag && *flag ? 1.f : 0.f;
+  stats[2] = status && *status ? 1.f : 0.f;
+}
+// After it: norm = sqrt(stats[0] / replicas) * inv; the step is skipped when any rank saw inf / nan or a device-side
+// wait that gave up; control = [gradient multiplier, skip], result = [norm, skip, wait gave up, norm after clipping].
+__global__ void step_control_kernel(const float* __restrict__ stats, float inv, float clip, float replicas,
+                                    float* __restrict__ control, float* __restrict__ result) {
+  const float norm = sqrtf(stats[0] / replicas) * inv;
+  const bool timed_out = stats[2] > 0.f;
+  const bool bad = stats[1] > 0.f || !isfinite(norm) || timed_out;
+  const float coef = (clip > 0.f && norm >= clip) ? clip / norm : 1.f;
+  control[0] = bad ? 0.f : coef * inv;
+  control[1] = bad ? 1.f : 0.f;
+  result[0] = norm;
+  result[1] = bad ? 1.f : 0.f;
+  result[2] = timed_out ? 1.f : 0.f;
+  result[3] = norm * coef;
+}
+// End of the step: a wait that gave up after the statistics were taken (parameter exchange) still reaches the host.
+__global__ void step_status_kernel(const int* __restrict__ status, float* __restrict__ result) {
+  if (status && *status) result[2] = 1.f;
+}
+
 // --------------------------------------------------------------- embedding
 // out[t, :] = W[id - vocab_start, :] when id is inside this rank's shard, else 0.
 template <typename T>
@@ -191,6 +218,19 @@ SB_API int sb200_sumsq(const void* g, long n, float* partial, float* out, int* f
   });
   SB_CHECK_LAUNCH();
   sumsq_final_kernel<<<1, 32, 0, stream>>>(partial, (int)b, out, scale, accumulate);
+  SB_CHECK_LAUNCH();
+  return SB_OK;
+}
+
+// The scalar arithmetic of an optimizer step as three one-thread kernels (see the kernels above): `which` = 0 pack
+// the overflow flag and the status word into stats before the all-reduce, 1 derive the gradient multiplier, the skip
+// flag and the values the host reads, 2 fold a late status into the result.
+SB_API int sb200_step_control(int which, float* stats, const int* flag, const int* status, float inv, float clip,
+                              float replicas, float* control, float* result, cudaStream_t stream) {
+  if (which == 0) step_pack_kernel<<<1, 1, 0, stream>>>(stats, flag, status);
+  else if (which == 1) step_control_kernel<<<1, 1, 0, stream>>>(stats, inv, clip, replicas, control, result);
+  else if (which == 2) step_status_kernel<<<1, 1, 0, stream>>>(status, result);
+  else return SB_ERR_BAD_ARG;
   SB_CHECK_LAUNCH();
   return SB_OK;
 }

@@ -128,7 +128,8 @@ SB_API int sb200_p2p_barrier(void* const* flag_ptrs, uint32_t* round_word, int r
   int rc = fill_ptrs(&f, flag_ptrs, W);
   if (rc) return rc;
   if (rank < 0 || rank >= W) return SB_ERR_BAD_ARG;
-  if (timeout_seconds <= 0.0 || timeout_seconds > 60.0) timeout_seconds = 10.0;
+  if (timeout_seconds <= 0.0) timeout_seconds = 10.0;
+  if (timeout_seconds > 60.0) timeout_seconds = 60.0;  // longest wait a kernel may spin
   p2p_barrier_kernel<<<1, 32, 0, stream>>>(f, round_word, rank, W, status,
                                            (unsigned long long)(timeout_seconds * 1e9));
   SB_CHECK_LAUNCH();

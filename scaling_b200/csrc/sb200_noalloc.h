@@ -22,13 +22,17 @@ extern "C" {
 // workspaces and the partial_rows count:
 //   dx[M, H], dw[H] (and db[H] for LayerNorm with bias) from dy[M, H], x[M, H], w[H], mean[M] (LayerNorm), rstd[M].
 //   rms != 0 selects RMSNorm; accumulate != 0 adds into dw / db; dtype is SB_DT_* of dy, x, w, dx, dw, db.
+//   dy, x, w, dx, dw and db must be 16-byte aligned (the kernels move 16 bytes per access); with a row length that
+//   is a multiple of the vector width this makes every row aligned as well.
 // Returns 0 on success, SB_ERR_TOO_LARGE (103) if H exceeds SB200_NOALLOC_MAX_H, SB_ERR_BAD_ARG (102) if H is not
-// a multiple of the 16-byte vector width, or the CUDA error code of a failed runtime call.
+// a multiple of the 16-byte vector width, a required pointer is null or one of the pointers above is not 16-byte
+// aligned (nothing is launched in these cases), or the CUDA error code of a failed runtime call.
 //
 // Contract:
 //  * The function never calls cudaMalloc, cudaFree or any other allocating routine.
 //  * The first call on each device looks up the device address of the workspace (cudaGetSymbolAddress) with that
-//    device current; make this first call before any stream capture begins on that device.
+//    device current; make this first call before any stream capture begins on that device, on any host thread (a
+//    capture in progress on another thread is disturbed by the look-up just the same).
 //  * All calls on a device share the one workspace.  Its contents after a call are unspecified; every call
 //    overwrites the rows it later reads, so nothing needs clearing in between.  Two calls whose kernels may run
 //    at the same time on one device (different streams without ordering) race on the workspace and must be

@@ -65,12 +65,29 @@ def needs_build() -> bool:
 
 
 def build(force: bool = False, verbose: bool = False) -> Path:
-    """Compile every source for sm_100a and link ``libsb200.so``.  Returns the library path."""
+    """Compile every source for sm_100a and link ``libsb200.so``.  Returns the library path.
+
+    Several ranks of one job may get here at the same time (fresh checkout, changed source): the build runs under
+    an exclusive file lock, the check is repeated once the lock is held, and objects and the library are written
+    under temporary names and moved into place, so that no process ever maps a half-written file."""
     if not force and not needs_build():
         return LIB_PATH
-    nvcc = _nvcc()
+    import fcntl
+
     BUILD_DIR.mkdir(exist_ok=True)
     LIB_DIR.mkdir(exist_ok=True)
+    with open(LIB_DIR / ".lock", "w") as lock:
+        fcntl.flock(lock, fcntl.LOCK_EX)
+        try:
+            if not force and not needs_build():  # another process built it while this one waited
+                return LIB_PATH
+            return _build_locked(force, verbose)
+        finally:
+            fcntl.flock(lock, fcntl.LOCK_UN)
+
+
+def _build_locked(force: bool, verbose: bool) -> Path:
+    nvcc = _nvcc()
     headers = sorted(CSRC.glob("*.cuh")) + sorted(CSRC.glob("*.h"))
     hdr_digest = _digest(headers)
 
@@ -80,7 +97,8 @@ def build(force: bool = False, verbose: bool = False) -> Path:
         dig = hashlib.sha256((hdr_digest + _digest([src])).encode()).hexdigest()
         if not force and obj.exists() and stamp.exists() and stamp.read_text() == dig:
             return obj
-        cmd = [nvcc, *NVCC_FLAGS, "-I", str(CSRC), "-c", str(src), "-o", str(obj)]
+        tmp = obj.with_suffix(f".{os.getpid()}.tmp.o")
+        cmd = [nvcc, *NVCC_FLAGS, "-I", str(CSRC), "-c", str(src), "-o", str(tmp)]
         if src.suffix == ".cpp":
             cmd.insert(1, "-x")
             cmd.insert(2, "cu")
@@ -92,15 +110,18 @@ def build(force: bool = False, verbose: bool = False) -> Path:
             raise RuntimeError(f"nvcc failed for {src.name}:\n{res.stdout}\n{res.stderr}")
         if verbose:
             sys.stderr.write(res.stderr)
+        os.replace(tmp, obj)
         stamp.write_text(dig)
         return obj
 
     with ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 1)) as ex:
         objs = list(ex.map(compile_one, sources()))
-    cmd = [nvcc, "-shared", "-o", str(LIB_PATH), *map(str, objs)]
+    tmp_lib = LIB_DIR / f"libsb200.{os.getpid()}.tmp.so"
+    cmd = [nvcc, "-shared", "-o", str(tmp_lib), *map(str, objs)]
     res = subprocess.run(cmd, capture_output=True, text=True)
     if res.returncode != 0:
         raise RuntimeError(f"link failed:\n{res.stdout}\n{res.stderr}")
+    os.replace(tmp_lib, LIB_PATH)  # a process that has the old file mapped keeps its inode
     deps = sources() + headers
     (LIB_DIR / "libsb200.sha256").write_text(_digest(deps))
     return LIB_PATH

@@ -75,6 +75,7 @@ _SIGS = {
     "sb200_adamw": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_long, c_float, c_float, c_float, c_float, c_float, c_float, c_float, c_void_p, c_void_p, c_int, c_int, c_void_p],
     "sb200_sumsq_max_partials": [],
     "sb200_sumsq": [c_void_p, c_long, c_void_p, c_void_p, c_void_p, c_float, c_int, c_int, c_void_p],
+    "sb200_step_control": [c_int, c_void_p, c_void_p, c_void_p, c_float, c_float, c_float, c_void_p, c_void_p, c_void_p],
     "sb200_embedding_fwd": [c_void_p, c_void_p, c_void_p, c_long, c_int, c_long, c_long, c_int, c_void_p],
     "sb200_embedding_bwd": [c_void_p, c_void_p, c_void_p, c_void_p, c_long, c_int, c_long, c_long, c_int, c_int, c_void_p],
     "sb200_p2p_max_ranks": [],

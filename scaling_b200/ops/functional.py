@@ -726,6 +726,34 @@ def sumsq_(g: torch.Tensor, out: torch.Tensor, flag: Optional[torch.Tensor], sca
         flag[0] = 1
 
 
+def step_control(which: int, stats: torch.Tensor, flag: torch.Tensor, control: torch.Tensor, result: torch.Tensor,
+                 inv: float = 1.0, clip: float = 0.0, replicas: float = 1.0) -> None:
+    """Scalar bookkeeping of an optimizer step on the device, one launch each, no host synchronisation.
+
+    ``which`` 0: ``stats[1:3] = [overflow flag, device status word]`` (before the statistics are summed over the
+    ranks); 1: from the summed ``stats`` derive ``control = [gradient multiplier, skip]`` and ``result = [global
+    norm, skip, a device-side wait gave up, norm after clipping]``; 2: fold a status raised after that into
+    ``result[2]``."""
+    if stats.is_cuda:
+        check(lib().sb200_step_control(which, stats.data_ptr(), flag.data_ptr(), status_word().data_ptr(), inv, clip,
+                                       replicas, control.data_ptr(), result.data_ptr(), stream()), "sb200_step_control")
+        return
+    if which == 0:
+        stats[1] = float(flag[0] != 0)
+        stats[2] = 0.0
+    elif which == 1:
+        norm = math.sqrt(float(stats[0]) / replicas) * inv if float(stats[0]) >= 0 else float("nan")
+        timed_out = float(stats[2]) > 0
+        bad = float(stats[1]) > 0 or not math.isfinite(norm) or timed_out
+        coef = clip / norm if (clip > 0.0 and norm >= clip) else 1.0
+        control[0] = 0.0 if bad else coef * inv
+        control[1] = float(bad)
+        result[0] = norm
+        result[1] = float(bad)
+        result[2] = float(timed_out)
+        result[3] = norm * coef
+
+
 def transpose2d(x: torch.Tensor) -> torch.Tensor:
     if x.is_cuda and x.dtype in _KERNEL_DTYPES and x.is_contiguous() and x.dim() == 2:
         out = torch.empty((x.shape[1], x.shape[0]), dtype=x.dtype, device=x.device)

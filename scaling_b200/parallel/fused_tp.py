@@ -25,7 +25,7 @@ import torch.distributed as dist
 from ..ops import _lib
 from ..ops import functional as K
 from ..ops._lib import check, lib
-from .fused_zero import _SymmetricBuffer
+from .fused_zero import _SymmetricBuffer, device_wait_limit_s
 
 _DECLARED = False
 FLAG_STRIDE = 8192  # output tiles of 128 rows a single fused GEMM may have
@@ -62,7 +62,7 @@ class FusedTPWorkspace:
         self.local = torch.zeros(2, dtype=torch.int32, device=device)  # [epoch, finished CTAs]
         self.use_multicast = (use_multicast and self.partial.multicast_ptr is not None
                               and self.out.multicast_ptr is not None)
-        self.timeout_s = float(os.environ.get("SB200_P2P_TIMEOUT_S", "10"))
+        self.timeout_s = device_wait_limit_s()
         self.launches = 0
         self._gathered_key: Any = None
         self._regathered: Any = None

@@ -31,6 +31,27 @@ from ..ops._lib import check, lib
 from ..ops.functional import status_word
 
 
+MAX_DEVICE_WAIT_S = 60.0
+
+
+def device_wait_limit_s() -> float:
+    """Limit of a device-side wait on a peer in seconds (``SB200_P2P_TIMEOUT_S``, default 10).  The kernels accept at
+    most 60 s (a longer spin would look like a hung GPU to everything else on the machine); larger or non-positive
+    settings are clamped, with a warning."""
+    raw = os.environ.get("SB200_P2P_TIMEOUT_S", "10")
+    try:
+        value = float(raw)
+    except ValueError:
+        value = -1.0
+    if 0.0 < value <= MAX_DEVICE_WAIT_S:
+        return value
+    clamped = MAX_DEVICE_WAIT_S if value > MAX_DEVICE_WAIT_S else 10.0
+    from ..core.logging import logger
+
+    logger.warning(f"SB200_P2P_TIMEOUT_S={raw!r} is outside (0, {MAX_DEVICE_WAIT_S:g}] seconds; using {clamped:g}")
+    return clamped
+
+
 def _ptr_array(ptrs: list[int]) -> Any:
     arr = (ctypes.c_void_p * len(ptrs))()
     for i, p in enumerate(ptrs):
@@ -79,7 +100,7 @@ class FusedZero:
         self.flags.tensor.zero_()
         self.round = torch.zeros(1, dtype=torch.int32, device=dev)
         self.use_multicast = use_multicast and all(b.multicast_ptr is not None for b in self.params)
-        self.timeout_s = float(os.environ.get("SB200_P2P_TIMEOUT_S", "10"))
+        self.timeout_s = device_wait_limit_s()
         torch.cuda.synchronize(dev)
         dist.barrier(group=group)  # every rank's flag words are zero before the first in-kernel barrier
 

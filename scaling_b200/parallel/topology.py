@@ -22,6 +22,12 @@ from .rng_tracker import CudaRNGStateTracker, RngTrackerState
 from .topology_config import TopologyConfig
 
 
+# Point-to-point groups between pipeline stages use at most this many CTAs per NCCL kernel; up to four such kernels
+# can be active at once on a middle stage (receive and send, in each direction).
+PIPE_P2P_MAX_CTAS = 2
+PIPE_P2P_RESERVED_SMS = 4 * PIPE_P2P_MAX_CTAS
+
+
 class TopologyState(TypedDict):
     model_parallel_constant_rng: RngTrackerState
 
@@ -114,6 +120,17 @@ class Topology:
             g = dist.new_group(ranks)
             if self.config.global_rank in ranks:
                 self._pipe_group = g
+        if self.pipe_parallel_size > 1:
+            # Point-to-point traffic between stages: one group per direction (activations towards the last stage,
+            # gradients towards the first).  Each group has its own communicators and streams, so a receive that is
+            # posted ahead of time in one direction never queues in front of a send in the other.  On NCCL the
+            # groups are limited to a few CTAs per kernel: a copy between two GPUs needs no more, and kernels that
+            # wait for their tensor-parallel peers leave that many SMs free (PIPE_P2P_RESERVED_SMS).
+            for ranks in self.all_pipe_parallel_groups:
+                for direction in ("down", "up"):
+                    g = dist.new_group(ranks, pg_options=self._p2p_group_options())
+                    if self.config.global_rank in ranks:
+                        setattr(self, f"_pipe_{direction}_group", g)
         for ranks in self.all_data_parallel_groups:
             g = dist.new_group(ranks)
             if self.config.global_rank in ranks:
@@ -123,6 +140,34 @@ class Topology:
             if self.config.global_rank in ranks:
                 self._model_group = g
         self.is_distributed_initialized = True
+
+    def _p2p_group_options(self) -> Any:
+        if self.backend != "nccl":
+            return None
+        try:
+            opts = dist.ProcessGroupNCCL.Options()
+            opts.config.max_ctas = PIPE_P2P_MAX_CTAS
+            opts.config.min_ctas = 1
+            return opts
+        except Exception:  # pragma: no cover - older builds without per-group NCCL configuration
+            return None
+
+    @property
+    def pipe_down_group(self) -> Any:
+        """Group that carries activations from a stage to the next (None without pipeline parallelism)."""
+        return getattr(self, "_pipe_down_group", None)
+
+    @property
+    def pipe_up_group(self) -> Any:
+        """Group that carries gradients (and the loss record) from a stage to an earlier one."""
+        return getattr(self, "_pipe_up_group", None)
+
+    @property
+    def reserved_sms(self) -> int:
+        """SMs that kernels waiting on their tensor-parallel peers must leave free on this layout: with pipeline
+        stages, send / receive kernels of the two point-to-point groups run beside the compute stream, and a kernel
+        whose CTAs wait for CTAs of another GPU must be completely resident however many of those are active."""
+        return PIPE_P2P_RESERVED_SMS if self.pipe_parallel_size > 1 else 0
 
     # ------------------------------------------------------------------ rng
     @property

@@ -3,7 +3,8 @@ from .embedding_dataset import EmbeddingBlendedDataset, EmbeddingDataset, Embedd
 from .finetuning_chat_dataset import FinetuningChatBlendedDataset, FinetuningChatDataset
 from .finetuning_text_dataset import FinetuningTextBlendedDataset, FinetuningTextDataset
 from .inference_settings import Control, InferenceSettings, InferenceSuppressionParameters
-from .text_dataset import LegacyBlendedDataset, SyntheticTextDataset, TextBlendedDataset, TextDataset, TextDatasetItem, pack_windows
+from .legacy_blended_dataset import LegacyBlendedDataset
+from .text_dataset import SyntheticTextDataset, TextBlendedDataset, TextDataset, TextDatasetItem, pack_windows
 from .text_image_dataset import TextImageBlendedDataset, TextImageDataset
 from .text_dataset_batch import TextDatasetBatch, TextDatasetBatchBeforeSync
 from .utils import (

@@ -142,6 +142,26 @@ class MMapIndexedDatasetBuilder:
             f.write(np.asarray(self._doc_idx, dtype=np.int64).tobytes(order="C"))
 
 
+def write_fixed_width_items(data_file: str, index_file: str, items: np.ndarray) -> None:
+    """Write a 2-D array as an "mmap" indexed dataset with one item per row (every item its own document), without
+    going through ``add_item`` row by row.  Files are written under temporary names and moved into place."""
+    items = np.ascontiguousarray(items)
+    n, width = items.shape
+    tmp_data, tmp_index = f"{data_file}.tmp.{os.getpid()}", f"{index_file}.tmp.{os.getpid()}"
+    items.tofile(tmp_data)
+    with open(tmp_index, "wb") as f:
+        f.write(MMAP_MAGIC)
+        f.write(struct.pack("<Q", 1))
+        f.write(struct.pack("<B", dtype_code(items.dtype)))
+        f.write(struct.pack("<Q", n))
+        f.write(struct.pack("<Q", n + 1))
+        f.write(np.full(n, width, dtype=np.int32).tobytes(order="C"))
+        f.write((np.arange(n, dtype=np.int64) * (width * items.dtype.itemsize)).tobytes(order="C"))
+        f.write(np.arange(n + 1, dtype=np.int64).tobytes(order="C"))
+    os.replace(tmp_data, data_file)
+    os.replace(tmp_index, index_file)
+
+
 class IndexedDataset(torch.utils.data.Dataset):
     """Reader of the "TNTIDX" layout; items are read from the data file on access."""
 

@@ -247,7 +247,10 @@ class TextBlendedDataset(BaseBlendedDataset[TextDataset]):
     """Several ``TextDataset``s blended by weight (src/scaling/transformer/data/text_dataset.py:455-469)."""
 
 
-class LegacyBlendedDataset(BaseBlendedDataset[TextDataset]):
-    """Blend of corpora stored as legacy indexed datasets (src/scaling/transformer/data/legacy_blended_dataset.py:22-283):
-    the same weighting and interleaving as ``TextBlendedDataset``; the sources are ``TextDataset``s opened with
-    ``legacy_dataset=True``."""
+def __getattr__(name: str):
+    # kept importable from here; the class lives in legacy_blended_dataset (which imports this module)
+    if name == "LegacyBlendedDataset":
+        from .legacy_blended_dataset import LegacyBlendedDataset
+
+        return LegacyBlendedDataset
+    raise AttributeError(name)

@@ -116,7 +116,8 @@ def blended_dataset_type(data_config: DataConfig) -> type[BaseBlendedDataset]:
         from .data.embedding_dataset import EmbeddingBlendedDataset
 
         return EmbeddingBlendedDataset
-    from .data.text_dataset import LegacyBlendedDataset, TextBlendedDataset
+    from .data.legacy_blended_dataset import LegacyBlendedDataset
+    from .data.text_dataset import TextBlendedDataset
 
     return LegacyBlendedDataset if data_config.legacy_dataset else TextBlendedDataset
 

@@ -279,3 +279,65 @@ def test_sampler_indices_follow_the_consumed_samples():
     assert resumed == r0[2:] and seed == 5
     wrapped, seed = batches(0, usable + 4, 1)
     assert wrapped == [r0[1]] and seed == 6  # the next epoch reshuffles the data with seed + epoch
+
+
+def _legacy_corpus(prefix: Path, n_docs: int, doc_len: int, base: int) -> None:
+    from scaling_b200.transformer.data.legacy_dataset.indexed_dataset import make_builder
+
+    b = make_builder(str(prefix) + ".bin", "mmap", vocab_size=1000)
+    for d in range(n_docs):
+        b.add_item(torch.arange(doc_len) + base + d)
+        b.end_document()
+    b.finalize(str(prefix) + ".idx")
+
+
+def test_legacy_blended_dataset_index_files_and_interleaving(tmp_path: Path):
+    """The legacy blend writes `.bin/.idx/.done` under the legacy cache name, interleaves the sources by always taking
+    from the dataset furthest below its target (checked against the plain loop), and a second instance reuses the files."""
+    import hashlib
+
+    from scaling_b200.core.data.blended_dataset_config import BlendedDatasetConfig
+    from scaling_b200.transformer.data import LegacyBlendedDataset
+    from scaling_b200.transformer.data.legacy_dataset.indexed_dataset import make_dataset
+
+    _legacy_corpus(tmp_path / "small", n_docs=6, doc_len=9, base=1)
+    _legacy_corpus(tmp_path / "large", n_docs=30, doc_len=9, base=500)
+    seq = 4
+    sets = [TextDataset(data_prefix=tmp_path / n, sequence_length=seq, seed=3, legacy_dataset=True) for n in ("small", "large")]
+    cfg = BlendedDatasetConfig(weight_by_num_documents=True, weighted_sampler_alpha=0.5, cache_directory=tmp_path / "cache")
+    blend = LegacyBlendedDataset(seed=3, config=cfg, datasets=sets)
+
+    counts = [len(s) for s in sets]
+    p = np.asarray(counts, dtype=np.float64) / sum(counts)
+    q = p ** 0.5 / (p ** 0.5).sum()
+    w = (q / p) / (q / p).sum()
+    assert np.allclose(blend.weights, w)
+    targets = np.array([max(1, int(x * n)) for n, x in zip(counts, w / w.max())], dtype=np.int64)
+    sampled = np.zeros(2, dtype=np.int64)
+    expected = []
+    while (sampled < targets).all():
+        i = int((sampled / targets).argmin())
+        expected.append([i, int(sampled[i])])
+        sampled[i] += 1
+    stem = blend.get_data_index_cache_filename_stem(3)
+    name = Path(stem).name
+    prefix_hash = hashlib.md5("small-large".encode()).hexdigest()
+    assert name.startswith(f"index_cache_blended_dataset_seed_3_seq_len_{seq}_prefix_{prefix_hash}_weights_")
+    assert all(Path(stem + ext).is_file() for ext in (".bin", ".idx", ".done"))
+    stored = make_dataset(stem, "mmap")
+    assert stored.dtype == np.int32 and [stored[i].tolist() for i in range(len(stored))] == expected
+    assert len(blend) == len(expected)
+    for k in (0, 1, len(expected) - 1):
+        d, j = expected[k]
+        assert torch.equal(blend[k].token_ids, sets[d][j].token_ids)
+
+    before = {ext: Path(stem + ext).stat().st_mtime_ns for ext in (".bin", ".idx", ".done")}
+    again = LegacyBlendedDataset(seed=3, config=cfg, datasets=sets)
+    assert {ext: Path(stem + ext).stat().st_mtime_ns for ext in before} == before and len(again) == len(blend)
+    # a rate limit per dataset (keyed by the stem of its prefix) caps the large corpus only
+    ep = BlendedDatasetConfig(weight_by_num_documents=True, weight_examples_proportional=True,
+                              cache_directory=tmp_path / "cache_ep")
+    capped = LegacyBlendedDataset(seed=3, config=ep, datasets=sets, ep_maximum_dict={"large": counts[0]})
+    assert np.allclose(capped.weights * np.asarray(counts) / (capped.weights * np.asarray(counts)).sum(), [0.5, 0.5])
+    single = LegacyBlendedDataset(seed=3, config=cfg, datasets=sets[:1])
+    assert len(single) == counts[0] and torch.equal(single[2].token_ids, sets[0][2].token_ids)

@@ -91,3 +91,64 @@ def test_resume_into_other_layout(tmp_path: Path):
         resumed = _losses(ws, iters=10, load_dir=str(tmp_path), **kw)
         for a, b in zip(resumed, full[6:]):
             assert abs(a - b) < 2e-3, (kw, resumed, full[6:])
+
+
+def _run_traced(rank, world_size, port, device, config, overlap):
+    """Two training steps of the pipelined MLP; returns (losses, instruction trace of the second step)."""
+    import os
+
+    os.environ["SB200_PIPE_OVERLAP"] = "1" if overlap else "0"
+    from scaling_b200.core.data import DataLoader
+    from scaling_b200.core.runner import LaunchConfig
+    from scaling_b200.models.mlp import (MLPConfig, MLPContext, SyntheticClassificationDataset, init_model,
+                                         init_optimizer, loss_function, metrics_aggregation_fn)
+    from scaling_b200.parallel import Topology
+
+    lc = LaunchConfig(master_port=port, master_addr="127.0.0.1", world_size=world_size, global_rank=rank,
+                      local_slot=rank, payload=copy.deepcopy(config))
+    cfg = MLPConfig.from_dict(lc.overwrite_config_dict_with_launcher_args(dict(lc.payload)))
+    topology = Topology(cfg.topology)
+    context = MLPContext(config=cfg, topology=topology)
+    context.initialize(master_addr="127.0.0.1", master_port=str(port), seed=cfg.trainer.seed)
+    model = init_model(context)
+    optimizer = init_optimizer(context, model)
+    loader = None
+    if topology.is_io_rank:
+        dataset = SyntheticClassificationDataset(n_samples=cfg.data.n_samples, seed=cfg.trainer.seed)
+        loader = DataLoader(seed=cfg.trainer.seed, consumed_samples=0, dataset=dataset, topology=topology)
+    losses = []
+    for step in range(3):
+        model.instruction_trace = [] if step == 2 else None
+        out = model.train_step(loader, optimizer, SyntheticClassificationDataset.sync_batch_to_model_parallel,
+                               loss_function, metrics_aggregation_fn)
+        losses.append(out.loss)
+    return losses, model.instruction_trace
+
+
+@pytest.mark.dist
+def test_pipeline_receives_are_posted_ahead_of_the_compute_before_them():
+    """With overlap on, a stage posts the receive of the next activation as soon as the current one has arrived (before
+    it runs the forward pass in between), and the receive of a gradient as soon as the forward pass it belongs to is
+    enqueued; the losses are those of the run that posts every receive where the schedule names it."""
+    config = _config(2, pp=2, ga=4, micro=4, iters=3)
+    (loss_a, trace0), (_, trace1) = dist_launcher(_run_traced, 2, config=config, overlap=True)
+    (loss_b, plain0), _ = dist_launcher(_run_traced, 2, config=config, overlap=False)
+    assert loss_a == loss_b and loss_a[0] is not None
+    assert not any(t.startswith("post ") for t in plain0)
+
+    def pos(trace, entry):
+        assert entry in trace, (entry, trace)
+        return trace.index(entry)
+
+    # last stage: activation of micro batch 1 is on its way while micro batch 0 is still being computed
+    assert pos(trace1, "RecvActivation mb=0") < pos(trace1, "post RecvActivation mb=1") < pos(trace1, "ForwardPass mb=0")
+    assert pos(trace1, "post RecvActivation mb=2") < pos(trace1, "ForwardPass mb=1")
+    # first stage: the gradient of micro batch 0 is awaited from the moment its forward pass is enqueued, i.e. during
+    # the forward pass of micro batch 1
+    assert pos(trace0, "ForwardPass mb=0") < pos(trace0, "post RecvGrad mb=0") < pos(trace0, "ForwardPass mb=1")
+    assert pos(trace0, "post RecvGrad mb=1") < pos(trace0, "BackwardPass mb=0")
+    # every posted receive is consumed by its instruction, in order
+    for trace, kind in ((trace1, "RecvActivation"), (trace0, "RecvGrad")):
+        posted = [t.split("mb=")[1] for t in trace if t.startswith(f"post {kind}")]
+        done = [t.split("mb=")[1] for t in trace if t.startswith(f"{kind} mb=")]
+        assert posted == [m for m in done if m in posted] and len(posted) >= 3

@@ -91,3 +91,18 @@ def test_noalloc_rejects_oversized_rows():
     rc = noalloc(x.data_ptr(), x.data_ptr(), v.data_ptr(), None, r.data_ptr(), x.data_ptr(), v.data_ptr(), None, 4, H,
                  1, 0, 1, torch.cuda.current_stream().cuda_stream)
     assert rc == 103  # SB_ERR_TOO_LARGE
+
+
+def test_noalloc_refuses_misaligned_pointers_before_any_launch():
+    noalloc, _, _ = _symbols()
+    H = 256
+    x = torch.zeros(4 * H + 8, device="cuda", dtype=torch.bfloat16)
+    v = torch.zeros(H, device="cuda", dtype=torch.bfloat16)
+    r = torch.ones(4, device="cuda")
+    stream = torch.cuda.current_stream().cuda_stream
+    torch.cuda.synchronize()
+    # dx two bytes off a 16-byte boundary: refused on the host (SB_ERR_BAD_ARG), so no kernel ever sees the pointer
+    rc = noalloc(x.data_ptr(), x.data_ptr(), v.data_ptr(), None, r.data_ptr(), x.data_ptr() + 2, v.data_ptr(), None, 4,
+                 H, 1, 0, 1, stream)
+    assert rc == 102
+    torch.cuda.synchronize()  # the context is untouched
