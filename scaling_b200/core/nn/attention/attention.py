@@ -158,10 +158,15 @@ class FlashAttention(_AttentionCore):
         """query ``[Tq, h, d]``, key/value ``[Tk, hkv, d]`` (token-major, packed) -> ``[Tq, h, d]``."""
         query, key, value = self._pre(query, key, value)
         use_window = self.local_attention_window_size if (local is None or local) else None
+        drop_p = self.dropout_p if self.training else 0.0
+        topology = getattr(self, "topology", None)
         out = flash_attention(
             query, key, value, cumulative_seq_lengths_query, cumulative_seq_lengths_key, causal=self.causal,
-            scale=self.query_key_scaling_factor, window=use_window,
-            dropout_p=self.dropout_p if self.training else 0.0, doc_ranges=doc_ranges,
+            scale=self.query_key_scaling_factor, window=use_window, dropout_p=drop_p, doc_ranges=doc_ranges,
+            # the kernel draws the mask from the topology's counter-based stream (same on all tensor-parallel ranks,
+            # whose heads differ) and recomputes it in the backward pass
+            rng_state=topology.kernel_rng if (drop_p > 0.0 and topology is not None and query.is_cuda) else None,
+            head_offset=topology.model_parallel_rank * query.shape[1] if topology is not None else 0,
         )
         return self._post(out)
 
@@ -300,6 +305,7 @@ class ParallelSelfAttention(torch.nn.Module):
                 masked_softmax_config=masked_softmax_config, num_local_attention_heads=num_local_attention_heads,
                 causal=causal, local_attention_window_size=local_attention_window_size, umup_mult=umup_mult,
             )
+            self.scaled_dot_product_attention.topology = topology  # source of the attention-dropout stream
         else:
             self.scaled_dot_product_attention = ScaledDotProductAttention(
                 head_dim=self.hidden_size_per_attention_head, dropout_p=dropout_attention_probs,
@@ -454,7 +460,7 @@ class ParallelSelfAttention(torch.nn.Module):
 
     def _packed_path_ok(self, x: torch.Tensor, use_cache: bool, reset_cache: bool) -> bool:
         """The fused projection -> rotary -> attention path covers training-style self-attention on CUDA with a
-        packed qkv weight, all heads global or all local, no adapters, no q/k norm, no attention dropout."""
+        packed qkv weight, all heads global or all local, no adapters, no q/k norm."""
         if not (self.use_flash_attention and self.qkv_in_one and x.is_cuda and x.dtype == torch.bfloat16):
             return False
         if use_cache or reset_cache or self.key_query_norm:
@@ -466,7 +472,7 @@ class ParallelSelfAttention(torch.nn.Module):
         if 0 < self.num_local_attention_heads < self.num_attention_heads:
             return False
         core = self.scaled_dot_product_attention
-        if core._use_umup or (core.dropout_p > 0.0 and self.training):
+        if core._use_umup or (core.dropout_p > 0.0 and self.training and self.topology is None):
             return False
         from ....ops import _lib
 
@@ -475,7 +481,7 @@ class ParallelSelfAttention(torch.nn.Module):
     def _packed_attention(self, x: torch.Tensor, cumulative_seq_lengths: Optional[torch.Tensor],
                           position_ids: Optional[torch.Tensor],
                           doc_ranges: Optional[tuple[torch.Tensor, torch.Tensor]]) -> torch.Tensor:
-        from ....ops.attention_kernel import packed_qkv_attention
+        from ....ops.attention_kernel import dropout_args, packed_qkv_attention
 
         b, s, _ = x.shape
         d = self.hidden_size_per_attention_head
@@ -488,8 +494,12 @@ class ParallelSelfAttention(torch.nn.Module):
                    else torch.arange(s, device=x.device, dtype=torch.int32).repeat(b))
         core = self.scaled_dot_product_attention
         window = core.local_attention_window_size if self.num_local_attention_heads > 0 else None
+        drop_p = core.dropout_p if self.training else 0.0
+        drop = dropout_args(drop_p, self.topology.kernel_rng if drop_p > 0.0 else None,
+                            self.topology.model_parallel_rank * self.num_attention_heads_per_partition
+                            if self.topology is not None else 0)
         ctx = packed_qkv_attention(qkv, pos, rotary, cumulative_seq_lengths, self.causal,
-                                   core.query_key_scaling_factor, window, doc_ranges)
+                                   core.query_key_scaling_factor, window, doc_ranges, drop)
         return ctx.reshape(b, s, -1)
 
     def _output_projection(self, hidden: torch.Tensor) -> torch.Tensor:

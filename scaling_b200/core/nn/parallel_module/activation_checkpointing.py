@@ -1,8 +1,8 @@
 """Activation checkpointing that also rewinds the tensor-parallel-constant RNG stream.
 
 The forward of a checkpointed block runs without building a graph and keeps only the block's
-inputs together with the generator states (CPU, current CUDA device, and the topology's
-model-parallel-constant tracker).  During backward the states are restored, the block is run
+inputs together with the generator states (CPU, current CUDA device, the topology's
+model-parallel-constant tracker, and the call counter of the counter-based dropout kernels).  During backward the states are restored, the block is run
 again with autograd enabled, and gradients flow through the recomputed graph.  Dropout therefore
 draws identical masks in the first and the recomputed pass, on every tensor-parallel rank.
 Same guarantee as the reference's fork of torch's non-reentrant checkpoint
@@ -24,9 +24,12 @@ def _capturing() -> bool:
 
 
 def _capture_rng(topology: Optional[Topology]) -> dict[str, Any]:
+    # the dropout kernels number their calls inside a step on the host: the recomputed pass starts from the number
+    # the first pass started from (a plain integer, also while a CUDA graph is being captured)
+    calls = {"kernel_rng_call": topology.kernel_rng.call_index} if topology is not None else {}
     if _capturing():
-        return {}  # a captured step contains no random ops (the engine only captures dropout-free models)
-    state: dict[str, Any] = {"cpu": torch.get_rng_state()}
+        return calls  # generator states cannot be read under capture; a captured step uses the dropout kernels only
+    state: dict[str, Any] = dict(calls, cpu=torch.get_rng_state())
     if torch.cuda.is_available() and torch.cuda.is_initialized():
         state["cuda"] = torch.cuda.get_rng_state()
     if topology is not None and topology.has_model_parallel_constant_rng:
@@ -35,7 +38,9 @@ def _capture_rng(topology: Optional[Topology]) -> dict[str, Any]:
 
 
 def _restore_rng(state: dict[str, Any], topology: Optional[Topology]) -> None:
-    if not state:
+    if "kernel_rng_call" in state and topology is not None:
+        topology.kernel_rng.call_index = state["kernel_rng_call"]
+    if "cpu" not in state:
         return
     torch.set_rng_state(state["cpu"])
     if "cuda" in state:

@@ -142,6 +142,7 @@ class ParallelModule(PipePartitionedModule, Generic[BaseLossInputGeneric, BaseDa
         self._graph_captures = 0
         self._graph_kernel_calls = 0
         self._graph_pending: list[Any] = []
+        self._kernel_dropout: Optional[bool] = None
         self._handlers: dict[str, Callable[..., None]] = {
             "LoadMicroBatch": self._do_load, "ForwardPass": self._do_forward, "Loss": self._do_loss,
             "BackwardPass": self._do_backward, "SendActivation": self._do_send_activation,
@@ -321,7 +322,8 @@ class ParallelModule(PipePartitionedModule, Generic[BaseLossInputGeneric, BaseDa
     def _graph_eligible(self, optimizer: Any) -> bool:
         """A whole optimizer step (all micro batches, backward, gradient reduction, AdamW, parameter all-gather)
         can be captured once and replayed when nothing in it depends on the host: one pipeline stage, batches
-        that reach the device without a tensor-parallel broadcast, no dropout, no loss scaling, profiler idle."""
+        that reach the device without a tensor-parallel broadcast, dropout only in the counter-based kernels, no loss
+        scaling, profiler idle."""
         if not self.enable_cuda_graph or self._graph_failed:
             return False
         if getattr(self, "_tensor_statistics_active", False):  # hooks of a statistics trace need the eager step
@@ -337,12 +339,25 @@ class ParallelModule(PipePartitionedModule, Generic[BaseLossInputGeneric, BaseDa
             return False
         if torch._C._get_tracing_state() is not None:
             return False
+        # Dropout is captured when it runs in the counter-based kernels (their seed and step are read from device
+        # memory, which the host advances before every replay); torch's generator-based dropout is not.
         for m in self._layers.modules():
-            if isinstance(m, torch.nn.Dropout) and m.p > 0.0:
+            if isinstance(m, torch.nn.Dropout) and m.p > 0.0 and not getattr(m, "kernel_dropout", False):
                 return False
-            if getattr(m, "dropout_p", 0.0) and m.training:
+            if getattr(m, "dropout_p", 0.0) and m.training and getattr(m, "topology", None) is None:
                 return False
         return True
+
+    def _begin_dropout_step(self) -> None:
+        """New dropout masks for this step (only where a dropout kernel is active: the update is a small
+        host-to-device copy)."""
+        if self._kernel_dropout is None:
+            self._kernel_dropout = any(
+                (isinstance(m, torch.nn.Dropout) and m.p > 0.0 and getattr(m, "kernel_dropout", False))
+                or (getattr(m, "dropout_p", 0.0) and getattr(m, "topology", None) is not None)
+                for m in self._layers.modules())
+        if self._kernel_dropout and self.topology.device.type == "cuda":
+            self.topology.kernel_rng.begin_step()
 
     @staticmethod
     def _batch_tensors(batch: Any) -> list[tuple[str, torch.Tensor]]:
@@ -467,6 +482,7 @@ class ParallelModule(PipePartitionedModule, Generic[BaseLossInputGeneric, BaseDa
         if not torch.is_grad_enabled():
             raise RuntimeError("train_step() requires gradients enabled. Use evaluation_step() instead.")
         self.step_timer.start()
+        self._begin_dropout_step()
         if self._graph_eligible(optimizer):
             self._layers.train()
             out = self._graphed_train_step(dataloader, optimizer, sync_batch_to_model_parallel, loss_function,

@@ -378,6 +378,40 @@ template <> __device__ __forceinline__ float from_f<float>(float v) { return v; 
 template <> __device__ __forceinline__ __nv_bfloat16 from_f<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
 template <> __device__ __forceinline__ __half from_f<__half>(float v) { return __float2half_rn(v); }
 
+// Philox4x32-10 (Salmon et al., "Parallel random numbers: as easy as 1, 2, 3", SC'11): counter-based generator, the
+// same (key, counter) always yields the same four 32-bit words, so a dropout mask is recomputed in the backward
+// pass (and in a recomputed forward pass) instead of being stored.
+__device__ __forceinline__ uint4 philox4x32(uint2 key, uint4 ctr) {
+  constexpr uint32_t M0 = 0xD2511F53u, M1 = 0xCD9E8D57u, W0 = 0x9E3779B9u, W1 = 0xBB67AE85u;
+#pragma unroll
+  for (int r = 0; r < 10; ++r) {
+    const uint32_t hi0 = __umulhi(M0, ctr.x), lo0 = M0 * ctr.x;
+    const uint32_t hi1 = __umulhi(M1, ctr.z), lo1 = M1 * ctr.z;
+    ctr = make_uint4(hi1 ^ ctr.y ^ key.x, lo1, hi0 ^ ctr.w ^ key.y, lo0);
+    key.x += W0;
+    key.y += W1;
+  }
+  return ctr;
+}
+// Random stream of the dropout kernels: key = seed, counter = (block of four consecutive elements or mask bytes,
+// index of the call inside the step, step).  rng points to {seed, step} in device memory, so that a captured CUDA
+// graph draws new masks on every replay once the step word has been advanced.
+struct DropoutRng {
+  uint2 key;
+  uint32_t call, step;
+};
+__device__ __forceinline__ DropoutRng dropout_rng(const long long* __restrict__ rng, uint32_t call) {
+  const unsigned long long seed = (unsigned long long)rng[0], step = (unsigned long long)rng[1];
+  DropoutRng r;
+  r.key = make_uint2((uint32_t)seed, (uint32_t)(seed >> 32) ^ (uint32_t)(step >> 32));
+  r.call = call;
+  r.step = (uint32_t)step;
+  return r;
+}
+__device__ __forceinline__ uint4 dropout_words(const DropoutRng& r, unsigned long long block) {
+  return philox4x32(r.key, make_uint4((uint32_t)block, (uint32_t)(block >> 32), r.call, r.step));
+}
+
 // 16-byte vector of T
 template <typename T> struct Vec16 {
   static constexpr int N = 16 / sizeof(T);

@@ -1,5 +1,5 @@
 // Memory-bound elementwise kernels for sm_100a: SwiGLU, GELU, RoPE, masked softmax,
-// residual add, 2-D transpose.  All use 16-byte vector accesses where the shape allows
+// dropout + residual add, 2-D transpose.  All use 16-byte vector accesses where the shape allows
 // and fp32 math with bf16/fp16/fp32 storage.
 //
 // Behaviour covered (reference files): silu(a) * g (src/scaling/core/nn/mlp.py:249),
@@ -98,9 +98,48 @@ __global__ void gelu_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ 
     dx[i] = sb::from_f<T>(sb::to_f(dy[i]) * gelu_grad_f(sb::to_f(x[i])));
 }
 
-// --------------------------------------------------------------- residual add
+// ------------------------------------------------------- dropout + residual
+// y = dropout(x) * xs + r * rs, with r optional (the output of a sub-block joining the residual stream:
+// src/scaling/transformer/model/layers/layer.py:264-269,283-288; xs / rs carry the u-muP residual scales).  Element g
+// (global index: elem_offset + position in this tensor, so that token shards of one tensor draw from one mask)
+// is kept iff word (g mod 4) of Philox block (g / 4) is >= thr; kept values are multiplied by keep_scale = 1/(1-p).
+// The backward kernel recomputes the mask: dx = dy * mask * keep_scale * xs.
+template <typename T, bool BWD>
+__global__ void dropout_add_kernel(const T* __restrict__ x, const T* __restrict__ r, T* __restrict__ y, long n,
+                                   uint32_t thr, float keep_scale, float xs, float rs,
+                                   const long long* __restrict__ rng, uint32_t call, long elem_offset) {
+  constexpr int V = sb::Vec16<T>::N;
+  const sb::DropoutRng st = sb::dropout_rng(rng, call);
+  const long nv = n / V;
+  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < nv; i += (long)gridDim.x * blockDim.x) {
+    auto xv = sb::ld16(x + i * V);
+    sb::Vec16<T> rv, o;
+    if (!BWD && r) rv = sb::ld16(r + i * V);
+    const unsigned long long g0 = (unsigned long long)(elem_offset + i * V);
+#pragma unroll
+    for (int b = 0; b < V / 4; ++b) {
+      const uint4 w = sb::dropout_words(st, g0 / 4 + b);
+      const uint32_t ws[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float kept = ws[k] >= thr ? sb::to_f(xv.e[b * 4 + k]) * keep_scale * xs : 0.f;
+        o.e[b * 4 + k] = sb::from_f<T>((!BWD && r) ? kept + sb::to_f(rv.e[b * 4 + k]) * rs : kept);
+      }
+    }
+    sb::st16(y + i * V, o);
+  }
+  for (long i = nv * V + blockIdx.x * (long)blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x) {
+    const unsigned long long g = (unsigned long long)(elem_offset + i);
+    const uint4 w = sb::dropout_words(st, g / 4);
+    const uint32_t ws[4] = {w.x, w.y, w.z, w.w};
+    const float kept = ws[g & 3] >= thr ? sb::to_f(x[i]) * keep_scale * xs : 0.f;
+    y[i] = sb::from_f<T>((!BWD && r) ? kept + sb::to_f(r[i]) * rs : kept);
+  }
+}
+// y = a * as + b * bs (the p = 0 form of the above)
 template <typename T>
-__global__ void add_kernel(const T* __restrict__ a, const T* __restrict__ b, T* __restrict__ y, long n) {
+__global__ void scaled_add_kernel(const T* __restrict__ a, const T* __restrict__ b, T* __restrict__ y, long n, float as,
+                                  float bs) {
   constexpr int V = sb::Vec16<T>::N;
   long nv = n / V;
   for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < nv; i += (long)gridDim.x * blockDim.x) {
@@ -108,11 +147,11 @@ __global__ void add_kernel(const T* __restrict__ a, const T* __restrict__ b, T* 
     auto bv = sb::ld16(b + i * V);
     sb::Vec16<T> o;
 #pragma unroll
-    for (int k = 0; k < V; ++k) o.e[k] = sb::from_f<T>(sb::to_f(av.e[k]) + sb::to_f(bv.e[k]));
+    for (int k = 0; k < V; ++k) o.e[k] = sb::from_f<T>(sb::to_f(av.e[k]) * as + sb::to_f(bv.e[k]) * bs);
     sb::st16(y + i * V, o);
   }
   for (long i = nv * V + blockIdx.x * (long)blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x)
-    y[i] = sb::from_f<T>(sb::to_f(a[i]) + sb::to_f(b[i]));
+    y[i] = sb::from_f<T>(sb::to_f(a[i]) * as + sb::to_f(b[i]) * bs);
 }
 
 // --------------------------------------------------------------------- RoPE
@@ -397,10 +436,38 @@ SB_API int sb200_gelu_bwd(const void* dy, const void* x, void* dx, long n, int d
   SB_CHECK_LAUNCH();
   return SB_OK;
 }
-SB_API int sb200_add(const void* a, const void* b, void* y, long n, int dtype, cudaStream_t stream) {
+// y = dropout(x, p) * x_scale + r * r_scale (backward = 0), or dx = dy * mask / (1 - p) * x_scale (backward = 1, r
+// unused).  r may be null (plain dropout).  p = 0 needs no random numbers (rng may be null): the call is a scaled add.
+// rng: device int64[2] = {seed, step}; call: index of this dropout inside the step; elem_offset: index of x[0] in
+// the tensor that the mask is defined on (non-zero for the token shards of sequence parallelism; a multiple of 4).
+SB_API int sb200_dropout_add(const void* x, const void* r, void* y, long n, float p, float x_scale, float r_scale,
+                             const long long* rng, unsigned int call, long elem_offset, int backward, int dtype,
+                             cudaStream_t stream) {
   if (n <= 0) return SB_OK;
+  if (p < 0.f || p >= 1.f || (elem_offset & 3)) return SB_ERR_BAD_ARG;
+  if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(r) | reinterpret_cast<uintptr_t>(y)) & 15)
+    return SB_ERR_BAD_ARG;
+  if (p == 0.f) {
+    if (backward || !r) return SB_ERR_BAD_ARG;  // nothing to do: the caller passes the tensor through
+    SB_DISPATCH_DTYPE(dtype, T, {
+      scaled_add_kernel<T><<<grid_for(n / sb::Vec16<T>::N + 1, 256), 256, 0, stream>>>((const T*)x, (const T*)r, (T*)y,
+                                                                                      n, x_scale, r_scale);
+    });
+    SB_CHECK_LAUNCH();
+    return SB_OK;
+  }
+  if (!rng) return SB_ERR_BAD_ARG;
+  const double t = (double)p * 4294967296.0;
+  const uint32_t thr = t >= 4294967295.0 ? 4294967295u : (uint32_t)t;
+  const float keep_scale = 1.f / (1.f - p);
   SB_DISPATCH_DTYPE(dtype, T, {
-    add_kernel<T><<<grid_for(n / sb::Vec16<T>::N + 1, 256), 256, 0, stream>>>((const T*)a, (const T*)b, (T*)y, n);
+    const int grid = grid_for(n / sb::Vec16<T>::N + 1, 256);
+    if (backward)
+      dropout_add_kernel<T, true><<<grid, 256, 0, stream>>>((const T*)x, nullptr, (T*)y, n, thr, keep_scale, x_scale,
+                                                            0.f, rng, call, elem_offset);
+    else
+      dropout_add_kernel<T, false><<<grid, 256, 0, stream>>>((const T*)x, (const T*)r, (T*)y, n, thr, keep_scale,
+                                                             x_scale, r_scale, rng, call, elem_offset);
   });
   SB_CHECK_LAUNCH();
   return SB_OK;

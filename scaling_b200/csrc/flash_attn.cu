@@ -49,7 +49,26 @@ struct FaParams {
   long lddq_tok, lddk_tok, lddv_tok;     // element strides of the gradient outputs: token rows ...
   int lddq_head, lddk_head, lddv_head;   // ... and heads inside a row
   int* status;
+  // dropout on the attention probabilities (DROP instantiations): probability (query t, head h, key k) is kept iff
+  // byte (k mod 16) of the Philox block (k / 16, (drop_head0 + h) * T + t, drop_call, step) is >= drop_thr8; kept ones are
+  // multiplied by keep_scale = 1 / (1 - drop_thr8 / 256).  rng = {seed, step} in device memory.
+  const long long* rng;
+  uint32_t drop_call, drop_thr8;
+  uint32_t drop_head0;  // index of this call's head 0 among all heads of the layer (tensor-parallel shards differ)
+  float keep_scale;
 };
+
+// mk[i] = keep (byte >= thr8) or 0 for the 32 keys kbase .. kbase + 31 (kbase a multiple of 32) of query row row_id
+__device__ __forceinline__ void drop_mask32(const sb::DropoutRng& st, uint32_t row_id, int kbase, uint32_t thr8,
+                                            float keep, float* mk) {
+#pragma unroll
+  for (int b = 0; b < 2; ++b) {
+    const uint4 w = sb::philox4x32(st.key, make_uint4((uint32_t)(kbase >> 4) + b, row_id, st.call, st.step));
+    const uint32_t ws[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+    for (int i = 0; i < 16; ++i) mk[b * 16 + i] = ((ws[i >> 2] >> ((i & 3) * 8)) & 0xffu) >= thr8 ? keep : 0.f;
+  }
+}
 
 // byte offset of element (row r, column c) inside a K-major operand made of 64-column panels of
 // 128 rows x 128 bytes with the 128-byte swizzle (16-byte chunk index xor (row % 8))
@@ -107,7 +126,7 @@ template <int D> struct FaFwdCfg {
   static constexpr int SMEM = TILE_BYTES * (1 + 2 + VST) + 2 * PANEL_BYTES + 1024 + 256;
 };
 
-template <int D>
+template <int D, bool DROP>
 __global__ void __launch_bounds__(FA_THREADS, FaFwdCfg<D>::TWO ? 2 : 1)
     fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                   const __grid_constant__ CUtensorMap tmV, const FaParams p) {
@@ -248,6 +267,9 @@ __global__ void __launch_bounds__(FA_THREADS, FaFwdCfg<D>::TWO ? 2 : 1)
     float o_acc[D];
 #pragma unroll
     for (int i = 0; i < D; ++i) o_acc[i] = 0.f;
+    sb::DropoutRng drng = {};
+    if (DROP) drng = sb::dropout_rng(p.rng, p.drop_call);
+    const uint32_t drow = (p.drop_head0 + (uint32_t)h) * (uint32_t)p.T + (uint32_t)t;
     bool ok = true;
     for (int j = 0; j < n_tiles && ok; ++j) {
       const int sbuf = j % SBUF;
@@ -306,6 +328,12 @@ __global__ void __launch_bounds__(FA_THREADS, FaFwdCfg<D>::TWO ? 2 : 1)
         }
 #pragma unroll
         for (int i = 0; i < 32; ++i) rs += pr[i];
+        if (DROP) {  // the row sum counts every probability; what reaches P V is the kept part (scaled at the end)
+          float mk[32];
+          drop_mask32(drng, drow, kv0 + ch * 32, p.drop_thr8, 1.f, mk);
+#pragma unroll
+          for (int i = 0; i < 32; ++i) pr[i] *= mk[i];
+        }
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
           uint4 u;
@@ -350,7 +378,7 @@ __global__ void __launch_bounds__(FA_THREADS, FaFwdCfg<D>::TWO ? 2 : 1)
           for (int i = 0; i < 32; ++i) o_acc[ch * 32 + i] = fmaf(o_acc[ch * 32 + i], alpha_prev, __uint_as_float(v[i]));
         }
         if (t < p.T) {
-          const float inv = l > 0.f ? 1.f / l : 0.f;
+          const float inv = l > 0.f ? (DROP ? p.keep_scale : 1.f) / l : 0.f;
           __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(p.O) + ((long)t * p.Hq + h) * D;
 #pragma unroll
           for (int g = 0; g < D / 8; ++g) {
@@ -406,7 +434,7 @@ __global__ void fa_bwd_delta_kernel(const __nv_bfloat16* __restrict__ O, const _
 //   ->  dV += P^T dO, dK += dS^T Q, reading the same tiles as MN-major A operands; both accumulate in TMEM
 //   (lanes = keys) over the whole loop.  With more than one split the results are written as fp32 partials
 //   and summed in a fixed order by fa_bwd_reduce_kernel.
-template <int D>
+template <int D, bool DROP>
 __global__ void __launch_bounds__(FA_BWD_THREADS, 1)
     fa_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                        const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
@@ -548,6 +576,8 @@ __global__ void __launch_bounds__(FA_BWD_THREADS, 1)
     const int r = quad * 32 + lane;  // query row inside the tile while computing P / dS, key row in the epilogue
     const uint32_t t_lane = tmem_base + ((uint32_t)(quad * 32) << 16);
     const float sl2 = p.scale_log2, sc = p.scale;
+    sb::DropoutRng drng = {};
+    if (DROP) drng = sb::dropout_rng(p.rng, p.drop_call);
     bool ok = true;
     for (int it = 0; it < n_iter && ok; ++it) {
       const int h = hk * group + h_begin + it / n_qt;
@@ -567,7 +597,18 @@ __global__ void __launch_bounds__(FA_BWD_THREADS, 1)
         sb::tmem_ld32(t_lane + DP_COL + ch * 32, dp);
         sb::tmem_ld_wait();
         float pv[32], dsv[32];
-        if (interior) {
+        if (DROP) {
+          // P V used the kept probabilities times keep_scale: dV takes the same, and dP = dO V^T passes the mask
+          float mk[32];
+          drop_mask32(drng, (p.drop_head0 + (uint32_t)h) * (uint32_t)p.T + (uint32_t)t, kv0 + ch * 32, p.drop_thr8, p.keep_scale, mk);
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const int kidx = kv0 + ch * 32 + i;
+            const float pr = (kidx >= lo && kidx <= hi) ? fast_exp2(fmaf(__uint_as_float(s[i]), sl2, -lse)) : 0.f;
+            pv[i] = pr * mk[i];
+            dsv[i] = pr * fmaf(__uint_as_float(dp[i]) * mk[i], sc, -dls);
+          }
+        } else if (interior) {
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
             const float pr = fast_exp2(fmaf(__uint_as_float(s[i]), sl2, -lse));
@@ -694,7 +735,7 @@ __global__ void fa_bwd_reduce_kernel(const float* __restrict__ partial, __nv_bfl
 
 // ============================================================================ backward: dQ
 // CTA = (query tile, head).  Per key tile: S = Q K^T, dP = dO V^T -> threads: dS (bf16) -> dQ += dS K
-template <int D>
+template <int D, bool DROP>
 __global__ void __launch_bounds__(FA_BWD_THREADS, 1)
     fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                      const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
@@ -820,6 +861,9 @@ __global__ void __launch_bounds__(FA_BWD_THREADS, 1)
     const float lse = t < p.T ? p.lse2[(long)h * p.T + t] : 0.f;
     const float dls = (t < p.T ? p.delta[(long)h * p.T + t] : 0.f) * sc;
     const uint32_t t_lane = tmem_base + ((uint32_t)(quad * 32) << 16);
+    sb::DropoutRng drng = {};
+    if (DROP) drng = sb::dropout_rng(p.rng, p.drop_call);
+    const uint32_t drow = (p.drop_head0 + (uint32_t)h) * (uint32_t)p.T + (uint32_t)t;
     bool ok = true;
     for (int j = 0; j < n_tiles && ok; ++j) {
       const int kv0 = (kv_begin + j) * TILE;
@@ -833,7 +877,16 @@ __global__ void __launch_bounds__(FA_BWD_THREADS, 1)
         sb::tmem_ld32(t_lane + DP_COL + ch * 32, dp);
         sb::tmem_ld_wait();
         float dsv[32];
-        if (interior) {
+        if (DROP) {
+          float mk[32];
+          drop_mask32(drng, drow, kv0 + ch * 32, p.drop_thr8, p.keep_scale, mk);
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const int kidx = kv0 + ch * 32 + i;
+            const float pr = (kidx >= lo && kidx <= hi) ? fast_exp2(fmaf(__uint_as_float(s[i]), sl2, -lse)) : 0.f;
+            dsv[i] = pr * fmaf(__uint_as_float(dp[i]) * mk[i], sc, -dls);
+          }
+        } else if (interior) {
 #pragma unroll
           for (int i = 0; i < 32; ++i)
             dsv[i] = fast_exp2(fmaf(__uint_as_float(s[i]), sl2, -lse)) * fmaf(__uint_as_float(dp[i]), sc, -dls);
@@ -937,15 +990,65 @@ template <int D> constexpr int fa_dq_smem() { return (D / 64) * PANEL_BYTES * 6 
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
+// dropout probability -> threshold on a random byte and the factor of the kept probabilities; p is quantised to 1/256
+int fa_dropout(FaParams* p, float dropout_p, const long long* rng, unsigned call, int head0) {
+  p->rng = nullptr; p->drop_call = 0; p->drop_thr8 = 0; p->keep_scale = 1.f; p->drop_head0 = (uint32_t)head0;
+  if (dropout_p <= 0.f) return SB_OK;
+  if (dropout_p >= 1.f || !rng) return SB_ERR_BAD_ARG;
+  int thr = (int)(dropout_p * 256.f + 0.5f);
+  if (thr < 1) thr = 1;
+  if (thr > 255) thr = 255;
+  p->rng = rng; p->drop_call = call; p->drop_thr8 = (uint32_t)thr;
+  p->keep_scale = 256.f / (float)(256 - thr);
+  return SB_OK;
+}
+
+template <int D, bool DROP>
+int fa_launch_fwd(dim3 grid, const CUtensorMap& tmQ, const CUtensorMap& tmK, const CUtensorMap& tmV, const FaParams& p,
+                  cudaStream_t stream) {
+  static bool set = false;
+  if (!set) {
+    cudaError_t e = cudaFuncSetAttribute(fa_fwd_kernel<D, DROP>, cudaFuncAttributeMaxDynamicSharedMemorySize, fa_fwd_smem<D>());
+    if (e != cudaSuccess) return (int)e;
+    set = true;
+  }
+  fa_fwd_kernel<D, DROP><<<grid, FA_THREADS, fa_fwd_smem<D>(), stream>>>(tmQ, tmK, tmV, p);
+  SB_CHECK_LAUNCH();
+  return SB_OK;
+}
+
+template <int D, bool DROP>
+int fa_launch_bwd(int tiles, int splits, int hps, const CUtensorMap& tmQ, const CUtensorMap& tmK, const CUtensorMap& tmV,
+                  const CUtensorMap& tmdO, const FaParams& p, float* dk_part, float* dv_part, cudaStream_t stream) {
+  static bool set = false;
+  if (!set) {
+    cudaError_t e = cudaFuncSetAttribute(fa_bwd_dkdv_kernel<D, DROP>, cudaFuncAttributeMaxDynamicSharedMemorySize, fa_dkdv_smem<D>());
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(fa_bwd_dq_kernel<D, DROP>, cudaFuncAttributeMaxDynamicSharedMemorySize, fa_dq_smem<D>());
+    if (e != cudaSuccess) return (int)e;
+    set = true;
+  }
+  fa_bwd_dkdv_kernel<D, DROP><<<dim3(tiles, p.Hkv, splits), FA_BWD_THREADS, fa_dkdv_smem<D>(), stream>>>(
+      tmQ, tmK, tmV, tmdO, p, tiles, hps, dk_part, dv_part);
+  SB_CHECK_LAUNCH();
+  fa_bwd_dq_kernel<D, DROP><<<dim3(tiles, p.Hq), FA_BWD_THREADS, fa_dq_smem<D>(), stream>>>(tmQ, tmK, tmV, tmdO, p);
+  SB_CHECK_LAUNCH();
+  return SB_OK;
+}
+
 }  // namespace
 
 // CUresult of the last failed tensor-map encode of the attention entry points (0 if none failed)
 SB_API int sb200_fa_last_driver_error() { return g_fa_last_driver_error; }
 
 // q: [T, Hq, D] view with token pitch ldq_tok and head pitch ldq_head (elements); k, v likewise; o: [T, Hq, D] contiguous.
+// dropout_p > 0 drops attention probabilities (quantised to a multiple of 1/256): rng = device int64[2] {seed, step},
+// call = index of this attention inside the step, head0 = index of head 0 among the heads of the whole layer; the
+// backward pass is given the same values.
 SB_API int sb200_fa_fwd(const void* q, const void* k, const void* v, void* o, float* lse2, const int* doc_start,
                         const int* doc_end, int T, int Hq, int Hkv, int D, long ldq_tok, int ldq_head, long ldk_tok,
-                        int ldk_head, long ldv_tok, int ldv_head, int causal, int window, float scale, int* status,
+                        int ldk_head, long ldv_tok, int ldv_head, int causal, int window, float scale,
+                        float dropout_p, const long long* rng, unsigned int call, int head0, int* status,
                         cudaStream_t stream) {
   if (T <= 0 || Hq <= 0) return SB_OK;
   if ((D != 64 && D != 128) || Hkv <= 0 || Hq % Hkv) return SB_ERR_BAD_ARG;
@@ -963,26 +1066,12 @@ SB_API int sb200_fa_fwd(const void* q, const void* k, const void* v, void* o, fl
   p.doc_start = doc_start; p.doc_end = doc_end;
   p.ldq_head = ldq_head; p.ldk_head = ldk_head; p.ldv_head = ldv_head;
   p.O = o; p.lse2 = lse2; p.status = status;
+  if ((rc = fa_dropout(&p, dropout_p, rng, call, head0))) return rc;
   dim3 grid((T + TILE - 1) / TILE, Hq);
-  if (D == 64) {
-    static bool set = false;
-    if (!set) {
-      cudaError_t e = cudaFuncSetAttribute(fa_fwd_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, fa_fwd_smem<64>());
-      if (e != cudaSuccess) return (int)e;
-      set = true;
-    }
-    fa_fwd_kernel<64><<<grid, FA_THREADS, fa_fwd_smem<64>(), stream>>>(tmQ, tmK, tmV, p);
-  } else {
-    static bool set = false;
-    if (!set) {
-      cudaError_t e = cudaFuncSetAttribute(fa_fwd_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, fa_fwd_smem<128>());
-      if (e != cudaSuccess) return (int)e;
-      set = true;
-    }
-    fa_fwd_kernel<128><<<grid, FA_THREADS, fa_fwd_smem<128>(), stream>>>(tmQ, tmK, tmV, p);
-  }
-  SB_CHECK_LAUNCH();
-  return SB_OK;
+  if (D == 64) return p.drop_thr8 ? fa_launch_fwd<64, true>(grid, tmQ, tmK, tmV, p, stream)
+                                  : fa_launch_fwd<64, false>(grid, tmQ, tmK, tmV, p, stream);
+  return p.drop_thr8 ? fa_launch_fwd<128, true>(grid, tmQ, tmK, tmV, p, stream)
+                     : fa_launch_fwd<128, false>(grid, tmQ, tmK, tmV, p, stream);
 }
 
 // Number of splits of the query-head group the dK/dV kernel uses for this problem (1 = results written directly).
@@ -1008,7 +1097,8 @@ SB_API int sb200_fa_bwd_strided(const void* q, const void* k, const void* v, con
                                 void* dv, const int* doc_start, const int* doc_end, int T, int Hq, int Hkv, int D,
                                 long ldq_tok, int ldq_head, long ldk_tok, int ldk_head, long ldv_tok, int ldv_head,
                                 long lddq_tok, int lddq_head, long lddk_tok, int lddk_head, long lddv_tok,
-                                int lddv_head, int causal, int window, float scale, int* status,
+                                int lddv_head, int causal, int window, float scale, float dropout_p,
+                                const long long* rng, unsigned int call, int head0, int* status,
                                 cudaStream_t stream) {
   if ((lddq_tok | lddq_head | lddk_tok | lddk_head | lddv_tok | lddv_head) & 7) return SB_ERR_BAD_ARG;
   if (T <= 0 || Hq <= 0) return SB_OK;
@@ -1046,34 +1136,14 @@ SB_API int sb200_fa_bwd_strided(const void* q, const void* k, const void* v, con
       fa_bwd_delta_kernel<128><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)o, (const __nv_bfloat16*)d_o, delta, T, Hq);
     SB_CHECK_LAUNCH();
   }
-  if (D == 64) {
-    static bool set = false;
-    if (!set) {
-      cudaError_t e = cudaFuncSetAttribute(fa_bwd_dkdv_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, fa_dkdv_smem<64>());
-      if (e == cudaSuccess)
-        e = cudaFuncSetAttribute(fa_bwd_dq_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, fa_dq_smem<64>());
-      if (e != cudaSuccess) return (int)e;
-      set = true;
-    }
-    fa_bwd_dkdv_kernel<64><<<dim3(tiles, Hkv, splits), FA_BWD_THREADS, fa_dkdv_smem<64>(), stream>>>(
-        tmQ, tmK, tmV, tmdO, p, tiles, hps, dk_part, dv_part);
-    SB_CHECK_LAUNCH();
-    fa_bwd_dq_kernel<64><<<dim3(tiles, Hq), FA_BWD_THREADS, fa_dq_smem<64>(), stream>>>(tmQ, tmK, tmV, tmdO, p);
-  } else {
-    static bool set = false;
-    if (!set) {
-      cudaError_t e = cudaFuncSetAttribute(fa_bwd_dkdv_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, fa_dkdv_smem<128>());
-      if (e == cudaSuccess)
-        e = cudaFuncSetAttribute(fa_bwd_dq_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, fa_dq_smem<128>());
-      if (e != cudaSuccess) return (int)e;
-      set = true;
-    }
-    fa_bwd_dkdv_kernel<128><<<dim3(tiles, Hkv, splits), FA_BWD_THREADS, fa_dkdv_smem<128>(), stream>>>(
-        tmQ, tmK, tmV, tmdO, p, tiles, hps, dk_part, dv_part);
-    SB_CHECK_LAUNCH();
-    fa_bwd_dq_kernel<128><<<dim3(tiles, Hq), FA_BWD_THREADS, fa_dq_smem<128>(), stream>>>(tmQ, tmK, tmV, tmdO, p);
-  }
-  SB_CHECK_LAUNCH();
+  if ((rc = fa_dropout(&p, dropout_p, rng, call, head0))) return rc;
+  if (D == 64)
+    rc = p.drop_thr8 ? fa_launch_bwd<64, true>(tiles, splits, hps, tmQ, tmK, tmV, tmdO, p, dk_part, dv_part, stream)
+                     : fa_launch_bwd<64, false>(tiles, splits, hps, tmQ, tmK, tmV, tmdO, p, dk_part, dv_part, stream);
+  else
+    rc = p.drop_thr8 ? fa_launch_bwd<128, true>(tiles, splits, hps, tmQ, tmK, tmV, tmdO, p, dk_part, dv_part, stream)
+                     : fa_launch_bwd<128, false>(tiles, splits, hps, tmQ, tmK, tmV, tmdO, p, dk_part, dv_part, stream);
+  if (rc) return rc;
   if (splits > 1) {
     const long n = (long)T * Hkv * D;
     const int blocks = (int)((n / 4 + 255) / 256);
@@ -1091,8 +1161,10 @@ SB_API int sb200_fa_bwd(const void* q, const void* k, const void* v, const void*
                         float* delta, float* dkv_partial, int splits, void* dq, void* dk, void* dv,
                         const int* doc_start, const int* doc_end, int T,
                         int Hq, int Hkv, int D, long ldq_tok, int ldq_head, long ldk_tok, int ldk_head, long ldv_tok,
-                        int ldv_head, int causal, int window, float scale, int* status, cudaStream_t stream) {
+                        int ldv_head, int causal, int window, float scale, float dropout_p, const long long* rng,
+                        unsigned int call, int head0, int* status, cudaStream_t stream) {
   return sb200_fa_bwd_strided(q, k, v, o, d_o, lse2, delta, dkv_partial, splits, dq, dk, dv, doc_start, doc_end, T, Hq,
                               Hkv, D, ldq_tok, ldq_head, ldk_tok, ldk_head, ldv_tok, ldv_head, (long)Hq * D, D,
-                              (long)Hkv * D, D, (long)Hkv * D, D, causal, window, scale, status, stream);
+                              (long)Hkv * D, D, (long)Hkv * D, D, causal, window, scale, dropout_p, rng, call, head0,
+                              status, stream);
 }

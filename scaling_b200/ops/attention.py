@@ -48,8 +48,10 @@ def attention_mask_from_cu_seqlens(cu_q: torch.Tensor, cu_k: torch.Tensor, tq: i
 
 def attention_reference(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_q: torch.Tensor,
                         cu_k: Optional[torch.Tensor], causal: bool, scale: float,
-                        window: Optional[int] = None, dropout_p: float = 0.0) -> torch.Tensor:
-    """Dense O(T^2) evaluation in fp32; returns ``[Tq, Hq, D]`` in the dtype of ``q``."""
+                        window: Optional[int] = None, dropout_p: float = 0.0,
+                        dropout_mask: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Dense O(T^2) evaluation in fp32; returns ``[Tq, Hq, D]`` in the dtype of ``q``.  ``dropout_mask``
+    (``[Hq, Tq, Tk]``, entries 0 or ``1 / (1 - p)``) replaces the random draw of ``dropout_p``."""
     cu_k = cu_q if cu_k is None else cu_k
     tq, hq, d = q.shape
     tk, hkv, _ = k.shape
@@ -62,7 +64,9 @@ def attention_reference(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_q:
     scores = scores.masked_fill(~allowed[None], float("-inf"))
     probs = torch.softmax(scores, dim=-1)
     probs = torch.nan_to_num(probs, nan=0.0)  # fully masked rows
-    if dropout_p > 0.0:
+    if dropout_mask is not None:
+        probs = probs * dropout_mask.to(probs.dtype)
+    elif dropout_p > 0.0:
         probs = torch.nn.functional.dropout(probs, dropout_p)
     out = torch.matmul(probs, vf)
     return out.transpose(0, 1).to(q.dtype)
@@ -94,13 +98,18 @@ def flash_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seqlen
                     cu_seqlens_k: Optional[torch.Tensor] = None, causal: bool = True,
                     scale: Optional[float] = None, window: Optional[int] = None,
                     dropout_p: float = 0.0,
-                    doc_ranges: Optional[tuple[torch.Tensor, torch.Tensor]] = None) -> torch.Tensor:
-    """``doc_ranges = (doc_start[T], doc_end[T])`` (int32) may replace ``cu_seqlens_q`` for self-attention."""
-    scale = 1.0 / math.sqrt(q.shape[-1]) if scale is None else scale
-    if dropout_p == 0.0 and kernel_supported(q, k, cu_seqlens_k):
-        from .attention_kernel import flash_attention_kernel
+                    doc_ranges: Optional[tuple[torch.Tensor, torch.Tensor]] = None,
+                    rng_state=None, head_offset: int = 0) -> torch.Tensor:
+    """``doc_ranges = (doc_start[T], doc_end[T])`` (int32) may replace ``cu_seqlens_q`` for self-attention.
 
-        return flash_attention_kernel(q, k, v, cu_seqlens_q, causal, scale, window, doc_ranges)
+    ``dropout_p > 0`` drops attention probabilities; inside the kernel when ``rng_state`` (the topology's
+    ``KernelDropoutState``) is given, where the mask is recomputed in the backward pass and costs no memory."""
+    scale = 1.0 / math.sqrt(q.shape[-1]) if scale is None else scale
+    if (dropout_p == 0.0 or rng_state is not None) and kernel_supported(q, k, cu_seqlens_k):
+        from .attention_kernel import dropout_args, flash_attention_kernel
+
+        return flash_attention_kernel(q, k, v, cu_seqlens_q, causal, scale, window, doc_ranges,
+                                      dropout_args(dropout_p, rng_state, head_offset))
     assert cu_seqlens_q is not None, "the dense attention path needs cumulative sequence lengths"
     if q.is_cuda and cu_seqlens_k is None and window is None:
         # head sizes the tcgen05 kernel does not cover: batched library attention over equal-length documents

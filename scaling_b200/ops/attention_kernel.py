@@ -2,7 +2,7 @@
 
 from __future__ import annotations
 
-from ctypes import c_float, c_int, c_long, c_void_p
+from ctypes import c_float, c_int, c_long, c_uint, c_void_p
 from typing import Optional
 
 import torch
@@ -18,13 +18,14 @@ def _declare() -> None:
     global _DECLARED
     if _DECLARED:
         return
+    drop = [c_float, c_void_p, c_uint, c_int]  # dropout probability, device {seed, step}, call index, first head
     _lib.declare("sb200_fa_fwd", [c_void_p] * 7 + [c_int] * 4 + [c_long, c_int, c_long, c_int, c_long, c_int, c_int,
-                                                                 c_int, c_float, c_void_p, c_void_p])
+                                                                 c_int, c_float] + drop + [c_void_p, c_void_p])
     _lib.declare("sb200_fa_bwd_splits", [c_int] * 4)
     _lib.declare("sb200_fa_bwd", [c_void_p] * 8 + [c_int] + [c_void_p] * 5 + [c_int] * 4 + [c_long, c_int, c_long, c_int, c_long, c_int, c_int,
-                                                                  c_int, c_float, c_void_p, c_void_p])
+                                                                  c_int, c_float] + drop + [c_void_p, c_void_p])
     _lib.declare("sb200_fa_bwd_strided", [c_void_p] * 8 + [c_int] + [c_void_p] * 5 + [c_int] * 4
-                 + [c_long, c_int] * 6 + [c_int, c_int, c_float, c_void_p, c_void_p])
+                 + [c_long, c_int] * 6 + [c_int, c_int, c_float] + drop + [c_void_p, c_void_p])
     _lib.declare("sb200_rope_multi", [c_void_p, c_void_p, c_int, c_int, c_int, c_long, c_long, c_int, c_long, c_float,
                                       c_int, c_int, c_int, c_void_p])
     _DECLARED = True
@@ -65,9 +66,10 @@ def _prep(t: torch.Tensor) -> torch.Tensor:
 
 class _FlashAttention(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, q, k, v, doc_start, doc_end, causal, scale, window):  # type: ignore[override]
+    def forward(ctx, q, k, v, doc_start, doc_end, causal, scale, window, drop):  # type: ignore[override]
         _declare()
         q, k, v = _prep(q), _prep(k), _prep(v)
+        dp, drng, dcall, dhead = drop
         T, Hq, D = q.shape
         Hkv = k.shape[1]
         o = torch.empty((T, Hq, D), dtype=q.dtype, device=q.device)
@@ -76,17 +78,18 @@ class _FlashAttention(torch.autograd.Function):
             lib().sb200_fa_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse2.data_ptr(),
                                doc_start.data_ptr(), doc_end.data_ptr(), T, Hq, Hkv, D, q.stride(0), q.stride(1),
                                k.stride(0), k.stride(1), v.stride(0), v.stride(1), int(causal),
-                               -1 if window is None else int(window), float(scale), status_word().data_ptr(), stream()),
+                               -1 if window is None else int(window), float(scale), dp, _lib.ptr(drng), dcall, dhead,
+                               status_word().data_ptr(), stream()),
             "sb200_fa_fwd",
         )
         ctx.save_for_backward(q, k, v, o, lse2, doc_start, doc_end)
-        ctx.cfg = (causal, scale, window)
+        ctx.cfg = (causal, scale, window, drop)
         return o
 
     @staticmethod
     def backward(ctx, do):  # type: ignore[override]
         q, k, v, o, lse2, doc_start, doc_end = ctx.saved_tensors
-        causal, scale, window = ctx.cfg
+        causal, scale, window, (dp, drng, dcall, dhead) = ctx.cfg
         T, Hq, D = q.shape
         Hkv = k.shape[1]
         do = do.contiguous()
@@ -104,23 +107,56 @@ class _FlashAttention(torch.autograd.Function):
                                dv.data_ptr(), doc_start.data_ptr(),
                                doc_end.data_ptr(), T, Hq, Hkv, D, q.stride(0), q.stride(1), k.stride(0), k.stride(1),
                                v.stride(0), v.stride(1), int(causal), -1 if window is None else int(window),
-                               float(scale), status_word().data_ptr(), stream()),
+                               float(scale), dp, _lib.ptr(drng), dcall, dhead, status_word().data_ptr(), stream()),
             "sb200_fa_bwd",
         )
-        return dq, dk, dv, None, None, None, None, None
+        return dq, dk, dv, None, None, None, None, None, None
+
+
+NO_DROPOUT = (0.0, None, 0, 0)
+
+
+def dropout_args(dropout_p: float, rng_state, head_offset: int = 0) -> tuple:
+    """(probability, device {seed, step}, call index, first head) for one attention call; draws the next call index
+    of the ``KernelDropoutState``.  ``head_offset`` is the index of this rank's first head among all heads of the layer
+    (tensor-parallel ranks share seed and call index and differ in their heads).  The kernels quantise the
+    probability to a multiple of 1/256."""
+    if dropout_p <= 0.0:
+        return NO_DROPOUT
+    assert rng_state is not None, "attention dropout in the kernel needs the topology's KernelDropoutState"
+    return (float(dropout_p), rng_state.tensor(), rng_state.next_call(), int(head_offset))
 
 
 def flash_attention_kernel(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seqlens: Optional[torch.Tensor],
                            causal: bool, scale: float, window: Optional[int],
-                           ranges: Optional[tuple[torch.Tensor, torch.Tensor]] = None) -> torch.Tensor:
+                           ranges: Optional[tuple[torch.Tensor, torch.Tensor]] = None,
+                           drop: tuple = NO_DROPOUT) -> torch.Tensor:
     if q.dtype != torch.bfloat16:
         # the kernels are bf16; fp16 inputs are converted (same exponent-safe range for attention inputs)
         out = flash_attention_kernel(q.to(torch.bfloat16), k.to(torch.bfloat16), v.to(torch.bfloat16), cu_seqlens,
-                                     causal, scale, window, ranges)
+                                     causal, scale, window, ranges, drop)
         return out.to(q.dtype)
     start, end = ranges if ranges is not None else doc_ranges(cu_seqlens, q.shape[0])
     _check_ranges(start, end, q.shape[0])
-    return _FlashAttention.apply(q, k, v, start, end, causal, scale, window)
+    return _FlashAttention.apply(q, k, v, start, end, causal, scale, window, drop)
+
+
+def attention_dropout_mask(T: int, heads: int, dropout_p: float, rng_state, call: int) -> torch.Tensor:
+    """The mask ``[heads, T, T]`` (0 or ``1 / (1 - p)`` with p quantised to 1/256) that the attention kernels apply
+    for the given call index at the state's current step, obtained by running the forward kernel on inputs that make
+    every allowed probability equal (q = 0) and reading the result through one-hot values; for tests."""
+    dev = rng_state.device
+    out = torch.zeros((heads, T, T), dtype=torch.float32, device=dev)
+    q = torch.zeros((T, heads, 64), dtype=torch.bfloat16, device=dev)
+    start = torch.zeros(T, dtype=torch.int32, device=dev)
+    end = torch.full((T,), T, dtype=torch.int32, device=dev)
+    for c0 in range(0, T, 64):  # 64 one-hot value columns at a time: o[t, h, j] = mask[h, t, c0 + j] / T
+        v = torch.zeros((T, heads, 64), dtype=torch.bfloat16, device=dev)
+        n = min(64, T - c0)
+        v[torch.arange(c0, c0 + n, device=dev), :, torch.arange(n, device=dev)] = 1.0
+        o = _FlashAttention.apply(q, q, v, start, end, False, 1.0, None, (float(dropout_p), rng_state.tensor(), call, 0))
+        out[:, :, c0:c0 + n] = (o.float() * T).permute(1, 0, 2)[:, :, :n]
+    return out
 
 
 class _PackedQKVAttention(torch.autograd.Function):
@@ -133,8 +169,9 @@ class _PackedQKVAttention(torch.autograd.Function):
     """
 
     @staticmethod
-    def forward(ctx, qkv, pos, rot, doc_start, doc_end, causal, scale, window):  # type: ignore[override]
+    def forward(ctx, qkv, pos, rot, doc_start, doc_end, causal, scale, window, drop):  # type: ignore[override]
         _declare()
+        dp, drng, dcall, dhead = drop
         T, H, D3 = qkv.shape
         D = D3 // 3
         assert qkv.is_contiguous() and qkv.dtype == torch.bfloat16
@@ -148,18 +185,18 @@ class _PackedQKVAttention(torch.autograd.Function):
         check(
             lib().sb200_fa_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse2.data_ptr(),
                                doc_start.data_ptr(), doc_end.data_ptr(), T, H, H, D, H * D3, D3, H * D3, D3, H * D3, D3,
-                               int(causal), -1 if window is None else int(window), float(scale),
-                               status_word().data_ptr(), stream()),
+                               int(causal), -1 if window is None else int(window), float(scale), dp, _lib.ptr(drng),
+                               dcall, dhead, status_word().data_ptr(), stream()),
             "sb200_fa_fwd",
         )
         ctx.save_for_backward(qkv, o, lse2, doc_start, doc_end, pos if rot is not None else None)
-        ctx.cfg = (causal, scale, window, rot)
+        ctx.cfg = (causal, scale, window, rot, drop)
         return o
 
     @staticmethod
     def backward(ctx, do):  # type: ignore[override]
         qkv, o, lse2, doc_start, doc_end, pos = ctx.saved_tensors
-        causal, scale, window, rot = ctx.cfg
+        causal, scale, window, rot, (dp, drng, dcall, dhead) = ctx.cfg
         T, H, D3 = qkv.shape
         D = D3 // 3
         do = do.contiguous()
@@ -177,15 +214,15 @@ class _PackedQKVAttention(torch.autograd.Function):
                                        lse2.data_ptr(), delta.data_ptr(), _lib.ptr(partial), splits, dq.data_ptr(),
                                        dk.data_ptr(), dv.data_ptr(), doc_start.data_ptr(), doc_end.data_ptr(), T, H, H,
                                        D, *ld, *ld, *ld, *ld, *ld, *ld, int(causal),
-                                       -1 if window is None else int(window), float(scale),
-                                       status_word().data_ptr(), stream()),
+                                       -1 if window is None else int(window), float(scale), dp, _lib.ptr(drng),
+                                       dcall, dhead, status_word().data_ptr(), stream()),
             "sb200_fa_bwd_strided",
         )
         if rot is not None:
             rot_dim, base, interleaved = rot
             check(lib().sb200_rope_multi(dqkv.data_ptr(), pos.data_ptr(), T, H, rot_dim, H * D3, D3, 2, D, float(base),
                                          int(interleaved), 1, _lib.dt(dqkv.dtype), stream()), "sb200_rope_multi")
-        return dqkv, None, None, None, None, None, None, None
+        return dqkv, None, None, None, None, None, None, None, None
 
 
 def packed_qkv_supported(qkv: torch.Tensor) -> bool:
@@ -197,7 +234,8 @@ def packed_qkv_supported(qkv: torch.Tensor) -> bool:
 def packed_qkv_attention(qkv: torch.Tensor, positions: Optional[torch.Tensor],
                          rotary: Optional[tuple[int, float, bool]], cu_seqlens: Optional[torch.Tensor], causal: bool,
                          scale: float, window: Optional[int],
-                         ranges: Optional[tuple[torch.Tensor, torch.Tensor]] = None) -> torch.Tensor:
+                         ranges: Optional[tuple[torch.Tensor, torch.Tensor]] = None,
+                         drop: tuple = NO_DROPOUT) -> torch.Tensor:
     """Rotary embedding + self-attention on a packed projection; returns ``[T, heads, d]``.
 
     ``rotary = (rotary dimensions, base, interleaved)`` or None; ``positions`` is ``[T]``.  ``qkv`` is overwritten
@@ -210,4 +248,4 @@ def packed_qkv_attention(qkv: torch.Tensor, positions: Optional[torch.Tensor],
         assert positions is not None
         pos = positions if positions.dtype == torch.int32 else positions.to(torch.int32)
         pos = pos.contiguous()
-    return _PackedQKVAttention.apply(qkv, pos, rotary, start, end, causal, scale, window)
+    return _PackedQKVAttention.apply(qkv, pos, rotary, start, end, causal, scale, window, drop)

@@ -532,9 +532,78 @@ def masked_softmax(x: torch.Tensor, mask: Optional[torch.Tensor], scale: float =
     return p.to(in_dtype)
 
 
-# --------------------------------------------------------------------------- add
-def add(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
-    return a + b
+# --------------------------------------------------------------------------- dropout + residual
+def _launch_dropout_add(x: torch.Tensor, r: Optional[torch.Tensor], y: torch.Tensor, p: float, x_scale: float,
+                        r_scale: float, rng: Optional[torch.Tensor], call: int, elem_offset: int, backward: bool) -> None:
+    check(lib().sb200_dropout_add(x.data_ptr(), ptr(r), y.data_ptr(), x.numel(), p, x_scale, r_scale, ptr(rng), call,
+                                  elem_offset, int(backward), dt(x.dtype), stream()), "sb200_dropout_add")
+
+
+class _DropoutAddFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, residual, p, x_scale, r_scale, rng, call, elem_offset, scale_grad):  # type: ignore[override]
+        xc = x.contiguous()
+        rc = None if residual is None else residual.contiguous()
+        y = torch.empty_like(xc)
+        _launch_dropout_add(xc, rc, y, p, x_scale, r_scale, rng, call, elem_offset, False)
+        # scale_grad False: the scales act on the forward values only (unit-scaling's scale_fwd)
+        ctx.args = (p, x_scale if scale_grad else 1.0, r_scale if scale_grad else 1.0, rng, call, elem_offset)
+        ctx.has_residual = residual is not None
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):  # type: ignore[override]
+        p, x_scale, r_scale, rng, call, elem_offset = ctx.args
+        dyc = dy.contiguous()
+        dx = dr = None
+        if ctx.needs_input_grad[0]:
+            if p == 0.0:
+                dx = dyc if x_scale == 1.0 else dyc * x_scale
+            else:
+                dx = torch.empty_like(dyc)
+                _launch_dropout_add(dyc, None, dx, p, x_scale, 0.0, rng, call, elem_offset, True)
+        if ctx.has_residual and ctx.needs_input_grad[1]:
+            dr = dyc if r_scale == 1.0 else dyc * r_scale
+        return dx, dr, None, None, None, None, None, None, None
+
+
+def dropout_add(x: torch.Tensor, residual: Optional[torch.Tensor], p: float, rng_state=None, training: bool = True,
+                x_scale: float = 1.0, r_scale: float = 1.0, elem_offset: int = 0,
+                scale_grad: bool = True) -> torch.Tensor:
+    """``dropout(x, p) * x_scale + residual * r_scale`` in one pass (``residual`` may be None: plain dropout).
+
+    ``rng_state`` is the ``KernelDropoutState`` of the topology: the mask depends on its seed and step (read on the
+    device), on the index of this call inside the step and on the element's index ``elem_offset + i``, and is
+    recomputed, not stored, for the backward pass.  On CPU tensors the torch expression is used."""
+    p = float(p) if training else 0.0
+    if p == 0.0 and residual is None:
+        return x if x_scale == 1.0 else x * x_scale
+    kernel = (x.is_cuda and x.dtype in _KERNEL_DTYPES and x.data_ptr() % 16 == 0 and elem_offset % 4 == 0
+              and (residual is None or (residual.dtype == x.dtype and residual.shape == x.shape)))
+    if kernel and p > 0.0 and rng_state is None:
+        kernel = False
+    if not kernel:
+        from ..core.nn.scale import scale_fwd
+
+        mul = (lambda t, s_: t * s_) if scale_grad else scale_fwd
+        y = torch.nn.functional.dropout(x, p, training=True) if p > 0.0 else x
+        if x_scale != 1.0:
+            y = mul(y, x_scale)
+        if residual is None:
+            return y
+        return y + (residual if r_scale == 1.0 else mul(residual, r_scale))
+    rng, call = (rng_state.tensor(), rng_state.next_call()) if p > 0.0 else (None, 0)
+    return _DropoutAddFn.apply(x, residual, p, float(x_scale), float(r_scale), rng, call, int(elem_offset), scale_grad)
+
+
+def dropout_mask(shape: tuple, p: float, rng_state, call: int, dtype: torch.dtype = torch.float32,
+                 elem_offset: int = 0) -> torch.Tensor:
+    """The mask (values 0 or ``1 / (1 - p)``) that ``dropout_add`` applies for the given call index at the state's
+    current step; for tests and debugging."""
+    ones = torch.ones(shape, dtype=dtype, device=rng_state.device)
+    out = torch.empty_like(ones)
+    _launch_dropout_add(ones, None, out, p, 1.0, 0.0, rng_state.tensor(), call, elem_offset, False)
+    return out
 
 
 # --------------------------------------------------------------------------- embedding

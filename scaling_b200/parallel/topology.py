@@ -18,7 +18,7 @@ import numpy as np
 import torch
 import torch.distributed as dist
 
-from .rng_tracker import CudaRNGStateTracker, RngTrackerState
+from .rng_tracker import CudaRNGStateTracker, KernelDropoutState, RngTrackerState
 from .topology_config import TopologyConfig
 
 
@@ -52,6 +52,7 @@ class Topology:
         )
         self._pipe_group = self._data_group = self._model_group = None
         self._rng: Optional[CudaRNGStateTracker] = None
+        self._kernel_rng: Optional[KernelDropoutState] = None
         self.is_distributed_initialized = False
         self._device: Optional[torch.device] = None
 
@@ -102,6 +103,7 @@ class Topology:
         # same seed on all model-parallel ranks of one (pipe, data) cell
         cell_seed = seed + self.get_global_rank(model_parallel_rank=0)
         self._rng = CudaRNGStateTracker(cell_seed, device=self.device)
+        self._kernel_rng = KernelDropoutState(cell_seed, self.device)
         if not dist.is_initialized():
             addr = master_addr or os.environ.get("MASTER_ADDR", "127.0.0.1")
             port = master_port or os.environ.get("MASTER_PORT", "29500")
@@ -179,15 +181,25 @@ class Topology:
         assert self._rng is not None, "topology is not initialized"
         return self._rng.fork
 
+    @property
+    def kernel_rng(self) -> KernelDropoutState:
+        """Counter-based random stream of the dropout kernels; the same on all tensor-parallel ranks of a replica."""
+        if self._kernel_rng is None:  # single process without torch.distributed
+            self._kernel_rng = KernelDropoutState(42 + (self.config.global_rank or 0), self.device)
+        return self._kernel_rng
+
     def state_dict(self) -> Optional[TopologyState]:
         if self._rng is None:
             return None
-        return {"model_parallel_constant_rng": self._rng.state_dict()}
+        return {"model_parallel_constant_rng": self._rng.state_dict(),  # type: ignore[typeddict-unknown-key]
+                "kernel_rng": self.kernel_rng.state_dict()}
 
     def load_state_dict(self, state_dict: Optional[dict[str, Any]]) -> None:
         if state_dict is None or self._rng is None:
             return
         self._rng.load_state_dict(state_dict["model_parallel_constant_rng"])
+        if "kernel_rng" in state_dict:
+            self.kernel_rng.load_state_dict(state_dict["kernel_rng"])
 
     # ------------------------------------------------------------------ coordinates
     def _need_rank(self) -> None:

@@ -14,6 +14,7 @@ import torch
 
 from ....core.nn.linear import VocabParallelEmbedding
 from ....core.nn.parallel_module import BaseLayer
+from ....ops import functional as K
 from ....parallel.topology import Topology
 from ...context.config import TransformerArchitectureConfig
 from ...data.text_dataset_batch import TextDatasetBatch
@@ -55,6 +56,7 @@ class BaseEmbeddingInput(BaseLayer[TextDatasetBatch, TransformerLayerIO, Transfo
             finetunable_token_ids=architecture_config.finetunable_token_ids,
         )
         self.dropout = torch.nn.Dropout(p=architecture_config.dropout_embedding)
+        self.dropout.kernel_dropout = True  # applied by the dropout kernel on the GPU
         if architecture_config.image_encoder:
             from ..image_encoder import ImageEncoder
 
@@ -90,8 +92,13 @@ class BaseEmbeddingInput(BaseLayer[TextDatasetBatch, TransformerLayerIO, Transfo
         # embedding then stays replicated until they are in, and is split over the ranks afterwards
         splice_full = sequence_parallel and (x.input_images is not None or self.softprompt_name is not None)
         h = self.embedding(x.input_token_ids, scatter_tokens=not splice_full)
-        if self.dropout.p > 0.0:
-            h = self._dropout(self.dropout, h)
+        if self.dropout.p > 0.0 and self.training:
+            if h.is_cuda and t is not None:  # counter-based mask from the topology's stream, one kernel
+                sharded = sequence_parallel and not splice_full
+                offset = t.model_parallel_rank * ((h.numel() + 3) // 4 * 4) if sharded else 0
+                h = K.dropout_add(h, None, self.dropout.p, t.kernel_rng, True, elem_offset=offset)
+            else:
+                h = self._dropout(self.dropout, h)
 
         if x.input_images is not None:
             img = self._dropout(self.image_encoder, x.input_images)

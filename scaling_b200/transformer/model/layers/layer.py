@@ -17,6 +17,7 @@ from ....core.nn.norm import get_norm
 from ....core.nn.residual import NormedResidualAdd, NormedResidualSplit
 from ....core.nn.rotary import RotaryConfig
 from ....core.nn.umup import UMuParametrization
+from ....ops import functional as K
 from ....parallel.topology import Topology
 from ...context.config import MLPType, TransformerArchitectureConfig
 from .base import TransformerLayerBaseIO, TransformerLayerIO, record_embedding
@@ -64,6 +65,7 @@ class TransformerLayer(TransformerLayerBaseIO):
             fp8_config_dense_out=a.fp8_config_attention_dense_out,
         )
         self.dropout_attention = torch.nn.Dropout(a.dropout_after_attention)
+        self.dropout_attention.kernel_dropout = True  # applied by the fused dropout + residual kernel on the GPU
         self.attn_residual_split = NormedResidualSplit(residual_mults, 2 * layer_index, True)
         self.attn_residual_add = NormedResidualAdd(residual_mults, 2 * layer_index, True)
         self.post_attention_layernorm = norm()
@@ -79,6 +81,7 @@ class TransformerLayer(TransformerLayerBaseIO):
             fp8_config=a.fp8_config_mlp, fp8_config_dense_out=a.fp8_config_mlp_dense_out,
         )
         self.dropout_mlp = torch.nn.Dropout(a.dropout_after_mlp)
+        self.dropout_mlp.kernel_dropout = True
         self.mlp_residual_split = NormedResidualSplit(residual_mults, 2 * layer_index + 1, True)
         self.mlp_residual_add = NormedResidualAdd(residual_mults, 2 * layer_index + 1, True)
         if a.adapter_config is not None:
@@ -116,6 +119,20 @@ class TransformerLayer(TransformerLayerBaseIO):
                 return module(x)
         return module(x)
 
+    def _dropout_residual(self, dropout: torch.nn.Dropout, add: NormedResidualAdd, branch: torch.Tensor,
+                          skip: torch.Tensor) -> torch.Tensor:
+        """``dropout(branch) + skip`` (with the u-muP scales of ``add``) as one kernel on the GPU: the mask comes from
+        the topology's counter-based stream, identical on all tensor-parallel ranks and recomputed in the backward
+        pass; token shards (sequence parallelism) take disjoint parts of it."""
+        t = self.topology
+        if not (branch.is_cuda and t is not None and branch.shape == skip.shape and branch.dtype == skip.dtype):
+            return add(self._dropout(dropout, branch), skip)
+        p = dropout.p if self.training else 0.0
+        xs, rs = (add.residual_scale, add.skip_scale) if add._use_umup else (1.0, 1.0)
+        sharded = t.config.sequence_parallel and t.config.model_parallel_size > 1
+        offset = t.model_parallel_rank * ((branch.numel() + 3) // 4 * 4) if sharded else 0
+        return K.dropout_add(branch, skip, p, t.kernel_rng, True, xs, rs, offset, scale_grad=not add._use_umup)
+
     def attention_block(self, hidden_state: torch.Tensor, cumulative_seq_lengths: torch.Tensor,
                         position_ids: torch.Tensor, use_cache: bool = False, reset_cache: bool = False,
                         cache_index: int = 0, attention_scores_manipulation: Optional[torch.Tensor] = None,
@@ -129,7 +146,7 @@ class TransformerLayer(TransformerLayerBaseIO):
             attentions_score_manipulation_log_additive=attentions_score_manipulation_log_additive,
             doc_ranges=doc_ranges,
         )
-        h = self.attn_residual_add(self._dropout(self.dropout_attention, branch), skip)
+        h = self._dropout_residual(self.dropout_attention, self.attn_residual_add, branch, skip)
         if hasattr(self, "attn_adapter_name"):
             h = h + self.apply_adapter(h, self.attn_adapter_name)
         return h
@@ -137,7 +154,7 @@ class TransformerLayer(TransformerLayerBaseIO):
     def mlp_block(self, hidden_state: torch.Tensor) -> torch.Tensor:
         branch, skip = self.mlp_residual_split(hidden_state)
         branch = self.mlp(self.post_attention_layernorm(branch))
-        h = self.mlp_residual_add(self._dropout(self.dropout_mlp, branch), skip)
+        h = self._dropout_residual(self.dropout_mlp, self.mlp_residual_add, branch, skip)
         if hasattr(self, "mlp_adapter_name"):
             h = h + self.apply_adapter(h, self.mlp_adapter_name)
         return h

@@ -457,3 +457,117 @@ def test_peer_barrier_wait_runs_out_and_reports_timeout():
     rc = lib().sb200_p2p_barrier(ptrs, rounds.data_ptr(), 0, 2, K.status_word().data_ptr(), 0.05, _lib.stream())
     torch.cuda.synchronize()
     K.check_status()
+
+
+# ---------------------------------------------------------------------------------------------- dropout kernels
+def _rng_state(seed=1234):
+    from scaling_b200.parallel.rng_tracker import KernelDropoutState
+
+    st = KernelDropoutState(seed, torch.device(DEV))
+    st.begin_step()
+    return st
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("n", [8 * 1000 + 3, 4096 * 6])
+def test_dropout_residual_kernel(dtype, n):
+    """y = dropout(x) * xs + r * rs against the same expression on the exported mask; the backward pass rebuilds the
+    mask; masks depend on (step, call, element) only, so token shards of a tensor see their part of the full mask."""
+    torch.manual_seed(3)
+    p = 0.25
+    st = _rng_state()
+    x = torch.randn(n, device=DEV, dtype=dtype, requires_grad=True)
+    r = torch.randn(n, device=DEV, dtype=dtype, requires_grad=True)
+    y = K.dropout_add(x, r, p, st, True, x_scale=0.5, r_scale=2.0)       # call 0
+    mask = K.dropout_mask((n,), p, st, 0)
+    kept = (mask > 0).float().mean().item()
+    assert abs(kept - (1 - p)) < 0.02
+    assert all(v == 0.0 or abs(v - 1 / (1 - p)) < 1e-6 for v in mask.unique().tolist())
+    ref = (x.detach().float() * mask * 0.5 + r.detach().float() * 2.0).to(dtype)
+    assert _rel(y, ref) < (1e-3 if dtype == torch.bfloat16 else 1e-6)
+    assert ((y.float() - r.detach().float() * 2.0).abs() < 1e-2 * (1 + r.detach().float().abs())).logical_or(mask > 0).all()
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    assert _rel(x.grad, dy.float() * mask * 0.5) < 1e-2 and ((x.grad == 0) == (mask == 0)).all()
+    assert torch.equal(r.grad.float(), (dy.float() * 2.0).to(dtype).float())
+    # another call index and another step give other masks; the same triple gives the same mask
+    assert not torch.equal(K.dropout_mask((n,), p, st, 1), mask)
+    assert torch.equal(K.dropout_mask((n,), p, st, 0), mask)
+    st.begin_step()
+    assert not torch.equal(K.dropout_mask((n,), p, st, 0), mask)
+    # shards: elements [a, b) of the tensor, processed on their own with elem_offset = a
+    a = (n // 3) // 4 * 4
+    full = K.dropout_mask((n,), p, st, 0)
+    assert torch.equal(K.dropout_mask((n - a,), p, st, 0, elem_offset=a), full[a:])
+    # p = 0: a plain scaled add, no random numbers
+    z = K.dropout_add(x.detach(), r.detach(), 0.0, None, True, x_scale=1.0, r_scale=1.0)
+    assert torch.equal(z, x.detach() + r.detach())
+
+
+def test_dropout_is_replayed_by_activation_checkpointing():
+    from scaling_b200.core.nn.parallel_module.activation_checkpointing import checkpoint
+    from scaling_b200.parallel import Topology, TopologyConfig
+
+    topo = Topology(TopologyConfig.from_dict({"world_size": 1, "model_parallel_size": 1, "pipe_parallel_size": 1,
+                                              "global_rank": 0, "local_slot": 0, "micro_batch_size": 1,
+                                              "gradient_accumulation_steps": 1}))
+    st = topo.kernel_rng
+    st.begin_step()
+    w = torch.randn(512, device=DEV, requires_grad=True)
+
+    def block(x):
+        return K.dropout_add(x * w, None, 0.5, st, True) + K.dropout_add(x, x, 0.3, st, True)
+
+    x = torch.randn(512, device=DEV)
+    plain = block(x)
+    plain.sum().backward()
+    g_plain, w.grad = w.grad.clone(), None
+    st.call_index = 0
+    ck = checkpoint(block, topo, x)
+    after = st.call_index
+    ck.sum().backward()
+    assert torch.equal(ck, plain) and torch.equal(w.grad, g_plain) and st.call_index == after == 2
+
+
+@pytest.mark.parametrize("T,Hq,Hkv,D,cu,causal", [
+    (256, 2, 2, 64, [0, 256], True),
+    (384, 4, 2, 64, [0, 100, 384], True),
+    (320, 2, 1, 128, [0, 320], True),
+    (256, 2, 2, 128, [0, 256], False),
+])
+def test_flash_attention_dropout(T, Hq, Hkv, D, cu, causal):
+    """Attention dropout inside the kernels against the dense expression with the kernels' own mask (read back by
+    `attention_dropout_mask`): forward, and the three gradients of the backward kernels, which rebuild the mask."""
+    from scaling_b200.ops.attention import attention_reference, flash_attention
+    from scaling_b200.ops.attention_kernel import attention_dropout_mask
+
+    torch.manual_seed(21)
+    p = 0.2
+    st = _rng_state(77)
+    q = torch.randn(T, Hq, D, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    k = torch.randn(T, Hkv, D, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    v = torch.randn(T, Hkv, D, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    cu_t = torch.tensor(cu, device=DEV, dtype=torch.int32)
+    scale = D ** -0.5
+    out = flash_attention(q, k, v, cu_t, None, causal=causal, scale=scale, dropout_p=p, rng_state=st)  # call 0
+    do = torch.randn_like(out)
+    out.backward(do)
+    K.check_status()
+    p_eff = round(p * 256) / 256
+    raw = attention_dropout_mask(T, Hq, p, st, 0)
+    mask = (raw > 0).float() / (1 - p_eff)
+    assert abs((raw > 0).float().mean().item() - (1 - p_eff)) < 0.01
+    qr, kr, vr = (t.detach().float().requires_grad_() for t in (q, k, v))
+    ref = attention_reference(qr, kr, vr, cu_t, None, causal, scale, None, dropout_mask=mask)
+    ref.backward(do.float())
+    assert _rel(out, ref) < 2e-2, _rel(out, ref)
+    assert _rel(q.grad, qr.grad) < 3e-2, _rel(q.grad, qr.grad)
+    assert _rel(k.grad, kr.grad) < 3e-2, _rel(k.grad, kr.grad)
+    assert _rel(v.grad, vr.grad) < 3e-2, _rel(v.grad, vr.grad)
+    # without dropout the result differs, with the same call index again it is reproduced bit for bit
+    st.call_index = 0
+    q2, k2, v2 = (t.detach().clone().requires_grad_() for t in (q, k, v))
+    out2 = flash_attention(q2, k2, v2, cu_t, None, causal=causal, scale=scale, dropout_p=p, rng_state=st)
+    out2.backward(do)
+    assert torch.equal(out, out2) and torch.equal(q.grad, q2.grad) and torch.equal(k.grad, k2.grad)
+    assert _rel(out, flash_attention(q, k, v, cu_t, None, causal=causal, scale=scale)) > 0.05
