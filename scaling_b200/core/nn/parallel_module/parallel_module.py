@@ -143,6 +143,7 @@ class ParallelModule(PipePartitionedModule, Generic[BaseLossInputGeneric, BaseDa
         self._graph_kernel_calls = 0
         self._graph_pending: list[Any] = []
         self._kernel_dropout: Optional[bool] = None
+        self._presynced: list[Any] = []
         self._handlers: dict[str, Callable[..., None]] = {
             "LoadMicroBatch": self._do_load, "ForwardPass": self._do_forward, "Loss": self._do_loss,
             "BackwardPass": self._do_backward, "SendActivation": self._do_send_activation,
@@ -297,39 +298,46 @@ class ParallelModule(PipePartitionedModule, Generic[BaseLossInputGeneric, BaseDa
         return optimizer_out
 
     def _post_receives_ahead(self, instructions: list[InstructionBase], position: int) -> None:
-        """Post the receives of the next RecvActivation and the next RecvGrad of this step now, so that the
-        transfers run while the instructions in between compute (the reference blocks in every receive:
-        src/scaling/core/nn/parallel_module/communicator.py:388-482).  Only the first receive of each kind that is
-        still ahead is posted, in schedule order, which keeps every link's receives in the order of its sends; a
-        gradient receive needs the output it belongs to, so it is posted once that forward pass has run."""
-        seen_act = seen_grad = False
+        """Post the next receive of this step now if only compute lies between here and its instruction, so that the
+        transfer runs under that compute (the reference blocks in every receive:
+        src/scaling/core/nn/parallel_module/communicator.py:388-482).
+
+        A posted receive is a kernel that waits for the sender.  It must never wait for a send that itself waits,
+        through the other stage's schedule, for a send this stage has not issued yet: on a GPU, kernels of different
+        streams can share a hardware queue, and the late send could sit behind the waiting receive.  Hence the rule:
+        the look-ahead stops at the first send instruction.  Everything the sender needs from this stage is then
+        already on its way when the receive is posted.  In the 1F1B schedule this posts the receive of the next
+        activation on every stage but the first right after the gradient of the previous micro batch has been sent,
+        i.e. under a whole forward and backward pass."""
         for ins in instructions[position + 1:]:
-            if ins.name == "RecvActivation" and not seen_act:
-                seen_act = True
+            name = ins.name
+            if name in ("SendActivation", "SendGrad"):
+                return
+            if name == "RecvActivation":
                 if self.communicator_in.post_recv() and self.instruction_trace is not None:
                     self.instruction_trace.append(f"post RecvActivation mb={ins.micro_batch_id}")
-            elif ins.name == "RecvGrad" and not seen_grad:
-                seen_grad = True
+                return
+            if name == "RecvGrad":
                 if self.pipe_buffer.has(BufferType.PIPELINE_STAGE_OUTPUT, ins.buffer_id):
                     out = self.pipe_buffer.get(BufferType.PIPELINE_STAGE_OUTPUT, ins.buffer_id)
                     tup = self._prepare_for_send(self._layers[-1].output_to_tuple(out))
                     if self.communicator_out.post_recv_grad(tup) and self.instruction_trace is not None:
                         self.instruction_trace.append(f"post RecvGrad mb={ins.micro_batch_id}")
-            if seen_act and seen_grad:
-                break
+                return
 
     # ------------------------------------------------------------------ CUDA-graph training step
     def _graph_eligible(self, optimizer: Any) -> bool:
         """A whole optimizer step (all micro batches, backward, gradient reduction, AdamW, parameter all-gather)
-        can be captured once and replayed when nothing in it depends on the host: one pipeline stage, batches
-        that reach the device without a tensor-parallel broadcast, dropout only in the counter-based kernels, no loss
+        can be captured once and replayed when nothing in it depends on the host: one pipeline stage (tensor-parallel
+        collectives, library or in-kernel, are captured with the rest; the batch is handed to the tensor-parallel
+        ranks before the replay), dropout only in the counter-based kernels, no loss
         scaling, profiler idle."""
         if not self.enable_cuda_graph or self._graph_failed:
             return False
         if getattr(self, "_tensor_statistics_active", False):  # hooks of a statistics trace need the eager step
             return False
         t = self.topology
-        if t.device.type != "cuda" or t.config.pipe_parallel_size != 1 or t.config.model_parallel_size != 1:
+        if t.device.type != "cuda" or t.config.pipe_parallel_size != 1:
             return False
         if not all(hasattr(optimizer, a) for a in ("begin_step", "step_device", "finish_step")):
             return False
@@ -381,8 +389,9 @@ class ParallelModule(PipePartitionedModule, Generic[BaseLossInputGeneric, BaseDa
         """Device work of one step on the static input batches; runs eagerly for warm-up and under capture."""
         t = self.topology
         self.pipe_buffer.reset()
+        presynced = t.config.model_parallel_size > 1  # then the static inputs are synchronised batches already
         for batch in self._graph_inputs:
-            b = sync(t, batch)
+            b = batch if presynced else sync(t, batch)
             out = self(b.only_inputs())
             result = loss_function(out, b.only_targets())
             loss, metrics = result if isinstance(result, tuple) else (result, None)
@@ -401,6 +410,13 @@ class ParallelModule(PipePartitionedModule, Generic[BaseLossInputGeneric, BaseDa
             for k, v in agg.items():
                 self._graph_metrics[k].copy_(torch.as_tensor(v, dtype=torch.float32, device=t.device))
 
+    def cuda_graph_state(self) -> str:
+        """How training steps are launched: "whole step" (one captured graph replayed per optimizer step), "eager"
+        (instruction list from the host) or "eager (capture failed)"."""
+        if self._graph is not None:
+            return "whole step"
+        return "eager (capture failed)" if self._graph_failed else "eager"
+
     def release_cuda_graph(self) -> None:
         """Drop the captured training step and its static buffers (call before destroying process groups: a graph
         that holds collectives keeps their communicators busy)."""
@@ -418,8 +434,15 @@ class ParallelModule(PipePartitionedModule, Generic[BaseLossInputGeneric, BaseDa
 
         t = self.topology
         ga = t.config.gradient_accumulation_steps
-        raw = [next(dataloader) for _ in range(ga)]
-        key = (sync, loss_function, metrics_aggregation_fn,
+        presync = t.config.model_parallel_size > 1
+        if presync:
+            # The hand-over of a batch to the tensor-parallel ranks reads sizes on the host: it runs here, ahead of
+            # the replay, on every rank of the group (only the first one has a data loader); the captured step starts
+            # from the synchronised batch.
+            raw = [sync(t, next(dataloader) if t.is_io_rank else None) for _ in range(ga)]
+        else:
+            raw = [next(dataloader) for _ in range(ga)]
+        key = (sync, loss_function, metrics_aggregation_fn, presync,
                tuple(tuple((type(b).__name__, k, tuple(v.shape), v.dtype) for k, v in self._batch_tensors(b)) for b in raw))
         if key != self._graph_signature:
             # new input signature: drop the old graph and start over (a bounded number of times)
@@ -427,7 +450,10 @@ class ParallelModule(PipePartitionedModule, Generic[BaseLossInputGeneric, BaseDa
             self._graph_captures += 1
             if self._graph_captures > 4:
                 self._graph_failed = True
-                self._graph_pending = raw
+                if presync:
+                    self._presynced = raw
+                else:
+                    self._graph_pending = raw
                 return None
             self._graph_signature = key
             self._graph_warmup_left = 2 if self._graph_captures == 1 else 1
@@ -457,17 +483,28 @@ class ParallelModule(PipePartitionedModule, Generic[BaseLossInputGeneric, BaseDa
                         self._graph_device_step(optimizer, sync, loss_function, metrics_aggregation_fn)
                     self._graph_kernel_calls = _lib.kernel_calls() - calls0
                     self._graph = graph
-                    graph.replay()
+                    failed = None
                 except Exception as e:  # noqa: BLE001 - any capture problem means: stay eager
+                    failed = e
+                    self._graph = None
+                # Ranks decide together: a step holds collectives, so either every rank replays it or none does.
+                if t.is_distributed_initialized and t.world_size > 1:
+                    flag = torch.tensor([0.0 if failed is None else 1.0], device=t.device)
+                    dist.all_reduce(flag)
+                    if flag.item() > 0 and failed is None:
+                        failed = RuntimeError("capture failed on another rank")
+                        self._graph = None
+                if failed is not None:
                     from ...logging import logger
 
-                    logger.warning(f"CUDA-graph capture of the training step failed ({type(e).__name__}: {e}); "
+                    logger.warning(f"CUDA-graph capture of the training step failed ({type(failed).__name__}: {failed}); "
                                    "continuing without graphs")
-                    self._graph = None
                     self._graph_failed = True
                     torch.cuda.synchronize()
                     optimizer.zero_grad()
                     self._graph_device_step(optimizer, sync, loss_function, metrics_aggregation_fn)
+                else:
+                    self._graph.replay()
         else:
             self._graph.replay()
             _lib.note_replayed_calls(self._graph_kernel_calls)
@@ -572,11 +609,14 @@ class ParallelModule(PipePartitionedModule, Generic[BaseLossInputGeneric, BaseDa
 
     def _do_load(self, ins: InstructionBase, dataloader: Any, sync: Callable, **_: Any) -> None:
         t = self.topology
-        batch = None
-        if t.is_io_rank:
-            assert dataloader is not None
-            batch = next(dataloader)
-        batch = sync(t, batch)
+        if self._presynced:  # batches that a step drew and synchronised before it fell back to this path
+            batch = self._presynced.pop(0)
+        else:
+            batch = None
+            if t.is_io_rank:
+                assert dataloader is not None
+                batch = next(dataloader)
+            batch = sync(t, batch)
         if t.is_first_pipe_parallel_rank:
             self.pipe_buffer.write(BufferType.PIPELINE_STAGE_INPUT, ins.buffer_id, batch.only_inputs())
         if t.is_last_pipe_parallel_rank:

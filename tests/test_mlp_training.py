@@ -127,9 +127,10 @@ def _run_traced(rank, world_size, port, device, config, overlap):
 
 @pytest.mark.dist
 def test_pipeline_receives_are_posted_ahead_of_the_compute_before_them():
-    """With overlap on, a stage posts the receive of the next activation as soon as the current one has arrived (before
-    it runs the forward pass in between), and the receive of a gradient as soon as the forward pass it belongs to is
-    enqueued; the losses are those of the run that posts every receive where the schedule names it."""
+    """With overlap on, a stage posts its next receive as soon as only compute lies between it and the receive's own
+    instruction (never across one of its own sends, which the sender may be waiting for): the last stage gets the next
+    activation while it runs forward and backward of the current micro batch, the first stage the next gradient while
+    it runs a backward pass.  The losses are those of the run that posts every receive where the schedule names it."""
     config = _config(2, pp=2, ga=4, micro=4, iters=3)
     (loss_a, trace0), (_, trace1) = dist_launcher(_run_traced, 2, config=config, overlap=True)
     (loss_b, plain0), _ = dist_launcher(_run_traced, 2, config=config, overlap=False)
@@ -143,10 +144,10 @@ def test_pipeline_receives_are_posted_ahead_of_the_compute_before_them():
     # last stage: activation of micro batch 1 is on its way while micro batch 0 is still being computed
     assert pos(trace1, "RecvActivation mb=0") < pos(trace1, "post RecvActivation mb=1") < pos(trace1, "ForwardPass mb=0")
     assert pos(trace1, "post RecvActivation mb=2") < pos(trace1, "ForwardPass mb=1")
-    # first stage: the gradient of micro batch 0 is awaited from the moment its forward pass is enqueued, i.e. during
-    # the forward pass of micro batch 1
-    assert pos(trace0, "ForwardPass mb=0") < pos(trace0, "post RecvGrad mb=0") < pos(trace0, "ForwardPass mb=1")
-    assert pos(trace0, "post RecvGrad mb=1") < pos(trace0, "BackwardPass mb=0")
+    assert pos(trace1, "SendGrad mb=0") < pos(trace1, "post RecvActivation mb=2")  # not across the stage's own send
+    # first stage, cool-down: the gradient of micro batch 3 is awaited while micro batch 2 runs backward
+    assert pos(trace0, "RecvGrad mb=2") < pos(trace0, "post RecvGrad mb=3") < pos(trace0, "BackwardPass mb=2")
+    assert pos(trace0, "SendActivation mb=1") < pos(trace0, "post RecvGrad mb=0")
     # every posted receive is consumed by its instruction, in order
     for trace, kind in ((trace1, "RecvActivation"), (trace0, "RecvGrad")):
         posted = [t.split("mb=")[1] for t in trace if t.startswith(f"post {kind}")]

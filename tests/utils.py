@@ -11,7 +11,8 @@ from typing import Any, Callable
 import torch
 import torch.multiprocessing as mp
 
-PROCESS_TIMEOUT = 300  # generous: a loaded test machine must not look like a hung rank
+# generous: a loaded test machine must not look like a hung rank (SB200_TEST_TIMEOUT_S overrides)
+PROCESS_TIMEOUT = int(os.environ.get("SB200_TEST_TIMEOUT_S", "300"))
 
 
 def find_free_port() -> int:
