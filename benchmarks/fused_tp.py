@@ -1,7 +1,7 @@
 """Microbenchmark of the tensor-parallel GEMMs with in-kernel collectives against GEMM + NCCL.
 
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P \\
-        -m scaling_b200.parallel.bench_fused_tp [--multicast 0|1] [--iters 10]
+        -m benchmarks.fused_tp [--multicast 0|1] [--iters 10]
 
 For every shape, the row-parallel forms (``x [M, K / N_ranks] @ w^T`` followed by reduce-scatter or all-reduce) and the
 column-parallel form (all-gather of ``[M / N_ranks, N]`` followed by a GEMM) are timed with CUDA events on the
@@ -19,14 +19,16 @@ import os
 import torch
 import torch.distributed as dist
 
-from ..ops import functional as K
-from .fused_tp import FusedTPWorkspace
+from scaling_b200.ops import functional as K
+from scaling_b200.parallel.fused_tp import FusedTPWorkspace
 
 GEMM_PEAK_FLOPS = 1.573e15  # measured cuBLAS bf16 burst on this part
 LINK_BYTES_PER_S = 770e9    # measured peer copy, per direction
 
-# (M tokens, N, K before the split): fc2 and attention output of the 125M decoder, the 7B MLP and attention output
-SHAPES = [(16384, 768, 3072), (16384, 768, 768), (4096, 4096, 11008), (4096, 4096, 4096), (2048, 768, 768)]
+# (M tokens, N, K before the split): fc2 and attention output of the 125M decoder; MLP and attention output of the
+# 7B model at 4096 and 8192 tokens, its output head (K = vocabulary)
+SHAPES = [(16384, 768, 3072), (16384, 768, 768), (4096, 4096, 11008), (4096, 4096, 4096), (8192, 4096, 11008),
+          (4096, 4096, 65536), (2048, 768, 768)]
 
 
 def main() -> None:

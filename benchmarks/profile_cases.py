@@ -1,6 +1,6 @@
 """Small, self-contained workloads of the hot kernels for timing and for profiler captures.
 
-    python -m scaling_b200.ops.profile_cases <case> [--iters N]
+    python -m benchmarks.profile_cases <case> [--iters N]
 
 Each case allocates a few hundred MB at most (inputs larger than the 126 MB L2, so DRAM figures mean something),
 runs two warm-up and ``--iters`` timed launches (default 3) with an L2 flush before each timed one, times the launches with CUDA events and
@@ -17,7 +17,7 @@ import sys
 
 import torch
 
-from . import functional as K
+from scaling_b200.ops import functional as K
 
 TOKENS = 8 * 2048
 HIDDEN = 768
@@ -88,7 +88,7 @@ def _attention_inputs():
 
 def case_attention_fwd(iters: int) -> dict:
     """Causal self-attention forward on the packed projection, 8 documents of 2048 tokens, 12 heads of 64."""
-    from .attention_kernel import packed_qkv_attention
+    from scaling_b200.ops.attention_kernel import packed_qkv_attention
 
     qkv, cu, pos = _attention_inputs()
     with torch.no_grad():
@@ -100,7 +100,7 @@ def case_attention_fwd(iters: int) -> dict:
 
 def case_attention_bwd(iters: int) -> dict:
     """Forward + backward of the same attention (backward = delta, dK/dV, dQ kernels and the inverse rotation)."""
-    from .attention_kernel import packed_qkv_attention
+    from scaling_b200.ops.attention_kernel import packed_qkv_attention
 
     qkv, cu, pos = _attention_inputs()
     src = qkv.requires_grad_()

@@ -22,6 +22,7 @@ from typing import Any, Callable, Generic, NamedTuple, Optional, Union
 import torch
 import torch.distributed as dist
 
+from ....parallel import fused_tp
 from ....parallel.topology import Topology
 from ....parallel.topology_config import ActivationCheckpointingType
 from ...profiler import Profiler, ProfilerConfig
@@ -389,6 +390,7 @@ class ParallelModule(PipePartitionedModule, Generic[BaseLossInputGeneric, BaseDa
         """Device work of one step on the static input batches; runs eagerly for warm-up and under capture."""
         t = self.topology
         self.pipe_buffer.reset()
+        fused_tp.begin_step()  # host-side only: the step issues the same fused launches eagerly, captured and replayed
         presynced = t.config.model_parallel_size > 1  # then the static inputs are synchronised batches already
         for batch in self._graph_inputs:
             b = batch if presynced else sync(t, batch)
@@ -533,6 +535,7 @@ class ParallelModule(PipePartitionedModule, Generic[BaseLossInputGeneric, BaseDa
         self._layers.train()
         self._set_channel("train")
         self.pipe_buffer.reset()
+        fused_tp.begin_step()
         self.profiler.step()
         opt_out = self._run(self.train_instructions, dataloader=dataloader, optimizer=optimizer,
                             sync=sync_batch_to_model_parallel, loss_function=loss_function, grad=True)
@@ -547,6 +550,7 @@ class ParallelModule(PipePartitionedModule, Generic[BaseLossInputGeneric, BaseDa
         self._layers.eval()
         self._set_channel("eval")
         self.pipe_buffer.reset()
+        fused_tp.begin_step()
         self.profiler.step()
         with torch.no_grad():
             self._run(self.evaluation_instructions, dataloader=dataloader, optimizer=None,

@@ -57,6 +57,14 @@ struct ArParams {
   // every rank pushes its [shard_rows, K] shard a_src into the rows [rank * shard_rows, ...) of partial[q] ([M, K])
   // of every rank q, and the tile loads of a row block wait for its arrival; the output is a plain local GEMM result.
   int mode;
+  // partial[] holds two buffers of half_elems elements; launch after launch alternates between them (half = 0 / 1,
+  // counted by the host from the last launch with sync_entry).  A buffer is therefore rewritten two launches after
+  // it was filled, and no rank can finish a launch before every peer has entered it (it needs their tiles, rows or
+  // completion flags): whoever read the buffer has finished by then.  sync_entry = 1 starts a new count: every rank
+  // first waits until all ranks have entered this launch.
+  long half_elems;
+  int half;
+  int sync_entry;
   int shard_rows;
   int unit_shift;     // tiles are visited from this one on (modulo their number): a different start on every rank
   long ld_out;
@@ -216,7 +224,7 @@ template <int BN, bool A_MN, bool B_MN, typename OutT, bool PAIR, bool FUSE>
 __global__ void __launch_bounds__(FUSE ? GEMM_THREADS + REDUCER_THREADS : GEMM_THREADS, 1)
     gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                         const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmP,
-                        const GemmParams p) {
+                        const __grid_constant__ CUtensorMap tmA2, const GemmParams p) {
   using Cfg = GemmCfg<BN, PAIR>;
   constexpr int STAGES = Cfg::STAGES;
   constexpr int CTAS = Cfg::CTAS;
@@ -253,6 +261,11 @@ __global__ void __launch_bounds__(FUSE ? GEMM_THREADS + REDUCER_THREADS : GEMM_T
   const int wait_rounds = (FUSE && p.ar.mode == AR_ALLGATHER) ? (int)(p.ar.timeout_ns / 2000000000ull) + 2 : 1;
   // position in this worker's sequence -> unit (tile, split); fused launches start at a rank-specific tile
   auto unit_at = [&](int i) { return FUSE ? (i + ushift) % num_units : i; };
+  // fused launches on the second buffer of the workspace: the gathered operand is read through tmA2, partial tiles
+  // are stored through tmP (which no fused reduction uses for a pre-activation output)
+  const CUtensorMap* mapA = (FUSE && p.ar.mode == AR_ALLGATHER && p.ar.half) ? &tmA2 : &tmA;
+  const CUtensorMap* mapC = (FUSE && p.ar.mode != AR_ALLGATHER && p.ar.half) ? &tmP : &tmC;
+  const long hoff = FUSE ? (long)p.ar.half * p.ar.half_elems : 0;  // element offset of the buffer in use
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -266,6 +279,17 @@ __global__ void __launch_bounds__(FUSE ? GEMM_THREADS + REDUCER_THREADS : GEMM_T
     *abort_flag = 0;
     *last_flag = 0;
     sb::mbar_fence_init();
+    if (FUSE && p.ar.sync_entry) {
+      // first launch of a count: nothing of this launch is written anywhere before every rank has entered it
+      const long slot = (long)(p.ar.W + 1) * p.ar.flag_stride;
+      if (blockIdx.x == 0)
+        for (int q = 0; q < p.ar.W; ++q) sb::st_release_sys(p.ar.flags[q] + slot + p.ar.rank, epoch);
+      for (int q = 0; q < p.ar.W; ++q)
+        if (!sb::wait_flag_ge(p.ar.flags[p.ar.rank] + slot + q, epoch, p.ar.timeout_ns)) {
+          *abort_flag = 1;
+          break;
+        }
+    }
   }
   if (warp == 1) {
     if (PAIR) {
@@ -285,7 +309,7 @@ __global__ void __launch_bounds__(FUSE ? GEMM_THREADS + REDUCER_THREADS : GEMM_T
   if (warp == 0) {
     // ------------------------------------------------------------ producer
     if (lane == 0) {
-      sb::tma_prefetch_desc(&tmA);
+      sb::tma_prefetch_desc(mapA);
       sb::tma_prefetch_desc(&tmB);
       int stage = 0;
       uint32_t phase = 0;
@@ -320,9 +344,9 @@ __global__ void __launch_bounds__(FUSE ? GEMM_THREADS + REDUCER_THREADS : GEMM_T
             if (A_MN) {
 #pragma unroll
               for (int j = 0; j < BM / 64; ++j)
-                sb::tma_load_2d_pair(a_s + j * 8192, &tmA, bar, m_blk * BM + j * 64, kb * BK);
+                sb::tma_load_2d_pair(a_s + j * 8192, mapA, bar, m_blk * BM + j * 64, kb * BK);
             } else {
-              sb::tma_load_2d_pair(a_s, &tmA, bar, kb * BK, m_blk * BM);
+              sb::tma_load_2d_pair(a_s, mapA, bar, kb * BK, m_blk * BM);
             }
             if (B_MN) {
 #pragma unroll
@@ -336,9 +360,9 @@ __global__ void __launch_bounds__(FUSE ? GEMM_THREADS + REDUCER_THREADS : GEMM_T
             if (A_MN) {
 #pragma unroll
               for (int j = 0; j < BM / 64; ++j)
-                sb::tma_load_2d(a_s + j * 8192, &tmA, &full_bar[stage], m_blk * BM + j * 64, kb * BK);
+                sb::tma_load_2d(a_s + j * 8192, mapA, &full_bar[stage], m_blk * BM + j * 64, kb * BK);
             } else {
-              sb::tma_load_2d(a_s, &tmA, &full_bar[stage], kb * BK, m_blk * BM);
+              sb::tma_load_2d(a_s, mapA, &full_bar[stage], kb * BK, m_blk * BM);
             }
             if (B_MN) {
 #pragma unroll
@@ -407,7 +431,7 @@ __global__ void __launch_bounds__(FUSE ? GEMM_THREADS + REDUCER_THREADS : GEMM_T
     int acc = 0;
     uint32_t acc_phase = 0;
     int bias_buf = 0;
-    OutT* C = reinterpret_cast<OutT*>(p.C);
+    OutT* C = reinterpret_cast<OutT*>(p.C) + ((FUSE && p.ar.mode != AR_ALLGATHER) ? hoff : 0);
     OutT* Cpre = reinterpret_cast<OutT*>(p.C_pre);
     const uint16_t* bias_raw = reinterpret_cast<const uint16_t*>(p.bias);
     const bool vec_ok = (p.ldc % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0) &&
@@ -564,7 +588,7 @@ __global__ void __launch_bounds__(FUSE ? GEMM_THREADS + REDUCER_THREADS : GEMM_T
             sb::fence_proxy_async_smem();
             __syncwarp();
             if (lane == 0) {
-              sb::tma_store_2d(pre_pass ? &tmP : &tmC, stage_buf, n0, row0);
+              sb::tma_store_2d(pre_pass ? &tmP : mapC, stage_buf, n0, row0);
               sb::tma_store_commit();
             }
           }
@@ -656,14 +680,10 @@ __global__ void __launch_bounds__(FUSE ? GEMM_THREADS + REDUCER_THREADS : GEMM_T
     bool rok = true;
     if (ar.mode == AR_ALLGATHER) {
       // ---------------------------------------------------------- gather: push this rank's rows of A to every rank
-      // A rank may be written to only once it has entered this launch: everything that read its copy of the
-      // gathered operand before (earlier kernels of its stream) has finished by then.
-      uint32_t* entered = ar.flags[ar.rank] + (long)(ar.W + 1) * ar.flag_stride;
-      if (blockIdx.x == 0 && rt < ar.W)
-        sb::st_release_sys(ar.flags[rt] + (long)(ar.W + 1) * ar.flag_stride + ar.rank, epoch);
-      if (rt < ar.W && !sb::wait_flag_ge(entered + rt, epoch, ar.timeout_ns)) *abort_flag = 1;
-      red_bar_sync();
-      if (*abort_flag) rok = false;
+      // The destination is the buffer that was not used by the previous launch (see ArParams::half): a rank's
+      // copy of it is free as soon as that rank has finished the launch before the previous one, which it has,
+      // since this rank could not have finished the previous launch without it.
+      if (*abort_flag) rok = false;  // the entry wait of a new count gave up
       const int kvec = p.K / 8;  // 16-byte vectors per row
       const int blocks = (ar.shard_rows + BM - 1) / BM;
       // a 128-row block is pushed by `groups` CTAs, each a range of columns, so that all CTAs of the launch share
@@ -688,7 +708,7 @@ __global__ void __launch_bounds__(FUSE ? GEMM_THREADS + REDUCER_THREADS : GEMM_T
             const int idx = base + j * REDUCER_THREADS;
             valid[j] = idx < total;
             const int row = r0 + idx / nv, col = (v0 + idx % nv) * 8;
-            doff[j] = ((long)ar.rank * ar.shard_rows + row) * p.K + col;
+            doff[j] = hoff + ((long)ar.rank * ar.shard_rows + row) * p.K + col;
             if (valid[j]) v[j] = __ldg(reinterpret_cast<const uint4*>(src + (long)row * ar.lda_src + col));
           }
           if (ar.partial_mc) {
@@ -740,7 +760,7 @@ __global__ void __launch_bounds__(FUSE ? GEMM_THREADS + REDUCER_THREADS : GEMM_T
 #pragma unroll
           for (int j = 0; j < UNR; ++j) {
             valid[j] = piece(base + j * REDUCER_THREADS, off[j]);
-            if (valid[j]) v[j] = multimem_sum16<OutT>(reinterpret_cast<const OutT*>(ar.partial_mc) + off[j]);
+            if (valid[j]) v[j] = multimem_sum16<OutT>(reinterpret_cast<const OutT*>(ar.partial_mc) + hoff + off[j]);
           }
           if (scatter) {
 #pragma unroll
@@ -768,7 +788,8 @@ __global__ void __launch_bounds__(FUSE ? GEMM_THREADS + REDUCER_THREADS : GEMM_T
             uint4 raw[UNR];
 #pragma unroll
             for (int j = 0; j < UNR; ++j)
-              if (valid[j]) raw[j] = *reinterpret_cast<const uint4*>(reinterpret_cast<const OutT*>(ar.partial[q]) + off[j]);
+              if (valid[j])
+                raw[j] = *reinterpret_cast<const uint4*>(reinterpret_cast<const OutT*>(ar.partial[q]) + hoff + off[j]);
 #pragma unroll
             for (int j = 0; j < UNR; ++j)
               if (valid[j]) {
@@ -811,18 +832,21 @@ __global__ void __launch_bounds__(FUSE ? GEMM_THREADS + REDUCER_THREADS : GEMM_T
   }
   if (threadIdx.x == 0 && *abort_flag && p.status) *p.status = SB_ERR_WAIT_TIMEOUT;
   if (FUSE && threadIdx.x == 0) {
-    // The last CTA of this launch tells every peer that this rank has finished reducing, then waits for the same
-    // message from all of them: when the launch ends, every tile of this rank's output has been written, and no
-    // peer reads this rank's partial buffer any more.
+    // All-reduce: the peers write this rank's output, so the last CTA of the launch tells every peer that this rank
+    // has finished reducing and waits for the same message from all of them; when the launch ends, every tile of
+    // the output has arrived.  The other two forms produce their output locally and need no message at the end
+    // (the partial / gathered buffers alternate between launches instead, see ArParams::half).
     const ArParams& ar = p.ar;
     __threadfence_system();
     if (atomicAdd(ar.done_ctas, 1u) == gridDim.x - 1) {
       *ar.done_ctas = 0;
-      for (int q = 0; q < ar.W; ++q)
-        sb::st_release_sys(ar.flags[q] + (long)ar.W * ar.flag_stride + ar.rank, epoch);
-      for (int q = 0; q < ar.W; ++q)
-        if (!sb::wait_flag_ge(ar.flags[ar.rank] + (long)ar.W * ar.flag_stride + q, epoch, ar.timeout_ns) && p.status)
-          *p.status = SB_ERR_WAIT_TIMEOUT;
+      if (ar.mode == AR_ALLREDUCE) {
+        for (int q = 0; q < ar.W; ++q)
+          sb::st_release_sys(ar.flags[q] + (long)ar.W * ar.flag_stride + ar.rank, epoch);
+        for (int q = 0; q < ar.W; ++q)
+          if (!sb::wait_flag_ge(ar.flags[ar.rank] + (long)ar.W * ar.flag_stride + q, epoch, ar.timeout_ns) && p.status)
+            *p.status = SB_ERR_WAIT_TIMEOUT;
+      }
       *ar.epoch = epoch;
       __threadfence();
     }
@@ -863,7 +887,7 @@ int make_tmap_2d(CUtensorMap* tm, const void* base, long rows, long cols, long l
 
 template <int BN, bool A_MN, bool B_MN, typename OutT, bool PAIR, bool FUSE = false>
 int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmC, const CUtensorMap& tmP,
-                const GemmParams& p, int sm_count, cudaStream_t stream) {
+                const GemmParams& p, int sm_count, cudaStream_t stream, const CUtensorMap* tmA2 = nullptr) {
   using Cfg = GemmCfg<BN, PAIR>;
   auto kern = gemm_tcgen05_kernel<BN, A_MN, B_MN, OutT, PAIR, FUSE>;
   static bool attr_set = false;
@@ -888,7 +912,7 @@ int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMa
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = PAIR ? 1 : 0;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, tmA, tmB, tmC, tmP, p);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, tmA, tmB, tmC, tmP, tmA2 ? *tmA2 : tmA, p);
   if (e != cudaSuccess) return (int)e;
   return SB_OK;
 }
@@ -1032,6 +1056,9 @@ SB_API int sb200_gemm(const void* A, const void* B, void* C, void* C_pre, const 
 // flags: (W + 2) * flag_stride uint32, zero before the first use, flag_stride >= number of 128-row output tiles;
 // partial_mc / out_mc: multicast addresses or null; epoch, done_ctas: one uint32 each in local device memory, zero
 // before the first use.  bias is given on one rank only in modes 0 and 1 (it is added once to the sum).
+// The buffers behind partial_ptrs hold 2 * half_elems elements: two buffers that consecutive launches on a workspace
+// use in turn (half = 0, 1, 0, ... on every rank alike).  sync_entry = 1 (with half = 0) starts the alternation anew,
+// e.g. at the start of a training step; that launch first waits until all ranks have entered it.
 //   mode 0 (all-reduce):     out_ptrs[rank][M, ldc] = sum_r A_r[M, K] op(B_r); partial: [M, ldc] per rank.
 //   mode 1 (reduce-scatter): C[M / W, ldc] = rows [rank * M / W, ...) of that sum (C is local memory).
 //   mode 2 (all-gather):     C[M, ldc] = act([A_0; A_1; ...; A_{W-1}] op(B) + bias) with A_r the [M / W, K] shard
@@ -1041,9 +1068,12 @@ SB_API int sb200_gemm_tp(const void* A, const void* B, void* C, void* C_pre, con
                          long lda, long ldb, long ldc, int b_mn, int act, int in_dtype, int mode,
                          void* const* partial_ptrs, void* const* out_ptrs, void* const* flag_ptrs, void* partial_mc,
                          void* out_mc, int flag_stride, uint32_t* epoch, unsigned int* done_ctas, int rank, int W,
-                         double timeout_seconds, int sm_count, int* status, cudaStream_t stream) {
+                         long half_elems, int half, int sync_entry, double timeout_seconds, int sm_count, int* status,
+                         cudaStream_t stream) {
   if (M <= 0 || N <= 0) return SB_OK;
   if (K <= 0 || W < 1 || W > AR_MAX_RANKS || rank < 0 || rank >= W) return SB_ERR_BAD_ARG;
+  if (half < 0 || half > 1 || half_elems < 0 || (half_elems & 7)) return SB_ERR_BAD_ARG;
+  if ((long)M * (mode == AR_ALLGATHER ? K : ldc) > half_elems && half_elems > 0) return SB_ERR_TOO_LARGE;
   if (in_dtype != SB_DT_BF16 || mode < 0 || mode > 2) return SB_ERR_BAD_ARG;
   if ((lda % 8) || (ldb % 8) || (ldc % 8) || (N % 8) || (K % 8)) return SB_ERR_BAD_ARG;
   if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15)) return SB_ERR_BAD_ARG;
@@ -1082,6 +1112,7 @@ SB_API int sb200_gemm_tp(const void* A, const void* B, void* C, void* C_pre, con
   // (measured: 207 us against 235 us for a 4096 x 4096 x 5504 problem).
   if (mode == AR_ALLGATHER && W <= 2) p.ar.partial_mc = nullptr;
   p.ar.flag_stride = flag_stride; p.ar.rank = rank; p.ar.W = W;
+  p.ar.half_elems = half_elems; p.ar.half = half; p.ar.sync_entry = sync_entry;
   p.ar.mode = mode; p.ar.shard_rows = mode == AR_ALLREDUCE ? M : M / W; p.ar.ld_out = ldc;
   p.ar.a_src = A; p.ar.lda_src = lda;
   // reduce-scatter: a rank multiplies its own rows last, so that the tiles it has to reduce arrive from the peers
@@ -1092,31 +1123,27 @@ SB_API int sb200_gemm_tp(const void* A, const void* B, void* C, void* C_pre, con
   if (timeout_seconds <= 0.0) timeout_seconds = 10.0;
   if (timeout_seconds > 60.0) timeout_seconds = 60.0;  // longest wait a kernel may spin
   p.ar.timeout_ns = (unsigned long long)(timeout_seconds * 1e9);
-  CUtensorMap tmA, tmB, tmC, tmP;
+  CUtensorMap tmA, tmB, tmC, tmP, tmA2;
   int rc;
   if ((rc = make_tmap_2d(&tmA, a_operand, M, K, a_ld, BM, 0))) return rc;
+  tmA2 = tmA;
+  if (mode == AR_ALLGATHER &&  // the gathered operand in the second buffer
+      (rc = make_tmap_2d(&tmA2, reinterpret_cast<const uint16_t*>(a_operand) + half_elems, M, K, a_ld, BM, 0)))
+    return rc;
   if (b_mn) rc = make_tmap_2d(&tmB, B, K, N, ldb, 64, 0);
   else rc = make_tmap_2d(&tmB, B, N, K, ldb, pair ? 128 : bn, 0);
   if (rc) return rc;
   if ((rc = make_tmap_out(&tmC, p.C, M, N, ldc, 0))) return rc;
   tmP = tmC;
   if (p.C_pre && (rc = make_tmap_out(&tmP, p.C_pre, M, N, ldc, 0))) return rc;
+  if (mode != AR_ALLGATHER &&  // partial tiles in the second buffer
+      (rc = make_tmap_out(&tmP, reinterpret_cast<uint16_t*>(p.C) + half_elems, M, N, ldc, 0)))
+    return rc;
   using T = __nv_bfloat16;
   if (pair) {
-    if (b_mn) return launch_gemm<256, false, true, T, true, true>(tmA, tmB, tmC, tmP, p, sm_count, stream);
-    return launch_gemm<256, false, false, T, true, true>(tmA, tmB, tmC, tmP, p, sm_count, stream);
+    if (b_mn) return launch_gemm<256, false, true, T, true, true>(tmA, tmB, tmC, tmP, p, sm_count, stream, &tmA2);
+    return launch_gemm<256, false, false, T, true, true>(tmA, tmB, tmC, tmP, p, sm_count, stream, &tmA2);
   }
-  if (b_mn) return launch_gemm<128, false, true, T, false, true>(tmA, tmB, tmC, tmP, p, sm_count, stream);
-  return launch_gemm<128, false, false, T, false, true>(tmA, tmB, tmC, tmP, p, sm_count, stream);
-}
-
-// The all-reduce form with its earlier argument list.
-SB_API int sb200_gemm_allreduce(const void* A, const void* B, const void* bias, int M, int N, int K, long lda, long ldb,
-                                long ldc, int b_mn, int in_dtype, void* const* partial_ptrs, void* const* out_ptrs,
-                                void* const* flag_ptrs, void* partial_mc, void* out_mc, int flag_stride,
-                                uint32_t* epoch, unsigned int* done_ctas, int rank, int W, double timeout_seconds,
-                                int sm_count, int* status, cudaStream_t stream) {
-  return sb200_gemm_tp(A, B, nullptr, nullptr, bias, M, N, K, lda, ldb, ldc, b_mn, 0, in_dtype, AR_ALLREDUCE, partial_ptrs,
-                       out_ptrs, flag_ptrs, partial_mc, out_mc, flag_stride, epoch, done_ctas, rank, W, timeout_seconds,
-                       sm_count, status, stream);
+  if (b_mn) return launch_gemm<128, false, true, T, false, true>(tmA, tmB, tmC, tmP, p, sm_count, stream, &tmA2);
+  return launch_gemm<128, false, false, T, false, true>(tmA, tmB, tmC, tmP, p, sm_count, stream, &tmA2);
 }

@@ -43,19 +43,24 @@ def _declare() -> None:
         _lib.declare("sb200_gemm_tp",
                      [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_long, c_long, c_long,
                       c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
-                      c_void_p, c_int, c_int, c_double, c_int, c_void_p, c_void_p])
+                      c_void_p, c_int, c_int, c_long, c_int, c_int, c_double, c_int, c_void_p, c_void_p])
         _DECLARED = True
 
 
 class FusedTPWorkspace:
     """Symmetric buffers of one tensor-parallel group: partial products / gathered operand, reduced output, flags."""
 
-    def __init__(self, group: dist.ProcessGroup, device: torch.device, max_elements: int, use_multicast: bool = True):
+    def __init__(self, group: dist.ProcessGroup, device: torch.device, max_elements: int, use_multicast: bool = True,
+                 reserved_sms: int = 0):
         self.group = group
+        # SMs the fused kernels leave free: their CTAs wait for CTAs of other GPUs, so all of them must be resident
+        # at once even while kernels of other streams (point-to-point copies between pipeline stages) hold SMs
+        self.reserved_sms = int(reserved_sms)
         self.world = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
         self.max_elements = int(max_elements)
-        self.partial = _SymmetricBuffer(self.max_elements, torch.bfloat16, device, group)
+        # two buffers that consecutive launches use in turn (see _launch)
+        self.partial = _SymmetricBuffer(2 * self.max_elements, torch.bfloat16, device, group)
         self.out = _SymmetricBuffer(self.max_elements, torch.bfloat16, device, group)
         self.flags = _SymmetricBuffer((self.world + 2) * FLAG_STRIDE, torch.int32, device, group)
         self.flags.tensor.zero_()
@@ -64,6 +69,8 @@ class FusedTPWorkspace:
                               and self.out.multicast_ptr is not None)
         self.timeout_s = device_wait_limit_s()
         self.launches = 0
+        self._count = 0        # launches since the alternation of the two buffers was last started
+        self._last_half = 0
         self._gathered_key: Any = None
         self._regathered: Any = None
         torch.cuda.synchronize(device)
@@ -79,12 +86,24 @@ class FusedTPWorkspace:
         assert need <= self.max_elements, f"fused workspace holds {self.max_elements} elements, need {need}"
         mc = self.use_multicast
         self.launches += 1
+        # Partial products / the gathered operand go to the two halves of `partial` in turn, which is what lets the
+        # reduce-scatter and all-gather forms run without a handshake at their start and end.  The first launch after
+        # restart_alternation() (start of a step) begins at half 0 and makes all ranks wait for each other once, so
+        # that a captured step can be replayed whatever its number of launches.
+        half, sync_entry = self._count & 1, int(self._count == 0)
+        self._count += 1
+        self._last_half = half
         check(lib().sb200_gemm_tp(
             a.data_ptr(), w.data_ptr(), _lib.ptr(c), _lib.ptr(c_pre), _lib.ptr(bias), M, N, Kd, a.stride(0),
             w.stride(0), N, int(b_mn), _ACT[act], _lib.dt(a.dtype), mode, self.partial.c_ptrs, self.out.c_ptrs,
             self.flags.c_ptrs, self.partial.multicast_ptr if mc else None, self.out.multicast_ptr if mc else None,
-            FLAG_STRIDE, self.local.data_ptr(), self.local.data_ptr() + 4, self.rank, self.world, self.timeout_s,
-            _lib.sm_count(), K.status_word().data_ptr(), _lib.stream()), "sb200_gemm_tp")
+            FLAG_STRIDE, self.local.data_ptr(), self.local.data_ptr() + 4, self.rank, self.world, self.max_elements,
+            half, sync_entry, self.timeout_s, max(2, _lib.sm_count() - self.reserved_sms) // 2 * 2,
+            K.status_word().data_ptr(), _lib.stream()), "sb200_gemm_tp")
+
+    def restart_alternation(self) -> None:
+        """The next launch starts a new count of the buffer alternation (all ranks call this at the same point)."""
+        self._count = 0
 
     def _verify(self, what: str, got: torch.Tensor, ref: torch.Tensor, shape: tuple) -> None:
         """SB200_FUSED_TP_VERIFY=1: every fused launch is compared with GEMM + NCCL (debugging aid; slow)."""
@@ -144,7 +163,8 @@ class FusedTPWorkspace:
 
     def gathered(self, M: int, Kd: int) -> torch.Tensor:
         """The operand gathered by the last :meth:`allgather_gemm` (a view of the workspace)."""
-        return self.partial.tensor[:M * Kd].view(M, Kd)
+        base = self._last_half * self.max_elements
+        return self.partial.tensor[base:base + M * Kd].view(M, Kd)
 
     def cached_gather(self, shard: torch.Tensor) -> Optional[torch.Tensor]:
         """The gathered rows of ``shard`` if the previous launch on this workspace gathered exactly this tensor
@@ -174,6 +194,14 @@ class FusedTPWorkspace:
 _WORKSPACES: dict[Any, Optional[FusedTPWorkspace]] = {}
 
 
+def begin_step() -> None:
+    """Start of a training or evaluation step (called by the engine on every rank): the fused workspaces start their
+    buffer alternation anew, so every step issues the same launches whether it runs eagerly or as a replayed graph."""
+    for ws in _WORKSPACES.values():
+        if ws is not None:
+            ws.restart_alternation()
+
+
 def workspace_for(topology: Any, elements: int) -> Optional[FusedTPWorkspace]:
     """The fused workspace of the topology's tensor-parallel group (created on first use by all ranks of the group
     together), or None where the fused path does not apply."""
@@ -183,17 +211,17 @@ def workspace_for(topology: Any, elements: int) -> Optional[FusedTPWorkspace]:
         return None
     if topology.config.model_parallel_size > 8 or not _lib.lib_has("sb200_gemm_tp"):
         return None
-    # With pipeline stages, NCCL send / receive kernels of other streams share the SMs with the fused kernels, whose
-    # CTAs wait for their peers' CTAs: kept apart, so that no wait can depend on a kernel that is not resident.
-    if topology.config.pipe_parallel_size > 1:
-        return None
     key = id(topology)
     ws = _WORKSPACES.get(key)
     if key not in _WORKSPACES or (ws is not None and ws.max_elements < elements):
         try:
             size = max(elements, int(os.environ.get("SB200_FUSED_TP_ELEMENTS", str(64 * 1024 * 1024))))
+            # With pipeline stages, send / receive kernels of other streams share the SMs with the fused kernels,
+            # whose CTAs wait for their peers' CTAs: the grid leaves as many SMs free as those copies can occupy
+            # (Topology.reserved_sms), so that no wait depends on a CTA that cannot become resident.
             ws = FusedTPWorkspace(topology.model_parallel_group, topology.device, size,
-                                  os.environ.get("SB200_P2P_MULTICAST", "1") != "0")
+                                  os.environ.get("SB200_P2P_MULTICAST", "1") != "0",
+                                  reserved_sms=getattr(topology, "reserved_sms", 0))
         except Exception as e:  # noqa: BLE001 - no peer access / symmetric memory on this machine
             from ..core.logging import logger
 

@@ -6,9 +6,15 @@ model keeps exactly the kernel's ordering rules and nothing of its arithmetic de
 
 * flags only grow: a flag word holds the epoch (launch number) of the last launch that set it, a wait is ``>= epoch``;
 * all-reduce / reduce-scatter: a tile's partial product is published to the tile's owner, the owner reduces once all
-  ranks have published, a launch ends only after every rank has reported the end of its reductions;
-* all-gather: a rank may be written to only after it has entered the launch; a row block is pushed in column groups,
-  each with its own flag; the tile loads of a block wait for all its groups;
+  ranks have published; an all-reduce launch (whose output is written by the peers) ends only after every rank has
+  reported the end of its reductions;
+* all-gather: a row block is pushed in column groups, each with its own flag; the tile loads of a block wait for all
+  its groups;
+* the partial products / the gathered operand live in two buffers that consecutive launches use in turn, so a
+  buffer is rewritten two launches after it was filled; no rank can finish a launch before every peer has entered
+  it, hence whoever read the buffer is done by then.  The first launch of a count (``sync_entry``) starts at buffer 0
+  and first waits until every rank has entered it (a captured training step is replayed from its first launch
+  whatever buffer its last launch used);
 * between launches a rank may read its gathered operand (linears that share an input): nobody may write it then.
 
 Random delays shuffle the interleavings.  The model checks the results against numpy, that no wait runs out, and that
@@ -39,7 +45,8 @@ class Workspace:
     def __init__(self, W: int, max_elements: int, flag_stride: int = 64):
         self.W = W
         self.stride = flag_stride
-        self.partial = [np.zeros(max_elements, dtype=np.float64) for _ in range(W)]
+        self.half_elems = max_elements
+        self.partial = [np.zeros(2 * max_elements, dtype=np.float64) for _ in range(W)]  # two buffers used in turn
         self.out = [np.zeros(max_elements, dtype=np.float64) for _ in range(W)]
         self.flags = [np.zeros((W + 2) * flag_stride, dtype=np.int64) for _ in range(W)]
         self.epoch = [0] * W
@@ -65,8 +72,8 @@ def _jitter(rng: random.Random, scale: float) -> None:
 
 
 def launch(ws: Workspace, rank: int, mode: int, a: np.ndarray, b: np.ndarray, ctas: int, seed: int,
-           jitter: float = 2e-4, timeout: float = 20.0, groups: int = 2,
-           wait_for_entry: bool = True) -> Optional[np.ndarray]:
+           jitter: float = 2e-4, timeout: float = 20.0, groups: int = 2, half: int = 0,
+           sync_entry: bool = False) -> Optional[np.ndarray]:
     """One rank's launch.  ``a``: ``[M, K]`` (modes 0, 1) or this rank's ``[M / W, K]`` shard (mode 2); ``b``: ``[K, N]``.
     Returns the reduced ``[M, N]`` (mode 0), this rank's rows of it (mode 1) or the local product (mode 2)."""
     W = ws.W
@@ -84,8 +91,18 @@ def launch(ws: Workspace, rank: int, mode: int, a: np.ndarray, b: np.ndarray, ct
     elif mode == ALLGATHER:
         shift = rank * (m_tiles // W)
     result = np.zeros((M, N)) if mode != REDUCE_SCATTER else np.zeros((shard_rows, N))
-    partial = ws.partial[rank][:M * N].reshape(M, N)
+    hoff = half * ws.half_elems
+
+    def buffer_of(q: int, cols: int) -> np.ndarray:
+        return ws.partial[q][hoff:hoff + M * cols].reshape(M, cols)
+
+    partial = buffer_of(rank, N)
     errors: list[BaseException] = []
+    if sync_entry:  # every CTA waits (thread 0 of the kernel, before the roles start); CTA 0 signals
+        for q in range(W):
+            ws.flags[q][(W + 1) * stride + rank] = epoch
+        for q in range(W):
+            _wait(ws.flags[rank], (W + 1) * stride + q, epoch, timeout, f"rank {rank}: entry of rank {q}", ws.failed)
 
     def tile_of(cta: int, i: int) -> int:
         return (cta + i * ctas + shift) % m_tiles
@@ -105,8 +122,7 @@ def launch(ws: Workspace, rank: int, mode: int, a: np.ndarray, b: np.ndarray, ct
                     for g in range(groups):  # tile loads wait for every column group of the row block
                         _wait(ws.flags[rank], src * stride + rb * groups + g, epoch, timeout,
                               f"rank {rank} rows of rank {src} block {rb} group {g}", ws.failed)
-                    gathered = ws.partial[rank][:M * K].reshape(M, K)
-                    result[rows] = gathered[rows] @ b
+                    result[rows] = buffer_of(rank, K)[rows] @ b
                 else:
                     _jitter(rng, jitter)
                     partial[rows] = a[rows] @ b  # epilogue: the partial tile, then the flag at the owner
@@ -118,12 +134,6 @@ def launch(ws: Workspace, rank: int, mode: int, a: np.ndarray, b: np.ndarray, ct
         rng = random.Random(seed * 1000 + 500 + cta)
         try:
             if mode == ALLGATHER:
-                if cta == 0:
-                    for q in range(W):
-                        ws.flags[q][(W + 1) * stride + rank] = epoch  # "entered": this rank may be written to
-                for q in range(W if wait_for_entry else 0):  # (switched off only to show what the rule prevents)
-                    _wait(ws.flags[rank], (W + 1) * stride + q, epoch, timeout, f"rank {rank}: entry of rank {q}",
-                          ws.failed)
                 blocks = shard_rows // BM
                 cw = (K + groups - 1) // groups
                 for item in range(cta, blocks * groups, ctas):
@@ -131,7 +141,7 @@ def launch(ws: Workspace, rank: int, mode: int, a: np.ndarray, b: np.ndarray, ct
                     _jitter(rng, jitter)
                     cols = slice(g * cw, min(K, (g + 1) * cw))
                     for q in range(W):
-                        dst = ws.partial[q][:M * K].reshape(M, K)
+                        dst = buffer_of(q, K)
                         dst[rank * shard_rows + rb * BM: rank * shard_rows + (rb + 1) * BM, cols] = \
                             a[rb * BM:(rb + 1) * BM, cols]
                     for q in range(W):
@@ -146,7 +156,7 @@ def launch(ws: Workspace, rank: int, mode: int, a: np.ndarray, b: np.ndarray, ct
                           ws.failed)
                 _jitter(rng, jitter)
                 rows = slice(tile * BM, (tile + 1) * BM)
-                total = sum(ws.partial[q][:M * N].reshape(M, N)[rows] for q in range(W))  # rank order
+                total = sum(buffer_of(q, N)[rows] for q in range(W))  # rank order
                 if mode == REDUCE_SCATTER:
                     result[tile * BM - rank * shard_rows: (tile + 1) * BM - rank * shard_rows] = total
                 else:
@@ -166,12 +176,14 @@ def launch(ws: Workspace, rank: int, mode: int, a: np.ndarray, b: np.ndarray, ct
             last = ws.done_ctas[rank] == ctas
             if last:
                 ws.done_ctas[rank] = 0
-        if last:  # the last CTA: tell every rank, wait for every rank, then advance the epoch
+        if last:  # the last CTA advances the epoch; after an all-reduce it first tells and waits for every rank
             try:
-                for q in range(W):
-                    ws.flags[q][W * stride + rank] = epoch
-                for q in range(W):
-                    _wait(ws.flags[rank], W * stride + q, epoch, timeout, f"rank {rank}: end of rank {q}", ws.failed)
+                if mode == ALLREDUCE:
+                    for q in range(W):
+                        ws.flags[q][W * stride + rank] = epoch
+                    for q in range(W):
+                        _wait(ws.flags[rank], W * stride + q, epoch, timeout, f"rank {rank}: end of rank {q}",
+                              ws.failed)
                 ws.epoch[rank] = epoch
             except BaseException as e:  # noqa: BLE001
                 errors.append(e)
@@ -189,10 +201,14 @@ def launch(ws: Workspace, rank: int, mode: int, a: np.ndarray, b: np.ndarray, ct
 
 
 def run_sequence(W: int, modes: list[int], seed: int = 0, ctas: int = 3, M: int = 24, N: int = 5, K: int = 6,
-                 jitter: float = 2e-4, wait_for_entry: bool = True, slow_reader: Optional[int] = None) -> None:
+                 jitter: float = 2e-4, alternate: bool = True, slow_reader: Optional[int] = None,
+                 step_length: Optional[int] = None) -> None:
     """All ranks run the same sequence of launches (as a training step does) with their own operands and random
     delays between launches; after an all-gather launch a rank keeps reading its gathered operand until it enters
-    its next launch and checks that it does not change.  Raises :class:`ProtocolError` on any violation."""
+    its next launch and checks that it does not change.  Every ``step_length`` launches (default: never again after
+    the first) the buffer alternation starts anew with a launch that synchronises on entry, as at the start of a
+    training step.  ``alternate=False`` keeps every launch in buffer 0 (to show what the alternation prevents).
+    Raises :class:`ProtocolError` on any violation."""
     M = (M + BM * W - 1) // (BM * W) * (BM * W)
     ws = Workspace(W, max(M * N, M * K))
     rng0 = np.random.default_rng(seed)
@@ -217,8 +233,10 @@ def run_sequence(W: int, modes: list[int], seed: int = 0, ctas: int = 3, M: int 
         try:
             for step, mode in enumerate(modes):
                 a, b, expect, full = operands[step]
+                count = step % step_length if step_length else step
+                half = count & 1 if alternate else 0
                 got = launch(ws, rank, mode, a[rank], b[rank], ctas, seed * 131 + step * 7 + rank, jitter,
-                             wait_for_entry=wait_for_entry)
+                             half=half, sync_entry=count == 0)
                 if not np.allclose(got, expect[rank]):
                     raise ProtocolError(f"rank {rank} launch {step} (mode {mode}): wrong result")
                 if mode == ALLGATHER:
@@ -227,7 +245,8 @@ def run_sequence(W: int, modes: list[int], seed: int = 0, ctas: int = 3, M: int 
                         _jitter(rng, 4 * jitter)
                         if rank == slow_reader:
                             time.sleep(0.05)
-                        if not np.array_equal(ws.partial[rank][:M * K].reshape(M, K), full):
+                        base = half * ws.half_elems
+                        if not np.array_equal(ws.partial[rank][base:base + M * K].reshape(M, K), full):
                             raise ProtocolError(f"rank {rank}: gathered operand changed after launch {step}")
                 else:
                     _jitter(rng, 4 * jitter)

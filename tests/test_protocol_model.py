@@ -24,10 +24,20 @@ def test_more_ctas_than_tiles_and_a_single_cta():
     run_sequence(2, LAYER_FORWARD, seed=4, ctas=1)
 
 
-def test_pushing_before_the_peer_has_entered_is_what_the_entry_flags_prevent():
-    """Without the rule, a rank that is still reading its gathered operand (a linear sharing the input) sees it
-    overwritten by a peer that has already started the next all-gather launch."""
+def test_a_buffer_is_rewritten_only_two_launches_later_which_is_what_the_alternation_is_for():
+    """With a single buffer and no handshake, a rank that is still reading its gathered operand (a linear sharing the
+    input) sees it overwritten by a peer that has already started the next all-gather launch."""
     with pytest.raises(ProtocolError, match="gathered operand changed"):
         for seed in range(5):  # the slow reader makes the overlap all but certain; a few seeds make it certain
-            run_sequence(2, [ALLGATHER, ALLGATHER], seed=seed, wait_for_entry=False, slow_reader=1, M=8, ctas=2)
-    run_sequence(2, [ALLGATHER, ALLGATHER], seed=0, wait_for_entry=True, slow_reader=1, M=8, ctas=2)
+            run_sequence(2, [ALLGATHER, ALLGATHER], seed=seed, alternate=False, slow_reader=1, M=8, ctas=2)
+    for seed in range(3):
+        run_sequence(2, [ALLGATHER, ALLGATHER, ALLGATHER], seed=seed, alternate=True, slow_reader=1, M=8, ctas=2)
+
+
+@pytest.mark.parametrize("ranks", [2, 3])
+def test_steps_with_an_odd_number_of_launches_restart_the_alternation(ranks):
+    """A replayed step always begins in buffer 0 with a launch that waits for all ranks, whatever buffer the last
+    launch of the previous step used."""
+    step = [ALLGATHER, REDUCE_SCATTER, ALLGATHER]
+    run_sequence(ranks, step * 4, seed=7, step_length=3, slow_reader=ranks - 1)
+    run_sequence(ranks, [REDUCE_SCATTER] * 5, seed=8, step_length=1)
