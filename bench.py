@@ -66,6 +66,8 @@ def parse_args() -> argparse.Namespace:
     p.add_argument("--grad-accum", type=int, default=None,
                    help="micro batches per step and data-parallel rank (default: from the config's global batch)")
     p.add_argument("--layers", type=int, default=None, help="override the layer count (exploration only)")
+    p.add_argument("--mp", type=int, default=None, help="override the config's tensor-parallel size")
+    p.add_argument("--pp", type=int, default=None, help="override the config's number of pipeline stages")
     p.add_argument("--sequence-parallel", action="store_true",
                    help="shard the activations between the tensor-parallel linears over the tokens")
     return p.parse_args()
@@ -74,6 +76,8 @@ def parse_args() -> argparse.Namespace:
 def layout(args: argparse.Namespace, world: int) -> dict:
     """Resolve the named config against the number of ranks: parallel sizes, accumulation steps, labels."""
     c = CONFIGS[args.config]
+    if getattr(args, "mp", None) or getattr(args, "pp", None):
+        c = dict(c, mp=args.mp or c["mp"], pp=args.pp or c["pp"])
     pp = c["pp"] if world % c["pp"] == 0 and world >= c["pp"] * min(c["mp"], 2) else 1
     mp = c["mp"]
     while mp > 1 and (world // pp) % mp:
