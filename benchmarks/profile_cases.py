@@ -116,6 +116,56 @@ def case_attention_bwd(iters: int) -> dict:
             "bytes": qkv.numel() * 2 * 3}
 
 
+def case_attention_fwd_d64(iters: int) -> dict:
+    """The forward kernel alone at head size 64 (separate q, k, v; no rotary embedding, no copies)."""
+    from scaling_b200.ops.attention import flash_attention
+
+    q, k, v = (torch.randn(TOKENS, HEADS, 64, device="cuda", dtype=torch.bfloat16) for _ in range(3))
+    cu = torch.arange(0, TOKENS + 1, 2048, device="cuda", dtype=torch.int32)
+    with torch.no_grad():
+        ms = _time(lambda: flash_attention(q, k, v, cu, None, causal=True), iters, _flush_buffer())
+    flops = 4.0 * 8 * HEADS * 2048 * 2048 * 64 / 2
+    return {"kernel": "fa_fwd_kernel<64>", "ms": ms, "tflops": flops / ms / 1e9, "bytes": 4 * q.numel() * 2}
+
+
+def _attention_inputs_d128():
+    """Two documents of 4096 tokens, 16 query / 4 key-value heads of 128 (the 7B model on two tensor-parallel ranks)."""
+    T, hq, hkv = 2 * 4096, 16, 4
+    q = torch.randn(T, hq, 128, device="cuda", dtype=torch.bfloat16)
+    k = torch.randn(T, hkv, 128, device="cuda", dtype=torch.bfloat16)
+    v = torch.randn(T, hkv, 128, device="cuda", dtype=torch.bfloat16)
+    cu = torch.arange(0, T + 1, 4096, device="cuda", dtype=torch.int32)
+    return q, k, v, cu, 4.0 * 2 * hq * 4096 * 4096 * 128 / 2
+
+
+def case_attention_fwd_d128(iters: int) -> dict:
+    """Causal grouped-query attention forward at head size 128."""
+    from scaling_b200.ops.attention import flash_attention
+
+    q, k, v, cu, flops = _attention_inputs_d128()
+    with torch.no_grad():
+        ms = _time(lambda: flash_attention(q, k, v, cu, None, causal=True), iters, _flush_buffer())
+    return {"kernel": "fa_fwd_kernel<128>", "ms": ms, "tflops": flops / ms / 1e9,
+            "bytes": (2 * q.numel() + 2 * k.numel()) * 2}
+
+
+def case_attention_bwd_d128(iters: int) -> dict:
+    """Forward + backward of the same attention (backward = delta, dK/dV with the head group split, dQ)."""
+    from scaling_b200.ops.attention import flash_attention
+
+    q, k, v, cu, flops = _attention_inputs_d128()
+    q.requires_grad_(), k.requires_grad_(), v.requires_grad_()
+    do = torch.randn_like(q)
+
+    def run():
+        flash_attention(q, k, v, cu, None, causal=True).backward(do)
+        q.grad = k.grad = v.grad = None
+
+    ms = _time(run, iters, _flush_buffer())
+    return {"kernel": "fa_fwd + fa_bwd_dkdv + fa_bwd_dq <128>", "ms": ms, "tflops": 3.5 * flops / ms / 1e9,
+            "bytes": (4 * q.numel() + 4 * k.numel()) * 2}
+
+
 def case_norm(iters: int) -> dict:
     """LayerNorm forward + backward on [16384, 768]."""
     x = torch.randn(TOKENS, HIDDEN, device="cuda", dtype=torch.bfloat16, requires_grad=True)
@@ -145,7 +195,8 @@ def case_adamw(iters: int) -> dict:
 
 
 CASES = {"gemm_fwd": case_gemm_fwd, "gemm_plain": case_gemm_plain, "gemm_wgrad": case_gemm_wgrad,
-         "attention_fwd": case_attention_fwd, "attention_bwd": case_attention_bwd, "norm": case_norm,
+         "attention_fwd": case_attention_fwd, "attention_bwd": case_attention_bwd,
+         "attention_fwd_d64": case_attention_fwd_d64, "attention_fwd_d128": case_attention_fwd_d128, "attention_bwd_d128": case_attention_bwd_d128, "norm": case_norm,
          "adamw": case_adamw}
 
 

@@ -21,6 +21,8 @@
 // All waits are bounded; on expiry the CTA raises *status and leaves through the common exit (TMEM freed).
 #include <cuda.h>
 
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace {
@@ -88,7 +90,6 @@ __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
   __nv_bfloat162 t = __floats2bfloat162_rn(a, b);
   return *reinterpret_cast<uint32_t*>(&t);
 }
-
 // K-major operand descriptor for k-step kk (16 elements per step) of a [128 x (64*panels)] tile
 __device__ __forceinline__ uint64_t desc_kmajor(uint32_t base, int kk) {
   return sb::umma_smem_desc(base + (kk >> 2) * PANEL_BYTES + (kk & 3) * 32, 16, 1024);
@@ -98,6 +99,20 @@ __device__ __forceinline__ uint64_t desc_kmajor(uint32_t base, int kk) {
 __device__ __forceinline__ uint64_t desc_mnmajor(uint32_t base, int kk) {
   return sb::umma_smem_desc(base + kk * 2048, PANEL_BYTES, 1024);
 }
+
+// Phase timing of the forward softmax warps (debug builds with -DSB200_FA_TIMING only): one thread per CTA adds the
+// cycles it spent in each phase of the tile loop to g_fa_phase; sb200_fa_timing reads / clears the totals.
+#ifdef SB200_FA_TIMING
+__device__ unsigned long long g_fa_phase[10];
+#define FA_T(i)                                                                          \
+  do {                                                                                   \
+    const long long now_ = clock64();                                                    \
+    if (timing_thread) atomicAdd(&g_fa_phase[i], (unsigned long long)(now_ - t_last));  \
+    t_last = now_;                                                                       \
+  } while (0)
+#else
+#define FA_T(i)
+#endif
 
 // allowed key range for query row t
 __device__ __forceinline__ void row_range(const FaParams& p, int t, int& lo, int& hi) {
@@ -119,28 +134,37 @@ __device__ __forceinline__ void row_range(const FaParams& p, int t, int& lo, int
 template <int D> struct FaFwdCfg {
   static constexpr bool TWO = D == 64;             // two CTAs per SM
   static constexpr int SBUF = TWO ? 1 : 2;         // S accumulators in TMEM
-  static constexpr int VST = TWO ? 1 : 2;          // V stages (K always has two)
+  // With two CTAs per SM there is room for three K / V stages per CTA.  K(j + 1) is loaded as soon as S(j) has been
+  // multiplied and is used a whole softmax later, so one K stage hides its load; V(j) is needed right after the
+  // softmax of tile j and its stage is released only by P V of the tile before, so V gets the second stage.
+  static constexpr int KST = TWO ? 1 : 2;          // K stages
+  static constexpr int VST = 2;                    // V stages
   static constexpr int TMEM_COLS = TWO ? 256 : 512;
   static constexpr int PANELS = D / 64;
   static constexpr int TILE_BYTES = PANELS * PANEL_BYTES;
-  static constexpr int SMEM = TILE_BYTES * (1 + 2 + VST) + 2 * PANEL_BYTES + 1024 + 256;
+  static constexpr int XCH_BYTES = 4096;  // row maxima / sums exchanged between the two threads of a row
+  static constexpr int SMEM = TILE_BYTES * (1 + KST + VST) + 2 * PANEL_BYTES + 1024 + 256 + XCH_BYTES;
 };
 
-template <int D, bool DROP>
-__global__ void __launch_bounds__(FA_THREADS, FaFwdCfg<D>::TWO ? 2 : 1)
+// ROWT = threads per query row: 1 (four softmax warps, thread = row) or 2 (eight softmax warps; warps w and w + 4
+// share the rows of a TMEM lane quadrant and take 64 key columns and half of the output columns each; they exchange
+// their row maxima through shared memory once per tile and their row sums once at the end).  Twice the warps hide
+// the TMEM and arithmetic latencies that two warps per scheduler leave exposed.
+template <int D, bool DROP, int ROWT>
+__global__ void __launch_bounds__(64 + 128 * ROWT, FaFwdCfg<D>::TWO ? 2 : 1)
     fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                   const __grid_constant__ CUtensorMap tmV, const FaParams p) {
   using Cfg = FaFwdCfg<D>;
   constexpr int PANELS = Cfg::PANELS;
   constexpr int TILE_BYTES = Cfg::TILE_BYTES;
-  constexpr int SBUF = Cfg::SBUF, VST = Cfg::VST;
+  constexpr int SBUF = Cfg::SBUF, VST = Cfg::VST, KST = Cfg::KST;
   constexpr uint32_t S_COL = 0;               // SBUF buffers of 128 columns
   constexpr uint32_t O_COL = SBUF * TILE;     // two O buffers of D columns
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sQ = smem;
-  uint8_t* sK = sQ + TILE_BYTES;           // 2 stages
-  uint8_t* sV = sK + 2 * TILE_BYTES;       // VST stages
+  uint8_t* sK = sQ + TILE_BYTES;           // KST stages
+  uint8_t* sV = sK + KST * TILE_BYTES;     // VST stages
   uint8_t* sP = sV + VST * TILE_BYTES;     // 2 panels
   uint64_t* bars = reinterpret_cast<uint64_t*>(sP + 2 * PANEL_BYTES);
   uint64_t* q_full = bars;          // 1
@@ -154,9 +178,17 @@ __global__ void __launch_bounds__(FA_THREADS, FaFwdCfg<D>::TWO ? 2 : 1)
   uint64_t* s_empty = bars + 14;    // 1 (single S buffer only)
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  float* xmax = reinterpret_cast<float*>(bars + 32);  // [tile parity][half][row]
+  float* xsum = xmax + 4 * TILE;                      // [half][row]
+  volatile int* xseq = reinterpret_cast<volatile int*>(xsum + 2 * TILE);  // [half][row]: tiles published so far
 
+#ifdef SB200_FA_TIMING
+  const long long t_entry = clock64();
+#endif
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int q0 = blockIdx.x * TILE;
+  // causal: later query tiles of a document see more keys; they are started first, so that the short ones fill the
+  // end of the launch instead of a few long ones determining it
+  const int q0 = (p.causal ? gridDim.x - 1 - blockIdx.x : blockIdx.x) * TILE;
   const int h = blockIdx.y;
   const int hk = h / (p.Hq / p.Hkv);
 
@@ -178,11 +210,13 @@ __global__ void __launch_bounds__(FA_THREADS, FaFwdCfg<D>::TWO ? 2 : 1)
       sb::mbar_init(&s_full[i], 1);
       sb::mbar_init(&o_full[i], 1);
     }
-    sb::mbar_init(p_full, 4);
-    sb::mbar_init(s_empty, 4);
+    sb::mbar_init(p_full, 4 * ROWT);
+    sb::mbar_init(s_empty, 4 * ROWT);
     *abort_flag = 0;
     sb::mbar_fence_init();
   }
+  if (ROWT == 2)
+    for (int i = threadIdx.x; i < 2 * TILE; i += blockDim.x) xseq[i] = 0;
   if (warp == 1) {
     sb::tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
     sb::tmem_relinquish();
@@ -201,8 +235,8 @@ __global__ void __launch_bounds__(FA_THREADS, FaFwdCfg<D>::TWO ? 2 : 1)
 #pragma unroll
       for (int pn = 0; pn < PANELS; ++pn) sb::tma_load_2d(sQ + pn * PANEL_BYTES, &tmQ, q_full, h * p.ldq_head + pn * 64, q0);
       for (int j = 0; j < n_tiles; ++j) {
-        const int kst = j & 1, vst = j % VST;
-        const uint32_t kph = (j >> 1) & 1, vph = (j / VST) & 1;
+        const int kst = j % KST, vst = j % VST;
+        const uint32_t kph = (j / KST) & 1, vph = (j / VST) & 1;
         const int kv0 = (kv_begin + j) * TILE;
         if (!sb::mbar_wait(&k_empty[kst], kph ^ 1, abort_flag)) break;
         sb::mbar_expect_tx(&k_full[kst], TILE_BYTES);
@@ -223,8 +257,8 @@ __global__ void __launch_bounds__(FA_THREADS, FaFwdCfg<D>::TWO ? 2 : 1)
       const uint32_t q_addr = sb::smem_u32(sQ), p_addr = sb::smem_u32(sP);
       bool ok = sb::mbar_wait(q_full, 0, abort_flag);
       auto issue_s = [&](int j) -> bool {
-        const int kst = j & 1, sbuf = j % SBUF;
-        if (!sb::mbar_wait(&k_full[kst], (j >> 1) & 1, abort_flag)) return false;
+        const int kst = j % KST, sbuf = j % SBUF;
+        if (!sb::mbar_wait(&k_full[kst], (j / KST) & 1, abort_flag)) return false;
         if (SBUF == 1 && j > 0) {  // the softmax threads have read S(j - 1) out of the only buffer
           if (!sb::mbar_wait(s_empty, (j - 1) & 1, abort_flag)) return false;
         }
@@ -254,67 +288,130 @@ __global__ void __launch_bounds__(FA_THREADS, FaFwdCfg<D>::TWO ? 2 : 1)
     }
   } else {
     const int quad = warp & 3;
+    const int half = ROWT == 2 ? (warp - 2) >> 2 : 0;  // which key columns and output columns of the row are this thread's
+    constexpr int CPT = 4 / ROWT;                      // 32-column chunks of S per thread
+    constexpr int DT = D / ROWT;                       // output columns per thread
+    const int c_begin = half * CPT, c_end = c_begin + CPT;
     const int r = quad * 32 + lane;   // row inside the tile = TMEM lane
     const int t = q0 + r;
     int lo, hi;
     row_range(p, t, lo, hi);
     const uint32_t t_lane = tmem_base + ((uint32_t)(quad * 32) << 16);
     const float sl2 = p.scale_log2;
+    // Hand `mine` to the other thread of this row and take its value: the value goes to `vals[half][row]`, then the
+    // row's sequence word is raised to `seq`; the partner's word is awaited with a bound (a partner that left after a
+    // failed wait has raised the abort flag).  Returns false when the wait ends without the partner's value.
+    auto exchange = [&](float* vals, int seq, float mine, float& other) -> bool {
+      volatile float* mine_slot = vals + half * TILE + r;
+      *mine_slot = mine;
+      __threadfence_block();
+      xseq[half * TILE + r] = seq;
+      unsigned spins = 0;
+      while (xseq[(half ^ 1) * TILE + r] < seq) {
+        if (*abort_flag || ++spins > (1u << 26)) {
+          *abort_flag = 1;
+          return false;
+        }
+      }
+      __threadfence_block();
+      other = *(volatile float*)(vals + (half ^ 1) * TILE + r);
+      return true;
+    };
     float m_raw = -1e30f;   // running maximum of the raw scores (the softmax scale is positive)
     float m = __fmul_rn(m_raw, sl2);  // the same in the exp2 domain; kept as a value of its own so that m - mx is exactly 0
                             // while the maximum does not move (recomputing the product could be fused differently)
     float l = 0.f, alpha_prev = 1.f;
-    float o_acc[D];
+    float o_acc[DT];
 #pragma unroll
-    for (int i = 0; i < D; ++i) o_acc[i] = 0.f;
+    for (int i = 0; i < DT; ++i) o_acc[i] = 0.f;
     sb::DropoutRng drng = {};
     if (DROP) drng = sb::dropout_rng(p.rng, p.drop_call);
     const uint32_t drow = (p.drop_head0 + (uint32_t)h) * (uint32_t)p.T + (uint32_t)t;
     bool ok = true;
+#ifdef SB200_FA_TIMING
+    const bool timing_thread = warp == 2 && lane == 0;
+    long long t_last = t_entry;
+    FA_T(7);  // prologue: barrier and TMEM set-up until the softmax threads are ready for the first tile
+#endif
     for (int j = 0; j < n_tiles && ok; ++j) {
       const int sbuf = j % SBUF;
       const int kv0 = (kv_begin + j) * TILE;
       const uint32_t s_addr = t_lane + S_COL + sbuf * TILE;
       if (!sb::mbar_wait(&s_full[sbuf], (j / SBUF) & 1, abort_flag)) { ok = false; break; }
       sb::tc_fence_after();
+      FA_T(0);
       const bool interior = kv0 >= lo && kv0 + TILE - 1 <= hi;  // every key of the tile is allowed for this row
-      // pass 1: row maximum
-      float mx_raw = m_raw;
-#pragma unroll 1
-      for (int ch = 0; ch < 4; ++ch) {
-        uint32_t v[32];
-        sb::tmem_ld32(s_addr + ch * 32, v);
+      // pass 1: row maximum (four independent chains: a 128-long dependent chain is not hidden by two warps per scheduler)
+      float mx4[4] = {m_raw, m_raw, m_raw, m_raw};
+      // With two threads per row a thread's 64 scores fit in registers: they are loaded once (both loads in flight
+      // together, one wait), the S buffer is released at once, and both passes work from registers.  With one thread
+      // per row the 128 scores are read from TMEM chunk by chunk in each pass.
+      constexpr bool KEEP_S = ROWT == 2;
+      uint32_t sv[KEEP_S ? CPT : 1][32];
+      if (KEEP_S) {
+#pragma unroll
+        for (int c = 0; c < CPT; ++c) sb::tmem_ld32(s_addr + (c_begin + c) * 32, sv[c]);
         sb::tmem_ld_wait();
+        if (SBUF == 1) {
+          sb::tc_fence_before();
+          __syncwarp();
+          if (lane == 0) sb::mbar_arrive(s_empty);
+        }
+      }
+#pragma unroll(KEEP_S ? CPT : 1)
+      for (int c = 0; c < CPT; ++c) {
+        const int ch = c_begin + c;
+        uint32_t vt[32];
+        if (!KEEP_S) {
+          sb::tmem_ld32(s_addr + ch * 32, vt);
+          sb::tmem_ld_wait();
+        }
+        const uint32_t (&v)[32] = KEEP_S ? sv[KEEP_S ? c : 0] : vt;
         if (interior) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) mx_raw = fmaxf(mx_raw, __uint_as_float(v[i]));
+          for (int i = 0; i < 32; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(v[i]));
         } else {
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
             const int kidx = kv0 + ch * 32 + i;
-            if (kidx >= lo && kidx <= hi) mx_raw = fmaxf(mx_raw, __uint_as_float(v[i]));
+            if (kidx >= lo && kidx <= hi) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(v[i]));
           }
         }
       }
+      float mx_raw = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+      FA_T(1);
+      if (ROWT == 2) {
+        // the row maximum over all 128 keys: the slots alternate with the tile parity, so a thread that is one tile
+        // ahead writes the other slot, and it cannot be two tiles ahead without the partner's value of the tile between
+        float other;
+        if (!exchange(xmax + (j & 1) * 2 * TILE, j + 1, mx_raw, other)) { ok = false; break; }
+        mx_raw = fmaxf(mx_raw, other);
+      }
       const float mx = __fmul_rn(mx_raw, sl2);  // never contracted into an FMA with its consumers
       const float alpha = fast_exp2(m - mx);
+      FA_T(2);
       // the previous P V must be done before P is overwritten
       if (j > 0) {
         if (!sb::mbar_wait(&o_full[(j - 1) & 1], ((j - 1) >> 1) & 1, abort_flag)) { ok = false; break; }
         sb::tc_fence_after();
       }
+      FA_T(3);
       // pass 2: probabilities -> shared memory (bf16, swizzled K-major), row sum
-      float rs = 0.f;
-#pragma unroll 1
-      for (int ch = 0; ch < 4; ++ch) {
-        uint32_t v[32];
-        sb::tmem_ld32(s_addr + ch * 32, v);
-        sb::tmem_ld_wait();
-        if (SBUF == 1 && ch == 3) {  // S is in registers: the next Q K^T may overwrite the buffer
-          sb::tc_fence_before();
-          __syncwarp();
-          if (lane == 0) sb::mbar_arrive(s_empty);
+      float rs4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll(KEEP_S ? CPT : 1)
+      for (int c = 0; c < CPT; ++c) {
+        const int ch = c_begin + c;
+        uint32_t vt[32];
+        if (!KEEP_S) {
+          sb::tmem_ld32(s_addr + ch * 32, vt);
+          sb::tmem_ld_wait();
+          if (SBUF == 1 && ch == c_end - 1) {  // this warp's part of S is in registers: the next Q K^T may overwrite it
+            sb::tc_fence_before();
+            __syncwarp();
+            if (lane == 0) sb::mbar_arrive(s_empty);
+          }
         }
+        const uint32_t (&v)[32] = KEEP_S ? sv[KEEP_S ? c : 0] : vt;
         float pr[32];
         if (interior) {
 #pragma unroll
@@ -327,7 +424,7 @@ __global__ void __launch_bounds__(FA_THREADS, FaFwdCfg<D>::TWO ? 2 : 1)
           }
         }
 #pragma unroll
-        for (int i = 0; i < 32; ++i) rs += pr[i];
+        for (int i = 0; i < 32; ++i) rs4[i & 3] += pr[i];
         if (DROP) {  // the row sum counts every probability; what reaches P V is the kept part (scaled at the end)
           float mk[32];
           drop_mask32(drng, drow, kv0 + ch * 32, p.drop_thr8, 1.f, mk);
@@ -344,18 +441,20 @@ __global__ void __launch_bounds__(FA_THREADS, FaFwdCfg<D>::TWO ? 2 : 1)
           *reinterpret_cast<uint4*>(sP + swz_offset(r, ch * 32 + g * 8)) = u;
         }
       }
+      FA_T(4);
       sb::fence_proxy_async_smem();
       sb::tc_fence_before();
       __syncwarp();
       if (lane == 0) sb::mbar_arrive(p_full);
-      l = l * alpha + rs;
+      FA_T(5);
+      l = l * alpha + ((rs4[0] + rs4[1]) + (rs4[2] + rs4[3]));
       // fold the previous tile's partial output into the running output
       if (j > 0) {
         const int pst = (j - 1) & 1;
 #pragma unroll
-        for (int ch = 0; ch < D / 32; ++ch) {
+        for (int ch = 0; ch < DT / 32; ++ch) {
           uint32_t v[32];
-          sb::tmem_ld32(t_lane + O_COL + pst * D + ch * 32, v);
+          sb::tmem_ld32(t_lane + O_COL + pst * D + half * DT + ch * 32, v);
           sb::tmem_ld_wait();
 #pragma unroll
           for (int i = 0; i < 32; ++i) o_acc[ch * 32 + i] = fmaf(o_acc[ch * 32 + i], alpha_prev, __uint_as_float(v[i]));
@@ -364,24 +463,30 @@ __global__ void __launch_bounds__(FA_THREADS, FaFwdCfg<D>::TWO ? 2 : 1)
       alpha_prev = alpha;
       m_raw = mx_raw;
       m = mx;
+      FA_T(6);
     }
     if (ok && n_tiles > 0) {
       const int pst = (n_tiles - 1) & 1;
       if (sb::mbar_wait(&o_full[pst], ((n_tiles - 1) >> 1) & 1, abort_flag)) {
         sb::tc_fence_after();
 #pragma unroll
-        for (int ch = 0; ch < D / 32; ++ch) {
+        for (int ch = 0; ch < DT / 32; ++ch) {
           uint32_t v[32];
-          sb::tmem_ld32(t_lane + O_COL + pst * D + ch * 32, v);
+          sb::tmem_ld32(t_lane + O_COL + pst * D + half * DT + ch * 32, v);
           sb::tmem_ld_wait();
 #pragma unroll
           for (int i = 0; i < 32; ++i) o_acc[ch * 32 + i] = fmaf(o_acc[ch * 32 + i], alpha_prev, __uint_as_float(v[i]));
         }
-        if (t < p.T) {
+        if (ROWT == 2) {  // the two threads of a row add their sums (same running maximum, so they are commensurable)
+          float other = 0.f;
+          if (!exchange(xsum, n_tiles + 1, l, other)) ok = false;
+          l += other;
+        }
+        if (ok && t < p.T) {
           const float inv = l > 0.f ? (DROP ? p.keep_scale : 1.f) / l : 0.f;
-          __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(p.O) + ((long)t * p.Hq + h) * D;
+          __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(p.O) + ((long)t * p.Hq + h) * D + half * DT;
 #pragma unroll
-          for (int g = 0; g < D / 8; ++g) {
+          for (int g = 0; g < DT / 8; ++g) {
             uint4 u;
             u.x = pack_bf16(o_acc[g * 8 + 0] * inv, o_acc[g * 8 + 1] * inv);
             u.y = pack_bf16(o_acc[g * 8 + 2] * inv, o_acc[g * 8 + 3] * inv);
@@ -389,10 +494,19 @@ __global__ void __launch_bounds__(FA_THREADS, FaFwdCfg<D>::TWO ? 2 : 1)
             u.w = pack_bf16(o_acc[g * 8 + 6] * inv, o_acc[g * 8 + 7] * inv);
             *reinterpret_cast<uint4*>(orow + g * 8) = u;
           }
-          if (p.lse2) p.lse2[(long)h * p.T + t] = l > 0.f ? m + log2f(l) : -1e30f;
+          if (p.lse2 && half == 0) p.lse2[(long)h * p.T + t] = l > 0.f ? m + log2f(l) : -1e30f;
         }
       }
     }
+#ifdef SB200_FA_TIMING
+    {
+      const long long now_ = clock64();
+      if (timing_thread) {
+        atomicAdd(&g_fa_phase[8], (unsigned long long)(now_ - t_last));   // last P V, normalisation, output
+        atomicAdd(&g_fa_phase[9], 1ull);                                  // CTAs
+      }
+    }
+#endif
   }
 
   if (*abort_flag) {
@@ -762,7 +876,7 @@ __global__ void __launch_bounds__(FA_BWD_THREADS, 1)
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int q0 = blockIdx.x * TILE;
+  const int q0 = (p.causal ? gridDim.x - 1 - blockIdx.x : blockIdx.x) * TILE;  // longest query tiles first
   const int h = blockIdx.y;
   const int hk = h / (p.Hq / p.Hkv);
   int lo_first, hi_first, lo_last, hi_last;
@@ -1003,18 +1117,33 @@ int fa_dropout(FaParams* p, float dropout_p, const long long* rng, unsigned call
   return SB_OK;
 }
 
-template <int D, bool DROP>
-int fa_launch_fwd(dim3 grid, const CUtensorMap& tmQ, const CUtensorMap& tmK, const CUtensorMap& tmV, const FaParams& p,
-                  cudaStream_t stream) {
+template <int D, bool DROP, int ROWT>
+int fa_launch_fwd_rowt(dim3 grid, const CUtensorMap& tmQ, const CUtensorMap& tmK, const CUtensorMap& tmV,
+                       const FaParams& p, cudaStream_t stream) {
   static bool set = false;
   if (!set) {
-    cudaError_t e = cudaFuncSetAttribute(fa_fwd_kernel<D, DROP>, cudaFuncAttributeMaxDynamicSharedMemorySize, fa_fwd_smem<D>());
+    cudaError_t e = cudaFuncSetAttribute(fa_fwd_kernel<D, DROP, ROWT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         fa_fwd_smem<D>());
     if (e != cudaSuccess) return (int)e;
     set = true;
   }
-  fa_fwd_kernel<D, DROP><<<grid, FA_THREADS, fa_fwd_smem<D>(), stream>>>(tmQ, tmK, tmV, p);
+  fa_fwd_kernel<D, DROP, ROWT><<<grid, 64 + 128 * ROWT, fa_fwd_smem<D>(), stream>>>(tmQ, tmK, tmV, p);
   SB_CHECK_LAUNCH();
   return SB_OK;
+}
+template <int D, bool DROP>
+int fa_launch_fwd(dim3 grid, const CUtensorMap& tmQ, const CUtensorMap& tmK, const CUtensorMap& tmV, const FaParams& p,
+                  cudaStream_t stream) {
+  // two threads per row pay off at head size 128 (one CTA per SM: eight instead of four softmax warps); at 64, two
+  // CTAs per SM already give eight.  SB200_FA_ROW_THREADS = 1 | 2 overrides the choice (for measurements).
+  static int rowt = 0;
+  if (!rowt) {
+    const char* e = getenv("SB200_FA_ROW_THREADS");
+    const int want = e ? atoi(e) : 0;
+    rowt = (want == 1 || want == 2) ? want : (D == 128 ? 2 : 1);
+  }
+  if (rowt == 1) return fa_launch_fwd_rowt<D, DROP, 1>(grid, tmQ, tmK, tmV, p, stream);
+  return fa_launch_fwd_rowt<D, DROP, 2>(grid, tmQ, tmK, tmV, p, stream);
 }
 
 template <int D, bool DROP>
@@ -1037,6 +1166,20 @@ int fa_launch_bwd(int tiles, int splits, int hps, const CUtensorMap& tmQ, const 
 }
 
 }  // namespace
+
+#ifdef SB200_FA_TIMING
+// out8: host array of 10 counters (cycles summed over one thread of every CTA; the last is the number of CTAs);
+// reset != 0 clears them afterwards
+SB_API int sb200_fa_timing(unsigned long long* out8, int reset) {
+  cudaError_t e = cudaMemcpyFromSymbol(out8, g_fa_phase, sizeof(g_fa_phase));
+  if (e != cudaSuccess) return (int)e;
+  if (reset) {
+    unsigned long long zero[10] = {};
+    e = cudaMemcpyToSymbol(g_fa_phase, zero, sizeof(zero));
+  }
+  return (int)e;
+}
+#endif
 
 // CUresult of the last failed tensor-map encode of the attention entry points (0 if none failed)
 SB_API int sb200_fa_last_driver_error() { return g_fa_last_driver_error; }
