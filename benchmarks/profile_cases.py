@@ -68,6 +68,26 @@ def case_gemm_plain(iters: int) -> dict:
             "bytes": (x.numel() + w.numel() + out.numel()) * 2}
 
 
+def case_gemm_fp8(iters: int) -> dict:
+    """fc2 forward with e4m3 operands: [16384, 3072] x [768, 3072]^T on the fp8 tensor-core path, bf16 result."""
+    x = torch.randn(TOKENS, 4 * HIDDEN, device="cuda").to(torch.float8_e4m3fn)
+    w = (torch.randn(HIDDEN, 4 * HIDDEN, device="cuda") * 0.02).to(torch.float8_e4m3fn)
+    ms = _time(lambda: K.gemm_fp8(x, w), iters, _flush_buffer())
+    flops = 2.0 * TOKENS * HIDDEN * 4 * HIDDEN
+    return {"kernel": "gemm_tcgen05 (fp8 operands, kind::f8f6f4)", "ms": ms, "tflops": flops / ms / 1e9,
+            "bytes": x.numel() + w.numel() + 2 * TOKENS * HIDDEN}
+
+
+def case_gemm_fp8_large(iters: int) -> dict:
+    """8192 x 8192 x 8192 with e4m3 operands (a compute-bound problem)."""
+    n = 8192
+    x = torch.randn(n, n, device="cuda").to(torch.float8_e4m3fn)
+    w = (torch.randn(n, n, device="cuda") * 0.02).to(torch.float8_e4m3fn)
+    ms = _time(lambda: K.gemm_fp8(x, w), iters, _flush_buffer())
+    return {"kernel": "gemm_tcgen05 (fp8 operands, kind::f8f6f4)", "ms": ms, "tflops": 2.0 * n ** 3 / ms / 1e9,
+            "bytes": 2 * n * n + 2 * n * n}
+
+
 def case_gemm_wgrad(iters: int) -> dict:
     """fc1 weight gradient: dY^T [3072, 16384] x X [16384, 768], accumulated into the gradient buffer."""
     x = torch.randn(TOKENS, HIDDEN, device="cuda", dtype=torch.bfloat16)
@@ -194,7 +214,7 @@ def case_adamw(iters: int) -> dict:
     return {"kernel": "adamw_kernel", "ms": ms, "gbs": nbytes / ms / 1e6, "bytes": nbytes}
 
 
-CASES = {"gemm_fwd": case_gemm_fwd, "gemm_plain": case_gemm_plain, "gemm_wgrad": case_gemm_wgrad,
+CASES = {"gemm_fp8": case_gemm_fp8, "gemm_fp8_large": case_gemm_fp8_large, "gemm_fwd": case_gemm_fwd, "gemm_plain": case_gemm_plain, "gemm_wgrad": case_gemm_wgrad,
          "attention_fwd": case_attention_fwd, "attention_bwd": case_attention_bwd,
          "attention_fwd_d64": case_attention_fwd_d64, "attention_fwd_d128": case_attention_fwd_d128, "attention_bwd_d128": case_attention_bwd_d128, "norm": case_norm,
          "adamw": case_adamw}

@@ -3,8 +3,10 @@
 Each of the three products (forward ``x w^T``, ``grad_y w`` and ``grad_y^T x``) rounds its two
 operands to the configured fp8 formats with saturation and without scaling factors, exactly what
 the reference's ``fp8_linear`` feeds to ``torch._scaled_mm`` (src/scaling/core/fp8/fp8_linear.py:10-110);
-a product whose dtype pair is ``None`` runs unquantised.  The rounded operands are multiplied by the
-tcgen05 GEMM with fp32 accumulation, which matches the scaled-mm result with unit scales.
+a product whose dtype pair is ``None`` runs unquantised.  On a GPU the rounded operands go to the fp8
+tensor-core GEMM (``tcgen05.mma kind::f8f6f4``, fp32 accumulation in TMEM), which is the scaled-mm result with
+unit scales; on CPU ranks, and for shapes whose reduction length is not a multiple of 16, they are widened and
+multiplied in the compute dtype, which gives the same values.
 """
 
 from __future__ import annotations
@@ -28,7 +30,11 @@ def _round(x: torch.Tensor, dtype: Optional[torch.dtype]) -> torch.Tensor:
 
 
 def _mm(a: torch.Tensor, b_t: torch.Tensor, compute: torch.dtype) -> torch.Tensor:
-    """``a @ b_t.T`` with both operands widened to ``compute``."""
+    """``a @ b_t.T``: on the fp8 tensor cores when both operands are fp8, else widened to ``compute``."""
+    if a.is_cuda and compute == torch.bfloat16:
+        a, b_t = a.contiguous(), b_t.contiguous()
+        if K.gemm_fp8_supported(a, b_t):
+            return K.gemm_fp8(a, b_t, out_dtype=compute)
     return K.gemm(a.to(compute).contiguous(), b_t.to(compute).contiguous()) if a.is_cuda and compute != torch.float32 \
         else a.to(compute) @ b_t.to(compute).t()
 
@@ -56,11 +62,11 @@ class _FP8Linear(torch.autograd.Function):
         if ctx.needs_input_grad[0]:
             g = _round(dy2, dt_gi[0]) if dt_gi else dy2
             wq = _round(w, dt_gi[1]) if dt_gi else w
-            dx = _mm(g, wq.to(compute).t().contiguous(), compute).view(x_shape).to(dy.dtype)
+            dx = _mm(g, wq.t().contiguous(), compute).view(x_shape).to(dy.dtype)
         if ctx.needs_input_grad[1]:
             xq = _round(x2, dt_gw[0]) if dt_gw else x2
             g = _round(dy2, dt_gw[1]) if dt_gw else dy2
-            dw = _mm(g.to(compute).t().contiguous(), xq.to(compute).t().contiguous(), compute)
+            dw = _mm(g.t().contiguous(), xq.t().contiguous(), compute)
             dw = dw.to(w.dtype if w.dtype not in (torch.float8_e4m3fn, torch.float8_e5m2) else dy.dtype)
         if has_bias and ctx.needs_input_grad[2]:
             db = dy2.sum(0)

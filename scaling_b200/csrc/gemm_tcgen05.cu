@@ -81,7 +81,8 @@ struct GemmParams {
   long ldc;
   int act;         // 0 none, 1 gelu
   int accumulate;  // C += result
-  int ab_fmt;      // 0 fp16, 1 bf16
+  int ab_fmt;      // 0 fp16, 1 bf16 (16-bit operands; also the format of the bias)
+  int a8_fmt, b8_fmt;  // 8-bit operands (AB8 instantiations): 0 e4m3, 1 e5m2
   int splits;      // k-splits per tile (1: none)
   int tma_store;   // 1: 16-bit C (and C_pre) leave through the tensor maps tmC / tmP
   float* ws_partial;  // split-K: [tiles * splits][BN / 32][128][32] floats
@@ -220,7 +221,9 @@ template <> __device__ __forceinline__ void load8<__half>(const __half* src, flo
 // replicas; or peer loads added in rank order) and store the result to every rank's output (multimem.st or peer
 // stores).  Tiles are reduced while later tiles are still being multiplied.  The last CTA of a launch exchanges
 // completion flags with the peers, so the kernel ends only when this rank's output is complete.
-template <int BN, bool A_MN, bool B_MN, typename OutT, bool PAIR, bool FUSE>
+// AB8: the operands are 8-bit floating point (e4m3 / e5m2, K-major): a k-block is 128 elements = the same 128 bytes per
+// row, an MMA instruction covers 32 of them (kind::f8f6f4), everything after the accumulator is unchanged.
+template <int BN, bool A_MN, bool B_MN, typename OutT, bool PAIR, bool FUSE, bool AB8 = false>
 __global__ void __launch_bounds__(FUSE ? GEMM_THREADS + REDUCER_THREADS : GEMM_THREADS, 1)
     gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                         const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmP,
@@ -251,7 +254,8 @@ __global__ void __launch_bounds__(FUSE ? GEMM_THREADS + REDUCER_THREADS : GEMM_T
   const int num_workers = PAIR ? gridDim.x >> 1 : gridDim.x;
   const int m_tiles = (p.M + BM * CTAS - 1) / (BM * CTAS);
   const int n_tiles = (p.N + BN - 1) / BN;
-  const int num_kb = (p.K + BK - 1) / BK;
+  constexpr int BKE = AB8 ? 2 * BK : BK;  // elements per k-block (128 bytes per row either way)
+  const int num_kb = (p.K + BKE - 1) / BKE;
   const int S = p.splits;
   const int num_units = m_tiles * n_tiles * S;
   const uint32_t epoch = FUSE ? *p.ar.epoch + 1 : 0;  // identifies this launch in the peers' flag words
@@ -344,32 +348,32 @@ __global__ void __launch_bounds__(FUSE ? GEMM_THREADS + REDUCER_THREADS : GEMM_T
             if (A_MN) {
 #pragma unroll
               for (int j = 0; j < BM / 64; ++j)
-                sb::tma_load_2d_pair(a_s + j * 8192, mapA, bar, m_blk * BM + j * 64, kb * BK);
+                sb::tma_load_2d_pair(a_s + j * 8192, mapA, bar, m_blk * BM + j * 64, kb * BKE);
             } else {
-              sb::tma_load_2d_pair(a_s, mapA, bar, kb * BK, m_blk * BM);
+              sb::tma_load_2d_pair(a_s, mapA, bar, kb * BKE, m_blk * BM);
             }
             if (B_MN) {
 #pragma unroll
               for (int j = 0; j < LOAD_BN / 64; ++j)
-                sb::tma_load_2d_pair(b_s + j * 8192, &tmB, bar, b_col0 + j * 64, kb * BK);
+                sb::tma_load_2d_pair(b_s + j * 8192, &tmB, bar, b_col0 + j * 64, kb * BKE);
             } else {
-              sb::tma_load_2d_pair(b_s, &tmB, bar, kb * BK, b_col0);
+              sb::tma_load_2d_pair(b_s, &tmB, bar, kb * BKE, b_col0);
             }
           } else {
             sb::mbar_expect_tx(&full_bar[stage], Cfg::STAGE_BYTES);
             if (A_MN) {
 #pragma unroll
               for (int j = 0; j < BM / 64; ++j)
-                sb::tma_load_2d(a_s + j * 8192, mapA, &full_bar[stage], m_blk * BM + j * 64, kb * BK);
+                sb::tma_load_2d(a_s + j * 8192, mapA, &full_bar[stage], m_blk * BM + j * 64, kb * BKE);
             } else {
-              sb::tma_load_2d(a_s, mapA, &full_bar[stage], kb * BK, m_blk * BM);
+              sb::tma_load_2d(a_s, mapA, &full_bar[stage], kb * BKE, m_blk * BM);
             }
             if (B_MN) {
 #pragma unroll
               for (int j = 0; j < BN / 64; ++j)
-                sb::tma_load_2d(b_s + j * 8192, &tmB, &full_bar[stage], n_blk * BN + j * 64, kb * BK);
+                sb::tma_load_2d(b_s + j * 8192, &tmB, &full_bar[stage], n_blk * BN + j * 64, kb * BKE);
             } else {
-              sb::tma_load_2d(b_s, &tmB, &full_bar[stage], kb * BK, n_blk * BN);
+              sb::tma_load_2d(b_s, &tmB, &full_bar[stage], kb * BKE, n_blk * BN);
             }
           }
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
@@ -379,7 +383,8 @@ __global__ void __launch_bounds__(FUSE ? GEMM_THREADS + REDUCER_THREADS : GEMM_T
   } else if (warp == 1) {
     // ---------------------------------------------------------- MMA issuer
     if (lane == 0 && rank == 0) {  // of a pair, the leader issues the MMAs for both CTAs
-      const uint32_t idesc = sb::umma_idesc_f16(BM * CTAS, BN, p.ab_fmt, A_MN ? 1u : 0u, B_MN ? 1u : 0u);
+      const uint32_t idesc = AB8 ? sb::umma_idesc_f8(BM * CTAS, BN, p.a8_fmt, p.b8_fmt)
+                                 : sb::umma_idesc_f16(BM * CTAS, BN, p.ab_fmt, A_MN ? 1u : 0u, B_MN ? 1u : 0u);
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
@@ -403,8 +408,14 @@ __global__ void __launch_bounds__(FUSE ? GEMM_THREADS + REDUCER_THREADS : GEMM_T
                                         : sb::umma_smem_desc(a_addr + k * 32, 16, 1024);
             const uint64_t bdesc = B_MN ? sb::umma_smem_desc(b_addr + k * 2048, 8192, 1024)
                                         : sb::umma_smem_desc(b_addr + k * 32, 16, 1024);
-            if (PAIR) sb::umma_f16_ss_pair(d_tmem, adesc, bdesc, idesc, (kb > kb0) || (k != 0));
-            else sb::umma_f16_ss(d_tmem, adesc, bdesc, idesc, (kb > kb0) || (k != 0));
+            const uint32_t acc_flag = (kb > kb0) || (k != 0);
+            if (AB8) {
+              if (PAIR) sb::umma_f8_ss_pair(d_tmem, adesc, bdesc, idesc, acc_flag);
+              else sb::umma_f8_ss(d_tmem, adesc, bdesc, idesc, acc_flag);
+            } else {
+              if (PAIR) sb::umma_f16_ss_pair(d_tmem, adesc, bdesc, idesc, acc_flag);
+              else sb::umma_f16_ss(d_tmem, adesc, bdesc, idesc, acc_flag);
+            }
           }
           // frees the smem stage (in both CTAs of a pair) once these MMAs retire
           if (PAIR) sb::umma_commit_pair(&empty_bar[stage], 3);
@@ -872,24 +883,27 @@ EncodeTiledFn get_encode_fn() {
 
 // 2-D row-major tensor [rows, cols] of 2-byte elements with leading dimension ld (elements);
 // box = [box_rows, 64 cols] with the 128-byte swizzle.
+// fp16 = 2 selects 1-byte elements (8-bit floats move as bytes): the box is then 128 elements wide.
 int make_tmap_2d(CUtensorMap* tm, const void* base, long rows, long cols, long ld, int box_rows, int fp16) {
   EncodeTiledFn fn = get_encode_fn();
   if (!fn) return SB_ERR_DRIVER;
+  const int esize = fp16 == 2 ? 1 : 2;
   cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-  cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * esize};
+  cuuint32_t box[2] = {(cuuint32_t)(128 / esize), (cuuint32_t)box_rows};
   cuuint32_t estr[2] = {1, 1};
-  CUresult r = fn(tm, fp16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+  CUresult r = fn(tm, fp16 == 2 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
+                                : (fp16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16), 2,
                   const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? SB_OK : SB_ERR_DRIVER;
 }
 
-template <int BN, bool A_MN, bool B_MN, typename OutT, bool PAIR, bool FUSE = false>
+template <int BN, bool A_MN, bool B_MN, typename OutT, bool PAIR, bool FUSE = false, bool AB8 = false>
 int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmC, const CUtensorMap& tmP,
                 const GemmParams& p, int sm_count, cudaStream_t stream, const CUtensorMap* tmA2 = nullptr) {
   using Cfg = GemmCfg<BN, PAIR>;
-  auto kern = gemm_tcgen05_kernel<BN, A_MN, B_MN, OutT, PAIR, FUSE>;
+  auto kern = gemm_tcgen05_kernel<BN, A_MN, B_MN, OutT, PAIR, FUSE, AB8>;
   static bool attr_set = false;
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
@@ -1040,6 +1054,48 @@ SB_API int sb200_gemm_ws(const void* A, const void* B, void* C, void* C_pre, con
   if (out_dtype == SB_DT_F16 && fp16)
     return dispatch_major<__half>(tmA, tmB, tmC, tmP, p, a_mn, b_mn, shape, sm_count, stream);
   return SB_ERR_BAD_ARG;
+}
+
+// C[M, N] = A[M, K] B[N, K]^T (+ bias) with 8-bit floating-point operands (a_fmt / b_fmt: 0 = e4m3, 1 = e5m2), fp32
+// accumulation on the tensor cores (kind::f8f6f4) and a bf16 or fp32 result; no scaling factors, like a scaled matmul
+// with unit scales (src/scaling/core/fp8/fp8_linear.py:34-43).  lda / ldb (elements = bytes) are multiples of 16.
+SB_API int sb200_gemm_fp8(const void* A, const void* B, void* C, const void* bias, int M, int N, int K, long lda,
+                          long ldb, long ldc, int a_fmt, int b_fmt, int accumulate, int out_dtype, int sm_count,
+                          void* workspace, long workspace_bytes, int* status, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return SB_OK;
+  if (K <= 0 || a_fmt < 0 || a_fmt > 1 || b_fmt < 0 || b_fmt > 1) return SB_ERR_BAD_ARG;
+  if (out_dtype != SB_DT_BF16 && out_dtype != SB_DT_F32) return SB_ERR_BAD_ARG;
+  if ((lda % 16) || (ldb % 16)) return SB_ERR_BAD_ARG;  // TMA: strides are multiples of 16 bytes
+  if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15)) return SB_ERR_BAD_ARG;
+  int shape = 128, splits = 1;
+  const bool ws_ok = workspace && (reinterpret_cast<uintptr_t>(workspace) & 15) == 0;
+  // a k-block of 128 bytes costs what a 16-bit k-block costs: choose tile and split as for a problem of K / 2
+  choose_shape(M, N, (K + 1) / 2, 0, 0, sm_count, ws_ok ? workspace_bytes : 0, &shape, &splits);
+  const int bn = shape == 128 ? 128 : 256;
+  const int b_rows = shape == 512 ? 128 : bn;
+  CUtensorMap tmA, tmB, tmC, tmP;
+  int rc;
+  if ((rc = make_tmap_2d(&tmA, A, M, K, lda, BM, 2))) return rc;
+  if ((rc = make_tmap_2d(&tmB, B, N, K, ldb, b_rows, 2))) return rc;
+  GemmParams p = {};
+  p.C = C; p.C_pre = nullptr; p.bias = bias; p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.act = 0;
+  p.accumulate = accumulate; p.ab_fmt = 1; p.a8_fmt = a_fmt; p.b8_fmt = b_fmt; p.status = status;
+  p.splits = splits;
+  p.ws_counter = reinterpret_cast<int*>(workspace);
+  p.ws_partial = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(workspace) + WS_COUNTER_BYTES);
+  p.tma_store = out_dtype == SB_DT_BF16 && !accumulate && (ldc % 8 == 0) && (reinterpret_cast<uintptr_t>(C) & 15) == 0;
+  tmC = tmA;
+  tmP = tmA;
+  if (p.tma_store && (rc = make_tmap_out(&tmC, C, M, N, ldc, 0))) return rc;
+  if (out_dtype == SB_DT_F32) {
+    if (shape == 512) return launch_gemm<256, false, false, float, true, false, true>(tmA, tmB, tmC, tmP, p, sm_count, stream);
+    if (shape == 256) return launch_gemm<256, false, false, float, false, false, true>(tmA, tmB, tmC, tmP, p, sm_count, stream);
+    return launch_gemm<128, false, false, float, false, false, true>(tmA, tmB, tmC, tmP, p, sm_count, stream);
+  }
+  using T = __nv_bfloat16;
+  if (shape == 512) return launch_gemm<256, false, false, T, true, false, true>(tmA, tmB, tmC, tmP, p, sm_count, stream);
+  if (shape == 256) return launch_gemm<256, false, false, T, false, false, true>(tmA, tmB, tmC, tmP, p, sm_count, stream);
+  return launch_gemm<128, false, false, T, false, false, true>(tmA, tmB, tmC, tmP, p, sm_count, stream);
 }
 
 // Same without a split-K workspace.

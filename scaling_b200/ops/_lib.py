@@ -83,6 +83,7 @@ _SIGS = {
     "sb200_p2p_reduce_scatter": [c_void_p, c_void_p, c_long, c_long, c_int, c_int, c_int, c_void_p],
     "sb200_p2p_all_gather": [c_void_p, c_void_p, c_void_p, c_long, c_long, c_int, c_int, c_int, c_void_p],
     "sb200_gemm_ws": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_long, c_long, c_long, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_long, c_void_p, c_void_p],
+    "sb200_gemm_fp8": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_long, c_long, c_long, c_int, c_int, c_int, c_int, c_int, c_void_p, c_long, c_void_p, c_void_p],
     "sb200_gemm": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_long, c_long, c_long, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
 }
 

@@ -133,6 +133,35 @@ def gemm(
     return out
 
 
+_FP8_FORMATS = {torch.float8_e4m3fn: 0, torch.float8_e5m2: 1}
+
+
+def gemm_fp8_supported(a: torch.Tensor, b: torch.Tensor) -> bool:
+    """True when ``gemm_fp8`` can multiply ``a [M, K]`` and ``b [N, K]`` on the fp8 tensor-core path."""
+    return (a.is_cuda and a.dtype in _FP8_FORMATS and b.dtype in _FP8_FORMATS and a.dim() == 2 and b.dim() == 2
+            and a.shape[1] == b.shape[1] and a.stride(1) == 1 and b.stride(1) == 1 and a.stride(0) % 16 == 0
+            and b.stride(0) % 16 == 0 and a.data_ptr() % 16 == 0 and b.data_ptr() % 16 == 0
+            and _lib.lib_has("sb200_gemm_fp8"))
+
+
+def gemm_fp8(a: torch.Tensor, b: torch.Tensor, bias: Optional[torch.Tensor] = None,
+             out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+    """``a [M, K] @ b [N, K]^T (+ bias)`` with fp8 (e4m3 / e5m2, mixed allowed) operands, unit scales, fp32
+    accumulation in TMEM (``tcgen05.mma kind::f8f6f4``), result in bf16 or fp32."""
+    assert gemm_fp8_supported(a, b), "gemm_fp8: operands must be row-major fp8 with rows of a multiple of 16 elements"
+    assert out_dtype in (torch.bfloat16, torch.float32)
+    M, Kd = a.shape
+    N = b.shape[0]
+    out = torch.empty((M, N), dtype=out_dtype, device=a.device)
+    if bias is not None and (bias.dtype != torch.bfloat16 or not bias.is_contiguous()):
+        bias = bias.to(torch.bfloat16).contiguous()
+    ws = _gemm_workspace(a.device)
+    check(lib().sb200_gemm_fp8(a.data_ptr(), b.data_ptr(), out.data_ptr(), ptr(bias), M, N, Kd, a.stride(0), b.stride(0),
+                               out.stride(0), _FP8_FORMATS[a.dtype], _FP8_FORMATS[b.dtype], 0, dt(out_dtype), sm_count(),
+                               ws.data_ptr(), ws.numel(), status_word().data_ptr(), stream()), "sb200_gemm_fp8")
+    return out
+
+
 _GEMM_WS: dict[int, torch.Tensor] = {}
 _GEMM_WS_BYTES = 64 * 1024 * 1024
 

@@ -571,3 +571,40 @@ def test_flash_attention_dropout(T, Hq, Hkv, D, cu, causal):
     out2.backward(do)
     assert torch.equal(out, out2) and torch.equal(q.grad, q2.grad) and torch.equal(k.grad, k2.grad)
     assert _rel(out, flash_attention(q, k, v, cu_t, None, causal=causal, scale=scale)) > 0.05
+
+
+# ---------------------------------------------------------------------------------------------- fp8 GEMM
+@pytest.mark.parametrize("M,N,K_", [(256, 256, 128), (300, 520, 1040), (4096, 768, 3072), (128, 128, 16), (2000, 3072, 768)])
+@pytest.mark.parametrize("fa,fb", [(torch.float8_e4m3fn, torch.float8_e4m3fn), (torch.float8_e5m2, torch.float8_e4m3fn),
+                                   (torch.float8_e4m3fn, torch.float8_e5m2)])
+def test_gemm_fp8(M, N, K_, fa, fb):
+    """fp8 operands on the tensor cores against the fp32 product of the same (exactly representable) values."""
+    torch.manual_seed(5)
+    a = (torch.randn(M, K_, device=DEV) * 0.5).to(fa)
+    b = (torch.randn(N, K_, device=DEV) * 0.5).to(fb)
+    bias = torch.randn(N, device=DEV, dtype=torch.bfloat16)
+    ref = a.float() @ b.float().t()
+    out32 = K.gemm_fp8(a, b, out_dtype=torch.float32)
+    assert _rel(out32, ref) < 1e-5, _rel(out32, ref)
+    row = ((out32 - ref).abs().amax(-1) / ref.abs().amax(-1).clamp_min(1e-3)).max().item()
+    assert row < 1e-4, row
+    out16 = K.gemm_fp8(a, b, bias=bias)
+    assert out16.dtype == torch.bfloat16 and _rel(out16, ref + bias.float()) < 4e-3
+    K.check_status()
+
+
+def test_fp8_linear_on_the_tensor_cores_matches_the_widened_product():
+    from scaling_b200.core.fp8.fp8_linear import fp8_linear
+
+    torch.manual_seed(6)
+    e4, e5 = torch.float8_e4m3fn, torch.float8_e5m2
+    x = torch.randn(4, 96, 256, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    w = (torch.randn(512, 256, device=DEV) * 0.05).to(torch.bfloat16).requires_grad_()
+    y = fp8_linear(x, w, None, dtypes_forward=(e4, e4), dtypes_grad_input=(e5, e4), dtypes_grad_weight=(e4, e5))
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    xq, wq = x.detach().to(e4).float(), w.detach().to(e4).float()
+    assert _rel(y.reshape(-1, 512), xq.reshape(-1, 256) @ wq.t()) < 4e-3
+    dyq5, dyq5b = dy.to(e5).float().reshape(-1, 512), dy.to(e5).float().reshape(-1, 512)
+    assert _rel(x.grad.reshape(-1, 256), dyq5 @ wq) < 4e-3
+    assert _rel(w.grad, dyq5b.t() @ xq.reshape(-1, 256)) < 4e-3
