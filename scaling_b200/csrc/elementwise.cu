@@ -210,7 +210,47 @@ __global__ void rope_vec_kernel(T* __restrict__ x, const int* __restrict__ pos, 
       }
     }
     T* tok = x + t * ld_tok;
-    for (int h = 0; h < n_heads; ++h) {
+    int h = 0;
+    if (mode == 0) {
+      // four (head, sub-tensor) slices at a time: eight 16-byte loads in flight per thread before the first store
+      const int n_slices = n_heads * n_sub;
+      int sl = 0;
+      for (; sl + 4 <= n_slices; sl += 4) {
+        sb::Vec16<T> a[4], b[4];
+        T* base[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          base[j] = tok + ((sl + j) / n_sub) * ld_head + ((sl + j) % n_sub) * ld_sub;
+          a[j] = sb::ld16(base[j] + c * V);
+          b[j] = sb::ld16(base[j] + half + c * V);
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+#pragma unroll
+          for (int i = 0; i < V; ++i) {
+            const float fa = sb::to_f(a[j].e[i]), fb = sb::to_f(b[j].e[i]);
+            a[j].e[i] = sb::from_f<T>(fa * cs[i] - fb * sn[i]);
+            b[j].e[i] = sb::from_f<T>(fb * cs[i] + fa * sn[i]);
+          }
+          sb::st16(base[j] + c * V, a[j]);
+          sb::st16(base[j] + half + c * V, b[j]);
+        }
+      }
+      for (; sl < n_slices; ++sl) {  // the slices that do not fill a group of four
+        T* bs = tok + (sl / n_sub) * ld_head + (sl % n_sub) * ld_sub;
+        sb::Vec16<T> a1 = sb::ld16(bs + c * V), b1 = sb::ld16(bs + half + c * V);
+#pragma unroll
+        for (int i = 0; i < V; ++i) {
+          const float fa = sb::to_f(a1.e[i]), fb = sb::to_f(b1.e[i]);
+          a1.e[i] = sb::from_f<T>(fa * cs[i] - fb * sn[i]);
+          b1.e[i] = sb::from_f<T>(fb * cs[i] + fa * sn[i]);
+        }
+        sb::st16(bs + c * V, a1);
+        sb::st16(bs + half + c * V, b1);
+      }
+      h = n_heads;  // mode 0 is done; the loop below serves mode 1
+    }
+    for (; h < n_heads; ++h) {
       for (int sub = 0; sub < n_sub; ++sub) {
         T* base = tok + h * ld_head + sub * ld_sub;
         if (mode == 0) {
@@ -289,6 +329,67 @@ __global__ void __launch_bounds__(256)
 #pragma unroll
       for (int w = 0; w < 8; ++w) s += red[w][t];
       partial[(long)blockIdx.y * N + col] = s;
+    }
+  }
+}
+// GELU backward with the bias gradient in the same pass: dx = dy * gelu'(x) is written and its column sums are taken
+// from the registers (the bias gradient of a linear layer with a fused GELU is the column sum of exactly this dx), which
+// saves the separate pass that would read dx again.  Same CTA / split layout and summation order as above.
+template <typename T>
+__global__ void __launch_bounds__(256)
+    gelu_bwd_colsum_kernel(const T* __restrict__ dy, const T* __restrict__ x, T* __restrict__ dx,
+                           float* __restrict__ partial, long M, int N, long rows_per_split) {
+  constexpr int V = sb::Vec16<T>::N;
+  __shared__ float red[8][32 * V];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int c = (blockIdx.x * 32 + lane) * V;
+  const long r0 = blockIdx.y * rows_per_split;
+  long r1 = r0 + rows_per_split;
+  if (r1 > M) r1 = M;
+  float acc[V];
+#pragma unroll
+  for (int i = 0; i < V; ++i) acc[i] = 0.f;
+  if (c < N) {
+    long r = r0 + warp;
+    for (; r + 24 < r1; r += 32) {  // four rows per thread in flight
+      sb::Vec16<T> d[4], v[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        d[j] = sb::ld16(dy + (r + 8 * j) * N + c);
+        v[j] = sb::ld16(x + (r + 8 * j) * N + c);
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        sb::Vec16<T> o;
+#pragma unroll
+        for (int i = 0; i < V; ++i) {
+          o.e[i] = sb::from_f<T>(sb::to_f(d[j].e[i]) * gelu_grad_f(sb::to_f(v[j].e[i])));
+          acc[i] += sb::to_f(o.e[i]);  // the rounded value: what a separate pass over dx would add
+        }
+        sb::st16(dx + (r + 8 * j) * N + c, o);
+      }
+    }
+    for (; r < r1; r += 8) {
+      const sb::Vec16<T> d = sb::ld16(dy + r * N + c), v = sb::ld16(x + r * N + c);
+      sb::Vec16<T> o;
+#pragma unroll
+      for (int i = 0; i < V; ++i) {
+        o.e[i] = sb::from_f<T>(sb::to_f(d.e[i]) * gelu_grad_f(sb::to_f(v.e[i])));
+        acc[i] += sb::to_f(o.e[i]);
+      }
+      sb::st16(dx + r * N + c, o);
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < V; ++i) red[warp][lane * V + i] = acc[i];
+  __syncthreads();
+  for (int t = threadIdx.x; t < 32 * V; t += 256) {
+    const int col = blockIdx.x * 32 * V + t;
+    if (col < N) {
+      float s2 = 0.f;
+#pragma unroll
+      for (int w = 0; w < 8; ++w) s2 += red[w][t];
+      partial[(long)blockIdx.y * N + col] = s2;
     }
   }
 }
@@ -518,6 +619,26 @@ SB_API int sb200_colsum_splits(long M, int N, int elem_size, int sm_count) {
   if (r > 128) r = 128;
   if (r < 1) r = 1;
   return (int)r;
+}
+// dx[M, N] = dy * gelu'(x) and bias_grad[N] (+)= column sums of dx, one pass (contiguous [M, N] tensors, N a multiple
+// of 16 bytes; partial: [splits, N] floats with splits from sb200_colsum_splits); deterministic.
+SB_API int sb200_gelu_bwd_colsum(const void* dy, const void* x, void* dx, void* bias_grad, float* partial, long M, int N,
+                                 int splits, int accumulate, int dtype, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return SB_OK;
+  if (splits < 1) return SB_ERR_BAD_ARG;
+  SB_DISPATCH_DTYPE(dtype, T, {
+    constexpr int V = sb::Vec16<T>::N;
+    if (N % V || ((reinterpret_cast<uintptr_t>(dy) | reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(dx)) & 15))
+      return SB_ERR_BAD_ARG;
+    const int strips = (N + 32 * V - 1) / (32 * V);
+    const long rows_per = (M + splits - 1) / splits;
+    gelu_bwd_colsum_kernel<T><<<dim3(strips, splits), 256, 0, stream>>>((const T*)dy, (const T*)x, (T*)dx, partial, M, N,
+                                                                         rows_per);
+    SB_CHECK_LAUNCH();
+    colsum_final_kernel<T><<<(N + 127) / 128, 128, 0, stream>>>(partial, (T*)bias_grad, splits, N, accumulate);
+  });
+  SB_CHECK_LAUNCH();
+  return SB_OK;
 }
 // out[N] (+)= column sums of x[M, N] (row stride ld elements, N and ld multiples of 16 bytes); deterministic.
 SB_API int sb200_colsum(const void* x, void* out, float* partial, long M, int N, long ld, int splits, int accumulate,

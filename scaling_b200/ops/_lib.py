@@ -61,6 +61,7 @@ _SIGS = {
     "sb200_swiglu_fwd": [c_void_p, c_void_p, c_void_p, c_long, c_int, c_long, c_long, c_long, c_float, c_int, c_void_p],
     "sb200_swiglu_bwd": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_long, c_int, c_long, c_long, c_long, c_long, c_long, c_float, c_int, c_void_p],
     "sb200_gelu_fwd": [c_void_p, c_void_p, c_long, c_int, c_void_p],
+    "sb200_gelu_bwd_colsum": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_long, c_int, c_int, c_int, c_int, c_void_p],
     "sb200_gelu_bwd": [c_void_p, c_void_p, c_void_p, c_long, c_int, c_void_p],
     "sb200_dropout_add": [c_void_p, c_void_p, c_void_p, c_long, c_float, c_float, c_float, c_void_p, ctypes.c_uint, c_long, c_int, c_int, c_void_p],
     "sb200_rope": [c_void_p, c_void_p, c_int, c_int, c_int, c_long, c_long, c_float, c_int, c_int, c_int, c_void_p],

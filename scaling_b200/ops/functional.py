@@ -219,8 +219,18 @@ class _LinearFn(torch.autograd.Function):
         dy2 = dy.reshape(-1, dy.shape[-1])
         if not dy2.is_contiguous():
             dy2 = dy2.contiguous()
+        want_db = ctx.has_bias and ctx.needs_input_grad[2]
+        bias_main = fused_grad_target(ctx.bias) if want_db else None
+        bias_done = False
         if ctx.act == "gelu":
-            dy2 = gelu_backward(dy2, pre)
+            fused = None
+            if bias_main is not None and bias_main.dtype == dy2.dtype:
+                # the bias gradient is the column sum of the GELU backward's output: one pass produces both
+                fused = gelu_backward_with_bias_grad(dy2, pre, bias_main, accumulate=True)
+            if fused is not None:
+                dy2, bias_done = fused, True
+            else:
+                dy2 = gelu_backward(dy2, pre)
         dx = dw = db = None
         if ctx.needs_input_grad[0]:
             dx = gemm(dy2, w, b_mn=True).view(ctx.x_shape)
@@ -230,10 +240,9 @@ class _LinearFn(torch.autograd.Function):
                 gemm(dy2, x2, a_mn=True, b_mn=True, out=main, accumulate=True)
             else:
                 dw = gemm(dy2, x2, a_mn=True, b_mn=True)
-        if ctx.has_bias and ctx.needs_input_grad[2]:
-            main = fused_grad_target(ctx.bias)
-            if main is not None and main.dtype == dy2.dtype:
-                column_sum(dy2, out=main, accumulate=True)
+        if want_db and not bias_done:
+            if bias_main is not None and bias_main.dtype == dy2.dtype:
+                column_sum(dy2, out=bias_main, accumulate=True)
             else:
                 db = column_sum(dy2)
         return dx, dw, db, None, None
@@ -430,6 +439,25 @@ def gelu_backward(dy: torch.Tensor, x: torch.Tensor) -> torch.Tensor:
     cdf = 0.5 * (1.0 + torch.erf(xf * 0.7071067811865476))
     pdf = torch.exp(-0.5 * xf * xf) * 0.3989422804014327
     return (dy.float() * (cdf + xf * pdf)).to(dy.dtype)
+
+
+def gelu_backward_with_bias_grad(dy: torch.Tensor, x: torch.Tensor, bias_grad: torch.Tensor,
+                                 accumulate: bool) -> Optional[torch.Tensor]:
+    """``dx = dy * gelu'(x)`` and ``bias_grad (+)= dx.sum(0)`` in one pass over ``[M, N]`` tensors (the bias gradient of
+    a linear layer with a fused GELU); returns None when the shapes do not fit the kernel (the caller then takes the
+    two separate ops)."""
+    M, N = dy.shape
+    if not (dy.is_cuda and dy.dtype in _KERNEL_DTYPES and dy.is_contiguous() and x.is_contiguous() and x.shape == dy.shape
+            and bias_grad.dtype == dy.dtype and bias_grad.is_contiguous() and N % (16 // dy.element_size()) == 0
+            and _lib.lib_has("sb200_gelu_bwd_colsum")):
+        return None
+    dx = torch.empty_like(dy)
+    splits = lib().sb200_colsum_splits(M, N, dy.element_size(), sm_count())
+    partial = torch.empty((splits, N), dtype=torch.float32, device=dy.device)
+    check(lib().sb200_gelu_bwd_colsum(dy.data_ptr(), x.data_ptr(), dx.data_ptr(), bias_grad.data_ptr(),
+                                      partial.data_ptr(), M, N, splits, int(accumulate), dt(dy.dtype), stream()),
+          "sb200_gelu_bwd_colsum")
+    return dx
 
 
 class _GeluFn(torch.autograd.Function):

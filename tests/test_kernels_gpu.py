@@ -608,3 +608,20 @@ def test_fp8_linear_on_the_tensor_cores_matches_the_widened_product():
     dyq5, dyq5b = dy.to(e5).float().reshape(-1, 512), dy.to(e5).float().reshape(-1, 512)
     assert _rel(x.grad.reshape(-1, 256), dyq5 @ wq) < 4e-3
     assert _rel(w.grad, dyq5b.t() @ xq.reshape(-1, 256)) < 4e-3
+
+
+@pytest.mark.parametrize("M,N", [(16384, 3072), (517, 264), (64, 8)])
+def test_gelu_backward_with_bias_gradient_in_one_pass(M, N):
+    torch.manual_seed(9)
+    dy = torch.randn(M, N, device=DEV, dtype=torch.bfloat16)
+    x = torch.randn(M, N, device=DEV, dtype=torch.bfloat16)
+    grad = torch.randn(N, device=DEV, dtype=torch.bfloat16)
+    before = grad.clone()
+    dx = K.gelu_backward_with_bias_grad(dy, x, grad, accumulate=True)
+    ref = K.gelu_backward(dy, x)
+    assert torch.equal(dx, ref)
+    want = before.float() + ref.float().sum(0)
+    assert _rel(grad, want) < 1e-2 and ((grad.float() - want).abs() < 0.02 * (1 + want.abs())).all()
+    again = before.clone()
+    K.gelu_backward_with_bias_grad(dy, x, again, accumulate=True)
+    assert torch.equal(again, grad)  # fixed summation order
