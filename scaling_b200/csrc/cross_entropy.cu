@@ -92,13 +92,13 @@ __global__ void __launch_bounds__(CE_THREADS)
   }
 }
 
-// loss[r] = log(gsum) + gmax - tgt ; dlogits[r, c] = (exp(x - gmax) / gsum - [c == tgt]) * coef[r]
+// loss[r] = log(gsum) + gmax - tgt ; dlogits[r, c] = (exp(x - gmax) / gsum - [c == tgt]) * coef[r] * scale_dev[0]
 template <typename T>
 __global__ void __launch_bounds__(CE_THREADS)
     ce_finalize_kernel(const T* __restrict__ logits, const long* __restrict__ targets, const float* __restrict__ gmax,
                        const float* __restrict__ gsum, const float* __restrict__ gtgt, const float* __restrict__ coef,
                        float* __restrict__ loss, T* __restrict__ dlogits, long N, int V, long ld, long ldd,
-                       long vocab_start) {
+                       long vocab_start, const float* __restrict__ scale_dev) {
   long r = blockIdx.x;
   if (r >= N) return;
   const float m = gmax[r], s = gsum[r];
@@ -107,7 +107,8 @@ __global__ void __launch_bounds__(CE_THREADS)
   const T* x = logits + r * ld;
   T* d = dlogits + r * ldd;
   const float inv = 1.f / s;
-  const float cf = coef ? coef[r] : 1.f;
+  // scale_dev: the upstream gradient of the loss (a device scalar), applied here instead of in a pass of its own
+  const float cf = (coef ? coef[r] : 1.f) * (scale_dev ? *scale_dev : 1.f);
   const long t = targets[r] - vocab_start;
   constexpr int VEC = sb::Vec16<T>::N;
   if ((V % VEC == 0) && (ld % VEC == 0) && (ldd % VEC == 0)) {
@@ -162,11 +163,12 @@ SB_API int sb200_ce_stats(const void* logits, const long* targets, float* row_ma
 }
 SB_API int sb200_ce_finalize(const void* logits, const long* targets, const float* gmax, const float* gsum,
                              const float* gtgt, const float* coef, float* loss, void* dlogits, long N, int V, long ld,
-                             long ldd, long vocab_start, int dtype, cudaStream_t stream) {
+                             long ldd, long vocab_start, const float* scale_dev, int dtype, cudaStream_t stream) {
   if (N <= 0 || V <= 0) return SB_OK;
   SB_DISPATCH_DTYPE(dtype, T, {
     ce_finalize_kernel<T><<<(unsigned)N, CE_THREADS, 0, stream>>>((const T*)logits, targets, gmax, gsum, gtgt, coef,
-                                                                   loss, (T*)dlogits, N, V, ld, ldd, vocab_start);
+                                                                   loss, (T*)dlogits, N, V, ld, ldd, vocab_start,
+                                                                   scale_dev);
   });
   SB_CHECK_LAUNCH();
   return SB_OK;

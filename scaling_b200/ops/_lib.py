@@ -71,7 +71,7 @@ _SIGS = {
     "sb200_colsum": [c_void_p, c_void_p, c_void_p, c_long, c_int, c_long, c_int, c_int, c_int, c_void_p],
     "sb200_transpose": [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     "sb200_ce_stats": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_long, c_int, c_long, c_long, c_int, c_void_p],
-    "sb200_ce_finalize": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_long, c_int, c_long, c_long, c_long, c_int, c_void_p],
+    "sb200_ce_finalize": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_long, c_int, c_long, c_long, c_long, c_void_p, c_int, c_void_p],
     "sb200_scale_by_dev": [c_void_p, c_void_p, c_float, c_long, c_int, c_void_p],
     "sb200_adamw": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_long, c_float, c_float, c_float, c_float, c_float, c_float, c_float, c_void_p, c_void_p, c_int, c_int, c_void_p],
     "sb200_sumsq_max_partials": [],

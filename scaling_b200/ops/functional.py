@@ -739,8 +739,9 @@ def ce_stats(logits: torch.Tensor, targets: torch.Tensor, vocab_start: int = 0, 
 
 def ce_finalize(logits: torch.Tensor, targets: torch.Tensor, gmax: torch.Tensor, gsum: torch.Tensor,
                 gtgt: torch.Tensor, coef: Optional[torch.Tensor], vocab_start: int = 0, want_grad: bool = True,
-                inplace: bool = True):
-    """Loss per token and (optionally) ``(softmax - onehot) * coef`` written over the logits."""
+                inplace: bool = True, scale_dev: Optional[torch.Tensor] = None):
+    """Loss per token and (optionally) ``(softmax - onehot) * coef * scale_dev[0]`` written over the logits
+    (``scale_dev``: a device scalar, e.g. the upstream gradient of the loss)."""
     N, V = logits.shape
     if logits.is_cuda and logits.dtype in _KERNEL_DTYPES:
         loss = torch.empty(N, dtype=torch.float32, device=logits.device)
@@ -751,7 +752,9 @@ def ce_finalize(logits: torch.Tensor, targets: torch.Tensor, gmax: torch.Tensor,
         check(
             lib().sb200_ce_finalize(logits.data_ptr(), tg.data_ptr(), gmax.data_ptr(), gsum.data_ptr(),
                                     gtgt.data_ptr(), ptr(coef), loss.data_ptr(), ptr(dl), N, V, logits.stride(0),
-                                    dl.stride(0) if dl is not None else 0, vocab_start, dt(logits.dtype), stream()),
+                                    dl.stride(0) if dl is not None else 0, vocab_start,
+                                    ptr(None if scale_dev is None else scale_dev.reshape(-1)[:1].float().contiguous()),
+                                    dt(logits.dtype), stream()),
             "sb200_ce_finalize",
         )
         return loss, dl
@@ -767,6 +770,8 @@ def ce_finalize(logits: torch.Tensor, targets: torch.Tensor, gmax: torch.Tensor,
         p = p - onehot
         if coef is not None:
             p = p * coef[:, None]
+        if scale_dev is not None:
+            p = p * scale_dev.reshape(-1)[0].float()
         dl = p.to(logits.dtype)
     return loss, dl
 

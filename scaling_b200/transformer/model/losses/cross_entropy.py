@@ -42,16 +42,20 @@ class _VocabParallelCrossEntropy(torch.autograd.Function):
             argmax = cand
         else:
             gmax, gsum, gtgt, argmax = rmax, rsum, tgt, aidx
-        loss_tok, dlogits = K.ce_finalize(logits, targets, gmax, gsum, gtgt, coef, vocab_start,
-                                          want_grad=ctx.needs_input_grad[0], inplace=False)
-        ctx.save_for_backward(dlogits)
+        # The loss needs the row statistics only.  The gradient with respect to the logits is written in the backward
+        # pass, over the logits themselves and already multiplied by the upstream gradient: the [tokens, vocabulary]
+        # matrix is read once here (statistics) and read and written once there.
+        loss_tok = torch.log(gsum) + gmax - gtgt
+        ctx.save_for_backward(logits, targets, gmax, gsum, gtgt, coef)
+        ctx.vocab_start = vocab_start
         ctx.mark_non_differentiable(argmax)
         return (loss_tok * coef).sum(), argmax
 
     @staticmethod
     def backward(ctx, grad_loss, _grad_argmax):  # type: ignore[override]
-        (dlogits,) = ctx.saved_tensors
-        K.scale_by_device_scalar(dlogits, grad_loss)
+        logits, targets, gmax, gsum, gtgt, coef = ctx.saved_tensors
+        _, dlogits = K.ce_finalize(logits, targets, gmax, gsum, gtgt, coef, ctx.vocab_start, want_grad=True,
+                                   inplace=logits.is_cuda, scale_dev=grad_loss)
         return dlogits, None, None, None, None
 
 
