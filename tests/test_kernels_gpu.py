@@ -625,3 +625,69 @@ def test_gelu_backward_with_bias_gradient_in_one_pass(M, N):
     again = before.clone()
     K.gelu_backward_with_bias_grad(dy, x, again, accumulate=True)
     assert torch.equal(again, grad)  # fixed summation order
+
+
+# ---------------------------------------------------------------------------------------------- edges and canaries
+def _rows_close(got, ref, tol):
+    """Largest absolute error of every row relative to that row's largest reference value: a wrong tile edge, a
+    dropped row or two swapped columns show up here even when the norm over the whole tensor hides them."""
+    got, ref = got.float(), ref.float()
+    err = (got - ref).abs().amax(dim=-1) / ref.abs().amax(dim=-1).clamp_min(1e-3)
+    return err.max().item() < tol, err.max().item()
+
+
+@pytest.mark.parametrize("M,N,K_", [(1, 8, 8), (127, 8, 72), (128, 128, 8), (129, 136, 72), (255, 264, 64), (257, 520, 136),
+                                    (384, 256, 8)])
+@pytest.mark.parametrize("mode", ["nt", "nn", "tn"])
+def test_gemm_tile_edges_and_canaries(M, N, K_, mode):
+    """One tile, one row / column more or less than a tile, reductions shorter than a k-block; the result goes into
+    the middle of a buffer whose border must come back untouched."""
+    torch.manual_seed(17)
+    dt = torch.bfloat16
+    if mode == "nt":
+        a, b = torch.randn(M, K_, device=DEV, dtype=dt), torch.randn(N, K_, device=DEV, dtype=dt)
+        ref, kw = a.float() @ b.float().t(), {}
+    elif mode == "nn":
+        a, b = torch.randn(M, K_, device=DEV, dtype=dt), torch.randn(K_, N, device=DEV, dtype=dt)
+        ref, kw = a.float() @ b.float(), {"b_mn": True}
+    else:
+        if M % 8:  # a transposed A operand needs rows of a multiple of 16 bytes
+            pytest.skip("M is the leading dimension of the transposed operand")
+        a, b = torch.randn(K_, M, device=DEV, dtype=dt), torch.randn(K_, N, device=DEV, dtype=dt)
+        ref, kw = a.float().t() @ b.float(), {"a_mn": True, "b_mn": True}
+    sentinel = -1234.0
+    buf = torch.full((M + 2, N + 16), sentinel, device=DEV, dtype=dt)
+    out = buf[1:M + 1, 8:N + 8]
+    K.gemm(a, b, out=out, **kw)
+    K.check_status()
+    ok, worst = _rows_close(out, ref, 2e-2)
+    assert ok, worst
+    border = buf.clone()
+    border[1:M + 1, 8:N + 8] = sentinel
+    assert (border == sentinel).all(), "the kernel wrote outside its output"
+
+
+@pytest.mark.parametrize("T", [1, 127, 128, 129, 257])
+@pytest.mark.parametrize("D", [64, 128])
+def test_flash_attention_tile_edges(T, D):
+    """Sequences of one token, one less, exactly and one more than a tile, alone and split into single-token and
+    odd-length documents; every row is checked on its own."""
+    from scaling_b200.ops.attention import attention_reference, flash_attention
+
+    torch.manual_seed(23)
+    cuts = sorted({0, T} | {c for c in (1, 2, T // 2, T - 1) if 0 < c < T})
+    for cu in ([0, T], cuts):
+        q = torch.randn(T, 2, D, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+        k = torch.randn(T, 1, D, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+        v = torch.randn(T, 1, D, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+        cu_t = torch.tensor(cu, device=DEV, dtype=torch.int32)
+        out = flash_attention(q, k, v, cu_t, None, causal=True, scale=D ** -0.5)
+        do = torch.randn_like(out)
+        out.backward(do)
+        K.check_status()
+        qr, kr, vr = (t.detach().float().requires_grad_() for t in (q, k, v))
+        ref = attention_reference(qr, kr, vr, cu_t, None, True, D ** -0.5)
+        ref.backward(do.float())
+        for got, want, tol in ((out, ref, 3e-2), (q.grad, qr.grad, 5e-2), (k.grad, kr.grad, 5e-2), (v.grad, vr.grad, 5e-2)):
+            ok, worst = _rows_close(got.reshape(T, -1), want.reshape(T, -1), tol)
+            assert ok, (cu, worst)
