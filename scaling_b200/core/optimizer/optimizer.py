@@ -181,14 +181,18 @@ class Optimizer(BaseOptimizer):
     def begin_step(self) -> None:
         self.step_index += 1
         cfg = self.config
-        t = self.adam_steps + 1
         values = []
         self._learning_rates = {}
         for i, g in enumerate(self.parameter_groups):
             lr = g.set_learning_rate(self.step_index)
             self._learning_rates[g.config.name or f"parameter_group_{i}"] = lr
-            values += [lr, 1.0 - cfg.beta1 ** t, 1.0 - cfg.beta2 ** t]
-        if self._hyper_host is None:
+            for _, _, born in g.step_ranges:
+                # Parameters whose moments started later than the others (added adapters next to restored weights)
+                # count their own updates, as torch's per-parameter ``state['step']`` does
+                # (src/scaling/core/optimizer/optimizer.py keeps ``step`` per parameter in its checkpoints).
+                t = self.adam_steps + 1 - born
+                values += [lr, 1.0 - cfg.beta1 ** t, 1.0 - cfg.beta2 ** t]
+        if self._hyper_host is None or self._hyper_host.numel() != len(values):
             self._hyper_host = torch.empty(len(values), dtype=torch.float32,
                                            pin_memory=self.topology.device.type == "cuda")
             self._hyper = torch.empty(len(values), dtype=torch.float32, device=self.topology.device)
@@ -221,12 +225,18 @@ class Optimizer(BaseOptimizer):
         K.step_control(1, self._stats, self._flag, self._control, self._result,
                        inv=1.0 / (dp * self.loss_scaler.current_scale), clip=float(cfg.gradient_clipping),
                        replicas=replicas)
-        for i, (g, r) in enumerate(zip(self.parameter_groups, reduced)):
+        slot = 0
+        for g, r in zip(self.parameter_groups, reduced):
             lo, hi = g.owned_range
-            p_lp = None if g.dtype == torch.float32 else g.flat_param[lo:hi]
-            K.adamw_step(g.master, g.exp_avg, g.exp_avg_sq, r if r.numel() == g.master.numel() else r[lo:hi], p_lp,
-                         g.current_lr, cfg.beta1, cfg.beta2, cfg.eps, g.weight_decay, self.adam_steps + 1,
-                         self._control, self._hyper[3 * i:3 * i + 3])
+            grad = r if r.numel() == g.master.numel() else r[lo:hi]
+            for a, b, born in g.step_ranges:  # one launch per range of equal age: one, but for the case above
+                a, b = max(a, lo) - lo, min(b, hi) - lo
+                if b > a:
+                    p_lp = None if g.dtype == torch.float32 else g.flat_param[lo + a:lo + b]
+                    K.adamw_step(g.master[a:b], g.exp_avg[a:b], g.exp_avg_sq[a:b], grad[a:b], p_lp, g.current_lr,
+                                 cfg.beta1, cfg.beta2, cfg.eps, g.weight_decay, self.adam_steps + 1 - born,
+                                 self._control, self._hyper[3 * slot:3 * slot + 3])
+                slot += 1
         if self._fused is not None:
             self._fused.all_gather(self)
         elif cfg.zero and dp > 1:
@@ -360,7 +370,7 @@ class Optimizer(BaseOptimizer):
                     "parameter": merged,
                     "meta": merged_meta.state_dict(),
                     "optimizer_state": {
-                        "step": torch.tensor(float(self.adam_steps)),
+                        "step": torch.tensor(float(self.adam_steps - g.born_at(a))),
                         "exp_avg": merge_parameter(m1[a:b].view(shape), meta, t),
                         "exp_avg_sq": merge_parameter(m2[a:b].view(shape), meta, t),
                     },
@@ -392,12 +402,14 @@ class Optimizer(BaseOptimizer):
             return cache[li]
 
         loaded_any = False
+        steps: list[list[int]] = []
         for g in self.parameter_groups:
             lo, hi = g.owned_range
+            steps.append([0] * len(g.parameters_original))
             # assemble the full-buffer fp32 states on the host, then keep the owned range
             full = {k: torch.zeros(g.padded_numel, dtype=torch.float32) for k in ("parameter", "exp_avg", "exp_avg_sq")}
             full["parameter"].copy_(g.flat_param.float().cpu())
-            for (a, b), p, meta in zip(g.param_slices(), g.parameters_original, g.parameter_metas):
+            for pi, ((a, b), p, meta) in enumerate(zip(g.param_slices(), g.parameters_original, g.parameter_metas)):
                 entry = None
                 candidates = sorted(meta.tied_layer_indices) if meta.is_tied else [meta.layer_index]
                 for li in candidates:
@@ -415,13 +427,14 @@ class Optimizer(BaseOptimizer):
                         if key in data["parameters"]:
                             entry = data["parameters"][key]
                             self.step_index = data["step_index"]
-                            self.adam_steps = int(entry["optimizer_state"]["step"])
+                            steps[-1][pi] = int(entry["optimizer_state"]["step"])
                             self.loss_scaler.load_state_dict(data["loss_scaler"])
                             break
                     if entry is not None:
                         break
                 if entry is None:
-                    logger.warning(f"no optimizer state found for {meta.key}; keeping fresh state")
+                    logger.warning(f"no optimizer state found for {meta.key}: it starts from zero moments and counts "
+                                   "its own updates for the bias correction")
                     continue
                 loaded_any = True
                 tensors = {"parameter": entry["parameter"], "exp_avg": entry["optimizer_state"]["exp_avg"],
@@ -436,6 +449,12 @@ class Optimizer(BaseOptimizer):
             g.exp_avg_sq.copy_(full["exp_avg_sq"][lo:hi])
         if not loaded_any:
             logger.warning(f"no optimizer state files found in {directory}")
+            return
+        # The optimizer's counter is the oldest parameter's; younger ones (no stored state: step 0) keep the difference.
+        self.adam_steps = max(max(s, default=0) for s in steps)
+        for g, s in zip(self.parameter_groups, steps):
+            g.set_parameter_steps([self.adam_steps - v for v in s])
+        self._hyper_host = None  # the number of ranges may have changed
 
 
 def _try_fused_zero(optimizer: "Optimizer") -> Any:

@@ -100,6 +100,7 @@ class OptimizerParamGroup:
         self.padded_numel = max(_align(cursor, 2 * dp * ALIGN_ELEMENTS), 2 * dp * ALIGN_ELEMENTS)
         self.partition_numel = self.padded_numel // dp
 
+        self.step_ranges: list[tuple[int, int, int]] = [(0, self.padded_numel, 0)]  # (start, end, born): see below
         self.flat_param = torch.zeros(self.padded_numel, dtype=self.dtype, device=self.device)
         self.flat_grad = torch.zeros(self.padded_numel, dtype=self.dtype, device=self.device)
         with torch.no_grad():
@@ -195,6 +196,27 @@ class OptimizerParamGroup:
         if self.dtype != torch.float32:
             self.master.copy_(self.flat_param[lo:hi])
 
+    # ------------------------------------------------------------------ age of the Adam state
+    def set_parameter_steps(self, born: list[int]) -> None:
+        """``born[i]``: how many optimizer updates had been applied when parameter ``i``'s moments started from zero.
+        Neighbouring parameters of equal age are merged into one range (one AdamW launch each)."""
+        ranges: list[tuple[int, int, int]] = []
+        slices = self.param_slices()
+        for i, ((a, _), age) in enumerate(zip(slices, born)):
+            end = slices[i + 1][0] if i + 1 < len(slices) else self.padded_numel
+            start = 0 if i == 0 else a
+            if ranges and ranges[-1][2] == age:
+                ranges[-1] = (ranges[-1][0], end, age)
+            else:
+                ranges.append((start, end, age))
+        self.step_ranges = ranges or [(0, self.padded_numel, 0)]
+
+    def born_at(self, offset: int) -> int:
+        for a, b, age in self.step_ranges:
+            if a <= offset < b:
+                return age
+        return 0
+
     # ------------------------------------------------------------------ views for checkpoints
     def param_slices(self) -> list[tuple[int, int]]:
         return [(off, off + p.numel()) for p, off in zip(self.parameters_original, self.offsets)]
@@ -210,6 +232,7 @@ class OptimizerParamGroup:
             "exp_avg": self.exp_avg.detach().clone().cpu(),
             "exp_avg_sq": self.exp_avg_sq.detach().clone().cpu(),
             "zero": self.zero,
+            "step_ranges": [list(r) for r in self.step_ranges],
         }
 
     def load_state_dict(self, state: dict[str, Any]) -> None:
@@ -219,6 +242,7 @@ class OptimizerParamGroup:
         self.master.copy_(state["master"])
         self.exp_avg.copy_(state["exp_avg"])
         self.exp_avg_sq.copy_(state["exp_avg_sq"])
+        self.step_ranges = [tuple(r) for r in state.get("step_ranges", [(0, self.padded_numel, 0)])]
         self.write_back_params()
 
     def write_back_params(self) -> None:

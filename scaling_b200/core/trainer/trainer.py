@@ -142,6 +142,10 @@ class BaseTrainer(Generic[BaseContextGeneric, ParallelModuleGeneric]):
             ignore_keys_in_checkpoint=ignore_keys_in_checkpoint,
         )
         if load_optimizer_states:
+            # a step captured earlier holds the addresses of the optimizer's per-step scalars, which a load may replace
+            release = getattr(self.parallel_module, "release_cuda_graph", None)
+            if release is not None:
+                release()
             self.optimizer.load_checkpoint(iteration_dir)
         else:
             self.optimizer.refresh_optimizer_after_model_change()

@@ -1,6 +1,8 @@
 """Engine plumbing on CPU ranks (gloo): batch broadcast, pipeline communicator, data loader resume, schedules, and
 how failures of a rank surface (on the host, never on a device)."""
 
+from pathlib import Path
+
 import numpy as np
 import pytest
 import torch
@@ -155,3 +157,71 @@ def _overflow_worker(rank, world_size, port, device):
 def test_overflow_on_one_rank_skips_the_step_everywhere():
     results = dist_launcher(_overflow_worker, 2)
     assert results[0] == results[1] == (True, 2.0, True)
+
+
+def _added_parameter_worker(rank, world_size, port, device, directory=None):
+    """Resume with a parameter that the checkpoint does not know: the restored ones continue their bias correction,
+    the new one starts its own, exactly as ``torch.optim.AdamW`` does with one ``step`` per parameter."""
+    from scaling_b200.core.optimizer import (LearningRateSchedulerConfig, Optimizer, OptimizerConfig,
+                                             OptimizerParamGroup, OptimizerParamGroupConfig)
+    from scaling_b200.core.nn.parameter_meta import CoreParameterMeta
+
+    t = _topology(rank, world_size, port)
+    zero = world_size > 1
+
+    def build(names):
+        torch.manual_seed(3)
+        params = []
+        for n in names:
+            i = "abc".index(n)
+            p = torch.nn.Parameter(torch.randn(70 + 10 * i))
+            CoreParameterMeta.register_on_parameter(p, is_model_parallel=False, layer_index=i, parameter_name=n)
+            params.append((n, p, p.core_parameter_meta))
+        group = OptimizerParamGroup(params, OptimizerParamGroupConfig(
+            name="g", weight_decay=0.01, learning_rate_scheduler=LearningRateSchedulerConfig(
+                learning_rate=0.01, learning_rate_decay_style="constant")))
+        opt = Optimizer(OptimizerConfig(zero=zero, beta1=0.9, beta2=0.95, eps=1e-8, gradient_clipping=0.0), [group], t)
+        return [p for _, p, _ in params], opt
+
+    def grads(step, params):
+        g = torch.Generator().manual_seed(100 + step)
+        for p in params:
+            p.grad.copy_(torch.randn(p.shape, generator=g))
+
+    old, opt = build(["a", "b"])
+    oracle = [torch.nn.Parameter(p.detach().clone()) for p in old]
+    ref = torch.optim.AdamW(oracle, lr=0.01, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.01)
+    for step in range(6):
+        grads(step, old)
+        for o, p in zip(oracle, old):
+            o.grad = p.grad.detach().clone()
+        opt.step()
+        ref.step()
+    first = max((o.detach() - p.detach()).abs().max().item() for o, p in zip(oracle, old))
+    opt.save_checkpoint(directory)
+    torch.distributed.barrier()
+
+    new, opt2 = build(["a", "c", "b"])  # the new parameter sits between the restored ones in the flat buffer
+    opt2.load_checkpoint(directory)
+    added = torch.nn.Parameter(new[1].detach().clone())
+    ref_added = torch.optim.AdamW([added], lr=0.01, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.01)
+    ages = [r[2] for r in opt2.parameter_groups[0].step_ranges]
+    errs = []
+    for step in range(6, 9):
+        grads(step, new)
+        for o, p in zip(oracle + [added], [new[0], new[2], new[1]]):
+            o.grad = p.grad.detach().clone()
+        opt2.step()
+        ref.step()
+        ref_added.step()
+        errs.append(max((o.detach() - p.detach()).abs().max().item()
+                        for o, p in zip(oracle + [added], [new[0], new[2], new[1]])))
+    return ages, opt2.adam_steps, max(errs + [first])
+
+
+@pytest.mark.parametrize("world_size", [1, 2])
+def test_a_parameter_added_at_resume_counts_its_own_adam_steps(tmp_path: Path, world_size):
+    results = dist_launcher(_added_parameter_worker, world_size, directory=str(tmp_path))
+    for ages, adam_steps, err in results:
+        assert ages == [0, 6, 0] and adam_steps == 9
+        assert err < 1e-6
