@@ -411,8 +411,17 @@ __global__ void colsum_final_kernel(const float* __restrict__ partial, T* __rest
                                     int accumulate) {
   const int c = blockIdx.x * blockDim.x + threadIdx.x;
   if (c >= N) return;
+  // eight loads in flight per thread (a chain of dependent loads from L2 made this kernel cost as much as the pass
+  // over the matrix); the order of the additions is fixed all the same
   float s = 0.f;
-  for (int r = 0; r < R; ++r) s += partial[(long)r * N + c];
+  int r = 0;
+  for (; r + 8 <= R; r += 8) {
+    float v[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] = __ldcg(partial + (long)(r + j) * N + c);
+    s += ((v[0] + v[1]) + (v[2] + v[3])) + ((v[4] + v[5]) + (v[6] + v[7]));
+  }
+  for (; r < R; ++r) s += __ldcg(partial + (long)r * N + c);
   if (accumulate) s += sb::to_f(out[c]);
   out[c] = sb::from_f<T>(s);
 }
@@ -625,7 +634,7 @@ SB_API int sb200_rope(void* x, const int* pos, int tokens, int n_heads, int rot_
 SB_API int sb200_colsum_splits(long M, int N, int elem_size, int sm_count) {
   const int V = 16 / (elem_size > 0 ? elem_size : 2);
   const int strips = (N + 32 * V - 1) / (32 * V);
-  long r = (2L * sm_count + strips - 1) / strips;
+  long r = (6L * sm_count + strips - 1) / strips;  // about six CTAs (48 warps) per SM: the loads of fewer do not cover HBM latency
   const long max_r = (M + 63) / 64;
   if (r > max_r) r = max_r;
   if (r > 128) r = 128;
@@ -647,7 +656,7 @@ SB_API int sb200_gelu_bwd_colsum(const void* dy, const void* x, void* dx, void* 
     gelu_bwd_colsum_kernel<T><<<dim3(strips, splits), 256, 0, stream>>>((const T*)dy, (const T*)x, (T*)dx, partial, M, N,
                                                                          rows_per);
     SB_CHECK_LAUNCH();
-    colsum_final_kernel<T><<<(N + 127) / 128, 128, 0, stream>>>(partial, (T*)bias_grad, splits, N, accumulate);
+    colsum_final_kernel<T><<<(N + 31) / 32, 32, 0, stream>>>(partial, (T*)bias_grad, splits, N, accumulate);
   });
   SB_CHECK_LAUNCH();
   return SB_OK;
@@ -664,7 +673,7 @@ SB_API int sb200_colsum(const void* x, void* out, float* partial, long M, int N,
     const long rows_per = (M + splits - 1) / splits;
     colsum_partial_kernel<T><<<dim3(strips, splits), 256, 0, stream>>>((const T*)x, partial, M, N, ld, rows_per);
     SB_CHECK_LAUNCH();
-    colsum_final_kernel<T><<<(N + 127) / 128, 128, 0, stream>>>(partial, (T*)out, splits, N, accumulate);
+    colsum_final_kernel<T><<<(N + 31) / 32, 32, 0, stream>>>(partial, (T*)out, splits, N, accumulate);
   });
   SB_CHECK_LAUNCH();
   return SB_OK;

@@ -265,6 +265,21 @@ __global__ void __launch_bounds__(FUSE ? GEMM_THREADS + REDUCER_THREADS : GEMM_T
   const int wait_rounds = (FUSE && p.ar.mode == AR_ALLGATHER) ? (int)(p.ar.timeout_ns / 2000000000ull) + 2 : 1;
   // position in this worker's sequence -> unit (tile, split); fused launches start at a rank-specific tile
   auto unit_at = [&](int i) { return FUSE ? (i + ushift) % num_units : i; };
+  // tile -> (row block of tiles, column block).  Tiles are numbered down groups of RASTER_M tile rows, so the tiles
+  // that run at the same time (consecutive numbers) cover about as many tile rows as tile columns and share their A
+  // and B panels in L2; numbering them row by row makes every wave sweep the whole of B, which for a wide N (a
+  // 12288- or 32000-column weight) is more than L2 holds.  Fused launches keep the row-major numbering that their
+  // ownership rules are written in.
+  constexpr int RASTER_M = PAIR ? 8 : 16;
+  auto tile_mn = [&](int tile) -> int2 {  // .x: tile row, .y: tile column
+    if (FUSE) return make_int2(tile / n_tiles, tile % n_tiles);
+    const int per_group = RASTER_M * n_tiles;
+    const int g = tile / per_group, r = tile - g * per_group;
+    const int first = g * RASTER_M;
+    const int gm = m_tiles - first < RASTER_M ? m_tiles - first : RASTER_M;
+    const int nb = r / gm;
+    return make_int2(first + (r - nb * gm), nb);
+  };
   // fused launches on the second buffer of the workspace: the gathered operand is read through tmA2, partial tiles
   // are stored through tmP (which no fused reduction uses for a pre-activation output)
   const CUtensorMap* mapA = (FUSE && p.ar.mode == AR_ALLGATHER && p.ar.half) ? &tmA2 : &tmA;
@@ -321,7 +336,8 @@ __global__ void __launch_bounds__(FUSE ? GEMM_THREADS + REDUCER_THREADS : GEMM_T
       for (int it = worker; it < num_units && ok; it += num_workers) {
         const int unit = unit_at(it);
         const int tile = unit / S, split = unit - tile * S;
-        const int m_blk = (tile / n_tiles) * CTAS + rank, n_blk = tile % n_tiles;
+        const int2 mn = tile_mn(tile);
+        const int m_blk = mn.x * CTAS + rank, n_blk = mn.y;
         const int kb0 = (int)((long)split * num_kb / S), kb1 = (int)((long)(split + 1) * num_kb / S);
         const int b_col0 = n_blk * BN + rank * LOAD_BN;  // first output column whose B rows this CTA loads
         if (FUSE && p.ar.mode == AR_ALLGATHER && m_blk * BM < p.M) {
@@ -460,7 +476,8 @@ __global__ void __launch_bounds__(FUSE ? GEMM_THREADS + REDUCER_THREADS : GEMM_T
     for (int it = worker; it < num_units; it += num_workers) {
       const int unit = unit_at(it);
       const int tile = unit / S;
-      const int m_blk = (tile / n_tiles) * CTAS + rank, n_blk = tile % n_tiles;
+      const int2 mn = tile_mn(tile);
+      const int m_blk = mn.x * CTAS + rank, n_blk = mn.y;
       const int ctile = tile * CTAS + rank;  // this CTA's part of the tile: index of its counter and partial slots
       if (ok && !sb::mbar_wait_rounds(&tfull_bar[acc], acc_phase, abort_flag, wait_rounds)) ok = false;
       sb::tc_fence_after();
@@ -599,7 +616,10 @@ __global__ void __launch_bounds__(FUSE ? GEMM_THREADS + REDUCER_THREADS : GEMM_T
             sb::fence_proxy_async_smem();
             __syncwarp();
             if (lane == 0) {
-              sb::tma_store_2d(pre_pass ? &tmP : mapC, stage_buf, n0, row0);
+              // accumulate: the memory system adds the box to C (the sum is rounded to the output type there, the
+              // product once before it, like a separate "C += product" on 16-bit tensors)
+              if (p.accumulate) sb::tma_reduce_add_2d(mapC, stage_buf, n0, row0);
+              else sb::tma_store_2d(pre_pass ? &tmP : mapC, stage_buf, n0, row0);
               sb::tma_store_commit();
             }
           }
@@ -1040,8 +1060,8 @@ SB_API int sb200_gemm_ws(const void* A, const void* B, void* C, void* C_pre, con
   p.ws_counter = reinterpret_cast<int*>(workspace);
   p.ws_partial = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(workspace) + WS_COUNTER_BYTES);
   const bool out16 = out_dtype != SB_DT_F32;
-  p.tma_store = out16 && !accumulate && (ldc % 8 == 0) && (reinterpret_cast<uintptr_t>(C) & 15) == 0 &&
-                (!C_pre || (reinterpret_cast<uintptr_t>(C_pre) & 15) == 0);
+  p.tma_store = out16 && (!accumulate || (!C_pre && act == 0)) && (ldc % 8 == 0) &&
+                (reinterpret_cast<uintptr_t>(C) & 15) == 0 && (!C_pre || (reinterpret_cast<uintptr_t>(C_pre) & 15) == 0);
   tmC = tmA;
   tmP = tmA;  // placeholders when the epilogue stores from registers
   if (p.tma_store) {

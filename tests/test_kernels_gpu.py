@@ -637,7 +637,7 @@ def _rows_close(got, ref, tol):
 
 
 @pytest.mark.parametrize("M,N,K_", [(1, 8, 8), (127, 8, 72), (128, 128, 8), (129, 136, 72), (255, 264, 64), (257, 520, 136),
-                                    (384, 256, 8)])
+                                    (384, 256, 8), (2312, 1288, 72)])
 @pytest.mark.parametrize("mode", ["nt", "nn", "tn"])
 def test_gemm_tile_edges_and_canaries(M, N, K_, mode):
     """One tile, one row / column more or less than a tile, reductions shorter than a k-block; the result goes into
@@ -665,6 +665,13 @@ def test_gemm_tile_edges_and_canaries(M, N, K_, mode):
     border = buf.clone()
     border[1:M + 1, 8:N + 8] = sentinel
     assert (border == sentinel).all(), "the kernel wrote outside its output"
+    K.gemm(a, b, out=out, accumulate=True, **kw)  # the accumulating form adds into memory through the same boxes
+    K.check_status()
+    ok, worst = _rows_close(out, 2 * ref, 3e-2)
+    assert ok, worst
+    border = buf.clone()
+    border[1:M + 1, 8:N + 8] = sentinel
+    assert (border == sentinel).all(), "the accumulating kernel wrote outside its output"
 
 
 @pytest.mark.parametrize("T", [1, 127, 128, 129, 257])
