@@ -3,9 +3,10 @@
 ``flash_attention`` takes token-major tensors ``q[Tq, Hq, D]``, ``k/v[Tk, Hkv, D]`` and cumulative
 sequence lengths (int32, ``[n_docs + 1]``), like the call the reference makes into the flash-attn
 package (src/scaling/core/nn/attention/attention.py:216-271).  On GPUs with bf16/fp16 inputs and
-``D in {64, 128}`` the hand-written tcgen05 kernels run (forward and deterministic backward); the
-dense torch expression below serves CPU ranks, odd head sizes, cross-length decoding with a KV
-cache, and is the numerical oracle of the kernel tests.
+``D in {64, 128}`` the hand-written tcgen05 kernels run (forward and deterministic backward; smaller head
+sizes are padded to these), and queries against a longer KV cache go to a streaming decode kernel; the
+dense torch expression below serves CPU ranks and head sizes above 128, and is the numerical oracle of
+the kernel tests.
 """
 
 from __future__ import annotations
@@ -105,11 +106,28 @@ def flash_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seqlen
     ``dropout_p > 0`` drops attention probabilities; inside the kernel when ``rng_state`` (the topology's
     ``KernelDropoutState``) is given, where the mask is recomputed in the backward pass and costs no memory."""
     scale = 1.0 / math.sqrt(q.shape[-1]) if scale is None else scale
+    if (cu_seqlens_k is not None and cu_seqlens_q is not None and q.shape[0] == k.shape[0]
+            and (cu_seqlens_k is cu_seqlens_q or cu_seqlens_q.numel() == cu_seqlens_k.numel() == 2)):
+        cu_seqlens_k = None  # one document with as many keys as queries (filling a KV cache): plain self-attention
+    d = q.shape[-1]
+    if d < 128 and d != 64 and q.is_cuda and q.dtype in (torch.bfloat16, torch.float16) and cu_seqlens_k is None:
+        # Head sizes between the two the kernel is built for: zero columns change neither the scores nor the
+        # probabilities and give zero output columns, so the padded problem is the same attention.
+        pad = (0, (64 if d < 64 else 128) - d)
+        F = torch.nn.functional
+        out = flash_attention(F.pad(q, pad), F.pad(k, pad), F.pad(v, pad), cu_seqlens_q, None, causal, scale, window,
+                              dropout_p, doc_ranges, rng_state, head_offset)
+        return out[..., :d]
     if (dropout_p == 0.0 or rng_state is not None) and kernel_supported(q, k, cu_seqlens_k):
         from .attention_kernel import dropout_args, flash_attention_kernel
 
         return flash_attention_kernel(q, k, v, cu_seqlens_q, causal, scale, window, doc_ranges,
                                       dropout_args(dropout_p, rng_state, head_offset))
+    if cu_seqlens_k is not None and cu_seqlens_q is not None and dropout_p == 0.0 and q.is_cuda:
+        from .attention_kernel import decode_supported, flash_decode
+
+        if decode_supported(q, k, v):  # a few queries against many cached keys: streaming kernel, forward only
+            return flash_decode(q, k, v, cu_seqlens_q, cu_seqlens_k, causal, scale, window)
     assert cu_seqlens_q is not None, "the dense attention path needs cumulative sequence lengths"
     if q.is_cuda and cu_seqlens_k is None and window is None:
         # head sizes the tcgen05 kernel does not cover: batched library attention over equal-length documents

@@ -249,3 +249,55 @@ def packed_qkv_attention(qkv: torch.Tensor, positions: Optional[torch.Tensor],
         pos = positions if positions.dtype == torch.int32 else positions.to(torch.int32)
         pos = pos.contiguous()
     return _PackedQKVAttention.apply(qkv, pos, rotary, start, end, causal, scale, window, drop)
+
+
+# ------------------------------------------------------------------------------------------ cross-length attention
+def key_ranges(cu_q: torch.Tensor, cu_k: torch.Tensor, tq: int, causal: bool,
+               window: Optional[int]) -> tuple[torch.Tensor, torch.Tensor]:
+    """For every packed query token the half-open range of packed key indices it may attend to (int32 ``[tq]`` each):
+    the keys of its own document, up to the causal diagonal (aligned to the end of the keys, so the last query sees
+    every key) and inside the local window.  Built with tensor operations only: no host synchronisation."""
+    cq, ck = cu_q.to(torch.int64), cu_k.to(torch.int64)
+    idx = torch.arange(tq, device=cq.device)
+    doc = (torch.searchsorted(cq, idx, right=True) - 1).clamp_(0, cq.numel() - 2)
+    len_q, len_k = (cq[1:] - cq[:-1])[doc], (ck[1:] - ck[:-1])[doc]
+    centre = idx - cq[doc] + (len_k - len_q)  # key position on the diagonal of this query
+    lo = torch.zeros_like(centre)
+    hi = len_k.clone()
+    if causal:
+        hi = torch.minimum(hi, centre + 1)
+    if window is not None and window >= 0:
+        lo = torch.maximum(lo, centre - window)
+        if not causal:
+            hi = torch.minimum(hi, centre + window + 1)
+    lo = lo.clamp_(min=0)
+    hi = torch.maximum(hi, lo)
+    base = ck[doc]
+    return (base + lo).to(torch.int32).contiguous(), (base + hi).to(torch.int32).contiguous()
+
+
+def decode_supported(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> bool:
+    return (q.is_cuda and q.dtype in (torch.bfloat16, torch.float16) and q.shape[-1] in (64, 128)
+            and q.shape[1] % k.shape[1] == 0 and k.shape == v.shape and _lib.lib_has("sb200_fa_decode")
+            and not (torch.is_grad_enabled() and (q.requires_grad or k.requires_grad or v.requires_grad)))
+
+
+def flash_decode(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_q: torch.Tensor, cu_k: torch.Tensor,
+                 causal: bool, scale: float, window: Optional[int]) -> torch.Tensor:
+    """Queries and keys of different lengths (decoding against a KV cache): ``q [Tq, Hq, D]``, ``k / v [Tk, Hkv, D]``.
+    Forward only."""
+    _lib.declare("sb200_fa_decode", [c_void_p] * 6 + [c_int] * 4 + [c_long] * 8 + [c_float, c_int, c_void_p])
+    q = q if q.stride(2) == 1 else q.contiguous()
+    k = k if _strides_ok(k) else k.contiguous()
+    v = v if _strides_ok(v) else v.contiguous()
+    lo, hi = key_ranges(cu_q, cu_k, q.shape[0], causal, window)
+    hi.clamp_(max=k.shape[0])  # cumulative lengths that overshoot the key tensor must not become addresses
+    out = torch.empty_like(q, memory_format=torch.contiguous_format)
+    check(
+        lib().sb200_fa_decode(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lo.data_ptr(), hi.data_ptr(),
+                              q.shape[0], q.shape[1], k.shape[1], q.shape[2], q.stride(0), q.stride(1), k.stride(0),
+                              k.stride(1), v.stride(0), v.stride(1), out.stride(0), out.stride(1), float(scale),
+                              _lib.dt(q.dtype), stream()),
+        "sb200_fa_decode",
+    )
+    return out

@@ -698,3 +698,49 @@ def test_flash_attention_tile_edges(T, D):
         for got, want, tol in ((out, ref, 3e-2), (q.grad, qr.grad, 5e-2), (k.grad, kr.grad, 5e-2), (v.grad, vr.grad, 5e-2)):
             ok, worst = _rows_close(got.reshape(T, -1), want.reshape(T, -1), tol)
             assert ok, (cu, worst)
+
+
+@pytest.mark.parametrize("D", [32, 80, 96])
+def test_flash_attention_head_sizes_between_the_native_ones(D):
+    """Head sizes other than 64 and 128 run on the same kernels, padded with zero columns."""
+    from scaling_b200.ops.attention import attention_reference, flash_attention
+
+    torch.manual_seed(31)
+    T = 384
+    cu = torch.tensor([0, 100, 384], device=DEV, dtype=torch.int32)
+    q = torch.randn(T, 4, D, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    k = torch.randn(T, 2, D, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    v = torch.randn(T, 2, D, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    out = flash_attention(q, k, v, cu, None, causal=True)
+    assert out.shape == q.shape
+    do = torch.randn_like(out)
+    out.backward(do)
+    K.check_status()
+    qr, kr, vr = (t.detach().float().requires_grad_() for t in (q, k, v))
+    ref = attention_reference(qr, kr, vr, cu, None, True, D ** -0.5)
+    ref.backward(do.float())
+    for got, want, tol in ((out, ref, 3e-2), (q.grad, qr.grad, 5e-2), (k.grad, kr.grad, 5e-2), (v.grad, vr.grad, 5e-2)):
+        ok, worst = _rows_close(got.reshape(T, -1), want.reshape(T, -1), tol)
+        assert ok, (D, worst)
+
+
+@pytest.mark.parametrize("D", [64, 128])
+@pytest.mark.parametrize("causal,window", [(True, None), (True, 100), (False, None), (False, 37)])
+def test_attention_of_few_queries_against_a_long_cache(D, causal, window):
+    """Queries shorter than the keys of their document (decoding with a KV cache): the streaming kernel against the
+    dense fp32 expression, with a document whose query sees a single key and one with as many queries as keys."""
+    from scaling_b200.ops.attention import attention_reference, flash_attention
+
+    torch.manual_seed(41)
+    cu_q = torch.tensor([0, 1, 4, 5, 37], device=DEV, dtype=torch.int32)
+    cu_k = torch.tensor([0, 700, 1500, 1501, 1533], device=DEV, dtype=torch.int32)
+    tq, tk = 37, 1533
+    q = torch.randn(tq, 8, D, device=DEV, dtype=torch.bfloat16)
+    cache = torch.randn(tk, 2, 2, D, device=DEV, dtype=torch.bfloat16)  # k and v interleaved: strided rows
+    k, v = cache[:, 0], cache[:, 1]
+    with torch.no_grad():
+        out = flash_attention(q, k, v, cu_q, cu_k, causal=causal, window=window)
+    K.check_status()
+    ref = attention_reference(q.float(), k.float(), v.float(), cu_q, cu_k, causal, D ** -0.5, window)
+    ok, worst = _rows_close(out.reshape(tq, -1), ref.reshape(tq, -1), 2e-2)
+    assert ok, worst
