@@ -99,9 +99,12 @@ template <int BN, bool PAIR> struct GemmCfg {
   static constexpr int A_BYTES = BM * BK * 2;
   static constexpr int B_BYTES = LOAD_BN * BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int STAGES = STAGE_BYTES == 49152 ? 4 : 6;
+  // 48 KB stages (a single CTA on a 256-wide tile): four of them and one staging box per epilogue warp; 32 KB stages:
+  // five and two staging boxes per warp, so that a warp fills one box while the TMA store still reads the other
+  static constexpr int STAGES = STAGE_BYTES == 49152 ? 4 : 5;
+  static constexpr int EPI_BUFS = STAGE_BYTES == 49152 ? 1 : 2;
   static constexpr int TMEM_COLS = 2 * BN;
-  static constexpr int EPI_BYTES = EPI_WARPS * STAGE_BOX_BYTES;
+  static constexpr int EPI_BYTES = EPI_WARPS * EPI_BUFS * STAGE_BOX_BYTES;
   static constexpr int BIAS_BYTES = 2 * BN * 2;  // two tiles' worth of 16-bit bias values
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_BYTES + BIAS_BYTES + 1024 /*align*/ + 256 /*barriers*/;
 };
@@ -454,7 +457,8 @@ __global__ void __launch_bounds__(FUSE ? GEMM_THREADS + REDUCER_THREADS : GEMM_T
     constexpr int HALF = BN / 2;
     constexpr int CHUNKS = HALF / 32;   // 32-column chunks per warp
     constexpr bool OUT16 = sizeof(OutT) == 2;
-    uint8_t* stage_buf = epi_stage + ew * STAGE_BOX_BYTES;
+    uint8_t* const stage_base = epi_stage + ew * (Cfg::EPI_BUFS * STAGE_BOX_BYTES);
+    int sbuf = 0;  // staging box the next store is built in
     int acc = 0;
     uint32_t acc_phase = 0;
     int bias_buf = 0;
@@ -574,7 +578,6 @@ __global__ void __launch_bounds__(FUSE ? GEMM_THREADS + REDUCER_THREADS : GEMM_T
       if (use_tma) {
         const int row0 = m_blk * BM + quad * 32;
         // swizzled position of 16-byte chunk j of this lane's row inside the 32 x 128-byte staging box
-        uint8_t* my_row = stage_buf + lane * 128;
         const int sw = lane & 7;
 #pragma unroll 1
         for (int bx = 0; bx < CHUNKS / 2; ++bx) {
@@ -584,7 +587,14 @@ __global__ void __launch_bounds__(FUSE ? GEMM_THREADS + REDUCER_THREADS : GEMM_T
           const int passes = Cpre ? 2 : 1;
           for (int pass = 0; pass < passes; ++pass) {
             const bool pre_pass = Cpre && pass == 0;
-            if (lane == 0) sb::tma_store_wait_read0();  // the previous store has finished reading the staging box
+            // the store that last used this box has finished reading it
+            uint8_t* const stage_buf = stage_base + sbuf * STAGE_BOX_BYTES;
+            uint8_t* const my_row = stage_buf + lane * 128;
+            if (lane == 0) {
+              if (Cfg::EPI_BUFS == 2) sb::tma_store_wait_read1();
+              else sb::tma_store_wait_read0();
+            }
+            sbuf ^= Cfg::EPI_BUFS - 1;
             __syncwarp();
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
