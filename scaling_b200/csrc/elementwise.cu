@@ -405,25 +405,34 @@ __global__ void __launch_bounds__(256)
     }
   }
 }
-// out[c] = (accumulate ? out[c] : 0) + sum_r partial[r][c], fixed order
+// out[c] = (accumulate ? out[c] : 0) + sum_r partial[r][c], fixed order.  A CTA owns 32 columns; warp w adds rows
+// w, w + 8, ... with four loads in flight (one thread per column walking all rows was a chain of dependent L2
+// round trips that cost as much as the pass over the matrix), then the eight warp sums are added in order.
 template <typename T>
-__global__ void colsum_final_kernel(const float* __restrict__ partial, T* __restrict__ out, int R, int N,
-                                    int accumulate) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= N) return;
-  // eight loads in flight per thread (a chain of dependent loads from L2 made this kernel cost as much as the pass
-  // over the matrix); the order of the additions is fixed all the same
+__global__ void __launch_bounds__(256)
+    colsum_final_kernel(const float* __restrict__ partial, T* __restrict__ out, int R, int N, int accumulate) {
+  __shared__ float red[8][32];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int c = blockIdx.x * 32 + lane;
   float s = 0.f;
-  int r = 0;
-  for (; r + 8 <= R; r += 8) {
-    float v[8];
-#pragma unroll
-    for (int j = 0; j < 8; ++j) v[j] = __ldcg(partial + (long)(r + j) * N + c);
-    s += ((v[0] + v[1]) + (v[2] + v[3])) + ((v[4] + v[5]) + (v[6] + v[7]));
+  if (c < N) {
+    int r = warp;
+    for (; r + 24 < R; r += 32) {
+      const float v0 = __ldcg(partial + (long)r * N + c), v1 = __ldcg(partial + (long)(r + 8) * N + c);
+      const float v2 = __ldcg(partial + (long)(r + 16) * N + c), v3 = __ldcg(partial + (long)(r + 24) * N + c);
+      s += (v0 + v1) + (v2 + v3);
+    }
+    for (; r < R; r += 8) s += __ldcg(partial + (long)r * N + c);
   }
-  for (; r < R; ++r) s += __ldcg(partial + (long)r * N + c);
-  if (accumulate) s += sb::to_f(out[c]);
-  out[c] = sb::from_f<T>(s);
+  red[warp][lane] = s;
+  __syncthreads();
+  if (warp == 0 && c < N) {
+    float t = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) t += red[w][lane];
+    if (accumulate) t += sb::to_f(out[c]);
+    out[c] = sb::from_f<T>(t);
+  }
 }
 
 // ----------------------------------------------------------- masked softmax
@@ -656,7 +665,7 @@ SB_API int sb200_gelu_bwd_colsum(const void* dy, const void* x, void* dx, void* 
     gelu_bwd_colsum_kernel<T><<<dim3(strips, splits), 256, 0, stream>>>((const T*)dy, (const T*)x, (T*)dx, partial, M, N,
                                                                          rows_per);
     SB_CHECK_LAUNCH();
-    colsum_final_kernel<T><<<(N + 31) / 32, 32, 0, stream>>>(partial, (T*)bias_grad, splits, N, accumulate);
+    colsum_final_kernel<T><<<(N + 31) / 32, 256, 0, stream>>>(partial, (T*)bias_grad, splits, N, accumulate);
   });
   SB_CHECK_LAUNCH();
   return SB_OK;
@@ -673,7 +682,7 @@ SB_API int sb200_colsum(const void* x, void* out, float* partial, long M, int N,
     const long rows_per = (M + splits - 1) / splits;
     colsum_partial_kernel<T><<<dim3(strips, splits), 256, 0, stream>>>((const T*)x, partial, M, N, ld, rows_per);
     SB_CHECK_LAUNCH();
-    colsum_final_kernel<T><<<(N + 31) / 32, 32, 0, stream>>>(partial, (T*)out, splits, N, accumulate);
+    colsum_final_kernel<T><<<(N + 31) / 32, 256, 0, stream>>>(partial, (T*)out, splits, N, accumulate);
   });
   SB_CHECK_LAUNCH();
   return SB_OK;

@@ -525,21 +525,30 @@ __global__ void __launch_bounds__(64 + 128 * ROWT, FaFwdCfg<D>::TWO ? 2 : 1)
 template <int D>
 __global__ void fa_bwd_delta_kernel(const __nv_bfloat16* __restrict__ O, const __nv_bfloat16* __restrict__ dO,
                                     float* __restrict__ delta, int T, int Hq) {
-  // one warp per (t, h)
-  int w = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-  int lane = threadIdx.x & 31;
-  if (w >= T * Hq) return;
-  int t = w / Hq, h = w % Hq;
-  const __nv_bfloat16* o = O + ((long)t * Hq + h) * D;
-  const __nv_bfloat16* d = dO + ((long)t * Hq + h) * D;
+  // D / 8 lanes per (t, h) row, one 16-byte load of O and of dO each: the kernel is a stream over both tensors
+  constexpr int LPR = D / 8;
+  const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long row = idx / LPR;
+  const int part = (int)(idx - row * LPR);
+  const bool valid = row < (long)T * Hq;
   float s = 0.f;
-  for (int i = lane * 2; i < D; i += 64) {
-    float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(o + i));
-    float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(d + i));
-    s += a.x * b.x + a.y * b.y;
+  if (valid) {
+    const uint4 a = *reinterpret_cast<const uint4*>(O + row * D + part * 8);
+    const uint4 b = *reinterpret_cast<const uint4*>(dO + row * D + part * 8);
+    const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 x = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&aw[i]));
+      const float2 y = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&bw[i]));
+      s = fmaf(x.x, y.x, fmaf(x.y, y.y, s));
+    }
   }
-  s = sb::warp_sum(s);
-  if (lane == 0) delta[(long)h * T + t] = s;
+#pragma unroll
+  for (int o = LPR / 2; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);  // rows do not straddle warps
+  if (valid && part == 0) {
+    const int t = (int)(row / Hq), h = (int)(row - (long)t * Hq);
+    delta[(long)h * T + t] = s;
+  }
 }
 
 // ============================================================================ backward: dK, dV
@@ -1271,8 +1280,8 @@ SB_API int sb200_fa_bwd_strided(const void* q, const void* k, const void* v, con
   float* dk_part = splits > 1 ? dkv_partial : nullptr;
   float* dv_part = splits > 1 ? dkv_partial + (long)splits * T * Hkv * D : nullptr;
   {
-    long warps = (long)T * Hq;
-    int blocks = (int)((warps * 32 + 255) / 256);
+    const long threads = (long)T * Hq * (D / 8);
+    int blocks = (int)((threads + 255) / 256);
     if (D == 64)
       fa_bwd_delta_kernel<64><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)o, (const __nv_bfloat16*)d_o, delta, T, Hq);
     else
