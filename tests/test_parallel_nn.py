@@ -207,3 +207,28 @@ def test_fp8_linear_stays_close_to_the_full_precision_linear():
     assert torch.isfinite(big).all() and big.max() == torch.finfo(e4).max
     # a product without a dtype pair runs unquantised
     assert torch.allclose(fp8_linear(x, w, b), ref)
+
+
+def test_key_ranges_of_cross_length_attention_match_the_dense_mask():
+    """The per-query key ranges that the decode kernel reads describe exactly the mask of the dense expression, for
+    queries shorter and longer than the keys, causal or not, with and without a local window."""
+    import itertools
+
+    from scaling_b200.ops.attention import attention_mask_from_cu_seqlens
+    from scaling_b200.ops.attention_kernel import key_ranges
+
+    gen = torch.Generator().manual_seed(5)
+    for trial in range(60):
+        docs = int(torch.randint(1, 4, (1,), generator=gen))
+        len_q = torch.randint(1, 6, (docs,), generator=gen)
+        len_k = len_q + torch.randint(0, 9, (docs,), generator=gen)
+        if trial % 5 == 0:
+            len_k = torch.maximum(len_q - 2, torch.ones_like(len_q))  # fewer keys than queries
+        cu_q = torch.cat([torch.zeros(1, dtype=torch.long), len_q.cumsum(0)]).int()
+        cu_k = torch.cat([torch.zeros(1, dtype=torch.long), len_k.cumsum(0)]).int()
+        tq, tk = int(cu_q[-1]), int(cu_k[-1])
+        for causal, window in itertools.product((True, False), (None, 0, 2, 100)):
+            allowed = attention_mask_from_cu_seqlens(cu_q, cu_k, tq, tk, causal, window)
+            lo, hi = key_ranges(cu_q, cu_k, tq, causal, window)
+            keys = torch.arange(tk)[None]
+            assert torch.equal(allowed, (keys >= lo[:, None]) & (keys < hi[:, None])), (cu_q, cu_k, causal, window)
