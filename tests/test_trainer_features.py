@@ -252,3 +252,49 @@ def test_evaluation_between_training_steps_agrees_across_layouts(tmp_path: Path)
         for a, b in zip(got, base):
             assert a.keys() == b.keys()
             assert all(abs(a[k] - b[k]) < 2e-5 * max(1.0, abs(b[k])) for k in a), (kw, got, base)
+
+
+def _run_with(load_dir, **trainer):
+    cfg = tiny_config(1, iters=2, load_dir=str(load_dir))
+    cfg["trainer"].update(trainer)
+    return dist_launcher(run_training, 1, config=cfg)[0]
+
+
+def test_older_layer_class_names_and_non_strict_loading(tmp_path: Path):
+    """A checkpoint whose files carry the layer class names of the earlier code base loads like a current one; keys
+    missing from or unknown to the model stop the load unless the config allows or ignores them."""
+    import shutil
+
+    import torch
+
+    from scaling_b200.core.nn.parallel_module.partitioned_module import _is_legacy_checkpoint, legacy_checkpoint_mapping
+
+    init = tmp_path / "init"
+    base = losses(1, save_initial=str(init), iters=2)
+    step = next(p for p in init.iterdir() if p.is_dir())
+
+    old = tmp_path / "old"
+    shutil.copytree(init, old)
+    renamed = 0
+    for f in sorted((old / step.name).glob("model_state_layer_*.pt")):
+        for new_name, old_name in legacy_checkpoint_mapping.items():
+            if f.name.endswith(f"_{new_name}.pt"):
+                f.rename(f.with_name(f.name.replace(f"_{new_name}.pt", f"_{old_name}.pt")))
+                renamed += 1
+    assert renamed >= 3 and _is_legacy_checkpoint([old / step.name]) and not _is_legacy_checkpoint([step])
+    assert _run_with(old) == base
+
+    holes = tmp_path / "holes"
+    shutil.copytree(init, holes)
+    block = holes / step.name / "model_state_layer_1_TransformerLayer.pt"
+    state = torch.load(block, weights_only=False)
+    del state["mlp.dense_in.bias"]
+    state["removed_module.weight"] = torch.zeros(3)
+    torch.save(state, block)
+    with pytest.raises(AssertionError, match="Unexpected keys in checkpoint"):
+        _run_with(holes, load_optimizer_states=False)
+    with pytest.raises(AssertionError, match="Missing keys in checkpoint"):
+        _run_with(holes, load_optimizer_states=False, ignore_keys_in_checkpoint=["removed_module"])
+    got = _run_with(holes, load_optimizer_states=False, ignore_keys_in_checkpoint=["removed_module"],
+                    allowed_missing_keys_in_checkpoint=[r"dense_in\.bias"])
+    assert len(got) == 2 and all(abs(a - b) < 0.05 for a, b in zip(got, base))
