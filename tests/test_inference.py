@@ -124,3 +124,22 @@ def test_checkpoint_of_a_tensor_parallel_run_loads_into_the_inference_module(tmp
     assert torch.allclose(logits["tp"], logits["one"], atol=2e-4), (logits["tp"] - logits["one"]).abs().max()
     with pytest.raises(AssertionError, match="Config file not found"):
         TransformerInferenceModule.from_checkpoint(tmp_path / "one", devices=("cpu",))  # the step folder is the checkpoint
+
+
+def test_sentence_embeddings_from_a_model_without_a_language_model_head():
+    """``encode`` returns one row of hidden states per sentence, padded to the longest prompt of its batch; an
+    instruction lengthens every prompt, ``max_length`` cuts it."""
+    tok = Tokenizer.from_words([f"w{i}" for i in range(30)])
+    torch.manual_seed(0)
+    arch = TransformerArchitectureConfig.from_dict(dict(ARCH, lm_head=False))
+    m = TransformerInferenceModule(get_transformer_layer_specs(architecture_config=arch), devices=("cpu",),
+                                   tokenizer=tok)
+    marks = dict(user_token="w1 ", embed_token="w2 ", pad_token="w0")
+    two = m.encode(["w5 w6", "w7 w8 w9 w10"], **marks)
+    one = m.encode("w5 w6 w7 w8 w9 w10", convert_to_tensor=True, **marks)
+    assert two.shape == (2, 6, 32) and tuple(one.shape) == (1, 8, 32) and isinstance(one, torch.Tensor)
+    assert torch.isfinite(torch.as_tensor(two)).all()
+    instructed = m.encode(["w5 w6"] * 5, instruction="w11 w12 ", batch_size=2, **marks)
+    assert instructed.shape == (5, 6, 32)
+    assert m.encode(["w5 " * 40], max_length=16, **marks).shape == (1, 16, 32)
+    assert m.encode_queries(["w5 w6"], **marks).shape == m.encode_corpus([{"title": "w5", "text": "w6"}], **marks).shape
