@@ -198,3 +198,22 @@ def test_multi_query_attention_with_fewer_kv_heads_than_tensor_parallel_ranks(tm
     tail = losses(1, load_dir=ckpt, arch=arch)
     for a, b in zip(head + tail, base):
         assert abs(a - b) < 2e-5 * max(1.0, abs(b)), (head, tail, base)
+
+
+@pytest.mark.dist
+def test_local_attention_windows_train_and_layouts_agree(tmp_path: Path):
+    """Heads restricted to a window of recent tokens (all of them, or the first two of four next to two global
+    heads): the window changes the result, and pipeline / tensor / data parallel layouts reproduce it."""
+    init = str(tmp_path / "init")
+    plain = losses(1, save_initial=init)
+    mixed_arch = {"num_local_attention_heads": 2, "local_attention_window_size": 8}
+    mixed = losses(1, load_dir=init, arch=mixed_arch)
+    assert mixed[-1] < mixed[0] and max(abs(a - b) for a, b in zip(mixed, plain)) > 1e-4
+    got = losses(2, load_dir=init, arch=mixed_arch, pp=2, ga=2, micro=2)
+    assert all(abs(a - b) < 2e-3 for a, b in zip(got, mixed)), (got, mixed)
+    all_arch = {"num_local_attention_heads": 4, "local_attention_window_size": 8}
+    local = losses(1, load_dir=init, arch=all_arch)
+    assert max(abs(a - b) for a, b in zip(local, mixed)) > 1e-5
+    for kw in (dict(mp=2), dict(zero=True)):
+        got = losses(2, load_dir=init, arch=all_arch, **kw)
+        assert all(abs(a - b) < 2e-3 for a, b in zip(got, local)), (kw, got, local)
