@@ -225,3 +225,28 @@ def test_a_parameter_added_at_resume_counts_its_own_adam_steps(tmp_path: Path, w
     for ages, adam_steps, err in results:
         assert ages == [0, 6, 0] and adam_steps == 9
         assert err < 1e-6
+
+
+def _pattern_on_another_stage_worker(rank, world_size, port, device):
+    """A finetuning pattern may match parameters of another pipeline stage only; it fails if it matches on no rank."""
+    from scaling_b200.transformer.context.config import TrainingGroupConfig
+    from scaling_b200.transformer.model.model import _extract_parameters
+
+    _topology(rank, world_size, port)
+    mine = [("stage0.image_encoder.w", torch.nn.Parameter(torch.zeros(1)), None)] if rank == 0 else \
+        [("stage1.summarization.w", torch.nn.Parameter(torch.zeros(1)), None)]
+    group = [TrainingGroupConfig(group_name="g", parameters_include=["summarization", "image_encoder"])]
+    (members, _), = _extract_parameters(group, mine, True)
+    try:
+        _extract_parameters([TrainingGroupConfig(group_name="g", parameters_include=["summarization", "nowhere"])],
+                            mine, True)
+        error = None
+    except ValueError as e:
+        error = str(e)
+    return [n for n, _, _ in members], error
+
+
+def test_finetuning_patterns_are_matched_over_all_ranks():
+    results = dist_launcher(_pattern_on_another_stage_worker, 2)
+    assert results[0][0] == ["stage0.image_encoder.w"] and results[1][0] == ["stage1.summarization.w"]
+    assert all("Unmatched finetunable parameters: {'nowhere'}" in r[1] for r in results)

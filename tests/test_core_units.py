@@ -350,3 +350,33 @@ def test_hyper_parameters_become_config_overrides():
     assert hparams_to_overrides({"layout": {"learning_rate": 1.0}, "learning_rate": 2.0})["learning_rate_scheduler"] == {
         "learning_rate": 1.0}
     assert hparams_to_overrides(None, {"a": 1}) == {"a": 1}
+
+
+def test_training_groups_select_parameters_by_pattern():
+    """Include / exclude patterns pick the members of an optimizer group; a pattern that matches nothing, a parameter
+    claimed by two groups and a parameter left without a group are errors (the last one can be allowed)."""
+    import pytest
+    import torch
+
+    from scaling_b200.transformer.context.config import TrainingGroupConfig
+    from scaling_b200.transformer.model.model import _extract_parameters
+
+    def named(*names):
+        return [(n, torch.nn.Parameter(torch.zeros(1)), None) for n in names]
+
+    params = named("layers.1.adapter_x.weight", "layers.1.adapter_x.bias", "layers.1.mlp.weight", "image_encoder.baz")
+    pick = [TrainingGroupConfig(group_name="g", parameters_include=["adapter_x", "image_encoder"],
+                                parameters_exclude=[r"\.bias$"])]
+    (members, group), = _extract_parameters(pick, params, allow_missing_params_in_optimizer=True)
+    assert [n for n, _, _ in members] == ["layers.1.adapter_x.weight", "image_encoder.baz"] and group.group_name == "g"
+    with pytest.raises(ValueError, match="not added to any optimizer group"):
+        _extract_parameters(pick, params, allow_missing_params_in_optimizer=False)
+    with pytest.raises(ValueError, match=r"Unmatched finetunable parameters: \{'summarization'\}"):
+        _extract_parameters([TrainingGroupConfig(group_name="g", parameters_include=["adapter_x", "summarization"])],
+                            params, True)
+    overlap = [TrainingGroupConfig(group_name="a", parameters_include=["adapter_x"]),
+               TrainingGroupConfig(group_name="b", parameters_include=[r"\.bias$"])]
+    with pytest.raises(ValueError, match="more then one training_group"):
+        _extract_parameters(overlap, params, True)
+    everything = _extract_parameters([TrainingGroupConfig(group_name="all")], params, False)
+    assert len(everything[0][0]) == 4
