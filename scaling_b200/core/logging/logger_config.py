@@ -50,6 +50,9 @@ def rank_selected(rank: Optional[int], ranks: Optional[list[int]]) -> bool:
     return rank in ranks if ranks is not None else rank == 0
 
 
+check_if_in_rank = rank_selected  # the name under which src/scaling/core/logging/logger_config.py:118 has it
+
+
 class LoggerConfig(BaseConfig):
     log_level: LogLevel = Field(LogLevel.INFO, description="console / file log level")
     log_dir: Optional[Path] = Field(None, description="directory for per-rank log files and tensorboard events")

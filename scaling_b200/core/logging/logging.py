@@ -154,7 +154,7 @@ class DeterminedLogger(Logger):
 
     def log_metrics(self, metrics: dict[str, Any], step: int, to_info: bool = True, to_wandb: bool = True) -> None:
         super().log_metrics(metrics, step, to_info=to_info, to_wandb=to_wandb)
-        if self.config.is_rank_in_determined_metrics_ranks(self.global_rank):
+        if self.determined_context is not None and self.config.is_rank_in_determined_metrics_ranks(self.global_rank):
             train = {k: v for k, v in metrics.items() if not k.startswith("evaluation")}
             evaluation = {k: v for k, v in metrics.items() if k.startswith("evaluation")}
             if train:
@@ -173,9 +173,11 @@ class _LoggerSingleton:
                   tensorboard_ranks: Optional[list[int]] = None) -> None:
         self._impl = Logger(config, name=name, global_rank=global_rank, tensorboard_ranks=tensorboard_ranks)
 
-    def configure_determined(self, config: LoggerConfig, determined_context: Any, determined_profiler: Any = None,
-                             name: Optional[str] = None, global_rank: Optional[int] = None,
-                             tensorboard_ranks: Optional[list[int]] = None) -> None:
+    def configure_determined(self, config: LoggerConfig, name: Optional[str] = None, global_rank: Optional[int] = None,
+                             determined_context: Any = None, tensorboard_ranks: Optional[list[int]] = None,
+                             determined_profiler: Any = None) -> None:
+        """Argument order of src/scaling/core/logging/logging.py:224-233; without a context the Determined sink
+        stays silent."""
         self._impl = DeterminedLogger(config, determined_context, determined_profiler, name=name,
                                       global_rank=global_rank, tensorboard_ranks=tensorboard_ranks)
 

@@ -380,3 +380,39 @@ def test_training_groups_select_parameters_by_pattern():
         _extract_parameters(overlap, params, True)
     everything = _extract_parameters([TrainingGroupConfig(group_name="all")], params, False)
     assert len(everything[0][0]) == 4
+
+
+def test_logger_rank_filter_sinks_and_wandb_key(monkeypatch):
+    """Metrics sinks default to global rank 0 and otherwise follow the configured rank list; the singleton swaps
+    its implementation on ``configure`` / ``configure_determined``; wandb needs a key from the config or the
+    environment."""
+    import pytest
+    from pydantic import ValidationError
+
+    from scaling_b200.core.logging import DeterminedLogger, Logger, LoggerConfig, logger
+    from scaling_b200.core.logging.logger_config import check_if_in_rank
+
+    for ranks in ([], None, [0], [42], [36]):
+        for rank in (None, 0, 42):
+            want = rank is not None and ((ranks is None and rank == 0) or (ranks is not None and rank in ranks))
+            assert check_if_in_rank(rank, ranks) == want
+    logger.configure(LoggerConfig())
+    assert type(logger._impl) is Logger
+    logger.configure_determined(LoggerConfig())
+    assert type(logger._impl) is DeterminedLogger
+    logger.log_metrics({"training/loss": 1.0}, step=1)  # no Determined context: nothing to report to, no error
+    logger.configure(LoggerConfig())
+    assert type(logger._impl) is Logger
+
+    monkeypatch.setenv("WANDB_API_KEY", "from-env")
+    assert LoggerConfig().wandb_api_key == "from-env"
+    assert LoggerConfig(wandb_api_key="given").wandb_api_key == "given"
+    assert LoggerConfig(use_wandb=True).wandb_api_key == "from-env"
+    monkeypatch.setenv("WANDB_API_KEY", "")
+    with pytest.raises(ValidationError, match="wandb api key needs to be provided"):
+        LoggerConfig(use_wandb=True)
+    monkeypatch.delenv("WANDB_API_KEY")
+    with pytest.raises(ValidationError):
+        LoggerConfig(use_wandb=True, wandb_api_key=None)
+    assert LoggerConfig(use_wandb=True, wandb_api_key="k").use_wandb
+    assert not LoggerConfig(use_wandb=False, wandb_api_key="").use_wandb
