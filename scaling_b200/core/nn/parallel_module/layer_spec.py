@@ -30,7 +30,22 @@ class LayerSpec:
 
 
 class TiedLayerSpec(LayerSpec):
-    def __init__(self, module_class: type, key: str, tied_weight_attributes: list[str], *args: Any, **kwargs: Any):
-        super().__init__(module_class, *args, **kwargs)
-        self.key = key
-        self.tied_weight_attributes = list(tied_weight_attributes)
+    """``TiedLayerSpec(module_class, key, tied_weight_attributes, *args, **kwargs)``; the three may also be given by
+    keyword or in the order ``(key, tied_weight_attributes, module_class)`` of
+    src/scaling/core/nn/parallel_module/layer_spec.py:19-32."""
+
+    def __init__(self, *args: Any, **kwargs: Any):
+        names = ("module_class", "key", "tied_weight_attributes")
+        given = {n: kwargs.pop(n) for n in names if n in kwargs}
+        rest = list(args)
+        order = names if (rest and isinstance(rest[0], type)) else ("key", "tied_weight_attributes", "module_class")
+        for n in order:
+            if n not in given:
+                if not rest:
+                    raise TypeError(f"TiedLayerSpec: missing argument '{n}'")
+                given[n] = rest.pop(0)
+        super().__init__(given["module_class"], *rest, **kwargs)
+        self.key = given["key"]
+        attributes = list(given["tied_weight_attributes"])
+        assert len(set(attributes)) == len(attributes), f"duplicates in tied_weight_attributes: {attributes}"
+        self.tied_weight_attributes = attributes

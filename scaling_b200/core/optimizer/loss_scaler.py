@@ -43,7 +43,10 @@ class LossScalerOutput(NamedTuple):
 
 
 class LossScaler:
-    def __init__(self, config: LossScalerConfig, parameters: Optional[list[torch.Tensor]] = None):
+    def __init__(self, config: LossScalerConfig, parameter_groups: Optional[list] = None,
+                 parameters: Optional[list[torch.Tensor]] = None):
+        # The gradients are not needed here: overflow is detected on the device inside the optimizer step and handed
+        # to ``step``; the arguments keep the constructor of src/scaling/core/optimizer/loss_scaler.py callable as is.
         self.config = config
         self._current_scale = config.initial_scale
         self._current_hysteresis = config.hysteresis

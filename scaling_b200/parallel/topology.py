@@ -93,10 +93,10 @@ class Topology:
     # ------------------------------------------------------------------ distributed init
     def initialize_distributed(
         self,
-        seed: int = 42,
         master_addr: Optional[str] = None,
         master_port: Optional[str] = None,
         torch_distributed_timeout_minutes: int = 20,
+        seed: int = 42,
     ) -> None:
         assert self.config.global_rank is not None, "global_rank is required to initialize torch.distributed"
         self.initialize_device()
@@ -317,8 +317,10 @@ class Topology:
         pipe_parallel_rank: Optional[int] = None,
         data_parallel_rank: Optional[int] = None,
         model_parallel_rank: Optional[int] = None,
-    ) -> list[int]:
-        """All global ranks matching the given coordinates (None = wildcard)."""
+        flatten: bool = True,
+    ) -> list:
+        """All global ranks matching the given coordinates (None = wildcard); ``flatten=False`` keeps the
+        ``[pipe][data][model]`` nesting."""
         sel = self._grid[
             slice(None) if pipe_parallel_rank is None else [pipe_parallel_rank],
             :,
@@ -326,4 +328,4 @@ class Topology:
         ]
         sel = sel[:, slice(None) if data_parallel_rank is None else [data_parallel_rank], :]
         sel = sel[:, :, slice(None) if model_parallel_rank is None else [model_parallel_rank]]
-        return [int(r) for r in sel.flatten()]
+        return [int(r) for r in sel.flatten()] if flatten else sel.tolist()

@@ -416,3 +416,25 @@ def test_logger_rank_filter_sinks_and_wandb_key(monkeypatch):
         LoggerConfig(use_wandb=True, wandb_api_key=None)
     assert LoggerConfig(use_wandb=True, wandb_api_key="k").use_wandb
     assert not LoggerConfig(use_wandb=False, wandb_api_key="").use_wandb
+
+
+def test_tied_layer_spec_argument_orders_and_rank_groups():
+    """``TiedLayerSpec`` takes its three leading arguments by keyword, module class first, or key first; rank groups
+    can be returned nested."""
+    import torch
+
+    from scaling_b200.core.nn.parallel_module.layer_spec import TiedLayerSpec
+    from scaling_b200.parallel import Topology, TopologyConfig
+
+    lin = torch.nn.Linear
+    specs = [TiedLayerSpec(lin, "k", ["weight"], 3, 4), TiedLayerSpec("k", ["weight"], lin, in_features=3, out_features=4),
+             TiedLayerSpec(module_class=lin, key="k", tied_weight_attributes=["weight"], in_features=3, out_features=4)]
+    for s in specs:
+        assert s.key == "k" and s.tied_weight_attributes == ["weight"] and s.initialize().weight.shape == (4, 3)
+    t = Topology(TopologyConfig.from_dict({"world_size": 8, "model_parallel_size": 2, "pipe_parallel_size": 2,
+                                           "data_parallel_size": 2, "global_rank": 0, "micro_batch_size": 1,
+                                           "gradient_accumulation_steps": 1, "device": "cpu", "backend": "gloo"}))
+    flat = t.get_global_rank_group(pipe_parallel_rank=1)
+    nested = t.get_global_rank_group(pipe_parallel_rank=1, flatten=False)
+    assert len(flat) == 4 and len(nested) == 1 and len(nested[0]) == 2 and len(nested[0][0]) == 2
+    assert [r for d in nested[0] for r in d] == flat
