@@ -73,8 +73,16 @@ class _FP8Linear(torch.autograd.Function):
         return dx, dw, db, None, None, None
 
 
-def fp8_linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None,
-               dtypes_forward: Optional[tuple[torch.dtype, torch.dtype]] = None,
-               dtypes_grad_input: Optional[tuple[torch.dtype, torch.dtype]] = None,
-               dtypes_grad_weight: Optional[tuple[torch.dtype, torch.dtype]] = None) -> torch.Tensor:
-    return _FP8Linear.apply(x, weight, bias, dtypes_forward, dtypes_grad_input, dtypes_grad_weight)
+E4M3, E5M2 = torch.float8_e4m3fn, torch.float8_e5m2
+
+
+def fp8_linear(input: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None,  # noqa: A002
+               dtypes_forward: Optional[tuple[torch.dtype, torch.dtype]] = (E4M3, E4M3),
+               dtypes_grad_input: Optional[tuple[torch.dtype, torch.dtype]] = (E5M2, E4M3),
+               dtypes_grad_weight: Optional[tuple[torch.dtype, torch.dtype]] = (E4M3, E5M2)) -> torch.Tensor:
+    """Signature and defaults of src/scaling/core/fp8/fp8_linear.py:76-83: e4m3 operands forward, e5m2 for the
+    incoming gradient in both backward products; ``None`` for a pair leaves that product unquantised."""
+    return _FP8Linear.apply(input, weight, bias, dtypes_forward, dtypes_grad_input, dtypes_grad_weight)
+
+
+to_fp8_saturated = saturating_cast  # the name in src/scaling/core/fp8/fp8_linear.py:10

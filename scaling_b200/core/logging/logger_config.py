@@ -50,7 +50,9 @@ def rank_selected(rank: Optional[int], ranks: Optional[list[int]]) -> bool:
     return rank in ranks if ranks is not None else rank == 0
 
 
-check_if_in_rank = rank_selected  # the name under which src/scaling/core/logging/logger_config.py:118 has it
+def check_if_in_rank(target_rank: Optional[int], ranks: Optional[list[int]]) -> bool:
+    """Name and signature of src/scaling/core/logging/logger_config.py:118."""
+    return rank_selected(target_rank, ranks)
 
 
 class LoggerConfig(BaseConfig):

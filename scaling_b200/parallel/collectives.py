@@ -149,13 +149,20 @@ class _ReduceScatterTokens(torch.autograd.Function):
 
 class _GatherTokens(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, topology):  # type: ignore[override]
+    def forward(ctx, x, topology, reduce_grad=True):  # type: ignore[override]
         ctx.topology = topology
+        ctx.reduce_grad = reduce_grad
         return all_gather_tokens_raw(x, topology)
 
     @staticmethod
     def backward(ctx, g):  # type: ignore[override]
-        return reduce_scatter_tokens_raw(g, ctx.topology), None
+        if ctx.reduce_grad:
+            return reduce_scatter_tokens_raw(g, ctx.topology), None, None
+        t = ctx.topology
+        n, r = t.model_parallel_size, t.model_parallel_rank
+        flat = g.contiguous().view(-1)
+        chunk = flat.numel() // n
+        return flat[r * chunk:(r + 1) * chunk].clone().view(_sp_out_shape(g.shape, n, gather=False)), None, None
 
 
 class _ShardTokens(torch.autograd.Function):
@@ -180,28 +187,60 @@ def shard_to_sequence_parallel_region(x: torch.Tensor, topology: Optional[Topolo
     return x if _size(topology) == 1 else _ShardTokens.apply(x, topology)
 
 
-def copy_to_tensor_model_parallel_region(x: torch.Tensor, topology: Optional[Topology]) -> torch.Tensor:
-    return x if _size(topology) == 1 else _CopyToRegion.apply(x, topology)
+# The six functions below take ``(input_tensor, topology)``; ``all_concat`` / ``all_shard`` also the form
+# ``(input_tensor, dim, topology)`` and ``gather_from_sequence_parallel_region`` the flag
+# ``tensor_parallel_output_grad`` of src/scaling/core/nn/linear/utils.py:195-252, so layers written against those run.
+def _dim_and_topology(args: tuple, kwargs: dict) -> tuple[int, Optional[Topology]]:
+    dim = kwargs.pop("dim", None)
+    topology = kwargs.pop("topology", None)
+    rest = list(args)
+    if rest and isinstance(rest[0], int) and not isinstance(rest[0], bool):
+        dim = rest.pop(0)
+    if rest:
+        topology = rest.pop(0)
+    assert not rest and not kwargs, f"unexpected arguments {rest} {kwargs}"
+    return (-1 if dim is None else dim), topology
 
 
-def all_reduce(x: torch.Tensor, topology: Optional[Topology]) -> torch.Tensor:
-    return x if _size(topology) == 1 else _AllReduce.apply(x, topology)
+def _on_last_dim(fn, x: torch.Tensor, dim: int, topology: Topology) -> torch.Tensor:
+    if dim in (-1, x.dim() - 1):
+        return fn(x, topology)
+    return fn(x.transpose(dim, -1), topology).transpose(dim, -1)
 
 
-def all_concat(x: torch.Tensor, topology: Optional[Topology]) -> torch.Tensor:
-    return x if _size(topology) == 1 else _AllConcat.apply(x, topology)
+def copy_to_tensor_model_parallel_region(input_tensor: torch.Tensor, topology: Optional[Topology]) -> torch.Tensor:
+    return input_tensor if _size(topology) == 1 else _CopyToRegion.apply(input_tensor, topology)
 
 
-def all_shard(x: torch.Tensor, topology: Optional[Topology]) -> torch.Tensor:
-    return x if _size(topology) == 1 else _AllShard.apply(x, topology)
+def all_reduce(input_tensor: torch.Tensor, topology: Optional[Topology]) -> torch.Tensor:
+    return input_tensor if _size(topology) == 1 else _AllReduce.apply(input_tensor, topology)
 
 
-def all_reduce_scatter_to_sequence_parallel(x: torch.Tensor, topology: Optional[Topology]) -> torch.Tensor:
-    return x if _size(topology) == 1 else _ReduceScatterTokens.apply(x, topology)
+def all_concat(input_tensor: torch.Tensor, *args, **kwargs) -> torch.Tensor:
+    """Gather the shards of dimension ``dim`` (default: the last) from the tensor-parallel ranks; backward keeps
+    this rank's shard of the gradient."""
+    dim, topology = _dim_and_topology(args, kwargs)
+    return input_tensor if _size(topology) == 1 else _on_last_dim(_AllConcat.apply, input_tensor, dim, topology)
 
 
-def gather_from_sequence_parallel_region(x: torch.Tensor, topology: Optional[Topology]) -> torch.Tensor:
-    return x if _size(topology) == 1 else _GatherTokens.apply(x, topology)
+def all_shard(input_tensor: torch.Tensor, *args, **kwargs) -> torch.Tensor:
+    """Keep this rank's shard of dimension ``dim`` (default: the last); backward gathers the gradient shards."""
+    dim, topology = _dim_and_topology(args, kwargs)
+    return input_tensor if _size(topology) == 1 else _on_last_dim(_AllShard.apply, input_tensor, dim, topology)
+
+
+def all_reduce_scatter_to_sequence_parallel(input_tensor: torch.Tensor, topology: Optional[Topology]) -> torch.Tensor:
+    return input_tensor if _size(topology) == 1 else _ReduceScatterTokens.apply(input_tensor, topology)
+
+
+def gather_from_sequence_parallel_region(input_tensor: torch.Tensor, topology: Optional[Topology],
+                                         tensor_parallel_output_grad: bool = True) -> torch.Tensor:
+    """Gather the token shards; the gradient is summed over the ranks and scattered back (the consumers are
+    tensor-parallel and see different gradients) or, with ``tensor_parallel_output_grad=False``, only split (the
+    consumers are replicated and every rank already holds the whole gradient)."""
+    if _size(topology) == 1:
+        return input_tensor
+    return _GatherTokens.apply(input_tensor, topology, tensor_parallel_output_grad)
 
 
 class SequenceShard:

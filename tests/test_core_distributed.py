@@ -250,3 +250,34 @@ def test_finetuning_patterns_are_matched_over_all_ranks():
     results = dist_launcher(_pattern_on_another_stage_worker, 2)
     assert results[0][0] == ["stage0.image_encoder.w"] and results[1][0] == ["stage1.summarization.w"]
     assert all("Unmatched finetunable parameters: {'nowhere'}" in r[1] for r in results)
+
+
+def _collective_forms_worker(rank, world_size, port, device):
+    """``all_concat`` / ``all_shard`` with an explicit dimension and the gather over tokens with and without the
+    gradient reduction, called the way src/scaling/core/nn/linear/utils.py:195-252 declares them."""
+    from scaling_b200.parallel.collectives import all_concat, all_shard, gather_from_sequence_parallel_region
+
+    t = _topology(rank, world_size, port, mp=2)
+    torch.manual_seed(1)
+    full = torch.randn(2, 4, 6)
+    mine = full[:, rank * 2:(rank + 1) * 2].clone().requires_grad_()
+    gathered = all_concat(mine, 1, t)
+    ok = torch.equal(gathered, full) and torch.equal(all_concat(input_tensor=mine, dim=1, topology=t), full)
+    (gathered * full).sum().backward()
+    ok &= torch.equal(mine.grad, full[:, rank * 2:(rank + 1) * 2])
+    ok &= torch.equal(all_shard(full, 1, t), full[:, rank * 2:(rank + 1) * 2])
+    ok &= torch.equal(all_shard(full, t), full[..., rank * 3:(rank + 1) * 3])
+    grads = []
+    for reduce_grad in (True, False):
+        tokens = full[:, rank * 2:(rank + 1) * 2].clone().requires_grad_()
+        out = gather_from_sequence_parallel_region(tokens, t, tensor_parallel_output_grad=reduce_grad)
+        ok &= out.shape == full.shape
+        (out * (rank + 1.0)).sum().backward()
+        grads.append(float(tokens.grad[0, 0, 0]))
+    return bool(ok), grads
+
+
+def test_collectives_accept_the_dimension_and_gradient_forms():
+    for rank, (ok, grads) in enumerate(dist_launcher(_collective_forms_worker, 2)):
+        assert ok
+        assert grads == [3.0, rank + 1.0]  # summed over both ranks' consumers, or this rank's own gradient only

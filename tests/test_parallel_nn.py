@@ -205,8 +205,9 @@ def test_fp8_linear_stays_close_to_the_full_precision_linear():
     # saturation instead of inf: values beyond the format's range clamp to its maximum
     big = fp8_linear(torch.full((1, 4), 1e6), torch.eye(4), None, dtypes_forward=(e4, e4))
     assert torch.isfinite(big).all() and big.max() == torch.finfo(e4).max
-    # a product without a dtype pair runs unquantised
-    assert torch.allclose(fp8_linear(x, w, b), ref)
+    # a product without a dtype pair runs unquantised; left out, the pairs default to the ones used above
+    assert torch.allclose(fp8_linear(x, w, b, None, None, None), ref)
+    assert torch.equal(fp8_linear(x, w, b), y)
 
 
 def test_key_ranges_of_cross_length_attention_match_the_dense_mask():
