@@ -119,8 +119,13 @@ class SimulationEngine:
     """Event simulation: compute instructions take their measured time, communication completes when
     both partners have arrived (plus the transfer time), the tied-gradient reduction is a barrier."""
 
-    def __init__(self, schedule_cls: Type, gradient_accumulation_steps: int, pipe_parallel_size: int,
-                 durations: Optional[dict[str, float]] = None, default_duration: float = 1.0):
+    def __init__(self, schedule_cls: Type, gradient_accumulation_steps: Any = None, pipe_parallel_size: int = 1,
+                 durations: Optional[dict[str, float]] = None, default_duration: float = 1.0,
+                 profile_data: Optional[dict] = None):
+        if isinstance(gradient_accumulation_steps, dict):  # SimulationEngine(schedule, profile_data)
+            profile_data, gradient_accumulation_steps = gradient_accumulation_steps, None
+        if profile_data is not None:
+            gradient_accumulation_steps, pipe_parallel_size, durations = self._read_profile(profile_data)
         self.stages = pipe_parallel_size
         self.durations = durations or {}
         self.default_duration = default_duration
@@ -131,8 +136,13 @@ class SimulationEngine:
 
     @classmethod
     def from_profile(cls, schedule_cls: Type, profile_file: str | Path) -> "SimulationEngine":
-        data = json.loads(Path(profile_file).read_text())
-        topo = data["topology"]
+        return cls(schedule_cls, profile_data=json.loads(Path(profile_file).read_text()))
+
+    @staticmethod
+    def _read_profile(data: dict) -> tuple[int, int, dict[str, float]]:
+        """(gradient accumulation steps, pipeline stages, mean duration per timer and per timer@stage) of a gathered
+        profile: sizes at the top level or under "topology", observations as dicts or as rows of "fields"."""
+        topo = data if "pipe_parallel_size" in data else data["topology"]
         fields = data.get("fields") or ["timer_name", "step", "micro_batch_id", "buffer_id", "pipe_parallel_rank",
                                         "data_parallel_rank", "model_parallel_rank", "duration"]
         sums: dict[str, list[float]] = defaultdict(list)
@@ -141,7 +151,7 @@ class SimulationEngine:
             sums[f"{rec['timer_name']}@{rec['pipe_parallel_rank']}"].append(float(rec["duration"]))
             sums[rec["timer_name"]].append(float(rec["duration"]))
         durations = {k: sum(v) / len(v) for k, v in sums.items()}
-        return cls(schedule_cls, topo["gradient_accumulation_steps"], topo["pipe_parallel_size"], durations)
+        return topo["gradient_accumulation_steps"], topo["pipe_parallel_size"], durations
 
     def get_duration(self, name: str, stage: int) -> float:
         for key in (f"{name}@{stage}", name, f"Instruction{name}"):

@@ -74,10 +74,18 @@ class Profiler:
         if self.topology.config.global_rank in (0, None) and self.config.profiler_output is not None:
             out = Path(self.config.profiler_output)
             out.parent.mkdir(parents=True, exist_ok=True)
+            # top-level sizes and one dict per observation as in src/scaling/core/profiler/profiler.py:94-101; the
+            # whole topology config in addition
+            tc = self.topology.config
+            fields = list(ProfilerObservation._fields)
+            rows = [r for part in (gathered or []) for r in (part or [])]
             payload = {
-                "topology": self.topology.config.as_dict(),
-                "fields": list(ProfilerObservation._fields),
-                "observations": [r for part in (gathered or []) for r in (part or [])],
+                "pipe_parallel_size": tc.pipe_parallel_size, "data_parallel_size": tc.data_parallel_size,
+                "model_parallel_size": tc.model_parallel_size,
+                "gradient_accumulation_steps": tc.gradient_accumulation_steps,
+                "topology": tc.as_dict(),
+                "fields": fields,
+                "observations": [dict(zip(fields, r)) if isinstance(r, (list, tuple)) else r for r in rows],
             }
             out.write_text(json.dumps(payload))
 

@@ -41,8 +41,9 @@ def test_profiler_writes_per_instruction_timings_under_pipeline_parallelism(tmp_
     cfg["profiler"] = {"profile_steps": 2, "profile_start_at_step": 1, "profiler_output": str(tmp_path / "profile.json")}
     dist_launcher(_profiled, 2, config=cfg)
     profile = json.loads((tmp_path / "profile.json").read_text())
-    fields = profile["fields"]
-    rows = [dict(zip(fields, r)) for r in profile["observations"]]
+    rows = profile["observations"]  # one record per timed instruction
+    assert profile["pipe_parallel_size"] == 2 and profile["gradient_accumulation_steps"] == 2
+    assert set(profile["fields"]) == set(rows[0])
     names = {r["timer_name"] for r in rows}
     assert {"ForwardPass", "BackwardPass", "SendActivation", "RecvActivation"} <= names, names
     assert {r["pipe_parallel_rank"] for r in rows} == {0, 1}  # gathered from both stages on rank 0
@@ -54,6 +55,9 @@ def test_profiler_writes_per_instruction_timings_under_pipeline_parallelism(tmp_
     engine = SimulationEngine.from_profile(PipelineScheduleTrain, tmp_path / "profile.json")
     engine.simulate()
     assert engine.summarize()["total_time"] > 0
+    again = SimulationEngine(PipelineScheduleTrain, profile)  # the gathered record itself
+    again.simulate()
+    assert again.summarize()["total_time"] == engine.summarize()["total_time"]
 
 
 def test_past_optimizer_states_are_deleted_and_latest_points_to_the_last_checkpoint(tmp_path: Path):
