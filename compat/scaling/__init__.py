@@ -29,7 +29,6 @@ RENAMED = {
     "scaling.core.topology.rng_tracker": "scaling_b200.parallel.rng_tracker",
     "scaling.core.nn.linear.column_parallel_linear": "scaling_b200.core.nn.linear.parallel_linear",
     "scaling.core.nn.linear.row_parallel_linear": "scaling_b200.core.nn.linear.parallel_linear",
-    "scaling.core.nn.linear.utils": "scaling_b200.parallel.collectives",
     "scaling.core.nn.lora_config": "scaling_b200.core.nn.lora",
     "scaling.core.nn.rotary_config": "scaling_b200.core.nn.rotary",
     "scaling.core.nn.masked_softmax.masked_softmax_config": "scaling_b200.core.nn.masked_softmax.masked_softmax",

@@ -21,10 +21,13 @@ import torch
 
 from ...parallel.topology import Topology
 from ..logging import logger
-from .base_dataset import BaseDataset
+from .base_dataset import BaseDataset, BaseDatasetBatch, BaseDatasetItem
 from .blended_dataset_config import BlendedDatasetConfig
 
 TDataset = TypeVar("TDataset", bound=BaseDataset)
+TItem = TypeVar("TItem", bound=BaseDatasetItem)
+TBatchBeforeSync = TypeVar("TBatchBeforeSync", bound=BaseDatasetBatch)
+TBatch = TypeVar("TBatch", bound=BaseDatasetBatch)
 
 
 def weights_by_num_docs(examples: Sequence[int], alpha: float = 0.3) -> np.ndarray:
@@ -37,7 +40,10 @@ def weights_by_num_docs(examples: Sequence[int], alpha: float = 0.3) -> np.ndarr
     p = n / n.sum()
     q = p ** alpha
     q = q / q.sum()
-    w = q / p
+    # multiply by the reciprocal (not: divide): the item counts are int(weight * documents), and the last bit of the
+    # weight decides whether a dataset contributes n or n - 1 items; this is the rounding of
+    # src/scaling/core/data/blended_dataset.py:50-56, so the same corpora give the same blend
+    w = q * (1 / p)
     return w / w.sum()
 
 
@@ -56,12 +62,14 @@ def weights_examples_proportional(examples: Sequence[int], temperature: float = 
     if temperature != 1.0:
         r = r ** (1.0 / temperature)
         r = r / r.sum()
-    w = r / p
+    w = r * (1 / p)  # reciprocal, as above
     return w / w.sum()
 
 
-def build_blend_index(targets: Sequence[int], stem: str) -> int:
-    """Write ``{stem}.bin`` (int64 pairs), ``{stem}.input.json`` and ``{stem}.meta.json``; returns the pair count."""
+def build_blend_index(targets: Sequence[int], stem: str, until_all: bool = True) -> int:
+    """Write ``{stem}.bin`` (int64 pairs), ``{stem}.input.json`` and ``{stem}.meta.json``; returns the pair count.
+    ``until_all``: go on until every dataset has given its target number of items (datasets that are done drop out);
+    ``False``: stop when the first dataset is done, as the legacy blend does."""
     from ...ops import _build
 
     arr = np.ascontiguousarray(np.asarray(targets, dtype=np.int64))
@@ -69,11 +77,11 @@ def build_blend_index(targets: Sequence[int], stem: str) -> int:
     if not lib_path.exists():
         _build.build()
     lib = ctypes.CDLL(str(lib_path))
-    fn = lib.sb200_blend_index
-    fn.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_char_p]
+    fn = lib.sb200_blend_index_ex
+    fn.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_char_p, ctypes.c_int]
     fn.restype = ctypes.c_long
     tmp = f"{stem}.bin.tmp.{os.getpid()}"
-    count = int(fn(arr.ctypes.data, int(arr.size), tmp.encode()))
+    count = int(fn(arr.ctypes.data, int(arr.size), tmp.encode(), int(until_all)))
     if count < 0:
         raise RuntimeError(f"blend index builder failed with code {count} for {stem}")
     os.replace(tmp, f"{stem}.bin")
@@ -86,8 +94,16 @@ def build_blend_index(targets: Sequence[int], stem: str) -> int:
     return count
 
 
-class BaseBlendedDataset(BaseDataset, Generic[TDataset]):
-    """Indexable union of ``datasets``; a single dataset passes through untouched."""
+class BaseBlendedDataset(BaseDataset, Generic[TItem, TBatchBeforeSync, TBatch, TDataset]):
+    """Indexable union of ``datasets``; a single dataset passes through untouched.
+
+    Generic over (item, batch before the tensor-parallel sync, batch, blended dataset class) like
+    src/scaling/core/data/blended_dataset.py:128-135; ``BaseBlendedDataset[SomeDataset]`` names the last one alone."""
+
+    def __class_getitem__(cls, params):  # type: ignore[no-untyped-def]
+        if not isinstance(params, tuple):
+            params = (BaseDatasetItem, BaseDatasetBatch, BaseDatasetBatch, params)
+        return super().__class_getitem__(params)
 
     def __init__(self, seed: int, config: BlendedDatasetConfig, datasets: Sequence[TDataset]) -> None:
         self.config = config
@@ -189,13 +205,17 @@ class BaseBlendedDataset(BaseDataset, Generic[TDataset]):
             self.dataset_indices = np.memmap(bin_file, mode="r", order="C", dtype=dtype, shape=shape)
         self.size = shape[0]
         # optional second shuffle so that neighbouring items do not follow the deterministic interleaving
-        self.random_index = None
-        if self.config.shuffle_dataset_indices and shuffle:
-            rng = np.random.RandomState(seed=seed)
-            if self.config.load_dataset_indices_to_memory:
+        # (an index held in memory is shuffled in place; a memory-mapped one is read through `random_index`, which is
+        # the identity without the shuffle)
+        reshuffle = self.config.shuffle_dataset_indices and shuffle
+        rng = np.random.RandomState(seed=seed)
+        if self.config.load_dataset_indices_to_memory:
+            self.random_index = None
+            if reshuffle:
                 rng.shuffle(self.dataset_indices)
-            else:
-                self.random_index = np.arange(self.size)
+        else:
+            self.random_index = np.arange(self.size)
+            if reshuffle:
                 rng.shuffle(self.random_index)
 
     def collate(self, batch: List[Any]):

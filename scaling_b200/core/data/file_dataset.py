@@ -23,8 +23,7 @@ def retry_array_from_file(file_handle: FileHandle, dtype: np.dtype, count: int, 
 
     def read(f: IO[Any]) -> np.ndarray:
         f.seek(offset)
-        raw = f.read(count * dtype.itemsize)
-        arr = np.frombuffer(raw, dtype=dtype, count=len(raw) // dtype.itemsize)
+        arr = np.fromfile(f, dtype=dtype, count=count)
         if len(arr) == 0 and count != 0:
             raise RetryableException(
                 f"Expected to read {count} elements of dtype {dtype} at offset {offset} from {file_handle._path}, "

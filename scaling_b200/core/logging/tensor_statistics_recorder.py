@@ -177,7 +177,7 @@ class TensorStatisticsRecorder:
     def __init__(self, config: TensorStatisticsRecorderConfig, context: Any, model: Any, logger: Any = None):
         from . import logger as default_logger
 
-        self.config = config
+        self.config = TensorStatisticsRecorderConfig.from_dict(config) if isinstance(config, dict) else config
         self.context = context
         self.model = model
         self.logger = logger if logger is not None else default_logger

@@ -86,7 +86,9 @@ class PipelineScheduleBase(ABC):
 
         engine = SimulationEngine.from_profile(cls, profile_file)
         engine.simulate()
-        return engine.visualize(milliseconds_per_pixel=milliseconds_per_pixel, pipe_pixels=pipe_pixels)
+        # (summary of the simulated run, timeline image), as src/scaling/core/nn/pipeline_schedule/base.py:222-239
+        return engine.summarize(), engine.visualize(milliseconds_per_pixel=milliseconds_per_pixel,
+                                                   pipe_pixels=pipe_pixels)
 
 
 class PipelineScheduleTrain(PipelineScheduleBase):

@@ -4,7 +4,7 @@ Two conventions, as in the reference (src/scaling/core/nn/rotary.py:142-255):
 ``RotaryEmbedding`` pairs element ``i`` with ``i + d/2`` ("rotate half", GPT-NeoX layout) and may
 rotate only the first ``dimensions`` of each head; ``RotaryEmbeddingComplex`` pairs ``2i`` with
 ``2i + 1`` (Llama layout).  Both accept ``[seq, batch, heads, head_dim]`` tensors and optional
-``[batch, seq]`` position ids.  Angles are evaluated in fp32 inside one fused kernel that rotates in
+``[seq, batch]`` position ids.  Angles are evaluated in fp32 inside one fused kernel that rotates in
 place on a contiguous copy; no cos/sin table is materialised (the reference caches the rotate-half
 table in the model dtype, so bf16 results differ in the last bit).
 """
@@ -36,8 +36,10 @@ def _positions_for(x_sbhd: torch.Tensor, position_ids: Optional[torch.Tensor]) -
     s, b = x_sbhd.shape[0], x_sbhd.shape[1]
     if position_ids is None:
         return torch.arange(s, device=x_sbhd.device, dtype=torch.int32).repeat_interleave(b)
-    # [b, s] -> token order of the [s, b, ...] tensor
-    return position_ids.t().reshape(-1)
+    # [s, b], the token order of the [s, b, ...] tensor (src/scaling/core/nn/attention/attention.py:838-844 turns the
+    # batch's [b, s] ids around before it calls the module)
+    assert position_ids.shape == (s, b), f"position ids {tuple(position_ids.shape)} for activations [{s}, {b}, ...]"
+    return position_ids.reshape(-1)
 
 
 class _RotaryBase(torch.nn.Module):

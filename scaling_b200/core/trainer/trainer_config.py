@@ -8,6 +8,7 @@ from typing import Any, List, Optional
 from pydantic import Field
 
 from ..config import BaseConfig
+from ..logging.tensor_statistics_recorder import TensorStatisticsRecorderConfig
 
 
 class TrainerConfig(BaseConfig):
@@ -42,6 +43,6 @@ class TrainerConfig(BaseConfig):
     separate_file_for_parameters: Optional[List[str]] = Field(
         None, description="parameters whose name contains one of these strings go to separate checkpoint files"
     )
-    tensor_statistics_recorder_config: Optional[Any] = Field(
-        None, description="TensorStatisticsRecorderConfig (or its dict) for recording tensor statistics"
+    tensor_statistics_recorder_config: Optional[TensorStatisticsRecorderConfig] = Field(
+        None, description="configuration for recording tensor statistics"
     )

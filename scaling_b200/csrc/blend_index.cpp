@@ -1,12 +1,13 @@
 // Host-side builder of the blended-dataset index (no device code).
 //
 // Given the number of items to draw from each of n source datasets, emit (dataset, item) pairs so that after every
-// step the dataset that lags furthest behind its target share comes next (ties: lowest dataset number); stop when
-// the first dataset reaches its target.  Items of a dataset are emitted in order 0, 1, 2, ... (the sources are
-// shuffled already).  Same sequence as the reference's index builder (the `blended_dataset_loop.sample` extension
-// called from src/scaling/core/data/blended_dataset.py:326-329; its Python form is
-// src/scaling/transformer/data/legacy_blended_dataset.py:214-229), computed with a heap in O(N log n) and exact
-// integer comparisons instead of O(N n) floating-point argmin passes.
+// step the dataset that lags furthest behind its target share comes next (ties: lowest dataset number).  Items of a
+// dataset are emitted in order 0, 1, 2, ... (the sources are shuffled already).  Two stopping rules: the blend of
+// src/scaling/core/data/blended_dataset.py:326-329 (the `blended_dataset_loop.sample` extension) runs until every
+// dataset has reached its target, finished datasets dropping out of the choice (its tests expect as many items as
+// the targets add up to); the Python loop of src/scaling/transformer/data/legacy_blended_dataset.py:214-229 stops
+// when the first dataset reaches its target.  Computed with a heap in O(N log n) and exact integer comparisons
+// instead of O(N n) floating-point argmin passes.
 #include <cstdint>
 #include <cstdio>
 #include <queue>
@@ -34,7 +35,8 @@ struct Later {
 
 // targets[n] > 0.  Writes int64 pairs (dataset, item) to `bin_path`; returns the number of pairs, or a negative
 // value: -1 bad arguments, -2 the file cannot be written.
-SB_API long sb200_blend_index(const int64_t* targets, int n, const char* bin_path) {
+//   until_all != 0: go on until every dataset has reached its target; 0: stop at the first that does.
+SB_API long sb200_blend_index_ex(const int64_t* targets, int n, const char* bin_path, int until_all) {
   if (!targets || n <= 0 || !bin_path) return -1;
   for (int i = 0; i < n; ++i)
     if (targets[i] <= 0) return -1;
@@ -46,7 +48,7 @@ SB_API long sb200_blend_index(const int64_t* targets, int n, const char* bin_pat
   buffer.reserve(1 << 16);
   long count = 0;
   bool ok = true;
-  while (true) {
+  while (!heap.empty()) {
     Entry e = heap.top();
     heap.pop();
     buffer.push_back(e.dataset);
@@ -57,10 +59,18 @@ SB_API long sb200_blend_index(const int64_t* targets, int n, const char* bin_pat
       ok = ok && std::fwrite(buffer.data(), sizeof(int64_t), buffer.size(), f) == buffer.size();
       buffer.clear();
     }
-    if (e.sampled >= e.target) break;  // one dataset is exhausted: the blend ends here
+    if (e.sampled >= e.target) {
+      if (!until_all) break;  // one dataset is exhausted: the blend ends here
+      continue;               // this dataset is done, the others go on
+    }
     heap.push(e);
   }
   if (!buffer.empty()) ok = ok && std::fwrite(buffer.data(), sizeof(int64_t), buffer.size(), f) == buffer.size();
   ok = (std::fclose(f) == 0) && ok;
   return ok ? count : -2;
+}
+
+// The first-exhausted rule under the earlier name.
+SB_API long sb200_blend_index(const int64_t* targets, int n, const char* bin_path) {
+  return sb200_blend_index_ex(targets, n, bin_path, 0);
 }

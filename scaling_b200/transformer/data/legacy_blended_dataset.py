@@ -122,7 +122,7 @@ class LegacyBlendedDataset(BaseBlendedDataset[TextDataset]):
             rnd = (lambda x: int(round(x))) if self.config.weight_examples_proportional else int
             targets = [max(1, rnd(p * n)) for n, p in zip(counts, scale)]
             scratch = f"{stem}.pairs.{os.getpid()}"
-            n_pairs = build_blend_index(targets, scratch)
+            n_pairs = build_blend_index(targets, scratch, until_all=False)
             pairs = np.fromfile(scratch + ".bin", dtype=np.int64).reshape(n_pairs, 2)
             write_fixed_width_items(stem + ".bin", stem + ".idx", pairs.astype(np.int32))
             for ext in (".bin", ".input.json", ".meta.json"):

@@ -99,6 +99,11 @@ class CrossEntropyLoss(torch.nn.Module):
         weights = batch.loss_weights.float().reshape(-1)
         targets = batch.target_token_ids.reshape(-1)
         loss, argmax = vocab_parallel_cross_entropy(logits, targets, weights, self.topology, sharded)
+        if self._use_umup:
+            # Unit scaling: the division by the sum of the loss weights acts on the value of the loss only, the
+            # gradient is that of the weighted sum (src/scaling/transformer/model/losses/cross_entropy.py:47-56 scales
+            # the summed loss with scale_fwd), so the logits receive gradients of unit scale whatever the batch size.
+            loss = scale_bwd(loss, weights.sum())
         mask = (weights > 0).float()
         accuracy = ((argmax == targets).float() * mask).sum() / mask.sum()
         return loss, {"accuracy": accuracy}

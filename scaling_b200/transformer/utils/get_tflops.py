@@ -103,9 +103,10 @@ class HardwareType(Enum):
 
     @classmethod
     def get_via_torch(cls) -> "HardwareType":
-        if not torch.cuda.is_available():
+        try:  # ask for the name first: without a device the call itself fails
+            name = torch.cuda.get_device_name().replace(" ", "").lower().replace("nvidia", "")
+        except Exception:  # noqa: BLE001
             return cls.DEFAULT
-        name = torch.cuda.get_device_name().replace(" ", "").lower().replace("nvidia", "")
         return next((x for x in cls if x != cls.DEFAULT and x.value in name), cls.DEFAULT)
 
 

@@ -23,23 +23,29 @@ def tok() -> Tokenizer:
     return Tokenizer.from_words(WORDS)
 
 
-def _oracle(targets):
+def _oracle(targets, until_all):
+    """The dataset furthest behind its target comes next; stop at the first finished dataset, or let finished ones
+    drop out and go on until all are done."""
     t = np.array(targets)
     s = np.zeros(len(t), dtype=np.int64)
     out = []
-    while (s < t).all():
-        i = int((s / t).argmin())
+    while (s < t).any() if until_all else (s < t).all():
+        share = np.where(s < t, s / t, np.inf)
+        i = int(share.argmin())
         out.append((i, int(s[i])))
         s[i] += 1
     return out
 
 
-@pytest.mark.parametrize("targets", [[5, 3, 9], [1, 1], [7], [100, 1, 33, 33], [2, 4, 8, 16, 32]])
-def test_blend_index_matches_greedy_oracle(tmp_path: Path, targets):
-    n = build_blend_index(targets, str(tmp_path / "idx"))
+@pytest.mark.parametrize("until_all", [True, False])
+@pytest.mark.parametrize("targets", [[5, 3, 9], [1, 1], [7], [100, 1, 33, 33], [2, 4, 8, 16, 32], [12, 12, 12]])
+def test_blend_index_matches_greedy_oracle(tmp_path: Path, targets, until_all):
+    n = build_blend_index(targets, str(tmp_path / "idx"), until_all=until_all)
     pairs = np.fromfile(tmp_path / "idx.bin", dtype=np.int64).reshape(-1, 2)
     assert n == len(pairs)
-    assert [tuple(p) for p in pairs.tolist()] == _oracle(targets)
+    assert [tuple(p) for p in pairs.tolist()] == _oracle(targets, until_all)
+    if until_all:
+        assert n == sum(targets)  # every dataset gives all it was asked for
     meta = json.loads((tmp_path / "idx.meta.json").read_text())
     assert meta == {"dtype": "int64", "shape": [n, 2]}
 

@@ -99,14 +99,14 @@ def test_rotary_position_ids_shift_the_rotation_and_partial_dims_pass_through():
     x = torch.randn(s, b, h, d)
     rot = RotaryEmbedding(RotaryConfig(dimensions=4))
     plain, _ = rot(x, x)
-    shifted, _ = rot(x, x, query_position_ids=torch.arange(3, 3 + s).view(1, s))
-    again, _ = rot(x[:2], x[:2], query_position_ids=torch.tensor([[3, 4]]))
+    shifted, _ = rot(x, x, query_position_ids=torch.arange(3, 3 + s).view(s, 1))
+    again, _ = rot(x[:2], x[:2], query_position_ids=torch.tensor([[3], [4]]))
     assert torch.equal(plain[..., 4:], x[..., 4:])  # only the first `dimensions` entries rotate
     assert torch.allclose(plain[0], x[0], atol=1e-6)  # position 0 is the identity
     assert torch.allclose(shifted[:2], again, atol=1e-6) and not torch.allclose(shifted, plain)
     # relative property: scores depend on position differences only
     q0, k0 = rot(x, x)
-    q3, k3 = rot(x, x, torch.arange(3, 3 + s).view(1, s), torch.arange(3, 3 + s).view(1, s))
+    q3, k3 = rot(x, x, torch.arange(3, 3 + s).view(s, 1), torch.arange(3, 3 + s).view(s, 1))
     assert torch.allclose(torch.einsum("sbhd,tbhd->bhst", q0, k0), torch.einsum("sbhd,tbhd->bhst", q3, k3), atol=1e-4)
 
 
