@@ -68,6 +68,9 @@ class _LMHeadBase(TransformerLayerBaseIO):
         t = self.topology
         if t is not None and t.config.model_parallel_size > 1 and (self.gather_logits or not self.training):
             logits = all_concat(logits, t)
+        if self.training and logits.grad_fn is not None:
+            # Nothing but the loss reads the logits of a training step: the loss may write their gradient over them.
+            logits._sb200_loss_may_overwrite = True  # type: ignore[attr-defined]
         return x.evolve(activations=logits, attention_scores_manipulation=None, embeddings_head=None)
 
 

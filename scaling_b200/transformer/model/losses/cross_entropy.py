@@ -26,7 +26,7 @@ from ..layers.base import TransformerLayerIO
 
 class _VocabParallelCrossEntropy(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, logits, targets, coef, group, vocab_start):  # type: ignore[override]
+    def forward(ctx, logits, targets, coef, group, vocab_start, overwrite=False):  # type: ignore[override]
         """logits ``[N, V_local]``, targets ``[N]``, coef ``[N]`` (weight / sum of weights).
         Returns (loss scalar fp32, global arg-max ``[N]``)."""
         rmax, rsum, tgt, aval, aidx = K.ce_stats(logits, targets, vocab_start)
@@ -43,11 +43,14 @@ class _VocabParallelCrossEntropy(torch.autograd.Function):
         else:
             gmax, gsum, gtgt, argmax = rmax, rsum, tgt, aidx
         # The loss needs the row statistics only.  The gradient with respect to the logits is written in the backward
-        # pass, over the logits themselves and already multiplied by the upstream gradient: the [tokens, vocabulary]
-        # matrix is read once here (statistics) and read and written once there.
+        # pass, already multiplied by the upstream gradient; over the logits themselves when their producer has said
+        # that nobody else reads them (``overwrite``: the language-model heads do so in training), so that the
+        # [tokens, vocabulary] matrix is read once here and read and written once there.  Logits from anywhere else
+        # (a tensor the caller still holds) are left alone and the gradient gets its own buffer.
         loss_tok = torch.log(gsum) + gmax - gtgt
         ctx.save_for_backward(logits, targets, gmax, gsum, gtgt, coef)
         ctx.vocab_start = vocab_start
+        ctx.overwrite = bool(overwrite)
         ctx.mark_non_differentiable(argmax)
         return (loss_tok * coef).sum(), argmax
 
@@ -55,8 +58,8 @@ class _VocabParallelCrossEntropy(torch.autograd.Function):
     def backward(ctx, grad_loss, _grad_argmax):  # type: ignore[override]
         logits, targets, gmax, gsum, gtgt, coef = ctx.saved_tensors
         _, dlogits = K.ce_finalize(logits, targets, gmax, gsum, gtgt, coef, ctx.vocab_start, want_grad=True,
-                                   inplace=logits.is_cuda, scale_dev=grad_loss)
-        return dlogits, None, None, None, None
+                                   inplace=logits.is_cuda and ctx.overwrite, scale_dev=grad_loss)
+        return dlogits, None, None, None, None, None
 
 
 def vocab_parallel_cross_entropy(logits: torch.Tensor, targets: torch.Tensor, weights: torch.Tensor,
@@ -69,8 +72,9 @@ def vocab_parallel_cross_entropy(logits: torch.Tensor, targets: torch.Tensor, we
         start = topology.model_parallel_rank * logits.shape[-1]
     w = weights.float().reshape(-1)
     coef = w / w.sum()
+    overwrite = bool(getattr(logits, "_sb200_loss_may_overwrite", False)) and logits.is_contiguous()
     flat = logits.reshape(-1, logits.shape[-1])
-    return _VocabParallelCrossEntropy.apply(flat, targets.reshape(-1), coef, group, start)
+    return _VocabParallelCrossEntropy.apply(flat, targets.reshape(-1), coef, group, start, overwrite)
 
 
 class CrossEntropyLoss(torch.nn.Module):
@@ -95,7 +99,11 @@ class CrossEntropyLoss(torch.nn.Module):
         if self._use_umup:
             full_vocab = self.vocab_size or local_vocab
             fwd, bwd = UMuParametrization.get_umup_cross_entropy_scales(self.umup_loss_mult, full_vocab)
-            logits = scale_bwd(scale_fwd(logits, fwd), bwd)
+            disposable = getattr(logits, "_sb200_loss_may_overwrite", False)
+            scaled = scale_bwd(scale_fwd(logits, fwd), bwd)
+            if disposable or scaled.data_ptr() != logits.data_ptr():  # the producer's word, or a copy of our own
+                scaled._sb200_loss_may_overwrite = True  # type: ignore[attr-defined]
+            logits = scaled
         weights = batch.loss_weights.float().reshape(-1)
         targets = batch.target_token_ids.reshape(-1)
         loss, argmax = vocab_parallel_cross_entropy(logits, targets, weights, self.topology, sharded)

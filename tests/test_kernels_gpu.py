@@ -744,3 +744,30 @@ def test_attention_of_few_queries_against_a_long_cache(D, causal, window):
     ref = attention_reference(q.float(), k.float(), v.float(), cu_q, cu_k, causal, D ** -0.5, window)
     ok, worst = _rows_close(out.reshape(tq, -1), ref.reshape(tq, -1), 2e-2)
     assert ok, worst
+
+
+def test_loss_overwrites_logits_only_when_their_producer_allows_it():
+    """The gradient of the loss is written over the logits only if their producer marked them as read by nobody
+    else; logits that the caller holds come back unchanged, with the same loss and gradient either way."""
+    from scaling_b200.transformer.model.losses.cross_entropy import vocab_parallel_cross_entropy
+
+    torch.manual_seed(3)
+    n, v = 64, 512
+    held = torch.randn(n, v, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    before = held.detach().clone()
+    targets = torch.randint(0, v, (n,), device=DEV)
+    weights = torch.ones(n, device=DEV)
+    loss, _ = vocab_parallel_cross_entropy(held, targets, weights, None, False)
+    loss.backward()
+    assert torch.equal(held.detach(), before)  # a leaf the caller still reads
+    ref = F.cross_entropy(before.float(), targets)
+    assert abs(loss.item() - ref.item()) < 2e-2
+
+    base = before.clone().requires_grad_()
+    temporary = base * 1.0
+    temporary._sb200_loss_may_overwrite = True
+    loss2, _ = vocab_parallel_cross_entropy(temporary, targets, weights, None, False)
+    loss2.backward()
+    assert loss2.item() == loss.item()
+    assert _rel(base.grad, held.grad) < 1e-3
+    assert not torch.equal(temporary.detach(), before)  # its storage now holds the gradient
