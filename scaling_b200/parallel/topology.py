@@ -28,6 +28,14 @@ PIPE_P2P_MAX_CTAS = 2
 PIPE_P2P_RESERVED_SMS = 4 * PIPE_P2P_MAX_CTAS
 
 
+def _destroy_process_group_quietly() -> None:
+    try:
+        if dist.is_available() and dist.is_initialized():
+            dist.destroy_process_group()
+    except Exception:  # noqa: BLE001 - the process is exiting anyway
+        pass
+
+
 class TopologyState(TypedDict):
     model_parallel_constant_rng: RngTrackerState
 
@@ -118,6 +126,13 @@ class Topology:
                 timeout=datetime.timedelta(minutes=torch_distributed_timeout_minutes),
                 **kwargs,
             )
+            if self.backend == "gloo":
+                # CPU ranks: tear the group down at interpreter exit.  A gloo group that is still alive when the
+                # process ends can abort it ("terminate called without an active exception") after the work is done.
+                # Not for NCCL: its teardown waits for the peers, and a rank that exits after a failure must not.
+                import atexit
+
+                atexit.register(_destroy_process_group_quietly)
         for ranks in self.all_pipe_parallel_groups:
             g = dist.new_group(ranks)
             if self.config.global_rank in ranks:
