@@ -68,9 +68,15 @@ class DataLoader:
             f"because dataset has only length {len(dataset)}"
         )
         self.sampler = RandomSampler(dataset, seed, consumed_samples, topology, shuffle)
+        # torch's loader draws a base seed whenever an iterator is created (at the first batch, and again at every
+        # new epoch): from a generator of its own, so that the global stream, which dropout reads, is the same
+        # whether a run started here or was resumed here
+        self._loader_generator = torch.Generator()
+        self._loader_generator.manual_seed(seed)
         self.dataloader = torch.utils.data.DataLoader(
             dataset=dataset, batch_sampler=self.sampler, num_workers=num_workers, collate_fn=dataset.collate,
             pin_memory=pin_memory and torch.cuda.is_available(), prefetch_factor=prefetch_factor,
+            generator=self._loader_generator,
         )
         self.iterator = self._iterate()
 

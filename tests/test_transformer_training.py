@@ -81,9 +81,15 @@ def test_transformer_layouts_agree(tmp_path: Path):
             assert abs(a - b) < 2e-3, (kw, got, base)
 
 
+DROPOUT = {"dropout_embedding": 0.1, "dropout_attention_probs": 0.1, "dropout_after_attention": 0.1,
+           "dropout_after_mlp": 0.1}
+
+
 @pytest.mark.dist
 @pytest.mark.parametrize("layout", [dict(world_size=1), dict(world_size=2, mp=2),
-                                    dict(world_size=2, pp=2, ga=2, micro=2, arch={"weight_tying": True})])
+                                    dict(world_size=2, pp=2, ga=2, micro=2, arch={"weight_tying": True}),
+                                    dict(world_size=1, arch=DROPOUT), dict(world_size=1, arch=DROPOUT, kernel="torch"),
+                                    dict(world_size=2, mp=2, arch=DROPOUT)])
 def test_transformer_resume_is_bit_identical(tmp_path: Path, layout):
     layout = dict(layout)
     ws = layout.pop("world_size")
