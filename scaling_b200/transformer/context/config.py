@@ -232,7 +232,11 @@ class TransformerConfig(BaseConfig):
     version: str = Field(".unknown.", description="version tag of the config")
     runner: RunnerConfig = Field(RunnerConfig(), description="launcher settings")
     logger: LoggerConfig = Field(LoggerConfig(), description="logging settings")
-    topology: TopologyConfig = Field(description="parallel layout and batch sizes")
+    topology: TopologyConfig = Field(
+        TopologyConfig(model_parallel_size=1, pipe_parallel_size=1, data_parallel_size=1, micro_batch_size=2,
+                       gradient_accumulation_steps=1),  # type: ignore[call-arg]
+        description="parallel layout and batch sizes (default: one process, micro batch 2)",
+    )
     optimizer: OptimizerConfig = Field(OptimizerConfig(), description="optimizer settings")
     training: TrainingConfig = Field(TrainingConfig(), description="training settings")
     training_groups: List[TrainingGroupConfig] = Field(default=[], description="parameter groups by regex")
