@@ -27,7 +27,7 @@
 
 namespace {
 
-constexpr int FA_THREADS = 192;      // forward: TMA warp, MMA warp, 4 softmax warps (thread = query row)
+// forward: TMA warp, MMA warp and 4 softmax warps with one thread per query row (192 threads) or 8 with two (320)
 constexpr int FA_BWD_THREADS = 320;  // backward: TMA warp, MMA warp, 8 warps (two threads share a row, 64 columns each)
 constexpr int TILE = 128;          // queries per CTA and keys per step
 constexpr int PANEL_BYTES = 16384; // 128 rows x 64 bf16
