@@ -103,6 +103,13 @@ class PbMemoryMap:
         if initialize:
             self.initialize()
 
+    # the two converters as methods too (src/scaling/core/data/pb_memory_map.py:249-300 has them on the class)
+    def dict2pb(self, pb_message: Message, data: dict) -> Message:
+        return dict2pb(pb_message, data)
+
+    def pb2dict(self, pb_message: Message) -> dict:
+        return pb2dict(pb_message)
+
     @property
     def file_path_data(self) -> Path:
         return Path(str(self.prefix_path) + ".bin")
