@@ -83,6 +83,9 @@ def _broadcast_from_first(tensor: torch.Tensor, process_group: Any) -> None:
     dist.broadcast(tensor.data, src, group=process_group)
 
 
+_broadcast_parameters = _broadcast_from_first  # name in src/scaling/core/nn/parallel_module/parallel_module.py:765
+
+
 class ParallelModule(PipePartitionedModule, Generic[BaseLossInputGeneric, BaseDatasetBatchGeneric]):
     def __init__(self, layer_specs: list[LayerSpec], topology: Topology,
                  profiler_config: ProfilerConfig = ProfilerConfig(), use_continuous_recommunication: bool = False):

@@ -132,6 +132,16 @@ def _first_match(name: str, patterns: Sequence[str]) -> Optional[str]:
     return next((p for p in patterns if re.search(p, name) is not None), None)
 
 
+def _find_matching_param(key: NamedParameterMeta, data: Sequence[str]) -> Optional[str]:
+    """First pattern of ``data`` found in the parameter's name (src/scaling/transformer/model/model.py:360)."""
+    return _first_match(key[0], data)
+
+
+def _filter_by_param(parameters_exclude: Sequence[str], parameter_list: list[NamedParameterMeta]) -> list[NamedParameterMeta]:
+    """The parameters whose names match none of the patterns (src/scaling/transformer/model/model.py:354)."""
+    return [p for p in parameter_list if _first_match(p[0], parameters_exclude) is None]
+
+
 def _all_gather_objects(obj):
     if dist.is_initialized() and dist.get_world_size() > 1:
         out = [None] * dist.get_world_size()
