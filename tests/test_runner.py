@@ -116,3 +116,15 @@ def test_transformer_training_script_under_the_launcher(tmp_path: Path):
     # embedding, two blocks, final norm, head: one file per layer whatever stage holds it
     assert [n.split("_")[3] for n in names] == ["0", "1", "2", "3", "4"], names
     assert (step_dir / "config.yml").is_file()
+
+
+def test_mlp_example_modules_are_importable_under_the_example_layout():
+    import yaml
+
+    from examples.mlp_example import context, data, model, train
+    from examples.mlp_example.config import MLPConfig
+
+    cfg = MLPConfig.from_dict(yaml.safe_load((Path(__file__).parents[1] / "examples/mlp_example/config.yml").read_text()))
+    assert cfg.architecture.hidden_dim > 0
+    assert callable(train.main) and hasattr(model, "get_layer_specs") and hasattr(data, "MNISTDataset")
+    assert context.MLPContext.__name__ == "MLPContext"
