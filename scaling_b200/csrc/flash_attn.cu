@@ -51,6 +51,7 @@ struct FaParams {
   long lddq_tok, lddk_tok, lddv_tok;     // element strides of the gradient outputs: token rows ...
   int lddq_head, lddk_head, lddv_head;   // ... and heads inside a row
   int* status;
+  int fp16;  // element type of q, k, v, o and the gradients: 1 = half, 0 = bf16 (selects the F16 instantiations)
   // dropout on the attention probabilities (DROP instantiations): probability (query t, head h, key k) is kept iff
   // byte (k mod 16) of the Philox block (k / 16, (drop_head0 + h) * T + t, drop_call, step) is >= drop_thr8; kept ones are
   // multiplied by keep_scale = 1 / (1 - drop_thr8 / 256).  rng = {seed, step} in device memory.
@@ -86,9 +87,16 @@ __device__ __forceinline__ float fast_exp2(float x) {
   return y;
 }
 
-__device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
-  __nv_bfloat162 t = __floats2bfloat162_rn(a, b);
-  return *reinterpret_cast<uint32_t*>(&t);
+// two floats as a pair of 16-bit values in the kernels' element type (F16: half, else bf16)
+template <bool F16>
+__device__ __forceinline__ uint32_t pack16(float a, float b) {
+  if constexpr (F16) {
+    __half2 t = __floats2half2_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&t);
+  } else {
+    __nv_bfloat162 t = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&t);
+  }
 }
 // K-major operand descriptor for k-step kk (16 elements per step) of a [128 x (64*panels)] tile
 __device__ __forceinline__ uint64_t desc_kmajor(uint32_t base, int kk) {
@@ -150,7 +158,7 @@ template <int D> struct FaFwdCfg {
 // share the rows of a TMEM lane quadrant and take 64 key columns and half of the output columns each; they exchange
 // their row maxima through shared memory once per tile and their row sums once at the end).  Twice the warps hide
 // the TMEM and arithmetic latencies that two warps per scheduler leave exposed.
-template <int D, bool DROP, int ROWT>
+template <int D, bool DROP, int ROWT, bool F16 = false>
 __global__ void __launch_bounds__(64 + 128 * ROWT, FaFwdCfg<D>::TWO ? 2 : 1)
     fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                   const __grid_constant__ CUtensorMap tmV, const FaParams p) {
@@ -252,8 +260,8 @@ __global__ void __launch_bounds__(64 + 128 * ROWT, FaFwdCfg<D>::TWO ? 2 : 1)
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      const uint32_t idesc_s = sb::umma_idesc_f16(TILE, TILE, 1, 0, 0);  // S = Q K^T: both K-major
-      const uint32_t idesc_o = sb::umma_idesc_f16(TILE, D, 1, 0, 1);     // O = P V: V is MN-major
+      const uint32_t idesc_s = sb::umma_idesc_f16(TILE, TILE, F16 ? 0 : 1, 0, 0);  // S = Q K^T: both K-major
+      const uint32_t idesc_o = sb::umma_idesc_f16(TILE, D, F16 ? 0 : 1, 0, 1);     // O = P V: V is MN-major
       const uint32_t q_addr = sb::smem_u32(sQ), p_addr = sb::smem_u32(sP);
       bool ok = sb::mbar_wait(q_full, 0, abort_flag);
       auto issue_s = [&](int j) -> bool {
@@ -434,10 +442,10 @@ __global__ void __launch_bounds__(64 + 128 * ROWT, FaFwdCfg<D>::TWO ? 2 : 1)
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
           uint4 u;
-          u.x = pack_bf16(pr[g * 8 + 0], pr[g * 8 + 1]);
-          u.y = pack_bf16(pr[g * 8 + 2], pr[g * 8 + 3]);
-          u.z = pack_bf16(pr[g * 8 + 4], pr[g * 8 + 5]);
-          u.w = pack_bf16(pr[g * 8 + 6], pr[g * 8 + 7]);
+          u.x = pack16<F16>(pr[g * 8 + 0], pr[g * 8 + 1]);
+          u.y = pack16<F16>(pr[g * 8 + 2], pr[g * 8 + 3]);
+          u.z = pack16<F16>(pr[g * 8 + 4], pr[g * 8 + 5]);
+          u.w = pack16<F16>(pr[g * 8 + 6], pr[g * 8 + 7]);
           *reinterpret_cast<uint4*>(sP + swz_offset(r, ch * 32 + g * 8)) = u;
         }
       }
@@ -488,10 +496,10 @@ __global__ void __launch_bounds__(64 + 128 * ROWT, FaFwdCfg<D>::TWO ? 2 : 1)
 #pragma unroll
           for (int g = 0; g < DT / 8; ++g) {
             uint4 u;
-            u.x = pack_bf16(o_acc[g * 8 + 0] * inv, o_acc[g * 8 + 1] * inv);
-            u.y = pack_bf16(o_acc[g * 8 + 2] * inv, o_acc[g * 8 + 3] * inv);
-            u.z = pack_bf16(o_acc[g * 8 + 4] * inv, o_acc[g * 8 + 5] * inv);
-            u.w = pack_bf16(o_acc[g * 8 + 6] * inv, o_acc[g * 8 + 7] * inv);
+            u.x = pack16<F16>(o_acc[g * 8 + 0] * inv, o_acc[g * 8 + 1] * inv);
+            u.y = pack16<F16>(o_acc[g * 8 + 2] * inv, o_acc[g * 8 + 3] * inv);
+            u.z = pack16<F16>(o_acc[g * 8 + 4] * inv, o_acc[g * 8 + 5] * inv);
+            u.w = pack16<F16>(o_acc[g * 8 + 6] * inv, o_acc[g * 8 + 7] * inv);
             *reinterpret_cast<uint4*>(orow + g * 8) = u;
           }
           if (p.lse2 && half == 0) p.lse2[(long)h * p.T + t] = l > 0.f ? m + log2f(l) : -1e30f;
@@ -522,7 +530,7 @@ __global__ void __launch_bounds__(64 + 128 * ROWT, FaFwdCfg<D>::TWO ? 2 : 1)
 }
 
 // ============================================================================ backward: delta
-template <int D>
+template <int D, bool F16 = false>
 __global__ void fa_bwd_delta_kernel(const __nv_bfloat16* __restrict__ O, const __nv_bfloat16* __restrict__ dO,
                                     float* __restrict__ delta, int T, int Hq) {
   // D / 8 lanes per (t, h) row, one 16-byte load of O and of dO each: the kernel is a stream over both tensors
@@ -538,8 +546,14 @@ __global__ void fa_bwd_delta_kernel(const __nv_bfloat16* __restrict__ O, const _
     const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {b.x, b.y, b.z, b.w};
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-      const float2 x = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&aw[i]));
-      const float2 y = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&bw[i]));
+      float2 x, y;  // the pointers are typed bf16; with F16 the same 16-bit words hold halves
+      if constexpr (F16) {
+        x = __half22float2(*reinterpret_cast<const __half2*>(&aw[i]));
+        y = __half22float2(*reinterpret_cast<const __half2*>(&bw[i]));
+      } else {
+        x = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&aw[i]));
+        y = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&bw[i]));
+      }
       s = fmaf(x.x, y.x, fmaf(x.y, y.y, s));
     }
   }
@@ -557,7 +571,7 @@ __global__ void fa_bwd_delta_kernel(const __nv_bfloat16* __restrict__ O, const _
 //   ->  dV += P^T dO, dK += dS^T Q, reading the same tiles as MN-major A operands; both accumulate in TMEM
 //   (lanes = keys) over the whole loop.  With more than one split the results are written as fp32 partials
 //   and summed in a fixed order by fa_bwd_reduce_kernel.
-template <int D, bool DROP>
+template <int D, bool DROP, bool F16 = false>
 __global__ void __launch_bounds__(FA_BWD_THREADS, 1)
     fa_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                        const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
@@ -653,8 +667,8 @@ __global__ void __launch_bounds__(FA_BWD_THREADS, 1)
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      const uint32_t idesc_nt = sb::umma_idesc_f16(TILE, TILE, 1, 0, 0);  // [q x D] x [keys x D]^T
-      const uint32_t idesc_acc = sb::umma_idesc_f16(TILE, D, 1, 1, 1);    // [q x keys]^T x [q x D]: both MN-major
+      const uint32_t idesc_nt = sb::umma_idesc_f16(TILE, TILE, F16 ? 0 : 1, 0, 0);  // [q x D] x [keys x D]^T
+      const uint32_t idesc_acc = sb::umma_idesc_f16(TILE, D, F16 ? 0 : 1, 1, 1);    // [q x keys]^T x [q x D]: both MN-major
       const uint32_t k_addr = sb::smem_u32(sK), v_addr = sb::smem_u32(sV), p_addr = sb::smem_u32(sP),
                      ds_addr = sb::smem_u32(sdS);
       bool ok = sb::mbar_wait(kv_full, 0, abort_flag);
@@ -754,14 +768,14 @@ __global__ void __launch_bounds__(FA_BWD_THREADS, 1)
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
           uint4 u, w;
-          u.x = pack_bf16(pv[g * 8 + 0], pv[g * 8 + 1]);
-          u.y = pack_bf16(pv[g * 8 + 2], pv[g * 8 + 3]);
-          u.z = pack_bf16(pv[g * 8 + 4], pv[g * 8 + 5]);
-          u.w = pack_bf16(pv[g * 8 + 6], pv[g * 8 + 7]);
-          w.x = pack_bf16(dsv[g * 8 + 0], dsv[g * 8 + 1]);
-          w.y = pack_bf16(dsv[g * 8 + 2], dsv[g * 8 + 3]);
-          w.z = pack_bf16(dsv[g * 8 + 4], dsv[g * 8 + 5]);
-          w.w = pack_bf16(dsv[g * 8 + 6], dsv[g * 8 + 7]);
+          u.x = pack16<F16>(pv[g * 8 + 0], pv[g * 8 + 1]);
+          u.y = pack16<F16>(pv[g * 8 + 2], pv[g * 8 + 3]);
+          u.z = pack16<F16>(pv[g * 8 + 4], pv[g * 8 + 5]);
+          u.w = pack16<F16>(pv[g * 8 + 6], pv[g * 8 + 7]);
+          w.x = pack16<F16>(dsv[g * 8 + 0], dsv[g * 8 + 1]);
+          w.y = pack16<F16>(dsv[g * 8 + 2], dsv[g * 8 + 3]);
+          w.z = pack16<F16>(dsv[g * 8 + 4], dsv[g * 8 + 5]);
+          w.w = pack16<F16>(dsv[g * 8 + 6], dsv[g * 8 + 7]);
           const uint32_t off = swz_offset(r, ch * 32 + g * 8);
           *reinterpret_cast<uint4*>(sP + off) = u;
           *reinterpret_cast<uint4*>(sdS + off) = w;
@@ -806,14 +820,14 @@ __global__ void __launch_bounds__(FA_BWD_THREADS, 1)
 #pragma unroll
             for (int g = 0; g < 4; ++g) {
               uint4 u, w;
-              u.x = pack_bf16(__uint_as_float(a[g * 8 + 0]), __uint_as_float(a[g * 8 + 1]));
-              u.y = pack_bf16(__uint_as_float(a[g * 8 + 2]), __uint_as_float(a[g * 8 + 3]));
-              u.z = pack_bf16(__uint_as_float(a[g * 8 + 4]), __uint_as_float(a[g * 8 + 5]));
-              u.w = pack_bf16(__uint_as_float(a[g * 8 + 6]), __uint_as_float(a[g * 8 + 7]));
-              w.x = pack_bf16(__uint_as_float(b[g * 8 + 0]), __uint_as_float(b[g * 8 + 1]));
-              w.y = pack_bf16(__uint_as_float(b[g * 8 + 2]), __uint_as_float(b[g * 8 + 3]));
-              w.z = pack_bf16(__uint_as_float(b[g * 8 + 4]), __uint_as_float(b[g * 8 + 5]));
-              w.w = pack_bf16(__uint_as_float(b[g * 8 + 6]), __uint_as_float(b[g * 8 + 7]));
+              u.x = pack16<F16>(__uint_as_float(a[g * 8 + 0]), __uint_as_float(a[g * 8 + 1]));
+              u.y = pack16<F16>(__uint_as_float(a[g * 8 + 2]), __uint_as_float(a[g * 8 + 3]));
+              u.z = pack16<F16>(__uint_as_float(a[g * 8 + 4]), __uint_as_float(a[g * 8 + 5]));
+              u.w = pack16<F16>(__uint_as_float(a[g * 8 + 6]), __uint_as_float(a[g * 8 + 7]));
+              w.x = pack16<F16>(__uint_as_float(b[g * 8 + 0]), __uint_as_float(b[g * 8 + 1]));
+              w.y = pack16<F16>(__uint_as_float(b[g * 8 + 2]), __uint_as_float(b[g * 8 + 3]));
+              w.z = pack16<F16>(__uint_as_float(b[g * 8 + 4]), __uint_as_float(b[g * 8 + 5]));
+              w.w = pack16<F16>(__uint_as_float(b[g * 8 + 6]), __uint_as_float(b[g * 8 + 7]));
               *reinterpret_cast<uint4*>(dv + g * 8) = u;
               *reinterpret_cast<uint4*>(dk + g * 8) = w;
             }
@@ -837,6 +851,7 @@ __global__ void __launch_bounds__(FA_BWD_THREADS, 1)
 
 // out[t, h, c] = bf16(sum_s partial[s][t, h, c]) in fixed order; partial rows are dense [T, H, D], the output has
 // element strides (ld_tok, ld_head)
+template <bool F16 = false>
 __global__ void fa_bwd_reduce_kernel(const float* __restrict__ partial, __nv_bfloat16* __restrict__ out, long n,
                                      int splits, int H, int D, long ld_tok, int ld_head) {
   long i = (blockIdx.x * (long)blockDim.x + threadIdx.x) * 4;
@@ -847,8 +862,8 @@ __global__ void fa_bwd_reduce_kernel(const float* __restrict__ partial, __nv_bfl
     acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
   }
   uint2 u;
-  u.x = pack_bf16(acc.x, acc.y);
-  u.y = pack_bf16(acc.z, acc.w);
+  u.x = pack16<F16>(acc.x, acc.y);
+  u.y = pack16<F16>(acc.z, acc.w);
   const long th = i / D;
   const int c = (int)(i - th * D);
   const long t = th / H;
@@ -858,7 +873,7 @@ __global__ void fa_bwd_reduce_kernel(const float* __restrict__ partial, __nv_bfl
 
 // ============================================================================ backward: dQ
 // CTA = (query tile, head).  Per key tile: S = Q K^T, dP = dO V^T -> threads: dS (bf16) -> dQ += dS K
-template <int D, bool DROP>
+template <int D, bool DROP, bool F16 = false>
 __global__ void __launch_bounds__(FA_BWD_THREADS, 1)
     fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                      const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
@@ -937,8 +952,8 @@ __global__ void __launch_bounds__(FA_BWD_THREADS, 1)
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      const uint32_t idesc_nt = sb::umma_idesc_f16(TILE, TILE, 1, 0, 0);
-      const uint32_t idesc_acc = sb::umma_idesc_f16(TILE, D, 1, 0, 1);
+      const uint32_t idesc_nt = sb::umma_idesc_f16(TILE, TILE, F16 ? 0 : 1, 0, 0);
+      const uint32_t idesc_acc = sb::umma_idesc_f16(TILE, D, F16 ? 0 : 1, 0, 1);
       const uint32_t q_addr = sb::smem_u32(sQ), do_addr = sb::smem_u32(sdO), k_base = sb::smem_u32(sK),
                      v_base = sb::smem_u32(sV), ds_addr = sb::smem_u32(sdS);
       bool ok = sb::mbar_wait(qdo_full, 0, abort_flag);
@@ -1029,10 +1044,10 @@ __global__ void __launch_bounds__(FA_BWD_THREADS, 1)
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
           uint4 w;
-          w.x = pack_bf16(dsv[g * 8 + 0], dsv[g * 8 + 1]);
-          w.y = pack_bf16(dsv[g * 8 + 2], dsv[g * 8 + 3]);
-          w.z = pack_bf16(dsv[g * 8 + 4], dsv[g * 8 + 5]);
-          w.w = pack_bf16(dsv[g * 8 + 6], dsv[g * 8 + 7]);
+          w.x = pack16<F16>(dsv[g * 8 + 0], dsv[g * 8 + 1]);
+          w.y = pack16<F16>(dsv[g * 8 + 2], dsv[g * 8 + 3]);
+          w.z = pack16<F16>(dsv[g * 8 + 4], dsv[g * 8 + 5]);
+          w.w = pack16<F16>(dsv[g * 8 + 6], dsv[g * 8 + 7]);
           *reinterpret_cast<uint4*>(sdS + swz_offset(r, ch * 32 + g * 8)) = w;
         }
       }
@@ -1053,10 +1068,10 @@ __global__ void __launch_bounds__(FA_BWD_THREADS, 1)
 #pragma unroll
           for (int g = 0; g < 4; ++g) {
             uint4 u;
-            u.x = pack_bf16(__uint_as_float(a[g * 8 + 0]), __uint_as_float(a[g * 8 + 1]));
-            u.y = pack_bf16(__uint_as_float(a[g * 8 + 2]), __uint_as_float(a[g * 8 + 3]));
-            u.z = pack_bf16(__uint_as_float(a[g * 8 + 4]), __uint_as_float(a[g * 8 + 5]));
-            u.w = pack_bf16(__uint_as_float(a[g * 8 + 6]), __uint_as_float(a[g * 8 + 7]));
+            u.x = pack16<F16>(__uint_as_float(a[g * 8 + 0]), __uint_as_float(a[g * 8 + 1]));
+            u.y = pack16<F16>(__uint_as_float(a[g * 8 + 2]), __uint_as_float(a[g * 8 + 3]));
+            u.z = pack16<F16>(__uint_as_float(a[g * 8 + 4]), __uint_as_float(a[g * 8 + 5]));
+            u.w = pack16<F16>(__uint_as_float(a[g * 8 + 6]), __uint_as_float(a[g * 8 + 7]));
             *reinterpret_cast<uint4*>(dq + ch * 32 + g * 8) = u;
           }
         }
@@ -1126,19 +1141,25 @@ int fa_dropout(FaParams* p, float dropout_p, const long long* rng, unsigned call
   return SB_OK;
 }
 
-template <int D, bool DROP, int ROWT>
-int fa_launch_fwd_rowt(dim3 grid, const CUtensorMap& tmQ, const CUtensorMap& tmK, const CUtensorMap& tmV,
+template <int D, bool DROP, int ROWT, bool F16>
+int fa_launch_fwd_type(dim3 grid, const CUtensorMap& tmQ, const CUtensorMap& tmK, const CUtensorMap& tmV,
                        const FaParams& p, cudaStream_t stream) {
   static bool set = false;
   if (!set) {
-    cudaError_t e = cudaFuncSetAttribute(fa_fwd_kernel<D, DROP, ROWT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t e = cudaFuncSetAttribute(fa_fwd_kernel<D, DROP, ROWT, F16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          fa_fwd_smem<D>());
     if (e != cudaSuccess) return (int)e;
     set = true;
   }
-  fa_fwd_kernel<D, DROP, ROWT><<<grid, 64 + 128 * ROWT, fa_fwd_smem<D>(), stream>>>(tmQ, tmK, tmV, p);
+  fa_fwd_kernel<D, DROP, ROWT, F16><<<grid, 64 + 128 * ROWT, fa_fwd_smem<D>(), stream>>>(tmQ, tmK, tmV, p);
   SB_CHECK_LAUNCH();
   return SB_OK;
+}
+template <int D, bool DROP, int ROWT>
+int fa_launch_fwd_rowt(dim3 grid, const CUtensorMap& tmQ, const CUtensorMap& tmK, const CUtensorMap& tmV,
+                       const FaParams& p, cudaStream_t stream) {
+  return p.fp16 ? fa_launch_fwd_type<D, DROP, ROWT, true>(grid, tmQ, tmK, tmV, p, stream)
+                : fa_launch_fwd_type<D, DROP, ROWT, false>(grid, tmQ, tmK, tmV, p, stream);
 }
 template <int D, bool DROP>
 int fa_launch_fwd(dim3 grid, const CUtensorMap& tmQ, const CUtensorMap& tmK, const CUtensorMap& tmV, const FaParams& p,
@@ -1155,23 +1176,32 @@ int fa_launch_fwd(dim3 grid, const CUtensorMap& tmQ, const CUtensorMap& tmK, con
   return fa_launch_fwd_rowt<D, DROP, 2>(grid, tmQ, tmK, tmV, p, stream);
 }
 
-template <int D, bool DROP>
-int fa_launch_bwd(int tiles, int splits, int hps, const CUtensorMap& tmQ, const CUtensorMap& tmK, const CUtensorMap& tmV,
-                  const CUtensorMap& tmdO, const FaParams& p, float* dk_part, float* dv_part, cudaStream_t stream) {
+template <int D, bool DROP, bool F16>
+int fa_launch_bwd_type(int tiles, int splits, int hps, const CUtensorMap& tmQ, const CUtensorMap& tmK,
+                       const CUtensorMap& tmV, const CUtensorMap& tmdO, const FaParams& p, float* dk_part,
+                       float* dv_part, cudaStream_t stream) {
   static bool set = false;
   if (!set) {
-    cudaError_t e = cudaFuncSetAttribute(fa_bwd_dkdv_kernel<D, DROP>, cudaFuncAttributeMaxDynamicSharedMemorySize, fa_dkdv_smem<D>());
+    cudaError_t e = cudaFuncSetAttribute(fa_bwd_dkdv_kernel<D, DROP, F16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         fa_dkdv_smem<D>());
     if (e == cudaSuccess)
-      e = cudaFuncSetAttribute(fa_bwd_dq_kernel<D, DROP>, cudaFuncAttributeMaxDynamicSharedMemorySize, fa_dq_smem<D>());
+      e = cudaFuncSetAttribute(fa_bwd_dq_kernel<D, DROP, F16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               fa_dq_smem<D>());
     if (e != cudaSuccess) return (int)e;
     set = true;
   }
-  fa_bwd_dkdv_kernel<D, DROP><<<dim3(tiles, p.Hkv, splits), FA_BWD_THREADS, fa_dkdv_smem<D>(), stream>>>(
+  fa_bwd_dkdv_kernel<D, DROP, F16><<<dim3(tiles, p.Hkv, splits), FA_BWD_THREADS, fa_dkdv_smem<D>(), stream>>>(
       tmQ, tmK, tmV, tmdO, p, tiles, hps, dk_part, dv_part);
   SB_CHECK_LAUNCH();
-  fa_bwd_dq_kernel<D, DROP><<<dim3(tiles, p.Hq), FA_BWD_THREADS, fa_dq_smem<D>(), stream>>>(tmQ, tmK, tmV, tmdO, p);
+  fa_bwd_dq_kernel<D, DROP, F16><<<dim3(tiles, p.Hq), FA_BWD_THREADS, fa_dq_smem<D>(), stream>>>(tmQ, tmK, tmV, tmdO, p);
   SB_CHECK_LAUNCH();
   return SB_OK;
+}
+template <int D, bool DROP>
+int fa_launch_bwd(int tiles, int splits, int hps, const CUtensorMap& tmQ, const CUtensorMap& tmK, const CUtensorMap& tmV,
+                  const CUtensorMap& tmdO, const FaParams& p, float* dk_part, float* dv_part, cudaStream_t stream) {
+  return p.fp16 ? fa_launch_bwd_type<D, DROP, true>(tiles, splits, hps, tmQ, tmK, tmV, tmdO, p, dk_part, dv_part, stream)
+                : fa_launch_bwd_type<D, DROP, false>(tiles, splits, hps, tmQ, tmK, tmV, tmdO, p, dk_part, dv_part, stream);
 }
 
 }  // namespace
@@ -1200,10 +1230,11 @@ SB_API int sb200_fa_last_driver_error() { return g_fa_last_driver_error; }
 SB_API int sb200_fa_fwd(const void* q, const void* k, const void* v, void* o, float* lse2, const int* doc_start,
                         const int* doc_end, int T, int Hq, int Hkv, int D, long ldq_tok, int ldq_head, long ldk_tok,
                         int ldk_head, long ldv_tok, int ldv_head, int causal, int window, float scale,
-                        float dropout_p, const long long* rng, unsigned int call, int head0, int* status,
+                        float dropout_p, const long long* rng, unsigned int call, int head0, int dtype, int* status,
                         cudaStream_t stream) {
   if (T <= 0 || Hq <= 0) return SB_OK;
   if ((D != 64 && D != 128) || Hkv <= 0 || Hq % Hkv) return SB_ERR_BAD_ARG;
+  if (dtype != SB_DT_BF16 && dtype != SB_DT_F16) return SB_ERR_BAD_ARG;
   if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o)) return SB_ERR_BAD_ARG;
   if ((ldq_tok % 8) || (ldk_tok % 8) || (ldv_tok % 8) || (ldq_head % 8) || (ldk_head % 8) || (ldv_head % 8))
     return SB_ERR_BAD_ARG;
@@ -1217,7 +1248,7 @@ SB_API int sb200_fa_fwd(const void* q, const void* k, const void* v, void* o, fl
   p.scale = scale; p.scale_log2 = scale * 1.4426950408889634f;
   p.doc_start = doc_start; p.doc_end = doc_end;
   p.ldq_head = ldq_head; p.ldk_head = ldk_head; p.ldv_head = ldv_head;
-  p.O = o; p.lse2 = lse2; p.status = status;
+  p.O = o; p.lse2 = lse2; p.status = status; p.fp16 = dtype == SB_DT_F16;
   if ((rc = fa_dropout(&p, dropout_p, rng, call, head0))) return rc;
   dim3 grid((T + TILE - 1) / TILE, Hq);
   if (D == 64) return p.drop_thr8 ? fa_launch_fwd<64, true>(grid, tmQ, tmK, tmV, p, stream)
@@ -1250,9 +1281,10 @@ SB_API int sb200_fa_bwd_strided(const void* q, const void* k, const void* v, con
                                 long ldq_tok, int ldq_head, long ldk_tok, int ldk_head, long ldv_tok, int ldv_head,
                                 long lddq_tok, int lddq_head, long lddk_tok, int lddk_head, long lddv_tok,
                                 int lddv_head, int causal, int window, float scale, float dropout_p,
-                                const long long* rng, unsigned int call, int head0, int* status,
+                                const long long* rng, unsigned int call, int head0, int dtype, int* status,
                                 cudaStream_t stream) {
   if ((lddq_tok | lddq_head | lddk_tok | lddk_head | lddv_tok | lddv_head) & 7) return SB_ERR_BAD_ARG;
+  if (dtype != SB_DT_BF16 && dtype != SB_DT_F16) return SB_ERR_BAD_ARG;
   if (T <= 0 || Hq <= 0) return SB_OK;
   if ((D != 64 && D != 128) || Hkv <= 0 || Hq % Hkv) return SB_ERR_BAD_ARG;
   if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o) || !aligned16(d_o) || !aligned16(dq) ||
@@ -1270,6 +1302,7 @@ SB_API int sb200_fa_bwd_strided(const void* q, const void* k, const void* v, con
   p.doc_start = doc_start; p.doc_end = doc_end;
   p.ldq_head = ldq_head; p.ldk_head = ldk_head; p.ldv_head = ldv_head; p.ldo_head = D;
   p.lse2 = const_cast<float*>(lse2); p.delta = delta; p.dQ = dq; p.dK = dk; p.dV = dv; p.status = status;
+  p.fp16 = dtype == SB_DT_F16;
   p.lddq_tok = lddq_tok; p.lddk_tok = lddk_tok; p.lddv_tok = lddv_tok;
   p.lddq_head = lddq_head; p.lddk_head = lddk_head; p.lddv_head = lddv_head;
   const int tiles = (T + TILE - 1) / TILE;
@@ -1282,10 +1315,15 @@ SB_API int sb200_fa_bwd_strided(const void* q, const void* k, const void* v, con
   {
     const long threads = (long)T * Hq * (D / 8);
     int blocks = (int)((threads + 255) / 256);
-    if (D == 64)
-      fa_bwd_delta_kernel<64><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)o, (const __nv_bfloat16*)d_o, delta, T, Hq);
-    else
-      fa_bwd_delta_kernel<128><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)o, (const __nv_bfloat16*)d_o, delta, T, Hq);
+    const __nv_bfloat16* o16 = (const __nv_bfloat16*)o;  // 16-bit words; the F16 instantiations read them as halves
+    const __nv_bfloat16* do16 = (const __nv_bfloat16*)d_o;
+    if (D == 64) {
+      if (p.fp16) fa_bwd_delta_kernel<64, true><<<blocks, 256, 0, stream>>>(o16, do16, delta, T, Hq);
+      else fa_bwd_delta_kernel<64, false><<<blocks, 256, 0, stream>>>(o16, do16, delta, T, Hq);
+    } else {
+      if (p.fp16) fa_bwd_delta_kernel<128, true><<<blocks, 256, 0, stream>>>(o16, do16, delta, T, Hq);
+      else fa_bwd_delta_kernel<128, false><<<blocks, 256, 0, stream>>>(o16, do16, delta, T, Hq);
+    }
     SB_CHECK_LAUNCH();
   }
   if ((rc = fa_dropout(&p, dropout_p, rng, call, head0))) return rc;
@@ -1299,10 +1337,17 @@ SB_API int sb200_fa_bwd_strided(const void* q, const void* k, const void* v, con
   if (splits > 1) {
     const long n = (long)T * Hkv * D;
     const int blocks = (int)((n / 4 + 255) / 256);
-    fa_bwd_reduce_kernel<<<blocks, 256, 0, stream>>>(dk_part, (__nv_bfloat16*)dk, n, splits, Hkv, D, lddk_tok,
-                                                     lddk_head);
-    fa_bwd_reduce_kernel<<<blocks, 256, 0, stream>>>(dv_part, (__nv_bfloat16*)dv, n, splits, Hkv, D, lddv_tok,
-                                                     lddv_head);
+    if (p.fp16) {
+      fa_bwd_reduce_kernel<true><<<blocks, 256, 0, stream>>>(dk_part, (__nv_bfloat16*)dk, n, splits, Hkv, D, lddk_tok,
+                                                             lddk_head);
+      fa_bwd_reduce_kernel<true><<<blocks, 256, 0, stream>>>(dv_part, (__nv_bfloat16*)dv, n, splits, Hkv, D, lddv_tok,
+                                                             lddv_head);
+    } else {
+      fa_bwd_reduce_kernel<false><<<blocks, 256, 0, stream>>>(dk_part, (__nv_bfloat16*)dk, n, splits, Hkv, D, lddk_tok,
+                                                              lddk_head);
+      fa_bwd_reduce_kernel<false><<<blocks, 256, 0, stream>>>(dv_part, (__nv_bfloat16*)dv, n, splits, Hkv, D, lddv_tok,
+                                                              lddv_head);
+    }
     SB_CHECK_LAUNCH();
   }
   return SB_OK;
@@ -1314,9 +1359,9 @@ SB_API int sb200_fa_bwd(const void* q, const void* k, const void* v, const void*
                         const int* doc_start, const int* doc_end, int T,
                         int Hq, int Hkv, int D, long ldq_tok, int ldq_head, long ldk_tok, int ldk_head, long ldv_tok,
                         int ldv_head, int causal, int window, float scale, float dropout_p, const long long* rng,
-                        unsigned int call, int head0, int* status, cudaStream_t stream) {
+                        unsigned int call, int head0, int dtype, int* status, cudaStream_t stream) {
   return sb200_fa_bwd_strided(q, k, v, o, d_o, lse2, delta, dkv_partial, splits, dq, dk, dv, doc_start, doc_end, T, Hq,
                               Hkv, D, ldq_tok, ldq_head, ldk_tok, ldk_head, ldv_tok, ldv_head, (long)Hq * D, D,
                               (long)Hkv * D, D, (long)Hkv * D, D, causal, window, scale, dropout_p, rng, call, head0,
-                              status, stream);
+                              dtype, status, stream);
 }

@@ -18,7 +18,8 @@ def _declare() -> None:
     global _DECLARED
     if _DECLARED:
         return
-    drop = [c_float, c_void_p, c_uint, c_int]  # dropout probability, device {seed, step}, call index, first head
+    # dropout probability, device {seed, step}, call index, first head; then the element type (SB_DT_BF16 / SB_DT_F16)
+    drop = [c_float, c_void_p, c_uint, c_int, c_int]
     _lib.declare("sb200_fa_fwd", [c_void_p] * 7 + [c_int] * 4 + [c_long, c_int, c_long, c_int, c_long, c_int, c_int,
                                                                  c_int, c_float] + drop + [c_void_p, c_void_p])
     _lib.declare("sb200_fa_bwd_splits", [c_int] * 4)
@@ -79,7 +80,7 @@ class _FlashAttention(torch.autograd.Function):
                                doc_start.data_ptr(), doc_end.data_ptr(), T, Hq, Hkv, D, q.stride(0), q.stride(1),
                                k.stride(0), k.stride(1), v.stride(0), v.stride(1), int(causal),
                                -1 if window is None else int(window), float(scale), dp, _lib.ptr(drng), dcall, dhead,
-                               status_word().data_ptr(), stream()),
+                               _lib.dt(q.dtype), status_word().data_ptr(), stream()),
             "sb200_fa_fwd",
         )
         ctx.save_for_backward(q, k, v, o, lse2, doc_start, doc_end)
@@ -107,7 +108,8 @@ class _FlashAttention(torch.autograd.Function):
                                dv.data_ptr(), doc_start.data_ptr(),
                                doc_end.data_ptr(), T, Hq, Hkv, D, q.stride(0), q.stride(1), k.stride(0), k.stride(1),
                                v.stride(0), v.stride(1), int(causal), -1 if window is None else int(window),
-                               float(scale), dp, _lib.ptr(drng), dcall, dhead, status_word().data_ptr(), stream()),
+                               float(scale), dp, _lib.ptr(drng), dcall, dhead, _lib.dt(q.dtype),
+                               status_word().data_ptr(), stream()),
             "sb200_fa_bwd",
         )
         return dq, dk, dv, None, None, None, None, None, None
@@ -131,11 +133,8 @@ def flash_attention_kernel(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu
                            causal: bool, scale: float, window: Optional[int],
                            ranges: Optional[tuple[torch.Tensor, torch.Tensor]] = None,
                            drop: tuple = NO_DROPOUT) -> torch.Tensor:
-    if q.dtype != torch.bfloat16:
-        # the kernels are bf16; fp16 inputs are converted (same exponent-safe range for attention inputs)
-        out = flash_attention_kernel(q.to(torch.bfloat16), k.to(torch.bfloat16), v.to(torch.bfloat16), cu_seqlens,
-                                     causal, scale, window, ranges, drop)
-        return out.to(q.dtype)
+    assert q.dtype in (torch.bfloat16, torch.float16) and k.dtype == q.dtype and v.dtype == q.dtype, (
+        f"the attention kernels take bf16 or fp16 tensors of one type, got {q.dtype}, {k.dtype}, {v.dtype}")
     start, end = ranges if ranges is not None else doc_ranges(cu_seqlens, q.shape[0])
     _check_ranges(start, end, q.shape[0])
     return _FlashAttention.apply(q, k, v, start, end, causal, scale, window, drop)
@@ -186,7 +185,7 @@ class _PackedQKVAttention(torch.autograd.Function):
             lib().sb200_fa_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse2.data_ptr(),
                                doc_start.data_ptr(), doc_end.data_ptr(), T, H, H, D, H * D3, D3, H * D3, D3, H * D3, D3,
                                int(causal), -1 if window is None else int(window), float(scale), dp, _lib.ptr(drng),
-                               dcall, dhead, status_word().data_ptr(), stream()),
+                               dcall, dhead, _lib.dt(qkv.dtype), status_word().data_ptr(), stream()),
             "sb200_fa_fwd",
         )
         ctx.save_for_backward(qkv, o, lse2, doc_start, doc_end, pos if rot is not None else None)
@@ -215,7 +214,7 @@ class _PackedQKVAttention(torch.autograd.Function):
                                        dk.data_ptr(), dv.data_ptr(), doc_start.data_ptr(), doc_end.data_ptr(), T, H, H,
                                        D, *ld, *ld, *ld, *ld, *ld, *ld, int(causal),
                                        -1 if window is None else int(window), float(scale), dp, _lib.ptr(drng),
-                                       dcall, dhead, status_word().data_ptr(), stream()),
+                                       dcall, dhead, _lib.dt(qkv.dtype), status_word().data_ptr(), stream()),
             "sb200_fa_bwd_strided",
         )
         if rot is not None:

@@ -771,3 +771,32 @@ def test_loss_overwrites_logits_only_when_their_producer_allows_it():
     assert loss2.item() == loss.item()
     assert _rel(base.grad, held.grad) < 1e-3
     assert not torch.equal(temporary.detach(), before)  # its storage now holds the gradient
+
+
+@pytest.mark.parametrize("D", [64, 128])
+def test_flash_attention_in_fp16_keeps_fp16_precision(D):
+    """Half-precision inputs run on half-precision tensor-core operands (P and dS are packed as halves), so the
+    result is as close to the fp32 expression as an fp16 kernel's: within 1e-3 on unit-scale outputs, which the same
+    inputs rounded to bf16 miss."""
+    from scaling_b200.ops.attention import attention_reference, flash_attention
+
+    torch.manual_seed(7)
+    T = 512
+    cu = torch.tensor([0, 200, 512], device=DEV, dtype=torch.int32)
+    q = torch.randn(T, 4, D, device=DEV, dtype=torch.float16, requires_grad=True)
+    k = torch.randn(T, 2, D, device=DEV, dtype=torch.float16, requires_grad=True)
+    v = torch.randn(T, 2, D, device=DEV, dtype=torch.float16, requires_grad=True)
+    out = flash_attention(q, k, v, cu, None, causal=True)
+    assert out.dtype == torch.float16
+    do = torch.randn_like(out)
+    out.backward(do)
+    K.check_status()
+    qr, kr, vr = (t.detach().float().requires_grad_() for t in (q, k, v))
+    ref = attention_reference(qr, kr, vr, cu, None, True, D ** -0.5)
+    ref.backward(do.float())
+    assert (out.float() - ref).abs().max().item() < 2e-3
+    for got, want in ((q.grad, qr.grad), (k.grad, kr.grad), (v.grad, vr.grad)):
+        ok, worst = _rows_close(got.reshape(T, -1), want.reshape(T, -1), 1e-2)
+        assert ok, worst
+    as_bf16 = flash_attention(q.detach().bfloat16(), k.detach().bfloat16(), v.detach().bfloat16(), cu, None, causal=True)
+    assert (as_bf16.float() - ref).abs().max().item() > (out.float() - ref).abs().max().item()
