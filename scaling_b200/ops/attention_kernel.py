@@ -173,7 +173,7 @@ class _PackedQKVAttention(torch.autograd.Function):
         dp, drng, dcall, dhead = drop
         T, H, D3 = qkv.shape
         D = D3 // 3
-        assert qkv.is_contiguous() and qkv.dtype == torch.bfloat16
+        assert qkv.is_contiguous() and qkv.dtype in (torch.bfloat16, torch.float16)
         if rot is not None:
             rot_dim, base, interleaved = rot
             check(lib().sb200_rope_multi(qkv.data_ptr(), pos.data_ptr(), T, H, rot_dim, H * D3, D3, 2, D, float(base),
@@ -226,7 +226,7 @@ class _PackedQKVAttention(torch.autograd.Function):
 
 def packed_qkv_supported(qkv: torch.Tensor) -> bool:
     """True when ``packed_qkv_attention`` can run on ``qkv[T, heads, 3 * d]``."""
-    return (qkv.is_cuda and qkv.dtype == torch.bfloat16 and qkv.dim() == 3 and qkv.shape[-1] % 3 == 0
+    return (qkv.is_cuda and qkv.dtype in (torch.bfloat16, torch.float16) and qkv.dim() == 3 and qkv.shape[-1] % 3 == 0
             and qkv.shape[-1] // 3 in (64, 128) and qkv.is_contiguous() and _lib.lib_has("sb200_fa_bwd_strided"))
 
 

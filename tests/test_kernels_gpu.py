@@ -378,13 +378,14 @@ def test_flash_attention(T, Hq, Hkv, D, cu, causal, window):
     (4352, 12, 64, [0, 2048, 4352], None, 64, False),   # enough heads x tiles to take the split dK/dV path
     (512, 3, 64, [0, 512], 100, None, False),
 ])
-def test_packed_qkv_attention(T, H, D, cu, window, rot, interleaved):
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_packed_qkv_attention(T, H, D, cu, window, rot, interleaved, dtype):
     """Fused rotary + attention on a packed [T, H, 3D] projection against rope + attention on separate tensors."""
     from scaling_b200.ops.attention import attention_reference
     from scaling_b200.ops.attention_kernel import packed_qkv_attention, packed_qkv_supported
 
     torch.manual_seed(12)
-    src = torch.randn(T, H, 3 * D, device=DEV, dtype=torch.bfloat16)
+    src = torch.randn(T, H, 3 * D, device=DEV, dtype=dtype)
     cu_t = torch.tensor(cu, device=DEV, dtype=torch.int32)
     pos = torch.cat([torch.arange(b - a, device=DEV, dtype=torch.int32) for a, b in zip(cu[:-1], cu[1:])])
     scale = D ** -0.5
